@@ -1,0 +1,257 @@
+/*
+ * sanic_b200 — C ABI of the B200 (sm_100a) backend for sanic's derived carriers.
+ *
+ * This is the drop-in boundary: what a `Backend` implementation on the reference
+ * side (src/compile.rs:87-108) binds instead of src/emit_metal.rs + src/metal.rs.
+ * Every entry point is `extern "C"`, takes plain pointers and sizes, returns an
+ * int32 status (0 = OK), never throws and never aborts. `sanic_last_error(ctx)`
+ * gives the text of the last failure on that context.
+ *
+ * All device pointers are CUdeviceptr-compatible addresses in the context's
+ * device. All work is enqueued on the caller's stream (a cudaStream_t passed as
+ * void*; NULL = the default stream). One context per device per process; calls
+ * on one context are not thread-safe.
+ *
+ * Paths cited below are relative to the reference project.
+ */
+#ifndef SANIC_B200_H
+#define SANIC_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct sanic_ctx sanic_ctx;
+
+/* Status codes. RunError / CompileError of src/compile.rs:18-78 map onto these. */
+enum {
+    SANIC_OK = 0,
+    SANIC_ERR_INVALID = 1,      /* CompileError::InvalidInput / RunError::Shape: bad argument */
+    SANIC_ERR_CUDA = 2,         /* RunError::Backend: a CUDA call failed */
+    SANIC_ERR_UNSUPPORTED = 3,  /* CompileError::Backend: no kernel for this carrier structure */
+    SANIC_ERR_TIMEOUT = 4,      /* a bounded device-side wait ran out */
+    SANIC_ERR_NCCL = 5,
+    SANIC_ERR_DTYPE = 6,        /* RunError::Dtype */
+    SANIC_ERR_NOMEM = 7
+};
+
+/* Storage widths (src/scalar.rs:181-201). */
+enum { SANIC_F32 = 1, SANIC_F16 = 2, SANIC_BF16 = 3, SANIC_U32 = 4, SANIC_I4 = 5 };
+
+/* ── context and memory: replaces MetalDevice open/alloc/read (src/metal.rs:149-490) ── */
+int32_t sanic_cuda_open(int32_t ordinal, sanic_ctx** out);
+int32_t sanic_cuda_close(sanic_ctx* ctx);
+const char* sanic_last_error(sanic_ctx* ctx);
+const char* sanic_version(void);
+
+/* Hardware facts only, as Backend::specs (src/compile.rs:91-93, src/cost.rs:33-60). */
+typedef struct {
+    int32_t sm_count;
+    int32_t cc_major, cc_minor;
+    int32_t max_smem_per_block;
+    int32_t l2_bytes;
+    int32_t warp;            /* SIMD width (src/plan.rs:458) */
+    uint64_t hbm_bytes;
+    double hbm_gbs_nominal;
+    double bf16_tflops_nominal;
+} sanic_device_specs;
+int32_t sanic_specs(sanic_ctx* ctx, sanic_device_specs* out);
+
+int32_t sanic_alloc(sanic_ctx* ctx, size_t bytes, void** dptr);
+int32_t sanic_free(sanic_ctx* ctx, void* dptr);
+int32_t sanic_upload(sanic_ctx* ctx, void* dst_dev, const void* src_host, size_t bytes, void* stream);
+int32_t sanic_download(sanic_ctx* ctx, void* dst_host, const void* src_dev, size_t bytes, void* stream);
+int32_t sanic_memset(sanic_ctx* ctx, void* dptr, int32_t byte, size_t bytes, void* stream);
+int32_t sanic_sync(sanic_ctx* ctx, void* stream);
+
+/* ── carrier structure: what the emitter keys kernel choice on (src/derive.rs:519-530) ── */
+enum { SANIC_SLOT_PLAIN_ADD = 1, SANIC_SLOT_PLAIN_MAX = 2, SANIC_SLOT_PLAIN_MIN = 3,
+       SANIC_SLOT_EXP_SHIFTED = 4, SANIC_SLOT_AT_EXTREMUM = 5 };
+typedef struct {
+    int32_t n_slots;
+    int32_t kind[4];      /* SANIC_SLOT_* */
+    int32_t ref[4];       /* max_slot (EXP_SHIFTED) or key_slot (AT_EXTREMUM) */
+    int32_t leaf_dtype;   /* storage of the streamed leaf: SANIC_F32 / SANIC_BF16 / SANIC_I4 */
+    int32_t in_body_contraction; /* 1 when a leaf is itself a contraction (QK^T in the fold body) */
+    int32_t deferred_div; /* 1 when project divides by a function of another slot (defer-div) */
+} sanic_carrier_desc;
+/* Kernel families the emitter can select (the K1..K4 rows of src/emit_metal.rs). */
+enum { SANIC_KERNEL_NONE = 0, SANIC_KERNEL_ONLINE_SOFTMAX_FOLD = 1, SANIC_KERNEL_DEFERRED_NORM_CONTRACTION = 2,
+       SANIC_KERNEL_PLAIN_CONTRACTION = 3, SANIC_KERNEL_GROUPED_I4_CONTRACTION = 4, SANIC_KERNEL_EXTREMUM_INDEX = 5 };
+/* Maps a carrier to a kernel family by slot kinds and leaves only, never by an
+ * operation name (the layering rule of tests/structure.rs:153-203; the analogue of
+ * the structural matching in src/emit_metal.rs:457-505). SANIC_ERR_UNSUPPORTED if none. */
+int32_t sanic_emit_select(const sanic_carrier_desc* carrier, int32_t* kernel_family);
+
+/* ── K2a: online-softmax fold (m, l, o) — replaces the cooperative fold kernel the
+ *    Metal emitter generates for this carrier (src/emit_metal.rs:760-1101) ── */
+typedef struct {
+    const void* q; const void* k; const void* v; void* out;
+    int32_t batch, q_heads, kv_heads;      /* q head h reads kv head h / (q_heads/kv_heads) (src/nn.rs:107-151) */
+    int32_t q_len, kv_len, head_dim, v_dim;
+    int32_t causal;                        /* where(i < j, -1e30, 0) (src/ir.rs:1511-1526) */
+    int32_t window;                        /* 0 = none; else query s sees keys s-window+1..s (tests/movement.rs:294-345) */
+    float scale;
+    const float* mask;                     /* optional additive mask [q_len, kv_len] (f32 path only) */
+    int32_t out_dtype;                     /* SANIC_F32 or SANIC_BF16 */
+} sanic_attn_params;
+/* f32 storage, f32 CUDA-core arithmetic: q [B,Hq,L,E], k [B,Hkv,S,E], v [B,Hkv,S,Ev], out [B,Hq,L,Ev]. */
+int32_t sanic_attn_fwd_f32(sanic_ctx* ctx, const sanic_attn_params* p, void* stream);
+/* bf16 storage, tensor-core contractions, f32 carrier in registers. E = Ev in {64, 128}. */
+int32_t sanic_attn_fwd_bf16(sanic_ctx* ctx, const sanic_attn_params* p, void* stream);
+
+/* Split-KV decode (one query token per sequence). Stage 1 folds contiguous chunks of
+ * the key axis into raw (m, l, o) accumulators exactly as run_carrier_split chunks it
+ * (src/interp.rs:597-631); stage 2 merges them with the derived combine
+ * (src/derive.rs:1700-1713) and either projects o/l or exports the merged carrier. */
+typedef struct {
+    const void* q;            /* [B, Hq, D] bf16 */
+    const void* k;            /* bf16; element strides below; head_dim contiguous */
+    const void* v;            /* bf16; v_transposed=0: [.., seq, D] ; 1: [.., D, seq] (examples/llama3_2.rs:160-173) */
+    int64_t k_batch_stride, k_head_stride, k_seq_stride;
+    int64_t v_batch_stride, v_head_stride, v_row_stride;  /* row = seq (v_transposed=0) or dim (1) */
+    int32_t v_transposed;
+    int32_t batch, q_heads, kv_heads, head_dim;
+    int32_t kv_len;           /* visible prefix length when kv_len_dev is NULL */
+    const int32_t* kv_len_dev;/* optional: device scalar holding position; visible length = *kv_len_dev + 1 */
+    int32_t window;           /* 0 = none */
+    int32_t n_splits;         /* chunks of the key axis per (batch, kv head) */
+    float scale;
+    float* partials;          /* scratch [B*Hq, n_splits, 2 + D] f32 (raw accumulators) */
+    float* carrier_out;       /* optional [B*Hq, 2 + D] f32: merged raw accumulator (m natural-log units, l, o) */
+    void* out;                /* optional projected output [B, Hq, D] */
+    int32_t out_dtype;        /* SANIC_F32 or SANIC_BF16 */
+} sanic_decode_params;
+int32_t sanic_attn_decode_splitkv(sanic_ctx* ctx, const sanic_decode_params* p, void* stream);
+size_t sanic_attn_decode_scratch_bytes(int32_t batch, int32_t q_heads, int32_t head_dim, int32_t n_splits);
+/* Suggested number of chunks for this device and shape (a multiple of the SM count in CTAs). */
+int32_t sanic_attn_decode_suggest_splits(sanic_ctx* ctx, int32_t batch, int32_t kv_heads, int32_t head_dim, int64_t kv_len);
+
+/* Stage 2 alone: merge n_parts raw accumulators [n_parts, rows, 2+D] left to right and
+ * project. This is the cross-device merge of interp::run_carrier_split (src/interp.rs:632-639). */
+int32_t sanic_carrier_merge(sanic_ctx* ctx, const float* parts, int32_t n_parts, int32_t rows, int32_t head_dim,
+                            float* carrier_out, void* out, int32_t out_dtype, void* stream);
+
+/* ── K2b: deferred-normaliser contraction (RMSNorm-fused GEMM), tcgen05 + TMA.
+ *    y = (sum_k x*g*W) / sqrt(sum_k x^2 / K + eps)  (tests/laws.rs:620-646, src/partition.rs:2591-2608) ── */
+typedef struct {
+    const void* x;      /* [M, K] bf16 */
+    const void* gamma;  /* [K] bf16 */
+    const void* w;      /* w_is_nk=1: [N, K] (checkpoint-native [out,in], examples/llama3_2.rs:85-90); 0: [K, N] */
+    void* y;            /* [M, N] */
+    int32_t M, N, K;
+    int32_t w_is_nk;
+    float eps;
+    int32_t out_dtype;  /* SANIC_BF16 or SANIC_F32 */
+} sanic_gemm_rmsnorm_params;
+int32_t sanic_gemm_rmsnorm(sanic_ctx* ctx, const sanic_gemm_rmsnorm_params* p, void* stream);
+
+/* ── K2c / plain contraction at decode batch sizes: y[b,o] = sum_k x[b,k] * W[o,k].
+ *    Weights bf16, or int4 nibbles (q+8, low nibble = even element, src/emit_metal.rs:179-181)
+ *    with a bf16 scale per `group` inputs (tests/metal.rs:1224-1236). Up to three weight
+ *    segments share one launch (q/k/v projections); a segment pair can be combined as
+ *    silu(a)*b (src/ir.rs:1500-1509); the result can be added to a residual. ── */
+enum { SANIC_EPI_STORE = 0, SANIC_EPI_RESIDUAL_ADD = 1, SANIC_EPI_SILU_MUL = 2 };
+typedef struct {
+    const void* x;            /* [batch, K] bf16 activations */
+    int32_t batch, K;
+    int32_t weight_dtype;     /* SANIC_BF16 or SANIC_I4 */
+    int32_t group;            /* int4 group size along K (64) */
+    int32_t n_segments;       /* 1..3 */
+    const void* w[3];         /* [rows_i, K] bf16 or [rows_i, K/2] bytes */
+    const void* scales[3];    /* [rows_i, K/group] bf16 (int4 only) */
+    int32_t rows[3];
+    void* out[3];             /* [batch, rows_i] */
+    int32_t out_dtype;        /* SANIC_F32 or SANIC_BF16 */
+    int32_t epilogue;         /* SANIC_EPI_* ; SILU_MUL needs n_segments == 2 with equal rows, result in out[0] */
+    const float* residual;    /* [batch, rows_0] f32 for RESIDUAL_ADD (may alias out[0] when out is f32) */
+} sanic_gemv_params;
+int32_t sanic_gemv(sanic_ctx* ctx, const sanic_gemv_params* p, void* stream);
+
+/* ── K2d: extremal-key payload fold (first-max index), u32 saturating store
+ *    (src/derive.rs:1714-1735, src/emit_metal.rs:186-190) ── */
+int32_t sanic_argmax(sanic_ctx* ctx, const float* x, int32_t rows, int32_t n, uint32_t* out_index,
+                     float* scratch /* >= rows*2*256 floats */, void* stream);
+
+/* ── K3: pointwise stages (src/emit_metal.rs:1118-1178) ── */
+/* xn = bf16((x * g) / sqrt(mean(x^2) + eps)) for rows of f32 x (src/nn.rs:165-169). */
+int32_t sanic_rmsnorm(sanic_ctx* ctx, const float* x, const void* gamma_bf16, int32_t rows, int32_t n, float eps,
+                      void* out_bf16, void* stream);
+/* Embedding gather: out[b,:] = widen(table[token[b],:]) (Stage::Gather, src/partition.rs:2938-2946). */
+int32_t sanic_embed_gather(sanic_ctx* ctx, const void* table_bf16, const int32_t* tokens, int32_t batch, int32_t hidden,
+                           int32_t vocab, float* out, void* stream);
+/* cos/sin table for RoPE: table[pos][f] = (cos(pos*inv_freq[f]), sin(pos*inv_freq[f])), angles and
+ * sincos evaluated in f64 on the device, stored f32. inv_freq is a HOST array of n_freq doubles: the
+ * schedule (plain theta^(-i/F) of src/nn.rs:197-199, or the llama3 blend of examples/llama3_2.rs:95-107)
+ * is the caller's policy, as in the reference. */
+int32_t sanic_rope_table(sanic_ctx* ctx, const double* inv_freq_host, int32_t n_freq, int32_t n_pos, float* table,
+                         void* stream);
+/* Rotate-half RoPE (src/nn.rs:176-194) on bf16 rows [rows, seq, D] with position = pos0 + s; in place allowed. */
+int32_t sanic_rope_bf16(sanic_ctx* ctx, const void* x, void* out, int64_t rows, int32_t seq, int32_t head_dim,
+                        const float* table, int32_t pos0, void* stream);
+/* Decode-step RoPE + in-place cache row write (src/nn.rs:208-212, src/graph.rs:127-160):
+ * qkv f32 [B, (Hq+2*Hkv)*D] -> q_out bf16 [B,Hq,D] (roped), K cache [B,Hkv,ctx,D] row pos <- bf16(rope(k)),
+ * V cache [B,Hkv,D,ctx] column pos <- bf16(v). Position read from the device scalar. */
+typedef struct {
+    const float* q; const float* k; const float* v;   /* [B, Hq*D], [B, Hkv*D], [B, Hkv*D] f32 */
+    void* q_out; void* k_cache; void* v_cache;
+    const float* table;         /* [ctx][D/2][2] from sanic_rope_table */
+    const int32_t* position;    /* device scalar */
+    int32_t batch, q_heads, kv_heads, head_dim, ctx;
+} sanic_rope_cache_params;
+int32_t sanic_rope_cache_write(sanic_ctx* ctx, const sanic_rope_cache_params* p, void* stream);
+/* position += 1 on the device, so a captured step replays without host writes. */
+int32_t sanic_advance_position(sanic_ctx* ctx, int32_t* position, void* stream);
+
+/* ── K4: typed load/store helpers exposed for bit-exactness tests (src/emit_metal.rs:123-232) ── */
+int32_t sanic_round_to_bf16(sanic_ctx* ctx, const float* x, size_t n, uint16_t* out_bits, void* stream);
+int32_t sanic_store_u32_saturating(sanic_ctx* ctx, const float* x, size_t n, uint32_t* out, void* stream);
+int32_t sanic_w4_unpack(sanic_ctx* ctx, const uint8_t* packed, size_t n_elems, float* out, void* stream);
+
+/* ── stateful stepping: Graph::compile_for / StepProgram::instantiate / Machine::step
+ *    (src/graph.rs:231-356) with capture/replay (src/compile.rs:820-1035, src/metal.rs:634-705) ── */
+typedef struct sanic_program sanic_program;
+enum { SANIC_STAGE_FUSED = 1, SANIC_STAGE_ELEMENTWISE = 2, SANIC_STAGE_GATHER = 3 };  /* src/partition.rs:44-98 */
+enum { SANIC_OP_GEMV = 1, SANIC_OP_DECODE_ATTN = 2, SANIC_OP_ARGMAX = 3, SANIC_OP_RMSNORM = 4, SANIC_OP_EMBED = 5,
+       SANIC_OP_ROPE_CACHE = 6, SANIC_OP_ADVANCE = 7 };
+typedef struct {
+    int32_t stage_kind;          /* SANIC_STAGE_* */
+    int32_t op;                  /* SANIC_OP_* */
+    sanic_carrier_desc carrier;  /* for FUSED stages: checked against the op by sanic_emit_select */
+    union {
+        sanic_gemv_params gemv;
+        sanic_decode_params decode;
+        struct { const float* x; int32_t rows, n; uint32_t* out; float* scratch; } argmax;
+        struct { const float* x; const void* gamma; int32_t rows, n; float eps; void* out; } rmsnorm;
+        struct { const void* table; const int32_t* tokens; int32_t batch, hidden, vocab; float* out; } embed;
+        sanic_rope_cache_params rope_cache;
+        struct { int32_t* position; } advance;
+    } u;
+} sanic_stage_desc;
+int32_t sanic_program_create(sanic_ctx* ctx, const sanic_stage_desc* stages, int32_t n_stages, sanic_program** out);
+int32_t sanic_program_destroy(sanic_program* prog);
+int32_t sanic_program_kernel_count(sanic_program* prog);
+/* Launch every stage in order on `stream` (Backend::execute, src/compile.rs:101-107). */
+int32_t sanic_program_run(sanic_program* prog, void* stream);
+/* Freeze the launch list into a CUDA graph (MetalDevice::capture) and replay it
+ * (MetalReplay::step_timed): gpu_seconds (optional) is the device time of this replay. */
+int32_t sanic_program_capture(sanic_program* prog, void* stream);
+int32_t sanic_program_step(sanic_program* prog, void* stream, double* gpu_seconds);
+
+/* ── multi-device split-KV: each device folds its slice of the key axis, the carriers are
+ *    exchanged and merged with the derived combine (src/interp.rs:538-554) ── */
+int32_t sanic_nccl_unique_id(uint8_t out_id[128]);
+int32_t sanic_nccl_init(sanic_ctx* ctx, int32_t rank, int32_t nranks, const uint8_t id[128]);
+int32_t sanic_nccl_shutdown(sanic_ctx* ctx);
+/* Runs the local split-KV fold (p->carrier_out must be set, p->out ignored), all-gathers the
+ * [rows, 2+D] carriers into `gathered` [nranks, rows, 2+D] and merges them into `out` on every rank. */
+int32_t sanic_splitkv_decode_step(sanic_ctx* ctx, const sanic_decode_params* p, float* gathered, void* out,
+                                  int32_t out_dtype, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SANIC_B200_H */

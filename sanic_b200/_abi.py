@@ -1,0 +1,155 @@
+"""ctypes declarations of include/sanic_b200.h.
+
+The library is required: importing this module raises if libsanic_b200.so has not been
+built. There is no CPU fallback behind any of these entry points.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libsanic_b200.so")
+
+OK, ERR_INVALID, ERR_CUDA, ERR_UNSUPPORTED, ERR_TIMEOUT, ERR_NCCL, ERR_DTYPE, ERR_NOMEM = range(8)
+F32, F16, BF16, U32, I4 = 1, 2, 3, 4, 5
+SLOT_PLAIN_ADD, SLOT_PLAIN_MAX, SLOT_PLAIN_MIN, SLOT_EXP_SHIFTED, SLOT_AT_EXTREMUM = 1, 2, 3, 4, 5
+KERNEL_NONE, KERNEL_ONLINE_SOFTMAX_FOLD, KERNEL_DEFERRED_NORM_CONTRACTION, KERNEL_PLAIN_CONTRACTION, \
+    KERNEL_GROUPED_I4_CONTRACTION, KERNEL_EXTREMUM_INDEX = range(6)
+EPI_STORE, EPI_RESIDUAL_ADD, EPI_SILU_MUL = 0, 1, 2
+STAGE_FUSED, STAGE_ELEMENTWISE, STAGE_GATHER = 1, 2, 3
+OP_GEMV, OP_DECODE_ATTN, OP_ARGMAX, OP_RMSNORM, OP_EMBED, OP_ROPE_CACHE, OP_ADVANCE = 1, 2, 3, 4, 5, 6, 7
+
+vp, i32, i64, f32 = C.c_void_p, C.c_int32, C.c_int64, C.c_float
+
+
+class DeviceSpecs(C.Structure):
+    _fields_ = [("sm_count", i32), ("cc_major", i32), ("cc_minor", i32), ("max_smem_per_block", i32), ("l2_bytes", i32),
+                ("warp", i32), ("hbm_bytes", C.c_uint64), ("hbm_gbs_nominal", C.c_double),
+                ("bf16_tflops_nominal", C.c_double)]
+
+
+class CarrierDesc(C.Structure):
+    _fields_ = [("n_slots", i32), ("kind", i32 * 4), ("ref", i32 * 4), ("leaf_dtype", i32),
+                ("in_body_contraction", i32), ("deferred_div", i32)]
+
+
+class AttnParams(C.Structure):
+    _fields_ = [("q", vp), ("k", vp), ("v", vp), ("out", vp), ("batch", i32), ("q_heads", i32), ("kv_heads", i32),
+                ("q_len", i32), ("kv_len", i32), ("head_dim", i32), ("v_dim", i32), ("causal", i32), ("window", i32),
+                ("scale", f32), ("mask", vp), ("out_dtype", i32)]
+
+
+class DecodeParams(C.Structure):
+    _fields_ = [("q", vp), ("k", vp), ("v", vp),
+                ("k_batch_stride", i64), ("k_head_stride", i64), ("k_seq_stride", i64),
+                ("v_batch_stride", i64), ("v_head_stride", i64), ("v_row_stride", i64),
+                ("v_transposed", i32), ("batch", i32), ("q_heads", i32), ("kv_heads", i32), ("head_dim", i32),
+                ("kv_len", i32), ("kv_len_dev", vp), ("window", i32), ("n_splits", i32), ("scale", f32),
+                ("partials", vp), ("carrier_out", vp), ("out", vp), ("out_dtype", i32)]
+
+
+class GemmRmsnormParams(C.Structure):
+    _fields_ = [("x", vp), ("gamma", vp), ("w", vp), ("y", vp), ("M", i32), ("N", i32), ("K", i32), ("w_is_nk", i32),
+                ("eps", f32), ("out_dtype", i32)]
+
+
+class GemvParams(C.Structure):
+    _fields_ = [("x", vp), ("batch", i32), ("K", i32), ("weight_dtype", i32), ("group", i32), ("n_segments", i32),
+                ("w", vp * 3), ("scales", vp * 3), ("rows", i32 * 3), ("out", vp * 3), ("out_dtype", i32),
+                ("epilogue", i32), ("residual", vp)]
+
+
+class RopeCacheParams(C.Structure):
+    _fields_ = [("q", vp), ("k", vp), ("v", vp), ("q_out", vp), ("k_cache", vp), ("v_cache", vp), ("table", vp),
+                ("position", vp), ("batch", i32), ("q_heads", i32), ("kv_heads", i32), ("head_dim", i32), ("ctx", i32)]
+
+
+class _ArgmaxStage(C.Structure):
+    _fields_ = [("x", vp), ("rows", i32), ("n", i32), ("out", vp), ("scratch", vp)]
+
+
+class _RmsnormStage(C.Structure):
+    _fields_ = [("x", vp), ("gamma", vp), ("rows", i32), ("n", i32), ("eps", f32), ("out", vp)]
+
+
+class _EmbedStage(C.Structure):
+    _fields_ = [("table", vp), ("tokens", vp), ("batch", i32), ("hidden", i32), ("vocab", i32), ("out", vp)]
+
+
+class _AdvanceStage(C.Structure):
+    _fields_ = [("position", vp)]
+
+
+class _StageUnion(C.Union):
+    _fields_ = [("gemv", GemvParams), ("decode", DecodeParams), ("argmax", _ArgmaxStage), ("rmsnorm", _RmsnormStage),
+                ("embed", _EmbedStage), ("rope_cache", RopeCacheParams), ("advance", _AdvanceStage)]
+
+
+class StageDesc(C.Structure):
+    _fields_ = [("stage_kind", i32), ("op", i32), ("carrier", CarrierDesc), ("u", _StageUnion)]
+
+
+# name -> (restype, argtypes); every symbol the header declares
+PROTOTYPES = {
+    "sanic_cuda_open": (i32, [i32, C.POINTER(vp)]),
+    "sanic_cuda_close": (i32, [vp]),
+    "sanic_last_error": (C.c_char_p, [vp]),
+    "sanic_version": (C.c_char_p, []),
+    "sanic_specs": (i32, [vp, C.POINTER(DeviceSpecs)]),
+    "sanic_alloc": (i32, [vp, C.c_size_t, C.POINTER(vp)]),
+    "sanic_free": (i32, [vp, vp]),
+    "sanic_upload": (i32, [vp, vp, vp, C.c_size_t, vp]),
+    "sanic_download": (i32, [vp, vp, vp, C.c_size_t, vp]),
+    "sanic_memset": (i32, [vp, vp, i32, C.c_size_t, vp]),
+    "sanic_sync": (i32, [vp, vp]),
+    "sanic_emit_select": (i32, [C.POINTER(CarrierDesc), C.POINTER(i32)]),
+    "sanic_attn_fwd_f32": (i32, [vp, C.POINTER(AttnParams), vp]),
+    "sanic_attn_fwd_bf16": (i32, [vp, C.POINTER(AttnParams), vp]),
+    "sanic_attn_decode_splitkv": (i32, [vp, C.POINTER(DecodeParams), vp]),
+    "sanic_attn_decode_scratch_bytes": (C.c_size_t, [i32, i32, i32, i32]),
+    "sanic_attn_decode_suggest_splits": (i32, [vp, i32, i32, i32, i64]),
+    "sanic_carrier_merge": (i32, [vp, vp, i32, i32, i32, vp, vp, i32, vp]),
+    "sanic_gemm_rmsnorm": (i32, [vp, C.POINTER(GemmRmsnormParams), vp]),
+    "sanic_gemv": (i32, [vp, C.POINTER(GemvParams), vp]),
+    "sanic_argmax": (i32, [vp, vp, i32, i32, vp, vp, vp]),
+    "sanic_rmsnorm": (i32, [vp, vp, vp, i32, i32, f32, vp, vp]),
+    "sanic_embed_gather": (i32, [vp, vp, vp, i32, i32, i32, vp, vp]),
+    "sanic_rope_table": (i32, [vp, C.POINTER(C.c_double), i32, i32, vp, vp]),
+    "sanic_rope_bf16": (i32, [vp, vp, vp, i64, i32, i32, vp, i32, vp]),
+    "sanic_rope_cache_write": (i32, [vp, C.POINTER(RopeCacheParams), vp]),
+    "sanic_advance_position": (i32, [vp, vp, vp]),
+    "sanic_round_to_bf16": (i32, [vp, vp, C.c_size_t, vp, vp]),
+    "sanic_store_u32_saturating": (i32, [vp, vp, C.c_size_t, vp, vp]),
+    "sanic_w4_unpack": (i32, [vp, vp, C.c_size_t, vp, vp]),
+    "sanic_program_create": (i32, [vp, C.POINTER(StageDesc), i32, C.POINTER(vp)]),
+    "sanic_program_destroy": (i32, [vp]),
+    "sanic_program_kernel_count": (i32, [vp]),
+    "sanic_program_run": (i32, [vp, vp]),
+    "sanic_program_capture": (i32, [vp, vp]),
+    "sanic_program_step": (i32, [vp, vp, C.POINTER(C.c_double)]),
+    "sanic_nccl_unique_id": (i32, [C.POINTER(C.c_uint8)]),
+    "sanic_nccl_init": (i32, [vp, i32, i32, C.POINTER(C.c_uint8)]),
+    "sanic_nccl_shutdown": (i32, [vp]),
+    "sanic_splitkv_decode_step": (i32, [vp, C.POINTER(DecodeParams), vp, vp, i32, vp]),
+}
+
+_lib = None
+
+
+def load():
+    """Load libsanic_b200.so and declare every prototype. Raises if the library is missing."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(
+            f"{LIB_PATH} is missing: build it with `python -m sanic_b200.build`. "
+            "sanic_b200 has no CPU fallback and cannot run without its CUDA library.")
+    lib = C.CDLL(LIB_PATH, mode=C.RTLD_GLOBAL)
+    for name, (res, args) in PROTOTYPES.items():
+        fn = getattr(lib, name)  # AttributeError if the library does not export a declared symbol
+        fn.restype = res
+        fn.argtypes = args
+    _lib = lib
+    return lib

@@ -1,0 +1,113 @@
+// Online-softmax fold in f32 storage and f32 CUDA-core arithmetic.
+//
+// One warp per query row. The key axis is streamed lane-split (lane j takes keys
+// j, j+32, ...); each lane keeps its own (m, l, o[Ev]) accumulator in registers and
+// the 32 lane accumulators are merged with a shuffle butterfly that applies the
+// carrier's own combine, the -inf guard included (reference src/derive.rs:1700-1713).
+// This is the lane_stream schedule of the reference's cooperative fold
+// (src/emit_metal.rs:760-1101, src/plan.rs:434-455), written for 32-wide warps.
+//
+// A tensor-core TF32 contraction has a 10-bit mantissa and cannot hold the 1e-5
+// relative bound this path is checked at, so the contraction runs as FP32 FMAs and
+// exp / division are the full-precision library routines.
+#include "common.cuh"
+
+namespace {
+using namespace sanic;
+
+template <int DV>
+__global__ void __launch_bounds__(128) attn_fwd_f32_kernel(sanic_attn_params p) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int row = blockIdx.x * 4 + warp;
+    const int bh = blockIdx.y;
+    const int b = bh / p.q_heads, h = bh % p.q_heads;
+    const int hk = h / (p.q_heads / p.kv_heads);
+    const int E = p.head_dim, Ev = p.v_dim, S = p.kv_len, L = p.q_len;
+
+    extern __shared__ float smem[];
+    float* qs = smem + warp * E;
+    const float* Q = (const float*)p.q + ((size_t)bh * L + (row < L ? row : 0)) * E;
+    for (int d = lane; d < E; d += 32) qs[d] = Q[d];
+    __syncwarp();
+    if (row >= L) return;
+
+    const float* K = (const float*)p.k + ((size_t)(b * p.kv_heads + hk) * S) * E;
+    const float* V = (const float*)p.v + ((size_t)(b * p.kv_heads + hk) * S) * Ev;
+
+    // Visible key range. A causal / window prefix mask contributes exact zeros outside
+    // it, so stopping the stream at the edge is bit-identical (src/emit_metal.rs:442-456).
+    int lo = 0, hi = S;
+    if (p.causal) hi = min(S, row + 1);
+    if (p.window > 0) { hi = min(S, row + 1); lo = max(0, row - p.window + 1); }
+
+    float m = -INFINITY, l = 0.0f;
+    float o[DV];
+#pragma unroll
+    for (int e = 0; e < DV; ++e) o[e] = 0.0f;
+
+    for (int j = lo + lane; j < hi; j += 32) {
+        const float4* kr = (const float4*)(K + (size_t)j * E);
+        float s = 0.0f;
+        for (int d4 = 0; d4 < E / 4; ++d4) {
+            float4 kv = kr[d4];
+            s = fmaf(qs[4 * d4 + 0], kv.x, s);
+            s = fmaf(qs[4 * d4 + 1], kv.y, s);
+            s = fmaf(qs[4 * d4 + 2], kv.z, s);
+            s = fmaf(qs[4 * d4 + 3], kv.w, s);
+        }
+        for (int d = E & ~3; d < E; ++d) s = fmaf(qs[d], K[(size_t)j * E + d], s);
+        s *= p.scale;
+        if (p.mask) s += p.mask[(size_t)row * S + j];
+        // element lift (s, 1, v) combined into the running accumulator
+        float mn = fmaxf(m, s);
+        float ra = (m > -INFINITY) ? expf(m - mn) : 0.0f;
+        float rb = (s > -INFINITY) ? expf(s - mn) : 0.0f;
+        l = l * ra + rb;
+        const float* vr = V + (size_t)j * Ev;
+#pragma unroll
+        for (int e = 0; e < DV; ++e)
+            if (e < Ev) o[e] = o[e] * ra + rb * vr[e];
+        m = mn;
+    }
+    // butterfly merge of the lane accumulators with the derived combine
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+        float mo = __shfl_xor_sync(0xffffffffu, m, off);
+        float lo_ = __shfl_xor_sync(0xffffffffu, l, off);
+        MloScale sc = mlo_rescale(m, mo);
+        l = l * sc.ra + lo_ * sc.rb;
+#pragma unroll
+        for (int e = 0; e < DV; ++e) {
+            float oo = __shfl_xor_sync(0xffffffffu, o[e], off);
+            o[e] = o[e] * sc.ra + oo * sc.rb;
+        }
+        m = sc.m;
+    }
+    // project: o / l
+    float* out = (float*)p.out + ((size_t)bh * L + row) * Ev;
+#pragma unroll
+    for (int e = 0; e < DV; ++e)
+        if (e < Ev && (e & 31) == lane) out[e] = o[e] / l;
+}
+}  // namespace
+
+extern "C" int32_t sanic_attn_fwd_f32(sanic_ctx* ctx, const sanic_attn_params* p, void* stream) {
+    if (!ctx || !p) return SANIC_ERR_INVALID;
+    SANIC_REQUIRE(ctx, p->q && p->k && p->v && p->out, "attn_fwd_f32: null tensor");
+    SANIC_REQUIRE(ctx, p->batch > 0 && p->q_heads > 0 && p->kv_heads > 0 && p->q_heads % p->kv_heads == 0,
+                  "attn_fwd_f32: query heads must be a multiple of key/value heads");
+    SANIC_REQUIRE(ctx, p->q_len > 0 && p->kv_len > 0, "attn_fwd_f32: empty sequence");
+    SANIC_REQUIRE(ctx, p->head_dim > 0 && p->head_dim % 4 == 0 && p->head_dim <= 1024,
+                  "attn_fwd_f32: head_dim must be a multiple of 4");
+    SANIC_REQUIRE(ctx, p->v_dim > 0 && p->v_dim <= 128, "attn_fwd_f32: v_dim must be in [1, 128]");
+    SANIC_REQUIRE(ctx, p->out_dtype == SANIC_F32, "attn_fwd_f32: output is f32");
+    SANIC_REQUIRE(ctx, !(p->causal && p->mask), "attn_fwd_f32: attn_mask and is_causal cannot both be set");
+    sanic_set_device(ctx);
+    dim3 grid((p->q_len + 3) / 4, p->batch * p->q_heads), block(128);
+    size_t smem = 4 * (size_t)p->head_dim * sizeof(float);
+    if (p->v_dim <= 32) attn_fwd_f32_kernel<32><<<grid, block, smem, (cudaStream_t)stream>>>(*p);
+    else if (p->v_dim <= 64) attn_fwd_f32_kernel<64><<<grid, block, smem, (cudaStream_t)stream>>>(*p);
+    else attn_fwd_f32_kernel<128><<<grid, block, smem, (cudaStream_t)stream>>>(*p);
+    SANIC_LAUNCH_CHECK(ctx, "attn_fwd_f32");
+    return SANIC_OK;
+}

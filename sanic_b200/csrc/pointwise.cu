@@ -1,0 +1,280 @@
+// Pointwise, gather and extremum-index stages of a decode step, plus the typed
+// load/store helpers exposed for bit-exactness tests. These are the K3/K4 rows of the
+// reference emitter (src/emit_metal.rs:123-232, 1118-1178 in the reference project).
+#include <vector>
+
+#include "common.cuh"
+
+namespace {
+using namespace sanic;
+
+// xn = bf16((x * g) / sqrt(sum(x^2) * (1/n) + eps)); one CTA per row, fixed summation order.
+__global__ void __launch_bounds__(256) rmsnorm_kernel(const float* x, const uint16_t* gamma, int n, float eps,
+                                                      uint16_t* out) {
+    __shared__ float wsum[8];
+    __shared__ float s_den;
+    const float* xr = x + (size_t)blockIdx.x * n;
+    float ss = 0.0f;
+    for (int i = threadIdx.x; i < n; i += 256) ss = fmaf(xr[i], xr[i], ss);
+    ss = warp_sum(ss);
+    if ((threadIdx.x & 31) == 0) wsum[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float tot = 0.0f;
+        for (int w = 0; w < 8; ++w) tot += wsum[w];
+        s_den = sqrtf(tot * (1.0f / (float)n) + eps);
+    }
+    __syncthreads();
+    float den = s_den;
+    for (int i = threadIdx.x; i < n; i += 256)
+        out[(size_t)blockIdx.x * n + i] = f32_to_bf16_bits((xr[i] * bf16_to_f32(gamma[i])) / den);
+}
+
+__global__ void embed_gather_kernel(const uint16_t* table, const int32_t* tokens, int hidden, int vocab, float* out) {
+    int b = blockIdx.x;
+    int tok = tokens[b];
+    tok = tok < 0 ? 0 : (tok >= vocab ? vocab - 1 : tok);  // the host validates; never read out of bounds
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x)
+        out[(size_t)b * hidden + i] = bf16_to_f32(table[(size_t)tok * hidden + i]);
+}
+
+__global__ void rope_table_kernel(const double* inv_freq, int n_freq, int n_pos, float* table) {
+    int idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= n_freq * n_pos) return;
+    int pos = idx / n_freq, f = idx % n_freq;
+    double s, c;
+    sincos((double)pos * inv_freq[f], &s, &c);
+    table[2 * (size_t)idx] = (float)c;
+    table[2 * (size_t)idx + 1] = (float)s;
+}
+
+// out[p=0,f] = x0*cos - x1*sin ; out[p=1,f] = x1*cos + x0*sin  (pair-major split of head_dim)
+__global__ void rope_bf16_kernel(const uint16_t* x, uint16_t* out, long long rows, int seq, int D, const float* table,
+                                 int pos0) {
+    const int F = D / 2;
+    long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    long long total = rows * seq * F;
+    if (idx >= total) return;
+    int f = (int)(idx % F);
+    long long rs = idx / F;
+    int s = (int)(rs % seq);
+    const float* cs = table + 2 * ((size_t)(pos0 + s) * F + f);
+    float c = cs[0], sn = cs[1];
+    size_t base = (size_t)rs * D;
+    float x0 = bf16_to_f32(x[base + f]), x1 = bf16_to_f32(x[base + F + f]);
+    out[base + f] = f32_to_bf16_bits(x0 * c + (-x1) * sn);
+    out[base + F + f] = f32_to_bf16_bits(x1 * c + x0 * sn);
+}
+
+__global__ void rope_cache_write_kernel(sanic_rope_cache_params p) {
+    const int D = p.head_dim, F = D / 2;
+    const int heads = p.q_heads + 2 * p.kv_heads;
+    int idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= p.batch * heads * F) return;
+    int f = idx % F;
+    int h = (idx / F) % heads;
+    int b = idx / (F * heads);
+    int pos = *p.position;
+    if (pos < 0 || pos >= p.ctx) return;
+    const float* cs = p.table + 2 * ((size_t)pos * F + f);
+    float c = cs[0], sn = cs[1];
+    if (h < p.q_heads) {
+        const float* q = p.q + ((size_t)b * p.q_heads + h) * D;
+        float x0 = q[f], x1 = q[F + f];
+        uint16_t* o = (uint16_t*)p.q_out + ((size_t)b * p.q_heads + h) * D;
+        o[f] = f32_to_bf16_bits(x0 * c + (-x1) * sn);
+        o[F + f] = f32_to_bf16_bits(x1 * c + x0 * sn);
+    } else if (h < p.q_heads + p.kv_heads) {
+        int hk = h - p.q_heads;
+        const float* k = p.k + ((size_t)b * p.kv_heads + hk) * D;
+        float x0 = k[f], x1 = k[F + f];
+        // in-place where(coord == pos, current, cache): only the written row is touched
+        uint16_t* o = (uint16_t*)p.k_cache + (((size_t)b * p.kv_heads + hk) * p.ctx + pos) * D;
+        o[f] = f32_to_bf16_bits(x0 * c + (-x1) * sn);
+        o[F + f] = f32_to_bf16_bits(x1 * c + x0 * sn);
+    } else {
+        int hk = h - p.q_heads - p.kv_heads;
+        const float* v = p.v + ((size_t)b * p.kv_heads + hk) * D;
+        uint16_t* o = (uint16_t*)p.v_cache + ((size_t)b * p.kv_heads + hk) * D * (size_t)p.ctx;
+        o[(size_t)f * p.ctx + pos] = f32_to_bf16_bits(v[f]);
+        o[(size_t)(F + f) * p.ctx + pos] = f32_to_bf16_bits(v[F + f]);
+    }
+}
+
+__global__ void advance_kernel(int32_t* position) { *position += 1; }
+
+// Extremal-key payload fold: state (max value, first index). Merge: larger key wins, equal
+// keys keep the smaller index (reference src/derive.rs:1714-1735). Symmetric, so any tree works.
+__device__ __forceinline__ void amax_merge(float& v, int& i, float v2, int i2) {
+    if (v2 > v || (v2 == v && i2 < i)) { v = v2; i = i2; }
+}
+constexpr int AMAX_CHUNKS = 128;
+__global__ void __launch_bounds__(256) argmax_partial_kernel(const float* x, int n, float* scratch) {
+    int row = blockIdx.y, chunk = blockIdx.x;
+    int lo = (int)(((long long)chunk * n) / AMAX_CHUNKS), hi = (int)(((long long)(chunk + 1) * n) / AMAX_CHUNKS);
+    const float* xr = x + (size_t)row * n;
+    float v = -INFINITY; int i = 0x7FFFFFFF;
+    for (int j = lo + threadIdx.x; j < hi; j += 256) amax_merge(v, i, xr[j], j);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        float v2 = __shfl_xor_sync(0xffffffffu, v, o); int i2 = __shfl_xor_sync(0xffffffffu, i, o);
+        amax_merge(v, i, v2, i2);
+    }
+    __shared__ float sv[8]; __shared__ int si[8];
+    if ((threadIdx.x & 31) == 0) { sv[threadIdx.x >> 5] = v; si[threadIdx.x >> 5] = i; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < 8; ++w) amax_merge(v, i, sv[w], si[w]);
+        scratch[((size_t)row * AMAX_CHUNKS + chunk) * 2] = v;
+        scratch[((size_t)row * AMAX_CHUNKS + chunk) * 2 + 1] = __int_as_float(i);
+    }
+}
+__global__ void __launch_bounds__(128) argmax_final_kernel(const float* scratch, uint32_t* out) {
+    int row = blockIdx.x;
+    float v = scratch[((size_t)row * AMAX_CHUNKS + threadIdx.x) * 2];
+    int i = __float_as_int(scratch[((size_t)row * AMAX_CHUNKS + threadIdx.x) * 2 + 1]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        float v2 = __shfl_xor_sync(0xffffffffu, v, o); int i2 = __shfl_xor_sync(0xffffffffu, i, o);
+        amax_merge(v, i, v2, i2);
+    }
+    __shared__ float sv[4]; __shared__ int si[4];
+    if ((threadIdx.x & 31) == 0) { sv[threadIdx.x >> 5] = v; si[threadIdx.x >> 5] = i; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < 4; ++w) amax_merge(v, i, sv[w], si[w]);
+        // the +inf identity of an empty fold saturates to u32::MAX
+        out[row] = (i == 0x7FFFFFFF) ? 0xFFFFFFFFu : (uint32_t)i;
+    }
+}
+
+__global__ void round_bf16_kernel(const float* x, size_t n, uint16_t* out) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) out[i] = f32_to_bf16_bits(x[i]);
+}
+__global__ void store_u32_kernel(const float* x, size_t n, uint32_t* out) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) out[i] = f32_to_u32_sat(x[i]);
+}
+__global__ void w4_unpack_kernel(const uint8_t* packed, size_t n, float* out) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) out[i] = (float)(int)((packed[i >> 1] >> ((i & 1) * 4)) & 0xF) - 8.0f;
+}
+}  // namespace
+
+extern "C" {
+
+int32_t sanic_rmsnorm(sanic_ctx* ctx, const float* x, const void* gamma, int32_t rows, int32_t n, float eps, void* out,
+                      void* stream) {
+    if (!ctx) return SANIC_ERR_INVALID;
+    SANIC_REQUIRE(ctx, x && gamma && out && rows > 0 && n > 0, "rmsnorm: bad arguments");
+    sanic_set_device(ctx);
+    rmsnorm_kernel<<<rows, 256, 0, (cudaStream_t)stream>>>(x, (const uint16_t*)gamma, n, eps, (uint16_t*)out);
+    SANIC_LAUNCH_CHECK(ctx, "rmsnorm");
+    return SANIC_OK;
+}
+
+int32_t sanic_embed_gather(sanic_ctx* ctx, const void* table, const int32_t* tokens, int32_t batch, int32_t hidden,
+                           int32_t vocab, float* out, void* stream) {
+    if (!ctx) return SANIC_ERR_INVALID;
+    SANIC_REQUIRE(ctx, table && tokens && out && batch > 0 && hidden > 0 && vocab > 0, "embed_gather: bad arguments");
+    sanic_set_device(ctx);
+    embed_gather_kernel<<<batch, 256, 0, (cudaStream_t)stream>>>((const uint16_t*)table, tokens, hidden, vocab, out);
+    SANIC_LAUNCH_CHECK(ctx, "embed_gather");
+    return SANIC_OK;
+}
+
+int32_t sanic_rope_table(sanic_ctx* ctx, const double* inv_freq_host, int32_t n_freq, int32_t n_pos, float* table,
+                         void* stream) {
+    if (!ctx) return SANIC_ERR_INVALID;
+    SANIC_REQUIRE(ctx, inv_freq_host && table && n_freq > 0 && n_pos > 0, "rope_table: bad arguments");
+    sanic_set_device(ctx);
+    double* d = nullptr;
+    SANIC_CUDA_CHECK(ctx, cudaMalloc(&d, sizeof(double) * n_freq));
+    cudaError_t e = cudaMemcpyAsync(d, inv_freq_host, sizeof(double) * n_freq, cudaMemcpyHostToDevice, (cudaStream_t)stream);
+    if (e == cudaSuccess) {
+        int total = n_freq * n_pos;
+        rope_table_kernel<<<(total + 255) / 256, 256, 0, (cudaStream_t)stream>>>(d, n_freq, n_pos, table);
+        e = cudaGetLastError();
+    }
+    if (e == cudaSuccess) e = cudaStreamSynchronize((cudaStream_t)stream);
+    cudaFree(d);
+    if (e != cudaSuccess) return sanic_fail(ctx, SANIC_ERR_CUDA, std::string("rope_table: ") + cudaGetErrorString(e));
+    return SANIC_OK;
+}
+
+int32_t sanic_rope_bf16(sanic_ctx* ctx, const void* x, void* out, int64_t rows, int32_t seq, int32_t head_dim,
+                        const float* table, int32_t pos0, void* stream) {
+    if (!ctx) return SANIC_ERR_INVALID;
+    SANIC_REQUIRE(ctx, x && out && table && rows > 0 && seq > 0 && head_dim > 0 && head_dim % 2 == 0 && pos0 >= 0,
+                  "rope_bf16: bad arguments");
+    sanic_set_device(ctx);
+    long long total = (long long)rows * seq * (head_dim / 2);
+    rope_bf16_kernel<<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
+        (const uint16_t*)x, (uint16_t*)out, rows, seq, head_dim, table, pos0);
+    SANIC_LAUNCH_CHECK(ctx, "rope_bf16");
+    return SANIC_OK;
+}
+
+int32_t sanic_rope_cache_write(sanic_ctx* ctx, const sanic_rope_cache_params* p, void* stream) {
+    if (!ctx || !p) return SANIC_ERR_INVALID;
+    SANIC_REQUIRE(ctx, p->q && p->k && p->v && p->q_out && p->k_cache && p->v_cache && p->table && p->position,
+                  "rope_cache_write: null tensor");
+    SANIC_REQUIRE(ctx, p->batch > 0 && p->q_heads > 0 && p->kv_heads > 0 && p->head_dim % 2 == 0 && p->ctx > 0,
+                  "rope_cache_write: bad shape");
+    sanic_set_device(ctx);
+    int total = p->batch * (p->q_heads + 2 * p->kv_heads) * (p->head_dim / 2);
+    rope_cache_write_kernel<<<(total + 255) / 256, 256, 0, (cudaStream_t)stream>>>(*p);
+    SANIC_LAUNCH_CHECK(ctx, "rope_cache_write");
+    return SANIC_OK;
+}
+
+int32_t sanic_advance_position(sanic_ctx* ctx, int32_t* position, void* stream) {
+    if (!ctx || !position) return SANIC_ERR_INVALID;
+    sanic_set_device(ctx);
+    advance_kernel<<<1, 1, 0, (cudaStream_t)stream>>>(position);
+    SANIC_LAUNCH_CHECK(ctx, "advance_position");
+    return SANIC_OK;
+}
+
+int32_t sanic_argmax(sanic_ctx* ctx, const float* x, int32_t rows, int32_t n, uint32_t* out_index, float* scratch,
+                     void* stream) {
+    if (!ctx) return SANIC_ERR_INVALID;
+    SANIC_REQUIRE(ctx, x && out_index && scratch && rows > 0 && n > 0, "argmax: bad arguments");
+    sanic_set_device(ctx);
+    argmax_partial_kernel<<<dim3(AMAX_CHUNKS, rows), 256, 0, (cudaStream_t)stream>>>(x, n, scratch);
+    SANIC_LAUNCH_CHECK(ctx, "argmax partial");
+    argmax_final_kernel<<<rows, 128, 0, (cudaStream_t)stream>>>(scratch, out_index);
+    SANIC_LAUNCH_CHECK(ctx, "argmax final");
+    return SANIC_OK;
+}
+
+int32_t sanic_round_to_bf16(sanic_ctx* ctx, const float* x, size_t n, uint16_t* out_bits, void* stream) {
+    if (!ctx) return SANIC_ERR_INVALID;
+    SANIC_REQUIRE(ctx, x && out_bits, "round_to_bf16: null tensor");
+    if (n == 0) return SANIC_OK;
+    sanic_set_device(ctx);
+    round_bf16_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(x, n, out_bits);
+    SANIC_LAUNCH_CHECK(ctx, "round_to_bf16");
+    return SANIC_OK;
+}
+int32_t sanic_store_u32_saturating(sanic_ctx* ctx, const float* x, size_t n, uint32_t* out, void* stream) {
+    if (!ctx) return SANIC_ERR_INVALID;
+    SANIC_REQUIRE(ctx, x && out, "store_u32: null tensor");
+    if (n == 0) return SANIC_OK;
+    sanic_set_device(ctx);
+    store_u32_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(x, n, out);
+    SANIC_LAUNCH_CHECK(ctx, "store_u32");
+    return SANIC_OK;
+}
+int32_t sanic_w4_unpack(sanic_ctx* ctx, const uint8_t* packed, size_t n_elems, float* out, void* stream) {
+    if (!ctx) return SANIC_ERR_INVALID;
+    SANIC_REQUIRE(ctx, packed && out, "w4_unpack: null tensor");
+    if (n_elems == 0) return SANIC_OK;
+    sanic_set_device(ctx);
+    w4_unpack_kernel<<<(unsigned)((n_elems + 255) / 256), 256, 0, (cudaStream_t)stream>>>(packed, n_elems, out);
+    SANIC_LAUNCH_CHECK(ctx, "w4_unpack");
+    return SANIC_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,155 @@
+// Launch lists and their frozen replays: the stateful-stepping half of the runtime.
+//
+// A program is the ordered stage list the emitter produced for one schedule
+// (reference src/partition.rs:101-127). `run` launches each stage on the caller's
+// stream (Backend::execute, src/compile.rs:101-107). `capture` freezes the list into a
+// CUDA graph and `step` replays it, which is what MetalDevice::capture /
+// run_graph_timed do with a pre-encoded command buffer (src/metal.rs:634-705). State
+// that changes between steps (position, tokens, caches) lives in device buffers the
+// stages read through pointers, so a replay needs no host writes.
+#include <new>
+#include <vector>
+
+#include "common.cuh"
+
+struct sanic_program {
+    sanic_ctx* ctx = nullptr;
+    std::vector<sanic_stage_desc> stages;
+    cudaGraph_t graph = nullptr;
+    cudaGraphExec_t exec = nullptr;
+    cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+    int kernels = 0;
+};
+
+namespace {
+int32_t check_stage(sanic_ctx* ctx, const sanic_stage_desc& s) {
+    if (s.stage_kind == SANIC_STAGE_FUSED) {
+        int32_t family = 0;
+        int32_t rc = sanic_emit_select(&s.carrier, &family);
+        if (rc != SANIC_OK) return sanic_fail(ctx, rc, "program: no kernel for this carrier structure");
+        bool ok = (s.op == SANIC_OP_GEMV && (family == SANIC_KERNEL_PLAIN_CONTRACTION ||
+                                            family == SANIC_KERNEL_GROUPED_I4_CONTRACTION)) ||
+                  (s.op == SANIC_OP_DECODE_ATTN && family == SANIC_KERNEL_ONLINE_SOFTMAX_FOLD) ||
+                  (s.op == SANIC_OP_ARGMAX && family == SANIC_KERNEL_EXTREMUM_INDEX);
+        if (!ok) return sanic_fail(ctx, SANIC_ERR_UNSUPPORTED, "program: stage op does not match its carrier");
+        if (s.op == SANIC_OP_GEMV) {
+            bool i4 = s.u.gemv.weight_dtype == SANIC_I4;
+            if (i4 != (family == SANIC_KERNEL_GROUPED_I4_CONTRACTION))
+                return sanic_fail(ctx, SANIC_ERR_DTYPE, "program: leaf storage does not match the weight buffer");
+        }
+    } else if (s.stage_kind == SANIC_STAGE_ELEMENTWISE) {
+        if (!(s.op == SANIC_OP_RMSNORM || s.op == SANIC_OP_ROPE_CACHE || s.op == SANIC_OP_ADVANCE))
+            return sanic_fail(ctx, SANIC_ERR_UNSUPPORTED, "program: not an elementwise stage");
+    } else if (s.stage_kind == SANIC_STAGE_GATHER) {
+        if (s.op != SANIC_OP_EMBED) return sanic_fail(ctx, SANIC_ERR_UNSUPPORTED, "program: not a gather stage");
+    } else {
+        return sanic_fail(ctx, SANIC_ERR_INVALID, "program: unknown stage kind");
+    }
+    return SANIC_OK;
+}
+int kernels_of(const sanic_stage_desc& s) { return s.op == SANIC_OP_ARGMAX ? 2 : 1; }
+
+int32_t run_stage(sanic_ctx* ctx, const sanic_stage_desc& s, void* stream) {
+    switch (s.op) {
+        case SANIC_OP_GEMV: return sanic_gemv(ctx, &s.u.gemv, stream);
+        case SANIC_OP_DECODE_ATTN: return sanic_attn_decode_splitkv(ctx, &s.u.decode, stream);
+        case SANIC_OP_ARGMAX:
+            return sanic_argmax(ctx, s.u.argmax.x, s.u.argmax.rows, s.u.argmax.n, s.u.argmax.out, s.u.argmax.scratch, stream);
+        case SANIC_OP_RMSNORM:
+            return sanic_rmsnorm(ctx, s.u.rmsnorm.x, s.u.rmsnorm.gamma, s.u.rmsnorm.rows, s.u.rmsnorm.n, s.u.rmsnorm.eps,
+                                 s.u.rmsnorm.out, stream);
+        case SANIC_OP_EMBED:
+            return sanic_embed_gather(ctx, s.u.embed.table, s.u.embed.tokens, s.u.embed.batch, s.u.embed.hidden,
+                                      s.u.embed.vocab, s.u.embed.out, stream);
+        case SANIC_OP_ROPE_CACHE: return sanic_rope_cache_write(ctx, &s.u.rope_cache, stream);
+        case SANIC_OP_ADVANCE: return sanic_advance_position(ctx, s.u.advance.position, stream);
+        default: return sanic_fail(ctx, SANIC_ERR_INVALID, "program: unknown op");
+    }
+}
+}  // namespace
+
+extern "C" {
+
+int32_t sanic_program_create(sanic_ctx* ctx, const sanic_stage_desc* stages, int32_t n_stages, sanic_program** out) {
+    if (!ctx || !out) return SANIC_ERR_INVALID;
+    *out = nullptr;
+    SANIC_REQUIRE(ctx, stages && n_stages > 0, "program: cannot compile an empty stage list");
+    sanic_program* p = new (std::nothrow) sanic_program();
+    if (!p) return SANIC_ERR_NOMEM;
+    p->ctx = ctx;
+    for (int i = 0; i < n_stages; ++i) {
+        int32_t rc = check_stage(ctx, stages[i]);
+        if (rc != SANIC_OK) { delete p; return rc; }
+        p->stages.push_back(stages[i]);
+        p->kernels += kernels_of(stages[i]);
+    }
+    *out = p;
+    return SANIC_OK;
+}
+
+int32_t sanic_program_destroy(sanic_program* p) {
+    if (!p) return SANIC_ERR_INVALID;
+    sanic_set_device(p->ctx);
+    if (p->exec) cudaGraphExecDestroy(p->exec);
+    if (p->graph) cudaGraphDestroy(p->graph);
+    if (p->ev0) cudaEventDestroy(p->ev0);
+    if (p->ev1) cudaEventDestroy(p->ev1);
+    delete p;
+    return SANIC_OK;
+}
+
+int32_t sanic_program_kernel_count(sanic_program* p) { return p ? p->kernels : -1; }
+
+int32_t sanic_program_run(sanic_program* p, void* stream) {
+    if (!p) return SANIC_ERR_INVALID;
+    for (const sanic_stage_desc& s : p->stages) {
+        int32_t rc = run_stage(p->ctx, s, stream);
+        if (rc != SANIC_OK) return rc;
+    }
+    return SANIC_OK;
+}
+
+int32_t sanic_program_capture(sanic_program* p, void* stream) {
+    if (!p) return SANIC_ERR_INVALID;
+    sanic_ctx* ctx = p->ctx;
+    SANIC_REQUIRE(ctx, stream != nullptr, "program_capture: needs a non-default stream");
+    sanic_set_device(ctx);
+    cudaStream_t st = (cudaStream_t)stream;
+    if (p->exec) { cudaGraphExecDestroy(p->exec); p->exec = nullptr; }
+    if (p->graph) { cudaGraphDestroy(p->graph); p->graph = nullptr; }
+    SANIC_CUDA_CHECK(ctx, cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal));
+    int32_t rc = sanic_program_run(p, stream);
+    cudaGraph_t g = nullptr;
+    cudaError_t e = cudaStreamEndCapture(st, &g);
+    if (rc != SANIC_OK) { if (g) cudaGraphDestroy(g); return rc; }
+    if (e != cudaSuccess) return sanic_fail(ctx, SANIC_ERR_CUDA, std::string("program_capture: ") + cudaGetErrorString(e));
+    p->graph = g;
+    SANIC_CUDA_CHECK(ctx, cudaGraphInstantiate(&p->exec, p->graph, 0));
+    if (!p->ev0) {
+        SANIC_CUDA_CHECK(ctx, cudaEventCreate(&p->ev0));
+        SANIC_CUDA_CHECK(ctx, cudaEventCreate(&p->ev1));
+    }
+    return SANIC_OK;
+}
+
+// A replay whose launch fails returns an error: the step's writes are untrustworthy and a
+// decode loop must not continue on them (reference src/metal.rs:666-705).
+int32_t sanic_program_step(sanic_program* p, void* stream, double* gpu_seconds) {
+    if (!p) return SANIC_ERR_INVALID;
+    sanic_ctx* ctx = p->ctx;
+    SANIC_REQUIRE(ctx, p->exec != nullptr, "program_step: capture the program first");
+    sanic_set_device(ctx);
+    cudaStream_t st = (cudaStream_t)stream;
+    if (gpu_seconds) SANIC_CUDA_CHECK(ctx, cudaEventRecord(p->ev0, st));
+    SANIC_CUDA_CHECK(ctx, cudaGraphLaunch(p->exec, st));
+    if (gpu_seconds) {
+        SANIC_CUDA_CHECK(ctx, cudaEventRecord(p->ev1, st));
+        SANIC_CUDA_CHECK(ctx, cudaEventSynchronize(p->ev1));
+        float ms = 0.0f;
+        SANIC_CUDA_CHECK(ctx, cudaEventElapsedTime(&ms, p->ev0, p->ev1));
+        *gpu_seconds = (double)ms * 1e-3;
+    }
+    return SANIC_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,256 @@
+"""Llama-3.2-1B-architecture decode step as a captured launch list.
+
+Mirrors the stateful-stepping API of the reference (`Graph::compile_for` ->
+`StepProgram::instantiate` -> `Machine::step`, src/graph.rs:231-356 of the reference project)
+for the decode graph of examples/llama3_2.rs:112-253, with a leading batch axis and a shared
+scalar position. The emitter's product is an ordered stage list (Fused / Elementwise / Gather,
+src/partition.rs:44-98); state (KV caches, position, token) lives in device buffers owned by
+the machine, and a step is one CUDA-graph replay with no host writes.
+
+Storage declarations (the graph's, not the kernels'): weights bf16 or int4+bf16 scales; caches
+bf16; the residual stream is pinned f32; every activation a projection reads, and q, are
+stored bf16 (a bf16 boundary policy).
+"""
+from __future__ import annotations
+
+import ctypes as C
+import math
+
+import torch
+
+from . import _abi as abi
+from .backend import (CompileError, CudaDevice, RunError, carrier_contraction, carrier_extremum_index,
+                      carrier_online_softmax)
+
+LLAMA_3_2_1B = dict(vocab=128256, layers=16, hidden=2048, q_heads=32, kv_heads=8, head_dim=64, ffn=8192)
+
+ROPE_THETA = 500000.0
+
+
+def llama3_inv_freq(n_freq: int):
+    """examples/llama3_2.rs:95-107 (factor 32, original context 8192, low/high 1/4)."""
+    out = []
+    for i in range(n_freq):
+        inv = math.exp(i * (-math.log(ROPE_THETA) / n_freq))
+        wave = 2.0 * math.pi / inv
+        smooth = (8192.0 / wave - 1.0) / (4.0 - 1.0)
+        scaled = inv / 32.0
+        blended = (1.0 - smooth) * scaled + smooth * inv
+        out.append(scaled if 8192.0 / 1.0 < wave else (inv if wave < 8192.0 / 4.0 else blended))
+    return out
+
+
+def random_weights(cfg: dict, seed: int, device, w4: bool = False):
+    """Random-init weights of the architecture: N(0, 0.02) bf16, norms N(1, 0.1); the int4 variant draws
+    integers uniform in [-8, 7] with a positive bf16 scale per 64 inputs."""
+    g = torch.Generator(device=device)
+    g.manual_seed(seed)
+    H, F, V = cfg["hidden"], cfg["ffn"], cfg["vocab"]
+    Hq, Hkv, D = cfg["q_heads"], cfg["kv_heads"], cfg["head_dim"]
+
+    def dense(rows, cols):
+        return (torch.randn(rows, cols, generator=g, device=device, dtype=torch.float32) * 0.02).to(torch.bfloat16)
+
+    def norm():
+        return (1.0 + 0.1 * torch.randn(H, generator=g, device=device, dtype=torch.float32)).to(torch.bfloat16)
+
+    def quant(rows, cols):
+        q = torch.randint(-8, 8, (rows, cols), generator=g, device=device, dtype=torch.int32)
+        u = (q + 8).to(torch.uint8)
+        packed = (u[:, 0::2] | (u[:, 1::2] << 4)).contiguous()  # low nibble = even element
+        s = 0.02 / 4.6 * (1.0 + 0.25 * torch.rand(rows, cols // 64, generator=g, device=device, dtype=torch.float32))
+        return packed, s.to(torch.bfloat16).contiguous()
+
+    w = dict(embed=dense(V, H), final_norm=norm(), attn_norm=[], mlp_norm=[])
+    shapes = dict(wq=(Hq * D, H), wk=(Hkv * D, H), wv=(Hkv * D, H), wo=(H, Hq * D), wgate=(F, H), wup=(F, H), wdown=(H, F))
+    for name in shapes:
+        w[name] = []
+        if w4:
+            w["s" + name[1:]] = []
+    for _ in range(cfg["layers"]):
+        w["attn_norm"].append(norm())
+        w["mlp_norm"].append(norm())
+        for name, (r, c) in shapes.items():
+            if w4:
+                pk, sc = quant(r, c)
+                w[name].append(pk)
+                w["s" + name[1:]].append(sc)
+            else:
+                w[name].append(dense(r, c))
+    return w
+
+
+def weights_to_oracle(w: dict, w4: bool):
+    """Host copies in the layout oracle.Llama takes (bf16 bits as uint16, packed int4 as uint8)."""
+    def bits(t):
+        return t.view(torch.int16).cpu().numpy().view("uint16")
+
+    out = dict(embed=bits(w["embed"]), final_norm=bits(w["final_norm"]),
+               attn_norm=[bits(t) for t in w["attn_norm"]], mlp_norm=[bits(t) for t in w["mlp_norm"]])
+    for name in ("wq", "wk", "wv", "wo", "wgate", "wup", "wdown"):
+        out[name] = [t.cpu().numpy() if w4 else bits(t) for t in w[name]]
+        if w4:
+            out["s" + name[1:]] = [bits(t) for t in w["s" + name[1:]]]
+    return out
+
+
+class LlamaMachine:
+    """The instantiated step program: owns state buffers, replays one captured graph per step."""
+
+    def __init__(self, dev: CudaDevice, cfg: dict, weights: dict, ctx: int, batch: int, w4: bool = False,
+                 capture: bool = True):
+        self.dev, self.cfg, self.ctx, self.batch, self.w4 = dev, dict(cfg), ctx, batch, w4
+        H, F, V, L = cfg["hidden"], cfg["ffn"], cfg["vocab"], cfg["layers"]
+        Hq, Hkv, D = cfg["q_heads"], cfg["kv_heads"], cfg["head_dim"]
+        if H != Hq * D or Hq % Hkv or D not in (64, 128):
+            raise CompileError("invalid graph: hidden must equal q_heads*head_dim and head_dim must be 64 or 128")
+        if ctx % 8:
+            raise CompileError("invalid input declaration: the cache sequence extent must be a multiple of 8")
+        td, B = dev.torch_device, batch
+        z = lambda shape, dt: torch.zeros(shape, dtype=dt, device=td)
+        self.w = weights
+        self.tokens = z((B,), torch.int32)
+        self.position = z((1,), torch.int32)
+        self.x = z((B, H), torch.float32)
+        self.xn = z((B, H), torch.bfloat16)
+        self.q = z((B, Hq * D), torch.float32)
+        self.k = z((B, Hkv * D), torch.float32)
+        self.v = z((B, Hkv * D), torch.float32)
+        self.qb = z((B, Hq, D), torch.bfloat16)
+        self.att = z((B, Hq, D), torch.bfloat16)
+        self.h = z((B, F), torch.bfloat16)
+        self.logits = z((B, V), torch.float32)
+        self.kcache = [z((B, Hkv, ctx, D), torch.bfloat16) for _ in range(L)]   # [kv, seq, hd]
+        self.vcache = [z((B, Hkv, D, ctx), torch.bfloat16) for _ in range(L)]   # [kv, hd, seq]
+        self.table = dev.rope_table(llama3_inv_freq(D // 2) if cfg.get("llama3_rope", 1) else
+                                    [math.exp(i * (-math.log(cfg.get("theta", ROPE_THETA)) / (D // 2))) for i in range(D // 2)],
+                                    ctx)
+        tiles = (ctx + 63) // 64
+        self.n_splits = max(1, min(tiles, -(-2 * dev.specs()["sm_count"] // (B * Hkv))))
+        self.partials = dev.decode_scratch(B, Hq, D, self.n_splits)
+        self.amax_scratch = z((B * 2 * 256,), torch.float32)
+        self.stream = torch.cuda.Stream(device=td)
+        self._build()
+        self.captured = False
+        if capture:
+            self.capture()
+
+    # ── stage list ──
+    def _gemv(self, x, names, layer, outs, epilogue=abi.EPI_STORE, residual=None, out_dtype=abi.F32):
+        ws = [self.w[n][layer] if layer is not None else self.w[n] for n in names]
+        sc = [self.w["s" + n[1:]][layer] for n in names] if (self.w4 and layer is not None) else None
+        s = abi.StageDesc()
+        s.stage_kind, s.op = abi.STAGE_FUSED, abi.OP_GEMV
+        s.carrier = carrier_contraction(abi.I4 if sc is not None else abi.BF16)
+        s.u.gemv = self.dev.gemv_params(x, ws, outs, sc, epilogue, residual, out_dtype)
+        return s
+
+    def _rmsnorm(self, gamma):
+        s = abi.StageDesc()
+        s.stage_kind, s.op = abi.STAGE_ELEMENTWISE, abi.OP_RMSNORM
+        s.u.rmsnorm.x, s.u.rmsnorm.gamma = self.x.data_ptr(), gamma.data_ptr()
+        s.u.rmsnorm.rows, s.u.rmsnorm.n, s.u.rmsnorm.eps = self.batch, self.cfg["hidden"], float(self.cfg.get("eps", 1e-5))
+        s.u.rmsnorm.out = self.xn.data_ptr()
+        return s
+
+    def _build(self):
+        cfg, B = self.cfg, self.batch
+        Hq, Hkv, D = cfg["q_heads"], cfg["kv_heads"], cfg["head_dim"]
+        st = []
+        s = abi.StageDesc()
+        s.stage_kind, s.op = abi.STAGE_GATHER, abi.OP_EMBED
+        s.u.embed.table, s.u.embed.tokens = self.w["embed"].data_ptr(), self.tokens.data_ptr()
+        s.u.embed.batch, s.u.embed.hidden, s.u.embed.vocab = B, cfg["hidden"], cfg["vocab"]
+        s.u.embed.out = self.x.data_ptr()
+        st.append(s)
+        for l in range(cfg["layers"]):
+            st.append(self._rmsnorm(self.w["attn_norm"][l]))
+            st.append(self._gemv(self.xn, ["wq", "wk", "wv"], l, [self.q, self.k, self.v]))
+            s = abi.StageDesc()
+            s.stage_kind, s.op = abi.STAGE_ELEMENTWISE, abi.OP_ROPE_CACHE
+            r = s.u.rope_cache
+            r.q, r.k, r.v = self.q.data_ptr(), self.k.data_ptr(), self.v.data_ptr()
+            r.q_out, r.k_cache, r.v_cache = self.qb.data_ptr(), self.kcache[l].data_ptr(), self.vcache[l].data_ptr()
+            r.table, r.position = self.table.data_ptr(), self.position.data_ptr()
+            r.batch, r.q_heads, r.kv_heads, r.head_dim, r.ctx = B, Hq, Hkv, D, self.ctx
+            st.append(s)
+            s = abi.StageDesc()
+            s.stage_kind, s.op = abi.STAGE_FUSED, abi.OP_DECODE_ATTN
+            s.carrier = carrier_online_softmax(abi.BF16)
+            s.u.decode, _ = self.dev.decode_params(self.qb, self.kcache[l], self.vcache[l], 1, v_transposed=True,
+                                                   n_splits=self.n_splits, kv_len_dev=self.position, out=self.att,
+                                                   partials=self.partials, out_dtype=abi.BF16)
+            st.append(s)
+            st.append(self._gemv(self.att.view(B, Hq * D), ["wo"], l, [self.x], abi.EPI_RESIDUAL_ADD, self.x))
+            st.append(self._rmsnorm(self.w["mlp_norm"][l]))
+            st.append(self._gemv(self.xn, ["wgate", "wup"], l, [self.h], abi.EPI_SILU_MUL, None, abi.BF16))
+            st.append(self._gemv(self.h, ["wdown"], l, [self.x], abi.EPI_RESIDUAL_ADD, self.x))
+        st.append(self._rmsnorm(self.w["final_norm"]))
+        st.append(self._gemv(self.xn, ["embed"], None, [self.logits]))
+        s = abi.StageDesc()
+        s.stage_kind, s.op = abi.STAGE_FUSED, abi.OP_ARGMAX
+        s.carrier = carrier_extremum_index()
+        s.u.argmax.x, s.u.argmax.rows, s.u.argmax.n = self.logits.data_ptr(), B, cfg["vocab"]
+        s.u.argmax.out, s.u.argmax.scratch = self.tokens.data_ptr(), self.amax_scratch.data_ptr()
+        st.append(s)
+        s = abi.StageDesc()
+        s.stage_kind, s.op = abi.STAGE_ELEMENTWISE, abi.OP_ADVANCE
+        s.u.advance.position = self.position.data_ptr()
+        st.append(s)
+        arr = (abi.StageDesc * len(st))(*st)
+        h = C.c_void_p()
+        self.dev._check(self.dev.lib.sanic_program_create(self.dev.h, arr, len(st), C.byref(h)), "program_create")
+        self.prog = h
+        self.n_stages = len(st)
+        self.kernel_count = int(self.dev.lib.sanic_program_kernel_count(h))
+
+    def capture(self):
+        torch.cuda.synchronize(self.dev.torch_device)
+        rc = self.dev.lib.sanic_program_capture(self.prog, C.c_void_p(self.stream.cuda_stream))
+        self.dev._check(rc, "program_capture")
+        self.captured = True
+
+    # ── Machine::step ──
+    def set_state(self, tokens, position: int):
+        if position < 0 or position >= self.ctx:
+            raise RunError(f"position {position} is outside the cache extent {self.ctx}")
+        self.tokens.copy_(torch.as_tensor(tokens, dtype=torch.int32).to(self.dev.torch_device))
+        self.position.fill_(position)
+        torch.cuda.synchronize(self.dev.torch_device)
+
+    def step(self, timed: bool = False):
+        """One decode step: token <- argmax(logits(token, position)); position += 1. Returns device seconds if timed."""
+        st = C.c_void_p(self.stream.cuda_stream)
+        if self.captured:
+            sec = C.c_double(0.0)
+            rc = self.dev.lib.sanic_program_step(self.prog, st, C.byref(sec) if timed else None)
+            self.dev._check(rc, "program_step")
+            return sec.value if timed else None
+        self.dev._check(self.dev.lib.sanic_program_run(self.prog, st), "program_run")
+        return None
+
+    def sync(self):
+        self.stream.synchronize()
+
+    def read_tokens(self):
+        self.sync()
+        return self.tokens.cpu().numpy().copy()
+
+    def load_caches(self, k_list, v_list):
+        for l in range(self.cfg["layers"]):
+            self.kcache[l].copy_(k_list[l])
+            self.vcache[l].copy_(v_list[l])
+        torch.cuda.synchronize(self.dev.torch_device)
+
+    def weight_bytes(self) -> int:
+        n = 0
+        for key, val in self.w.items():
+            for t in (val if isinstance(val, list) else [val]):
+                n += t.numel() * t.element_size()
+        return n
+
+    def __del__(self):
+        try:
+            self.dev.lib.sanic_program_destroy(self.prog)
+        except Exception:
+            pass

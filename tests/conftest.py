@@ -10,6 +10,7 @@ if ROOT not in sys.path:
 
 def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (run on a B200 box)")
+    config.addinivalue_line("markers", "slow: full-size case that takes tens of seconds")
 
 
 def pytest_collection_modifyitems(config, items):

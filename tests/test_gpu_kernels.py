@@ -1,0 +1,361 @@
+"""GPU parity: every kernel family, called through the C ABI, against the CPU oracle on the same
+seeded inputs. Inputs are rounded to their declared storage dtype before either side sees them.
+
+Tolerances (stated once):
+  * f32 storage: max |g - e| / (1 + |e|) <= 1e-5 against the f64 oracle
+  * bf16 storage: <= 2e-2 of the same normalised error
+  * indices, int4 unpacking, bf16 rounding, u32 saturation: bit-exact
+"""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import oracle as orc
+
+pytestmark = pytest.mark.gpu
+
+F32_TOL = 1e-5
+BF16_TOL = 2e-2
+
+
+@pytest.fixture(scope="module")
+def dev():
+    from sanic_b200 import CudaDevice
+    return CudaDevice(0)
+
+
+def nerr(got, exp):
+    got = np.asarray(got, dtype=np.float64)
+    exp = np.asarray(exp, dtype=np.float64)
+    assert got.shape == exp.shape, (got.shape, exp.shape)
+    assert np.all(np.isfinite(got)), "non-finite values in the GPU result"
+    return float(np.max(np.abs(got - exp) / (1.0 + np.abs(exp))))
+
+
+def normal(seed, *shape):
+    return orc.Xorshift(seed).normal(*shape)
+
+
+def f32t(a, dev):
+    return torch.tensor(np.asarray(a, dtype=np.float32), device=dev.torch_device)
+
+
+def bf16t(a, dev):
+    """Round to bf16 with the oracle's rounding and upload; returns (tensor, widened f64 values)."""
+    bits = orc.to_bf16_bits(a)
+    t = torch.tensor(bits.view(np.int16), device=dev.torch_device).view(torch.bfloat16)
+    return t, orc.from_bf16_bits(bits)
+
+
+# ───────────────────────── f32 online-softmax fold (config 1) ─────────────────────────
+def test_attn_f32_known_answers(dev):
+    # reference tests/compile.rs:236-261 and tests/nn.rs:15-137
+    q = f32t([[1, 0], [0, 1]], dev).view(1, 1, 2, 2)
+    v = f32t([[2, 3], [5, 7]], dev).view(1, 1, 2, 2)
+    out = dev.attn_fwd_f32(q, q.clone(), v).cpu().numpy().ravel()
+    lit = np.array([2.990715, 4.3209534, 4.009285, 5.6790466])
+    assert np.all(np.abs(out - lit) < 64 * np.finfo(np.float32).eps * 2 * (1 + np.abs(lit)))
+    # additive mask + explicit scale
+    q = f32t([[1.0], [1.0]], dev).view(1, 1, 2, 1)
+    k = f32t([[1.0], [2.0], [3.0]], dev).view(1, 1, 3, 1)
+    v = f32t([[10.0], [20.0], [30.0]], dev).view(1, 1, 3, 1)
+    # head_dim 1 is not a multiple of 4: pad the contraction with zeros (adds exact zeros)
+    qp = torch.zeros(1, 1, 2, 4, device=dev.torch_device); qp[..., :1] = q
+    kp = torch.zeros(1, 1, 3, 4, device=dev.torch_device); kp[..., :1] = k
+    mask = f32t([[0.0, -1e30, -1e30], [0.0, 0.0, -1e30]], dev)
+    out = dev.attn_fwd_f32(qp, kp, v, scale=2.0, mask=mask).cpu().numpy().ravel()
+    w = math.exp(2.0) / (1.0 + math.exp(2.0))
+    assert nerr(out, [10.0, 10.0 * (1 - w) + 20.0 * w]) < F32_TOL
+    # causal, rectangular: upper-left aligned
+    q0 = torch.zeros(1, 1, 2, 4, device=dev.torch_device)
+    k0 = torch.zeros(1, 1, 3, 4, device=dev.torch_device)
+    v0 = f32t([[10.0], [20.0], [90.0]], dev).view(1, 1, 3, 1)
+    assert nerr(dev.attn_fwd_f32(q0, k0, v0, causal=True, scale=0.5).cpu().numpy().ravel(), [10.0, 15.0]) < F32_TOL
+    # GQA 4 query heads over 2 kv heads
+    q1 = torch.zeros(1, 4, 1, 4, device=dev.torch_device); q1[..., 0] = 1.0
+    k1 = torch.zeros(1, 2, 1, 4, device=dev.torch_device); k1[0, 0, 0, 0] = 1.0; k1[0, 1, 0, 0] = 2.0
+    v1 = f32t([10.0, 20.0], dev).view(1, 2, 1, 1)
+    assert nerr(dev.attn_fwd_f32(q1, k1, v1).cpu().numpy().ravel(), [10.0, 10.0, 20.0, 20.0]) < F32_TOL
+
+
+def test_attn_f32_config1(dev):
+    # Q [256x64], K, V [1024x64] i.i.d. N(0,1), scale 1/8, no mask
+    q = orc.round_to(orc.DT_F32, normal(0xC0F1601, 256, 64))
+    k = orc.round_to(orc.DT_F32, normal(0xC0F1602, 1024, 64))
+    v = orc.round_to(orc.DT_F32, normal(0xC0F1603, 1024, 64))
+    exp = orc.sdpa(q, k, v, scale=0.125)
+    got = dev.attn_fwd_f32(f32t(q, dev).view(1, 1, 256, 64), f32t(k, dev).view(1, 1, 1024, 64),
+                           f32t(v, dev).view(1, 1, 1024, 64), scale=0.125).cpu().numpy()[0, 0]
+    assert nerr(got, exp) <= F32_TOL
+    rel = np.max(np.abs(got - exp) / np.maximum(np.abs(exp), 1e-2))
+    assert rel <= 1e-4  # plain relative error away from zero crossings
+
+
+@pytest.mark.parametrize("shape", [(2, 3, 3, 5, 7, 4, 6), (1, 4, 2, 33, 70, 8, 32), (1, 2, 2, 7, 130, 64, 128)])
+@pytest.mark.parametrize("mode", ["plain", "causal", "window"])
+def test_attn_f32_shapes_and_masks(dev, shape, mode):
+    B, Hq, Hkv, L, S, E, Ev = shape
+    if mode != "plain":
+        S = L  # causal / window cases are square
+    q = orc.round_to(orc.DT_F32, normal(1 + L, B, Hq, L, E))
+    k = orc.round_to(orc.DT_F32, normal(2 + L, B, Hkv, S, E))
+    v = orc.round_to(orc.DT_F32, normal(3 + L, B, Hkv, S, Ev))
+    scale = 1.0 / math.sqrt(E)
+    if mode == "plain":
+        exp = orc.sdpa(q, k, v, scale=scale, enable_gqa=True)
+        got = dev.attn_fwd_f32(f32t(q, dev), f32t(k, dev), f32t(v, dev), scale=scale)
+    elif mode == "causal":
+        exp = orc.sdpa(q, k, v, is_causal=True, scale=scale, enable_gqa=True)
+        got = dev.attn_fwd_f32(f32t(q, dev), f32t(k, dev), f32t(v, dev), causal=True, scale=scale)
+    else:
+        w = 4 if L > 4 else 2
+        exp = orc.sdpa_window(q, k, v, w, scale=scale)
+        got = dev.attn_fwd_f32(f32t(q, dev), f32t(k, dev), f32t(v, dev), window=w, scale=scale)
+    assert nerr(got.cpu().numpy(), exp) <= F32_TOL
+
+
+def test_attn_f32_rejects_bad_arguments(dev):
+    from sanic_b200 import RunError
+    q = torch.zeros(1, 3, 2, 4, device=dev.torch_device)
+    k = torch.zeros(1, 2, 2, 4, device=dev.torch_device)
+    with pytest.raises(RunError):  # 3 query heads over 2 kv heads
+        dev.attn_fwd_f32(q, k, k.clone())
+    with pytest.raises(RunError):  # wrong dtype
+        dev.attn_fwd_f32(q.to(torch.bfloat16), k, k.clone())
+
+
+# ───────────────────────── split-KV decode ─────────────────────────
+def _decode_case(dev, B, Hq, Hkv, D, S, kv_len, vt, n_splits, window=0, seed=11):
+    q, qv = bf16t(normal(seed, B, Hq, D), dev)
+    k, kv = bf16t(normal(seed + 1, B, Hkv, S, D), dev)
+    v, vv = bf16t(normal(seed + 2, B, Hkv, S, D), dev)
+    vdev = v.transpose(2, 3).contiguous() if vt else v
+    lo = max(0, kv_len - window) if window else 0
+    exp, car = orc.sdpa_carrier_split(qv.reshape(B, Hq, 1, D), kv[:, :, lo:kv_len], vv[:, :, lo:kv_len], 1,
+                                      enable_gqa=True, return_carriers=True)
+    ref = orc.sdpa(qv.reshape(B, Hq, 1, D), kv[:, :, lo:kv_len], vv[:, :, lo:kv_len], enable_gqa=True)
+    assert nerr(exp, ref) < 1e-12
+    out, gcar = dev.attn_decode(q, k, vdev, kv_len, v_transposed=vt, n_splits=n_splits, window=window,
+                                return_carrier=True, out_dtype=torch.float32)
+    torch.cuda.synchronize()
+    assert nerr(out.cpu().numpy(), exp.reshape(B, Hq, D)) <= BF16_TOL
+    gc = gcar.cpu().numpy().astype(np.float64).reshape(B, Hq, D + 2)
+    car = car.reshape(B, Hq, D + 2)
+    # raw accumulators: same max; l and o agree up to the bf16 rounding of P
+    assert np.max(np.abs(gc[..., 0] - car[..., 0])) <= 1e-4 * (1 + np.max(np.abs(car[..., 0])))
+    assert nerr(gc[..., 1], car[..., 1]) <= BF16_TOL
+    assert nerr(gc[..., 2:] / gc[..., 1:2], car[..., 2:] / car[..., 1:2]) <= BF16_TOL
+    return out
+
+
+@pytest.mark.parametrize("D", [64, 128])
+@pytest.mark.parametrize("vt", [False, True])
+def test_decode_basic(dev, D, vt):
+    _decode_case(dev, B=2, Hq=8, Hkv=2, D=D, S=512, kv_len=512, vt=vt, n_splits=3)
+
+
+@pytest.mark.parametrize("kv_len,n_splits", [(1, 1), (1, 4), (63, 1), (64, 2), (65, 2), (200, 7), (1000, 16), (1030, 9)])
+def test_decode_ragged_lengths_and_splits(dev, kv_len, n_splits):
+    _decode_case(dev, B=1, Hq=32, Hkv=8, D=64, S=1056, kv_len=kv_len, vt=True, n_splits=n_splits)
+    _decode_case(dev, B=1, Hq=4, Hkv=1, D=128, S=1056, kv_len=kv_len, vt=False, n_splits=n_splits)
+
+
+@pytest.mark.parametrize("group", [1, 2, 8, 16])
+def test_decode_gqa_groups(dev, group):
+    _decode_case(dev, B=2, Hq=2 * group, Hkv=2, D=64, S=320, kv_len=300, vt=False, n_splits=2)
+
+
+def test_decode_window(dev):
+    _decode_case(dev, B=1, Hq=8, Hkv=2, D=64, S=1024, kv_len=700, vt=True, n_splits=3, window=256)
+    _decode_case(dev, B=1, Hq=8, Hkv=2, D=128, S=1024, kv_len=700, vt=False, n_splits=2, window=100)
+
+
+def test_decode_position_from_device_scalar(dev):
+    B, Hq, Hkv, D, S = 1, 8, 2, 64, 256
+    q, qv = bf16t(normal(5, B, Hq, D), dev)
+    k, kv = bf16t(normal(6, B, Hkv, S, D), dev)
+    v, vv = bf16t(normal(7, B, Hkv, S, D), dev)
+    import ctypes as C
+    pos = torch.tensor([99], dtype=torch.int32, device=dev.torch_device)
+    out = dev.empty((B, Hq, D), torch.float32)
+    from sanic_b200 import abi
+    p, _keep = dev.decode_params(q, k, v, 1, n_splits=2, kv_len_dev=pos, out=out, out_dtype=abi.F32)
+    dev._check(dev.lib.sanic_attn_decode_splitkv(dev.h, C.byref(p), dev.stream()), "decode")
+    exp = orc.sdpa(qv.reshape(B, Hq, 1, D), kv[:, :, :100], vv[:, :, :100], enable_gqa=True).reshape(B, Hq, D)
+    assert nerr(out.cpu().numpy(), exp) <= BF16_TOL
+    # a second launch reuses the scratch (ticket counters were reset by the first)
+    pos.fill_(199)
+    dev._check(dev.lib.sanic_attn_decode_splitkv(dev.h, C.byref(p), dev.stream()), "decode")
+    exp = orc.sdpa(qv.reshape(B, Hq, 1, D), kv[:, :, :200], vv[:, :, :200], enable_gqa=True).reshape(B, Hq, D)
+    assert nerr(out.cpu().numpy(), exp) <= BF16_TOL
+
+
+def test_decode_long_axis_round_trip(dev):
+    # size-independent property at a long key axis: any chunking gives the same answer, and
+    # folding two halves on their own then merging equals folding the whole.
+    B, Hq, Hkv, D, S = 1, 8, 2, 128, 65536
+    g = torch.Generator(device=dev.torch_device); g.manual_seed(3)
+    q = torch.randn(B, Hq, D, generator=g, device=dev.torch_device).to(torch.bfloat16)
+    k = torch.randn(B, Hkv, S, D, generator=g, device=dev.torch_device).to(torch.bfloat16)
+    v = torch.randn(B, Hkv, S, D, generator=g, device=dev.torch_device).to(torch.bfloat16)
+    outs = [dev.attn_decode(q, k, v, S, n_splits=n, out_dtype=torch.float32).cpu().numpy() for n in (1, 5, 64, 148)]
+    for o in outs[1:]:
+        assert nerr(o, outs[0]) <= 2e-3
+    _, ca = dev.attn_decode(q, k[:, :, :S // 2].contiguous(), v[:, :, :S // 2].contiguous(), S // 2, n_splits=8, return_carrier=True)
+    _, cb = dev.attn_decode(q, k[:, :, S // 2:].contiguous(), v[:, :, S // 2:].contiguous(), S // 2, n_splits=8, return_carrier=True)
+    merged = dev.carrier_merge(torch.stack([ca, cb])).cpu().numpy().reshape(B, Hq, D)
+    assert nerr(merged, outs[0]) <= 2e-3
+    # against the oracle on one (batch, kv head)
+    qv = q.float().cpu().numpy().astype(np.float64)[:, :4].reshape(1, 4, 1, D)
+    exp = orc.sdpa(qv, k[:, :1].float().cpu().numpy().astype(np.float64), v[:, :1].float().cpu().numpy().astype(np.float64),
+                   enable_gqa=True).reshape(4, D)
+    assert nerr(outs[0][0, :4], exp) <= BF16_TOL
+
+
+def test_carrier_merge_matches_oracle(dev):
+    rng = orc.Xorshift(0x6408)
+    n_parts, rows, D = 5, 12, 64
+    parts = np.empty((n_parts, rows, D + 2))
+    parts[..., 0] = rng.uniform(n_parts, rows) * 20.0
+    parts[..., 1] = np.abs(rng.uniform(n_parts, rows)) * 50.0 + 0.1
+    parts[..., 2:] = rng.uniform(n_parts, rows, D) * 30.0
+    # an identity partial (an all-masked shard): m = -inf, l = 0, o = 0 must be absorbed
+    parts[1, :, 0] = -np.inf; parts[1, :, 1] = 0.0; parts[1, :, 2:] = 0.0
+    parts = orc.round_to(orc.DT_F32, parts)
+    exp = orc.carrier_merge_mlo(parts)
+    got, car = dev.carrier_merge(f32t(parts, dev), return_carrier=True)
+    assert nerr(got.cpu().numpy(), exp) <= F32_TOL
+    c = car.cpu().numpy()
+    assert nerr(c[:, 2:] / c[:, 1:2], exp) <= F32_TOL
+
+
+# ───────────────────────── decode-batch contraction ─────────────────────────
+@pytest.mark.parametrize("batch", [1, 3, 8, 16])
+@pytest.mark.parametrize("K,rows", [(256, 48), (2048, 512), (8192, 64)])
+def test_gemv_bf16(dev, batch, K, rows):
+    x, xv = bf16t(normal(21, batch, K), dev)
+    w, wv = bf16t(normal(22, rows, K) * 0.02, dev)
+    exp = orc.gemv_bf16w(orc.to_bf16_bits(wv), xv)
+    got = dev.gemv(x, [w]).cpu().numpy()
+    assert nerr(got, exp) <= 1e-4
+    got16 = dev.gemv(x, [w], out_dtype=torch.bfloat16).float().cpu().numpy()
+    assert nerr(got16, exp) <= BF16_TOL
+
+
+def _w4(rows, K, seed, dev):
+    rng = orc.Xorshift(seed)
+    q = np.clip(np.floor(rng.uniform(rows * K) * 8.0), -8, 7).astype(np.int8)
+    packed = orc.w4_pack(q)
+    scales = 0.02 / 4.6 * (1.0 + 0.25 * np.abs(rng.uniform(rows, K // 64)))
+    st, sv = bf16t(scales, dev)
+    pt = torch.tensor(packed.reshape(rows, K // 2), device=dev.torch_device)
+    return q, packed, pt, st, sv
+
+
+@pytest.mark.parametrize("batch", [1, 5, 16])
+@pytest.mark.parametrize("K,rows", [(128, 16), (2048, 256), (8192, 32)])
+def test_gemv_w4(dev, batch, K, rows):
+    q, packed, pt, st, sv = _w4(rows, K, 31 + batch, dev)
+    x, xv = bf16t(normal(32, batch, K), dev)
+    exp = orc.w4_gemv(packed, sv, xv, rows, group=64)
+    got = dev.gemv(x, [pt], scales=[st]).cpu().numpy()
+    assert nerr(got, exp) <= 2e-4
+
+
+def test_w4_unpack_is_bit_exact(dev):
+    q, packed, pt, _, _ = _w4(64, 512, 77, dev)
+    got = dev.w4_unpack(pt.reshape(-1), q.size).cpu().numpy()
+    assert np.array_equal(got, q.astype(np.float32))
+    assert np.array_equal(got.astype(np.float64), orc.w4_unpack(packed, q.size))
+    allb = torch.arange(256, dtype=torch.uint8, device=dev.torch_device)
+    got = dev.w4_unpack(allb, 512).cpu().numpy().reshape(256, 2)
+    assert np.array_equal(got[:, 0], (np.arange(256) & 15) - 8.0) and np.array_equal(got[:, 1], (np.arange(256) >> 4) - 8.0)
+
+
+def test_gemv_segments_and_epilogues(dev):
+    from sanic_b200 import abi
+    batch, K = 4, 512
+    x, xv = bf16t(normal(41, batch, K), dev)
+    ws = [bf16t(normal(42 + i, r, K) * 0.05, dev) for i, r in enumerate((128, 32, 32))]
+    outs = dev.gemv(x, [w for w, _ in ws])
+    for (w, wv), o in zip(ws, outs):
+        assert nerr(o.cpu().numpy(), orc.gemv_bf16w(orc.to_bf16_bits(wv), xv)) <= 1e-4
+    # silu(a) * b over a weight pair
+    a = orc.gemv_bf16w(orc.to_bf16_bits(ws[1][1]), xv)
+    b = orc.gemv_bf16w(orc.to_bf16_bits(ws[2][1]), xv)
+    exp = (a * (1.0 / (1.0 + np.exp(-a)))) * b
+    got = dev.gemv(x, [ws[1][0], ws[2][0]], epilogue=abi.EPI_SILU_MUL)
+    assert nerr(got.cpu().numpy(), exp) <= 1e-4
+    # residual add, in place on the f32 residual stream
+    res = f32t(normal(49, batch, 128), dev)
+    exp = res.cpu().numpy().astype(np.float64) + orc.gemv_bf16w(orc.to_bf16_bits(ws[0][1]), xv)
+    import ctypes as C
+    p = dev.gemv_params(x, [ws[0][0]], [res], None, abi.EPI_RESIDUAL_ADD, res, abi.F32)
+    dev._check(dev.lib.sanic_gemv(dev.h, C.byref(p), dev.stream()), "gemv")
+    assert nerr(res.cpu().numpy(), exp) <= 1e-4
+
+
+def test_gemv_rejects_bad_arguments(dev):
+    from sanic_b200 import RunError
+    x = torch.zeros(17, 256, dtype=torch.bfloat16, device=dev.torch_device)
+    w = torch.zeros(16, 256, dtype=torch.bfloat16, device=dev.torch_device)
+    with pytest.raises(RunError):
+        dev.gemv(x, [w])          # batch > 16
+    with pytest.raises(RunError):
+        dev.gemv(x[:2, :100].contiguous(), [w[:, :100].contiguous()])   # K not a multiple of 64
+
+
+# ───────────────────────── extremum index, pointwise, typed stores ─────────────────────────
+def test_argmax_first_maximum(dev):
+    x = f32t([[2, 5, 5, 1, 5, 2, 0, 5]], dev)
+    assert dev.argmax(x).cpu().tolist() == [1]      # reference tests/compile.rs:139-171
+    rng = orc.Xorshift(0xA6A5)
+    logits = rng.uniform(5, 20); logits[:, 3] = 9.0; logits[:, 11] = 9.0
+    assert dev.argmax(f32t(logits, dev)).cpu().tolist() == [3] * 5
+    big = orc.round_to(orc.DT_F32, normal(99, 16, 128256))
+    big[3, 77777] = big[3, 100000] = 50.0
+    exp = orc.argmax(big).astype(np.int64)
+    assert exp[3] == 77777
+    assert np.array_equal(dev.argmax(f32t(big, dev)).cpu().numpy().astype(np.int64), exp)
+
+
+def test_round_to_bf16_bit_exact(dev):
+    vals = np.array([0.0, -0.0, 1.0, 1.0 + 1.0 / 512.0, 1.0 + 3.0 / 512.0, -1.0 - 1.0 / 512.0, 65504.0, 3.4e38, -3.4e38,
+                     np.inf, -np.inf, 1e-40, math.pi, -math.e, 0.1, 123456789.0], dtype=np.float64)  # tests/metal.rs:2177-2250
+    rnd = orc.Xorshift(5).normal(100000) * np.exp(orc.Xorshift(6).uniform(100000) * 30.0)
+    allv = np.concatenate([vals, rnd]).astype(np.float32)
+    got = dev.round_to_bf16_bits(torch.tensor(allv, device=dev.torch_device)).cpu().numpy().view(np.uint16)
+    assert np.array_equal(got, orc.to_bf16_bits(allv.astype(np.float64)))
+    nan = dev.round_to_bf16_bits(torch.tensor([float("nan")], device=dev.torch_device)).cpu().numpy().view(np.uint16)
+    assert (nan[0] & 0x7FC0) == 0x7FC0
+
+
+def test_u32_store_saturates(dev):
+    x = torch.tensor([0.0, 3.0, 128255.0, float("inf"), 5e9, -1.0], device=dev.torch_device)
+    got = dev.store_u32_saturating(x).cpu().numpy().view(np.uint32)
+    assert got.tolist() == [0, 3, 128255, 0xFFFFFFFF, 0xFFFFFFFF, 0]   # reference src/emit_metal.rs:186-190
+
+
+def test_rmsnorm_and_rope(dev):
+    x = orc.round_to(orc.DT_F32, normal(61, 5, 2048))
+    g, gv = bf16t(1.0 + 0.1 * normal(62, 2048), dev)
+    exp = orc.round_to(orc.DT_BF16, orc.rms_norm(x, gv))
+    got = dev.rmsnorm(f32t(x, dev), g).float().cpu().numpy()
+    assert nerr(got, exp) <= 2.0 ** -7      # at most one bf16 ulp on a rounding boundary
+    assert np.mean(got == exp) > 0.999
+    # rotate-half RoPE on bf16 rows, positions 0..seq-1 (reference src/nn.rs:176-194)
+    xr, xrv = bf16t(normal(63, 2, 3, 40, 64), dev)
+    inv = orc.rope_inv_freq(500000.0, 32)
+    table = dev.rope_table(list(inv), 48)
+    exp = orc.round_to(orc.DT_BF16, orc.rope(xrv, np.arange(40.0)[None, None, :], inv))
+    got = dev.rope_bf16(xr, table).float().cpu().numpy()
+    assert nerr(got, exp) <= 2.0 ** -7
+    assert np.mean(got == exp) > 0.995
+
+
+def test_embed_gather(dev):
+    t, tv = bf16t(normal(71, 50, 64), dev)
+    tok = torch.tensor([3, 49, 0], dtype=torch.int32, device=dev.torch_device)
+    assert np.array_equal(dev.embed_gather(t, tok).cpu().numpy().astype(np.float64), tv[[3, 49, 0]])
