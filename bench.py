@@ -1,0 +1,353 @@
+#!/usr/bin/env python
+"""Benchmark of the hot path: long-context split-KV decode attention (BASELINE.json config 5).
+
+    python bench.py --gpus N --steps K --warmup W [--impl reference]
+
+One step = one decode-attention pass over the whole KV cache (batch 4, 32 query heads, 8 KV
+heads, head_dim 128, bf16, 1,048,576 keys per sequence, sharded along the sequence over N
+GPUs): each GPU folds its slice to (m, l, o) carriers, the carriers are all-gathered over NCCL
+and merged with the derived combine. `value` is whole-job algorithmic HBM GB/s (K and V bytes of
+all ranks divided by the max-over-ranks device time); total work is fixed as N grows (strong
+scaling). Inputs are seeded synthetic N(0,1) tensors; each rank's slice (>= 2 GB) is far larger
+than L2, so every step streams from HBM.
+
+Extra objects on the JSON line: `roofline` (dominant kernel, live CUDA-event timing),
+`cpu_baseline` (the CPU oracle timed on a bounded sample), `e2e` (host q in, host output out),
+`clocks`, `gpu_launches`, and at N=1 a `suite` with the other single-GPU configurations.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+B, HQ, HKV, D = 4, 32, 8, 128
+L_FULL = 1 << 20
+METRIC = "split-KV decode attention HBM throughput (B4 Hq32 Hkv8 D128 bf16, 1,048,576 keys/sequence)"
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        d = json.load(open(path))
+        return float(d["hbm_gbs"]), float(d.get("bf16_tflops", 1590.0)), "measured"
+    return 6650.0, 1590.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.proc, self.lines = index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                                          "-lms", "100", "-i", str(self.index)], stdout=subprocess.PIPE, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unsampled"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        mhz, mx, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            parts = [p.strip() for p in ln.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                mhz.append(float(parts[0]))
+                mx = float(parts[1])
+            except ValueError:
+                continue
+            for n, v in zip(names, parts[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        mhz.sort()
+        top = mhz[len(mhz) // 2:] if mhz else []     # samples under load: the upper half
+        return {"sm_mhz": (top[len(top) // 2] if top else None), "sm_max_mhz": mx, "reasons": sorted(reasons),
+                "samples": len(mhz)}
+
+
+# ───────────────────────── CPU reference arm / cpu_baseline ─────────────────────────
+def cpu_sample(l_sample: int, repeats: int = 1, seed: int = 1234):
+    """The oracle (a restatement of the reference's dense f64 interpreter path) on a bounded sample:
+    all 4x32 heads, `l_sample` keys per sequence. Returns (GB/s of bf16 K+V bytes, seconds, threads)."""
+    import numpy as np
+    from oracle import oracle as orc
+    rng = np.random.default_rng(seed)
+    q = orc.round_to(orc.DT_BF16, rng.standard_normal((B, HQ, 1, D)))
+    k = orc.round_to(orc.DT_BF16, rng.standard_normal((B, HKV, l_sample, D)))
+    v = orc.round_to(orc.DT_BF16, rng.standard_normal((B, HKV, l_sample, D)))
+    best = float("inf")
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        orc.sdpa(q, k, v, enable_gqa=True)
+        best = min(best, time.perf_counter() - t0)
+    nbytes = 2 * B * HKV * l_sample * D * 2
+    return nbytes / best / 1e9, best, orc.num_threads()
+
+
+def run_reference(args):
+    """Reference arm: the CPU interpreter path on the box's host cores. The reference is Rust and
+    cannot be built here, so this times the oracle port with every host thread OpenMP gives it."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    l_sample = args.cpu_sample_keys
+    times = []
+    for i in range(args.warmup + args.steps):
+        gbs, sec, threads = cpu_sample(l_sample, 1, seed=1234 + i)
+        if i >= args.warmup:
+            times.append(sec)
+    sec = sum(times) / len(times)
+    nbytes = 2 * B * HKV * l_sample * D * 2
+    val = nbytes / sec / 1e9
+    sample = f"{l_sample} of {L_FULL} keys per sequence, all {B}x{HQ} heads, dense f64, {threads} OpenMP threads"
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": val, "unit": "GB/s", "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "f64", "data": "synthetic",
+        "config": {"workload": "split-KV decode attention, CPU interpreter path, bounded sample", "sample": sample},
+        "cpu_baseline": {"value": val, "unit": "GB/s", "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": val, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+# ───────────────────────── single-GPU suite (other configurations) ─────────────────────────
+def time_events(fn, steps, warmup, torch):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+    for a, b in evs:
+        a.record()
+        fn()
+        b.record()
+    torch.cuda.synchronize()
+    ts = sorted(a.elapsed_time(b) for a, b in evs)
+    return ts[len(ts) // 2] * 1e-3, ts[0] * 1e-3
+
+
+def suite(dev, torch, hbm_peak, tf_peak, quick):
+    import numpy as np
+    from sanic_b200 import llama
+    out = {}
+    td = dev.torch_device
+    g = torch.Generator(device=td)
+    g.manual_seed(7)
+    # config 1: f32 naive attention Q[256x64] K,V[1024x64] (launch-latency bound parity case)
+    q = torch.randn(1, 1, 256, 64, generator=g, device=td)
+    k = torch.randn(1, 1, 1024, 64, generator=g, device=td)
+    v = torch.randn(1, 1, 1024, 64, generator=g, device=td)
+    med, best = time_events(lambda: dev.attn_fwd_f32(q, k, v, scale=0.125), 20, 3, torch)
+    out["c1_attn_f32_us"] = {"median": med * 1e6, "min": best * 1e6}
+    # config 4: Llama-3.2-1B-architecture decode step, ctx 1024 (+32 steps), CUDA-graph replays
+    cfg = llama.LLAMA_3_2_1B
+    for name, batch, w4 in (("bf16_b1", 1, False), ("bf16_b16", 16, False), ("int4_b1", 1, True)):
+        w = llama.random_weights(cfg, 11, td, w4=w4)
+        m = llama.LlamaMachine(dev, cfg, w, ctx=1088, batch=batch, w4=w4)
+        rng = np.random.default_rng(3)
+        # prefill 1024 positions from random token ids by decoding on the device
+        for p in range(1024 if not quick else 64):
+            if p % 64 == 0:
+                m.set_state(rng.integers(0, cfg["vocab"], size=batch).astype(np.int32), p)
+            m.step()
+        m.sync()
+        m.set_state(rng.integers(0, cfg["vocab"], size=batch).astype(np.int32), 1024)
+        for _ in range(3):
+            m.step()
+        m.sync()
+        secs = [m.step(timed=True) for _ in range(32)]
+        sec = sorted(secs)[len(secs) // 2]
+        kv_bytes = batch * cfg["layers"] * 2 * cfg["kv_heads"] * 1040 * cfg["head_dim"] * 2
+        wb = m.weight_bytes()
+        out[f"c4_llama_decode_{name}"] = {
+            "tok_per_s": batch / sec, "ms_per_step": sec * 1e3, "launches_per_step": m.kernel_count,
+            "algorithmic_bytes": wb + kv_bytes, "achieved_gbs": (wb + kv_bytes) / sec / 1e9,
+            "frac_of_hbm_peak": (wb + kv_bytes) / sec / 1e9 / hbm_peak}
+        del m, w
+        torch.cuda.empty_cache()
+    return out
+
+
+# ───────────────────────── the product arm ─────────────────────────
+def run_ours(args):
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+    import sanic_b200
+    from sanic_b200.splitkv import SplitKVDecoder, shard_range
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    dev = sanic_b200.CudaDevice(local)
+    td = dev.torch_device
+    hbm_peak, tf_peak, peak_kind = measured_peaks()
+
+    L = args.kv_len
+    lo, hi = shard_range(L, rank, world)
+    n_local = hi - lo
+    g = torch.Generator(device=td)
+    g.manual_seed(1000 + rank)
+    k = torch.empty((B, HKV, n_local, D), dtype=torch.bfloat16, device=td)
+    v = torch.empty_like(k)
+    for t in (k, v):                       # chunked fill keeps the f32 temporaries small
+        for b in range(B):
+            for h in range(HKV):
+                t[b, h].copy_(torch.randn(n_local, D, generator=g, device=td, dtype=torch.float32))
+    total = args.steps + args.warmup
+    gq = torch.Generator(device="cpu")
+    gq.manual_seed(77)                     # the same queries on every rank
+    q_host = torch.randn(total, B, HQ, D, generator=gq).to(torch.bfloat16).pin_memory()
+    q_dev = q_host.to(td)
+    out_host = torch.empty((B, HQ, D), dtype=torch.bfloat16).pin_memory()
+    dec = SplitKVDecoder(dev, k, v)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(step_fn):
+        for i in range(args.warmup):
+            step_fn(i)
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(args.steps):
+            step_fn(args.warmup + i)
+        e1.record()
+        barrier()
+        ms = torch.tensor([e0.elapsed_time(e1)], device=td)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item()) * 1e-3
+
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    # device-resident inputs
+    sec = timed(lambda i: dec.step(q_dev[i]))
+
+    # end to end through the public call: q from pinned host memory, result read back to the host
+    def e2e_step(i):
+        qd = q_host[i].to(td, non_blocking=True)
+        o = dec.step(qd)
+        out_host.copy_(o, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+    sec_e2e = timed(e2e_step)
+    clocks = sampler.stop() if rank == 0 else None
+
+    # dominant kernel alone (the local fold), live CUDA events on the launching stream
+    import ctypes as C
+    car = torch.empty((B * HQ, D + 2), dtype=torch.float32, device=td)
+    p, _keep = dev.decode_params(q_dev[0], k, v, n_local, n_splits=dec.n_splits, carrier_out=car)
+    def fold_only():
+        dev._check(dev.lib.sanic_attn_decode_splitkv(dev.h, C.byref(p), dev.stream()), "decode")
+    evs = []
+    for i in range(3 + args.steps):
+        a, b_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(); fold_only(); b_.record()
+        if i >= 3:
+            evs.append((a, b_))
+    torch.cuda.synchronize()
+    kt = torch.tensor([sum(a.elapsed_time(b_) for a, b_ in evs) / len(evs) * 1e-3], device=td)
+    if world > 1:
+        dist.all_reduce(kt, op=dist.ReduceOp.MAX)
+    kern_sec = float(kt.item())
+
+    bytes_total = 2 * B * HKV * L * D * 2
+    bytes_local = 2 * B * HKV * n_local * D * 2
+    line = None
+    if rank == 0:
+        achieved = bytes_local / kern_sec / 1e9
+        line = {
+            "metric": METRIC, "value": bytes_total * args.steps / sec / 1e9, "unit": "GB/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec / args.steps * 1e3,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": f"split-KV decode attention B{B} Hq{HQ} Hkv{HKV} D{D} bf16, {L} keys/sequence "
+                                   f"sharded over {world} GPU(s) on the sequence axis",
+                       "kv_bytes_total": bytes_total, "n_splits_per_gpu": dec.n_splits,
+                       "l2": "inputs larger than L2 (>= 2 GB per GPU per step), no flush needed",
+                       "exchange": "NCCL all-gather of (m,l,o) carriers + derived combine" if world > 1 else "none (1 GPU)"},
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
+                         "frac": achieved / hbm_peak, "traffic": TRAFFIC_RATIO_DECODE * bytes_local if TRAFFIC_RATIO_DECODE else None,
+                         "kernel": "attn_decode_kernel<128,false>", "peak_kind": f"of {peak_kind}",
+                         "kernel_ms": kern_sec * 1e3, "algorithmic_bytes_per_launch": bytes_local},
+            "e2e": {"value": bytes_total * args.steps / sec_e2e / 1e9, "unit": "GB/s",
+                    "h2d_bytes_per_step": B * HQ * D * 2, "d2h_bytes_per_step": B * HQ * D * 2,
+                    "ms_per_step": sec_e2e / args.steps * 1e3},
+            "gpu_launches": args.steps * (1 if world == 1 else 2),
+            "clocks": clocks,
+        }
+        if not args.no_cpu and world == 1:
+            gbs, csec, threads = cpu_sample(args.cpu_sample_keys, 1)
+            line["cpu_baseline"] = {"value": gbs, "unit": "GB/s", "cores": threads, "kind": "port",
+                                    "sample": f"{args.cpu_sample_keys} of {L} keys per sequence, all {B}x{HQ} heads, "
+                                              f"dense f64 oracle, {csec:.2f} s"}
+    del dec, k, v
+    torch.cuda.empty_cache()
+    if rank == 0 and world == 1 and not args.no_suite:
+        try:
+            line["suite"] = suite(dev, torch, hbm_peak, tf_peak, args.quick)
+        except Exception as e:  # the headline line must still print
+            line["suite"] = {"error": repr(e)}
+    if rank == 0:
+        print(json.dumps(line))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+# dram bytes / algorithmic bytes of attn_decode_kernel from the ncu capture summarised in
+# profiles/attn_decode_splitkv.md (None until a capture exists)
+TRAFFIC_RATIO_DECODE = None
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--kv-len", type=int, default=L_FULL)
+    ap.add_argument("--cpu-sample-keys", type=int, default=4096)
+    ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--no-suite", action="store_true")
+    ap.add_argument("--quick", action="store_true", help="shorter prefill in the suite")
+    args = ap.parse_args()
+    if args.warmup < 3:
+        args.warmup = 3
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

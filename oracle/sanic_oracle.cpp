@@ -193,10 +193,13 @@ Value matmul(const Value& a, const Value& b) {
             const double* ar = &a.data[(bi * m + i) * k];
             const double* bb = &b.data[bi * k * n];
             double* orow = &o.data[(bi * m + i) * n];
-            for (size_t j = 0; j < n; ++j) {
-                double acc = 0.0;  // Monoid::Add identity, left fold over k
-                for (size_t kk = 0; kk < k; ++kk) acc = acc + ar[kk] * bb[kk * n + j];
-                orow[j] = acc;
+            // every output starts at the Add identity and takes its k terms in index order;
+            // the k loop is outermost only so that the inner loop walks memory contiguously
+            for (size_t j = 0; j < n; ++j) orow[j] = 0.0;
+            for (size_t kk = 0; kk < k; ++kk) {
+                const double a_ik = ar[kk];
+                const double* brow = bb + kk * n;
+                for (size_t j = 0; j < n; ++j) orow[j] = orow[j] + a_ik * brow[j];
             }
         }
     return o;

@@ -46,16 +46,19 @@ __global__ void __launch_bounds__(128) attn_fwd_f32_kernel(sanic_attn_params p) 
     for (int e = 0; e < DV; ++e) o[e] = 0.0f;
 
     for (int j = lo + lane; j < hi; j += 32) {
-        const float4* kr = (const float4*)(K + (size_t)j * E);
         float s = 0.0f;
-        for (int d4 = 0; d4 < E / 4; ++d4) {
-            float4 kv = kr[d4];
-            s = fmaf(qs[4 * d4 + 0], kv.x, s);
-            s = fmaf(qs[4 * d4 + 1], kv.y, s);
-            s = fmaf(qs[4 * d4 + 2], kv.z, s);
-            s = fmaf(qs[4 * d4 + 3], kv.w, s);
+        if ((E & 3) == 0) {
+            const float4* kr = (const float4*)(K + (size_t)j * E);
+            for (int d4 = 0; d4 < E / 4; ++d4) {
+                float4 kv = kr[d4];
+                s = fmaf(qs[4 * d4 + 0], kv.x, s);
+                s = fmaf(qs[4 * d4 + 1], kv.y, s);
+                s = fmaf(qs[4 * d4 + 2], kv.z, s);
+                s = fmaf(qs[4 * d4 + 3], kv.w, s);
+            }
+        } else {
+            for (int d = 0; d < E; ++d) s = fmaf(qs[d], K[(size_t)j * E + d], s);
         }
-        for (int d = E & ~3; d < E; ++d) s = fmaf(qs[d], K[(size_t)j * E + d], s);
         s *= p.scale;
         if (p.mask) s += p.mask[(size_t)row * S + j];
         // element lift (s, 1, v) combined into the running accumulator
@@ -97,8 +100,7 @@ extern "C" int32_t sanic_attn_fwd_f32(sanic_ctx* ctx, const sanic_attn_params* p
     SANIC_REQUIRE(ctx, p->batch > 0 && p->q_heads > 0 && p->kv_heads > 0 && p->q_heads % p->kv_heads == 0,
                   "attn_fwd_f32: query heads must be a multiple of key/value heads");
     SANIC_REQUIRE(ctx, p->q_len > 0 && p->kv_len > 0, "attn_fwd_f32: empty sequence");
-    SANIC_REQUIRE(ctx, p->head_dim > 0 && p->head_dim % 4 == 0 && p->head_dim <= 1024,
-                  "attn_fwd_f32: head_dim must be a multiple of 4");
+    SANIC_REQUIRE(ctx, p->head_dim > 0 && p->head_dim <= 1024, "attn_fwd_f32: head_dim must be in [1, 1024]");
     SANIC_REQUIRE(ctx, p->v_dim > 0 && p->v_dim <= 128, "attn_fwd_f32: v_dim must be in [1, 128]");
     SANIC_REQUIRE(ctx, p->out_dtype == SANIC_F32, "attn_fwd_f32: output is f32");
     SANIC_REQUIRE(ctx, !(p->causal && p->mask), "attn_fwd_f32: attn_mask and is_causal cannot both be set");

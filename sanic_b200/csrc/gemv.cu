@@ -274,8 +274,9 @@ extern "C" int32_t sanic_gemv(sanic_ctx* ctx, const sanic_gemv_params* p, void* 
     SegTable segs{};
     int tiles = 0;
     for (int i = 0; i < p->n_segments; ++i) {
-        SANIC_REQUIRE(ctx, p->w[i] && p->out[i] && p->rows[i] > 0 && p->rows[i] % 16 == 0,
+        SANIC_REQUIRE(ctx, p->w[i] && p->rows[i] > 0 && p->rows[i] % 16 == 0,
                       "gemv: segment rows must be a positive multiple of 16");
+        SANIC_REQUIRE(ctx, p->out[i] || (dual && i == 1), "gemv: null output");
         SANIC_REQUIRE(ctx, ((uintptr_t)p->w[i] % 16) == 0, "gemv: weights must be 16-byte aligned");
         SANIC_REQUIRE(ctx, p->weight_dtype != SANIC_I4 || p->scales[i], "gemv: int4 weights need scales");
         segs.w[i] = p->w[i];
