@@ -67,6 +67,10 @@ class CudaDevice:
     def stream(self):
         return C.c_void_p(torch.cuda.current_stream(self.torch_device).cuda_stream)
 
+    def sync(self):
+        """Wait for the current stream and surface any device-side status (bounded waits that ran out)."""
+        self._check(self.lib.sanic_sync(self.h, self.stream()), "sync")
+
     def specs(self) -> dict:
         s = abi.DeviceSpecs()
         self._check(self.lib.sanic_specs(self.h, C.byref(s)), "specs")

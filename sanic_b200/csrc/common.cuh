@@ -21,6 +21,10 @@ struct sanic_ctx {
     int nccl_rank = 0, nccl_nranks = 1;
     // cached driver entry point for tensor-map encoding (gemm_rmsnorm.cu)
     void* encode_tiled = nullptr;
+    // device-side status word in mapped pinned memory: kernels with bounded waits write a
+    // nonzero code here, the host reads it without a synchronising copy
+    int* status_host = nullptr;
+    int* status_dev = nullptr;
 };
 
 static inline int32_t sanic_fail(sanic_ctx* ctx, int32_t code, const std::string& msg) {

@@ -1,5 +1,365 @@
+// Deferred-normaliser contraction (RMSNorm-fused GEMM) on the 5th-generation tensor cores.
+//
+//   y[i,j] = (sum_k x[i,k] * g[k] * W[k,j]) / sqrt(sum_k x[i,k]^2 / K + eps)
+//
+// The derived carrier has two Plain(Add) slots over the same K stream and a project that
+// divides once at the end (reference tests/laws.rs:620-646, src/partition.rs:2591-2608), so
+// the main loop is a plain tensor-core GEMM on A' = bf16(x * g) and the epilogue scales each
+// row by 1/sqrt(.). The fusion lives in the prologue of each K stage: the A tile that TMA
+// brought into shared memory is rewritten in place (x * g) by a transform warpgroup, which also
+// accumulates sum x^2 per row from the same bytes; x is read from HBM exactly once.
+//
+// Persistent kernel, one CTA per SM, 128x256 output tile, BK = 64, 4-stage TMA ring.
+//   warp 0      TMA producer (cp.async.bulk.tensor, 128B swizzle, mbarrier complete_tx)
+//   warp 1      MMA issuer (tcgen05.mma cta_group::1 kind::f16, M=128 N=256 K=16 per instruction)
+//   warp 2      TMEM allocator (512 columns = two 128x256 f32 accumulators, double buffered)
+//   warps 4-11  A transform: x*g in place + sum x^2 (two threads per row)
+//   warps 12-15 epilogue: tcgen05.ld, * rsqrt, bf16/f32 stores, overlapped with the next tile
+// Every mbarrier wait is bounded; on expiry the kernel records an error code in the context's
+// status word, drains and frees its TMEM, and the next sanic_sync returns SANIC_ERR_TIMEOUT.
+//
+// Roofline: tensor-bound. FLOPs = 2*M*N*K; HBM bytes = x + W + y (about 117 MB at
+// 4096x2048x8192, 61 us at 2.25 PFLOP/s).
+#include <cuda.h>
+
 #include "common.cuh"
+
+namespace {
+using namespace sanic;
+
+constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4;
+constexpr int A_BYTES = BM * BK * 2;          // 16 KB
+constexpr int B_BYTES = BN * BK * 2;          // 32 KB
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int MAX_K = 8192;
+constexpr int NTHREADS = 512;
+constexpr uint32_t SPIN_LIMIT = 1u << 24;
+
+struct Shared {
+    uint64_t full[STAGES], ready[STAGES], empty[STAGES];
+    uint64_t tmem_full[2], tmem_empty[2], ss_full[2], ss_empty[2];
+    uint32_t tmem_base;
+    volatile int abort_flag;
+    float ss[2][2][BM];   // [accumulator slot][row half][row]
+};
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+// Bounded wait. Returns false if the limit ran out or another role already gave up.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, Shared* sh, int* err, int code) {
+    uint32_t addr = smem_u32(bar);
+    for (uint32_t it = 0; it < SPIN_LIMIT; ++it) {
+        uint32_t done;
+        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                     : "=r"(done) : "r"(addr), "r"(parity) : "memory");
+        if (done) return true;
+        if ((it & 1023u) == 1023u && sh->abort_flag) return false;
+    }
+    sh->abort_flag = 1;
+    atomicCAS(err, 0, code);
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                 ::"r"(dst), "l"((uint64_t)map), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                 ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Shared-memory matrix descriptor (128B swizzle). lbo / sbo in bytes.
+__device__ __forceinline__ uint64_t make_desc(uint32_t saddr, uint32_t lbo, uint32_t sbo) {
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr >> 4) & 0x3FFF);
+    d |= (uint64_t)((lbo >> 4) & 0x3FFF) << 16;
+    d |= (uint64_t)((sbo >> 4) & 0x3FFF) << 32;
+    d |= (uint64_t)1 << 46;   // descriptor version of this architecture
+    d |= (uint64_t)2 << 61;   // SWIZZLE_128B
+    return d;
+}
+
+struct Pipe {
+    int stage = 0;
+    uint32_t phase = 0;
+    __device__ void advance() { if (++stage == STAGES) { stage = 0; phase ^= 1; } }
+};
+
+__global__ void __launch_bounds__(NTHREADS, 1)
+gemm_rmsnorm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                    const uint16_t* __restrict__ gamma, void* __restrict__ y, int M, int N, int K, int w_is_nk,
+                    float eps, int out_dtype, int* err) {
+    extern __shared__ unsigned char smem_dyn[];
+    const uint32_t raw = smem_u32(smem_dyn);
+    const uint32_t base = (raw + 1023u) & ~1023u;              // swizzle atoms need 1024-byte alignment
+    unsigned char* aligned = smem_dyn + (base - raw);
+    uint16_t* gsm = (uint16_t*)(aligned + STAGES * STAGE_BYTES);  // gamma, padded to a multiple of BK
+    Shared* sh = (Shared*)(aligned + STAGES * STAGE_BYTES + MAX_K * 2);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int kblocks = (K + BK - 1) / BK;
+    const int m_tiles = (M + BM - 1) / BM, n_tiles = (N + BN - 1) / BN;
+    const int tiles = m_tiles * n_tiles;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) { mbar_init(&sh->full[s], 1); mbar_init(&sh->ready[s], 8); mbar_init(&sh->empty[s], 1); }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(&sh->tmem_full[a], 1); mbar_init(&sh->tmem_empty[a], 4);
+            mbar_init(&sh->ss_full[a], 8); mbar_init(&sh->ss_empty[a], 4);
+        }
+        sh->abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    for (int i = threadIdx.x; i < kblocks * BK; i += NTHREADS) gsm[i] = (i < K) ? gamma[i] : (uint16_t)0;
+    if (warp == 2) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sh->tmem_base)), "r"(512));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = sh->tmem_base;
+
+    if (warp == 0) {
+        // ── TMA producer ──
+        if (lane == 0) {
+            Pipe p; p.phase = 1;
+            bool ok = true;
+            for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
+                const int m0 = (t % m_tiles) * BM, n0 = (t / m_tiles) * BN;
+                for (int kb = 0; kb < kblocks; ++kb) {
+                    ok = mbar_wait(&sh->empty[p.stage], p.phase, sh, err, 1);
+                    if (!ok) break;
+                    const uint32_t sa = base + p.stage * STAGE_BYTES, sb = sa + A_BYTES;
+                    mbar_expect_tx(&sh->full[p.stage], STAGE_BYTES);
+                    tma_load_2d(sa, &map_a, &sh->full[p.stage], kb * BK, m0);
+                    if (w_is_nk) {
+                        tma_load_2d(sb, &map_b, &sh->full[p.stage], kb * BK, n0);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < BN / 64; ++j)
+                            tma_load_2d(sb + j * (64 * BK * 2), &map_b, &sh->full[p.stage], n0 + 64 * j, kb * BK);
+                    }
+                    p.advance();
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ── MMA issuer ──
+        if (lane == 0) {
+            // instruction descriptor: D f32, A/B bf16, A K-major, B K- or MN-major, N=256, M=128
+            const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((w_is_nk ? 0u : 1u) << 16) |
+                                   ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+            Pipe p;
+            int use = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x, ++use) {
+                const int a = use & 1;
+                ok = mbar_wait(&sh->tmem_empty[a], ((use >> 1) & 1) ^ 1, sh, err, 2);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t acc = tmem + a * BN;
+                for (int kb = 0; kb < kblocks; ++kb) {
+                    ok = mbar_wait(&sh->ready[p.stage], p.phase, sh, err, 3);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint32_t sa = base + p.stage * STAGE_BYTES, sb = sa + A_BYTES;
+                    const uint64_t adesc = make_desc(sa, 16, 1024);
+                    const uint64_t bdesc = w_is_nk ? make_desc(sb, 16, 1024) : make_desc(sb, 64 * BK * 2, 1024);
+#pragma unroll
+                    for (int k = 0; k < BK / 16; ++k) {
+                        // K-major: 16 elements = 32 bytes along the swizzled row; MN-major: 16 k-rows = 2048 bytes
+                        const uint64_t ad = adesc + (uint64_t)(k * 2);
+                        const uint64_t bd = bdesc + (uint64_t)(w_is_nk ? k * 2 : k * 128);
+                        umma_f16(acc, ad, bd, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                    }
+                    umma_commit(&sh->empty[p.stage]);      // stage reusable once these MMAs have read it
+                    p.advance();
+                }
+                if (ok) umma_commit(&sh->tmem_full[a]);
+            }
+        }
+    } else if (warp >= 4 && warp < 12) {
+        // ── A transform: x*g in place, sum x^2 ──
+        const int idx = threadIdx.x - 128;
+        const int row = idx & (BM - 1), half = idx >> 7;   // half 0: chunks 0-3, half 1: chunks 4-7
+        Pipe p;
+        int use = 0;
+        bool ok = true;
+        for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x, ++use) {
+            const int a = use & 1;
+            float ss = 0.0f;
+            for (int kb = 0; kb < kblocks; ++kb) {
+                ok = mbar_wait(&sh->full[p.stage], p.phase, sh, err, 4);
+                if (!ok) break;
+                unsigned char* arow = aligned + p.stage * STAGE_BYTES + row * 128;
+#pragma unroll
+                for (int c4 = 0; c4 < 4; ++c4) {
+                    const int c = half * 4 + c4;
+                    uint4* ptr = (uint4*)(arow + ((c ^ (row & 7)) << 4));
+                    uint4 v = *ptr;
+                    const uint4 gv = *(const uint4*)(gsm + kb * BK + c * 8);
+                    uint32_t xs[4] = {v.x, v.y, v.z, v.w};
+                    const uint32_t gs[4] = {gv.x, gv.y, gv.z, gv.w};
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        float x0 = bf16lo(xs[j]), x1 = bf16hi(xs[j]);
+                        ss = fmaf(x0, x0, ss); ss = fmaf(x1, x1, ss);
+                        xs[j] = pack_bf16x2(x0 * bf16lo(gs[j]), x1 * bf16hi(gs[j]));
+                    }
+                    *ptr = make_uint4(xs[0], xs[1], xs[2], xs[3]);
+                }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic writes -> visible to the MMA
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&sh->ready[p.stage]);
+                p.advance();
+            }
+            if (!ok) break;
+            ok = mbar_wait(&sh->ss_empty[a], ((use >> 1) & 1) ^ 1, sh, err, 5);
+            if (!ok) break;
+            sh->ss[a][half][row] = ss;
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&sh->ss_full[a]);
+        }
+    } else if (warp >= 12) {
+        // ── epilogue ──
+        const int q = warp & 3;                      // TMEM lane quarter this warp may read
+        const int row = q * 32 + lane;
+        int use = 0;
+        bool ok = true;
+        const float inv_k = 1.0f / (float)K;
+        for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x, ++use) {
+            const int a = use & 1;
+            const int m0 = (t % m_tiles) * BM, n0 = (t / m_tiles) * BN;
+            ok = mbar_wait(&sh->ss_full[a], (use >> 1) & 1, sh, err, 6);
+            if (!ok) break;
+            const float ssv = sh->ss[a][0][row] + sh->ss[a][1][row];
+            const float rstd = 1.0f / sqrtf(ssv * inv_k + eps);
+            ok = mbar_wait(&sh->tmem_full[a], (use >> 1) & 1, sh, err, 7);
+            if (!ok) break;
+            tc_fence_after();
+            const int gr = m0 + row;
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; ++c) {
+                uint32_t r[32];
+                tmem_ld32(tmem + ((uint32_t)(q * 32) << 16) + a * BN + c * 32, r);
+                const int gc = n0 + c * 32;
+                if (gr < M && gc < N) {
+                    if (out_dtype == SANIC_BF16) {
+                        uint32_t pk[16];
+#pragma unroll
+                        for (int j = 0; j < 16; ++j)
+                            pk[j] = pack_bf16x2(__uint_as_float(r[2 * j]) * rstd, __uint_as_float(r[2 * j + 1]) * rstd);
+                        uint16_t* dst = (uint16_t*)y + (size_t)gr * N + gc;
+                        if (gc + 32 <= N) {
+#pragma unroll
+                            for (int j = 0; j < 4; ++j)
+                                *(uint4*)(dst + 8 * j) = make_uint4(pk[4 * j], pk[4 * j + 1], pk[4 * j + 2], pk[4 * j + 3]);
+                        } else {
+                            for (int j = 0; j < 32 && gc + j < N; ++j)
+                                dst[j] = (uint16_t)((j & 1) ? (pk[j >> 1] >> 16) : (pk[j >> 1] & 0xFFFF));
+                        }
+                    } else {
+                        float* dst = (float*)y + (size_t)gr * N + gc;
+                        if (gc + 32 <= N) {
+#pragma unroll
+                            for (int j = 0; j < 8; ++j)
+                                *(float4*)(dst + 4 * j) = make_float4(__uint_as_float(r[4 * j]) * rstd, __uint_as_float(r[4 * j + 1]) * rstd,
+                                                                      __uint_as_float(r[4 * j + 2]) * rstd, __uint_as_float(r[4 * j + 3]) * rstd);
+                        } else {
+                            for (int j = 0; j < 32 && gc + j < N; ++j) dst[j] = __uint_as_float(r[j]) * rstd;
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) { mbar_arrive(&sh->tmem_empty[a]); mbar_arrive(&sh->ss_empty[a]); }
+        }
+    }
+    // teardown: every role has left its loop (normally or after a bounded wait ran out)
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 2) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512));
+    }
+}
+
+typedef CUresult (*encode_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                              const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                              CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+int32_t encode_2d(sanic_ctx* ctx, CUtensorMap* map, const void* ptr, uint64_t inner, uint64_t outer, uint32_t box_inner,
+                  uint32_t box_outer) {
+    if (!ctx->encode_tiled) {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q);
+        if (e != cudaSuccess || !fn) return sanic_fail(ctx, SANIC_ERR_CUDA, "cuTensorMapEncodeTiled is not available");
+        ctx->encode_tiled = fn;
+    }
+    cuuint64_t dims[2] = {inner, outer};
+    cuuint64_t strides[1] = {inner * 2};
+    cuuint32_t box[2] = {box_inner, box_outer};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = ((encode_fn)ctx->encode_tiled)(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims,
+                                                strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                                CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return sanic_fail(ctx, SANIC_ERR_CUDA, "cuTensorMapEncodeTiled failed (" + std::to_string((int)r) + ")");
+    return SANIC_OK;
+}
+}  // namespace
+
 extern "C" int32_t sanic_gemm_rmsnorm(sanic_ctx* ctx, const sanic_gemm_rmsnorm_params* p, void* stream) {
-    (void)p; (void)stream;
-    return sanic_fail(ctx, SANIC_ERR_UNSUPPORTED, "gemm_rmsnorm: not built yet");
+    if (!ctx || !p) return SANIC_ERR_INVALID;
+    SANIC_REQUIRE(ctx, p->x && p->gamma && p->w && p->y, "gemm_rmsnorm: null tensor");
+    SANIC_REQUIRE(ctx, p->M > 0 && p->N > 0 && p->K > 0, "gemm_rmsnorm: empty extent");
+    SANIC_REQUIRE(ctx, p->K % 8 == 0 && p->N % 8 == 0, "gemm_rmsnorm: K and N must be multiples of 8 (16-byte rows)");
+    SANIC_REQUIRE(ctx, p->K <= MAX_K, "gemm_rmsnorm: K is limited to 8192");
+    SANIC_REQUIRE(ctx, ((uintptr_t)p->x % 16) == 0 && ((uintptr_t)p->w % 16) == 0 && ((uintptr_t)p->y % 16) == 0,
+                  "gemm_rmsnorm: tensors must be 16-byte aligned");
+    SANIC_REQUIRE(ctx, p->out_dtype == SANIC_BF16 || p->out_dtype == SANIC_F32, "gemm_rmsnorm: output must be bf16 or f32");
+    sanic_set_device(ctx);
+    CUtensorMap map_a, map_b;
+    int32_t rc = encode_2d(ctx, &map_a, p->x, (uint64_t)p->K, (uint64_t)p->M, BK, BM);
+    if (rc != SANIC_OK) return rc;
+    if (p->w_is_nk) rc = encode_2d(ctx, &map_b, p->w, (uint64_t)p->K, (uint64_t)p->N, BK, BN);
+    else rc = encode_2d(ctx, &map_b, p->w, (uint64_t)p->N, (uint64_t)p->K, 64, BK);
+    if (rc != SANIC_OK) return rc;
+
+    cudaStream_t st = (cudaStream_t)stream;
+    const int smem = STAGES * STAGE_BYTES + MAX_K * 2 + (int)sizeof(Shared) + 1024;
+    SANIC_CUDA_CHECK(ctx, cudaFuncSetAttribute(gemm_rmsnorm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    const int tiles = ((p->M + BM - 1) / BM) * ((p->N + BN - 1) / BN);
+    const int grid = tiles < ctx->sm_count ? tiles : ctx->sm_count;
+    gemm_rmsnorm_kernel<<<grid, NTHREADS, smem, st>>>(map_a, map_b, (const uint16_t*)p->gamma, p->y, p->M, p->N, p->K,
+                                                      p->w_is_nk, p->eps, p->out_dtype, ctx->status_dev);
+    SANIC_LAUNCH_CHECK(ctx, "gemm_rmsnorm");
+    return SANIC_OK;
 }

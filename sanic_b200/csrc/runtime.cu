@@ -34,6 +34,12 @@ int32_t sanic_cuda_open(int32_t ordinal, sanic_ctx** out) {
         delete ctx;
         return SANIC_ERR_UNSUPPORTED;
     }
+    if (cudaHostAlloc((void**)&ctx->status_host, sizeof(int), cudaHostAllocMapped) != cudaSuccess ||
+        cudaHostGetDevicePointer((void**)&ctx->status_dev, ctx->status_host, 0) != cudaSuccess) {
+        delete ctx;
+        return SANIC_ERR_CUDA;
+    }
+    *ctx->status_host = 0;
     *out = ctx;
     return SANIC_OK;
 }
@@ -41,6 +47,7 @@ int32_t sanic_cuda_open(int32_t ordinal, sanic_ctx** out) {
 int32_t sanic_cuda_close(sanic_ctx* ctx) {
     if (!ctx) return SANIC_ERR_INVALID;
     sanic_nccl_shutdown(ctx);
+    if (ctx->status_host) { cudaSetDevice(ctx->device); cudaFreeHost(ctx->status_host); }
     delete ctx;
     return SANIC_OK;
 }
@@ -96,6 +103,12 @@ int32_t sanic_sync(sanic_ctx* ctx, void* stream) {
     if (!ctx) return SANIC_ERR_INVALID;
     sanic_set_device(ctx);
     SANIC_CUDA_CHECK(ctx, cudaStreamSynchronize((cudaStream_t)stream));
+    // a kernel whose bounded wait ran out left its code in the status word
+    int code = *(volatile int*)ctx->status_host;
+    if (code != 0) {
+        *ctx->status_host = 0;
+        return sanic_fail(ctx, SANIC_ERR_TIMEOUT, "a bounded device-side wait ran out (code " + std::to_string(code) + ")");
+    }
     return SANIC_OK;
 }
 

@@ -127,7 +127,8 @@ class LlamaMachine:
                                     ctx)
         tiles = (ctx + 63) // 64
         self.n_splits = max(1, min(tiles, -(-2 * dev.specs()["sm_count"] // (B * Hkv))))
-        self.partials = dev.decode_scratch(B, Hq, D, self.n_splits)
+        # the machine owns its scratch: two machines stepping on different streams must not share one
+        self.partials = z((dev.lib.sanic_attn_decode_scratch_bytes(B, Hq, D, self.n_splits) // 4,), torch.float32)
         self.amax_scratch = z((B * 2 * 256,), torch.float32)
         self.stream = torch.cuda.Stream(device=td)
         self._build()

@@ -359,3 +359,38 @@ def test_embed_gather(dev):
     t, tv = bf16t(normal(71, 50, 64), dev)
     tok = torch.tensor([3, 49, 0], dtype=torch.int32, device=dev.torch_device)
     assert np.array_equal(dev.embed_gather(t, tok).cpu().numpy().astype(np.float64), tv[[3, 49, 0]])
+
+
+# ───────────────────────── deferred-normaliser contraction (tcgen05) ─────────────────────────
+def _gemm_case(dev, M, K, N, w_is_nk, out_dtype=torch.bfloat16, seed=81):
+    x, xv = bf16t(normal(seed, M, K), dev)
+    g, gv = bf16t(1.0 + 0.1 * normal(seed + 1, K), dev)
+    wshape = (N, K) if w_is_nk else (K, N)
+    w, wv = bf16t(0.02 * normal(seed + 2, *wshape), dev)
+    y = dev.gemm_rmsnorm(x, g, w, eps=1e-5, w_is_nk=w_is_nk, out_dtype=out_dtype)
+    dev.sync()     # surfaces a bounded wait that ran out as an error instead of a hang
+    exp = orc.rmsnorm_gemm(xv, gv, wv, eps=1e-5, w_is_nk=w_is_nk)
+    got = y.float().cpu().numpy()
+    # bf16 rounding of x*g (2^-9 per term, random sign) then of the output
+    assert nerr(got, exp) <= BF16_TOL
+    # the carrier form (two Add slots, divide once) is what the kernel computes
+    car = orc.rmsnorm_gemm(xv[:4], gv, wv, eps=1e-5, w_is_nk=w_is_nk, blocks=4)
+    assert nerr(got[:4], car) <= BF16_TOL
+    return got, exp
+
+
+@pytest.mark.parametrize("w_is_nk", [True, False])
+def test_gemm_rmsnorm_one_tile(dev, w_is_nk):
+    _gemm_case(dev, 128, 256, 256, w_is_nk)
+
+
+@pytest.mark.parametrize("w_is_nk", [True, False])
+def test_gemm_rmsnorm_multi_tile_and_edges(dev, w_is_nk):
+    _gemm_case(dev, 384, 512, 768, w_is_nk, out_dtype=torch.float32)
+    _gemm_case(dev, 200, 320, 264, w_is_nk)       # ragged M, K not a multiple of 64, N not a multiple of 256
+
+
+def test_gemm_rmsnorm_many_tiles_per_cta(dev):
+    # more tiles than SMs: exercises the accumulator double buffer and barrier phases
+    got, exp = _gemm_case(dev, 2048, 256, 8192, True)
+    assert got.shape == (2048, 8192)
