@@ -120,7 +120,8 @@ typedef struct {
     int32_t window;           /* 0 = none */
     int32_t n_splits;         /* chunks of the key axis per (batch, kv head) */
     float scale;
-    float* partials;          /* scratch [B*Hq, n_splits, 2 + D] f32 (raw accumulators) */
+    float* partials;          /* scratch of sanic_attn_decode_scratch_bytes() bytes, zero-filled once before its
+                                 first use: raw accumulators [B*Hq, n_splits, 2 + D] then one ticket per (batch, kv head) */
     float* carrier_out;       /* optional [B*Hq, 2 + D] f32: merged raw accumulator (m natural-log units, l, o) */
     void* out;                /* optional projected output [B, Hq, D] */
     int32_t out_dtype;        /* SANIC_F32 or SANIC_BF16 */
@@ -129,6 +130,23 @@ int32_t sanic_attn_decode_splitkv(sanic_ctx* ctx, const sanic_decode_params* p, 
 size_t sanic_attn_decode_scratch_bytes(int32_t batch, int32_t q_heads, int32_t head_dim, int32_t n_splits);
 /* Suggested number of chunks for this device and shape (a multiple of the SM count in CTAs). */
 int32_t sanic_attn_decode_suggest_splits(sanic_ctx* ctx, int32_t batch, int32_t kv_heads, int32_t head_dim, int64_t kv_len);
+
+/* Same fold for callers that cannot allocate device memory. This entry point has no counterpart in
+ * the reference. Some hosts of this library may not call cudaMalloc at the point where they decode:
+ * code running inside a CUDA-graph capture or a latency-critical serving loop where an allocation
+ * would synchronise the device, plugins that are handed a fixed arena by their framework, and
+ * processes whose memory is fully budgeted up front. For them the split-KV scratch lives in a static
+ * device array inside the library (4 MiB of partial accumulators plus 4096 ticket counters, held on
+ * every device that loads the library until the process exits). `p->partials` is ignored; inputs and
+ * outputs are still the caller's. The call fails with SANIC_ERR_INVALID, and says so, when
+ * batch*q_heads*n_splits*(head_dim+2) floats exceed sanic_attn_decode_static_scratch_capacity() bytes
+ * or batch*kv_heads exceeds 4096. It calls no cudaMalloc, cudaFree or allocating library routine.
+ * The first call on a device looks up the array's device address (cudaGetSymbolAddress); make that
+ * first call before starting any stream capture. All calls share the one array and it keeps the last
+ * call's contents: the counters are cleared on the stream at every call, and two calls that overlap
+ * on the GPU (different streams, or different threads) race on it. */
+int32_t sanic_attn_decode_splitkv_static(sanic_ctx* ctx, const sanic_decode_params* p, void* stream);
+size_t sanic_attn_decode_static_scratch_capacity(void);
 
 /* Stage 2 alone: merge n_parts raw accumulators [n_parts, rows, 2+D] left to right and
  * project. This is the cross-device merge of interp::run_carrier_split (src/interp.rs:632-639). */

@@ -107,6 +107,8 @@ PROTOTYPES = {
     "sanic_attn_fwd_f32": (i32, [vp, C.POINTER(AttnParams), vp]),
     "sanic_attn_fwd_bf16": (i32, [vp, C.POINTER(AttnParams), vp]),
     "sanic_attn_decode_splitkv": (i32, [vp, C.POINTER(DecodeParams), vp]),
+    "sanic_attn_decode_splitkv_static": (i32, [vp, C.POINTER(DecodeParams), vp]),
+    "sanic_attn_decode_static_scratch_capacity": (C.c_size_t, []),
     "sanic_attn_decode_scratch_bytes": (C.c_size_t, [i32, i32, i32, i32]),
     "sanic_attn_decode_suggest_splits": (i32, [vp, i32, i32, i32, i64]),
     "sanic_carrier_merge": (i32, [vp, vp, i32, i32, i32, vp, vp, i32, vp]),

@@ -308,12 +308,7 @@ __global__ void carrier_merge_kernel(const float* parts, int n_parts, int rows, 
 template <int D, bool VT>
 int32_t launch_decode(sanic_ctx* ctx, const sanic_decode_params& p, cudaStream_t st) {
     auto kern = attn_decode_kernel<D, VT>;
-    static bool configured[4] = {false, false, false, false};
-    int slot = (D == 128 ? 2 : 0) + (VT ? 1 : 0);
-    if (!configured[slot]) {
-        SANIC_CUDA_CHECK(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<D>::SMEM));
-        configured[slot] = true;
-    }
+    SANIC_CUDA_CHECK(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<D>::SMEM));
     int* counters = (int*)(p.partials + (size_t)p.batch * p.q_heads * p.n_splits * (D + 2));
     dim3 grid(p.n_splits, p.kv_heads, p.batch);
     kern<<<grid, 128, Cfg<D>::SMEM, st>>>(p, counters);
@@ -345,8 +340,54 @@ int32_t sanic_attn_decode_suggest_splits(sanic_ctx* ctx, int32_t batch, int32_t 
     return (int32_t)target;
 }
 
+static int32_t decode_validate_and_launch(sanic_ctx* ctx, const sanic_decode_params* p, void* stream);
+
 int32_t sanic_attn_decode_splitkv(sanic_ctx* ctx, const sanic_decode_params* p, void* stream) {
     if (!ctx || !p) return SANIC_ERR_INVALID;
+    return decode_validate_and_launch(ctx, p, stream);
+}
+
+// ── the entry point for callers that cannot allocate ──
+// Scratch for the split-KV fold lives in this file-scope device array instead of a buffer the
+// caller allocates. Every device that loads the library holds these bytes until the process exits.
+#define SANIC_STATIC_SCRATCH_FLOATS (1u << 20)   /* 4 MiB of partial accumulators */
+#define SANIC_STATIC_SCRATCH_COUNTERS 4096u      /* one ticket per (batch, kv head) */
+static __device__ __align__(256) float g_decode_scratch[SANIC_STATIC_SCRATCH_FLOATS + SANIC_STATIC_SCRATCH_COUNTERS];
+
+size_t sanic_attn_decode_static_scratch_capacity(void) { return (size_t)SANIC_STATIC_SCRATCH_FLOATS * sizeof(float); }
+
+int32_t sanic_attn_decode_splitkv_static(sanic_ctx* ctx, const sanic_decode_params* p, void* stream) {
+    if (!ctx || !p) return SANIC_ERR_INVALID;
+    SANIC_REQUIRE(ctx, p->batch > 0 && p->q_heads > 0 && p->kv_heads > 0 && p->n_splits >= 1 && p->head_dim > 0,
+                  "attn_decode_static: bad shape");
+    const size_t need = (size_t)p->batch * p->q_heads * p->n_splits * (p->head_dim + 2);
+    if (need > SANIC_STATIC_SCRATCH_FLOATS || (size_t)p->batch * p->kv_heads > SANIC_STATIC_SCRATCH_COUNTERS)
+        return sanic_fail(ctx, SANIC_ERR_INVALID,
+                          "attn_decode_static: batch*q_heads*n_splits*(head_dim+2) = " + std::to_string(need) +
+                          " floats exceeds the built-in scratch of " + std::to_string(SANIC_STATIC_SCRATCH_FLOATS) +
+                          " floats; use fewer splits or sanic_attn_decode_splitkv with caller scratch");
+    sanic_set_device(ctx);
+    // In host code the array's name is only a handle. Its device address is looked up once per
+    // device, with that device current; the kernel is given that address, never the name.
+    static float* dev_addr[64] = {nullptr};
+    SANIC_REQUIRE(ctx, ctx->device >= 0 && ctx->device < 64, "attn_decode_static: device ordinal out of range");
+    if (!dev_addr[ctx->device]) {
+        void* ptr = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&ptr, g_decode_scratch);
+        if (e != cudaSuccess || !ptr)
+            return sanic_fail(ctx, SANIC_ERR_CUDA, std::string("attn_decode_static: cudaGetSymbolAddress: ") + cudaGetErrorString(e));
+        dev_addr[ctx->device] = (float*)ptr;
+    }
+    float* scratch = dev_addr[ctx->device];
+    // The ticket counters must start at zero. They sit right after this call's partials; the array
+    // keeps whatever the previous call left, so clear them on the stream (no allocation involved).
+    SANIC_CUDA_CHECK(ctx, cudaMemsetAsync(scratch + need, 0, (size_t)p->batch * p->kv_heads * sizeof(int), (cudaStream_t)stream));
+    sanic_decode_params local = *p;
+    local.partials = scratch;
+    return decode_validate_and_launch(ctx, &local, stream);
+}
+
+static int32_t decode_validate_and_launch(sanic_ctx* ctx, const sanic_decode_params* p, void* stream) {
     SANIC_REQUIRE(ctx, p->q && p->k && p->v && p->partials, "attn_decode: null tensor or scratch");
     SANIC_REQUIRE(ctx, p->out || p->carrier_out, "attn_decode: no output requested");
     SANIC_REQUIRE(ctx, p->head_dim == 64 || p->head_dim == 128, "attn_decode: head_dim must be 64 or 128");
