@@ -133,8 +133,7 @@ int32_t sanic_attn_decode_suggest_splits(sanic_ctx* ctx, int32_t batch, int32_t 
 
 /* Same fold for callers that cannot allocate device memory. This entry point has no counterpart in
  * the reference. Some hosts of this library may not call cudaMalloc at the point where they decode:
- * code running inside a CUDA-graph capture or a latency-critical serving loop where an allocation
- * would synchronise the device, plugins that are handed a fixed arena by their framework, and
+ * a latency-critical serving loop where an allocation would synchronise the device, plugins that are handed a fixed arena by their framework, and
  * processes whose memory is fully budgeted up front. For them the split-KV scratch lives in a static
  * device array inside the library (4 MiB of partial accumulators plus 4096 ticket counters, held on
  * every device that loads the library until the process exits). `p->partials` is ignored; inputs and

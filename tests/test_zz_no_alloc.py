@@ -1,7 +1,7 @@
 """The allocation-free decode entry point against the ordinary one.
 
 `sanic_attn_decode_splitkv_static` exists for hosts that must not allocate device memory where
-they decode: a serving loop or a CUDA-graph capture where an allocation would stall the device,
+they decode: a serving loop where an allocation would stall the device,
 a plugin that is given a fixed arena, a process whose memory is budgeted up front. Its split-KV
 scratch is a static array inside the library instead of a caller buffer. This file calls it
 through the C ABI twice in a row (the second call meets whatever the first left in the shared
