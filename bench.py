@@ -162,6 +162,35 @@ def suite(dev, torch, hbm_peak, tf_peak, quick):
     v = torch.randn(1, 1, 1024, 64, generator=g, device=td)
     med, best = time_events(lambda: dev.attn_fwd_f32(q, k, v, scale=0.125), 20, 3, torch)
     out["c1_attn_f32_us"] = {"median": med * 1e6, "min": best * 1e6}
+    # config 2: RMSNorm-fused GEMM, x[4096x2048] g[2048] W[2048x8192] bf16, f32 accumulation, bf16 output
+    M, K, N = 4096, 2048, 8192
+    x = torch.randn(M, K, generator=g, device=td).to(torch.bfloat16)
+    gam = (1.0 + 0.1 * torch.randn(K, generator=g, device=td)).to(torch.bfloat16)
+    for name, nk in (("w_nk", True), ("w_kn", False)):
+        w = (0.02 * torch.randn((N, K) if nk else (K, N), generator=g, device=td)).to(torch.bfloat16)
+        med, best = time_events(lambda: dev.gemm_rmsnorm(x, gam, w, w_is_nk=nk), 20, 3, torch)
+        dev.sync()
+        fl = 2.0 * M * N * K
+        out[f"c2_gemm_rmsnorm_{name}"] = {"us_median": med * 1e6, "us_min": best * 1e6, "tflops": fl / med / 1e12,
+                                          "frac_of_bf16_peak": fl / med / 1e12 / tf_peak}
+        del w
+    del x
+    # config 3: causal flash attention with RoPE, B8 Hq32 Hkv8 D64 S4096 bf16 (+ 1024-token window)
+    Bq, Hq3, Hk3, S3 = 8, 32, 8, 4096
+    q3 = torch.randn(Bq, Hq3, S3, 64, generator=g, device=td).to(torch.bfloat16)
+    k3 = torch.randn(Bq, Hk3, S3, 64, generator=g, device=td).to(torch.bfloat16)
+    v3 = torch.randn(Bq, Hk3, S3, 64, generator=g, device=td).to(torch.bfloat16)
+    table = dev.rope_table([math.exp(i * (-math.log(500000.0) / 32)) for i in range(32)], S3)
+    qr, kr = torch.empty_like(q3), torch.empty_like(k3)
+    med_r, _ = time_events(lambda: (dev.rope_bf16(q3, table, out=qr), dev.rope_bf16(k3, table, out=kr)), 10, 3, torch)
+    for name, win, fl in (("causal", 0, 5.498e11), ("causal_window1024", 1024, 2.405e11)):
+        med, best = time_events(lambda: dev.attn_fwd_bf16(qr, kr, v3, causal=True, window=win), 10, 3, torch)
+        dev.sync()
+        out[f"c3_flash_{name}"] = {"attn_us_median": med * 1e6, "attn_us_min": best * 1e6, "rope_us": med_r * 1e6,
+                                   "tflops_attn_only": fl / med / 1e12, "tflops_with_rope": fl / (med + med_r) / 1e12,
+                                   "frac_of_bf16_peak": fl / med / 1e12 / tf_peak}
+    del q3, k3, v3, qr, kr
+    torch.cuda.empty_cache()
     # config 4: Llama-3.2-1B-architecture decode step, ctx 1024 (+32 steps), CUDA-graph replays
     cfg = llama.LLAMA_3_2_1B
     for name, batch, w4 in (("bf16_b1", 1, False), ("bf16_b16", 16, False), ("int4_b1", 1, True)):

@@ -1,5 +1,317 @@
-#include "common.cuh"
+// Online-softmax fold for prefill (FlashAttention forward), bf16 storage, head_dim 64, on the
+// 5th-generation tensor cores: S = Q K^T and O += P V are tcgen05 MMAs with TMEM accumulators,
+// Q/K/V tiles arrive by TMA, and the (m, l, o) carrier of each query row is kept by the thread that
+// owns that row (one TMEM lane per row, so row max and row sum need no shuffles).
+//
+// One CTA folds 256 query rows of one (batch, query head) as two 128-row tiles that ping-pong on
+// the tensor core: while one tile's softmax warpgroup turns S into P, the other tile's MMAs run.
+//   warp 0       TMA producer: Q once, then K_j / V_j tiles of 128 keys through a 3-stage ring
+//   warp 1       MMA issuer: per key tile  PV(0,j) QK(0,j+1) PV(1,j) QK(1,j+1)
+//   warp 2       TMEM allocator (S0 S1 O0 O1 = 128+128+64+64 columns of 512)
+//   warps 4-7    softmax + correction + epilogue of tile 0
+//   warps 8-11   the same for tile 1
+// Masks: causal (key > row), sliding window (key < row - window + 1) and the ragged key tail are
+// applied only in tiles that straddle an edge; tiles wholly outside the visible range are never
+// loaded (a prefix-masked fold may stop at the mask edge: it contributes exact zeros).
+// The rescale of O by exp(m_old - m_new) is skipped when no row of the warp moved its max.
+// Every mbarrier wait is bounded and reports through the context's status word.
+//
+// Roofline: tensor-bound, 4*B*Hq*S^2*D/2 FLOP for causal; the exponentials (one per score) run on
+// the 16-per-clock SFU and bound the tensor pipe to about half of its peak at head_dim 64.
+#include "tc_common.cuh"
+
+namespace {
+using namespace sanic;
+using namespace sanic::tc;
+
+constexpr int D = 64, BM = 128, BN = 128, KV_STAGES = 3;
+constexpr int Q_BYTES = BM * D * 2;        // 16 KB per query tile
+constexpr int KV_BYTES = BN * D * 2;       // 16 KB per K or V tile
+constexpr int P_BYTES = BM * BN * 2;       // 32 KB per P tile (two 64-key halves)
+constexpr int NTHREADS = 384;
+
+struct FShared {
+    uint64_t q_full, k_full[KV_STAGES], v_full[KV_STAGES], kv_empty[KV_STAGES];
+    uint64_t s_full[2], p_full[2], pv_done[2];
+    uint32_t tmem_base;
+    volatile int abort_flag;
+};
+
+struct FParams {
+    void* out;
+    int batch, q_heads, kv_heads, q_len, kv_len, causal, window;
+    float scale;
+};
+
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+// key-tile range [jb, je) that tile rows [r0, r0+127] can see
+__device__ __forceinline__ void tile_range(const FParams& p, int r0, int nkv, int& jb, int& je) {
+    jb = 0; je = nkv;
+    if (r0 >= p.q_len) { jb = je = 0; return; }
+    int rmax = min(r0 + BM - 1, p.q_len - 1);
+    if (p.causal || p.window > 0) je = min(nkv, rmax / BN + 1);
+    if (p.window > 0) jb = max(0, r0 - p.window + 1) / BN;
+}
+
+__global__ void __launch_bounds__(NTHREADS, 1)
+attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                   const __grid_constant__ CUtensorMap map_v, FParams p, int* err) {
+    extern __shared__ unsigned char smem_dyn[];
+    const uint32_t raw = smem_u32(smem_dyn);
+    const uint32_t base = (raw + 1023u) & ~1023u;
+    unsigned char* aligned = smem_dyn + (base - raw);
+    const uint32_t q_addr = base, kv_addr = base + 2 * Q_BYTES, p_addr = kv_addr + KV_STAGES * 2 * KV_BYTES;
+    FShared* sh = (FShared*)(aligned + 2 * Q_BYTES + KV_STAGES * 2 * KV_BYTES + 2 * P_BYTES);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int mb = gridDim.x - 1 - blockIdx.x;      // heaviest (latest) query blocks first
+    const int h = blockIdx.y, b = blockIdx.z;
+    const int hk = h / (p.q_heads / p.kv_heads);
+    const int m0 = mb * 2 * BM;
+    const int nkv = (p.kv_len + BN - 1) / BN;
+    int jb_t[2], je_t[2];
+    tile_range(p, m0, nkv, jb_t[0], je_t[0]);
+    tile_range(p, m0 + BM, nkv, jb_t[1], je_t[1]);
+    const bool act1 = je_t[1] > jb_t[1];
+    const int j_begin = act1 ? min(jb_t[0], jb_t[1]) : jb_t[0];
+    const int j_end = act1 ? max(je_t[0], je_t[1]) : je_t[0];
+
+    if (threadIdx.x == 0) {
+        mbar_init(&sh->q_full, 1);
+        for (int s = 0; s < KV_STAGES; ++s) { mbar_init(&sh->k_full[s], 1); mbar_init(&sh->v_full[s], 1); mbar_init(&sh->kv_empty[s], 1); }
+        for (int t = 0; t < 2; ++t) { mbar_init(&sh->s_full[t], 1); mbar_init(&sh->p_full[t], 4); mbar_init(&sh->pv_done[t], 1); }
+        sh->abort_flag = 0;
+        mbar_init_fence();
+    }
+    if (warp == 2) tmem_alloc(&sh->tmem_base, 512);
+    fence_before();
+    __syncthreads();
+    fence_after();
+    const uint32_t tmem = sh->tmem_base;
+    volatile int* abortp = &sh->abort_flag;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            const int qrow = (b * p.q_heads + h) * p.q_len + m0;
+            mbar_expect_tx(&sh->q_full, 2 * Q_BYTES);
+            tma_load_2d(q_addr, &map_q, &sh->q_full, 0, qrow);
+            tma_load_2d(q_addr + Q_BYTES, &map_q, &sh->q_full, 0, qrow + BM);
+            const int krow = (b * p.kv_heads + hk) * p.kv_len;
+            int stage = 0; uint32_t phase = 1;
+            for (int j = j_begin; j < j_end; ++j) {
+                if (!mbar_wait(&sh->kv_empty[stage], phase, abortp, err, 11)) break;
+                const uint32_t ka = kv_addr + stage * 2 * KV_BYTES;
+                mbar_expect_tx(&sh->k_full[stage], KV_BYTES);
+                tma_load_2d(ka, &map_k, &sh->k_full[stage], 0, krow + j * BN);
+                mbar_expect_tx(&sh->v_full[stage], KV_BYTES);
+                tma_load_2d(ka + KV_BYTES, &map_v, &sh->v_full[stage], 0, krow + j * BN);
+                if (++stage == KV_STAGES) { stage = 0; phase ^= 1; }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc_qk = make_idesc(BM, BN, false);
+            constexpr uint32_t idesc_pv = make_idesc(BM, D, true);
+            int it[2] = {0, 0};        // PV issues so far per tile
+            bool ok = mbar_wait(&sh->q_full, 0, abortp, err, 12);
+            auto issue_qk = [&](int t, int stage) {
+                const uint64_t ad = make_desc(q_addr + t * Q_BYTES, 16, 1024);
+                const uint64_t bd = make_desc(kv_addr + stage * 2 * KV_BYTES, 16, 1024);
+#pragma unroll
+                for (int k = 0; k < D / 16; ++k) umma_f16(tmem + t * BN, ad + 2 * k, bd + 2 * k, idesc_qk, k > 0 ? 1u : 0u);
+                umma_commit(&sh->s_full[t]);
+            };
+            int stage = 0; uint32_t phase = 0;
+            if (ok && j_end > j_begin) {
+                ok = mbar_wait(&sh->k_full[0], 0, abortp, err, 13);
+                fence_after();
+                if (ok) for (int t = 0; t < 2; ++t) if (j_begin >= jb_t[t] && j_begin < je_t[t]) issue_qk(t, 0);
+            }
+            for (int j = j_begin; j < j_end && ok; ++j) {
+                const int nstage = (stage + 1 == KV_STAGES) ? 0 : stage + 1;
+                const uint32_t nphase = (stage + 1 == KV_STAGES) ? phase ^ 1 : phase;
+                bool v_ready = false, k_next_ready = false;
+                for (int t = 0; t < 2 && ok; ++t) {
+                    if (j >= jb_t[t] && j < je_t[t]) {
+                        if (!v_ready) { ok = mbar_wait(&sh->v_full[stage], phase, abortp, err, 14); v_ready = true; if (!ok) break; }
+                        ok = mbar_wait(&sh->p_full[t], it[t] & 1, abortp, err, 15);
+                        if (!ok) break;
+                        fence_after();
+                        const uint32_t pa = p_addr + t * P_BYTES;
+                        const uint64_t vd = make_desc(kv_addr + stage * 2 * KV_BYTES + KV_BYTES, 1024, 1024);
+#pragma unroll
+                        for (int k = 0; k < BN / 16; ++k) {
+                            const uint64_t ad = make_desc(pa + (k >> 2) * (BM * 128), 16, 1024) + 2 * (k & 3);
+                            umma_f16(tmem + 256 + t * D, ad, vd + 128 * k, idesc_pv, (it[t] > 0 || k > 0) ? 1u : 0u);
+                        }
+                        umma_commit(&sh->pv_done[t]);
+                        it[t]++;
+                    }
+                    if (j + 1 < j_end && j + 1 >= jb_t[t] && j + 1 < je_t[t]) {
+                        if (!k_next_ready) { ok = mbar_wait(&sh->k_full[nstage], nphase, abortp, err, 16); k_next_ready = true; if (!ok) break; fence_after(); }
+                        issue_qk(t, nstage);
+                    }
+                }
+                if (ok) umma_commit(&sh->kv_empty[stage]);
+                stage = nstage; phase = nphase;
+            }
+        }
+    } else if (warp >= 4) {
+        // ── softmax, correction and epilogue for tile t; this thread owns query row r0 + row ──
+        const int t = (warp - 4) >> 2;
+        const int q4 = warp & 3;
+        const int row = q4 * 32 + lane;
+        const int r0 = m0 + t * BM;
+        const int grow = r0 + row;                    // global query position
+        const uint32_t lane_base = (uint32_t)(q4 * 32) << 16;
+        const uint32_t s_tmem = tmem + lane_base + t * BN;
+        const uint32_t o_tmem = tmem + lane_base + 256 + t * D;
+        unsigned char* prow = aligned + (p_addr - base) + t * P_BYTES + row * 128;
+        const float sl2 = p.scale * LOG2E;
+        float m = -INFINITY, l = 0.0f;
+        int it = 0;
+        bool ok = true;
+        for (int j = jb_t[t]; j < je_t[t] && ok; ++j, ++it) {
+            ok = mbar_wait(&sh->s_full[t], it & 1, abortp, err, 21);
+            if (!ok) break;
+            fence_after();
+            const int k0 = j * BN;
+            // does this tile straddle a mask edge for any of the 128 rows?
+            bool edge = (k0 + BN > p.kv_len);
+            if (p.causal || p.window > 0) edge = edge || (k0 + BN - 1 > r0);
+            if (p.window > 0) edge = edge || (k0 < r0 + BM - 1 - p.window + 1);
+            int klo = 0, khi = p.kv_len;              // visible keys of this row: [klo, khi)
+            if (p.causal || p.window > 0) khi = min(khi, grow + 1);
+            if (p.window > 0) klo = max(0, grow - p.window + 1);
+            // pass 1: row max
+            float mx = -INFINITY;
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; ++c) {
+                uint32_t r[32];
+                tmem_ld32(s_tmem + c * 32, r);
+                if (edge) {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) { int kk = k0 + c * 32 + i; if (kk >= klo && kk < khi) mx = fmaxf(mx, __uint_as_float(r[i])); }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(r[i]));
+                }
+            }
+            const float m_new = fmaxf(m, mx * sl2);
+            const float alpha = (m > -INFINITY) ? ex2(m - m_new) : 0.0f;   // weight 0 for an empty accumulator
+            const float msub = (m_new > -INFINITY) ? m_new : 0.0f;
+            if (it > 0) {
+                ok = mbar_wait(&sh->pv_done[t], (it - 1) & 1, abortp, err, 22);  // O_t final for tile j-1, P_t free
+                if (!ok) break;
+                fence_after();
+                if (__any_sync(0xffffffffu, alpha != 1.0f)) {
+#pragma unroll 1
+                    for (int c = 0; c < D / 32; ++c) {
+                        uint32_t r[32];
+                        tmem_ld32(o_tmem + c * 32, r);
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+                        tmem_st32(o_tmem + c * 32, r);
+                    }
+                    tmem_st_wait();
+                }
+            }
+            // pass 2: P = exp2(S*sl2 - m_new) -> bf16 -> shared (K-major, 128B swizzle), row sum
+            float sum = 0.0f;
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; ++c) {
+                uint32_t r[32];
+                tmem_ld32(s_tmem + c * 32, r);
+                uint32_t pk[16];
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    float s0 = __uint_as_float(r[2 * i]), s1 = __uint_as_float(r[2 * i + 1]);
+                    if (edge) {
+                        int kk = k0 + c * 32 + 2 * i;
+                        if (!(kk >= klo && kk < khi)) s0 = -INFINITY;
+                        if (!(kk + 1 >= klo && kk + 1 < khi)) s1 = -INFINITY;
+                    }
+                    float p0 = ex2(fmaf(s0, sl2, -msub)), p1 = ex2(fmaf(s1, sl2, -msub));
+                    sum += p0 + p1;
+                    pk[i] = pack_bf16x2(p0, p1);
+                }
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const int cc = c * 4 + q;                 // 16-byte chunk index along the 128 keys
+                    unsigned char* dst = prow + (cc >> 3) * (BM * 128) + (((cc & 7) ^ (row & 7)) << 4);
+                    *(uint4*)dst = make_uint4(pk[4 * q], pk[4 * q + 1], pk[4 * q + 2], pk[4 * q + 3]);
+                }
+            }
+            l = l * alpha + sum;
+            m = m_new;
+            fence_before();
+            fence_async_smem();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&sh->p_full[t]);
+        }
+        // epilogue: project o / l and store bf16 rows
+        if (ok && it > 0) {
+            ok = mbar_wait(&sh->pv_done[t], (it - 1) & 1, abortp, err, 23);
+            if (ok) {
+                fence_after();
+                const float inv = 1.0f / l;
+                uint16_t* dst = (uint16_t*)p.out + ((size_t)(b * p.q_heads + h) * p.q_len + grow) * D;
+#pragma unroll 1
+                for (int c = 0; c < D / 32; ++c) {
+                    uint32_t r[32];
+                    tmem_ld32(o_tmem + c * 32, r);
+                    if (grow < p.q_len) {
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            uint32_t w0 = pack_bf16x2(__uint_as_float(r[8 * q]) * inv, __uint_as_float(r[8 * q + 1]) * inv);
+                            uint32_t w1 = pack_bf16x2(__uint_as_float(r[8 * q + 2]) * inv, __uint_as_float(r[8 * q + 3]) * inv);
+                            uint32_t w2 = pack_bf16x2(__uint_as_float(r[8 * q + 4]) * inv, __uint_as_float(r[8 * q + 5]) * inv);
+                            uint32_t w3 = pack_bf16x2(__uint_as_float(r[8 * q + 6]) * inv, __uint_as_float(r[8 * q + 7]) * inv);
+                            *(uint4*)(dst + c * 32 + q * 8) = make_uint4(w0, w1, w2, w3);
+                        }
+                    }
+                }
+            }
+        }
+    }
+    fence_before();
+    __syncthreads();
+    if (warp == 2) { fence_after(); tmem_dealloc(tmem, 512); }
+}
+}  // namespace
+
 extern "C" int32_t sanic_attn_fwd_bf16(sanic_ctx* ctx, const sanic_attn_params* p, void* stream) {
-    (void)p; (void)stream;
-    return sanic_fail(ctx, SANIC_ERR_UNSUPPORTED, "attn_fwd_bf16: not built yet");
+    if (!ctx || !p) return SANIC_ERR_INVALID;
+    SANIC_REQUIRE(ctx, p->q && p->k && p->v && p->out, "attn_fwd_bf16: null tensor");
+    SANIC_REQUIRE(ctx, p->batch > 0 && p->q_heads > 0 && p->kv_heads > 0 && p->q_heads % p->kv_heads == 0,
+                  "attn_fwd_bf16: query heads must be a multiple of key/value heads");
+    SANIC_REQUIRE(ctx, p->q_len > 0 && p->kv_len > 0, "attn_fwd_bf16: empty sequence");
+    if (p->head_dim != 64 || p->v_dim != 64)
+        return sanic_fail(ctx, SANIC_ERR_UNSUPPORTED, "attn_fwd_bf16: head_dim and v_dim must be 64");
+    SANIC_REQUIRE(ctx, !p->mask, "attn_fwd_bf16: additive masks are served by the f32 path");
+    SANIC_REQUIRE(ctx, !(p->causal || p->window > 0) || p->q_len == p->kv_len,
+                  "attn_fwd_bf16: causal and window masks need equal query and key lengths");
+    SANIC_REQUIRE(ctx, p->out_dtype == SANIC_BF16, "attn_fwd_bf16: output is bf16");
+    SANIC_REQUIRE(ctx, ((uintptr_t)p->q % 16) == 0 && ((uintptr_t)p->k % 16) == 0 && ((uintptr_t)p->v % 16) == 0 &&
+                  ((uintptr_t)p->out % 16) == 0, "attn_fwd_bf16: tensors must be 16-byte aligned");
+    sanic_set_device(ctx);
+    CUtensorMap mq, mk, mv;
+    int32_t rc = sanic::tc::encode_bf16_2d(ctx, &mq, p->q, D, (uint64_t)p->batch * p->q_heads * p->q_len, D, BM);
+    if (rc != SANIC_OK) return rc;
+    rc = sanic::tc::encode_bf16_2d(ctx, &mk, p->k, D, (uint64_t)p->batch * p->kv_heads * p->kv_len, D, BN);
+    if (rc != SANIC_OK) return rc;
+    rc = sanic::tc::encode_bf16_2d(ctx, &mv, p->v, D, (uint64_t)p->batch * p->kv_heads * p->kv_len, D, BN);
+    if (rc != SANIC_OK) return rc;
+    FParams fp{p->out, p->batch, p->q_heads, p->kv_heads, p->q_len, p->kv_len, p->causal, p->window, p->scale};
+    const int smem = 2 * Q_BYTES + KV_STAGES * 2 * KV_BYTES + 2 * P_BYTES + (int)sizeof(FShared) + 1024;
+    SANIC_CUDA_CHECK(ctx, cudaFuncSetAttribute(attn_fwd_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    dim3 grid((p->q_len + 2 * BM - 1) / (2 * BM), p->q_heads, p->batch);
+    attn_fwd_tc_kernel<<<grid, NTHREADS, smem, (cudaStream_t)stream>>>(mq, mk, mv, fp, ctx->status_dev);
+    SANIC_LAUNCH_CHECK(ctx, "attn_fwd_bf16");
+    return SANIC_OK;
 }

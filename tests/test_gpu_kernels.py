@@ -394,3 +394,64 @@ def test_gemm_rmsnorm_many_tiles_per_cta(dev):
     # more tiles than SMs: exercises the accumulator double buffer and barrier phases
     got, exp = _gemm_case(dev, 2048, 256, 8192, True)
     assert got.shape == (2048, 8192)
+
+
+# ───────────────────────── prefill online-softmax fold (tcgen05) ─────────────────────────
+def _flash_case(dev, B, Hq, Hkv, Lq, Lk, mode, window=0, seed=91):
+    q, qv = bf16t(normal(seed, B, Hq, Lq, 64), dev)
+    k, kv = bf16t(normal(seed + 1, B, Hkv, Lk, 64), dev)
+    v, vv = bf16t(normal(seed + 2, B, Hkv, Lk, 64), dev)
+    if mode == "plain":
+        exp = orc.sdpa(qv, kv, vv, enable_gqa=True)
+        got = dev.attn_fwd_bf16(q, k, v)
+    elif mode == "causal":
+        exp = orc.sdpa(qv, kv, vv, is_causal=True, enable_gqa=True)
+        got = dev.attn_fwd_bf16(q, k, v, causal=True)
+    else:
+        exp = orc.sdpa_window(qv, kv, vv, window)
+        got = dev.attn_fwd_bf16(q, k, v, causal=True, window=window)
+    dev.sync()
+    assert nerr(got.float().cpu().numpy(), exp) <= BF16_TOL
+
+
+@pytest.mark.parametrize("mode", ["plain", "causal"])
+@pytest.mark.parametrize("L", [128, 256, 384, 640])
+def test_flash_fwd_square(dev, mode, L):
+    _flash_case(dev, 1, 4, 2, L, L, mode)
+
+
+def test_flash_fwd_ragged_and_gqa(dev):
+    _flash_case(dev, 2, 8, 2, 200, 300, "plain")      # ragged key tail, query tail, rectangular
+    _flash_case(dev, 1, 4, 1, 77, 77, "causal")       # shorter than one tile
+    _flash_case(dev, 1, 2, 2, 1000, 1000, "causal")   # ragged on both axes, 4 query blocks
+
+
+@pytest.mark.parametrize("window", [1, 100, 128, 300])
+def test_flash_fwd_sliding_window(dev, window):
+    _flash_case(dev, 1, 4, 2, 700, 700, "window", window=window)
+
+
+def test_flash_fwd_rope_pipeline_long(dev):
+    # size-independent checks at a longer sequence: causal row 0 equals V row 0, and the output is
+    # unchanged when keys beyond the causal edge are replaced (they must never be read into a result)
+    B, Hq, Hkv, L = 1, 8, 2, 2048
+    g = torch.Generator(device=dev.torch_device); g.manual_seed(17)
+    q = torch.randn(B, Hq, L, 64, generator=g, device=dev.torch_device).to(torch.bfloat16)
+    k = torch.randn(B, Hkv, L, 64, generator=g, device=dev.torch_device).to(torch.bfloat16)
+    v = torch.randn(B, Hkv, L, 64, generator=g, device=dev.torch_device).to(torch.bfloat16)
+    inv = orc.rope_inv_freq(500000.0, 32)
+    table = dev.rope_table(list(inv), L)
+    qr, kr = dev.rope_bf16(q, table), dev.rope_bf16(k, table)
+    out = dev.attn_fwd_bf16(qr, kr, v, causal=True)
+    dev.sync()
+    assert torch.equal(out[:, :, 0], v[:, :, 0].repeat_interleave(Hq // Hkv, dim=1))
+    half = L // 2
+    k2, v2 = kr.clone(), v.clone()
+    k2[:, :, half:] = 7.0; v2[:, :, half:] = -3.0
+    out2 = dev.attn_fwd_bf16(qr, k2, v2, causal=True)
+    dev.sync()
+    assert torch.equal(out[:, :, :half], out2[:, :, :half])
+    # one head against the oracle
+    exp = orc.sdpa(qr[0, :4].float().cpu().numpy().astype(np.float64), kr[0, :1].float().cpu().numpy().astype(np.float64),
+                   v[0, :1].float().cpu().numpy().astype(np.float64), is_causal=True, enable_gqa=True)
+    assert nerr(out[0, :4].float().cpu().numpy(), exp) <= BF16_TOL
