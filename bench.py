@@ -149,24 +149,28 @@ def time_events(fn, steps, warmup, torch):
     return ts[len(ts) // 2] * 1e-3, ts[0] * 1e-3
 
 
-def suite(dev, torch, hbm_peak, tf_peak, quick):
+def suite(dev, torch, hbm_peak, tf_peak, quick, only=None, c2_shape=(4096, 2048, 8192), c3_shape=(8, 4096), fused=True):
     import numpy as np
     from sanic_b200 import llama
     out = {}
+    want = lambda name: only is None or any(o in name for o in only)
     td = dev.torch_device
     g = torch.Generator(device=td)
     g.manual_seed(7)
     # config 1: f32 naive attention Q[256x64] K,V[1024x64] (launch-latency bound parity case)
-    q = torch.randn(1, 1, 256, 64, generator=g, device=td)
-    k = torch.randn(1, 1, 1024, 64, generator=g, device=td)
-    v = torch.randn(1, 1, 1024, 64, generator=g, device=td)
-    med, best = time_events(lambda: dev.attn_fwd_f32(q, k, v, scale=0.125), 20, 3, torch)
-    out["c1_attn_f32_us"] = {"median": med * 1e6, "min": best * 1e6}
+    if want("c1"):
+        q = torch.randn(1, 1, 256, 64, generator=g, device=td)
+        k = torch.randn(1, 1, 1024, 64, generator=g, device=td)
+        v = torch.randn(1, 1, 1024, 64, generator=g, device=td)
+        med, best = time_events(lambda: dev.attn_fwd_f32(q, k, v, scale=0.125), 20, 3, torch)
+        out["c1_attn_f32_us"] = {"median": med * 1e6, "min": best * 1e6}
     # config 2: RMSNorm-fused GEMM, x[4096x2048] g[2048] W[2048x8192] bf16, f32 accumulation, bf16 output
-    M, K, N = 4096, 2048, 8192
+    M, K, N = c2_shape
     x = torch.randn(M, K, generator=g, device=td).to(torch.bfloat16)
     gam = (1.0 + 0.1 * torch.randn(K, generator=g, device=td)).to(torch.bfloat16)
     for name, nk in (("w_nk", True), ("w_kn", False)):
+        if not want("c2"):
+            continue
         w = (0.02 * torch.randn((N, K) if nk else (K, N), generator=g, device=td)).to(torch.bfloat16)
         med, best = time_events(lambda: dev.gemm_rmsnorm(x, gam, w, w_is_nk=nk), 20, 3, torch)
         dev.sync()
@@ -176,14 +180,17 @@ def suite(dev, torch, hbm_peak, tf_peak, quick):
         del w
     del x
     # config 3: causal flash attention with RoPE, B8 Hq32 Hkv8 D64 S4096 bf16 (+ 1024-token window)
-    Bq, Hq3, Hk3, S3 = 8, 32, 8, 4096
+    Bq, Hq3, Hk3, S3 = c3_shape[0], 32, 8, c3_shape[1]
+    c3_scale = (Bq * S3 * S3) / (8.0 * 4096 * 4096)
     q3 = torch.randn(Bq, Hq3, S3, 64, generator=g, device=td).to(torch.bfloat16)
     k3 = torch.randn(Bq, Hk3, S3, 64, generator=g, device=td).to(torch.bfloat16)
     v3 = torch.randn(Bq, Hk3, S3, 64, generator=g, device=td).to(torch.bfloat16)
     table = dev.rope_table([math.exp(i * (-math.log(500000.0) / 32)) for i in range(32)], S3)
     qr, kr = torch.empty_like(q3), torch.empty_like(k3)
     med_r, _ = time_events(lambda: (dev.rope_bf16(q3, table, out=qr), dev.rope_bf16(k3, table, out=kr)), 10, 3, torch)
-    for name, win, fl in (("causal", 0, 5.498e11), ("causal_window1024", 1024, 2.405e11)):
+    for name, win, fl in (("causal", 0, 5.498e11 * c3_scale), ("causal_window1024", 1024, 2.405e11 * c3_scale)):
+        if not want("c3"):
+            continue
         med, best = time_events(lambda: dev.attn_fwd_bf16(qr, kr, v3, causal=True, window=win), 10, 3, torch)
         dev.sync()
         out[f"c3_flash_{name}"] = {"attn_us_median": med * 1e6, "attn_us_min": best * 1e6, "rope_us": med_r * 1e6,
@@ -194,8 +201,10 @@ def suite(dev, torch, hbm_peak, tf_peak, quick):
     # config 4: Llama-3.2-1B-architecture decode step, ctx 1024 (+32 steps), CUDA-graph replays
     cfg = llama.LLAMA_3_2_1B
     for name, batch, w4 in (("bf16_b1", 1, False), ("bf16_b16", 16, False), ("int4_b1", 1, True)):
+        if not want("c4_" + name):
+            continue
         w = llama.random_weights(cfg, 11, td, w4=w4)
-        m = llama.LlamaMachine(dev, cfg, w, ctx=1088, batch=batch, w4=w4)
+        m = llama.LlamaMachine(dev, cfg, w, ctx=1088, batch=batch, w4=w4, fused=fused)
         rng = np.random.default_rng(3)
         # prefill 1024 positions from random token ids by decoding on the device
         for p in range(1024 if not quick else 64):
@@ -343,7 +352,8 @@ def run_ours(args):
     torch.cuda.empty_cache()
     if rank == 0 and world == 1 and not args.no_suite:
         try:
-            line["suite"] = suite(dev, torch, hbm_peak, tf_peak, args.quick)
+            line["suite"] = suite(dev, torch, hbm_peak, tf_peak, args.quick, args.only.split(",") if args.only else None,
+                                  tuple(int(t) for t in args.c2_shape.split(",")), tuple(int(t) for t in args.c3_shape.split(",")), not args.llama_unfused)
         except Exception as e:  # the headline line must still print
             line["suite"] = {"error": repr(e)}
     if rank == 0:
@@ -369,6 +379,10 @@ def main():
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-suite", action="store_true")
     ap.add_argument("--quick", action="store_true", help="shorter prefill in the suite")
+    ap.add_argument("--only", default="", help="comma-separated substrings of suite entries to run (c1,c2,c3,c4_bf16_b1,...)")
+    ap.add_argument("--c2-shape", default="4096,2048,8192", help="M,K,N of the suite's GEMM (small cases for profiling)")
+    ap.add_argument("--llama-unfused", action="store_true", help="one stage per graph cone in the decode step")
+    ap.add_argument("--c3-shape", default="8,4096", help="batch,sequence of the suite's prefill attention")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3

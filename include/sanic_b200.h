@@ -171,7 +171,7 @@ int32_t sanic_gemm_rmsnorm(sanic_ctx* ctx, const sanic_gemm_rmsnorm_params* p, v
  *    with a bf16 scale per `group` inputs (tests/metal.rs:1224-1236). Up to three weight
  *    segments share one launch (q/k/v projections); a segment pair can be combined as
  *    silu(a)*b (src/ir.rs:1500-1509); the result can be added to a residual. ── */
-enum { SANIC_EPI_STORE = 0, SANIC_EPI_RESIDUAL_ADD = 1, SANIC_EPI_SILU_MUL = 2 };
+enum { SANIC_EPI_STORE = 0, SANIC_EPI_RESIDUAL_ADD = 1, SANIC_EPI_SILU_MUL = 2, SANIC_EPI_ROPE_CACHE = 3 };
 typedef struct {
     const void* x;            /* [batch, K] bf16 activations */
     int32_t batch, K;
@@ -185,6 +185,15 @@ typedef struct {
     int32_t out_dtype;        /* SANIC_F32 or SANIC_BF16 */
     int32_t epilogue;         /* SANIC_EPI_* ; SILU_MUL needs n_segments == 2 with equal rows, result in out[0] */
     const float* residual;    /* [batch, rows_0] f32 for RESIDUAL_ADD (may alias out[0] when out is f32) */
+    /* Optional inlined producer cone (the partitioner's leaf inlining, src/partition.rs:860-1016): when norm_x is
+     * set, the activations are bf16((norm_x * norm_gamma) / sqrt(mean(norm_x^2) + norm_eps)) computed inside the
+     * kernel from the f32 rows norm_x [batch, K], and `x` is ignored. */
+    const float* norm_x; const void* norm_gamma; float norm_eps;
+    /* ROPE_CACHE epilogue (three segments q, k, v of one decode step): rotate-half RoPE at *rope_position on q and
+     * k, q -> rope_q_out bf16 [B,Hq,D], k -> row *rope_position of the K cache [B,Hkv,ctx,D], v -> column
+     * *rope_position of the V cache [B,Hkv,D,ctx] (src/nn.rs:176-212); out[] is ignored. */
+    const float* rope_table; const int32_t* rope_position; void* rope_q_out; void* rope_k_cache; void* rope_v_cache;
+    int32_t rope_q_heads, rope_kv_heads, rope_head_dim, rope_ctx;
 } sanic_gemv_params;
 int32_t sanic_gemv(sanic_ctx* ctx, const sanic_gemv_params* p, void* stream);
 

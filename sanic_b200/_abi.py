@@ -16,7 +16,7 @@ F32, F16, BF16, U32, I4 = 1, 2, 3, 4, 5
 SLOT_PLAIN_ADD, SLOT_PLAIN_MAX, SLOT_PLAIN_MIN, SLOT_EXP_SHIFTED, SLOT_AT_EXTREMUM = 1, 2, 3, 4, 5
 KERNEL_NONE, KERNEL_ONLINE_SOFTMAX_FOLD, KERNEL_DEFERRED_NORM_CONTRACTION, KERNEL_PLAIN_CONTRACTION, \
     KERNEL_GROUPED_I4_CONTRACTION, KERNEL_EXTREMUM_INDEX = range(6)
-EPI_STORE, EPI_RESIDUAL_ADD, EPI_SILU_MUL = 0, 1, 2
+EPI_STORE, EPI_RESIDUAL_ADD, EPI_SILU_MUL, EPI_ROPE_CACHE = 0, 1, 2, 3
 STAGE_FUSED, STAGE_ELEMENTWISE, STAGE_GATHER = 1, 2, 3
 OP_GEMV, OP_DECODE_ATTN, OP_ARGMAX, OP_RMSNORM, OP_EMBED, OP_ROPE_CACHE, OP_ADVANCE = 1, 2, 3, 4, 5, 6, 7
 
@@ -57,7 +57,9 @@ class GemmRmsnormParams(C.Structure):
 class GemvParams(C.Structure):
     _fields_ = [("x", vp), ("batch", i32), ("K", i32), ("weight_dtype", i32), ("group", i32), ("n_segments", i32),
                 ("w", vp * 3), ("scales", vp * 3), ("rows", i32 * 3), ("out", vp * 3), ("out_dtype", i32),
-                ("epilogue", i32), ("residual", vp)]
+                ("epilogue", i32), ("residual", vp), ("norm_x", vp), ("norm_gamma", vp), ("norm_eps", f32),
+                ("rope_table", vp), ("rope_position", vp), ("rope_q_out", vp), ("rope_k_cache", vp), ("rope_v_cache", vp),
+                ("rope_q_heads", i32), ("rope_kv_heads", i32), ("rope_head_dim", i32), ("rope_ctx", i32)]
 
 
 class RopeCacheParams(C.Structure):

@@ -222,15 +222,17 @@ class CudaDevice:
             p.rows[i] = w.shape[0]
             if w4:
                 p.scales[i] = scales[i].data_ptr()
-            if i < len(outs):
+            if i < len(outs) and outs[i] is not None:
                 p.out[i] = outs[i].data_ptr()
         p.out_dtype, p.epilogue = out_dtype, epilogue
         p.residual = residual.data_ptr() if residual is not None else None
         return p
 
-    def gemv(self, x, weights, scales=None, epilogue=abi.EPI_STORE, residual=None, out_dtype=torch.float32):
-        """x [batch, K] bf16; weights: list of [rows, K] bf16 or [rows, K/2] uint8 (+ scales [rows, K/64] bf16)."""
-        self._on_device("x", x, torch.bfloat16)
+    def gemv(self, x, weights, scales=None, epilogue=abi.EPI_STORE, residual=None, out_dtype=torch.float32,
+             norm_gamma=None, norm_eps=1e-5):
+        """x [batch, K] bf16; weights: list of [rows, K] bf16 or [rows, K/2] uint8 (+ scales [rows, K/64] bf16).
+        With norm_gamma, x is the f32 residual stream and its RMSNorm is inlined into the contraction."""
+        self._on_device("x", x, torch.float32 if norm_gamma is not None else torch.bfloat16)
         weights = list(weights)
         for i, w in enumerate(weights):
             self._on_device(f"w[{i}]", w)
@@ -239,6 +241,9 @@ class CudaDevice:
         outs = [self.empty((batch, weights[i].shape[0]), out_dtype) for i in range(n_out)]
         p = self.gemv_params(x, weights, outs, scales, epilogue, residual,
                              abi.BF16 if out_dtype == torch.bfloat16 else abi.F32)
+        if norm_gamma is not None:
+            self._on_device("norm_gamma", norm_gamma, torch.bfloat16)
+            p.norm_x, p.norm_gamma, p.norm_eps = x.data_ptr(), norm_gamma.data_ptr(), float(norm_eps)
         self._check(self.lib.sanic_gemv(self.h, C.byref(p), self.stream()), "gemv")
         return outs[0] if n_out == 1 else outs
 

@@ -84,6 +84,8 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(sanic_decode_params p,
     constexpr int KS = D / 16;   // k-steps of the QK^T contraction
     constexpr int NT = D / 8;    // n-tiles of the output
 
+    griddep_launch();
+    griddep_wait();   // q, the caches and the position come from the previous kernels of the step
     const int kv_len = p.kv_len_dev ? (*p.kv_len_dev + 1) : p.kv_len;
     const int hi = kv_len;
     const int lo = (p.window > 0) ? max(0, kv_len - p.window) : 0;
@@ -259,12 +261,24 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(sanic_decode_params p,
     for (int idx = tid; idx < group * D; idx += 128) {
         int r = idx / D, d = idx % D;
         size_t row = (size_t)b * p.q_heads + (size_t)hk * group + r;
-        const volatile float* part = p.partials + row * p.n_splits * W;
-        float m = part[0], l = part[1], ov = part[2 + d];
-        for (int s = 1; s < p.n_splits; ++s) {
-            const volatile float* pb = part + (size_t)s * W;
-            MloScale sc = mlo_rescale(m, pb[0]);
-            l = l * sc.ra + pb[1] * sc.rb; ov = ov * sc.ra + pb[2 + d] * sc.rb; m = sc.m;
+        const float* part = p.partials + row * p.n_splits * W;
+        // The partials were written by other CTAs: read them from L2 (ld.global.cg), all loads
+        // independent of the combine chain so their latencies overlap. The combine itself runs
+        // left to right over the chunks, as stage 2 of the split reduction does.
+        float m = __ldcg(part), l = __ldcg(part + 1), ov = __ldcg(part + 2 + d);
+        for (int s0 = 1; s0 < p.n_splits; s0 += 8) {
+            float mb[8], lb[8], ob[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const bool in = s0 + u < p.n_splits;
+                const float* pb = part + (size_t)(in ? s0 + u : 0) * W;
+                mb[u] = in ? __ldcg(pb) : -INFINITY; lb[u] = in ? __ldcg(pb + 1) : 0.0f; ob[u] = in ? __ldcg(pb + 2 + d) : 0.0f;
+            }
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                MloScale sc = mlo_rescale(m, mb[u]);     // an identity partial (-inf, 0, 0) is absorbed
+                l = l * sc.ra + lb[u] * sc.rb; ov = ov * sc.ra + ob[u] * sc.rb; m = sc.m;
+            }
         }
         if (p.carrier_out) {
             float* c = p.carrier_out + row * W;
@@ -311,8 +325,8 @@ int32_t launch_decode(sanic_ctx* ctx, const sanic_decode_params& p, cudaStream_t
     SANIC_CUDA_CHECK(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<D>::SMEM));
     int* counters = (int*)(p.partials + (size_t)p.batch * p.q_heads * p.n_splits * (D + 2));
     dim3 grid(p.n_splits, p.kv_heads, p.batch);
-    kern<<<grid, 128, Cfg<D>::SMEM, st>>>(p, counters);
-    SANIC_LAUNCH_CHECK(ctx, "attn_decode_splitkv");
+    cudaError_t le = launch_pdl(kern, grid, dim3(128), (size_t)Cfg<D>::SMEM, st, p, counters);
+    if (le != cudaSuccess) return sanic_fail(ctx, SANIC_ERR_CUDA, std::string("attn_decode_splitkv: ") + cudaGetErrorString(le));
     return SANIC_OK;
 }
 }  // namespace

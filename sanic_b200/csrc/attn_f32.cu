@@ -1,11 +1,12 @@
 // Online-softmax fold in f32 storage and f32 CUDA-core arithmetic.
 //
-// One warp per query row. The key axis is streamed lane-split (lane j takes keys
-// j, j+32, ...); each lane keeps its own (m, l, o[Ev]) accumulator in registers and
-// the 32 lane accumulators are merged with a shuffle butterfly that applies the
-// carrier's own combine, the -inf guard included (reference src/derive.rs:1700-1713).
-// This is the lane_stream schedule of the reference's cooperative fold
-// (src/emit_metal.rs:760-1101, src/plan.rs:434-455), written for 32-wide warps.
+// One CTA of 8 warps per query row. The key axis is streamed lane-split (the 256 threads
+// take keys j, j+256, ...); each lane keeps its own (m, l, o[Ev]) accumulator in registers,
+// the 32 lane accumulators of a warp are merged with a shuffle butterfly and the 8 warp
+// accumulators through shared memory, every merge applying the carrier's own combine,
+// the -inf guard included (reference src/derive.rs:1700-1713). This is the lane_stream x
+// sgs schedule of the reference's cooperative fold (src/emit_metal.rs:760-1101,
+// src/plan.rs:434-455), written for 32-wide warps.
 //
 // A tensor-core TF32 contraction has a 10-bit mantissa and cannot hold the 1e-5
 // relative bound this path is checked at, so the contraction runs as FP32 FMAs and
@@ -15,21 +16,23 @@
 namespace {
 using namespace sanic;
 
+constexpr int FW = 8;   // warps (simdgroups) per query row
+
 template <int DV>
-__global__ void __launch_bounds__(128) attn_fwd_f32_kernel(sanic_attn_params p) {
+__global__ void __launch_bounds__(FW * 32) attn_fwd_f32_kernel(sanic_attn_params p) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int row = blockIdx.x * 4 + warp;
+    const int row = blockIdx.x;
     const int bh = blockIdx.y;
     const int b = bh / p.q_heads, h = bh % p.q_heads;
     const int hk = h / (p.q_heads / p.kv_heads);
     const int E = p.head_dim, Ev = p.v_dim, S = p.kv_len, L = p.q_len;
 
     extern __shared__ float smem[];
-    float* qs = smem + warp * E;
-    const float* Q = (const float*)p.q + ((size_t)bh * L + (row < L ? row : 0)) * E;
-    for (int d = lane; d < E; d += 32) qs[d] = Q[d];
-    __syncwarp();
-    if (row >= L) return;
+    float* qs = smem;                 // [E]
+    float* ws = smem + E;             // [FW][DV + 2] warp accumulators
+    const float* Q = (const float*)p.q + ((size_t)bh * L + row) * E;
+    for (int d = threadIdx.x; d < E; d += FW * 32) qs[d] = Q[d];
+    __syncthreads();
 
     const float* K = (const float*)p.k + ((size_t)(b * p.kv_heads + hk) * S) * E;
     const float* V = (const float*)p.v + ((size_t)(b * p.kv_heads + hk) * S) * Ev;
@@ -45,7 +48,7 @@ __global__ void __launch_bounds__(128) attn_fwd_f32_kernel(sanic_attn_params p) 
 #pragma unroll
     for (int e = 0; e < DV; ++e) o[e] = 0.0f;
 
-    for (int j = lo + lane; j < hi; j += 32) {
+    for (int j = lo + threadIdx.x; j < hi; j += FW * 32) {
         float s = 0.0f;
         if ((E & 3) == 0) {
             const float4* kr = (const float4*)(K + (size_t)j * E);
@@ -86,11 +89,26 @@ __global__ void __launch_bounds__(128) attn_fwd_f32_kernel(sanic_attn_params p) 
         }
         m = sc.m;
     }
-    // project: o / l
-    float* out = (float*)p.out + ((size_t)bh * L + row) * Ev;
+    // merge the warp accumulators left to right, then project: o / l
+    if (lane == 0) { ws[warp * (DV + 2)] = m; ws[warp * (DV + 2) + 1] = l; }
 #pragma unroll
     for (int e = 0; e < DV; ++e)
-        if (e < Ev && (e & 31) == lane) out[e] = o[e] / l;
+        if ((e & 31) == lane) ws[warp * (DV + 2) + 2 + e] = o[e];
+    __syncthreads();
+    if (warp == 0) {
+        float* out = (float*)p.out + ((size_t)bh * L + row) * Ev;
+        for (int e = lane; e < Ev; e += 32) {
+            float mm = ws[0], ll = ws[1], oo = ws[2 + e];
+#pragma unroll
+            for (int w = 1; w < FW; ++w) {
+                MloScale sc = mlo_rescale(mm, ws[w * (DV + 2)]);
+                ll = ll * sc.ra + ws[w * (DV + 2) + 1] * sc.rb;
+                oo = oo * sc.ra + ws[w * (DV + 2) + 2 + e] * sc.rb;
+                mm = sc.m;
+            }
+            out[e] = oo / ll;
+        }
+    }
 }
 }  // namespace
 
@@ -105,10 +123,11 @@ extern "C" int32_t sanic_attn_fwd_f32(sanic_ctx* ctx, const sanic_attn_params* p
     SANIC_REQUIRE(ctx, p->out_dtype == SANIC_F32, "attn_fwd_f32: output is f32");
     SANIC_REQUIRE(ctx, !(p->causal && p->mask), "attn_fwd_f32: attn_mask and is_causal cannot both be set");
     sanic_set_device(ctx);
-    dim3 grid((p->q_len + 3) / 4, p->batch * p->q_heads), block(128);
-    size_t smem = 4 * (size_t)p->head_dim * sizeof(float);
-    if (p->v_dim <= 32) attn_fwd_f32_kernel<32><<<grid, block, smem, (cudaStream_t)stream>>>(*p);
-    else if (p->v_dim <= 64) attn_fwd_f32_kernel<64><<<grid, block, smem, (cudaStream_t)stream>>>(*p);
+    dim3 grid(p->q_len, p->batch * p->q_heads), block(FW * 32);
+    const int dv = p->v_dim <= 32 ? 32 : (p->v_dim <= 64 ? 64 : 128);
+    size_t smem = ((size_t)p->head_dim + (size_t)FW * (dv + 2)) * sizeof(float);
+    if (dv == 32) attn_fwd_f32_kernel<32><<<grid, block, smem, (cudaStream_t)stream>>>(*p);
+    else if (dv == 64) attn_fwd_f32_kernel<64><<<grid, block, smem, (cudaStream_t)stream>>>(*p);
     else attn_fwd_f32_kernel<128><<<grid, block, smem, (cudaStream_t)stream>>>(*p);
     SANIC_LAUNCH_CHECK(ctx, "attn_fwd_f32");
     return SANIC_OK;

@@ -29,6 +29,10 @@ constexpr int Q_BYTES = BM * D * 2;        // 16 KB per query tile
 constexpr int KV_BYTES = BN * D * 2;       // 16 KB per K or V tile
 constexpr int P_BYTES = BM * BN * 2;       // 32 KB per P tile (two 64-key halves)
 constexpr int NTHREADS = 384;
+#ifndef SANIC_FLASH_POLY_EVERY
+#define SANIC_FLASH_POLY_EVERY 0
+#endif
+constexpr int POLY_EVERY = SANIC_FLASH_POLY_EVERY;   // every n-th pair sends one exponential to the FMA-pipe polynomial (0 = none)
 
 struct FShared {
     uint64_t q_full, k_full[KV_STAGES], v_full[KV_STAGES], kv_empty[KV_STAGES];
@@ -47,6 +51,21 @@ __device__ __forceinline__ float ex2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
+}
+
+// exp2 on the FMA pipes: round-to-nearest split x = n + f with f in [-0.5, 0.5] by the magic-number
+// add, a degree-3 minimax polynomial for 2^f (max relative error 7.5e-5, far below the 2^-9 of
+// the bf16 P it feeds), and n added into the exponent field. The SFU evaluates 16 exponentials
+// per clock per SM, which at head_dim 64 is twice the time of the tile's MMAs, so every other
+// score takes this path and the two pipes run side by side.
+__device__ __forceinline__ float ex2_poly(float x) {
+    x = fmaxf(x, -126.0f);
+    const float t = x + 12582912.0f;             // 1.5 * 2^23: the integer part lands in the low mantissa bits
+    const float f = x - (t - 12582912.0f);
+    float p = fmaf(0.05517164617776871f, f, 0.2426111251115799f);
+    p = fmaf(p, f, 0.6932609677314758f);
+    p = fmaf(p, f, 0.9999280571937561f);
+    return __int_as_float(__float_as_int(p) + (__float_as_int(t) << 23));
 }
 
 // key-tile range [jb, je) that tile rows [r0, r0+127] can see
@@ -188,67 +207,65 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             int klo = 0, khi = p.kv_len;              // visible keys of this row: [klo, khi)
             if (p.causal || p.window > 0) khi = min(khi, grow + 1);
             if (p.window > 0) klo = max(0, grow - p.window + 1);
-            // pass 1: row max
-            float mx = -INFINITY;
-#pragma unroll 1
-            for (int c = 0; c < BN / 32; ++c) {
-                uint32_t r[32];
-                tmem_ld32(s_tmem + c * 32, r);
-                if (edge) {
+            // the whole score row of this tile in registers: one TMEM round trip
+            uint32_t r[BN];
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) { int kk = k0 + c * 32 + i; if (kk >= klo && kk < khi) mx = fmaxf(mx, __uint_as_float(r[i])); }
-                } else {
+            for (int c = 0; c < BN / 32; ++c) tmem_ld32_nowait(s_tmem + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&r[c * 32]));
+            tmem_ld_wait();
+            if (edge) {
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(r[i]));
-                }
+                for (int i = 0; i < BN; ++i) { int kk = k0 + i; if (!(kk >= klo && kk < khi)) r[i] = 0xFF800000u; }  // -inf
             }
-            const float m_new = fmaxf(m, mx * sl2);
-            const float alpha = (m > -INFINITY) ? ex2(m - m_new) : 0.0f;   // weight 0 for an empty accumulator
-            const float msub = (m_new > -INFINITY) ? m_new : 0.0f;
+            // eight independent chains instead of one 128-long dependent chain of max
+            float mxs[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) mxs[i] = __uint_as_float(r[i]);
+#pragma unroll
+            for (int i = 8; i < BN; ++i) mxs[i & 7] = fmaxf(mxs[i & 7], __uint_as_float(r[i]));
+            const float mx = fmaxf(fmaxf(fmaxf(mxs[0], mxs[1]), fmaxf(mxs[2], mxs[3])), fmaxf(fmaxf(mxs[4], mxs[5]), fmaxf(mxs[6], mxs[7])));
+            // Lazy rescale: keep the reference max until the running max has moved by more than
+            // 2^8; exp2(s - m_ref) then stays below 256, well inside bf16/f32 range, and o / l is
+            // unchanged because both carry the same reference.
+            const float m_cand = fmaxf(m, mx * sl2);
+            const bool need = (m_cand - m > 8.0f) || (!(m > -INFINITY) && m_cand > -INFINITY);
+            float alpha = 1.0f;
+            if (need) { alpha = (m > -INFINITY) ? ex2(m - m_cand) : 0.0f; m = m_cand; }
+            const float msub = (m > -INFINITY) ? m : 0.0f;
             if (it > 0) {
                 ok = mbar_wait(&sh->pv_done[t], (it - 1) & 1, abortp, err, 22);  // O_t final for tile j-1, P_t free
                 if (!ok) break;
                 fence_after();
-                if (__any_sync(0xffffffffu, alpha != 1.0f)) {
+                if (__any_sync(0xffffffffu, need)) {
 #pragma unroll 1
                     for (int c = 0; c < D / 32; ++c) {
-                        uint32_t r[32];
-                        tmem_ld32(o_tmem + c * 32, r);
+                        uint32_t o[32];
+                        tmem_ld32(o_tmem + c * 32, o);
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-                        tmem_st32(o_tmem + c * 32, r);
+                        for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                        tmem_st32(o_tmem + c * 32, o);
                     }
                     tmem_st_wait();
                 }
             }
-            // pass 2: P = exp2(S*sl2 - m_new) -> bf16 -> shared (K-major, 128B swizzle), row sum
-            float sum = 0.0f;
-#pragma unroll 1
-            for (int c = 0; c < BN / 32; ++c) {
-                uint32_t r[32];
-                tmem_ld32(s_tmem + c * 32, r);
-                uint32_t pk[16];
+            // P = exp2(S*sl2 - m_ref) -> bf16 -> shared (K-major, 128B swizzle), row sum
+            float sums[8] = {0, 0, 0, 0, 0, 0, 0, 0};
 #pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    float s0 = __uint_as_float(r[2 * i]), s1 = __uint_as_float(r[2 * i + 1]);
-                    if (edge) {
-                        int kk = k0 + c * 32 + 2 * i;
-                        if (!(kk >= klo && kk < khi)) s0 = -INFINITY;
-                        if (!(kk + 1 >= klo && kk + 1 < khi)) s1 = -INFINITY;
-                    }
-                    float p0 = ex2(fmaf(s0, sl2, -msub)), p1 = ex2(fmaf(s1, sl2, -msub));
-                    sum += p0 + p1;
+            for (int cc = 0; cc < BN / 8; ++cc) {
+                uint32_t pk[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    float p0 = ex2(fmaf(__uint_as_float(r[cc * 8 + 2 * i]), sl2, -msub));
+                    float p1 = (POLY_EVERY > 0 && ((cc * 4 + i) % (POLY_EVERY > 0 ? POLY_EVERY : 1)) == 0)
+                                   ? ex2_poly(fmaf(__uint_as_float(r[cc * 8 + 2 * i + 1]), sl2, -msub))
+                                   : ex2(fmaf(__uint_as_float(r[cc * 8 + 2 * i + 1]), sl2, -msub));
+                    sums[2 * i] += p0; sums[2 * i + 1] += p1;
                     pk[i] = pack_bf16x2(p0, p1);
                 }
-#pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    const int cc = c * 4 + q;                 // 16-byte chunk index along the 128 keys
-                    unsigned char* dst = prow + (cc >> 3) * (BM * 128) + (((cc & 7) ^ (row & 7)) << 4);
-                    *(uint4*)dst = make_uint4(pk[4 * q], pk[4 * q + 1], pk[4 * q + 2], pk[4 * q + 3]);
-                }
+                unsigned char* dst = prow + (cc >> 3) * (BM * 128) + (((cc & 7) ^ (row & 7)) << 4);
+                *(uint4*)dst = make_uint4(pk[0], pk[1], pk[2], pk[3]);
             }
+            const float sum = ((sums[0] + sums[1]) + (sums[2] + sums[3])) + ((sums[4] + sums[5]) + (sums[6] + sums[7]));
             l = l * alpha + sum;
-            m = m_new;
             fence_before();
             fence_async_smem();
             __syncwarp();

@@ -3,6 +3,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <cstdlib>
 #include <string>
 
 #include "../../include/sanic_b200.h"
@@ -53,6 +54,25 @@ static inline int sanic_set_device(sanic_ctx* ctx) { return (int)cudaSetDevice(c
 
 #ifdef __CUDACC__
 namespace sanic {
+
+// Programmatic dependent launch: a kernel launched this way may start while its predecessor in the
+// stream drains. It must execute griddep_wait() before it touches memory the predecessor wrote
+// (every kernel of a chain does, so completion stays transitive) and may call griddep_launch()
+// early to let its own successor begin its prologue.
+template <typename... KArgs, typename... Args>
+static inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                                     Args... args) {
+    static const bool pdl = (getenv("SANIC_NO_PDL") == nullptr);   // SANIC_NO_PDL=1: plain stream order (for A/B timing)
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr; cfg.numAttrs = pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void griddep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float LN2 = 0.6931471805599453f;

@@ -229,7 +229,9 @@ gemm_rmsnorm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     for (int j = 0; j < 4; ++j) {
                         float x0 = bf16lo(xs[j]), x1 = bf16hi(xs[j]);
                         ss = fmaf(x0, x0, ss); ss = fmaf(x1, x1, ss);
-                        xs[j] = pack_bf16x2(x0 * bf16lo(gs[j]), x1 * bf16hi(gs[j]));
+                        // bf16 x bf16 is exact in f32, so the packed bf16 multiply (round to nearest even
+                        // of the exact product) equals bf16(float(x) * float(g)) bit for bit
+                        asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(xs[j]) : "r"(xs[j]), "r"(gs[j]));
                     }
                     *ptr = make_uint4(xs[0], xs[1], xs[2], xs[3]);
                 }

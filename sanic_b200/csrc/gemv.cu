@@ -16,8 +16,19 @@
 // scale is pure axis structure).
 //
 // Work split: one CTA = 16 output rows (x 2 matrices for the silu(a)*b pair), its 8
-// warps take contiguous K ranges and are summed in a fixed order through shared memory,
-// so results are deterministic.
+// warps take contiguous K ranges and are summed in a fixed order through shared memory.
+// When there are too few row tiles to fill the SMs, a thread-block cluster of 2-8 CTAs
+// shares a tile, splits K, and rank 0 adds the peers' sums in rank order through
+// distributed shared memory. Results are deterministic.
+//
+// Fusions that remove launches from a decode step:
+//   * NORM: the producer cone of the activations (RMSNorm of the f32 residual stream) is
+//     inlined: every CTA recomputes the row norms (a few KB from L2) and builds its bf16
+//     activation fragments as bf16((x*g) * (1/den)) on the fly.
+//   * ROPE_CACHE epilogue: for the q/k/v projections the CTA's 16 rows are the rotate-half
+//     partners (d, d + D/2) of one head, so the epilogue rotates them and writes q, the K
+//     cache row and the V cache column of the current position in place.
+// Launched with programmatic dependent launch: weight prefetch runs before the wait.
 #include "common.cuh"
 
 namespace {
@@ -32,6 +43,11 @@ struct SegTable {
     int rows[3];
     int tile_begin[4];
 };
+struct Fused {
+    const float* norm_x; const uint16_t* norm_gamma; float norm_eps;
+    const float* rope_table; const int32_t* rope_position; uint16_t* rope_q_out; uint16_t* rope_k_cache; uint16_t* rope_v_cache;
+    int q_heads, kv_heads, head_dim, ctx;
+};
 
 __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
     uint32_t r;
@@ -43,19 +59,90 @@ __device__ __forceinline__ uint32_t nib_pair(uint32_t w) {  // (w & 0x000F000F) 
     asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(r) : "r"(w), "r"(0x000F000Fu), "r"(0x43004300u));
     return r;
 }
+__device__ __forceinline__ const void* pick3(const void* const (&a)[3], int i) { return i == 0 ? a[0] : (i == 1 ? a[1] : a[2]); }
 
-template <bool W4, int NT, bool DUAL>
-__global__ void __launch_bounds__(GW * 32) gemv_mma_kernel(const uint16_t* __restrict__ x, int batch, int K,
+// 8 consecutive activations of batch column n starting at k as four packed bf16x2 registers.
+template <bool NORM>
+__device__ __forceinline__ uint4 load_x8(const uint16_t* xrow, const float* xf, const uint16_t* gamma, float den, int k,
+                                         bool ok) {
+    if (!ok) return make_uint4(0, 0, 0, 0);
+    if (!NORM) return __ldg((const uint4*)(xrow + k));
+    float4 a = __ldg((const float4*)(xf + k)), b = __ldg((const float4*)(xf + k + 4));
+    uint4 g = __ldg((const uint4*)(gamma + k));
+    uint4 r;
+    // `den` holds 1/sqrt(mean(x^2)+eps): one multiply per element instead of a division
+    r.x = pack_bf16x2((a.x * bf16lo(g.x)) * den, (a.y * bf16hi(g.x)) * den);
+    r.y = pack_bf16x2((a.z * bf16lo(g.y)) * den, (a.w * bf16hi(g.y)) * den);
+    r.z = pack_bf16x2((b.x * bf16lo(g.z)) * den, (b.y * bf16hi(g.z)) * den);
+    r.w = pack_bf16x2((b.z * bf16lo(g.w)) * den, (b.w * bf16hi(g.w)) * den);
+    return r;
+}
+
+template <bool W4, int NT, bool DUAL, bool NORM>
+__global__ void __launch_bounds__(GW * 32, 2) gemv_mma_kernel(const uint16_t* __restrict__ x, int batch, int K,
                                                            SegTable segs, int n_segments, int out_dtype, int epilogue,
-                                                           const float* residual) {
+                                                           const float* residual, Fused fz, int KS) {
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, t = lane & 3;
+    // KS CTAs of one thread-block cluster share a row tile and split K between them
+    const int gtile = (int)blockIdx.x / KS, krank = (int)blockIdx.x % KS;
     int seg = 0;
     if (!DUAL) {
-        while (seg + 1 < n_segments && (int)blockIdx.x >= segs.tile_begin[seg + 1]) ++seg;
+        if (n_segments > 1 && gtile >= segs.tile_begin[1]) seg = 1;
+        if (n_segments > 2 && gtile >= segs.tile_begin[2]) seg = 2;
     }
-    const int row0 = ((int)blockIdx.x - segs.tile_begin[seg]) * 16;
+    const int tile = gtile - (seg == 0 ? segs.tile_begin[0] : (seg == 1 ? segs.tile_begin[1] : segs.tile_begin[2]));
+    const bool rope = (epilogue == SANIC_EPI_ROPE_CACHE);
+    // weight rows of A-fragment rows g and g+8
+    int wrow0, wrow1;
+    if (rope) {   // rotate-half partners of one head: d = 8*sub + g and d + D/2
+        const int tph = fz.head_dim / 16, head = tile / tph, sub = tile % tph;
+        wrow0 = head * fz.head_dim + 8 * sub + g;
+        wrow1 = wrow0 + fz.head_dim / 2;
+    } else {
+        wrow0 = tile * 16 + g;
+        wrow1 = wrow0 + 8;
+    }
     constexpr int NM = DUAL ? 2 : 1;
+    const int nblk = K / 64;
+    const int cb0 = (krank * nblk) / KS, cb1 = ((krank + 1) * nblk) / KS;   // this CTA's K range, in 64-blocks
+    const int b0 = cb0 + (warp * (cb1 - cb0)) / GW, b1 = cb0 + ((warp + 1) * (cb1 - cb0)) / GW;
+
+    // Weights do not depend on the previous kernel of the step: ask L2 for this warp's whole weight
+    // slice (16 rows x its K range) before waiting for that kernel, so HBM keeps streaming while
+    // the predecessor drains.
+    {
+        const size_t row_bytes = W4 ? (size_t)K / 2 : (size_t)K * 2;
+        const int blk_bytes = W4 ? 32 : 128;
+        const int span = (b1 - b0) * blk_bytes;
+        const int lines = (span + 127) / 128;
+#pragma unroll
+        for (int mI = 0; mI < NM; ++mI) {
+            const char* wbase = (const char*)pick3(segs.w, DUAL ? mI : seg);
+            for (int i = lane; i < 16 * lines; i += 32) {
+                const int r = i / lines, ln = i % lines;
+                const size_t wrow = (r < 8) ? (size_t)(wrow0 - g + r) : (size_t)(wrow1 - g + r - 8);
+                asm volatile("prefetch.global.L2 [%0];" ::"l"(wbase + wrow * row_bytes + (size_t)b0 * blk_bytes + (size_t)ln * 128));
+            }
+        }
+    }
+    griddep_launch();
+    griddep_wait();
+
+    __shared__ float s_den[16];
+    if (NORM) {
+        for (int n = warp; n < batch; n += GW) {
+            const float* xr = fz.norm_x + (size_t)n * K;
+            float ss = 0.0f;
+            for (int i = lane * 4; i < K; i += 128) {
+                float4 v = __ldg((const float4*)(xr + i));
+                ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
+            }
+            ss = warp_sum(ss);
+            if (lane == 0) s_den[n] = 1.0f / sqrtf(ss * (1.0f / (float)K) + fz.norm_eps);
+        }
+        __syncthreads();
+    }
 
     float acc[NM][NT][4];
 #pragma unroll
@@ -63,79 +150,74 @@ __global__ void __launch_bounds__(GW * 32) gemv_mma_kernel(const uint16_t* __res
 #pragma unroll
         for (int j = 0; j < NT; ++j) acc[mI][j][0] = acc[mI][j][1] = acc[mI][j][2] = acc[mI][j][3] = 0.0f;
 
-    const int nblk = K / 64;
-    const int b0 = (warp * nblk) / GW, b1 = ((warp + 1) * nblk) / GW;
     const uint16_t* xrow[NT];
+    const float* xf[NT];
+    float den[NT];
     bool xok[NT];
 #pragma unroll
     for (int j = 0; j < NT; ++j) {
         xok[j] = (8 * j + g) < batch;
-        xrow[j] = x + (size_t)(xok[j] ? (8 * j + g) : 0) * K;
+        const int n = xok[j] ? (8 * j + g) : 0;
+        xrow[j] = x + (size_t)n * K;
+        xf[j] = NORM ? fz.norm_x + (size_t)n * K : nullptr;
+        den[j] = NORM ? s_den[n] : 1.0f;
     }
+    const uint16_t* gam = fz.norm_gamma;
 
     if (!W4) {
         const uint16_t* wr[NM][2];
 #pragma unroll
         for (int mI = 0; mI < NM; ++mI) {
-            const uint16_t* W = (const uint16_t*)segs.w[DUAL ? mI : seg];
-            wr[mI][0] = W + (size_t)(row0 + g) * K;
-            wr[mI][1] = W + (size_t)(row0 + g + 8) * K;
+            const uint16_t* W = (const uint16_t*)pick3(segs.w, DUAL ? mI : seg);
+            wr[mI][0] = W + (size_t)wrow0 * K;
+            wr[mI][1] = W + (size_t)wrow1 * K;
         }
         constexpr int U = DUAL ? 2 : 4;
-        int blk = b0;
-        for (; blk + U <= b1; blk += U) {
+        for (int blk = b0; blk < b1; blk += U) {
+            const int nb = min(U, b1 - blk);      // uniform across the warp
             uint4 a[U][NM][2][2];
             uint4 xb[U][NT][2];
 #pragma unroll
             for (int u = 0; u < U; ++u) {
-                int kb = (blk + u) * 64;
+                if (u < nb) {
+                    int kb = (blk + u) * 64;
 #pragma unroll
-                for (int mI = 0; mI < NM; ++mI)
+                    for (int mI = 0; mI < NM; ++mI)
 #pragma unroll
-                    for (int r = 0; r < 2; ++r) {
-                        a[u][mI][r][0] = ldg_stream16(wr[mI][r] + kb + t * 8);
-                        a[u][mI][r][1] = ldg_stream16(wr[mI][r] + kb + 32 + t * 8);
-                    }
+                        for (int r = 0; r < 2; ++r) {
+                            a[u][mI][r][0] = ldg_stream16(wr[mI][r] + kb + t * 8);
+                            a[u][mI][r][1] = ldg_stream16(wr[mI][r] + kb + 32 + t * 8);
+                        }
+                }
             }
 #pragma unroll
             for (int u = 0; u < U; ++u) {
-                int kb = (blk + u) * 64;
+                if (u < nb) {
+                    int kb = (blk + u) * 64;
 #pragma unroll
-                for (int j = 0; j < NT; ++j) {
-                    xb[u][j][0] = xok[j] ? __ldg((const uint4*)(xrow[j] + kb + t * 8)) : make_uint4(0, 0, 0, 0);
-                    xb[u][j][1] = xok[j] ? __ldg((const uint4*)(xrow[j] + kb + 32 + t * 8)) : make_uint4(0, 0, 0, 0);
+                    for (int j = 0; j < NT; ++j) {
+                        xb[u][j][0] = load_x8<NORM>(xrow[j], xf[j], gam, den[j], kb + t * 8, xok[j]);
+                        xb[u][j][1] = load_x8<NORM>(xrow[j], xf[j], gam, den[j], kb + 32 + t * 8, xok[j]);
+                    }
                 }
             }
 #pragma unroll
-            for (int u = 0; u < U; ++u)
+            for (int u = 0; u < U; ++u) {
+                if (u < nb) {
 #pragma unroll
-                for (int mI = 0; mI < NM; ++mI)
+                    for (int mI = 0; mI < NM; ++mI)
 #pragma unroll
-                    for (int j = 0; j < NT; ++j)
+                        for (int j = 0; j < NT; ++j)
 #pragma unroll
-                        for (int hf = 0; hf < 2; ++hf) {
-                            const uint4& r0 = a[u][mI][0][hf];
-                            const uint4& r1 = a[u][mI][1][hf];
-                            const uint4& xv = xb[u][j][hf];
-                            mma_bf16_16816(acc[mI][j], r0.x, r1.x, r0.y, r1.y, xv.x, xv.y);
-                            mma_bf16_16816(acc[mI][j], r0.z, r1.z, r0.w, r1.w, xv.z, xv.w);
-                        }
-        }
-        for (; blk < b1; ++blk) {
-            int kb = blk * 64;
-#pragma unroll
-            for (int mI = 0; mI < NM; ++mI)
-#pragma unroll
-                for (int hf = 0; hf < 2; ++hf) {
-                    uint4 r0 = ldg_stream16(wr[mI][0] + kb + hf * 32 + t * 8);
-                    uint4 r1 = ldg_stream16(wr[mI][1] + kb + hf * 32 + t * 8);
-#pragma unroll
-                    for (int j = 0; j < NT; ++j) {
-                        uint4 xv = xok[j] ? __ldg((const uint4*)(xrow[j] + kb + hf * 32 + t * 8)) : make_uint4(0, 0, 0, 0);
-                        mma_bf16_16816(acc[mI][j], r0.x, r1.x, r0.y, r1.y, xv.x, xv.y);
-                        mma_bf16_16816(acc[mI][j], r0.z, r1.z, r0.w, r1.w, xv.z, xv.w);
-                    }
+                            for (int hf = 0; hf < 2; ++hf) {
+                                const uint4& r0 = a[u][mI][0][hf];
+                                const uint4& r1 = a[u][mI][1][hf];
+                                const uint4& xv = xb[u][j][hf];
+                                mma_bf16_16816(acc[mI][j], r0.x, r1.x, r0.y, r1.y, xv.x, xv.y);
+                                mma_bf16_16816(acc[mI][j], r0.z, r1.z, r0.w, r1.w, xv.z, xv.w);
+                            }
                 }
+            }
         }
     } else {
         const int G = K / 64;  // groups per row
@@ -143,12 +225,13 @@ __global__ void __launch_bounds__(GW * 32) gemv_mma_kernel(const uint16_t* __res
         const uint16_t* sr[NM][2];
 #pragma unroll
         for (int mI = 0; mI < NM; ++mI) {
-            const uint8_t* W = (const uint8_t*)segs.w[DUAL ? mI : seg];
-            const uint16_t* S = segs.scales[DUAL ? mI : seg];
-            wr[mI][0] = W + (size_t)(row0 + g) * (K / 2);
-            wr[mI][1] = W + (size_t)(row0 + g + 8) * (K / 2);
-            sr[mI][0] = S + (size_t)(row0 + g) * G;
-            sr[mI][1] = S + (size_t)(row0 + g + 8) * G;
+            const uint8_t* W = (const uint8_t*)pick3(segs.w, DUAL ? mI : seg);
+            const int si = DUAL ? mI : seg;
+            const uint16_t* S = si == 0 ? segs.scales[0] : (si == 1 ? segs.scales[1] : segs.scales[2]);
+            wr[mI][0] = W + (size_t)wrow0 * (K / 2);
+            wr[mI][1] = W + (size_t)wrow1 * (K / 2);
+            sr[mI][0] = S + (size_t)wrow0 * G;
+            sr[mI][1] = S + (size_t)wrow1 * G;
         }
         constexpr int U = DUAL ? 2 : 4;
         const uint32_t ONES = 0x3F803F80u;
@@ -156,8 +239,8 @@ __global__ void __launch_bounds__(GW * 32) gemv_mma_kernel(const uint16_t* __res
             int kb = blk * 64 + t * 16;
 #pragma unroll
             for (int j = 0; j < NT; ++j) {
-                uint4 xa = xok[j] ? __ldg((const uint4*)(xrow[j] + kb)) : make_uint4(0, 0, 0, 0);
-                uint4 xc = xok[j] ? __ldg((const uint4*)(xrow[j] + kb + 8)) : make_uint4(0, 0, 0, 0);
+                uint4 xa = load_x8<NORM>(xrow[j], xf[j], gam, den[j], kb, xok[j]);
+                uint4 xc = load_x8<NORM>(xrow[j], xf[j], gam, den[j], kb + 8, xok[j]);
                 // activation pairs matching the nibble pairing (n_i, n_{i+4})
                 uint32_t bA0 = prmt(xa.x, xa.z, 0x5410), bA1 = prmt(xa.x, xa.z, 0x7632);
                 uint32_t bA2 = prmt(xa.y, xa.w, 0x5410), bA3 = prmt(xa.y, xa.w, 0x7632);
@@ -183,33 +266,25 @@ __global__ void __launch_bounds__(GW * 32) gemv_mma_kernel(const uint16_t* __res
                 }
             }
         };
-        int blk = b0;
-        for (; blk + U <= b1; blk += U) {
+        for (int blk = b0; blk < b1; blk += U) {
+            const int nb = min(U, b1 - blk);
             uint2 wv[U][NM][2];
             float sc[U][NM][2];
 #pragma unroll
-            for (int u = 0; u < U; ++u)
+            for (int u = 0; u < U; ++u) {
+                if (u < nb) {
 #pragma unroll
-                for (int mI = 0; mI < NM; ++mI)
+                    for (int mI = 0; mI < NM; ++mI)
 #pragma unroll
-                    for (int r = 0; r < 2; ++r) {
-                        wv[u][mI][r] = ldg_stream8(wr[mI][r] + (size_t)(blk + u) * 32 + t * 8);
-                        sc[u][mI][r] = bf16_to_f32(__ldg(sr[mI][r] + blk + u));
-                    }
-#pragma unroll
-            for (int u = 0; u < U; ++u) do_group(wv[u], sc[u], blk + u);
-        }
-        for (; blk < b1; ++blk) {
-            uint2 wv[NM][2];
-            float sc[NM][2];
-#pragma unroll
-            for (int mI = 0; mI < NM; ++mI)
-#pragma unroll
-                for (int r = 0; r < 2; ++r) {
-                    wv[mI][r] = ldg_stream8(wr[mI][r] + (size_t)blk * 32 + t * 8);
-                    sc[mI][r] = bf16_to_f32(__ldg(sr[mI][r] + blk));
+                        for (int r = 0; r < 2; ++r) {
+                            wv[u][mI][r] = ldg_stream8(wr[mI][r] + (size_t)(blk + u) * 32 + t * 8);
+                            sc[u][mI][r] = bf16_to_f32(__ldg(sr[mI][r] + blk + u));
+                        }
                 }
-            do_group(wv, sc, blk);
+            }
+#pragma unroll
+            for (int u = 0; u < U; ++u)
+                if (u < nb) do_group(wv[u], sc[u], blk + u);
         }
     }
 
@@ -225,58 +300,144 @@ __global__ void __launch_bounds__(GW * 32) gemv_mma_kernel(const uint16_t* __res
             red[warp][mI][g + 8][8 * j + 2 * t + 1] = acc[mI][j][3];
         }
     __syncthreads();
+    // CTA sum in a fixed warp order, then (KS > 1) the cluster's CTAs are summed in rank order by
+    // rank 0 through distributed shared memory: deterministic, no global scratch.
+    __shared__ float csum[NM][16][8 * NT + 1];
+    for (int idx = tid; idx < NM * 16 * 8 * NT; idx += GW * 32) {
+        const int n = idx % (8 * NT), r = (idx / (8 * NT)) % 16, mI = idx / (8 * NT * 16);
+        float sv = 0.0f;
+#pragma unroll
+        for (int w = 0; w < GW; ++w) sv += red[w][mI][r][n];
+        csum[mI][r][n] = sv;
+    }
+    __syncthreads();
+    if (KS > 1) {
+        asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+        if (krank == 0) {
+            for (int idx = tid; idx < NM * 16 * 8 * NT; idx += GW * 32) {
+                const int n = idx % (8 * NT), r = (idx / (8 * NT)) % 16, mI = idx / (8 * NT * 16);
+                float sv = csum[mI][r][n];
+                const uint32_t local = smem_u32(&csum[mI][r][n]);
+                for (int kr = 1; kr < KS; ++kr) {
+                    uint32_t remote; float v;
+                    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(kr));
+                    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote));
+                    sv += v;
+                }
+                red[0][mI][r][n] = sv;     // rank 0 publishes the cluster total for its epilogue
+            }
+        }
+        // peers stay alive until rank 0 has read their shared memory
+        asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+        if (krank != 0) return;
+        __syncthreads();
+    } else {
+        for (int idx = tid; idx < NM * 16 * 8 * NT; idx += GW * 32) {
+            const int n = idx % (8 * NT), r = (idx / (8 * NT)) % 16, mI = idx / (8 * NT * 16);
+            red[0][mI][r][n] = csum[mI][r][n];
+        }
+        __syncthreads();
+    }
+    if (rope) {
+        // thread (r < 8, n): partners a = row r (d0 = 8*sub + r) and b = row r + 8 (d0 + D/2)
+        const int D = fz.head_dim, F = D / 2, tph = D / 16;
+        const int head = tile / tph, sub = tile % tph;
+        const int pos = *fz.rope_position;
+        for (int idx = tid; idx < 8 * batch; idx += GW * 32) {
+            const int n = idx / 8, r = idx % 8;
+            const float a = red[0][0][r][n], b = red[0][0][r + 8][n];
+            const int d0 = 8 * sub + r;
+            if (pos < 0 || pos >= fz.ctx) continue;
+            if (seg < 2) {
+                const float* cs = fz.rope_table + 2 * ((size_t)pos * F + d0);
+                const float c = cs[0], sn = cs[1];
+                const uint16_t o0 = f32_to_bf16_bits(a * c + (-b) * sn), o1 = f32_to_bf16_bits(b * c + a * sn);
+                uint16_t* dst = (seg == 0) ? fz.rope_q_out + ((size_t)n * fz.q_heads + head) * D
+                                           : fz.rope_k_cache + (((size_t)n * fz.kv_heads + head) * fz.ctx + pos) * D;
+                dst[d0] = o0; dst[d0 + F] = o1;
+            } else {
+                uint16_t* dst = fz.rope_v_cache + ((size_t)n * fz.kv_heads + head) * D * (size_t)fz.ctx;
+                dst[(size_t)d0 * fz.ctx + pos] = f32_to_bf16_bits(a);
+                dst[(size_t)(d0 + F) * fz.ctx + pos] = f32_to_bf16_bits(b);
+            }
+        }
+        return;
+    }
+    const int row0 = tile * 16;
+    const int rows = seg == 0 ? segs.rows[0] : (seg == 1 ? segs.rows[1] : segs.rows[2]);
+    void* outp = seg == 0 ? segs.out[0] : (seg == 1 ? segs.out[1] : segs.out[2]);
     for (int idx = tid; idx < 16 * batch; idx += GW * 32) {
         int n = idx / 16, r = idx % 16;  // consecutive threads -> consecutive rows (contiguous in out[n][row])
-        float v[NM];
-#pragma unroll
-        for (int mI = 0; mI < NM; ++mI) {
-            float s = 0.0f;
-#pragma unroll
-            for (int w = 0; w < GW; ++w) s += red[w][mI][r][n];
-            v[mI] = s;
-        }
-        float y = v[0];
+        float y = red[0][0][r][n];
         if (DUAL) {  // silu(a) * b = (a * 1/(1+exp(-a))) * b  (reference src/ir.rs:1500-1509)
-            float sig = 1.0f / (1.0f + expf(-v[0]));
-            y = (v[0] * sig) * v[NM - 1];
+            const float ga = y, up = red[0][NM - 1][r][n];
+            float sig = 1.0f / (1.0f + expf(-ga));
+            y = (ga * sig) * up;
         }
-        int rows = segs.rows[seg];
         size_t oi = (size_t)n * rows + row0 + r;
         if (epilogue == SANIC_EPI_RESIDUAL_ADD) y = residual[oi] + y;
-        if (out_dtype == SANIC_BF16) ((uint16_t*)segs.out[seg])[oi] = f32_to_bf16_bits(y);
-        else ((float*)segs.out[seg])[oi] = y;
+        if (out_dtype == SANIC_BF16) ((uint16_t*)outp)[oi] = f32_to_bf16_bits(y);
+        else ((float*)outp)[oi] = y;
     }
 }
 
-template <bool W4, int NT, bool DUAL>
-int32_t launch(sanic_ctx* ctx, const sanic_gemv_params& p, const SegTable& segs, int tiles, cudaStream_t st) {
-    gemv_mma_kernel<W4, NT, DUAL><<<tiles, GW * 32, 0, st>>>((const uint16_t*)p.x, p.batch, p.K, segs, p.n_segments,
-                                                             p.out_dtype, p.epilogue, p.residual);
-    SANIC_LAUNCH_CHECK(ctx, "gemv");
+template <bool W4, int NT, bool DUAL, bool NORM>
+int32_t launch(sanic_ctx* ctx, const sanic_gemv_params& p, const SegTable& segs, const Fused& fz, int tiles, cudaStream_t st) {
+    // Few row tiles cannot fill 148 SMs: split K over a cluster of KS CTAs per tile (each warp keeps
+    // at least one 64-block of K).
+    int KS = 1;
+    const int nblk = p.K / 64;
+    static const int ks_cap = getenv("SANIC_GEMV_KS") ? atoi(getenv("SANIC_GEMV_KS")) : 1;   // tuning knob: measured no gain on B200 at decode shapes, so off by default
+    while (KS < ks_cap && tiles * KS < 2 * ctx->sm_count && nblk / (KS * 2) >= GW) KS *= 2;
+    static const bool pdl = (getenv("SANIC_NO_PDL") == nullptr);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(tiles * KS); cfg.blockDim = dim3(GW * 32); cfg.dynamicSmemBytes = 0; cfg.stream = st;
+    cudaLaunchAttribute attr[2];
+    int na = 0;
+    if (pdl) { attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization; attr[na].val.programmaticStreamSerializationAllowed = 1; ++na; }
+    if (KS > 1) { attr[na].id = cudaLaunchAttributeClusterDimension; attr[na].val.clusterDim.x = KS; attr[na].val.clusterDim.y = 1; attr[na].val.clusterDim.z = 1; ++na; }
+    cfg.attrs = attr; cfg.numAttrs = na;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemv_mma_kernel<W4, NT, DUAL, NORM>, (const uint16_t*)p.x, p.batch, p.K, segs,
+                                       p.n_segments, p.out_dtype, p.epilogue, p.residual, fz, KS);
+    if (e != cudaSuccess) return sanic_fail(ctx, SANIC_ERR_CUDA, std::string("gemv: ") + cudaGetErrorString(e));
     return SANIC_OK;
+}
+template <bool W4, int NT, bool DUAL>
+int32_t launch_n(sanic_ctx* ctx, const sanic_gemv_params& p, const SegTable& segs, const Fused& fz, int tiles, cudaStream_t st) {
+    return fz.norm_x ? launch<W4, NT, DUAL, true>(ctx, p, segs, fz, tiles, st) : launch<W4, NT, DUAL, false>(ctx, p, segs, fz, tiles, st);
 }
 }  // namespace
 
 extern "C" int32_t sanic_gemv(sanic_ctx* ctx, const sanic_gemv_params* p, void* stream) {
     if (!ctx || !p) return SANIC_ERR_INVALID;
-    SANIC_REQUIRE(ctx, p->x && p->batch >= 1 && p->batch <= 16, "gemv: batch must be in [1, 16]");
+    SANIC_REQUIRE(ctx, (p->x || p->norm_x) && p->batch >= 1 && p->batch <= 16, "gemv: batch must be in [1, 16]");
     SANIC_REQUIRE(ctx, p->K >= 64 && p->K % 64 == 0, "gemv: K must be a multiple of 64");
     SANIC_REQUIRE(ctx, p->n_segments >= 1 && p->n_segments <= 3, "gemv: 1..3 weight segments");
     if (p->weight_dtype != SANIC_BF16 && p->weight_dtype != SANIC_I4)
         return sanic_fail(ctx, SANIC_ERR_DTYPE, "gemv: weights must be bf16 or int4");
     SANIC_REQUIRE(ctx, p->weight_dtype != SANIC_I4 || p->group == 64, "gemv: int4 group size must be 64");
     SANIC_REQUIRE(ctx, p->out_dtype == SANIC_F32 || p->out_dtype == SANIC_BF16, "gemv: output must be f32 or bf16");
-    SANIC_REQUIRE(ctx, ((uintptr_t)p->x % 16) == 0, "gemv: activations must be 16-byte aligned");
-    bool dual = p->epilogue == SANIC_EPI_SILU_MUL;
+    SANIC_REQUIRE(ctx, ((uintptr_t)p->x % 16) == 0 && ((uintptr_t)p->norm_x % 16) == 0 && ((uintptr_t)p->norm_gamma % 16) == 0,
+                  "gemv: activations must be 16-byte aligned");
+    SANIC_REQUIRE(ctx, !p->norm_x || p->norm_gamma, "gemv: an inlined norm needs its weight");
+    const bool dual = p->epilogue == SANIC_EPI_SILU_MUL;
+    const bool rope = p->epilogue == SANIC_EPI_ROPE_CACHE;
     SANIC_REQUIRE(ctx, !dual || (p->n_segments == 2 && p->rows[0] == p->rows[1]), "gemv: silu-mul needs two equal segments");
     SANIC_REQUIRE(ctx, p->epilogue != SANIC_EPI_RESIDUAL_ADD || (p->residual && p->n_segments == 1),
                   "gemv: residual-add needs one segment and a residual");
+    if (rope) {
+        SANIC_REQUIRE(ctx, p->n_segments == 3 && p->rope_table && p->rope_position && p->rope_q_out && p->rope_k_cache &&
+                      p->rope_v_cache, "gemv: the rope-cache epilogue needs q, k, v segments and its buffers");
+        SANIC_REQUIRE(ctx, (p->rope_head_dim == 64 || p->rope_head_dim == 128) && p->rope_ctx > 0 &&
+                      p->rows[0] == p->rope_q_heads * p->rope_head_dim && p->rows[1] == p->rope_kv_heads * p->rope_head_dim &&
+                      p->rows[2] == p->rows[1], "gemv: rope-cache segment rows must be heads * head_dim");
+    }
     SegTable segs{};
     int tiles = 0;
     for (int i = 0; i < p->n_segments; ++i) {
         SANIC_REQUIRE(ctx, p->w[i] && p->rows[i] > 0 && p->rows[i] % 16 == 0,
                       "gemv: segment rows must be a positive multiple of 16");
-        SANIC_REQUIRE(ctx, p->out[i] || (dual && i == 1), "gemv: null output");
+        SANIC_REQUIRE(ctx, p->out[i] || (dual && i == 1) || rope, "gemv: null output");
         SANIC_REQUIRE(ctx, ((uintptr_t)p->w[i] % 16) == 0, "gemv: weights must be 16-byte aligned");
         SANIC_REQUIRE(ctx, p->weight_dtype != SANIC_I4 || p->scales[i], "gemv: int4 weights need scales");
         segs.w[i] = p->w[i];
@@ -287,14 +448,17 @@ extern "C" int32_t sanic_gemv(sanic_ctx* ctx, const sanic_gemv_params* p, void* 
         if (!dual || i == 0) tiles += p->rows[i] / 16;
     }
     for (int i = p->n_segments; i < 4; ++i) segs.tile_begin[i] = tiles;
+    Fused fz{p->norm_x, (const uint16_t*)p->norm_gamma, p->norm_eps, p->rope_table, p->rope_position,
+             (uint16_t*)p->rope_q_out, (uint16_t*)p->rope_k_cache, (uint16_t*)p->rope_v_cache,
+             p->rope_q_heads, p->rope_kv_heads, p->rope_head_dim, p->rope_ctx};
     sanic_set_device(ctx);
     cudaStream_t st = (cudaStream_t)stream;
-    bool w4 = p->weight_dtype == SANIC_I4;
-    bool wide = p->batch > 8;
+    const bool w4 = p->weight_dtype == SANIC_I4;
+    const bool wide = p->batch > 8;
     if (dual) {
-        if (w4) return wide ? launch<true, 2, true>(ctx, *p, segs, tiles, st) : launch<true, 1, true>(ctx, *p, segs, tiles, st);
-        return wide ? launch<false, 2, true>(ctx, *p, segs, tiles, st) : launch<false, 1, true>(ctx, *p, segs, tiles, st);
+        if (w4) return wide ? launch_n<true, 2, true>(ctx, *p, segs, fz, tiles, st) : launch_n<true, 1, true>(ctx, *p, segs, fz, tiles, st);
+        return wide ? launch_n<false, 2, true>(ctx, *p, segs, fz, tiles, st) : launch_n<false, 1, true>(ctx, *p, segs, fz, tiles, st);
     }
-    if (w4) return wide ? launch<true, 2, false>(ctx, *p, segs, tiles, st) : launch<true, 1, false>(ctx, *p, segs, tiles, st);
-    return wide ? launch<false, 2, false>(ctx, *p, segs, tiles, st) : launch<false, 1, false>(ctx, *p, segs, tiles, st);
+    if (w4) return wide ? launch_n<true, 2, false>(ctx, *p, segs, fz, tiles, st) : launch_n<true, 1, false>(ctx, *p, segs, fz, tiles, st);
+    return wide ? launch_n<false, 2, false>(ctx, *p, segs, fz, tiles, st) : launch_n<false, 1, false>(ctx, *p, segs, fz, tiles, st);
 }

@@ -13,6 +13,8 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(const float* x, const uint
                                                       uint16_t* out) {
     __shared__ float wsum[8];
     __shared__ float s_den;
+    griddep_launch();
+    griddep_wait();
     const float* xr = x + (size_t)blockIdx.x * n;
     float ss = 0.0f;
     for (int i = threadIdx.x; i < n; i += 256) ss = fmaf(xr[i], xr[i], ss);
@@ -31,6 +33,8 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(const float* x, const uint
 }
 
 __global__ void embed_gather_kernel(const uint16_t* table, const int32_t* tokens, int hidden, int vocab, float* out) {
+    griddep_launch();
+    griddep_wait();
     int b = blockIdx.x;
     int tok = tokens[b];
     tok = tok < 0 ? 0 : (tok >= vocab ? vocab - 1 : tok);  // the host validates; never read out of bounds
@@ -48,9 +52,33 @@ __global__ void rope_table_kernel(const double* inv_freq, int n_freq, int n_pos,
     table[2 * (size_t)idx + 1] = (float)s;
 }
 
-// out[p=0,f] = x0*cos - x1*sin ; out[p=1,f] = x1*cos + x0*sin  (pair-major split of head_dim)
+// out[p=0,f] = x0*cos - x1*sin ; out[p=1,f] = x1*cos + x0*sin  (pair-major split of head_dim).
+// One thread rotates 8 consecutive frequencies: two 16-byte loads, two 16-byte stores.
 __global__ void rope_bf16_kernel(const uint16_t* x, uint16_t* out, long long rows, int seq, int D, const float* table,
                                  int pos0) {
+    const int F = D / 2, FV = F / 8;
+    long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    long long total = rows * seq * FV;
+    if (idx >= total) return;
+    int f = (int)(idx % FV) * 8;
+    long long rs = idx / FV;
+    int s = (int)(rs % seq);
+    const float4* cs = (const float4*)(table + 2 * ((size_t)(pos0 + s) * F + f));
+    size_t base = (size_t)rs * D;
+    uint4 a = *(const uint4*)(x + base + f), b = *(const uint4*)(x + base + F + f);
+    uint32_t av[4] = {a.x, a.y, a.z, a.w}, bv[4] = {b.x, b.y, b.z, b.w}, oa[4], ob[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        float4 t = cs[i];   // (cos, sin) of frequencies f+2i and f+2i+1
+        float x0 = bf16lo(av[i]), x1 = bf16lo(bv[i]), y0 = bf16hi(av[i]), y1 = bf16hi(bv[i]);
+        oa[i] = pack_bf16x2(x0 * t.x + (-x1) * t.y, y0 * t.z + (-y1) * t.w);
+        ob[i] = pack_bf16x2(x1 * t.x + x0 * t.y, y1 * t.z + y0 * t.w);
+    }
+    *(uint4*)(out + base + f) = make_uint4(oa[0], oa[1], oa[2], oa[3]);
+    *(uint4*)(out + base + F + f) = make_uint4(ob[0], ob[1], ob[2], ob[3]);
+}
+__global__ void rope_bf16_scalar_kernel(const uint16_t* x, uint16_t* out, long long rows, int seq, int D,
+                                        const float* table, int pos0) {
     const int F = D / 2;
     long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     long long total = rows * seq * F;
@@ -67,6 +95,8 @@ __global__ void rope_bf16_kernel(const uint16_t* x, uint16_t* out, long long row
 }
 
 __global__ void rope_cache_write_kernel(sanic_rope_cache_params p) {
+    griddep_launch();
+    griddep_wait();
     const int D = p.head_dim, F = D / 2;
     const int heads = p.q_heads + 2 * p.kv_heads;
     int idx = blockIdx.x * blockDim.x + threadIdx.x;
@@ -101,7 +131,10 @@ __global__ void rope_cache_write_kernel(sanic_rope_cache_params p) {
     }
 }
 
-__global__ void advance_kernel(int32_t* position) { *position += 1; }
+__global__ void advance_kernel(int32_t* position) {
+    griddep_wait();
+    *position += 1;
+}
 
 // Extremal-key payload fold: state (max value, first index). Merge: larger key wins, equal
 // keys keep the smaller index (reference src/derive.rs:1714-1735). Symmetric, so any tree works.
@@ -110,6 +143,8 @@ __device__ __forceinline__ void amax_merge(float& v, int& i, float v2, int i2) {
 }
 constexpr int AMAX_CHUNKS = 128;
 __global__ void __launch_bounds__(256) argmax_partial_kernel(const float* x, int n, float* scratch) {
+    griddep_launch();
+    griddep_wait();
     int row = blockIdx.y, chunk = blockIdx.x;
     int lo = (int)(((long long)chunk * n) / AMAX_CHUNKS), hi = (int)(((long long)(chunk + 1) * n) / AMAX_CHUNKS);
     const float* xr = x + (size_t)row * n;
@@ -130,6 +165,8 @@ __global__ void __launch_bounds__(256) argmax_partial_kernel(const float* x, int
     }
 }
 __global__ void __launch_bounds__(128) argmax_final_kernel(const float* scratch, uint32_t* out) {
+    griddep_launch();
+    griddep_wait();
     int row = blockIdx.x;
     float v = scratch[((size_t)row * AMAX_CHUNKS + threadIdx.x) * 2];
     int i = __float_as_int(scratch[((size_t)row * AMAX_CHUNKS + threadIdx.x) * 2 + 1]);
@@ -169,8 +206,7 @@ int32_t sanic_rmsnorm(sanic_ctx* ctx, const float* x, const void* gamma, int32_t
     if (!ctx) return SANIC_ERR_INVALID;
     SANIC_REQUIRE(ctx, x && gamma && out && rows > 0 && n > 0, "rmsnorm: bad arguments");
     sanic_set_device(ctx);
-    rmsnorm_kernel<<<rows, 256, 0, (cudaStream_t)stream>>>(x, (const uint16_t*)gamma, n, eps, (uint16_t*)out);
-    SANIC_LAUNCH_CHECK(ctx, "rmsnorm");
+    SANIC_CUDA_CHECK(ctx, launch_pdl(rmsnorm_kernel, dim3(rows), dim3(256), 0, (cudaStream_t)stream, x, (const uint16_t*)gamma, n, eps, (uint16_t*)out));
     return SANIC_OK;
 }
 
@@ -179,8 +215,7 @@ int32_t sanic_embed_gather(sanic_ctx* ctx, const void* table, const int32_t* tok
     if (!ctx) return SANIC_ERR_INVALID;
     SANIC_REQUIRE(ctx, table && tokens && out && batch > 0 && hidden > 0 && vocab > 0, "embed_gather: bad arguments");
     sanic_set_device(ctx);
-    embed_gather_kernel<<<batch, 256, 0, (cudaStream_t)stream>>>((const uint16_t*)table, tokens, hidden, vocab, out);
-    SANIC_LAUNCH_CHECK(ctx, "embed_gather");
+    SANIC_CUDA_CHECK(ctx, launch_pdl(embed_gather_kernel, dim3(batch), dim3(256), 0, (cudaStream_t)stream, (const uint16_t*)table, tokens, hidden, vocab, out));
     return SANIC_OK;
 }
 
@@ -209,9 +244,15 @@ int32_t sanic_rope_bf16(sanic_ctx* ctx, const void* x, void* out, int64_t rows, 
     SANIC_REQUIRE(ctx, x && out && table && rows > 0 && seq > 0 && head_dim > 0 && head_dim % 2 == 0 && pos0 >= 0,
                   "rope_bf16: bad arguments");
     sanic_set_device(ctx);
-    long long total = (long long)rows * seq * (head_dim / 2);
-    rope_bf16_kernel<<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
-        (const uint16_t*)x, (uint16_t*)out, rows, seq, head_dim, table, pos0);
+    if (head_dim % 16 == 0 && ((uintptr_t)x % 16) == 0 && ((uintptr_t)out % 16) == 0) {
+        long long total = (long long)rows * seq * (head_dim / 16);
+        rope_bf16_kernel<<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
+            (const uint16_t*)x, (uint16_t*)out, rows, seq, head_dim, table, pos0);
+    } else {
+        long long total = (long long)rows * seq * (head_dim / 2);
+        rope_bf16_scalar_kernel<<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
+            (const uint16_t*)x, (uint16_t*)out, rows, seq, head_dim, table, pos0);
+    }
     SANIC_LAUNCH_CHECK(ctx, "rope_bf16");
     return SANIC_OK;
 }
@@ -224,16 +265,14 @@ int32_t sanic_rope_cache_write(sanic_ctx* ctx, const sanic_rope_cache_params* p,
                   "rope_cache_write: bad shape");
     sanic_set_device(ctx);
     int total = p->batch * (p->q_heads + 2 * p->kv_heads) * (p->head_dim / 2);
-    rope_cache_write_kernel<<<(total + 255) / 256, 256, 0, (cudaStream_t)stream>>>(*p);
-    SANIC_LAUNCH_CHECK(ctx, "rope_cache_write");
+    SANIC_CUDA_CHECK(ctx, launch_pdl(rope_cache_write_kernel, dim3((total + 255) / 256), dim3(256), 0, (cudaStream_t)stream, *p));
     return SANIC_OK;
 }
 
 int32_t sanic_advance_position(sanic_ctx* ctx, int32_t* position, void* stream) {
     if (!ctx || !position) return SANIC_ERR_INVALID;
     sanic_set_device(ctx);
-    advance_kernel<<<1, 1, 0, (cudaStream_t)stream>>>(position);
-    SANIC_LAUNCH_CHECK(ctx, "advance_position");
+    SANIC_CUDA_CHECK(ctx, launch_pdl(advance_kernel, dim3(1), dim3(1), 0, (cudaStream_t)stream, position));
     return SANIC_OK;
 }
 
@@ -242,10 +281,8 @@ int32_t sanic_argmax(sanic_ctx* ctx, const float* x, int32_t rows, int32_t n, ui
     if (!ctx) return SANIC_ERR_INVALID;
     SANIC_REQUIRE(ctx, x && out_index && scratch && rows > 0 && n > 0, "argmax: bad arguments");
     sanic_set_device(ctx);
-    argmax_partial_kernel<<<dim3(AMAX_CHUNKS, rows), 256, 0, (cudaStream_t)stream>>>(x, n, scratch);
-    SANIC_LAUNCH_CHECK(ctx, "argmax partial");
-    argmax_final_kernel<<<rows, 128, 0, (cudaStream_t)stream>>>(scratch, out_index);
-    SANIC_LAUNCH_CHECK(ctx, "argmax final");
+    SANIC_CUDA_CHECK(ctx, launch_pdl(argmax_partial_kernel, dim3(AMAX_CHUNKS, rows), dim3(256), 0, (cudaStream_t)stream, x, n, scratch));
+    SANIC_CUDA_CHECK(ctx, launch_pdl(argmax_final_kernel, dim3(rows), dim3(128), 0, (cudaStream_t)stream, (const float*)scratch, out_index));
     return SANIC_OK;
 }
 

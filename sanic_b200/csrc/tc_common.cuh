@@ -34,7 +34,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
     atomicCAS(err, 0, code);
     return false;
 }
-// 2-D tiled TMA load into this CTA's shared memory, completion counted on an mbarrier (no multicast).
+// 2-D tiled TMA load into this CTA's shared memory, completion counted on an mbarrier; one CTA is the only destination.
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
                  ::"r"(dst), "l"((uint64_t)map), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");

@@ -98,8 +98,8 @@ class LlamaMachine:
     """The instantiated step program: owns state buffers, replays one captured graph per step."""
 
     def __init__(self, dev: CudaDevice, cfg: dict, weights: dict, ctx: int, batch: int, w4: bool = False,
-                 capture: bool = True):
-        self.dev, self.cfg, self.ctx, self.batch, self.w4 = dev, dict(cfg), ctx, batch, w4
+                 capture: bool = True, fused: bool = True):
+        self.dev, self.cfg, self.ctx, self.batch, self.w4, self.fused = dev, dict(cfg), ctx, batch, w4, fused
         H, F, V, L = cfg["hidden"], cfg["ffn"], cfg["vocab"], cfg["layers"]
         Hq, Hkv, D = cfg["q_heads"], cfg["kv_heads"], cfg["head_dim"]
         if H != Hq * D or Hq % Hkv or D not in (64, 128):
@@ -126,7 +126,9 @@ class LlamaMachine:
                                     [math.exp(i * (-math.log(cfg.get("theta", ROPE_THETA)) / (D // 2))) for i in range(D // 2)],
                                     ctx)
         tiles = (ctx + 63) // 64
-        self.n_splits = max(1, min(tiles, -(-2 * dev.specs()["sm_count"] // (B * Hkv))))
+        # chunks of the key axis per (batch, kv head): about 64 CTAs in all (measured best at ctx ~1k: 8 chunks at
+        # batch 1, 1 at batch 16), at least 2 tiles of 64 keys per chunk
+        self.n_splits = max(1, min(max(1, tiles // 2), -(-64 // (B * Hkv))))
         # the machine owns its scratch: two machines stepping on different streams must not share one
         self.partials = z((dev.lib.sanic_attn_decode_scratch_bytes(B, Hq, D, self.n_splits) // 4,), torch.float32)
         self.amax_scratch = z((B * 2 * 256,), torch.float32)
@@ -137,13 +139,23 @@ class LlamaMachine:
             self.capture()
 
     # ── stage list ──
-    def _gemv(self, x, names, layer, outs, epilogue=abi.EPI_STORE, residual=None, out_dtype=abi.F32):
+    def _gemv(self, x, names, layer, outs, epilogue=abi.EPI_STORE, residual=None, out_dtype=abi.F32, norm=None,
+              rope_layer=None):
         ws = [self.w[n][layer] if layer is not None else self.w[n] for n in names]
         sc = [self.w["s" + n[1:]][layer] for n in names] if (self.w4 and layer is not None) else None
         s = abi.StageDesc()
         s.stage_kind, s.op = abi.STAGE_FUSED, abi.OP_GEMV
         s.carrier = carrier_contraction(abi.I4 if sc is not None else abi.BF16)
-        s.u.gemv = self.dev.gemv_params(x, ws, outs, sc, epilogue, residual, out_dtype)
+        g = self.dev.gemv_params(x, ws, outs, sc, epilogue, residual, out_dtype)
+        if norm is not None:      # the RMSNorm cone of the residual stream is inlined into the fold's leaf
+            g.norm_x, g.norm_gamma, g.norm_eps = self.x.data_ptr(), norm.data_ptr(), float(self.cfg.get("eps", 1e-5))
+        if rope_layer is not None:
+            cfg = self.cfg
+            g.rope_table, g.rope_position = self.table.data_ptr(), self.position.data_ptr()
+            g.rope_q_out = self.qb.data_ptr()
+            g.rope_k_cache, g.rope_v_cache = self.kcache[rope_layer].data_ptr(), self.vcache[rope_layer].data_ptr()
+            g.rope_q_heads, g.rope_kv_heads, g.rope_head_dim, g.rope_ctx = cfg["q_heads"], cfg["kv_heads"], cfg["head_dim"], self.ctx
+        s.u.gemv = g
         return s
 
     def _rmsnorm(self, gamma):
@@ -155,8 +167,12 @@ class LlamaMachine:
         return s
 
     def _build(self):
+        """The launch list. fused=True: 5 launches per layer (norm and RoPE/cache write ride the projections);
+        fused=False: one stage per graph cone (9 per layer), kept for comparison and tests."""
         cfg, B = self.cfg, self.batch
         Hq, Hkv, D = cfg["q_heads"], cfg["kv_heads"], cfg["head_dim"]
+        fused = self.fused
+        inline_norm = fused and B <= 4    # at larger batch every CTA re-deriving the normalised rows costs more than a launch
         st = []
         s = abi.StageDesc()
         s.stage_kind, s.op = abi.STAGE_GATHER, abi.OP_EMBED
@@ -165,16 +181,22 @@ class LlamaMachine:
         s.u.embed.out = self.x.data_ptr()
         st.append(s)
         for l in range(cfg["layers"]):
-            st.append(self._rmsnorm(self.w["attn_norm"][l]))
-            st.append(self._gemv(self.xn, ["wq", "wk", "wv"], l, [self.q, self.k, self.v]))
-            s = abi.StageDesc()
-            s.stage_kind, s.op = abi.STAGE_ELEMENTWISE, abi.OP_ROPE_CACHE
-            r = s.u.rope_cache
-            r.q, r.k, r.v = self.q.data_ptr(), self.k.data_ptr(), self.v.data_ptr()
-            r.q_out, r.k_cache, r.v_cache = self.qb.data_ptr(), self.kcache[l].data_ptr(), self.vcache[l].data_ptr()
-            r.table, r.position = self.table.data_ptr(), self.position.data_ptr()
-            r.batch, r.q_heads, r.kv_heads, r.head_dim, r.ctx = B, Hq, Hkv, D, self.ctx
-            st.append(s)
+            if fused:
+                if not inline_norm:
+                    st.append(self._rmsnorm(self.w["attn_norm"][l]))
+                st.append(self._gemv(self.xn, ["wq", "wk", "wv"], l, [], abi.EPI_ROPE_CACHE,
+                                     norm=self.w["attn_norm"][l] if inline_norm else None, rope_layer=l))
+            else:
+                st.append(self._rmsnorm(self.w["attn_norm"][l]))
+                st.append(self._gemv(self.xn, ["wq", "wk", "wv"], l, [self.q, self.k, self.v]))
+                s = abi.StageDesc()
+                s.stage_kind, s.op = abi.STAGE_ELEMENTWISE, abi.OP_ROPE_CACHE
+                r = s.u.rope_cache
+                r.q, r.k, r.v = self.q.data_ptr(), self.k.data_ptr(), self.v.data_ptr()
+                r.q_out, r.k_cache, r.v_cache = self.qb.data_ptr(), self.kcache[l].data_ptr(), self.vcache[l].data_ptr()
+                r.table, r.position = self.table.data_ptr(), self.position.data_ptr()
+                r.batch, r.q_heads, r.kv_heads, r.head_dim, r.ctx = B, Hq, Hkv, D, self.ctx
+                st.append(s)
             s = abi.StageDesc()
             s.stage_kind, s.op = abi.STAGE_FUSED, abi.OP_DECODE_ATTN
             s.carrier = carrier_online_softmax(abi.BF16)
@@ -183,11 +205,18 @@ class LlamaMachine:
                                                    partials=self.partials, out_dtype=abi.BF16)
             st.append(s)
             st.append(self._gemv(self.att.view(B, Hq * D), ["wo"], l, [self.x], abi.EPI_RESIDUAL_ADD, self.x))
-            st.append(self._rmsnorm(self.w["mlp_norm"][l]))
-            st.append(self._gemv(self.xn, ["wgate", "wup"], l, [self.h], abi.EPI_SILU_MUL, None, abi.BF16))
+            if inline_norm:
+                st.append(self._gemv(self.xn, ["wgate", "wup"], l, [self.h], abi.EPI_SILU_MUL, None, abi.BF16,
+                                     norm=self.w["mlp_norm"][l]))
+            else:
+                st.append(self._rmsnorm(self.w["mlp_norm"][l]))
+                st.append(self._gemv(self.xn, ["wgate", "wup"], l, [self.h], abi.EPI_SILU_MUL, None, abi.BF16))
             st.append(self._gemv(self.h, ["wdown"], l, [self.x], abi.EPI_RESIDUAL_ADD, self.x))
-        st.append(self._rmsnorm(self.w["final_norm"]))
-        st.append(self._gemv(self.xn, ["embed"], None, [self.logits]))
+        if inline_norm:
+            st.append(self._gemv(self.xn, ["embed"], None, [self.logits], norm=self.w["final_norm"]))
+        else:
+            st.append(self._rmsnorm(self.w["final_norm"]))
+            st.append(self._gemv(self.xn, ["embed"], None, [self.logits]))
         s = abi.StageDesc()
         s.stage_kind, s.op = abi.STAGE_FUSED, abi.OP_ARGMAX
         s.carrier = carrier_extremum_index()

@@ -297,6 +297,57 @@ def test_gemv_segments_and_epilogues(dev):
     assert nerr(res.cpu().numpy(), exp) <= 1e-4
 
 
+@pytest.mark.parametrize("batch,w4", [(1, False), (16, False), (3, True)])
+def test_gemv_with_inlined_rmsnorm(dev, batch, w4):
+    K, rows = 2048, 128
+    x = orc.round_to(orc.DT_F32, normal(51, batch, K) * 3.0)
+    g, gv = bf16t(1.0 + 0.1 * normal(52, K), dev)
+    xn = orc.round_to(orc.DT_BF16, orc.rms_norm(x, gv))         # the declared stored(bf16) point
+    if w4:
+        q, packed, pt, st, sv = _w4(rows, K, 53, dev)
+        exp = orc.w4_gemv(packed, sv, xn, rows, group=64)
+        got = dev.gemv(f32t(x, dev), [pt], scales=[st], norm_gamma=g).cpu().numpy()
+    else:
+        w, wv = bf16t(normal(54, rows, K) * 0.02, dev)
+        exp = orc.gemv_bf16w(orc.to_bf16_bits(wv), xn)
+        got = dev.gemv(f32t(x, dev), [w], norm_gamma=g).cpu().numpy()
+    assert nerr(got, exp) <= 5e-4      # a bf16 rounding boundary of xn may fall either way in f32
+
+
+def test_gemv_rope_cache_epilogue_equals_separate_stages(dev):
+    import ctypes as C
+    from sanic_b200 import abi
+    B, Hq, Hkv, D, ctx, K, pos = 3, 4, 2, 64, 40, 256, 17
+    x, _ = bf16t(normal(61, B, K), dev)
+    wq, _ = bf16t(normal(62, Hq * D, K) * 0.05, dev)
+    wk, _ = bf16t(normal(63, Hkv * D, K) * 0.05, dev)
+    wv, _ = bf16t(normal(64, Hkv * D, K) * 0.05, dev)
+    table = dev.rope_table(list(orc.llama3_inv_freq(D // 2)), ctx)
+    position = torch.tensor([pos], dtype=torch.int32, device=dev.torch_device)
+    z = lambda *s: torch.zeros(*s, dtype=torch.bfloat16, device=dev.torch_device)
+    # separate stages
+    q, k, v = dev.gemv(x, [wq, wk, wv])
+    qa, ka, va = z(B, Hq, D), z(B, Hkv, ctx, D), z(B, Hkv, D, ctx)
+    r = abi.RopeCacheParams()
+    r.q, r.k, r.v, r.q_out, r.k_cache, r.v_cache = (t.data_ptr() for t in (q, k, v, qa, ka, va))
+    r.table, r.position = table.data_ptr(), position.data_ptr()
+    r.batch, r.q_heads, r.kv_heads, r.head_dim, r.ctx = B, Hq, Hkv, D, ctx
+    dev._check(dev.lib.sanic_rope_cache_write(dev.h, C.byref(r), dev.stream()), "rope_cache_write")
+    # fused epilogue
+    qb, kb, vb = z(B, Hq, D), z(B, Hkv, ctx, D), z(B, Hkv, D, ctx)
+    p = dev.gemv_params(x, [wq, wk, wv], [], None, abi.EPI_ROPE_CACHE, None, abi.F32)
+    p.rope_table, p.rope_position = table.data_ptr(), position.data_ptr()
+    p.rope_q_out, p.rope_k_cache, p.rope_v_cache = qb.data_ptr(), kb.data_ptr(), vb.data_ptr()
+    p.rope_q_heads, p.rope_kv_heads, p.rope_head_dim, p.rope_ctx = Hq, Hkv, D, ctx
+    dev._check(dev.lib.sanic_gemv(dev.h, C.byref(p), dev.stream()), "gemv rope")
+    torch.cuda.synchronize()
+    assert torch.equal(qa, qb) and torch.equal(ka, kb) and torch.equal(va, vb)
+    assert ka[:, :, pos].abs().sum() > 0 and ka[:, :, :pos].abs().sum() == 0    # only the written row is touched
+    # and against the oracle's rope of the projected rows
+    qo = orc.rope(q.cpu().numpy().astype(np.float64).reshape(B, Hq, D), float(pos), orc.llama3_inv_freq(D // 2))
+    assert nerr(qb.float().cpu().numpy(), orc.round_to(orc.DT_BF16, qo)) <= 2.0 ** -7
+
+
 def test_gemv_rejects_bad_arguments(dev):
     from sanic_b200 import RunError
     x = torch.zeros(17, 256, dtype=torch.bfloat16, device=dev.torch_device)

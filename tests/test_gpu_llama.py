@@ -22,10 +22,10 @@ def dev():
     return CudaDevice(0)
 
 
-def run_pair(dev, cfg, ctx, batch, w4, steps, prefill, seed=5):
+def run_pair(dev, cfg, ctx, batch, w4, steps, prefill, seed=5, fused=True):
     from sanic_b200 import llama
     w = llama.random_weights(cfg, seed, dev.torch_device, w4=w4)
-    m = llama.LlamaMachine(dev, cfg, w, ctx=ctx, batch=batch, w4=w4)
+    m = llama.LlamaMachine(dev, cfg, w, ctx=ctx, batch=batch, w4=w4, fused=fused)
     ocfg = dict(cfg, ctx=ctx, batch=batch, w4=int(w4), group=64, round_acts=1, llama3_rope=1)
     o = orc.Llama(ocfg, llama.weights_to_oracle(w, w4))
     rng = np.random.default_rng(seed)
@@ -42,7 +42,7 @@ def run_pair(dev, cfg, ctx, batch, w4, steps, prefill, seed=5):
     cur = rng.integers(0, cfg["vocab"], size=batch).astype(np.int32)
     m.set_state(cur, prefill)
     ocur = cur.copy()
-    mism = []
+    ties = 0
     for s in range(steps):
         m.step()
         got = m.read_tokens()
@@ -51,11 +51,19 @@ def run_pair(dev, cfg, ctx, batch, w4, steps, prefill, seed=5):
         ol = o.logits()
         err = np.max(np.abs(lg - ol) / (1.0 + np.abs(ol)))
         assert err <= 2e-2, f"step {s}: logits differ by {err}"
-        if not np.array_equal(got, ocur):
-            top = np.sort(ol, axis=1)
-            mism.append((s, got.tolist(), ocur.tolist(), (top[:, -1] - top[:, -2]).tolist()))
-            break
-    assert not mism, f"greedy tokens diverged (step, gpu, oracle, oracle top-2 gaps): {mism}"
+        bad = np.nonzero(got != ocur)[0]
+        if bad.size:
+            # A different token is an error unless the oracle's own top-2 gap on that row is inside
+            # the bf16 bound: then both indices are maxima to within the storage precision (a tie).
+            top = np.sort(ol[bad], axis=1)
+            gaps = top[:, -1] - top[:, -2]
+            tol = 2e-2 * (1.0 + np.abs(top[:, -1]))
+            assert np.all(gaps <= tol), f"step {s}: tokens {got[bad]} vs oracle {ocur[bad]}, oracle top-2 gaps {gaps}"
+            assert np.all(np.abs(ol[bad, got[bad]] - top[:, -1]) <= tol)
+            ties += int(bad.size)
+            m.tokens.copy_(torch.as_tensor(ocur).to(m.tokens.device))   # continue both sides from the same token
+            torch.cuda.synchronize()
+    assert ties <= max(1, steps * batch // 16), f"{ties} near-tie steps out of {steps * batch}"
     return m
 
 
@@ -63,6 +71,13 @@ def run_pair(dev, cfg, ctx, batch, w4, steps, prefill, seed=5):
 @pytest.mark.parametrize("w4", [False, True])
 def test_small_model_32_greedy_steps(dev, batch, w4):
     run_pair(dev, SMALL, ctx=128, batch=batch, w4=w4, steps=32, prefill=40)
+
+
+@pytest.mark.parametrize("w4", [False, True])
+def test_small_model_one_stage_per_cone(dev, w4):
+    # the unfused launch list (norm, projections, RoPE + cache write as separate stages: 8 per layer)
+    m = run_pair(dev, SMALL, ctx=128, batch=2, w4=w4, steps=32, prefill=40, fused=False)
+    assert m.n_stages == 1 + 8 * SMALL["layers"] + 4
 
 
 def test_batch16_and_replay_equals_eager(dev):
@@ -79,6 +94,7 @@ def test_batch16_and_replay_equals_eager(dev):
     assert np.array_equal(a.read_tokens(), b.read_tokens())
     assert int(a.position.item()) == 12
     assert a.kernel_count == a.n_stages + 1
+    assert a.n_stages == 1 + 7 * SMALL["layers"] + 4      # batch 16: norms stay separate stages, RoPE rides the projection
 
 
 def test_machine_refuses_bad_state(dev):
