@@ -5,9 +5,11 @@
 //
 // One CTA folds 256 query rows of one (batch, query head) as two 128-row tiles that ping-pong on
 // the tensor core: while one tile's softmax warpgroup turns S into P, the other tile's MMAs run.
-//   warp 0       TMA producer: Q once, then K_j / V_j tiles of 128 keys through a 3-stage ring
+//   warp 0       TMA producer: Q once, then K_j / V_j tiles of 128 keys through a 5-stage ring
 //   warp 1       MMA issuer: per key tile  PV(0,j) QK(0,j+1) PV(1,j) QK(1,j+1)
-//   warp 2       TMEM allocator (S0 S1 O0 O1 = 128+128+64+64 columns of 512)
+//   warp 2       TMEM allocator (S0 S1 | P0 P1 | O0 O1 = 2x128 + 2x64 + 2x64 columns, all 512)
+// P never touches shared memory: the softmax threads write bf16 pairs back to tensor memory and
+// the PV MMA takes its A operand from there.
 //   warps 4-7    softmax + correction + epilogue of tile 0
 //   warps 8-11   the same for tile 1
 // Masks: causal (key > row), sliding window (key < row - window + 1) and the ragged key tail are
@@ -24,10 +26,11 @@ namespace {
 using namespace sanic;
 using namespace sanic::tc;
 
-constexpr int D = 64, BM = 128, BN = 128, KV_STAGES = 3;
+constexpr int D = 64, BM = 128, BN = 128, KV_STAGES = 5;
+// tensor-memory columns: S0 S1 (f32 scores), P0 P1 (bf16 probabilities, two per column), O0 O1 (f32 outputs)
+constexpr int TM_S = 0, TM_P = 256, TM_O = 384;
 constexpr int Q_BYTES = BM * D * 2;        // 16 KB per query tile
 constexpr int KV_BYTES = BN * D * 2;       // 16 KB per K or V tile
-constexpr int P_BYTES = BM * BN * 2;       // 32 KB per P tile (two 64-key halves)
 constexpr int NTHREADS = 384;
 #ifndef SANIC_FLASH_POLY_EVERY
 #define SANIC_FLASH_POLY_EVERY 0
@@ -84,8 +87,8 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     const uint32_t raw = smem_u32(smem_dyn);
     const uint32_t base = (raw + 1023u) & ~1023u;
     unsigned char* aligned = smem_dyn + (base - raw);
-    const uint32_t q_addr = base, kv_addr = base + 2 * Q_BYTES, p_addr = kv_addr + KV_STAGES * 2 * KV_BYTES;
-    FShared* sh = (FShared*)(aligned + 2 * Q_BYTES + KV_STAGES * 2 * KV_BYTES + 2 * P_BYTES);
+    const uint32_t q_addr = base, kv_addr = base + 2 * Q_BYTES;
+    FShared* sh = (FShared*)(aligned + 2 * Q_BYTES + KV_STAGES * 2 * KV_BYTES);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int mb = gridDim.x - 1 - blockIdx.x;      // heaviest (latest) query blocks first
@@ -142,7 +145,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                 const uint64_t ad = make_desc(q_addr + t * Q_BYTES, 16, 1024);
                 const uint64_t bd = make_desc(kv_addr + stage * 2 * KV_BYTES, 16, 1024);
 #pragma unroll
-                for (int k = 0; k < D / 16; ++k) umma_f16(tmem + t * BN, ad + 2 * k, bd + 2 * k, idesc_qk, k > 0 ? 1u : 0u);
+                for (int k = 0; k < D / 16; ++k) umma_f16(tmem + TM_S + t * BN, ad + 2 * k, bd + 2 * k, idesc_qk, k > 0 ? 1u : 0u);
                 umma_commit(&sh->s_full[t]);
             };
             int stage = 0; uint32_t phase = 0;
@@ -161,13 +164,11 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                         ok = mbar_wait(&sh->p_full[t], it[t] & 1, abortp, err, 15);
                         if (!ok) break;
                         fence_after();
-                        const uint32_t pa = p_addr + t * P_BYTES;
                         const uint64_t vd = make_desc(kv_addr + stage * 2 * KV_BYTES + KV_BYTES, 1024, 1024);
 #pragma unroll
-                        for (int k = 0; k < BN / 16; ++k) {
-                            const uint64_t ad = make_desc(pa + (k >> 2) * (BM * 128), 16, 1024) + 2 * (k & 3);
-                            umma_f16(tmem + 256 + t * D, ad, vd + 128 * k, idesc_pv, (it[t] > 0 || k > 0) ? 1u : 0u);
-                        }
+                        for (int k = 0; k < BN / 16; ++k)      // A = P_t from tensor memory: 16 keys = 8 columns per step
+                            umma_f16_ts(tmem + TM_O + t * D, tmem + TM_P + t * (BN / 2) + 8 * k, vd + 128 * k, idesc_pv,
+                                        (it[t] > 0 || k > 0) ? 1u : 0u);
                         umma_commit(&sh->pv_done[t]);
                         it[t]++;
                     }
@@ -188,9 +189,9 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         const int r0 = m0 + t * BM;
         const int grow = r0 + row;                    // global query position
         const uint32_t lane_base = (uint32_t)(q4 * 32) << 16;
-        const uint32_t s_tmem = tmem + lane_base + t * BN;
-        const uint32_t o_tmem = tmem + lane_base + 256 + t * D;
-        unsigned char* prow = aligned + (p_addr - base) + t * P_BYTES + row * 128;
+        const uint32_t s_tmem = tmem + lane_base + TM_S + t * BN;
+        const uint32_t p_tmem = tmem + lane_base + TM_P + t * (BN / 2);
+        const uint32_t o_tmem = tmem + lane_base + TM_O + t * D;
         const float sl2 = p.scale * LOG2E;
         float m = -INFINITY, l = 0.0f;
         int it = 0;
@@ -247,27 +248,27 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                     tmem_st_wait();
                 }
             }
-            // P = exp2(S*sl2 - m_ref) -> bf16 -> shared (K-major, 128B swizzle), row sum
+            // P = exp2(S*sl2 - m_ref) -> bf16 pairs -> tensor memory (the A operand of the PV MMA), row sum
             float sums[8] = {0, 0, 0, 0, 0, 0, 0, 0};
 #pragma unroll
-            for (int cc = 0; cc < BN / 8; ++cc) {
-                uint32_t pk[4];
+            for (int hb = 0; hb < 2; ++hb) {
+                uint32_t pk[32];
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    float p0 = ex2(fmaf(__uint_as_float(r[cc * 8 + 2 * i]), sl2, -msub));
-                    float p1 = (POLY_EVERY > 0 && ((cc * 4 + i) % (POLY_EVERY > 0 ? POLY_EVERY : 1)) == 0)
-                                   ? ex2_poly(fmaf(__uint_as_float(r[cc * 8 + 2 * i + 1]), sl2, -msub))
-                                   : ex2(fmaf(__uint_as_float(r[cc * 8 + 2 * i + 1]), sl2, -msub));
-                    sums[2 * i] += p0; sums[2 * i + 1] += p1;
+                for (int i = 0; i < 32; ++i) {
+                    const int c = hb * 64 + 2 * i;
+                    float p0 = ex2(fmaf(__uint_as_float(r[c]), sl2, -msub));
+                    float p1 = (POLY_EVERY > 0 && (i % (POLY_EVERY > 0 ? POLY_EVERY : 1)) == 0)
+                                   ? ex2_poly(fmaf(__uint_as_float(r[c + 1]), sl2, -msub))
+                                   : ex2(fmaf(__uint_as_float(r[c + 1]), sl2, -msub));
+                    sums[(2 * i) & 7] += p0; sums[(2 * i + 1) & 7] += p1;
                     pk[i] = pack_bf16x2(p0, p1);
                 }
-                unsigned char* dst = prow + (cc >> 3) * (BM * 128) + (((cc & 7) ^ (row & 7)) << 4);
-                *(uint4*)dst = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                tmem_st32(p_tmem + hb * 32, pk);
             }
+            tmem_st_wait();
             const float sum = ((sums[0] + sums[1]) + (sums[2] + sums[3])) + ((sums[4] + sums[5]) + (sums[6] + sums[7]));
             l = l * alpha + sum;
             fence_before();
-            fence_async_smem();
             __syncwarp();
             if (lane == 0) mbar_arrive(&sh->p_full[t]);
         }
@@ -325,7 +326,7 @@ extern "C" int32_t sanic_attn_fwd_bf16(sanic_ctx* ctx, const sanic_attn_params* 
     rc = sanic::tc::encode_bf16_2d(ctx, &mv, p->v, D, (uint64_t)p->batch * p->kv_heads * p->kv_len, D, BN);
     if (rc != SANIC_OK) return rc;
     FParams fp{p->out, p->batch, p->q_heads, p->kv_heads, p->q_len, p->kv_len, p->causal, p->window, p->scale};
-    const int smem = 2 * Q_BYTES + KV_STAGES * 2 * KV_BYTES + 2 * P_BYTES + (int)sizeof(FShared) + 1024;
+    const int smem = 2 * Q_BYTES + KV_STAGES * 2 * KV_BYTES + (int)sizeof(FShared) + 1024;
     SANIC_CUDA_CHECK(ctx, cudaFuncSetAttribute(attn_fwd_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     dim3 grid((p->q_len + 2 * BM - 1) / (2 * BM), p->q_heads, p->batch);
     attn_fwd_tc_kernel<<<grid, NTHREADS, smem, (cudaStream_t)stream>>>(mq, mk, mv, fp, ctx->status_dev);
