@@ -55,7 +55,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                                          "-lms", "100", "-i", str(self.index)], stdout=subprocess.PIPE, text=True)
+                                          "-lms", "50", "-i", str(self.index)], stdout=subprocess.PIPE, text=True)
             threading.Thread(target=self._read, daemon=True).start()
         except Exception:
             self.proc = None
@@ -363,15 +363,15 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
-# dram bytes / algorithmic bytes of attn_decode_kernel from the ncu capture summarised in
-# profiles/attn_decode_splitkv.md (None until a capture exists)
-TRAFFIC_RATIO_DECODE = None
+# dram bytes (read + write) / algorithmic bytes of attn_decode_kernel, from the ncu capture summarised in
+# profiles/attn_decode_splitkv.md (a 65,536-key case; traffic grows in proportion to the keys streamed)
+TRAFFIC_RATIO_DECODE = 1.0067
 
 
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--kv-len", type=int, default=L_FULL)

@@ -8,10 +8,10 @@
 //   warp 0       TMA producer: Q once, then K_j / V_j tiles of 128 keys through a 5-stage ring
 //   warp 1       MMA issuer: per key tile  PV(0,j) QK(0,j+1) PV(1,j) QK(1,j+1)
 //   warp 2       TMEM allocator (S0 S1 | P0 P1 | O0 O1 = 2x128 + 2x64 + 2x64 columns, all 512)
-// P never touches shared memory: the softmax threads write bf16 pairs back to tensor memory and
-// the PV MMA takes its A operand from there.
 //   warps 4-7    softmax + correction + epilogue of tile 0
 //   warps 8-11   the same for tile 1
+// P never touches shared memory: the softmax threads write bf16 pairs back to tensor memory and
+// the PV MMA takes its A operand from there.
 // Masks: causal (key > row), sliding window (key < row - window + 1) and the ragged key tail are
 // applied only in tiles that straddle an edge; tiles wholly outside the visible range are never
 // loaded (a prefix-masked fold may stop at the mask edge: it contributes exact zeros).
