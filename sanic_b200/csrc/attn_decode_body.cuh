@@ -1,0 +1,286 @@
+// Body of the split-KV decode fold, shared by the stand-alone kernel (attn_decode.cu) and the persistent
+// decode-step kernel (decode_step.cu). See attn_decode.cu for the design notes.
+#pragma once
+#include "common.cuh"
+
+namespace sanic {
+namespace decode {
+
+constexpr int KT = 64;        // keys per tile
+constexpr int NWARP = 4;
+
+template <int D> struct Cfg {
+    static constexpr int STAGES = (D == 128) ? 3 : 4;
+    static constexpr int TILE_BYTES = KT * D * 2;            // one K (or V) tile
+    static constexpr int STAGE_BYTES = 2 * TILE_BYTES;
+    static constexpr int MERGE_FLOATS = NWARP * 16 * (D + 2);
+    static constexpr int SMEM = STAGES * STAGE_BYTES > MERGE_FLOATS * 4 ? STAGES * STAGE_BYTES : MERGE_FLOATS * 4;
+};
+
+// Issue the cp.async copies of one K tile and one V tile into a stage.
+template <int D, bool VT>
+__device__ __forceinline__ void load_tile(const sanic_decode_params& p, const uint16_t* Kb, const uint16_t* Vb,
+                                          uint32_t stage_addr, int key0, int hi, int tid) {
+    constexpr int CPR = D / 8;  // 16-byte chunks per key row
+    // K tile: [D/64 halves][64 keys][128 B], chunk index xor (key & 7)
+#pragma unroll
+    for (int i = 0; i < (KT * CPR) / 128; ++i) {
+        int id = i * 128 + tid;
+        int key = id / CPR, c = id % CPR;
+        int half = c >> 3, cc = c & 7;
+        int gk = key0 + key;
+        bool ok = gk < hi;
+        const uint16_t* src = Kb + (size_t)(ok ? gk : 0) * p.k_seq_stride + c * 8;
+        uint32_t dst = stage_addr + half * (KT * 128) + key * 128 + ((cc ^ (key & 7)) << 4);
+        cp_async16(dst, src, ok ? 16 : 0);
+    }
+    uint32_t vaddr = stage_addr + Cfg<D>::TILE_BYTES;
+    if (!VT) {
+#pragma unroll
+        for (int i = 0; i < (KT * CPR) / 128; ++i) {
+            int id = i * 128 + tid;
+            int key = id / CPR, c = id % CPR;
+            int half = c >> 3, cc = c & 7;
+            int gk = key0 + key;
+            bool ok = gk < hi;
+            const uint16_t* src = Vb + (size_t)(ok ? gk : 0) * p.v_row_stride + c * 8;
+            uint32_t dst = vaddr + half * (KT * 128) + key * 128 + ((cc ^ (key & 7)) << 4);
+            cp_async16(dst, src, ok ? 16 : 0);
+        }
+    } else {
+        // V^T tile: [D rows][64 keys = 128 B], chunk index xor (d & 7)
+#pragma unroll
+        for (int i = 0; i < (D * 8) / 128; ++i) {
+            int id = i * 128 + tid;
+            int d = id >> 3, c = id & 7;
+            int gk = key0 + c * 8;
+            bool ok = gk < hi;
+            const uint16_t* src = Vb + (size_t)d * p.v_row_stride + (ok ? gk : 0);
+            uint32_t dst = vaddr + d * 128 + ((c ^ (d & 7)) << 4);
+            cp_async16(dst, src, ok ? 16 : 0);
+        }
+    }
+}
+
+// One (chunk, kv head, batch) item of the fold, executed by 128 threads (tid in [0, 128)). `smem_raw` is the
+// caller's dynamic shared memory (Cfg<D>::SMEM bytes, 128-byte aligned); `pdl` as in gemv_tile.
+template <int D, bool VT>
+__device__ __forceinline__ void attn_decode_tile(const sanic_decode_params& p, int* counters, int split, int hk, int b,
+                                                 unsigned char* smem_raw, int tid, bool pdl) {
+    const int warp = tid >> 5, lane = tid & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int group = p.q_heads / p.kv_heads;
+    constexpr int KS = D / 16;   // k-steps of the QK^T contraction
+    constexpr int NT = D / 8;    // n-tiles of the output
+
+    if (pdl) { griddep_launch(); griddep_wait(); }   // q, the caches and the position come from the previous kernels of the step
+    const int kv_len = p.kv_len_dev ? (*p.kv_len_dev + 1) : p.kv_len;
+    const int hi = kv_len;
+    const int lo = (p.window > 0) ? max(0, kv_len - p.window) : 0;
+    const int T0 = lo / KT, T1 = (hi + KT - 1) / KT;
+    const int nT = T1 - T0;
+    const int t_begin = T0 + (int)(((long long)split * nT) / p.n_splits);
+    const int t_end = T0 + (int)(((long long)(split + 1) * nT) / p.n_splits);
+    const int n_tiles = t_end - t_begin;
+
+    const uint16_t* Kb = (const uint16_t*)p.k + (size_t)b * p.k_batch_stride + (size_t)hk * p.k_head_stride;
+    const uint16_t* Vb = (const uint16_t*)p.v + (size_t)b * p.v_batch_stride + (size_t)hk * p.v_head_stride;
+    const uint32_t smem_base = smem_u32(smem_raw);
+
+    // Q fragments: row r = query head hk*group + r, zero beyond the group.
+    uint32_t qa[KS][2];  // [ks][0] = (a0,a1) cols 2t,2t+1 ; [ks][1] = (a4,a5) cols 8+2t,+1 ; rows g (rows g+8 via qb)
+    uint32_t qb[KS][2];  // rows g+8
+    {
+        const uint16_t* Q = (const uint16_t*)p.q + ((size_t)b * p.q_heads + (size_t)hk * group) * D;
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks) {
+            qa[ks][0] = (g < group) ? *(const uint32_t*)(Q + (size_t)g * D + ks * 16 + 2 * t) : 0u;
+            qa[ks][1] = (g < group) ? *(const uint32_t*)(Q + (size_t)g * D + ks * 16 + 8 + 2 * t) : 0u;
+            qb[ks][0] = (g + 8 < group) ? *(const uint32_t*)(Q + (size_t)(g + 8) * D + ks * 16 + 2 * t) : 0u;
+            qb[ks][1] = (g + 8 < group) ? *(const uint32_t*)(Q + (size_t)(g + 8) * D + ks * 16 + 8 + 2 * t) : 0u;
+        }
+    }
+
+    float o[NT][4];
+#pragma unroll
+    for (int i = 0; i < NT; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f; }
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.0f, l1 = 0.0f;  // rows g and g+8 (log2 units)
+    const float sl2 = p.scale * LOG2E;
+
+    constexpr int STAGES = Cfg<D>::STAGES;
+#pragma unroll
+    for (int s = 0; s < STAGES - 1; ++s) {
+        if (s < n_tiles) load_tile<D, VT>(p, Kb, Vb, smem_base + s * Cfg<D>::STAGE_BYTES, (t_begin + s) * KT, hi, tid);
+        cp_async_commit();
+    }
+
+    for (int it = 0; it < n_tiles; ++it) {
+        cp_async_wait<STAGES - 2>();
+        __syncthreads();
+        {   // prefetch tile it + STAGES - 1 into the stage consumed at iteration it - 1
+            int nx = it + STAGES - 1;
+            if (nx < n_tiles)
+                load_tile<D, VT>(p, Kb, Vb, smem_base + (nx % STAGES) * Cfg<D>::STAGE_BYTES, (t_begin + nx) * KT, hi, tid);
+            cp_async_commit();
+        }
+        const uint32_t ks_addr = smem_base + (it % STAGES) * Cfg<D>::STAGE_BYTES;
+        const uint32_t vs_addr = ks_addr + Cfg<D>::TILE_BYTES;
+        const int key0 = (t_begin + it) * KT + warp * 16;
+
+        // S = Q K^T for this warp's 16 keys
+        float s0[4] = {0, 0, 0, 0}, s1[4] = {0, 0, 0, 0};
+        {
+            const int mi = lane >> 3, r = lane & 7;
+            const int krow = warp * 16 + (mi >> 1) * 8 + r;
+#pragma unroll
+            for (int ks = 0; ks < KS; ++ks) {
+                int c = 2 * ks + (mi & 1);
+                int half = c >> 3, cc = c & 7;
+                uint32_t addr = ks_addr + half * (KT * 128) + krow * 128 + ((cc ^ (krow & 7)) << 4);
+                uint32_t r0, r1, r2, r3;
+                ldmatrix_x4(addr, r0, r1, r2, r3);
+                mma_bf16_16816(s0, qa[ks][0], qb[ks][0], qa[ks][1], qb[ks][1], r0, r1);
+                mma_bf16_16816(s1, qa[ks][0], qb[ks][0], qa[ks][1], qb[ks][1], r2, r3);
+            }
+        }
+        // mask, scale to log2 units, online-softmax update
+        {
+            int kA = key0 + 2 * t, kB = key0 + 8 + 2 * t;
+            bool vA0 = (kA >= lo) && (kA < hi), vA1 = (kA + 1 >= lo) && (kA + 1 < hi);
+            bool vB0 = (kB >= lo) && (kB < hi), vB1 = (kB + 1 >= lo) && (kB + 1 < hi);
+            s0[0] = vA0 ? s0[0] * sl2 : -INFINITY; s0[1] = vA1 ? s0[1] * sl2 : -INFINITY;
+            s0[2] = vA0 ? s0[2] * sl2 : -INFINITY; s0[3] = vA1 ? s0[3] * sl2 : -INFINITY;
+            s1[0] = vB0 ? s1[0] * sl2 : -INFINITY; s1[1] = vB1 ? s1[1] * sl2 : -INFINITY;
+            s1[2] = vB0 ? s1[2] * sl2 : -INFINITY; s1[3] = vB1 ? s1[3] * sl2 : -INFINITY;
+        }
+        float mx0 = fmaxf(fmaxf(s0[0], s0[1]), fmaxf(s1[0], s1[1]));
+        float mx1 = fmaxf(fmaxf(s0[2], s0[3]), fmaxf(s1[2], s1[3]));
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1)); mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1)); mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+        float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
+        // a side whose max is -inf carries weight 0 (the guard of the derived combine)
+        float a0 = (m0 > -INFINITY) ? exp2f(m0 - mn0) : 0.0f;
+        float a1 = (m1 > -INFINITY) ? exp2f(m1 - mn1) : 0.0f;
+        float sub0 = (mn0 > -INFINITY) ? mn0 : 0.0f, sub1 = (mn1 > -INFINITY) ? mn1 : 0.0f;
+        float p00 = exp2f(s0[0] - sub0), p01 = exp2f(s0[1] - sub0), p10 = exp2f(s1[0] - sub0), p11 = exp2f(s1[1] - sub0);
+        float p02 = exp2f(s0[2] - sub1), p03 = exp2f(s0[3] - sub1), p12 = exp2f(s1[2] - sub1), p13 = exp2f(s1[3] - sub1);
+        l0 = l0 * a0 + (p00 + p01 + p10 + p11);
+        l1 = l1 * a1 + (p02 + p03 + p12 + p13);
+        m0 = mn0; m1 = mn1;
+#pragma unroll
+        for (int i = 0; i < NT; ++i) { o[i][0] *= a0; o[i][1] *= a0; o[i][2] *= a1; o[i][3] *= a1; }
+        uint32_t pa0 = pack_bf16x2(p00, p01), pa1 = pack_bf16x2(p02, p03);
+        uint32_t pa2 = pack_bf16x2(p10, p11), pa3 = pack_bf16x2(p12, p13);
+
+        // O += P V over this warp's 16 keys
+        {
+            const int mi = lane >> 3, r = lane & 7;
+#pragma unroll
+            for (int dp = 0; dp < D / 16; ++dp) {
+                uint32_t addr;
+                if (!VT) {
+                    int krow = warp * 16 + (mi & 1) * 8 + r;
+                    int c = 2 * dp + (mi >> 1);
+                    int half = c >> 3, cc = c & 7;
+                    addr = vs_addr + half * (KT * 128) + krow * 128 + ((cc ^ (krow & 7)) << 4);
+                    uint32_t r0, r1, r2, r3;
+                    ldmatrix_x4_trans(addr, r0, r1, r2, r3);
+                    mma_bf16_16816(o[2 * dp], pa0, pa1, pa2, pa3, r0, r1);
+                    mma_bf16_16816(o[2 * dp + 1], pa0, pa1, pa2, pa3, r2, r3);
+                } else {
+                    int drow = 16 * dp + (mi >> 1) * 8 + r;
+                    int c = 2 * warp + (mi & 1);
+                    addr = vs_addr + drow * 128 + ((c ^ (drow & 7)) << 4);
+                    uint32_t r0, r1, r2, r3;
+                    ldmatrix_x4(addr, r0, r1, r2, r3);
+                    mma_bf16_16816(o[2 * dp], pa0, pa1, pa2, pa3, r0, r1);
+                    mma_bf16_16816(o[2 * dp + 1], pa0, pa1, pa2, pa3, r2, r3);
+                }
+            }
+        }
+    }
+    cp_async_wait<0>();
+    __syncthreads();  // every warp is done with the tile ring: reuse it for the warp merge
+
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 1); l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+
+    float* ms = (float*)smem_raw;  // [warp][16 rows][D + 2]
+    {
+        float* w0 = ms + (warp * 16 + g) * (D + 2);
+        float* w1 = ms + (warp * 16 + g + 8) * (D + 2);
+        if (t == 0) { w0[0] = m0; w0[1] = l0; w1[0] = m1; w1[1] = l1; }
+#pragma unroll
+        for (int i = 0; i < NT; ++i) {
+            w0[2 + 8 * i + 2 * t] = o[i][0]; w0[2 + 8 * i + 2 * t + 1] = o[i][1];
+            w1[2 + 8 * i + 2 * t] = o[i][2]; w1[2 + 8 * i + 2 * t + 1] = o[i][3];
+        }
+    }
+    __syncthreads();
+    // merge the 4 warp carriers (left to right) and write this chunk's partial
+    const int W = D + 2;
+    for (int idx = tid; idx < group * D; idx += 128) {
+        int r = idx / D, d = idx % D;
+        float m = ms[(0 * 16 + r) * W], l = ms[(0 * 16 + r) * W + 1], ov = ms[(0 * 16 + r) * W + 2 + d];
+#pragma unroll
+        for (int w = 1; w < NWARP; ++w) {
+            float mb = ms[(w * 16 + r) * W], lb = ms[(w * 16 + r) * W + 1], ob = ms[(w * 16 + r) * W + 2 + d];
+            float M = fmaxf(m, mb);
+            float ra = (m > -INFINITY) ? exp2f(m - M) : 0.0f, rb = (mb > -INFINITY) ? exp2f(mb - M) : 0.0f;
+            l = l * ra + lb * rb; ov = ov * ra + ob * rb; m = M;
+        }
+        float* part = p.partials + (((size_t)b * p.q_heads + (size_t)hk * group + r) * p.n_splits + split) * W;
+        part[2 + d] = ov;
+        if (d == 0) { part[0] = m * LN2; part[1] = l; }  // m back in natural-log units
+    }
+
+    // stage 2 by the last CTA of this (batch, kv head)
+    __shared__ int s_last;
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+        int ticket = atomicAdd(&counters[b * p.kv_heads + hk], 1);
+        s_last = (ticket == p.n_splits - 1);
+        if (s_last) counters[b * p.kv_heads + hk] = 0;  // ready for the next launch
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    for (int idx = tid; idx < group * D; idx += 128) {
+        int r = idx / D, d = idx % D;
+        size_t row = (size_t)b * p.q_heads + (size_t)hk * group + r;
+        const float* part = p.partials + row * p.n_splits * W;
+        // The partials were written by other CTAs: read them from L2 (ld.global.cg), all loads
+        // independent of the combine chain so their latencies overlap. The combine itself runs
+        // left to right over the chunks, as stage 2 of the split reduction does.
+        float m = __ldcg(part), l = __ldcg(part + 1), ov = __ldcg(part + 2 + d);
+        for (int s0 = 1; s0 < p.n_splits; s0 += 8) {
+            float mb[8], lb[8], ob[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const bool in = s0 + u < p.n_splits;
+                const float* pb = part + (size_t)(in ? s0 + u : 0) * W;
+                mb[u] = in ? __ldcg(pb) : -INFINITY; lb[u] = in ? __ldcg(pb + 1) : 0.0f; ob[u] = in ? __ldcg(pb + 2 + d) : 0.0f;
+            }
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                MloScale sc = mlo_rescale(m, mb[u]);     // an identity partial (-inf, 0, 0) is absorbed
+                l = l * sc.ra + lb[u] * sc.rb; ov = ov * sc.ra + ob[u] * sc.rb; m = sc.m;
+            }
+        }
+        if (p.carrier_out) {
+            float* c = p.carrier_out + row * W;
+            c[2 + d] = ov;
+            if (d == 0) { c[0] = m; c[1] = l; }
+        }
+        if (p.out) {
+            float v = ov / l;  // project
+            if (p.out_dtype == SANIC_BF16) ((uint16_t*)p.out)[row * D + d] = f32_to_bf16_bits(v);
+            else ((float*)p.out)[row * D + d] = v;
+        }
+    }
+}
+
+
+}  // namespace decode
+}  // namespace sanic

@@ -39,7 +39,7 @@ constexpr int POLY_EVERY = SANIC_FLASH_POLY_EVERY;   // every n-th pair sends on
 
 struct FShared {
     uint64_t q_full, k_full[KV_STAGES], v_full[KV_STAGES], kv_empty[KV_STAGES];
-    uint64_t s_full[2], p_full[2], pv_done[2];
+    uint64_t s_full[2], s_free[2], p_full[2], pv_done[2];
     uint32_t tmem_base;
     volatile int abort_flag;
 };
@@ -106,7 +106,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     if (threadIdx.x == 0) {
         mbar_init(&sh->q_full, 1);
         for (int s = 0; s < KV_STAGES; ++s) { mbar_init(&sh->k_full[s], 1); mbar_init(&sh->v_full[s], 1); mbar_init(&sh->kv_empty[s], 1); }
-        for (int t = 0; t < 2; ++t) { mbar_init(&sh->s_full[t], 1); mbar_init(&sh->p_full[t], 4); mbar_init(&sh->pv_done[t], 1); }
+        for (int t = 0; t < 2; ++t) { mbar_init(&sh->s_full[t], 1); mbar_init(&sh->s_free[t], 4); mbar_init(&sh->p_full[t], 4); mbar_init(&sh->pv_done[t], 1); }
         sh->abort_flag = 0;
         mbar_init_fence();
     }
@@ -139,46 +139,59 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         if (lane == 0) {
             constexpr uint32_t idesc_qk = make_idesc(BM, BN, false);
             constexpr uint32_t idesc_pv = make_idesc(BM, D, true);
-            int it[2] = {0, 0};        // PV issues so far per tile
             bool ok = mbar_wait(&sh->q_full, 0, abortp, err, 12);
-            auto issue_qk = [&](int t, int stage) {
-                const uint64_t ad = make_desc(q_addr + t * Q_BYTES, 16, 1024);
-                const uint64_t bd = make_desc(kv_addr + stage * 2 * KV_BYTES, 16, 1024);
+            fence_after();
+            // The two tiles advance independently. QK(t, j+1) is issued as soon as tile t's softmax
+            // warps have pulled S(t, j) into registers, so the next scores are ready before the
+            // exponentials of the current ones finish; PV(t, j) follows when P(t, j) is written.
+            // This thread serves the four events (S free / P full, per tile) in arrival order.
+            int jq[2] = {jb_t[0], jb_t[1]};      // next key tile whose QK is to be issued
+            int jp[2] = {jb_t[0], jb_t[1]};      // next key tile whose PV is to be issued
+            int jr = j_begin;                    // next ring slot to hand back to the producer
+            uint32_t idle = 0;
+            while (ok && (jp[0] < je_t[0] || jp[1] < je_t[1])) {
+                bool progressed = false;
 #pragma unroll
-                for (int k = 0; k < D / 16; ++k) umma_f16(tmem + TM_S + t * BN, ad + 2 * k, bd + 2 * k, idesc_qk, k > 0 ? 1u : 0u);
-                umma_commit(&sh->s_full[t]);
-            };
-            int stage = 0; uint32_t phase = 0;
-            if (ok && j_end > j_begin) {
-                ok = mbar_wait(&sh->k_full[0], 0, abortp, err, 13);
-                fence_after();
-                if (ok) for (int t = 0; t < 2; ++t) if (j_begin >= jb_t[t] && j_begin < je_t[t]) issue_qk(t, 0);
-            }
-            for (int j = j_begin; j < j_end && ok; ++j) {
-                const int nstage = (stage + 1 == KV_STAGES) ? 0 : stage + 1;
-                const uint32_t nphase = (stage + 1 == KV_STAGES) ? phase ^ 1 : phase;
-                bool v_ready = false, k_next_ready = false;
-                for (int t = 0; t < 2 && ok; ++t) {
-                    if (j >= jb_t[t] && j < je_t[t]) {
-                        if (!v_ready) { ok = mbar_wait(&sh->v_full[stage], phase, abortp, err, 14); v_ready = true; if (!ok) break; }
-                        ok = mbar_wait(&sh->p_full[t], it[t] & 1, abortp, err, 15);
-                        if (!ok) break;
-                        fence_after();
-                        const uint64_t vd = make_desc(kv_addr + stage * 2 * KV_BYTES + KV_BYTES, 1024, 1024);
+                for (int t = 0; t < 2; ++t) {
+                    if (jq[t] < je_t[t]) {
+                        const int j = jq[t], nq = j - jb_t[t], u = j - j_begin;
+                        const int stage = u % KV_STAGES;
+                        if ((nq == 0 || mbar_test(&sh->s_free[t], (nq - 1) & 1)) &&
+                            mbar_test(&sh->k_full[stage], (u / KV_STAGES) & 1)) {
+                            fence_after();
+                            const uint64_t ad = make_desc(q_addr + t * Q_BYTES, 16, 1024);
+                            const uint64_t bd = make_desc(kv_addr + stage * 2 * KV_BYTES, 16, 1024);
 #pragma unroll
-                        for (int k = 0; k < BN / 16; ++k)      // A = P_t from tensor memory: 16 keys = 8 columns per step
-                            umma_f16_ts(tmem + TM_O + t * D, tmem + TM_P + t * (BN / 2) + 8 * k, vd + 128 * k, idesc_pv,
-                                        (it[t] > 0 || k > 0) ? 1u : 0u);
-                        umma_commit(&sh->pv_done[t]);
-                        it[t]++;
+                            for (int k = 0; k < D / 16; ++k) umma_f16(tmem + TM_S + t * BN, ad + 2 * k, bd + 2 * k, idesc_qk, k > 0 ? 1u : 0u);
+                            umma_commit(&sh->s_full[t]);
+                            jq[t]++; progressed = true;
+                        }
                     }
-                    if (j + 1 < j_end && j + 1 >= jb_t[t] && j + 1 < je_t[t]) {
-                        if (!k_next_ready) { ok = mbar_wait(&sh->k_full[nstage], nphase, abortp, err, 16); k_next_ready = true; if (!ok) break; fence_after(); }
-                        issue_qk(t, nstage);
+                    if (jp[t] < jq[t]) {
+                        const int j = jp[t], np = j - jb_t[t], u = j - j_begin;
+                        const int stage = u % KV_STAGES;
+                        if (mbar_test(&sh->p_full[t], np & 1) && mbar_test(&sh->v_full[stage], (u / KV_STAGES) & 1)) {
+                            fence_after();
+                            const uint64_t vd = make_desc(kv_addr + stage * 2 * KV_BYTES + KV_BYTES, 1024, 1024);
+#pragma unroll
+                            for (int k = 0; k < BN / 16; ++k)      // A = P_t from tensor memory: 16 keys = 8 columns per step
+                                umma_f16_ts(tmem + TM_O + t * D, tmem + TM_P + t * (BN / 2) + 8 * k, vd + 128 * k, idesc_pv,
+                                            (np > 0 || k > 0) ? 1u : 0u);
+                            umma_commit(&sh->pv_done[t]);
+                            jp[t]++; progressed = true;
+                        }
                     }
                 }
-                if (ok) umma_commit(&sh->kv_empty[stage]);
-                stage = nstage; phase = nphase;
+                // a ring slot goes back once neither tile still has a QK or PV to issue on it
+                while (jr < j_end && !(jp[0] < je_t[0] && jp[0] <= jr) && !(jp[1] < je_t[1] && jp[1] <= jr)) {
+                    umma_commit(&sh->kv_empty[(jr - j_begin) % KV_STAGES]);
+                    ++jr;
+                }
+                if (progressed) idle = 0;
+                else if (++idle > SPIN_LIMIT || ((idle & 1023u) == 0 && *abortp)) {
+                    if (idle > SPIN_LIMIT) { *abortp = 1; atomicCAS(err, 0, 13); }
+                    ok = false;
+                }
             }
         }
     } else if (warp >= 4) {
@@ -213,6 +226,9 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
 #pragma unroll
             for (int c = 0; c < BN / 32; ++c) tmem_ld32_nowait(s_tmem + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&r[c * 32]));
             tmem_ld_wait();
+            fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&sh->s_free[t]);   // S_t is in registers: the next QK of this tile may overwrite it
             if (edge) {
 #pragma unroll
                 for (int i = 0; i < BN; ++i) { int kk = k0 + i; if (!(kk >= klo && kk < khi)) r[i] = 0xFF800000u; }  // -inf

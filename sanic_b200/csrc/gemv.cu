@@ -29,356 +29,17 @@
 //     partners (d, d + D/2) of one head, so the epilogue rotates them and writes q, the K
 //     cache row and the V cache column of the current position in place.
 // Launched with programmatic dependent launch: weight prefetch runs before the wait.
-#include "common.cuh"
+#include "gemv_body.cuh"
 
 namespace {
 using namespace sanic;
-
-constexpr int GW = 8;  // warps per CTA
-
-struct SegTable {
-    const void* w[3];
-    const uint16_t* scales[3];
-    void* out[3];
-    int rows[3];
-    int tile_begin[4];
-};
-struct Fused {
-    const float* norm_x; const uint16_t* norm_gamma; float norm_eps;
-    const float* rope_table; const int32_t* rope_position; uint16_t* rope_q_out; uint16_t* rope_k_cache; uint16_t* rope_v_cache;
-    int q_heads, kv_heads, head_dim, ctx;
-};
-
-__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
-    uint32_t r;
-    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(sel));
-    return r;
-}
-__device__ __forceinline__ uint32_t nib_pair(uint32_t w) {  // (w & 0x000F000F) | 0x43004300
-    uint32_t r;
-    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(r) : "r"(w), "r"(0x000F000Fu), "r"(0x43004300u));
-    return r;
-}
-__device__ __forceinline__ const void* pick3(const void* const (&a)[3], int i) { return i == 0 ? a[0] : (i == 1 ? a[1] : a[2]); }
-
-// 8 consecutive activations of batch column n starting at k as four packed bf16x2 registers.
-template <bool NORM>
-__device__ __forceinline__ uint4 load_x8(const uint16_t* xrow, const float* xf, const uint16_t* gamma, float den, int k,
-                                         bool ok) {
-    if (!ok) return make_uint4(0, 0, 0, 0);
-    if (!NORM) return __ldg((const uint4*)(xrow + k));
-    float4 a = __ldg((const float4*)(xf + k)), b = __ldg((const float4*)(xf + k + 4));
-    uint4 g = __ldg((const uint4*)(gamma + k));
-    uint4 r;
-    // `den` holds 1/sqrt(mean(x^2)+eps): one multiply per element instead of a division
-    r.x = pack_bf16x2((a.x * bf16lo(g.x)) * den, (a.y * bf16hi(g.x)) * den);
-    r.y = pack_bf16x2((a.z * bf16lo(g.y)) * den, (a.w * bf16hi(g.y)) * den);
-    r.z = pack_bf16x2((b.x * bf16lo(g.z)) * den, (b.y * bf16hi(g.z)) * den);
-    r.w = pack_bf16x2((b.z * bf16lo(g.w)) * den, (b.w * bf16hi(g.w)) * den);
-    return r;
-}
+using namespace sanic::gemv;
 
 template <bool W4, int NT, bool DUAL, bool NORM>
 __global__ void __launch_bounds__(GW * 32, 2) gemv_mma_kernel(const uint16_t* __restrict__ x, int batch, int K,
                                                            SegTable segs, int n_segments, int out_dtype, int epilogue,
                                                            const float* residual, Fused fz, int KS) {
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int g = lane >> 2, t = lane & 3;
-    // KS CTAs of one thread-block cluster share a row tile and split K between them
-    const int gtile = (int)blockIdx.x / KS, krank = (int)blockIdx.x % KS;
-    int seg = 0;
-    if (!DUAL) {
-        if (n_segments > 1 && gtile >= segs.tile_begin[1]) seg = 1;
-        if (n_segments > 2 && gtile >= segs.tile_begin[2]) seg = 2;
-    }
-    const int tile = gtile - (seg == 0 ? segs.tile_begin[0] : (seg == 1 ? segs.tile_begin[1] : segs.tile_begin[2]));
-    const bool rope = (epilogue == SANIC_EPI_ROPE_CACHE);
-    // weight rows of A-fragment rows g and g+8
-    int wrow0, wrow1;
-    if (rope) {   // rotate-half partners of one head: d = 8*sub + g and d + D/2
-        const int tph = fz.head_dim / 16, head = tile / tph, sub = tile % tph;
-        wrow0 = head * fz.head_dim + 8 * sub + g;
-        wrow1 = wrow0 + fz.head_dim / 2;
-    } else {
-        wrow0 = tile * 16 + g;
-        wrow1 = wrow0 + 8;
-    }
-    constexpr int NM = DUAL ? 2 : 1;
-    const int nblk = K / 64;
-    const int cb0 = (krank * nblk) / KS, cb1 = ((krank + 1) * nblk) / KS;   // this CTA's K range, in 64-blocks
-    const int b0 = cb0 + (warp * (cb1 - cb0)) / GW, b1 = cb0 + ((warp + 1) * (cb1 - cb0)) / GW;
-
-    // Weights do not depend on the previous kernel of the step: ask L2 for this warp's whole weight
-    // slice (16 rows x its K range) before waiting for that kernel, so HBM keeps streaming while
-    // the predecessor drains.
-    {
-        const size_t row_bytes = W4 ? (size_t)K / 2 : (size_t)K * 2;
-        const int blk_bytes = W4 ? 32 : 128;
-        const int span = (b1 - b0) * blk_bytes;
-        const int lines = (span + 127) / 128;
-#pragma unroll
-        for (int mI = 0; mI < NM; ++mI) {
-            const char* wbase = (const char*)pick3(segs.w, DUAL ? mI : seg);
-            for (int i = lane; i < 16 * lines; i += 32) {
-                const int r = i / lines, ln = i % lines;
-                const size_t wrow = (r < 8) ? (size_t)(wrow0 - g + r) : (size_t)(wrow1 - g + r - 8);
-                asm volatile("prefetch.global.L2 [%0];" ::"l"(wbase + wrow * row_bytes + (size_t)b0 * blk_bytes + (size_t)ln * 128));
-            }
-        }
-    }
-    griddep_launch();
-    griddep_wait();
-
-    __shared__ float s_den[16];
-    if (NORM) {
-        for (int n = warp; n < batch; n += GW) {
-            const float* xr = fz.norm_x + (size_t)n * K;
-            float ss = 0.0f;
-            for (int i = lane * 4; i < K; i += 128) {
-                float4 v = __ldg((const float4*)(xr + i));
-                ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
-            }
-            ss = warp_sum(ss);
-            if (lane == 0) s_den[n] = 1.0f / sqrtf(ss * (1.0f / (float)K) + fz.norm_eps);
-        }
-        __syncthreads();
-    }
-
-    float acc[NM][NT][4];
-#pragma unroll
-    for (int mI = 0; mI < NM; ++mI)
-#pragma unroll
-        for (int j = 0; j < NT; ++j) acc[mI][j][0] = acc[mI][j][1] = acc[mI][j][2] = acc[mI][j][3] = 0.0f;
-
-    const uint16_t* xrow[NT];
-    const float* xf[NT];
-    float den[NT];
-    bool xok[NT];
-#pragma unroll
-    for (int j = 0; j < NT; ++j) {
-        xok[j] = (8 * j + g) < batch;
-        const int n = xok[j] ? (8 * j + g) : 0;
-        xrow[j] = x + (size_t)n * K;
-        xf[j] = NORM ? fz.norm_x + (size_t)n * K : nullptr;
-        den[j] = NORM ? s_den[n] : 1.0f;
-    }
-    const uint16_t* gam = fz.norm_gamma;
-
-    if (!W4) {
-        const uint16_t* wr[NM][2];
-#pragma unroll
-        for (int mI = 0; mI < NM; ++mI) {
-            const uint16_t* W = (const uint16_t*)pick3(segs.w, DUAL ? mI : seg);
-            wr[mI][0] = W + (size_t)wrow0 * K;
-            wr[mI][1] = W + (size_t)wrow1 * K;
-        }
-        constexpr int U = DUAL ? 2 : 4;
-        for (int blk = b0; blk < b1; blk += U) {
-            const int nb = min(U, b1 - blk);      // uniform across the warp
-            uint4 a[U][NM][2][2];
-            uint4 xb[U][NT][2];
-#pragma unroll
-            for (int u = 0; u < U; ++u) {
-                if (u < nb) {
-                    int kb = (blk + u) * 64;
-#pragma unroll
-                    for (int mI = 0; mI < NM; ++mI)
-#pragma unroll
-                        for (int r = 0; r < 2; ++r) {
-                            a[u][mI][r][0] = ldg_stream16(wr[mI][r] + kb + t * 8);
-                            a[u][mI][r][1] = ldg_stream16(wr[mI][r] + kb + 32 + t * 8);
-                        }
-                }
-            }
-#pragma unroll
-            for (int u = 0; u < U; ++u) {
-                if (u < nb) {
-                    int kb = (blk + u) * 64;
-#pragma unroll
-                    for (int j = 0; j < NT; ++j) {
-                        xb[u][j][0] = load_x8<NORM>(xrow[j], xf[j], gam, den[j], kb + t * 8, xok[j]);
-                        xb[u][j][1] = load_x8<NORM>(xrow[j], xf[j], gam, den[j], kb + 32 + t * 8, xok[j]);
-                    }
-                }
-            }
-#pragma unroll
-            for (int u = 0; u < U; ++u) {
-                if (u < nb) {
-#pragma unroll
-                    for (int mI = 0; mI < NM; ++mI)
-#pragma unroll
-                        for (int j = 0; j < NT; ++j)
-#pragma unroll
-                            for (int hf = 0; hf < 2; ++hf) {
-                                const uint4& r0 = a[u][mI][0][hf];
-                                const uint4& r1 = a[u][mI][1][hf];
-                                const uint4& xv = xb[u][j][hf];
-                                mma_bf16_16816(acc[mI][j], r0.x, r1.x, r0.y, r1.y, xv.x, xv.y);
-                                mma_bf16_16816(acc[mI][j], r0.z, r1.z, r0.w, r1.w, xv.z, xv.w);
-                            }
-                }
-            }
-        }
-    } else {
-        const int G = K / 64;  // groups per row
-        const uint8_t* wr[NM][2];
-        const uint16_t* sr[NM][2];
-#pragma unroll
-        for (int mI = 0; mI < NM; ++mI) {
-            const uint8_t* W = (const uint8_t*)pick3(segs.w, DUAL ? mI : seg);
-            const int si = DUAL ? mI : seg;
-            const uint16_t* S = si == 0 ? segs.scales[0] : (si == 1 ? segs.scales[1] : segs.scales[2]);
-            wr[mI][0] = W + (size_t)wrow0 * (K / 2);
-            wr[mI][1] = W + (size_t)wrow1 * (K / 2);
-            sr[mI][0] = S + (size_t)wrow0 * G;
-            sr[mI][1] = S + (size_t)wrow1 * G;
-        }
-        constexpr int U = DUAL ? 2 : 4;
-        const uint32_t ONES = 0x3F803F80u;
-        auto do_group = [&](const uint2 (&wv)[NM][2], const float (&sc)[NM][2], int blk) {
-            int kb = blk * 64 + t * 16;
-#pragma unroll
-            for (int j = 0; j < NT; ++j) {
-                uint4 xa = load_x8<NORM>(xrow[j], xf[j], gam, den[j], kb, xok[j]);
-                uint4 xc = load_x8<NORM>(xrow[j], xf[j], gam, den[j], kb + 8, xok[j]);
-                // activation pairs matching the nibble pairing (n_i, n_{i+4})
-                uint32_t bA0 = prmt(xa.x, xa.z, 0x5410), bA1 = prmt(xa.x, xa.z, 0x7632);
-                uint32_t bA2 = prmt(xa.y, xa.w, 0x5410), bA3 = prmt(xa.y, xa.w, 0x7632);
-                uint32_t bC0 = prmt(xc.x, xc.z, 0x5410), bC1 = prmt(xc.x, xc.z, 0x7632);
-                uint32_t bC2 = prmt(xc.y, xc.w, 0x5410), bC3 = prmt(xc.y, xc.w, 0x7632);
-                float c1[4] = {0, 0, 0, 0};
-                mma_bf16_16816(c1, ONES, ONES, ONES, ONES, bA0, bA1);
-                mma_bf16_16816(c1, ONES, ONES, ONES, ONES, bA2, bA3);
-                mma_bf16_16816(c1, ONES, ONES, ONES, ONES, bC0, bC1);
-                mma_bf16_16816(c1, ONES, ONES, ONES, ONES, bC2, bC3);
-#pragma unroll
-                for (int mI = 0; mI < NM; ++mI) {
-                    uint32_t w0a = wv[mI][0].x, w0b = wv[mI][0].y, w1a = wv[mI][1].x, w1b = wv[mI][1].y;
-                    float c[4] = {0, 0, 0, 0};
-                    mma_bf16_16816(c, nib_pair(w0a), nib_pair(w1a), nib_pair(w0a >> 4), nib_pair(w1a >> 4), bA0, bA1);
-                    mma_bf16_16816(c, nib_pair(w0a >> 8), nib_pair(w1a >> 8), nib_pair(w0a >> 12), nib_pair(w1a >> 12), bA2, bA3);
-                    mma_bf16_16816(c, nib_pair(w0b), nib_pair(w1b), nib_pair(w0b >> 4), nib_pair(w1b >> 4), bC0, bC1);
-                    mma_bf16_16816(c, nib_pair(w0b >> 8), nib_pair(w1b >> 8), nib_pair(w0b >> 12), nib_pair(w1b >> 12), bC2, bC3);
-                    acc[mI][j][0] = fmaf(sc[mI][0], fmaf(-136.0f, c1[0], c[0]), acc[mI][j][0]);
-                    acc[mI][j][1] = fmaf(sc[mI][0], fmaf(-136.0f, c1[1], c[1]), acc[mI][j][1]);
-                    acc[mI][j][2] = fmaf(sc[mI][1], fmaf(-136.0f, c1[2], c[2]), acc[mI][j][2]);
-                    acc[mI][j][3] = fmaf(sc[mI][1], fmaf(-136.0f, c1[3], c[3]), acc[mI][j][3]);
-                }
-            }
-        };
-        for (int blk = b0; blk < b1; blk += U) {
-            const int nb = min(U, b1 - blk);
-            uint2 wv[U][NM][2];
-            float sc[U][NM][2];
-#pragma unroll
-            for (int u = 0; u < U; ++u) {
-                if (u < nb) {
-#pragma unroll
-                    for (int mI = 0; mI < NM; ++mI)
-#pragma unroll
-                        for (int r = 0; r < 2; ++r) {
-                            wv[u][mI][r] = ldg_stream8(wr[mI][r] + (size_t)(blk + u) * 32 + t * 8);
-                            sc[u][mI][r] = bf16_to_f32(__ldg(sr[mI][r] + blk + u));
-                        }
-                }
-            }
-#pragma unroll
-            for (int u = 0; u < U; ++u)
-                if (u < nb) do_group(wv[u], sc[u], blk + u);
-        }
-    }
-
-    // deterministic cross-warp sum: red[warp][matrix][row 0..15][col 0..8*NT)
-    __shared__ float red[GW][NM][16][8 * NT + 1];
-#pragma unroll
-    for (int mI = 0; mI < NM; ++mI)
-#pragma unroll
-        for (int j = 0; j < NT; ++j) {
-            red[warp][mI][g][8 * j + 2 * t] = acc[mI][j][0];
-            red[warp][mI][g][8 * j + 2 * t + 1] = acc[mI][j][1];
-            red[warp][mI][g + 8][8 * j + 2 * t] = acc[mI][j][2];
-            red[warp][mI][g + 8][8 * j + 2 * t + 1] = acc[mI][j][3];
-        }
-    __syncthreads();
-    // CTA sum in a fixed warp order, then (KS > 1) the cluster's CTAs are summed in rank order by
-    // rank 0 through distributed shared memory: deterministic, no global scratch.
-    __shared__ float csum[NM][16][8 * NT + 1];
-    for (int idx = tid; idx < NM * 16 * 8 * NT; idx += GW * 32) {
-        const int n = idx % (8 * NT), r = (idx / (8 * NT)) % 16, mI = idx / (8 * NT * 16);
-        float sv = 0.0f;
-#pragma unroll
-        for (int w = 0; w < GW; ++w) sv += red[w][mI][r][n];
-        csum[mI][r][n] = sv;
-    }
-    __syncthreads();
-    if (KS > 1) {
-        asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-        if (krank == 0) {
-            for (int idx = tid; idx < NM * 16 * 8 * NT; idx += GW * 32) {
-                const int n = idx % (8 * NT), r = (idx / (8 * NT)) % 16, mI = idx / (8 * NT * 16);
-                float sv = csum[mI][r][n];
-                const uint32_t local = smem_u32(&csum[mI][r][n]);
-                for (int kr = 1; kr < KS; ++kr) {
-                    uint32_t remote; float v;
-                    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(kr));
-                    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote));
-                    sv += v;
-                }
-                red[0][mI][r][n] = sv;     // rank 0 publishes the cluster total for its epilogue
-            }
-        }
-        // peers stay alive until rank 0 has read their shared memory
-        asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-        if (krank != 0) return;
-        __syncthreads();
-    } else {
-        for (int idx = tid; idx < NM * 16 * 8 * NT; idx += GW * 32) {
-            const int n = idx % (8 * NT), r = (idx / (8 * NT)) % 16, mI = idx / (8 * NT * 16);
-            red[0][mI][r][n] = csum[mI][r][n];
-        }
-        __syncthreads();
-    }
-    if (rope) {
-        // thread (r < 8, n): partners a = row r (d0 = 8*sub + r) and b = row r + 8 (d0 + D/2)
-        const int D = fz.head_dim, F = D / 2, tph = D / 16;
-        const int head = tile / tph, sub = tile % tph;
-        const int pos = *fz.rope_position;
-        for (int idx = tid; idx < 8 * batch; idx += GW * 32) {
-            const int n = idx / 8, r = idx % 8;
-            const float a = red[0][0][r][n], b = red[0][0][r + 8][n];
-            const int d0 = 8 * sub + r;
-            if (pos < 0 || pos >= fz.ctx) continue;
-            if (seg < 2) {
-                const float* cs = fz.rope_table + 2 * ((size_t)pos * F + d0);
-                const float c = cs[0], sn = cs[1];
-                const uint16_t o0 = f32_to_bf16_bits(a * c + (-b) * sn), o1 = f32_to_bf16_bits(b * c + a * sn);
-                uint16_t* dst = (seg == 0) ? fz.rope_q_out + ((size_t)n * fz.q_heads + head) * D
-                                           : fz.rope_k_cache + (((size_t)n * fz.kv_heads + head) * fz.ctx + pos) * D;
-                dst[d0] = o0; dst[d0 + F] = o1;
-            } else {
-                uint16_t* dst = fz.rope_v_cache + ((size_t)n * fz.kv_heads + head) * D * (size_t)fz.ctx;
-                dst[(size_t)d0 * fz.ctx + pos] = f32_to_bf16_bits(a);
-                dst[(size_t)(d0 + F) * fz.ctx + pos] = f32_to_bf16_bits(b);
-            }
-        }
-        return;
-    }
-    const int row0 = tile * 16;
-    const int rows = seg == 0 ? segs.rows[0] : (seg == 1 ? segs.rows[1] : segs.rows[2]);
-    void* outp = seg == 0 ? segs.out[0] : (seg == 1 ? segs.out[1] : segs.out[2]);
-    for (int idx = tid; idx < 16 * batch; idx += GW * 32) {
-        int n = idx / 16, r = idx % 16;  // consecutive threads -> consecutive rows (contiguous in out[n][row])
-        float y = red[0][0][r][n];
-        if (DUAL) {  // silu(a) * b = (a * 1/(1+exp(-a))) * b  (reference src/ir.rs:1500-1509)
-            const float ga = y, up = red[0][NM - 1][r][n];
-            float sig = 1.0f / (1.0f + expf(-ga));
-            y = (ga * sig) * up;
-        }
-        size_t oi = (size_t)n * rows + row0 + r;
-        if (epilogue == SANIC_EPI_RESIDUAL_ADD) y = residual[oi] + y;
-        if (out_dtype == SANIC_BF16) ((uint16_t*)outp)[oi] = f32_to_bf16_bits(y);
-        else ((float*)outp)[oi] = y;
-    }
+    gemv_tile<W4, NT, DUAL, NORM>(x, batch, K, segs, n_segments, out_dtype, epilogue, residual, fz, KS, (int)blockIdx.x, true);
 }
 
 template <bool W4, int NT, bool DUAL, bool NORM>

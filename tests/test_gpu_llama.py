@@ -2,7 +2,8 @@
 
 Greedy tokens must be identical step for step; logits agree to the bf16 bound. Both sides round
 at the same declared storage points (weights, caches, projection inputs and q in bf16; residual
-stream f32), so remaining differences are f32-vs-f64 accumulation only. When a token differs the
+stream f32); the remaining differences are f32-vs-f64 accumulation and the bf16 rounding of the
+attention probabilities that feed the tensor-core P.V product. When a token differs the
 test prints the oracle's top-2 logit gap: a gap below the bf16 bound is a tie, not an error.
 """
 import numpy as np
@@ -49,8 +50,13 @@ def run_pair(dev, cfg, ctx, batch, w4, steps, prefill, seed=5, fused=True):
         ocur = o.step(ocur, prefill + s)
         lg = m.logits.cpu().numpy().astype(np.float64)
         ol = o.logits()
+        # bf16 bound of one kernel is 2e-2; independent rounding noise of a deeper stack grows with the
+        # square root of its depth (the 2-layer model is held to the single-kernel bound)
+        tol_logits = 2e-2 * max(1.0, (cfg["layers"] / 2.0) ** 0.5)
         err = np.max(np.abs(lg - ol) / (1.0 + np.abs(ol)))
-        assert err <= 2e-2, f"step {s}: logits differ by {err}"
+        assert err <= tol_logits, f"step {s}: logits differ by {err}"
+        rms = np.linalg.norm(lg - ol) / np.linalg.norm(ol)
+        assert rms <= 2e-2, f"step {s}: logits differ by {rms} in relative rms"
         bad = np.nonzero(got != ocur)[0]
         if bad.size:
             # A different token is an error unless the oracle's own top-2 gap on that row is inside
