@@ -32,10 +32,6 @@ constexpr int TM_S = 0, TM_P = 256, TM_O = 384;
 constexpr int Q_BYTES = BM * D * 2;        // 16 KB per query tile
 constexpr int KV_BYTES = BN * D * 2;       // 16 KB per K or V tile
 constexpr int NTHREADS = 384;
-#ifndef SANIC_FLASH_POLY_EVERY
-#define SANIC_FLASH_POLY_EVERY 0
-#endif
-constexpr int POLY_EVERY = SANIC_FLASH_POLY_EVERY;   // every n-th pair sends one exponential to the FMA-pipe polynomial (0 = none)
 
 struct FShared {
     uint64_t q_full, k_full[KV_STAGES], v_full[KV_STAGES], kv_empty[KV_STAGES];
@@ -56,19 +52,10 @@ __device__ __forceinline__ float ex2(float x) {
     return y;
 }
 
-// exp2 on the FMA pipes: round-to-nearest split x = n + f with f in [-0.5, 0.5] by the magic-number
-// add, a degree-3 minimax polynomial for 2^f (max relative error 7.5e-5, far below the 2^-9 of
-// the bf16 P it feeds), and n added into the exponent field. The SFU evaluates 16 exponentials
-// per clock per SM, which at head_dim 64 is twice the time of the tile's MMAs, so every other
-// score takes this path and the two pipes run side by side.
-__device__ __forceinline__ float ex2_poly(float x) {
-    x = fmaxf(x, -126.0f);
-    const float t = x + 12582912.0f;             // 1.5 * 2^23: the integer part lands in the low mantissa bits
-    const float f = x - (t - 12582912.0f);
-    float p = fmaf(0.05517164617776871f, f, 0.2426111251115799f);
-    p = fmaf(p, f, 0.6932609677314758f);
-    p = fmaf(p, f, 0.9999280571937561f);
-    return __int_as_float(__float_as_int(p) + (__float_as_int(t) << 23));
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float y;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(y) : "f"(a), "f"(b), "f"(c));
+    return y;
 }
 
 // key-tile range [jb, je) that tile rows [r0, r0+127] can see
@@ -188,9 +175,12 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                     ++jr;
                 }
                 if (progressed) idle = 0;
-                else if (++idle > SPIN_LIMIT || ((idle & 1023u) == 0 && *abortp)) {
-                    if (idle > SPIN_LIMIT) { *abortp = 1; atomicCAS(err, 0, 13); }
-                    ok = false;
+                else {
+                    __nanosleep(64);     // back off: a tight probe loop slows the other warps' barrier waits
+                    if (++idle > (SPIN_LIMIT >> 4) || ((idle & 1023u) == 0 && *abortp)) {
+                        if (idle > (SPIN_LIMIT >> 4)) { *abortp = 1; atomicCAS(err, 0, 13); }
+                        ok = false;
+                    }
                 }
             }
         }
@@ -221,25 +211,33 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             int klo = 0, khi = p.kv_len;              // visible keys of this row: [klo, khi)
             if (p.causal || p.window > 0) khi = min(khi, grow + 1);
             if (p.window > 0) klo = max(0, grow - p.window + 1);
-            // the whole score row of this tile in registers: one TMEM round trip
+            // The whole score row of this tile goes to registers in four 32-column loads; the row max of
+            // one chunk is taken while the next chunk is in flight.
             uint32_t r[BN];
+            float mxs[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+            tmem_ld32_nowait(s_tmem, *reinterpret_cast<uint32_t(*)[32]>(&r[0]));
 #pragma unroll
-            for (int c = 0; c < BN / 32; ++c) tmem_ld32_nowait(s_tmem + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&r[c * 32]));
-            tmem_ld_wait();
-            fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&sh->s_free[t]);   // S_t is in registers: the next QK of this tile may overwrite it
-            if (edge) {
+            for (int c = 0; c < BN / 32; ++c) {
+                tmem_ld_wait();
+                if (c + 1 < BN / 32) tmem_ld32_nowait(s_tmem + (c + 1) * 32, *reinterpret_cast<uint32_t(*)[32]>(&r[(c + 1) * 32]));
+                else {
+                    fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&sh->s_free[t]);   // S_t is in registers: the next QK of this tile may overwrite it
+                }
+                if (edge) {
 #pragma unroll
-                for (int i = 0; i < BN; ++i) { int kk = k0 + i; if (!(kk >= klo && kk < khi)) r[i] = 0xFF800000u; }  // -inf
+                    for (int i = c * 32; i < c * 32 + 32; ++i) { int kk = k0 + i; if (!(kk >= klo && kk < khi)) r[i] = 0xFF800000u; }  // -inf
+                }
+#pragma unroll
+                for (int i = 0; i < 32; i += 8) {      // four independent chains of three-input max
+                    mxs[0] = max3(mxs[0], __uint_as_float(r[c * 32 + i]), __uint_as_float(r[c * 32 + i + 1]));
+                    mxs[1] = max3(mxs[1], __uint_as_float(r[c * 32 + i + 2]), __uint_as_float(r[c * 32 + i + 3]));
+                    mxs[2] = max3(mxs[2], __uint_as_float(r[c * 32 + i + 4]), __uint_as_float(r[c * 32 + i + 5]));
+                    mxs[3] = max3(mxs[3], __uint_as_float(r[c * 32 + i + 6]), __uint_as_float(r[c * 32 + i + 7]));
+                }
             }
-            // eight independent chains instead of one 128-long dependent chain of max
-            float mxs[8];
-#pragma unroll
-            for (int i = 0; i < 8; ++i) mxs[i] = __uint_as_float(r[i]);
-#pragma unroll
-            for (int i = 8; i < BN; ++i) mxs[i & 7] = fmaxf(mxs[i & 7], __uint_as_float(r[i]));
-            const float mx = fmaxf(fmaxf(fmaxf(mxs[0], mxs[1]), fmaxf(mxs[2], mxs[3])), fmaxf(fmaxf(mxs[4], mxs[5]), fmaxf(mxs[6], mxs[7])));
+            const float mx = fmaxf(fmaxf(mxs[0], mxs[1]), fmaxf(mxs[2], mxs[3]));
             // Lazy rescale: keep the reference max until the running max has moved by more than
             // 2^8; exp2(s - m_ref) then stays below 256, well inside bf16/f32 range, and o / l is
             // unchanged because both carry the same reference.
@@ -248,42 +246,40 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             float alpha = 1.0f;
             if (need) { alpha = (m > -INFINITY) ? ex2(m - m_cand) : 0.0f; m = m_cand; }
             const float msub = (m > -INFINITY) ? m : 0.0f;
-            if (it > 0) {
-                ok = mbar_wait(&sh->pv_done[t], (it - 1) & 1, abortp, err, 22);  // O_t final for tile j-1, P_t free
-                if (!ok) break;
-                fence_after();
-                if (__any_sync(0xffffffffu, need)) {
-#pragma unroll 1
-                    for (int c = 0; c < D / 32; ++c) {
-                        uint32_t o[32];
-                        tmem_ld32(o_tmem + c * 32, o);
-#pragma unroll
-                        for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-                        tmem_st32(o_tmem + c * 32, o);
-                    }
-                    tmem_st_wait();
-                }
-            }
-            // P = exp2(S*sl2 - m_ref) -> bf16 pairs -> tensor memory (the A operand of the PV MMA), row sum
+            // P = exp2(S*sl2 - m_ref) as bf16 pairs, packed in place over the score registers, and the row
+            // sum. The first half is stored while the second half is still in the SFU; only at that store
+            // is the previous PV of this tile needed (it has read P_t and finished O_t).
             float sums[8] = {0, 0, 0, 0, 0, 0, 0, 0};
 #pragma unroll
             for (int hb = 0; hb < 2; ++hb) {
-                uint32_t pk[32];
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    const int c = hb * 64 + 2 * i;
-                    float p0 = ex2(fmaf(__uint_as_float(r[c]), sl2, -msub));
-                    float p1 = (POLY_EVERY > 0 && (i % (POLY_EVERY > 0 ? POLY_EVERY : 1)) == 0)
-                                   ? ex2_poly(fmaf(__uint_as_float(r[c + 1]), sl2, -msub))
-                                   : ex2(fmaf(__uint_as_float(r[c + 1]), sl2, -msub));
+                for (int i = hb * 32; i < hb * 32 + 32; ++i) {
+                    const float p0 = ex2(fmaf(__uint_as_float(r[2 * i]), sl2, -msub));
+                    const float p1 = ex2(fmaf(__uint_as_float(r[2 * i + 1]), sl2, -msub));
                     sums[(2 * i) & 7] += p0; sums[(2 * i + 1) & 7] += p1;
-                    pk[i] = pack_bf16x2(p0, p1);
+                    r[i] = pack_bf16x2(p0, p1);
                 }
-                tmem_st32(p_tmem + hb * 32, pk);
+                if (hb == 0 && it > 0) {
+                    ok = mbar_wait(&sh->pv_done[t], (it - 1) & 1, abortp, err, 22);
+                    if (!ok) break;
+                    fence_after();
+                    if (__any_sync(0xffffffffu, need)) {
+#pragma unroll 1
+                        for (int c = 0; c < D / 32; ++c) {
+                            uint32_t o[32];
+                            tmem_ld32(o_tmem + c * 32, o);
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                            tmem_st32(o_tmem + c * 32, o);
+                        }
+                    }
+                }
+                tmem_st32(p_tmem + hb * 32, *reinterpret_cast<uint32_t(*)[32]>(&r[hb * 32]));
             }
-            tmem_st_wait();
+            if (!ok) break;
             const float sum = ((sums[0] + sums[1]) + (sums[2] + sums[3])) + ((sums[4] + sums[5]) + (sums[6] + sums[7]));
             l = l * alpha + sum;
+            tmem_st_wait();
             fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&sh->p_full[t]);
