@@ -75,6 +75,13 @@ __device__ __forceinline__ void tile_range(const FParams& p, int r0, int nkv, in
     if (p.window > 0) jb = max(0, r0 - p.window + 1) / BN;
 }
 
+// Item index of this CTA's n-th round: rounds alternate direction over the CTAs so that the CTA that got
+// the heaviest item of one round gets the lightest of the next.
+__device__ __forceinline__ int item_of_round(int n) {
+    const int G = gridDim.x, c = blockIdx.x;
+    return n * G + ((n & 1) ? G - 1 - c : c);
+}
+
 // Items are ordered heaviest first (latest query block first; within a block the query heads of one
 // key/value head are adjacent so concurrent CTAs share K/V tiles in L2).
 __device__ __forceinline__ Item make_item(const FParams& p, int k, int nkv) {
@@ -122,14 +129,14 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     const uint32_t tmem = sh->tmem_base;
     volatile int* abortp = &sh->abort_flag;
 
-    // Every role walks the same item sequence: item = blockIdx.x, + gridDim.x, ... ; all barrier
+    // Every role walks the same item sequence: its own sub-list; all barrier
     // parities come from running counts, so nothing is re-initialised between items.
     if (warp == 0) {
         if (lane == 0) {
             int stage = 0; uint32_t phase = 1;
             bool ok = true;
             int n = 0;
-            for (int k = blockIdx.x; k < p.n_items && ok; k += gridDim.x, ++n) {
+            for (int k = item_of_round(0); k < p.n_items && ok; k = item_of_round(++n)) {
                 const Item w = make_item(p, k, nkv);
                 const int qb = n & 1;
                 ok = mbar_wait(&sh->q_empty[qb], ((n >> 1) & 1) ^ 1, abortp, err, 10);
@@ -164,7 +171,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             uint32_t u_base = 0;                 // key tiles of all earlier items: position in the K/V ring
             uint32_t n_qk[2] = {0, 0}, n_pv[2] = {0, 0};   // QK / PV issues so far per tile, over all items
             uint32_t n_act[2] = {0, 0};          // earlier items in which the tile had work (its O was read back)
-            for (int k = blockIdx.x; k < p.n_items && ok; k += gridDim.x, ++n) {
+            for (int k = item_of_round(0); k < p.n_items && ok; k = item_of_round(++n)) {
                 const Item w = make_item(p, k, nkv);
                 const int qb = n & 1;
                 ok = mbar_wait(&sh->q_full[qb], (n >> 1) & 1, abortp, err, 12);
@@ -244,14 +251,15 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         const float sl2 = p.scale * LOG2E;
         uint32_t n_it = 0;           // key tiles folded so far by this tile, over all items
         bool ok = true;
-        for (int k = blockIdx.x; k < p.n_items && ok; k += gridDim.x) {
+        int n = 0;
+        for (int k = item_of_round(0); k < p.n_items && ok; k = item_of_round(++n)) {
             const Item w = make_item(p, k, nkv);
             const int r0 = w.m0 + t * BM;
             const int grow = r0 + row;                    // global query position
             float m = -INFINITY, l = 0.0f;
             for (int j = w.jb[t]; j < w.je[t] && ok; ++j, ++n_it) {
                 const bool first = (j == w.jb[t]);
-                ok = mbar_wait(&sh->s_full[t], n_it & 1, abortp, err, 21);
+                ok = mbar_wait_spin(&sh->s_full[t], n_it & 1, abortp, err, 21);
                 if (!ok) break;
                 fence_after();
                 const int k0 = j * BN;
@@ -311,7 +319,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                         r[i] = pack_bf16x2(p0, p1);
                     }
                     if (hb == 0 && n_it > 0) {
-                        ok = mbar_wait(&sh->pv_done[t], (n_it - 1) & 1, abortp, err, 22);
+                        ok = mbar_wait_spin(&sh->pv_done[t], (n_it - 1) & 1, abortp, err, 22);
                         if (!ok) break;
                         fence_after();
                         if (!first && __any_sync(0xffffffffu, need)) {
@@ -337,7 +345,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             }
             // epilogue: read O_t back, release it for the next item, project o / l and store bf16 rows
             if (ok && w.je[t] > w.jb[t]) {
-                ok = mbar_wait(&sh->pv_done[t], (n_it - 1) & 1, abortp, err, 23);
+                ok = mbar_wait_spin(&sh->pv_done[t], (n_it - 1) & 1, abortp, err, 23);
                 if (!ok) break;
                 fence_after();
                 uint32_t o[D];

@@ -41,6 +41,17 @@ __device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
                  : "=r"(done) : "r"(smem_u32(bar)), "r"(parity) : "memory");
     return done != 0;
 }
+// Bounded wait that never parks the thread: for waits on the critical path, where the wake-up
+// latency of a suspended try_wait costs more than the probes.
+__device__ __forceinline__ bool mbar_wait_spin(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* err, int code) {
+    for (uint32_t it = 0; it < SPIN_LIMIT; ++it) {
+        if (mbar_test(bar, parity)) return true;
+        if ((it & 1023u) == 1023u && *abort_flag) return false;
+    }
+    *abort_flag = 1;
+    atomicCAS(err, 0, code);
+    return false;
+}
 // 2-D tiled TMA load into this CTA's shared memory, completion counted on an mbarrier; one CTA is the only destination.
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
