@@ -60,6 +60,16 @@ __device__ __forceinline__ float ex2(float x) {
     return y;
 }
 
+// Packed pairs: one instruction for two adjacent columns.
+__device__ __forceinline__ void ffma2(float& d0, float& d1, float a0, float a1, float b, float c) {
+    asm("{\n\t.reg .b64 ra, rb, rc, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %4};\n\tmov.b64 rc, {%5, %5};\n\t"
+        "fma.rn.f32x2 rd, ra, rb, rc;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+        : "=f"(d0), "=f"(d1) : "f"(a0), "f"(a1), "f"(b), "f"(c));
+}
+__device__ __forceinline__ void fadd2(float& d0, float& d1, float a0, float a1) {   // d += a
+    asm("{\n\t.reg .b64 ra, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rd, {%0, %1};\n\tadd.rn.f32x2 rd, rd, ra;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+        : "+f"(d0), "+f"(d1) : "f"(a0), "f"(a1));
+}
 __device__ __forceinline__ float max3(float a, float b, float c) {
     float y;
     asm("max.f32 %0, %1, %2, %3;" : "=f"(y) : "f"(a), "f"(b), "f"(c));
@@ -313,9 +323,10 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                 for (int hb = 0; hb < 2; ++hb) {
 #pragma unroll
                     for (int i = hb * 32; i < hb * 32 + 32; ++i) {
-                        const float p0 = ex2(fmaf(__uint_as_float(r[2 * i]), sl2, -msub));
-                        const float p1 = ex2(fmaf(__uint_as_float(r[2 * i + 1]), sl2, -msub));
-                        sums[(2 * i) & 7] += p0; sums[(2 * i + 1) & 7] += p1;
+                        float x0, x1;
+                        ffma2(x0, x1, __uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]), sl2, -msub);
+                        const float p0 = ex2(x0), p1 = ex2(x1);
+                        fadd2(sums[(2 * i) & 7], sums[(2 * i + 1) & 7], p0, p1);
                         r[i] = pack_bf16x2(p0, p1);
                     }
                     if (hb == 0 && n_it > 0) {
