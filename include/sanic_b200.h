@@ -266,6 +266,10 @@ int32_t sanic_program_run(sanic_program* prog, void* stream);
  * (MetalReplay::step_timed): gpu_seconds (optional) is the device time of this replay. */
 int32_t sanic_program_capture(sanic_program* prog, void* stream);
 int32_t sanic_program_step(sanic_program* prog, void* stream, double* gpu_seconds);
+/* One step with a device time per stage (MetalDevice::run_kernel_timed, src/metal.rs:431-447). `seconds`
+ * receives min(cap, stages) entries and *n_out their count; a program captured in its single-kernel form
+ * reports one entry per phase (argmax is two). The step is a real one: state advances. Synchronises `stream`. */
+int32_t sanic_program_stage_times(sanic_program* prog, void* stream, double* seconds, int32_t cap, int32_t* n_out);
 
 /* ── multi-device split-KV: each device folds its slice of the key axis, the carriers are
  *    exchanged and merged with the derived combine (src/interp.rs:538-554) ── */

@@ -132,6 +132,7 @@ PROTOTYPES = {
     "sanic_program_run": (i32, [vp, vp]),
     "sanic_program_capture": (i32, [vp, vp]),
     "sanic_program_step": (i32, [vp, vp, C.POINTER(C.c_double)]),
+    "sanic_program_stage_times": (i32, [vp, vp, C.POINTER(C.c_double), i32, C.POINTER(i32)]),
     "sanic_nccl_unique_id": (i32, [C.POINTER(C.c_uint8)]),
     "sanic_nccl_init": (i32, [vp, i32, i32, C.POINTER(C.c_uint8)]),
     "sanic_nccl_shutdown": (i32, [vp]),

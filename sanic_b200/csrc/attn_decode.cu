@@ -24,7 +24,7 @@ using namespace sanic::decode;
 template <int D, bool VT>
 __global__ void __launch_bounds__(128) attn_decode_kernel(sanic_decode_params p, int* counters) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
-    attn_decode_tile<D, VT>(p, counters, (int)blockIdx.x, (int)blockIdx.y, (int)blockIdx.z, smem_raw, (int)threadIdx.x, true);
+    attn_decode_tile<D, VT>(p, counters, (int)blockIdx.x, (int)blockIdx.y, (int)blockIdx.z, smem_raw, (int)threadIdx.x, true, 0);
 }
 
 // Stage 2 on its own: merge n_parts raw accumulators and project.
@@ -136,18 +136,8 @@ int32_t sanic_attn_decode_splitkv_static(sanic_ctx* ctx, const sanic_decode_para
 }
 
 static int32_t decode_validate_and_launch(sanic_ctx* ctx, const sanic_decode_params* p, void* stream) {
-    SANIC_REQUIRE(ctx, p->q && p->k && p->v && p->partials, "attn_decode: null tensor or scratch");
-    SANIC_REQUIRE(ctx, p->out || p->carrier_out, "attn_decode: no output requested");
-    SANIC_REQUIRE(ctx, p->head_dim == 64 || p->head_dim == 128, "attn_decode: head_dim must be 64 or 128");
-    SANIC_REQUIRE(ctx, p->batch > 0 && p->kv_heads > 0 && p->q_heads % p->kv_heads == 0 &&
-                  p->q_heads / p->kv_heads <= 16, "attn_decode: GQA group must divide and be <= 16");
-    SANIC_REQUIRE(ctx, p->n_splits >= 1, "attn_decode: n_splits must be >= 1");
-    SANIC_REQUIRE(ctx, p->kv_len_dev || p->kv_len >= 1, "attn_decode: empty key axis");
-    SANIC_REQUIRE(ctx, p->k_seq_stride % 8 == 0 && p->k_head_stride % 8 == 0 && p->k_batch_stride % 8 == 0 &&
-                  p->v_row_stride % 8 == 0 && p->v_head_stride % 8 == 0 && p->v_batch_stride % 8 == 0 &&
-                  ((uintptr_t)p->k % 16) == 0 && ((uintptr_t)p->v % 16) == 0 && ((uintptr_t)p->q % 4) == 0,
-                  "attn_decode: K/V rows must be 16-byte aligned");
-    SANIC_REQUIRE(ctx, p->out_dtype == SANIC_F32 || p->out_dtype == SANIC_BF16 || !p->out, "attn_decode: bad out dtype");
+    int32_t rc = host_validate(ctx, p);
+    if (rc != SANIC_OK) return rc;
     sanic_set_device(ctx);
     cudaStream_t st = (cudaStream_t)stream;
     if (p->head_dim == 128) return p->v_transposed ? launch_decode<128, true>(ctx, *p, st) : launch_decode<128, false>(ctx, *p, st);

@@ -62,11 +62,15 @@ __device__ __forceinline__ void load_tile(const sanic_decode_params& p, const ui
     }
 }
 
+// Barrier over the 128 threads of one item (named barrier `id`; id 0 in a 128-thread CTA is the CTA barrier).
+__device__ __forceinline__ void tile_sync(int id) { asm volatile("bar.sync %0, 128;" ::"r"(id) : "memory"); }
+
 // One (chunk, kv head, batch) item of the fold, executed by 128 threads (tid in [0, 128)). `smem_raw` is the
-// caller's dynamic shared memory (Cfg<D>::SMEM bytes, 128-byte aligned); `pdl` as in gemv_tile.
+// caller's dynamic shared memory (Cfg<D>::SMEM bytes, 128-byte aligned); `pdl` as in gemv_tile; `bar_id` is the
+// named barrier the 128 threads meet on.
 template <int D, bool VT>
 __device__ __forceinline__ void attn_decode_tile(const sanic_decode_params& p, int* counters, int split, int hk, int b,
-                                                 unsigned char* smem_raw, int tid, bool pdl) {
+                                                 unsigned char* smem_raw, int tid, bool pdl, int bar_id) {
     const int warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, t = lane & 3;
     const int group = p.q_heads / p.kv_heads;
@@ -87,17 +91,17 @@ __device__ __forceinline__ void attn_decode_tile(const sanic_decode_params& p, i
     const uint16_t* Vb = (const uint16_t*)p.v + (size_t)b * p.v_batch_stride + (size_t)hk * p.v_head_stride;
     const uint32_t smem_base = smem_u32(smem_raw);
 
-    // Q fragments: row r = query head hk*group + r, zero beyond the group.
+    // Q fragments (read from L2: another SM may have written q earlier in the same kernel): row r = query head hk*group + r, zero beyond the group.
     uint32_t qa[KS][2];  // [ks][0] = (a0,a1) cols 2t,2t+1 ; [ks][1] = (a4,a5) cols 8+2t,+1 ; rows g (rows g+8 via qb)
     uint32_t qb[KS][2];  // rows g+8
     {
         const uint16_t* Q = (const uint16_t*)p.q + ((size_t)b * p.q_heads + (size_t)hk * group) * D;
 #pragma unroll
         for (int ks = 0; ks < KS; ++ks) {
-            qa[ks][0] = (g < group) ? *(const uint32_t*)(Q + (size_t)g * D + ks * 16 + 2 * t) : 0u;
-            qa[ks][1] = (g < group) ? *(const uint32_t*)(Q + (size_t)g * D + ks * 16 + 8 + 2 * t) : 0u;
-            qb[ks][0] = (g + 8 < group) ? *(const uint32_t*)(Q + (size_t)(g + 8) * D + ks * 16 + 2 * t) : 0u;
-            qb[ks][1] = (g + 8 < group) ? *(const uint32_t*)(Q + (size_t)(g + 8) * D + ks * 16 + 8 + 2 * t) : 0u;
+            qa[ks][0] = (g < group) ? __ldcg((const uint32_t*)(Q + (size_t)g * D + ks * 16 + 2 * t)) : 0u;
+            qa[ks][1] = (g < group) ? __ldcg((const uint32_t*)(Q + (size_t)g * D + ks * 16 + 8 + 2 * t)) : 0u;
+            qb[ks][0] = (g + 8 < group) ? __ldcg((const uint32_t*)(Q + (size_t)(g + 8) * D + ks * 16 + 2 * t)) : 0u;
+            qb[ks][1] = (g + 8 < group) ? __ldcg((const uint32_t*)(Q + (size_t)(g + 8) * D + ks * 16 + 8 + 2 * t)) : 0u;
         }
     }
 
@@ -116,7 +120,7 @@ __device__ __forceinline__ void attn_decode_tile(const sanic_decode_params& p, i
 
     for (int it = 0; it < n_tiles; ++it) {
         cp_async_wait<STAGES - 2>();
-        __syncthreads();
+        tile_sync(bar_id);
         {   // prefetch tile it + STAGES - 1 into the stage consumed at iteration it - 1
             int nx = it + STAGES - 1;
             if (nx < n_tiles)
@@ -200,7 +204,7 @@ __device__ __forceinline__ void attn_decode_tile(const sanic_decode_params& p, i
         }
     }
     cp_async_wait<0>();
-    __syncthreads();  // every warp is done with the tile ring: reuse it for the warp merge
+    tile_sync(bar_id);  // every warp is done with the tile ring: reuse it for the warp merge
 
     l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 1); l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
@@ -216,7 +220,7 @@ __device__ __forceinline__ void attn_decode_tile(const sanic_decode_params& p, i
             w1[2 + 8 * i + 2 * t] = o[i][2]; w1[2 + 8 * i + 2 * t + 1] = o[i][3];
         }
     }
-    __syncthreads();
+    tile_sync(bar_id);
     // merge the 4 warp carriers (left to right) and write this chunk's partial
     const int W = D + 2;
     for (int idx = tid; idx < group * D; idx += 128) {
@@ -237,13 +241,13 @@ __device__ __forceinline__ void attn_decode_tile(const sanic_decode_params& p, i
     // stage 2 by the last CTA of this (batch, kv head)
     __shared__ int s_last;
     __threadfence();
-    __syncthreads();
+    tile_sync(bar_id);
     if (tid == 0) {
         int ticket = atomicAdd(&counters[b * p.kv_heads + hk], 1);
         s_last = (ticket == p.n_splits - 1);
         if (s_last) counters[b * p.kv_heads + hk] = 0;  // ready for the next launch
     }
-    __syncthreads();
+    tile_sync(bar_id);
     if (!s_last) return;
     __threadfence();
     for (int idx = tid; idx < group * D; idx += 128) {
@@ -281,6 +285,22 @@ __device__ __forceinline__ void attn_decode_tile(const sanic_decode_params& p, i
     }
 }
 
+// Host side: the argument checks of one split-KV fold.
+inline int32_t host_validate(sanic_ctx* ctx, const sanic_decode_params* p) {
+    SANIC_REQUIRE(ctx, p->q && p->k && p->v && p->partials, "attn_decode: null tensor or scratch");
+    SANIC_REQUIRE(ctx, p->out || p->carrier_out, "attn_decode: no output requested");
+    SANIC_REQUIRE(ctx, p->head_dim == 64 || p->head_dim == 128, "attn_decode: head_dim must be 64 or 128");
+    SANIC_REQUIRE(ctx, p->batch > 0 && p->kv_heads > 0 && p->q_heads % p->kv_heads == 0 &&
+                  p->q_heads / p->kv_heads <= 16, "attn_decode: GQA group must divide and be <= 16");
+    SANIC_REQUIRE(ctx, p->n_splits >= 1, "attn_decode: n_splits must be >= 1");
+    SANIC_REQUIRE(ctx, p->kv_len_dev || p->kv_len >= 1, "attn_decode: empty key axis");
+    SANIC_REQUIRE(ctx, p->k_seq_stride % 8 == 0 && p->k_head_stride % 8 == 0 && p->k_batch_stride % 8 == 0 &&
+                  p->v_row_stride % 8 == 0 && p->v_head_stride % 8 == 0 && p->v_batch_stride % 8 == 0 &&
+                  ((uintptr_t)p->k % 16) == 0 && ((uintptr_t)p->v % 16) == 0 && ((uintptr_t)p->q % 4) == 0,
+                  "attn_decode: K/V rows must be 16-byte aligned");
+    SANIC_REQUIRE(ctx, p->out_dtype == SANIC_F32 || p->out_dtype == SANIC_BF16 || !p->out, "attn_decode: bad out dtype");
+    return SANIC_OK;
+}
 
 }  // namespace decode
 }  // namespace sanic

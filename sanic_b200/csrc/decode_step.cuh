@@ -1,0 +1,23 @@
+// One decode step as ONE persistent kernel: the stage list of a program becomes a phase table that a
+// co-resident grid walks, with a grid-wide barrier between phases instead of a kernel boundary.
+#pragma once
+#include <vector>
+
+#include "common.cuh"
+
+namespace sanic {
+namespace step {
+
+struct Plan;
+
+// Builds the phase table for `stages`. Returns SANIC_ERR_UNSUPPORTED (and leaves *out null) when the list
+// holds a stage the persistent kernel does not implement; the caller then keeps its launch list.
+int32_t build(sanic_ctx* ctx, const std::vector<sanic_stage_desc>& stages, Plan** out);
+// Enqueues one step: a 4-byte clear of the barrier word, then the cooperative launch.
+int32_t launch(sanic_ctx* ctx, Plan* plan, cudaStream_t stream);
+int phases(const Plan* plan);
+int32_t phase_times(sanic_ctx* ctx, Plan* plan, double* seconds, int cap);
+void destroy(Plan* plan);
+
+}  // namespace step
+}  // namespace sanic

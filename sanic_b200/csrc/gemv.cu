@@ -39,7 +39,8 @@ template <bool W4, int NT, bool DUAL, bool NORM>
 __global__ void __launch_bounds__(GW * 32, 2) gemv_mma_kernel(const uint16_t* __restrict__ x, int batch, int K,
                                                            SegTable segs, int n_segments, int out_dtype, int epilogue,
                                                            const float* residual, Fused fz, int KS) {
-    gemv_tile<W4, NT, DUAL, NORM>(x, batch, K, segs, n_segments, out_dtype, epilogue, residual, fz, KS, (int)blockIdx.x, true);
+    __shared__ float scratch[scratch_floats<NT, DUAL>()];
+    gemv_tile<W4, NT, DUAL, NORM>(x, batch, K, segs, n_segments, out_dtype, epilogue, residual, fz, KS, (int)blockIdx.x, true, scratch);
 }
 
 template <bool W4, int NT, bool DUAL, bool NORM>
@@ -71,47 +72,12 @@ int32_t launch_n(sanic_ctx* ctx, const sanic_gemv_params& p, const SegTable& seg
 
 extern "C" int32_t sanic_gemv(sanic_ctx* ctx, const sanic_gemv_params* p, void* stream) {
     if (!ctx || !p) return SANIC_ERR_INVALID;
-    SANIC_REQUIRE(ctx, (p->x || p->norm_x) && p->batch >= 1 && p->batch <= 16, "gemv: batch must be in [1, 16]");
-    SANIC_REQUIRE(ctx, p->K >= 64 && p->K % 64 == 0, "gemv: K must be a multiple of 64");
-    SANIC_REQUIRE(ctx, p->n_segments >= 1 && p->n_segments <= 3, "gemv: 1..3 weight segments");
-    if (p->weight_dtype != SANIC_BF16 && p->weight_dtype != SANIC_I4)
-        return sanic_fail(ctx, SANIC_ERR_DTYPE, "gemv: weights must be bf16 or int4");
-    SANIC_REQUIRE(ctx, p->weight_dtype != SANIC_I4 || p->group == 64, "gemv: int4 group size must be 64");
-    SANIC_REQUIRE(ctx, p->out_dtype == SANIC_F32 || p->out_dtype == SANIC_BF16, "gemv: output must be f32 or bf16");
-    SANIC_REQUIRE(ctx, ((uintptr_t)p->x % 16) == 0 && ((uintptr_t)p->norm_x % 16) == 0 && ((uintptr_t)p->norm_gamma % 16) == 0,
-                  "gemv: activations must be 16-byte aligned");
-    SANIC_REQUIRE(ctx, !p->norm_x || p->norm_gamma, "gemv: an inlined norm needs its weight");
-    const bool dual = p->epilogue == SANIC_EPI_SILU_MUL;
-    const bool rope = p->epilogue == SANIC_EPI_ROPE_CACHE;
-    SANIC_REQUIRE(ctx, !dual || (p->n_segments == 2 && p->rows[0] == p->rows[1]), "gemv: silu-mul needs two equal segments");
-    SANIC_REQUIRE(ctx, p->epilogue != SANIC_EPI_RESIDUAL_ADD || (p->residual && p->n_segments == 1),
-                  "gemv: residual-add needs one segment and a residual");
-    if (rope) {
-        SANIC_REQUIRE(ctx, p->n_segments == 3 && p->rope_table && p->rope_position && p->rope_q_out && p->rope_k_cache &&
-                      p->rope_v_cache, "gemv: the rope-cache epilogue needs q, k, v segments and its buffers");
-        SANIC_REQUIRE(ctx, (p->rope_head_dim == 64 || p->rope_head_dim == 128) && p->rope_ctx > 0 &&
-                      p->rows[0] == p->rope_q_heads * p->rope_head_dim && p->rows[1] == p->rope_kv_heads * p->rope_head_dim &&
-                      p->rows[2] == p->rows[1], "gemv: rope-cache segment rows must be heads * head_dim");
-    }
-    SegTable segs{};
+    SegTable segs;
+    Fused fz;
     int tiles = 0;
-    for (int i = 0; i < p->n_segments; ++i) {
-        SANIC_REQUIRE(ctx, p->w[i] && p->rows[i] > 0 && p->rows[i] % 16 == 0,
-                      "gemv: segment rows must be a positive multiple of 16");
-        SANIC_REQUIRE(ctx, p->out[i] || (dual && i == 1) || rope, "gemv: null output");
-        SANIC_REQUIRE(ctx, ((uintptr_t)p->w[i] % 16) == 0, "gemv: weights must be 16-byte aligned");
-        SANIC_REQUIRE(ctx, p->weight_dtype != SANIC_I4 || p->scales[i], "gemv: int4 weights need scales");
-        segs.w[i] = p->w[i];
-        segs.scales[i] = (const uint16_t*)p->scales[i];
-        segs.out[i] = p->out[i];
-        segs.rows[i] = p->rows[i];
-        segs.tile_begin[i] = tiles;
-        if (!dual || i == 0) tiles += p->rows[i] / 16;
-    }
-    for (int i = p->n_segments; i < 4; ++i) segs.tile_begin[i] = tiles;
-    Fused fz{p->norm_x, (const uint16_t*)p->norm_gamma, p->norm_eps, p->rope_table, p->rope_position,
-             (uint16_t*)p->rope_q_out, (uint16_t*)p->rope_k_cache, (uint16_t*)p->rope_v_cache,
-             p->rope_q_heads, p->rope_kv_heads, p->rope_head_dim, p->rope_ctx};
+    int32_t rc = host_prepare(ctx, p, segs, fz, tiles);
+    if (rc != SANIC_OK) return rc;
+    const bool dual = p->epilogue == SANIC_EPI_SILU_MUL;
     sanic_set_device(ctx);
     cudaStream_t st = (cudaStream_t)stream;
     const bool w4 = p->weight_dtype == SANIC_I4;

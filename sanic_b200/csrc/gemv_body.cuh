@@ -34,12 +34,16 @@ __device__ __forceinline__ uint32_t nib_pair(uint32_t w) {  // (w & 0x000F000F) 
 __device__ __forceinline__ const void* pick3(const void* const (&a)[3], int i) { return i == 0 ? a[0] : (i == 1 ? a[1] : a[2]); }
 
 // 8 consecutive activations of batch column n starting at k as four packed bf16x2 registers.
-template <bool NORM>
+// L2READ: the activations may have been written by another SM earlier in the same kernel (the persistent
+// decode step), so they are read from L2; a stand-alone kernel reads them through L1, where every tile
+// after the first on an SM hits.
+template <bool NORM, bool L2READ>
 __device__ __forceinline__ uint4 load_x8(const uint16_t* xrow, const float* xf, const uint16_t* gamma, float den, int k,
                                          bool ok) {
     if (!ok) return make_uint4(0, 0, 0, 0);
-    if (!NORM) return __ldg((const uint4*)(xrow + k));
-    float4 a = __ldg((const float4*)(xf + k)), b = __ldg((const float4*)(xf + k + 4));
+    if (!NORM) return L2READ ? __ldcg((const uint4*)(xrow + k)) : __ldg((const uint4*)(xrow + k));
+    float4 a = L2READ ? __ldcg((const float4*)(xf + k)) : __ldg((const float4*)(xf + k));
+    float4 b = L2READ ? __ldcg((const float4*)(xf + k + 4)) : __ldg((const float4*)(xf + k + 4));
     uint4 g = __ldg((const uint4*)(gamma + k));
     uint4 r;
     // `den` holds 1/sqrt(mean(x^2)+eps): one multiply per element instead of a division
@@ -50,13 +54,55 @@ __device__ __forceinline__ uint4 load_x8(const uint16_t* xrow, const float* xf, 
     return r;
 }
 
+// 1/sqrt(mean(x^2) + eps) of every activation row into scratch[0..batch): every warp sums its eighth of each
+// row, so the norm costs one load round trip, not sixteen. All GW*32 threads of the block call this.
+template <bool L2READ>
+__device__ __forceinline__ void row_norms(const Fused& fz, int batch, int K, float* scratch) {
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    float* s_den = scratch;
+    float (*s_part)[GW] = reinterpret_cast<float (*)[GW]>(scratch + 16);
+    const int kw = K / GW;
+    for (int n = 0; n < batch; ++n) {
+        const float* xr = fz.norm_x + (size_t)n * K + warp * kw;
+        float ss = 0.0f;
+        for (int i = lane * 4; i < kw; i += 128) {
+            float4 v = L2READ ? __ldcg((const float4*)(xr + i)) : __ldg((const float4*)(xr + i));
+            ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
+        }
+        ss = warp_sum(ss);
+        if (lane == 0) s_part[n][warp] = ss;
+    }
+    __syncthreads();
+    if (tid < batch) {
+        float tot = 0.0f;
+#pragma unroll
+        for (int w = 0; w < GW; ++w) tot += s_part[tid][w];
+        s_den[tid] = 1.0f / sqrtf(tot * (1.0f / (float)K) + fz.norm_eps);
+    }
+    __syncthreads();
+}
+
+// Shared scratch one tile needs, in floats: row norms [16], their per-warp parts [16][GW], the per-warp
+// accumulators [GW][NM][16][8*NT+1] and the block sum [NM][16][8*NT+1].
+template <int NT, bool DUAL>
+__host__ __device__ constexpr int scratch_floats() {
+    return 16 + 16 * GW + (GW + 1) * (DUAL ? 2 : 1) * 16 * (8 * NT + 1);
+}
+
 // One row tile of the contraction. `block` is the linear block index (tile * KS + K-rank); `pdl` says
 // whether the caller is a stand-alone kernel that must order itself after its stream predecessor.
-template <bool W4, int NT, bool DUAL, bool NORM>
+// PERSIST is the form the persistent decode step calls: activations (and the residual) are read from L2
+// and the row norms are already in scratch[0..batch), computed once per phase by the caller.
+template <bool W4, int NT, bool DUAL, bool NORM, bool PERSIST = false>
 __device__ __forceinline__ void gemv_tile(const uint16_t* __restrict__ x, int batch, int K, const SegTable& segs,
                                           int n_segments, int out_dtype, int epilogue, const float* residual,
-                                          const Fused& fz, int KS, int block, bool pdl) {
+                                          const Fused& fz, int KS, int block, bool pdl, float* scratch) {
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    // carve the caller's shared scratch (scratch_floats<NT, DUAL>() floats)
+    constexpr int NMs = DUAL ? 2 : 1, RW = 8 * NT + 1;
+    float* s_den = scratch;                                                                                  // [16]
+    float (*red)[NMs][16][RW] = reinterpret_cast<float (*)[NMs][16][RW]>(scratch + 16 + 16 * GW);            // [GW][NM][16][RW]
+    float (*csum)[16][RW] = reinterpret_cast<float (*)[16][RW]>(scratch + 16 + 16 * GW + GW * NMs * 16 * RW);  // [NM][16][RW]
     const int g = lane >> 2, t = lane & 3;
     // KS CTAs of one thread-block cluster share a row tile and split K between them
     const int gtile = block / KS, krank = block % KS;
@@ -102,30 +148,7 @@ __device__ __forceinline__ void gemv_tile(const uint16_t* __restrict__ x, int ba
     }
     if (pdl) { griddep_launch(); griddep_wait(); }
 
-    __shared__ float s_den[16];
-    __shared__ float s_part[16][GW];
-    if (NORM) {
-        // every warp sums its eighth of each row, so the norm costs one load round trip, not sixteen
-        const int kw = K / GW;
-        for (int n = 0; n < batch; ++n) {
-            const float* xr = fz.norm_x + (size_t)n * K + warp * kw;
-            float ss = 0.0f;
-            for (int i = lane * 4; i < kw; i += 128) {
-                float4 v = __ldg((const float4*)(xr + i));
-                ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
-            }
-            ss = warp_sum(ss);
-            if (lane == 0) s_part[n][warp] = ss;
-        }
-        __syncthreads();
-        if (tid < batch) {
-            float tot = 0.0f;
-#pragma unroll
-            for (int w = 0; w < GW; ++w) tot += s_part[tid][w];
-            s_den[tid] = 1.0f / sqrtf(tot * (1.0f / (float)K) + fz.norm_eps);
-        }
-        __syncthreads();
-    }
+    if (NORM && !PERSIST) row_norms<false>(fz, batch, K, scratch);
 
     float acc[NM][NT][4];
 #pragma unroll
@@ -179,8 +202,8 @@ __device__ __forceinline__ void gemv_tile(const uint16_t* __restrict__ x, int ba
                     int kb = (blk + u) * 64;
 #pragma unroll
                     for (int j = 0; j < NT; ++j) {
-                        xb[u][j][0] = load_x8<NORM>(xrow[j], xf[j], gam, den[j], kb + t * 8, xok[j]);
-                        xb[u][j][1] = load_x8<NORM>(xrow[j], xf[j], gam, den[j], kb + 32 + t * 8, xok[j]);
+                        xb[u][j][0] = load_x8<NORM, PERSIST>(xrow[j], xf[j], gam, den[j], kb + t * 8, xok[j]);
+                        xb[u][j][1] = load_x8<NORM, PERSIST>(xrow[j], xf[j], gam, den[j], kb + 32 + t * 8, xok[j]);
                     }
                 }
             }
@@ -222,8 +245,8 @@ __device__ __forceinline__ void gemv_tile(const uint16_t* __restrict__ x, int ba
             int kb = blk * 64 + t * 16;
 #pragma unroll
             for (int j = 0; j < NT; ++j) {
-                uint4 xa = load_x8<NORM>(xrow[j], xf[j], gam, den[j], kb, xok[j]);
-                uint4 xc = load_x8<NORM>(xrow[j], xf[j], gam, den[j], kb + 8, xok[j]);
+                uint4 xa = load_x8<NORM, PERSIST>(xrow[j], xf[j], gam, den[j], kb, xok[j]);
+                uint4 xc = load_x8<NORM, PERSIST>(xrow[j], xf[j], gam, den[j], kb + 8, xok[j]);
                 // activation pairs matching the nibble pairing (n_i, n_{i+4})
                 uint32_t bA0 = prmt(xa.x, xa.z, 0x5410), bA1 = prmt(xa.x, xa.z, 0x7632);
                 uint32_t bA2 = prmt(xa.y, xa.w, 0x5410), bA3 = prmt(xa.y, xa.w, 0x7632);
@@ -272,7 +295,6 @@ __device__ __forceinline__ void gemv_tile(const uint16_t* __restrict__ x, int ba
     }
 
     // deterministic cross-warp sum: red[warp][matrix][row 0..15][col 0..8*NT)
-    __shared__ float red[GW][NM][16][8 * NT + 1];
 #pragma unroll
     for (int mI = 0; mI < NM; ++mI)
 #pragma unroll
@@ -285,7 +307,6 @@ __device__ __forceinline__ void gemv_tile(const uint16_t* __restrict__ x, int ba
     __syncthreads();
     // CTA sum in a fixed warp order, then (KS > 1) the cluster's CTAs are summed in rank order by
     // rank 0 through distributed shared memory: deterministic, no global scratch.
-    __shared__ float csum[NM][16][8 * NT + 1];
     for (int idx = tid; idx < NM * 16 * 8 * NT; idx += GW * 32) {
         const int n = idx % (8 * NT), r = (idx / (8 * NT)) % 16, mI = idx / (8 * NT * 16);
         float sv = 0.0f;
@@ -358,12 +379,58 @@ __device__ __forceinline__ void gemv_tile(const uint16_t* __restrict__ x, int ba
             y = (ga * sig) * up;
         }
         size_t oi = (size_t)n * rows + row0 + r;
-        if (epilogue == SANIC_EPI_RESIDUAL_ADD) y = residual[oi] + y;
+        if (epilogue == SANIC_EPI_RESIDUAL_ADD) y = (PERSIST ? __ldcg(residual + oi) : residual[oi]) + y;
         if (out_dtype == SANIC_BF16) ((uint16_t*)outp)[oi] = f32_to_bf16_bits(y);
         else ((float*)outp)[oi] = y;
     }
 }
 
+// Host side: validate one contraction and build the kernel's segment table. `tiles` is the number of
+// 16-row tiles (one thread block each, before any K split).
+inline int32_t host_prepare(sanic_ctx* ctx, const sanic_gemv_params* p, SegTable& segs, Fused& fz, int& tiles) {
+    SANIC_REQUIRE(ctx, (p->x || p->norm_x) && p->batch >= 1 && p->batch <= 16, "gemv: batch must be in [1, 16]");
+    SANIC_REQUIRE(ctx, p->K >= 64 && p->K % 64 == 0, "gemv: K must be a multiple of 64");
+    SANIC_REQUIRE(ctx, p->n_segments >= 1 && p->n_segments <= 3, "gemv: 1..3 weight segments");
+    if (p->weight_dtype != SANIC_BF16 && p->weight_dtype != SANIC_I4)
+        return sanic_fail(ctx, SANIC_ERR_DTYPE, "gemv: weights must be bf16 or int4");
+    SANIC_REQUIRE(ctx, p->weight_dtype != SANIC_I4 || p->group == 64, "gemv: int4 group size must be 64");
+    SANIC_REQUIRE(ctx, p->out_dtype == SANIC_F32 || p->out_dtype == SANIC_BF16, "gemv: output must be f32 or bf16");
+    SANIC_REQUIRE(ctx, ((uintptr_t)p->x % 16) == 0 && ((uintptr_t)p->norm_x % 16) == 0 && ((uintptr_t)p->norm_gamma % 16) == 0,
+                  "gemv: activations must be 16-byte aligned");
+    SANIC_REQUIRE(ctx, !p->norm_x || p->norm_gamma, "gemv: an inlined norm needs its weight");
+    const bool dual = p->epilogue == SANIC_EPI_SILU_MUL;
+    const bool rope = p->epilogue == SANIC_EPI_ROPE_CACHE;
+    SANIC_REQUIRE(ctx, !dual || (p->n_segments == 2 && p->rows[0] == p->rows[1]), "gemv: silu-mul needs two equal segments");
+    SANIC_REQUIRE(ctx, p->epilogue != SANIC_EPI_RESIDUAL_ADD || (p->residual && p->n_segments == 1),
+                  "gemv: residual-add needs one segment and a residual");
+    if (rope) {
+        SANIC_REQUIRE(ctx, p->n_segments == 3 && p->rope_table && p->rope_position && p->rope_q_out && p->rope_k_cache &&
+                      p->rope_v_cache, "gemv: the rope-cache epilogue needs q, k, v segments and its buffers");
+        SANIC_REQUIRE(ctx, (p->rope_head_dim == 64 || p->rope_head_dim == 128) && p->rope_ctx > 0 &&
+                      p->rows[0] == p->rope_q_heads * p->rope_head_dim && p->rows[1] == p->rope_kv_heads * p->rope_head_dim &&
+                      p->rows[2] == p->rows[1], "gemv: rope-cache segment rows must be heads * head_dim");
+    }
+    segs = SegTable{};
+    tiles = 0;
+    for (int i = 0; i < p->n_segments; ++i) {
+        SANIC_REQUIRE(ctx, p->w[i] && p->rows[i] > 0 && p->rows[i] % 16 == 0,
+                      "gemv: segment rows must be a positive multiple of 16");
+        SANIC_REQUIRE(ctx, p->out[i] || (dual && i == 1) || rope, "gemv: null output");
+        SANIC_REQUIRE(ctx, ((uintptr_t)p->w[i] % 16) == 0, "gemv: weights must be 16-byte aligned");
+        SANIC_REQUIRE(ctx, p->weight_dtype != SANIC_I4 || p->scales[i], "gemv: int4 weights need scales");
+        segs.w[i] = p->w[i];
+        segs.scales[i] = (const uint16_t*)p->scales[i];
+        segs.out[i] = p->out[i];
+        segs.rows[i] = p->rows[i];
+        segs.tile_begin[i] = tiles;
+        if (!dual || i == 0) tiles += p->rows[i] / 16;
+    }
+    for (int i = p->n_segments; i < 4; ++i) segs.tile_begin[i] = tiles;
+    fz = Fused{p->norm_x, (const uint16_t*)p->norm_gamma, p->norm_eps, p->rope_table, p->rope_position,
+               (uint16_t*)p->rope_q_out, (uint16_t*)p->rope_k_cache, (uint16_t*)p->rope_v_cache,
+               p->rope_q_heads, p->rope_kv_heads, p->rope_head_dim, p->rope_ctx};
+    return SANIC_OK;
+}
 
 }  // namespace gemv
 }  // namespace sanic

@@ -11,6 +11,7 @@
 #include <vector>
 
 #include "common.cuh"
+#include "decode_step.cuh"
 
 struct sanic_program {
     sanic_ctx* ctx = nullptr;
@@ -18,7 +19,9 @@ struct sanic_program {
     cudaGraph_t graph = nullptr;
     cudaGraphExec_t exec = nullptr;
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;
-    int kernels = 0;
+    int kernels = 0;          // kernels one run of the launch list starts
+    int step_kernels = 0;     // kernels one replay of the captured step starts
+    sanic::step::Plan* plan = nullptr;   // the persistent single-kernel form of the step, when the list allows it
 };
 
 namespace {
@@ -94,11 +97,12 @@ int32_t sanic_program_destroy(sanic_program* p) {
     if (p->graph) cudaGraphDestroy(p->graph);
     if (p->ev0) cudaEventDestroy(p->ev0);
     if (p->ev1) cudaEventDestroy(p->ev1);
+    sanic::step::destroy(p->plan);
     delete p;
     return SANIC_OK;
 }
 
-int32_t sanic_program_kernel_count(sanic_program* p) { return p ? p->kernels : -1; }
+int32_t sanic_program_kernel_count(sanic_program* p) { return p ? (p->exec ? p->step_kernels : p->kernels) : -1; }
 
 int32_t sanic_program_run(sanic_program* p, void* stream) {
     if (!p) return SANIC_ERR_INVALID;
@@ -117,8 +121,17 @@ int32_t sanic_program_capture(sanic_program* p, void* stream) {
     cudaStream_t st = (cudaStream_t)stream;
     if (p->exec) { cudaGraphExecDestroy(p->exec); p->exec = nullptr; }
     if (p->graph) { cudaGraphDestroy(p->graph); p->graph = nullptr; }
+    // SANIC_PERSISTENT_STEP=1 lowers the whole list into one cooperative kernel (decode_step.cu) when every
+    // stage has a phase there; otherwise, and by default, the replay is the launch list itself.
+    static const bool want_persistent = getenv("SANIC_PERSISTENT_STEP") && atoi(getenv("SANIC_PERSISTENT_STEP")) != 0;
+    if (p->plan) { sanic::step::destroy(p->plan); p->plan = nullptr; }
+    if (want_persistent) {
+        int32_t brc = sanic::step::build(ctx, p->stages, &p->plan);
+        if (brc != SANIC_OK && brc != SANIC_ERR_UNSUPPORTED) return brc;
+    }
     SANIC_CUDA_CHECK(ctx, cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal));
-    int32_t rc = sanic_program_run(p, stream);
+    int32_t rc = p->plan ? sanic::step::launch(ctx, p->plan, st) : sanic_program_run(p, stream);
+    p->step_kernels = p->plan ? 1 : p->kernels;
     cudaGraph_t g = nullptr;
     cudaError_t e = cudaStreamEndCapture(st, &g);
     if (rc != SANIC_OK) { if (g) cudaGraphDestroy(g); return rc; }
@@ -150,6 +163,44 @@ int32_t sanic_program_step(sanic_program* p, void* stream, double* gpu_seconds) 
         *gpu_seconds = (double)ms * 1e-3;
     }
     return SANIC_OK;
+}
+
+// One step with a device time per stage (reference MetalDevice::run_kernel_timed, src/metal.rs:431-447: per-kernel
+// times measured inside the one submission). A program captured in its persistent form reports the clock stamps
+// its kernel takes at every phase boundary (argmax counts as two phases); otherwise the stages run from the launch
+// list with an event between them. The step is a real one: state advances.
+int32_t sanic_program_stage_times(sanic_program* p, void* stream, double* seconds, int32_t cap, int32_t* n_out) {
+    if (!p || !seconds || !n_out || cap < 0) return SANIC_ERR_INVALID;
+    sanic_ctx* ctx = p->ctx;
+    sanic_set_device(ctx);
+    cudaStream_t st = (cudaStream_t)stream;
+    if (p->exec && p->plan) {
+        SANIC_CUDA_CHECK(ctx, cudaGraphLaunch(p->exec, st));
+        SANIC_CUDA_CHECK(ctx, cudaStreamSynchronize(st));
+        *n_out = sanic::step::phase_times(ctx, p->plan, seconds, cap);
+        return SANIC_OK;
+    }
+    const int n = (int)p->stages.size();
+    std::vector<cudaEvent_t> ev(n + 1, nullptr);
+    int32_t rc = SANIC_OK;
+    for (int i = 0; i <= n && rc == SANIC_OK; ++i)
+        if (cudaEventCreate(&ev[i]) != cudaSuccess) rc = sanic_fail(ctx, SANIC_ERR_CUDA, "program_stage_times: cannot create events");
+    if (rc == SANIC_OK && cudaEventRecord(ev[0], st) != cudaSuccess) rc = sanic_fail(ctx, SANIC_ERR_CUDA, "program_stage_times: event record failed");
+    for (int i = 0; i < n && rc == SANIC_OK; ++i) {
+        rc = run_stage(ctx, p->stages[i], stream);
+        if (rc == SANIC_OK && cudaEventRecord(ev[i + 1], st) != cudaSuccess) rc = sanic_fail(ctx, SANIC_ERR_CUDA, "program_stage_times: event record failed");
+    }
+    if (rc == SANIC_OK && cudaStreamSynchronize(st) != cudaSuccess) rc = sanic_fail(ctx, SANIC_ERR_CUDA, "program_stage_times: the step failed");
+    if (rc == SANIC_OK) {
+        *n_out = std::min<int32_t>(cap, n);
+        for (int i = 0; i < *n_out; ++i) {
+            float ms = 0.0f;
+            cudaEventElapsedTime(&ms, ev[i], ev[i + 1]);
+            seconds[i] = (double)ms * 1e-3;
+        }
+    }
+    for (cudaEvent_t e : ev) if (e) cudaEventDestroy(e);
+    return rc;
 }
 
 }  // extern "C"

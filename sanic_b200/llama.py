@@ -259,6 +259,15 @@ class LlamaMachine:
         self.dev._check(self.dev.lib.sanic_program_run(self.prog, st), "program_run")
         return None
 
+    def step_stage_times(self):
+        """One decode step with a device time per stage (MetalDevice::run_kernel_timed): list of seconds."""
+        st = C.c_void_p(self.stream.cuda_stream)
+        cap = 4 * self.n_stages + 8
+        buf = (C.c_double * cap)()
+        n = C.c_int32(0)
+        self.dev._check(self.dev.lib.sanic_program_stage_times(self.prog, st, buf, cap, C.byref(n)), "program_stage_times")
+        return [buf[i] for i in range(n.value)]
+
     def sync(self):
         self.stream.synchronize()
 
