@@ -265,6 +265,11 @@ int32_t sanic_program_run(sanic_program* prog, void* stream);
 /* Freeze the launch list into a CUDA graph (MetalDevice::capture) and replay it
  * (MetalReplay::step_timed): gpu_seconds (optional) is the device time of this replay. */
 int32_t sanic_program_capture(sanic_program* prog, void* stream);
+/* The same, lowered into one cooperative kernel that walks the stage list with grid-wide barriers instead of
+ * kernel boundaries (no counterpart in the reference: Metal has one command buffer per step,
+ * src/metal.rs:634-705, but no device-wide barrier inside a dispatch). SANIC_ERR_UNSUPPORTED when a stage
+ * has no phase in that kernel (RoPE as its own stage, head_dim 128, an inlined norm at batch > 8). */
+int32_t sanic_program_capture_persistent(sanic_program* prog, void* stream);
 int32_t sanic_program_step(sanic_program* prog, void* stream, double* gpu_seconds);
 /* One step with a device time per stage (MetalDevice::run_kernel_timed, src/metal.rs:431-447). `seconds`
  * receives min(cap, stages) entries and *n_out their count; a program captured in its single-kernel form

@@ -131,6 +131,7 @@ PROTOTYPES = {
     "sanic_program_kernel_count": (i32, [vp]),
     "sanic_program_run": (i32, [vp, vp]),
     "sanic_program_capture": (i32, [vp, vp]),
+    "sanic_program_capture_persistent": (i32, [vp, vp]),
     "sanic_program_step": (i32, [vp, vp, C.POINTER(C.c_double)]),
     "sanic_program_stage_times": (i32, [vp, vp, C.POINTER(C.c_double), i32, C.POINTER(i32)]),
     "sanic_nccl_unique_id": (i32, [C.POINTER(C.c_uint8)]),

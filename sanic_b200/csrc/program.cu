@@ -113,21 +113,19 @@ int32_t sanic_program_run(sanic_program* p, void* stream) {
     return SANIC_OK;
 }
 
-int32_t sanic_program_capture(sanic_program* p, void* stream) {
-    if (!p) return SANIC_ERR_INVALID;
+static int32_t capture_impl(sanic_program* p, void* stream, bool want_persistent) {
     sanic_ctx* ctx = p->ctx;
     SANIC_REQUIRE(ctx, stream != nullptr, "program_capture: needs a non-default stream");
     sanic_set_device(ctx);
     cudaStream_t st = (cudaStream_t)stream;
     if (p->exec) { cudaGraphExecDestroy(p->exec); p->exec = nullptr; }
     if (p->graph) { cudaGraphDestroy(p->graph); p->graph = nullptr; }
-    // SANIC_PERSISTENT_STEP=1 lowers the whole list into one cooperative kernel (decode_step.cu) when every
-    // stage has a phase there; otherwise, and by default, the replay is the launch list itself.
-    static const bool want_persistent = getenv("SANIC_PERSISTENT_STEP") && atoi(getenv("SANIC_PERSISTENT_STEP")) != 0;
     if (p->plan) { sanic::step::destroy(p->plan); p->plan = nullptr; }
     if (want_persistent) {
         int32_t brc = sanic::step::build(ctx, p->stages, &p->plan);
-        if (brc != SANIC_OK && brc != SANIC_ERR_UNSUPPORTED) return brc;
+        if (brc != SANIC_OK) return brc == SANIC_ERR_UNSUPPORTED
+                                        ? sanic_fail(ctx, brc, "program_capture_persistent: a stage of this list has no phase in the persistent kernel")
+                                        : brc;
     }
     SANIC_CUDA_CHECK(ctx, cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal));
     int32_t rc = p->plan ? sanic::step::launch(ctx, p->plan, st) : sanic_program_run(p, stream);
@@ -143,6 +141,17 @@ int32_t sanic_program_capture(sanic_program* p, void* stream) {
         SANIC_CUDA_CHECK(ctx, cudaEventCreate(&p->ev1));
     }
     return SANIC_OK;
+}
+
+int32_t sanic_program_capture(sanic_program* p, void* stream) {
+    if (!p) return SANIC_ERR_INVALID;
+    return capture_impl(p, stream, false);
+}
+
+// The same replay as ONE cooperative kernel that walks the stage list with grid-wide barriers (decode_step.cu).
+int32_t sanic_program_capture_persistent(sanic_program* p, void* stream) {
+    if (!p) return SANIC_ERR_INVALID;
+    return capture_impl(p, stream, true);
 }
 
 // A replay whose launch fails returns an error: the step's writes are untrustworthy and a

@@ -98,7 +98,7 @@ class LlamaMachine:
     """The instantiated step program: owns state buffers, replays one captured graph per step."""
 
     def __init__(self, dev: CudaDevice, cfg: dict, weights: dict, ctx: int, batch: int, w4: bool = False,
-                 capture: bool = True, fused: bool = True):
+                 capture: bool = True, fused: bool = True, persistent: bool = False):
         self.dev, self.cfg, self.ctx, self.batch, self.w4, self.fused = dev, dict(cfg), ctx, batch, w4, fused
         H, F, V, L = cfg["hidden"], cfg["ffn"], cfg["vocab"], cfg["layers"]
         Hq, Hkv, D = cfg["q_heads"], cfg["kv_heads"], cfg["head_dim"]
@@ -135,6 +135,7 @@ class LlamaMachine:
         self.stream = torch.cuda.Stream(device=td)
         self._build()
         self.captured = False
+        self.persistent = persistent
         if capture:
             self.capture()
 
@@ -236,9 +237,11 @@ class LlamaMachine:
 
     def capture(self):
         torch.cuda.synchronize(self.dev.torch_device)
-        rc = self.dev.lib.sanic_program_capture(self.prog, C.c_void_p(self.stream.cuda_stream))
+        fn = self.dev.lib.sanic_program_capture_persistent if self.persistent else self.dev.lib.sanic_program_capture
+        rc = fn(self.prog, C.c_void_p(self.stream.cuda_stream))
         self.dev._check(rc, "program_capture")
         self.captured = True
+        self.kernel_count = int(self.dev.lib.sanic_program_kernel_count(self.prog))   # kernels one replay starts
 
     # ── Machine::step ──
     def set_state(self, tokens, position: int):

@@ -23,10 +23,10 @@ def dev():
     return CudaDevice(0)
 
 
-def run_pair(dev, cfg, ctx, batch, w4, steps, prefill, seed=5, fused=True):
+def run_pair(dev, cfg, ctx, batch, w4, steps, prefill, seed=5, fused=True, persistent=False):
     from sanic_b200 import llama
     w = llama.random_weights(cfg, seed, dev.torch_device, w4=w4)
-    m = llama.LlamaMachine(dev, cfg, w, ctx=ctx, batch=batch, w4=w4, fused=fused)
+    m = llama.LlamaMachine(dev, cfg, w, ctx=ctx, batch=batch, w4=w4, fused=fused, persistent=persistent)
     ocfg = dict(cfg, ctx=ctx, batch=batch, w4=int(w4), group=64, round_acts=1, llama3_rope=1)
     o = orc.Llama(ocfg, llama.weights_to_oracle(w, w4))
     rng = np.random.default_rng(seed)
@@ -84,6 +84,15 @@ def test_small_model_one_stage_per_cone(dev, w4):
     # the unfused launch list (norm, projections, RoPE + cache write as separate stages: 8 per layer)
     m = run_pair(dev, SMALL, ctx=128, batch=2, w4=w4, steps=32, prefill=40, fused=False)
     assert m.n_stages == 1 + 8 * SMALL["layers"] + 4
+
+
+@pytest.mark.parametrize("batch,w4", [(1, False), (3, True), (16, False)])
+def test_single_kernel_step(dev, batch, w4):
+    # the same stage list lowered into one cooperative kernel with grid barriers between the stages
+    m = run_pair(dev, SMALL, ctx=128, batch=batch, w4=w4, steps=32, prefill=40, persistent=True)
+    assert m.kernel_count == 1
+    times = m.step_stage_times()
+    assert len(times) == m.n_stages + 1 and all(t >= 0.0 for t in times)      # argmax is two phases
 
 
 def test_batch16_and_replay_equals_eager(dev):
