@@ -149,7 +149,7 @@ def time_events(fn, steps, warmup, torch):
     return ts[len(ts) // 2] * 1e-3, ts[0] * 1e-3
 
 
-def suite(dev, torch, hbm_peak, tf_peak, quick, only=None, c2_shape=(4096, 2048, 8192), c3_shape=(8, 4096), fused=True):
+def suite(dev, torch, hbm_peak, tf_peak, quick, only=None, c2_shape=(4096, 2048, 8192), c3_shape=(8, 4096), fused=True, persistent=False):
     import numpy as np
     from sanic_b200 import llama
     out = {}
@@ -204,7 +204,7 @@ def suite(dev, torch, hbm_peak, tf_peak, quick, only=None, c2_shape=(4096, 2048,
         if not want("c4_" + name):
             continue
         w = llama.random_weights(cfg, 11, td, w4=w4)
-        m = llama.LlamaMachine(dev, cfg, w, ctx=1088, batch=batch, w4=w4, fused=fused)
+        m = llama.LlamaMachine(dev, cfg, w, ctx=1088, batch=batch, w4=w4, fused=fused, persistent=persistent)
         rng = np.random.default_rng(3)
         # prefill 1024 positions from random token ids by decoding on the device
         for p in range(1024 if not quick else 64):
@@ -353,7 +353,7 @@ def run_ours(args):
     if rank == 0 and world == 1 and not args.no_suite:
         try:
             line["suite"] = suite(dev, torch, hbm_peak, tf_peak, args.quick, args.only.split(",") if args.only else None,
-                                  tuple(int(t) for t in args.c2_shape.split(",")), tuple(int(t) for t in args.c3_shape.split(",")), not args.llama_unfused)
+                                  tuple(int(t) for t in args.c2_shape.split(",")), tuple(int(t) for t in args.c3_shape.split(",")), not args.llama_unfused, args.llama_persistent)
         except Exception as e:  # the headline line must still print
             line["suite"] = {"error": repr(e)}
     if rank == 0:
@@ -382,6 +382,7 @@ def main():
     ap.add_argument("--only", default="", help="comma-separated substrings of suite entries to run (c1,c2,c3,c4_bf16_b1,...)")
     ap.add_argument("--c2-shape", default="4096,2048,8192", help="M,K,N of the suite's GEMM (small cases for profiling)")
     ap.add_argument("--llama-unfused", action="store_true", help="one stage per graph cone in the decode step")
+    ap.add_argument("--llama-persistent", action="store_true", help="replay the decode step as one cooperative kernel instead of the launch list")
     ap.add_argument("--c3-shape", default="8,4096", help="batch,sequence of the suite's prefill attention")
     args = ap.parse_args()
     if args.warmup < 3:

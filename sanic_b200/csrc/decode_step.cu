@@ -26,9 +26,16 @@ namespace step {
 namespace {
 
 enum { PH_GEMV = 1, PH_DECODE, PH_EMBED, PH_RMSNORM, PH_ARGMAX_PART, PH_ARGMAX_FINAL, PH_ADVANCE };
-constexpr int THREADS = 256;
+constexpr int CONSUMERS = 256;              // warps 0-7: the phase bodies
+constexpr int THREADS = CONSUMERS + 32;     // warp 8: the weight producer
 constexpr int AMAX_CHUNKS = 128;
-constexpr unsigned BARRIER_SPIN_LIMIT = 1u << 22;
+constexpr unsigned SPIN_LIMIT = 1u << 22;
+constexpr int SLOTS = 4;                    // weight ring
+constexpr int SLOT_BYTES = 34816;           // 32 rows x (1024 + 64) B, the largest stage
+constexpr int SCRATCH_BYTES = 20480;        // contraction scratch (row norms, cross-warp sums) | pointwise scratch
+constexpr int XS_BYTES = 66560;             // a phase's activations, bf16, norm applied: 16 rows x (2048 + 32) x 2 B
+constexpr int SHARED_BYTES = SCRATCH_BYTES + XS_BYTES;   // the attention K/V ring overlays both
+constexpr int RING_BYTES = SLOTS * SLOT_BYTES;
 
 struct Phase {
     int op, n_blocks;
@@ -43,15 +50,77 @@ struct Phase {
     int i0, i1, i2; float f0;
 };
 
+// One ring stage of a contraction: `rows` weight rows (16, or 32 for the silu-mul pair) x `stage_k` inputs.
+struct Geom { int stage_k, n_stages, rows, row_bytes, pitch; };
+__host__ __device__ inline Geom geom_of(bool w4, bool dual, int K) {
+    Geom g;
+    const int cap = dual ? 512 : 1024;
+    g.stage_k = K < cap ? K : cap;
+    g.n_stages = K / g.stage_k;
+    g.rows = dual ? 32 : 16;
+    g.row_bytes = w4 ? g.stage_k / 2 : g.stage_k * 2;
+    g.pitch = g.row_bytes + (w4 ? 32 : 64);      // rows land 4 bank groups apart: conflict-free fragment reads
+    return g;
+}
+
+// weight row (within its matrix) of fragment row r (0..15) of row tile `tile`
+__device__ __forceinline__ int weight_row(int epilogue, const gemv::Fused& fz, int tile, int r) {
+    if (epilogue == SANIC_EPI_ROPE_CACHE) {      // rotate-half partners d = 8*sub + r and d + D/2 of one head
+        const int tph = fz.head_dim / 16, head = tile / tph, sub = tile % tph;
+        return head * fz.head_dim + 8 * sub + (r & 7) + (r >= 8 ? fz.head_dim / 2 : 0);
+    }
+    return tile * 16 + r;
+}
+__device__ __forceinline__ void seg_of_tile(const gemv::SegTable& segs, int n_segments, bool dual, int gtile, int& seg, int& tile) {
+    seg = 0;
+    if (!dual) {
+        if (n_segments > 1 && gtile >= segs.tile_begin[1]) seg = 1;
+        if (n_segments > 2 && gtile >= segs.tile_begin[2]) seg = 2;
+    }
+    tile = gtile - (seg == 0 ? segs.tile_begin[0] : (seg == 1 ? segs.tile_begin[1] : segs.tile_begin[2]));
+}
+
 __device__ __forceinline__ unsigned ld_acquire(const unsigned* p) {
     unsigned v;
     asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
     return v;
 }
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(done) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return done != 0;
+}
+// bar[0]: arrivals so far in this launch, bar[1]: abort word. Every wait below is bounded and gives up when the
+// abort word is set; the one that runs out of spins sets it and records a code in the status word.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, unsigned* gbar, int* err, int code) {
+    for (unsigned it = 0; it < SPIN_LIMIT; ++it) {
+        if (mbar_test(bar, parity)) return true;
+        if ((it & 4095u) == 4095u && ld_acquire(gbar + 1) != 0) return false;
+    }
+    atomicExch(gbar + 1, 1u);
+    atomicCAS(err, 0, code);
+    return false;
+}
+// one contiguous row piece, global -> shared, completion counted in bytes on an mbarrier of this CTA
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
 
-// bar[0]: arrivals so far in this launch, bar[1]: abort word
+__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 2, 256;" ::: "memory"); }
+
 __device__ __forceinline__ bool grid_barrier(unsigned* bar, unsigned target, int* err, int* s_ok) {
-    __syncthreads();
+    consumer_sync();
     if (threadIdx.x == 0) {
         __threadfence();
         atomicAdd(bar, 1u);
@@ -59,61 +128,173 @@ __device__ __forceinline__ bool grid_barrier(unsigned* bar, unsigned target, int
         unsigned spins = 0;
         while (ld_acquire(bar) < target) {
             if ((++spins & 63u) == 0 && ld_acquire(bar + 1) != 0) { ok = 0; break; }
-            if (spins > BARRIER_SPIN_LIMIT) { atomicExch(bar + 1, 1u); atomicCAS(err, 0, 31); ok = 0; break; }
+            if (spins > SPIN_LIMIT) { atomicExch(bar + 1, 1u); atomicCAS(err, 0, 31); ok = 0; break; }
         }
         __threadfence();
         *s_ok = ok;
     }
-    __syncthreads();
+    consumer_sync();
     return *s_ok != 0;
 }
 
-// Each phase body is its own function so that its registers are allocated apart from the other bodies'.
+struct Ring {
+    uint64_t* full; uint64_t* empty;     // [SLOTS] each
+    uint32_t base;                       // shared-memory address of slot 0
+    unsigned char* ptr;                  // generic pointer to slot 0
+};
+
+// The consumers' half of a contraction phase: weights come out of the ring, activations from L2.
 template <bool W4, int NT, bool DUAL, bool NORM>
-__device__ __noinline__ void run_gemv(const Phase& P, float* scratch) {
-    if (NORM) gemv::row_norms<true>(P.fz, P.batch, P.K, scratch);   // once per phase, not per tile
-    for (int blk = blockIdx.x; blk < P.n_blocks; blk += gridDim.x) {
-        gemv::gemv_tile<W4, NT, DUAL, NORM, true>(P.x, P.batch, P.K, P.segs, P.n_segments, P.out_dtype, P.epilogue, P.residual,
-                                           P.fz, 1, blk, false, scratch);
-        __syncthreads();   // the scratch is reused by the next tile
+__device__ __forceinline__ bool consume_gemv(const Phase& P, const Ring& ring, uint32_t& drained, float* scratch, unsigned* gbar, int* err) {
+    using namespace gemv;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int g = lane >> 2, t = lane & 3;
+    constexpr int NM = DUAL ? 2 : 1;
+    constexpr int UNIT = W4 ? 64 : 32;       // k values one pass of a warp covers
+    const Geom G = geom_of(W4, DUAL, P.K);
+    const int units = G.stage_k / UNIT;
+    const int u0 = (warp * units) / GW, u1 = ((warp + 1) * units) / GW;
+    if (NORM) row_norms<true>(P.fz, P.batch, P.K, scratch);   // once per phase
+    // The phase's activations (norm applied) are the same for every tile: they are staged in shared memory, as a
+    // whole when batch x K fits (one L2 round trip per phase), else one ring stage's K range at a time. Rows sit
+    // 4 bank groups apart, like the weight rows. The inner loop reads activations from shared memory only.
+    unsigned char* xs = (unsigned char*)scratch + SCRATCH_BYTES;
+    const bool whole = (size_t)P.batch * (P.K * 2 + 64) <= (size_t)XS_BYTES;
+    const int xspan = whole ? P.K : G.stage_k;       // k values per staged row
+    const int xpitch = xspan * 2 + 64;
+    auto stage_x = [&](int k_begin) {
+        const int cpr = xspan / 8;       // 16-byte chunks per row
+        for (int idx = tid; idx < P.batch * cpr; idx += CONSUMERS) {
+            const int n = idx / cpr, c = idx % cpr;
+            const uint4 v = load_x8<NORM, true>(P.x + (size_t)n * P.K, NORM ? P.fz.norm_x + (size_t)n * P.K : nullptr, P.fz.norm_gamma,
+                                                NORM ? scratch[n] : 1.0f, k_begin + c * 8, true);
+            *(uint4*)(xs + (size_t)n * xpitch + c * 16) = v;
+        }
+    };
+    if (whole) { stage_x(0); consumer_sync(); }
+    // this thread's activation rows (batch columns g and g + 8); a column beyond the batch reads zeros
+    const bool xok0 = g < P.batch, xok1 = NT > 1 && (g + 8) < P.batch;
+    const unsigned char* xs0 = xs + (size_t)(xok0 ? g : 0) * xpitch;
+    const unsigned char* xs1 = xs + (size_t)(xok1 ? g + 8 : 0) * xpitch;
+    constexpr int MAXU = W4 ? 2 : 4;         // units per warp per stage at the largest stage (1024 / UNIT / 8)
+    bool ok = true;
+    for (int gt = blockIdx.x; gt < P.n_blocks && ok; gt += gridDim.x) {
+        int seg, tile;
+        seg_of_tile(P.segs, P.n_segments, DUAL, gt, seg, tile);
+        float acc[NM][NT][4];
+#pragma unroll
+        for (int mI = 0; mI < NM; ++mI)
+#pragma unroll
+            for (int j = 0; j < NT; ++j) acc[mI][j][0] = acc[mI][j][1] = acc[mI][j][2] = acc[mI][j][3] = 0.0f;
+        // int4: scale rows of fragment rows g and g+8
+        const uint16_t* sr[NM][2];
+        if (W4) {
+#pragma unroll
+            for (int mI = 0; mI < NM; ++mI) {
+                const int si = DUAL ? mI : seg;
+                const uint16_t* S = si == 0 ? P.segs.scales[0] : (si == 1 ? P.segs.scales[1] : P.segs.scales[2]);
+                sr[mI][0] = S + (size_t)weight_row(P.epilogue, P.fz, tile, g) * (P.K / 64);
+                sr[mI][1] = S + (size_t)weight_row(P.epilogue, P.fz, tile, g + 8) * (P.K / 64);
+            }
+        }
+        for (int s = 0; s < G.n_stages; ++s, ++drained) {
+            const int slot = drained % SLOTS;
+            const uint32_t parity = (drained / SLOTS) & 1;
+            const int kbase = s * G.stage_k;
+            const int xbase = whole ? 0 : kbase;
+            if (!whole) { consumer_sync(); stage_x(kbase); consumer_sync(); }
+            // activations (and scales) of this warp's units first: their L2 latency hides behind the wait for the weights
+            uint4 xb[MAXU][NT][W4 ? 2 : 1];
+            float sc[MAXU][NM][2];
+#pragma unroll
+            for (int u = 0; u < MAXU; ++u) {
+                if (u0 + u < u1) {
+                    const int k = kbase + (u0 + u) * UNIT;
+#pragma unroll
+                    for (int j = 0; j < NT; ++j) {
+                        const unsigned char* xr = j == 0 ? xs0 : xs1;
+                        const bool xk = j == 0 ? xok0 : xok1;
+                        const int kk = k - xbase + (W4 ? t * 16 : t * 8);
+                        xb[u][j][0] = xk ? *(const uint4*)(xr + (size_t)kk * 2) : make_uint4(0, 0, 0, 0);
+                        if (W4) xb[u][j][W4 ? 1 : 0] = xk ? *(const uint4*)(xr + (size_t)(kk + 8) * 2) : make_uint4(0, 0, 0, 0);
+                    }
+                    if (W4) {
+#pragma unroll
+                        for (int mI = 0; mI < NM; ++mI) {
+                            sc[u][mI][0] = bf16_to_f32(__ldg(sr[mI][0] + k / 64));
+                            sc[u][mI][1] = bf16_to_f32(__ldg(sr[mI][1] + k / 64));
+                        }
+                    }
+                }
+            }
+            ok = mbar_wait(&ring.full[slot], parity, gbar, err, 32);
+            if (!ok) break;
+            const unsigned char* sb = ring.ptr + (size_t)slot * SLOT_BYTES;
+#pragma unroll
+            for (int u = 0; u < MAXU; ++u) {
+                if (u0 + u < u1) {
+                    const int ku = (u0 + u) * UNIT;          // offset inside the stage
+                    if (!W4) {
+#pragma unroll
+                        for (int mI = 0; mI < NM; ++mI) {
+                            const uint4 r0 = *(const uint4*)(sb + (size_t)(mI * 16 + g) * G.pitch + (ku + t * 8) * 2);
+                            const uint4 r1 = *(const uint4*)(sb + (size_t)(mI * 16 + g + 8) * G.pitch + (ku + t * 8) * 2);
+#pragma unroll
+                            for (int j = 0; j < NT; ++j) {
+                                const uint4& xv = xb[u][j][0];
+                                mma_bf16_16816(acc[mI][j], r0.x, r1.x, r0.y, r1.y, xv.x, xv.y);
+                                mma_bf16_16816(acc[mI][j], r0.z, r1.z, r0.w, r1.w, xv.z, xv.w);
+                            }
+                        }
+                    } else {
+                        const uint32_t ONES = 0x3F803F80u;
+#pragma unroll
+                        for (int j = 0; j < NT; ++j) {
+                            const uint4 xa = xb[u][j][0], xc = xb[u][j][W4 ? 1 : 0];
+                            // activation pairs matching the nibble pairing (n_i, n_{i+4})
+                            const uint32_t bA0 = prmt(xa.x, xa.z, 0x5410), bA1 = prmt(xa.x, xa.z, 0x7632);
+                            const uint32_t bA2 = prmt(xa.y, xa.w, 0x5410), bA3 = prmt(xa.y, xa.w, 0x7632);
+                            const uint32_t bC0 = prmt(xc.x, xc.z, 0x5410), bC1 = prmt(xc.x, xc.z, 0x7632);
+                            const uint32_t bC2 = prmt(xc.y, xc.w, 0x5410), bC3 = prmt(xc.y, xc.w, 0x7632);
+                            float c1[4] = {0, 0, 0, 0};
+                            mma_bf16_16816(c1, ONES, ONES, ONES, ONES, bA0, bA1);
+                            mma_bf16_16816(c1, ONES, ONES, ONES, ONES, bA2, bA3);
+                            mma_bf16_16816(c1, ONES, ONES, ONES, ONES, bC0, bC1);
+                            mma_bf16_16816(c1, ONES, ONES, ONES, ONES, bC2, bC3);
+#pragma unroll
+                            for (int mI = 0; mI < NM; ++mI) {
+                                const uint2 w0 = *(const uint2*)(sb + (size_t)(mI * 16 + g) * G.pitch + ku / 2 + t * 8);
+                                const uint2 w1 = *(const uint2*)(sb + (size_t)(mI * 16 + g + 8) * G.pitch + ku / 2 + t * 8);
+                                float c[4] = {0, 0, 0, 0};
+                                mma_bf16_16816(c, nib_pair(w0.x), nib_pair(w1.x), nib_pair(w0.x >> 4), nib_pair(w1.x >> 4), bA0, bA1);
+                                mma_bf16_16816(c, nib_pair(w0.x >> 8), nib_pair(w1.x >> 8), nib_pair(w0.x >> 12), nib_pair(w1.x >> 12), bA2, bA3);
+                                mma_bf16_16816(c, nib_pair(w0.y), nib_pair(w1.y), nib_pair(w0.y >> 4), nib_pair(w1.y >> 4), bC0, bC1);
+                                mma_bf16_16816(c, nib_pair(w0.y >> 8), nib_pair(w1.y >> 8), nib_pair(w0.y >> 12), nib_pair(w1.y >> 12), bC2, bC3);
+                                acc[mI][j][0] = fmaf(sc[u][mI][0], fmaf(-136.0f, c1[0], c[0]), acc[mI][j][0]);
+                                acc[mI][j][1] = fmaf(sc[u][mI][0], fmaf(-136.0f, c1[1], c[1]), acc[mI][j][1]);
+                                acc[mI][j][2] = fmaf(sc[u][mI][1], fmaf(-136.0f, c1[2], c[2]), acc[mI][j][2]);
+                                acc[mI][j][3] = fmaf(sc[u][mI][1], fmaf(-136.0f, c1[3], c[3]), acc[mI][j][3]);
+                            }
+                        }
+                    }
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&ring.empty[slot]);     // this warp is done reading the slot
+        }
+        if (!ok) break;
+        tile_finish<NT, DUAL, true>(acc, P.batch, P.segs, P.out_dtype, P.epilogue, P.residual, P.fz, 1, 0, seg, tile, scratch);
+        consumer_sync();   // the scratch is reused by the next tile
     }
+    return ok;
 }
 
 template <bool VT>
-__device__ __noinline__ void run_decode(const Phase& P, int per_b, unsigned char* dyn, int tid) {
+__device__ __forceinline__ void run_decode(const Phase& P, int per_b, unsigned char* shared, int tid) {
     for (int it = blockIdx.x; it < P.n_blocks; it += gridDim.x) {
         const int b = it / per_b, hk = (it % per_b) / P.dec.n_splits, split = it % P.dec.n_splits;
-        decode::attn_decode_tile<64, VT>(P.dec, P.counters, split, hk, b, dyn, tid, false, 1);
+        decode::attn_decode_tile<64, VT>(P.dec, P.counters, split, hk, b, shared, tid, false, 1);
         decode::tile_sync(1);
-    }
-}
-
-// Ask L2 for the weights of this CTA's first tile of a contraction phase (16 rows x K per matrix).
-__device__ __forceinline__ void prefetch_gemv(const Phase& P) {
-    if ((int)blockIdx.x >= P.n_blocks) return;
-    const bool w4 = P.variant & 1, dual = (P.variant & 4) != 0;
-    const int gtile = blockIdx.x;
-    int seg = 0;
-    if (!dual) {
-        if (P.n_segments > 1 && gtile >= P.segs.tile_begin[1]) seg = 1;
-        if (P.n_segments > 2 && gtile >= P.segs.tile_begin[2]) seg = 2;
-    }
-    const int tile = gtile - P.segs.tile_begin[seg];
-    const size_t row_bytes = w4 ? (size_t)P.K / 2 : (size_t)P.K * 2;
-    const int lines = (int)((row_bytes + 127) / 128);
-    for (int mI = 0; mI < (dual ? 2 : 1); ++mI) {
-        const char* wbase = (const char*)P.segs.w[dual ? mI : seg];
-        for (int i = threadIdx.x; i < 16 * lines; i += THREADS) {
-            const int r = i / lines, ln = i % lines;
-            size_t wrow;
-            if (P.epilogue == SANIC_EPI_ROPE_CACHE) {   // rows 8*sub + r and their rotate-half partners
-                const int tph = P.fz.head_dim / 16, head = tile / tph, sub = tile % tph;
-                wrow = (size_t)head * P.fz.head_dim + 8 * sub + (r & 7) + (r >= 8 ? P.fz.head_dim / 2 : 0);
-            } else {
-                wrow = (size_t)tile * 16 + r;
-            }
-            asm volatile("prefetch.global.L2 [%0];" ::"l"(wbase + wrow * row_bytes + (size_t)ln * 128));
-        }
     }
 }
 
@@ -121,159 +302,215 @@ __device__ __forceinline__ void amax_merge(float& v, int& i, float v2, int i2) {
     if (v2 > v || (v2 == v && i2 < i)) { v = v2; i = i2; }
 }
 
+// One instantiation per batch width (a program's contractions share it): fewer bodies per kernel keep the
+// register allocation of each one clean. Weight storage may differ per stage (int4 layers, bf16 lm_head);
+// ANY_I4 = false leaves the int4 bodies out for programs that have none.
+template <int NT, bool ANY_I4>
 __global__ void __launch_bounds__(THREADS, 1)
 decode_step_kernel(const Phase* __restrict__ phases, int n_phases, unsigned* bar, int* err, unsigned long long* stamps) {
-    extern __shared__ __align__(128) unsigned char dyn[];
+    extern __shared__ __align__(128) unsigned char dyn[];       // [weight ring][shared region]
     __shared__ Phase ph[2];
+    __shared__ __align__(8) uint64_t s_full[SLOTS], s_empty[SLOTS];
     __shared__ int s_ok;
+    __shared__ unsigned s_produced;
     const int tid = threadIdx.x;
-    constexpr int PW = sizeof(Phase) / 4;
-    for (int w = tid; w < PW; w += THREADS) ((int*)&ph[0])[w] = __ldg((const int*)&phases[0] + w);
-    __syncthreads();
-    // CTA 0 stamps the device clock at every phase boundary (per-stage times inside the one launch)
-    if (blockIdx.x == 0 && tid == 0) { unsigned long long g; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(g)); stamps[0] = g; }
-
-    for (int i = 0; i < n_phases; ++i) {
-        const Phase& P = ph[i & 1];
-        if (i + 1 < n_phases)   // next descriptor: in shared memory by the time the barrier releases
-            for (int w = tid; w < PW; w += THREADS) ((int*)&ph[(i + 1) & 1])[w] = __ldg((const int*)&phases[i + 1] + w);
-
-        switch (P.op) {
-            case PH_GEMV: {
-                float* scratch = (float*)dyn;
-                switch (P.variant & 15) {
-                    case 0: run_gemv<false, 1, false, false>(P, scratch); break;
-                    case 1: run_gemv<true, 1, false, false>(P, scratch); break;
-                    case 2: run_gemv<false, 2, false, false>(P, scratch); break;
-                    case 3: run_gemv<true, 2, false, false>(P, scratch); break;
-                    case 4: run_gemv<false, 1, true, false>(P, scratch); break;
-                    case 5: run_gemv<true, 1, true, false>(P, scratch); break;
-                    case 6: run_gemv<false, 2, true, false>(P, scratch); break;
-                    case 7: run_gemv<true, 2, true, false>(P, scratch); break;
-                    case 8: run_gemv<false, 1, false, true>(P, scratch); break;
-                    case 9: run_gemv<true, 1, false, true>(P, scratch); break;
-                    case 12: run_gemv<false, 1, true, true>(P, scratch); break;
-                    case 13: run_gemv<true, 1, true, true>(P, scratch); break;
-                    default: break;    // the host never emits other variants
-                }
-                break;
-            }
-            case PH_DECODE: {
-                // one item = (chunk, kv head, batch) on the first 128 threads; the ring needs the whole dynamic buffer
-                const int per_b = P.dec.n_splits * P.dec.kv_heads;
-                if (tid < 128) {
-                    if (P.variant & 1) run_decode<true>(P, per_b, dyn, tid);
-                    else run_decode<false>(P, per_b, dyn, tid);
-                }
-                break;
-            }
-            case PH_EMBED: {   // out[b,:] = widen(table[token[b],:])
-                const uint16_t* table = (const uint16_t*)P.a;
-                const int32_t* tokens = (const int32_t*)P.b;
-                float* out = (float*)P.c;
-                const int hidden = P.i1, vocab = P.i2;
-                for (int b = blockIdx.x; b < P.n_blocks; b += gridDim.x) {
-                    int tok = __ldcg(tokens + b);
-                    tok = tok < 0 ? 0 : (tok >= vocab ? vocab - 1 : tok);
-                    for (int k = tid; k < hidden; k += THREADS) out[(size_t)b * hidden + k] = bf16_to_f32(table[(size_t)tok * hidden + k]);
-                }
-                break;
-            }
-            case PH_RMSNORM: {   // xn = bf16((x * g) / sqrt(sum(x^2) * (1/n) + eps)), fixed summation order
-                const float* x = (const float*)P.a;
-                const uint16_t* gamma = (const uint16_t*)P.b;
-                uint16_t* out = (uint16_t*)P.c;
-                const int n = P.i1;
-                float* wsum = (float*)dyn;
-                for (int row = blockIdx.x; row < P.n_blocks; row += gridDim.x) {
-                    const float* xr = x + (size_t)row * n;
-                    float ss = 0.0f;
-                    for (int k = tid; k < n; k += THREADS) { const float v = __ldcg(xr + k); ss = fmaf(v, v, ss); }
-                    ss = warp_sum(ss);
-                    if ((tid & 31) == 0) wsum[tid >> 5] = ss;
-                    __syncthreads();
-                    if (tid == 0) {
-                        float tot = 0.0f;
-                        for (int w = 0; w < 8; ++w) tot += wsum[w];
-                        wsum[8] = sqrtf(tot * (1.0f / (float)n) + P.f0);
-                    }
-                    __syncthreads();
-                    const float den = wsum[8];
-                    for (int k = tid; k < n; k += THREADS)
-                        out[(size_t)row * n + k] = f32_to_bf16_bits((__ldcg(xr + k) * bf16_to_f32(gamma[k])) / den);
-                    __syncthreads();
-                }
-                break;
-            }
-            case PH_ARGMAX_PART: {   // (max value, first index) per chunk of a row
-                const float* x = (const float*)P.a;
-                const int n = P.i1;
-                float* sv = (float*)dyn; int* si = (int*)dyn + 8;
-                for (int blk = blockIdx.x; blk < P.n_blocks; blk += gridDim.x) {
-                    const int row = blk / AMAX_CHUNKS, chunk = blk % AMAX_CHUNKS;
-                    const int lo = (int)(((long long)chunk * n) / AMAX_CHUNKS), hi = (int)(((long long)(chunk + 1) * n) / AMAX_CHUNKS);
-                    const float* xr = x + (size_t)row * n;
-                    float v = -INFINITY; int idx = 0x7FFFFFFF;
-                    for (int j = lo + tid; j < hi; j += THREADS) amax_merge(v, idx, __ldcg(xr + j), j);
-#pragma unroll
-                    for (int o = 16; o > 0; o >>= 1) {
-                        float v2 = __shfl_xor_sync(0xffffffffu, v, o); int i2 = __shfl_xor_sync(0xffffffffu, idx, o);
-                        amax_merge(v, idx, v2, i2);
-                    }
-                    if ((tid & 31) == 0) { sv[tid >> 5] = v; si[tid >> 5] = idx; }
-                    __syncthreads();
-                    if (tid == 0) {
-                        for (int w = 1; w < 8; ++w) amax_merge(v, idx, sv[w], si[w]);
-                        P.scratch[((size_t)row * AMAX_CHUNKS + chunk) * 2] = v;
-                        P.scratch[((size_t)row * AMAX_CHUNKS + chunk) * 2 + 1] = __int_as_float(idx);
-                    }
-                    __syncthreads();
-                }
-                break;
-            }
-            case PH_ARGMAX_FINAL: {
-                uint32_t* out = (uint32_t*)P.c;
-                float* sv = (float*)dyn; int* si = (int*)dyn + 8;
-                for (int row = blockIdx.x; row < P.n_blocks; row += gridDim.x) {
-                    float v = -INFINITY; int idx = 0x7FFFFFFF;
-                    if (tid < AMAX_CHUNKS) {
-                        v = __ldcg(P.scratch + ((size_t)row * AMAX_CHUNKS + tid) * 2);
-                        idx = __float_as_int(__ldcg(P.scratch + ((size_t)row * AMAX_CHUNKS + tid) * 2 + 1));
-                    }
-#pragma unroll
-                    for (int o = 16; o > 0; o >>= 1) {
-                        float v2 = __shfl_xor_sync(0xffffffffu, v, o); int i2 = __shfl_xor_sync(0xffffffffu, idx, o);
-                        amax_merge(v, idx, v2, i2);
-                    }
-                    if ((tid & 31) == 0) { sv[tid >> 5] = v; si[tid >> 5] = idx; }
-                    __syncthreads();
-                    if (tid == 0) {
-                        for (int w = 1; w < 8; ++w) amax_merge(v, idx, sv[w], si[w]);
-                        out[row] = (idx == 0x7FFFFFFF) ? 0xFFFFFFFFu : (uint32_t)idx;   // the +inf identity saturates to u32::MAX
-                    }
-                    __syncthreads();
-                }
-                break;
-            }
-            case PH_ADVANCE:
-                if (blockIdx.x == 0 && tid == 0) *(int32_t*)P.c += 1;
-                break;
-            default: break;
-        }
-
-        if (i + 1 < n_phases) {
-            __syncthreads();                          // the next descriptor is complete in shared memory
-            const Phase& N = ph[(i + 1) & 1];
-            if (N.op == PH_GEMV) prefetch_gemv(N);
-            if (!grid_barrier(bar, (unsigned)(i + 1) * gridDim.x, err, &s_ok)) return;
-        }
-        if (blockIdx.x == 0 && tid == 0) { unsigned long long g; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(g)); stamps[i + 1] = g; }
+    unsigned char* shared = dyn + RING_BYTES;
+    Ring ring{s_full, s_empty, smem_u32(dyn), dyn};
+    if (tid == 0) {
+        for (int i = 0; i < SLOTS; ++i) { mbar_init(&s_full[i], 1); mbar_init(&s_empty[i], gemv::GW); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        s_produced = 0;
     }
+    constexpr int PW = sizeof(Phase) / 4;
+    if (tid < CONSUMERS)
+        for (int w = tid; w < PW; w += CONSUMERS) ((int*)&ph[0])[w] = __ldg((const int*)&phases[0] + w);
+    __syncthreads();
+
+    if (tid >= CONSUMERS) {
+        // ── producer warp: streams the weights of every contraction phase, in the order the consumers will want
+        //    them, as far ahead as the ring allows. Weights never change, so it may run ahead of the grid barriers;
+        //    HBM keeps streaming while the consumers wait for activations. ──
+        const int lane = tid - CONSUMERS;
+        unsigned fill = 0;
+        bool ok = true;
+        for (int i = 0; i < n_phases && ok; ++i) {
+            const Phase& P = phases[i];
+            if (P.op != PH_GEMV) continue;
+            const bool w4 = P.variant & 1, dual = (P.variant & 4) != 0;
+            const Geom G = geom_of(w4, dual, P.K);
+            const size_t full_row = w4 ? (size_t)P.K / 2 : (size_t)P.K * 2;
+            for (int gt = blockIdx.x; gt < P.n_blocks && ok; gt += gridDim.x) {
+                int seg, tile;
+                seg_of_tile(P.segs, P.n_segments, dual, gt, seg, tile);
+                const char* src_row = nullptr;
+                if (lane < G.rows) {
+                    const int mI = lane >> 4, r = lane & 15;
+                    const int si = dual ? mI : seg;
+                    const char* W = (const char*)(si == 0 ? P.segs.w[0] : (si == 1 ? P.segs.w[1] : P.segs.w[2]));
+                    src_row = W + (size_t)weight_row(P.epilogue, P.fz, tile, r) * full_row;
+                }
+                for (int s = 0; s < G.n_stages && ok; ++s, ++fill) {
+                    const int slot = fill % SLOTS;
+                    if (lane == 0) {
+                        ok = mbar_wait(&s_empty[slot], ((fill / SLOTS) & 1) ^ 1, bar, err, 33);
+                        if (ok) mbar_expect_tx(&s_full[slot], (uint32_t)(G.rows * G.row_bytes));
+                    }
+                    ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+                    if (ok && lane < G.rows)
+                        bulk_load(ring.base + slot * SLOT_BYTES + lane * G.pitch, src_row + (size_t)s * G.row_bytes, (uint32_t)G.row_bytes, &s_full[slot]);
+                }
+            }
+        }
+        if (lane == 0) s_produced = fill;
+    } else {
+        // ── consumers: walk the phases ──
+        uint32_t drained = 0;
+        bool ok = true;
+        if (blockIdx.x == 0 && tid == 0) { unsigned long long g; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(g)); stamps[0] = g; }
+        for (int i = 0; i < n_phases && ok; ++i) {
+            const Phase& P = ph[i & 1];
+            if (i + 1 < n_phases)   // next descriptor: in shared memory by the time the barrier releases
+                for (int w = tid; w < PW; w += CONSUMERS) ((int*)&ph[(i + 1) & 1])[w] = __ldg((const int*)&phases[i + 1] + w);
+            switch (P.op) {
+                case PH_GEMV: {
+                    float* scratch = (float*)shared;
+                    switch (((P.variant >> 1) & 6) | (P.variant & 1)) {      // bit0: int4, bit1: silu-mul pair, bit2: inlined norm
+                        case 0: ok = consume_gemv<false, NT, false, false>(P, ring, drained, scratch, bar, err); break;
+                        case 1: if (ANY_I4) ok = consume_gemv<true, NT, false, false>(P, ring, drained, scratch, bar, err); break;
+                        case 2: ok = consume_gemv<false, NT, true, false>(P, ring, drained, scratch, bar, err); break;
+                        case 3: if (ANY_I4) ok = consume_gemv<true, NT, true, false>(P, ring, drained, scratch, bar, err); break;
+                        case 4: if (NT == 1) ok = consume_gemv<false, 1, false, true>(P, ring, drained, scratch, bar, err); break;
+                        case 5: if (NT == 1 && ANY_I4) ok = consume_gemv<true, 1, false, true>(P, ring, drained, scratch, bar, err); break;
+                        case 6: if (NT == 1) ok = consume_gemv<false, 1, true, true>(P, ring, drained, scratch, bar, err); break;
+                        case 7: if (NT == 1 && ANY_I4) ok = consume_gemv<true, 1, true, true>(P, ring, drained, scratch, bar, err); break;
+                    }
+                    break;
+                }
+                case PH_DECODE: {
+                    // one item = (chunk, kv head, batch) on the first 128 threads; its K/V ring is the shared region
+                    const int per_b = P.dec.n_splits * P.dec.kv_heads;
+                    if (tid < 128) {
+                        if (P.variant & 1) run_decode<true>(P, per_b, shared, tid);
+                        else run_decode<false>(P, per_b, shared, tid);
+                    }
+                    break;
+                }
+                case PH_EMBED: {   // out[b,:] = widen(table[token[b],:])
+                    const uint16_t* table = (const uint16_t*)P.a;
+                    const int32_t* tokens = (const int32_t*)P.b;
+                    float* out = (float*)P.c;
+                    const int hidden = P.i1, vocab = P.i2;
+                    for (int b = blockIdx.x; b < P.n_blocks; b += gridDim.x) {
+                        int tok = __ldcg(tokens + b);
+                        tok = tok < 0 ? 0 : (tok >= vocab ? vocab - 1 : tok);
+                        for (int k = tid; k < hidden; k += CONSUMERS) out[(size_t)b * hidden + k] = bf16_to_f32(table[(size_t)tok * hidden + k]);
+                    }
+                    break;
+                }
+                case PH_RMSNORM: {   // xn = bf16((x * g) / sqrt(sum(x^2) * (1/n) + eps)), fixed summation order
+                    const float* x = (const float*)P.a;
+                    const uint16_t* gamma = (const uint16_t*)P.b;
+                    uint16_t* out = (uint16_t*)P.c;
+                    const int n = P.i1;
+                    float* wsum = (float*)shared;
+                    for (int row = blockIdx.x; row < P.n_blocks; row += gridDim.x) {
+                        const float* xr = x + (size_t)row * n;
+                        float ss = 0.0f;
+                        for (int k = tid; k < n; k += CONSUMERS) { const float v = __ldcg(xr + k); ss = fmaf(v, v, ss); }
+                        ss = warp_sum(ss);
+                        if ((tid & 31) == 0) wsum[tid >> 5] = ss;
+                        consumer_sync();
+                        if (tid == 0) {
+                            float tot = 0.0f;
+                            for (int w = 0; w < 8; ++w) tot += wsum[w];
+                            wsum[8] = sqrtf(tot * (1.0f / (float)n) + P.f0);
+                        }
+                        consumer_sync();
+                        const float den = wsum[8];
+                        for (int k = tid; k < n; k += CONSUMERS)
+                            out[(size_t)row * n + k] = f32_to_bf16_bits((__ldcg(xr + k) * bf16_to_f32(gamma[k])) / den);
+                        consumer_sync();
+                    }
+                    break;
+                }
+                case PH_ARGMAX_PART: {   // (max value, first index) per chunk of a row
+                    const float* x = (const float*)P.a;
+                    const int n = P.i1;
+                    float* sv = (float*)shared; int* si = (int*)shared + 8;
+                    for (int blk = blockIdx.x; blk < P.n_blocks; blk += gridDim.x) {
+                        const int row = blk / AMAX_CHUNKS, chunk = blk % AMAX_CHUNKS;
+                        const int lo = (int)(((long long)chunk * n) / AMAX_CHUNKS), hi = (int)(((long long)(chunk + 1) * n) / AMAX_CHUNKS);
+                        const float* xr = x + (size_t)row * n;
+                        float v = -INFINITY; int idx = 0x7FFFFFFF;
+                        for (int j = lo + tid; j < hi; j += CONSUMERS) amax_merge(v, idx, __ldcg(xr + j), j);
+#pragma unroll
+                        for (int o = 16; o > 0; o >>= 1) {
+                            float v2 = __shfl_xor_sync(0xffffffffu, v, o); int i2 = __shfl_xor_sync(0xffffffffu, idx, o);
+                            amax_merge(v, idx, v2, i2);
+                        }
+                        if ((tid & 31) == 0) { sv[tid >> 5] = v; si[tid >> 5] = idx; }
+                        consumer_sync();
+                        if (tid == 0) {
+                            for (int w = 1; w < 8; ++w) amax_merge(v, idx, sv[w], si[w]);
+                            P.scratch[((size_t)row * AMAX_CHUNKS + chunk) * 2] = v;
+                            P.scratch[((size_t)row * AMAX_CHUNKS + chunk) * 2 + 1] = __int_as_float(idx);
+                        }
+                        consumer_sync();
+                    }
+                    break;
+                }
+                case PH_ARGMAX_FINAL: {
+                    uint32_t* out = (uint32_t*)P.c;
+                    float* sv = (float*)shared; int* si = (int*)shared + 8;
+                    for (int row = blockIdx.x; row < P.n_blocks; row += gridDim.x) {
+                        float v = -INFINITY; int idx = 0x7FFFFFFF;
+                        if (tid < AMAX_CHUNKS) {
+                            v = __ldcg(P.scratch + ((size_t)row * AMAX_CHUNKS + tid) * 2);
+                            idx = __float_as_int(__ldcg(P.scratch + ((size_t)row * AMAX_CHUNKS + tid) * 2 + 1));
+                        }
+#pragma unroll
+                        for (int o = 16; o > 0; o >>= 1) {
+                            float v2 = __shfl_xor_sync(0xffffffffu, v, o); int i2 = __shfl_xor_sync(0xffffffffu, idx, o);
+                            amax_merge(v, idx, v2, i2);
+                        }
+                        if ((tid & 31) == 0) { sv[tid >> 5] = v; si[tid >> 5] = idx; }
+                        consumer_sync();
+                        if (tid == 0) {
+                            for (int w = 1; w < 8; ++w) amax_merge(v, idx, sv[w], si[w]);
+                            out[row] = (idx == 0x7FFFFFFF) ? 0xFFFFFFFFu : (uint32_t)idx;   // the +inf identity saturates to u32::MAX
+                        }
+                        consumer_sync();
+                    }
+                    break;
+                }
+                case PH_ADVANCE:
+                    if (blockIdx.x == 0 && tid == 0) *(int32_t*)P.c += 1;
+                    break;
+                default: break;
+            }
+            if (ok && i + 1 < n_phases) ok = grid_barrier(bar, (unsigned)(i + 1) * gridDim.x, err, &s_ok);
+            if (blockIdx.x == 0 && tid == 0) { unsigned long long g; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(g)); stamps[i + 1] = g; }
+        }
+        if (!ok && tid == 0) atomicExch(bar + 1, 1u);      // make sure the producer stops too
+    }
+    // Leave only when no copy into this CTA's shared memory is still in flight: after the producer has stopped,
+    // thread 0 waits (bounded) for every stage that was issued, consumed or not.
+    __syncthreads();
+    if (tid == 0) {
+        const unsigned produced = s_produced;
+        const unsigned first = produced > SLOTS ? produced - SLOTS : 0;
+        for (unsigned f = first; f < produced; ++f) {
+            bool done = false;
+            for (unsigned it = 0; it < SPIN_LIMIT && !done; ++it) done = mbar_test(&s_full[f % SLOTS], (f / SLOTS) & 1);
+        }
+    }
+    __syncthreads();
 }
 
 }  // namespace
 
 struct Plan {
+    const void* kernel = nullptr;
     Phase* d_phases = nullptr;
     unsigned* d_bar = nullptr;
     unsigned long long* d_stamps = nullptr;
@@ -295,7 +532,8 @@ void destroy(Plan* plan) {
 int32_t build(sanic_ctx* ctx, const std::vector<sanic_stage_desc>& stages, Plan** out) {
     *out = nullptr;
     std::vector<Phase> ph;
-    size_t smem = 64 * 4;    // pointwise phases
+    int group = -1;      // 1: batch > 8, shared by every contraction of the program
+    bool any_i4 = false;
     for (const sanic_stage_desc& s : stages) {
         Phase P{};
         switch (s.op) {
@@ -307,12 +545,17 @@ int32_t build(sanic_ctx* ctx, const std::vector<sanic_stage_desc>& stages, Plan*
                 const bool w4 = g.weight_dtype == SANIC_I4, wide = g.batch > 8, dual = g.epilogue == SANIC_EPI_SILU_MUL,
                            norm = g.norm_x != nullptr;
                 if (norm && wide) return SANIC_ERR_UNSUPPORTED;
+                if (group >= 0 && group != (wide ? 1 : 0)) return SANIC_ERR_UNSUPPORTED;
+                group = wide ? 1 : 0;
+                any_i4 = any_i4 || w4;
+                {   // a ring stage must give every warp at least one pass
+                    const Geom G = geom_of(w4, dual, g.K);
+                    if (G.stage_k < 256 || g.K % G.stage_k != 0) return SANIC_ERR_UNSUPPORTED;
+                }
                 P.op = PH_GEMV; P.n_blocks = tiles;
                 P.variant = (w4 ? 1 : 0) | (wide ? 2 : 0) | (dual ? 4 : 0) | (norm ? 8 : 0);
                 P.x = (const uint16_t*)g.x; P.batch = g.batch; P.K = g.K; P.n_segments = g.n_segments;
                 P.out_dtype = g.out_dtype; P.epilogue = g.epilogue; P.residual = g.residual;
-                smem = std::max(smem, (size_t)(wide ? (dual ? gemv::scratch_floats<2, true>() : gemv::scratch_floats<2, false>())
-                                                    : (dual ? gemv::scratch_floats<1, true>() : gemv::scratch_floats<1, false>())) * 4);
                 break;
             }
             case SANIC_OP_DECODE_ATTN: {
@@ -325,7 +568,6 @@ int32_t build(sanic_ctx* ctx, const std::vector<sanic_stage_desc>& stages, Plan*
                 if (d.head_dim != 64) return SANIC_ERR_UNSUPPORTED;
                 P.variant = d.v_transposed ? 1 : 0;
                 P.counters = (int*)(d.partials + (size_t)d.batch * d.q_heads * d.n_splits * (d.head_dim + 2));
-                smem = std::max(smem, (size_t)decode::Cfg<64>::SMEM);
                 break;
             }
             case SANIC_OP_EMBED:
@@ -358,10 +600,14 @@ int32_t build(sanic_ctx* ctx, const std::vector<sanic_stage_desc>& stages, Plan*
         }
         ph.push_back(P);
     }
+    static_assert(gemv::scratch_floats<2, true>() * 4 <= SCRATCH_BYTES && decode::Cfg<64>::SMEM <= SHARED_BYTES, "shared region too small");
+    const size_t smem = RING_BYTES + SHARED_BYTES;
     sanic_set_device(ctx);
-    SANIC_CUDA_CHECK(ctx, cudaFuncSetAttribute(decode_step_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    const void* kernel = group == 1 ? (any_i4 ? (const void*)decode_step_kernel<2, true> : (const void*)decode_step_kernel<2, false>)
+                                    : (any_i4 ? (const void*)decode_step_kernel<1, true> : (const void*)decode_step_kernel<1, false>);
+    SANIC_CUDA_CHECK(ctx, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     int per_sm = 0;
-    SANIC_CUDA_CHECK(ctx, cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, decode_step_kernel, THREADS, smem));
+    SANIC_CUDA_CHECK(ctx, cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, THREADS, smem));
     if (per_sm < 1) return sanic_fail(ctx, SANIC_ERR_UNSUPPORTED, "step: the persistent kernel does not fit on an SM");
     int coop = 0;
     SANIC_CUDA_CHECK(ctx, cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, ctx->device));
@@ -369,6 +615,7 @@ int32_t build(sanic_ctx* ctx, const std::vector<sanic_stage_desc>& stages, Plan*
     Plan* plan = new (std::nothrow) Plan();
     if (!plan) return SANIC_ERR_NOMEM;
     plan->n = (int)ph.size();
+    plan->kernel = kernel;
     plan->grid = ctx->sm_count;     // one block per SM: each phase body may use the whole register file
     plan->smem = smem;
     cudaError_t e = cudaMalloc(&plan->d_phases, ph.size() * sizeof(Phase));
@@ -390,7 +637,7 @@ int32_t launch(sanic_ctx* ctx, Plan* plan, cudaStream_t stream) {
     int* err = ctx->status_dev;
     unsigned long long* stamps = plan->d_stamps;
     void* args[] = {(void*)&phases_arg, (void*)&n, (void*)&bar, (void*)&err, (void*)&stamps};
-    cudaError_t e = cudaLaunchCooperativeKernel((const void*)decode_step_kernel, dim3(plan->grid), dim3(THREADS), args, plan->smem, stream);
+    cudaError_t e = cudaLaunchCooperativeKernel(plan->kernel, dim3(plan->grid), dim3(THREADS), args, plan->smem, stream);
     if (e != cudaSuccess) return sanic_fail(ctx, SANIC_ERR_CUDA, std::string("step: ") + cudaGetErrorString(e));
     return SANIC_OK;
 }

@@ -54,8 +54,17 @@ __device__ __forceinline__ uint4 load_x8(const uint16_t* xrow, const float* xf, 
     return r;
 }
 
+// Block barrier of the tile's GW*32 threads: the CTA barrier in a stand-alone kernel; in the persistent
+// step the block also holds a producer warp that never joins, so the consumers meet on a named barrier.
+template <bool PERSIST>
+__device__ __forceinline__ void block_sync() {
+    if (PERSIST) asm volatile("bar.sync 2, 256;" ::: "memory");
+    else __syncthreads();
+}
+
 // 1/sqrt(mean(x^2) + eps) of every activation row into scratch[0..batch): every warp sums its eighth of each
 // row, so the norm costs one load round trip, not sixteen. All GW*32 threads of the block call this.
+// L2READ is also the persistent-step form (reads through L2, consumer barrier).
 template <bool L2READ>
 __device__ __forceinline__ void row_norms(const Fused& fz, int batch, int K, float* scratch) {
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -72,14 +81,14 @@ __device__ __forceinline__ void row_norms(const Fused& fz, int batch, int K, flo
         ss = warp_sum(ss);
         if (lane == 0) s_part[n][warp] = ss;
     }
-    __syncthreads();
+    block_sync<L2READ>();
     if (tid < batch) {
         float tot = 0.0f;
 #pragma unroll
         for (int w = 0; w < GW; ++w) tot += s_part[tid][w];
         s_den[tid] = 1.0f / sqrtf(tot * (1.0f / (float)K) + fz.norm_eps);
     }
-    __syncthreads();
+    block_sync<L2READ>();
 }
 
 // Shared scratch one tile needs, in floats: row norms [16], their per-warp parts [16][GW], the per-warp
@@ -87,6 +96,108 @@ __device__ __forceinline__ void row_norms(const Fused& fz, int batch, int K, flo
 template <int NT, bool DUAL>
 __host__ __device__ constexpr int scratch_floats() {
     return 16 + 16 * GW + (GW + 1) * (DUAL ? 2 : 1) * 16 * (8 * NT + 1);
+}
+
+// Second half of a tile: the GW warps' partial sums are added in a fixed order, then the epilogue runs.
+template <int NT, bool DUAL, bool PERSIST>
+__device__ __forceinline__ void tile_finish(float (&acc)[DUAL ? 2 : 1][NT][4], int batch, const SegTable& segs, int out_dtype,
+                                            int epilogue, const float* residual, const Fused& fz, int KS, int krank, int seg,
+                                            int tile, float* scratch) {
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int g = lane >> 2, t = lane & 3;
+    constexpr int NM = DUAL ? 2 : 1, RW = 8 * NT + 1;
+    float (*red)[NM][16][RW] = reinterpret_cast<float (*)[NM][16][RW]>(scratch + 16 + 16 * GW);            // [GW][NM][16][RW]
+    float (*csum)[16][RW] = reinterpret_cast<float (*)[16][RW]>(scratch + 16 + 16 * GW + GW * NM * 16 * RW);  // [NM][16][RW]
+    const bool rope = (epilogue == SANIC_EPI_ROPE_CACHE);
+    // deterministic cross-warp sum: red[warp][matrix][row 0..15][col 0..8*NT)
+#pragma unroll
+    for (int mI = 0; mI < NM; ++mI)
+#pragma unroll
+        for (int j = 0; j < NT; ++j) {
+            red[warp][mI][g][8 * j + 2 * t] = acc[mI][j][0];
+            red[warp][mI][g][8 * j + 2 * t + 1] = acc[mI][j][1];
+            red[warp][mI][g + 8][8 * j + 2 * t] = acc[mI][j][2];
+            red[warp][mI][g + 8][8 * j + 2 * t + 1] = acc[mI][j][3];
+        }
+    block_sync<PERSIST>();
+    // CTA sum in a fixed warp order, then (KS > 1) the cluster's CTAs are summed in rank order by
+    // rank 0 through distributed shared memory: deterministic, no global scratch.
+    for (int idx = tid; idx < NM * 16 * 8 * NT; idx += GW * 32) {
+        const int n = idx % (8 * NT), r = (idx / (8 * NT)) % 16, mI = idx / (8 * NT * 16);
+        float sv = 0.0f;
+#pragma unroll
+        for (int w = 0; w < GW; ++w) sv += red[w][mI][r][n];
+        csum[mI][r][n] = sv;
+    }
+    block_sync<PERSIST>();
+    if (KS > 1) {
+        asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+        if (krank == 0) {
+            for (int idx = tid; idx < NM * 16 * 8 * NT; idx += GW * 32) {
+                const int n = idx % (8 * NT), r = (idx / (8 * NT)) % 16, mI = idx / (8 * NT * 16);
+                float sv = csum[mI][r][n];
+                const uint32_t local = smem_u32(&csum[mI][r][n]);
+                for (int kr = 1; kr < KS; ++kr) {
+                    uint32_t remote; float v;
+                    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(kr));
+                    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote));
+                    sv += v;
+                }
+                red[0][mI][r][n] = sv;     // rank 0 publishes the cluster total for its epilogue
+            }
+        }
+        // peers stay alive until rank 0 has read their shared memory
+        asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+        if (krank != 0) return;
+        block_sync<PERSIST>();
+    } else {
+        for (int idx = tid; idx < NM * 16 * 8 * NT; idx += GW * 32) {
+            const int n = idx % (8 * NT), r = (idx / (8 * NT)) % 16, mI = idx / (8 * NT * 16);
+            red[0][mI][r][n] = csum[mI][r][n];
+        }
+        block_sync<PERSIST>();
+    }
+    if (rope) {
+        // thread (r < 8, n): partners a = row r (d0 = 8*sub + r) and b = row r + 8 (d0 + D/2)
+        const int D = fz.head_dim, F = D / 2, tph = D / 16;
+        const int head = tile / tph, sub = tile % tph;
+        const int pos = *fz.rope_position;
+        for (int idx = tid; idx < 8 * batch; idx += GW * 32) {
+            const int n = idx / 8, r = idx % 8;
+            const float a = red[0][0][r][n], b = red[0][0][r + 8][n];
+            const int d0 = 8 * sub + r;
+            if (pos < 0 || pos >= fz.ctx) continue;
+            if (seg < 2) {
+                const float* cs = fz.rope_table + 2 * ((size_t)pos * F + d0);
+                const float c = cs[0], sn = cs[1];
+                const uint16_t o0 = f32_to_bf16_bits(a * c + (-b) * sn), o1 = f32_to_bf16_bits(b * c + a * sn);
+                uint16_t* dst = (seg == 0) ? fz.rope_q_out + ((size_t)n * fz.q_heads + head) * D
+                                           : fz.rope_k_cache + (((size_t)n * fz.kv_heads + head) * fz.ctx + pos) * D;
+                dst[d0] = o0; dst[d0 + F] = o1;
+            } else {
+                uint16_t* dst = fz.rope_v_cache + ((size_t)n * fz.kv_heads + head) * D * (size_t)fz.ctx;
+                dst[(size_t)d0 * fz.ctx + pos] = f32_to_bf16_bits(a);
+                dst[(size_t)(d0 + F) * fz.ctx + pos] = f32_to_bf16_bits(b);
+            }
+        }
+        return;
+    }
+    const int row0 = tile * 16;
+    const int rows = seg == 0 ? segs.rows[0] : (seg == 1 ? segs.rows[1] : segs.rows[2]);
+    void* outp = seg == 0 ? segs.out[0] : (seg == 1 ? segs.out[1] : segs.out[2]);
+    for (int idx = tid; idx < 16 * batch; idx += GW * 32) {
+        int n = idx / 16, r = idx % 16;  // consecutive threads -> consecutive rows (contiguous in out[n][row])
+        float y = red[0][0][r][n];
+        if (DUAL) {  // silu(a) * b = (a * 1/(1+exp(-a))) * b  (reference src/ir.rs:1500-1509)
+            const float ga = y, up = red[0][NM - 1][r][n];
+            float sig = 1.0f / (1.0f + expf(-ga));
+            y = (ga * sig) * up;
+        }
+        size_t oi = (size_t)n * rows + row0 + r;
+        if (epilogue == SANIC_EPI_RESIDUAL_ADD) y = (PERSIST ? __ldcg(residual + oi) : residual[oi]) + y;
+        if (out_dtype == SANIC_BF16) ((uint16_t*)outp)[oi] = f32_to_bf16_bits(y);
+        else ((float*)outp)[oi] = y;
+    }
 }
 
 // One row tile of the contraction. `block` is the linear block index (tile * KS + K-rank); `pdl` says
@@ -99,10 +210,7 @@ __device__ __forceinline__ void gemv_tile(const uint16_t* __restrict__ x, int ba
                                           const Fused& fz, int KS, int block, bool pdl, float* scratch) {
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     // carve the caller's shared scratch (scratch_floats<NT, DUAL>() floats)
-    constexpr int NMs = DUAL ? 2 : 1, RW = 8 * NT + 1;
     float* s_den = scratch;                                                                                  // [16]
-    float (*red)[NMs][16][RW] = reinterpret_cast<float (*)[NMs][16][RW]>(scratch + 16 + 16 * GW);            // [GW][NM][16][RW]
-    float (*csum)[16][RW] = reinterpret_cast<float (*)[16][RW]>(scratch + 16 + 16 * GW + GW * NMs * 16 * RW);  // [NM][16][RW]
     const int g = lane >> 2, t = lane & 3;
     // KS CTAs of one thread-block cluster share a row tile and split K between them
     const int gtile = block / KS, krank = block % KS;
@@ -294,95 +402,7 @@ __device__ __forceinline__ void gemv_tile(const uint16_t* __restrict__ x, int ba
         }
     }
 
-    // deterministic cross-warp sum: red[warp][matrix][row 0..15][col 0..8*NT)
-#pragma unroll
-    for (int mI = 0; mI < NM; ++mI)
-#pragma unroll
-        for (int j = 0; j < NT; ++j) {
-            red[warp][mI][g][8 * j + 2 * t] = acc[mI][j][0];
-            red[warp][mI][g][8 * j + 2 * t + 1] = acc[mI][j][1];
-            red[warp][mI][g + 8][8 * j + 2 * t] = acc[mI][j][2];
-            red[warp][mI][g + 8][8 * j + 2 * t + 1] = acc[mI][j][3];
-        }
-    __syncthreads();
-    // CTA sum in a fixed warp order, then (KS > 1) the cluster's CTAs are summed in rank order by
-    // rank 0 through distributed shared memory: deterministic, no global scratch.
-    for (int idx = tid; idx < NM * 16 * 8 * NT; idx += GW * 32) {
-        const int n = idx % (8 * NT), r = (idx / (8 * NT)) % 16, mI = idx / (8 * NT * 16);
-        float sv = 0.0f;
-#pragma unroll
-        for (int w = 0; w < GW; ++w) sv += red[w][mI][r][n];
-        csum[mI][r][n] = sv;
-    }
-    __syncthreads();
-    if (KS > 1) {
-        asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-        if (krank == 0) {
-            for (int idx = tid; idx < NM * 16 * 8 * NT; idx += GW * 32) {
-                const int n = idx % (8 * NT), r = (idx / (8 * NT)) % 16, mI = idx / (8 * NT * 16);
-                float sv = csum[mI][r][n];
-                const uint32_t local = smem_u32(&csum[mI][r][n]);
-                for (int kr = 1; kr < KS; ++kr) {
-                    uint32_t remote; float v;
-                    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(kr));
-                    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote));
-                    sv += v;
-                }
-                red[0][mI][r][n] = sv;     // rank 0 publishes the cluster total for its epilogue
-            }
-        }
-        // peers stay alive until rank 0 has read their shared memory
-        asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-        if (krank != 0) return;
-        __syncthreads();
-    } else {
-        for (int idx = tid; idx < NM * 16 * 8 * NT; idx += GW * 32) {
-            const int n = idx % (8 * NT), r = (idx / (8 * NT)) % 16, mI = idx / (8 * NT * 16);
-            red[0][mI][r][n] = csum[mI][r][n];
-        }
-        __syncthreads();
-    }
-    if (rope) {
-        // thread (r < 8, n): partners a = row r (d0 = 8*sub + r) and b = row r + 8 (d0 + D/2)
-        const int D = fz.head_dim, F = D / 2, tph = D / 16;
-        const int head = tile / tph, sub = tile % tph;
-        const int pos = *fz.rope_position;
-        for (int idx = tid; idx < 8 * batch; idx += GW * 32) {
-            const int n = idx / 8, r = idx % 8;
-            const float a = red[0][0][r][n], b = red[0][0][r + 8][n];
-            const int d0 = 8 * sub + r;
-            if (pos < 0 || pos >= fz.ctx) continue;
-            if (seg < 2) {
-                const float* cs = fz.rope_table + 2 * ((size_t)pos * F + d0);
-                const float c = cs[0], sn = cs[1];
-                const uint16_t o0 = f32_to_bf16_bits(a * c + (-b) * sn), o1 = f32_to_bf16_bits(b * c + a * sn);
-                uint16_t* dst = (seg == 0) ? fz.rope_q_out + ((size_t)n * fz.q_heads + head) * D
-                                           : fz.rope_k_cache + (((size_t)n * fz.kv_heads + head) * fz.ctx + pos) * D;
-                dst[d0] = o0; dst[d0 + F] = o1;
-            } else {
-                uint16_t* dst = fz.rope_v_cache + ((size_t)n * fz.kv_heads + head) * D * (size_t)fz.ctx;
-                dst[(size_t)d0 * fz.ctx + pos] = f32_to_bf16_bits(a);
-                dst[(size_t)(d0 + F) * fz.ctx + pos] = f32_to_bf16_bits(b);
-            }
-        }
-        return;
-    }
-    const int row0 = tile * 16;
-    const int rows = seg == 0 ? segs.rows[0] : (seg == 1 ? segs.rows[1] : segs.rows[2]);
-    void* outp = seg == 0 ? segs.out[0] : (seg == 1 ? segs.out[1] : segs.out[2]);
-    for (int idx = tid; idx < 16 * batch; idx += GW * 32) {
-        int n = idx / 16, r = idx % 16;  // consecutive threads -> consecutive rows (contiguous in out[n][row])
-        float y = red[0][0][r][n];
-        if (DUAL) {  // silu(a) * b = (a * 1/(1+exp(-a))) * b  (reference src/ir.rs:1500-1509)
-            const float ga = y, up = red[0][NM - 1][r][n];
-            float sig = 1.0f / (1.0f + expf(-ga));
-            y = (ga * sig) * up;
-        }
-        size_t oi = (size_t)n * rows + row0 + r;
-        if (epilogue == SANIC_EPI_RESIDUAL_ADD) y = (PERSIST ? __ldcg(residual + oi) : residual[oi]) + y;
-        if (out_dtype == SANIC_BF16) ((uint16_t*)outp)[oi] = f32_to_bf16_bits(y);
-        else ((float*)outp)[oi] = y;
-    }
+    tile_finish<NT, DUAL, PERSIST>(acc, batch, segs, out_dtype, epilogue, residual, fz, KS, krank, seg, tile, scratch);
 }
 
 // Host side: validate one contraction and build the kernel's segment table. `tiles` is the number of
