@@ -27,11 +27,12 @@ namespace {
 
 enum { PH_GEMV = 1, PH_DECODE, PH_EMBED, PH_RMSNORM, PH_ARGMAX_PART, PH_ARGMAX_FINAL, PH_ADVANCE };
 constexpr int CONSUMERS = 256;              // warps 0-7: the phase bodies
-constexpr int THREADS = CONSUMERS + 32;     // warp 8: the weight producer
+constexpr int PRODUCERS = 4;                // warps 8..: the weight producers, ring stages dealt round-robin
+constexpr int THREADS = CONSUMERS + 32 * PRODUCERS;
 constexpr int AMAX_CHUNKS = 128;
 constexpr unsigned SPIN_LIMIT = 1u << 22;
 constexpr int SLOTS = 4;                    // weight ring
-constexpr int SLOT_BYTES = 34816;           // 32 rows x (1024 + 64) B, the largest stage
+constexpr int SLOT_BYTES = 35840;           // the largest stage: 32 int4 rows x (1024 + 32) B + 32 x 64 B of scales
 constexpr int SCRATCH_BYTES = 20480;        // contraction scratch (row norms, cross-warp sums) | pointwise scratch
 constexpr int XS_BYTES = 66560;             // a phase's activations, bf16, norm applied: 16 rows x (2048 + 32) x 2 B
 constexpr int SHARED_BYTES = SCRATCH_BYTES + XS_BYTES;   // the attention K/V ring overlays both
@@ -50,16 +51,19 @@ struct Phase {
     int i0, i1, i2; float f0;
 };
 
-// One ring stage of a contraction: `rows` weight rows (16, or 32 for the silu-mul pair) x `stage_k` inputs.
-struct Geom { int stage_k, n_stages, rows, row_bytes, pitch; };
+// One ring stage of a contraction: `rows` weight rows (16, or 32 for the silu-mul pair) x `stage_k` inputs, about
+// 32 KB, each row one bulk copy of 1-2 KB; int4 stages carry their bf16 group scales behind the weights.
+struct Geom { int stage_k, n_stages, rows, row_bytes, pitch, scale_off, scale_row_bytes; };
 __host__ __device__ inline Geom geom_of(bool w4, bool dual, int K) {
     Geom g;
-    const int cap = dual ? 512 : 1024;
+    const int cap = (dual ? 512 : 1024) * (w4 ? 4 : 1);
     g.stage_k = K < cap ? K : cap;
     g.n_stages = K / g.stage_k;
     g.rows = dual ? 32 : 16;
     g.row_bytes = w4 ? g.stage_k / 2 : g.stage_k * 2;
     g.pitch = g.row_bytes + (w4 ? 32 : 64);      // rows land 4 bank groups apart: conflict-free fragment reads
+    g.scale_off = g.rows * g.pitch;
+    g.scale_row_bytes = (w4 && g.stage_k >= 512) ? g.stage_k / 64 * 2 : 0;   // 0: too short for a bulk copy, read from global
     return g;
 }
 
@@ -122,15 +126,15 @@ __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 2, 256;
 __device__ __forceinline__ bool grid_barrier(unsigned* bar, unsigned target, int* err, int* s_ok) {
     consumer_sync();
     if (threadIdx.x == 0) {
-        __threadfence();
-        atomicAdd(bar, 1u);
+        // Release-arrive without waiting for the old value, then acquire-poll: the block barrier before orders the
+        // other threads' writes ahead of this release, the one after hands the acquired view to them.
+        asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(bar) : "memory");
         int ok = 1;
         unsigned spins = 0;
         while (ld_acquire(bar) < target) {
             if ((++spins & 63u) == 0 && ld_acquire(bar + 1) != 0) { ok = 0; break; }
             if (spins > SPIN_LIMIT) { atomicExch(bar + 1, 1u); atomicCAS(err, 0, 31); ok = 0; break; }
         }
-        __threadfence();
         *s_ok = ok;
     }
     consumer_sync();
@@ -176,7 +180,6 @@ __device__ __forceinline__ bool consume_gemv(const Phase& P, const Ring& ring, u
     const bool xok0 = g < P.batch, xok1 = NT > 1 && (g + 8) < P.batch;
     const unsigned char* xs0 = xs + (size_t)(xok0 ? g : 0) * xpitch;
     const unsigned char* xs1 = xs + (size_t)(xok1 ? g + 8 : 0) * xpitch;
-    constexpr int MAXU = W4 ? 2 : 4;         // units per warp per stage at the largest stage (1024 / UNIT / 8)
     bool ok = true;
     for (int gt = blockIdx.x; gt < P.n_blocks && ok; gt += gridDim.x) {
         int seg, tile;
@@ -186,9 +189,9 @@ __device__ __forceinline__ bool consume_gemv(const Phase& P, const Ring& ring, u
         for (int mI = 0; mI < NM; ++mI)
 #pragma unroll
             for (int j = 0; j < NT; ++j) acc[mI][j][0] = acc[mI][j][1] = acc[mI][j][2] = acc[mI][j][3] = 0.0f;
-        // int4: scale rows of fragment rows g and g+8
+        // int4 with stages too short to carry their scales: scale rows of fragment rows g and g+8 in global memory
         const uint16_t* sr[NM][2];
-        if (W4) {
+        if (W4 && G.scale_row_bytes == 0) {
 #pragma unroll
             for (int mI = 0; mI < NM; ++mI) {
                 const int si = DUAL ? mI : seg;
@@ -203,78 +206,72 @@ __device__ __forceinline__ bool consume_gemv(const Phase& P, const Ring& ring, u
             const int kbase = s * G.stage_k;
             const int xbase = whole ? 0 : kbase;
             if (!whole) { consumer_sync(); stage_x(kbase); consumer_sync(); }
-            // activations (and scales) of this warp's units first: their L2 latency hides behind the wait for the weights
-            uint4 xb[MAXU][NT][W4 ? 2 : 1];
-            float sc[MAXU][NM][2];
+            ok = mbar_wait(&ring.full[slot], parity, gbar, err, 32);
+            if (!ok) break;
+            const unsigned char* sb = ring.ptr + (size_t)slot * SLOT_BYTES;
+#pragma unroll 2
+            for (int u = u0; u < u1; ++u) {
+                const int ku = u * UNIT;                 // offset inside the stage
+                const int kx = kbase + ku - xbase;       // offset inside the staged activations
+                if (!W4) {
+                    uint4 xv[NT];
 #pragma unroll
-            for (int u = 0; u < MAXU; ++u) {
-                if (u0 + u < u1) {
-                    const int k = kbase + (u0 + u) * UNIT;
+                    for (int j = 0; j < NT; ++j) {
+                        const unsigned char* xr = j == 0 ? xs0 : xs1;
+                        xv[j] = (j == 0 ? xok0 : xok1) ? *(const uint4*)(xr + (size_t)(kx + t * 8) * 2) : make_uint4(0, 0, 0, 0);
+                    }
+#pragma unroll
+                    for (int mI = 0; mI < NM; ++mI) {
+                        const uint4 r0 = *(const uint4*)(sb + (size_t)(mI * 16 + g) * G.pitch + (ku + t * 8) * 2);
+                        const uint4 r1 = *(const uint4*)(sb + (size_t)(mI * 16 + g + 8) * G.pitch + (ku + t * 8) * 2);
+#pragma unroll
+                        for (int j = 0; j < NT; ++j) {
+                            mma_bf16_16816(acc[mI][j], r0.x, r1.x, r0.y, r1.y, xv[j].x, xv[j].y);
+                            mma_bf16_16816(acc[mI][j], r0.z, r1.z, r0.w, r1.w, xv[j].z, xv[j].w);
+                        }
+                    }
+                } else {
+                    const uint32_t ONES = 0x3F803F80u;
+                    float sc[NM][2];
+#pragma unroll
+                    for (int mI = 0; mI < NM; ++mI) {
+                        if (G.scale_row_bytes) {
+                            sc[mI][0] = bf16_to_f32(*(const uint16_t*)(sb + G.scale_off + (size_t)(mI * 16 + g) * G.scale_row_bytes + u * 2));
+                            sc[mI][1] = bf16_to_f32(*(const uint16_t*)(sb + G.scale_off + (size_t)(mI * 16 + g + 8) * G.scale_row_bytes + u * 2));
+                        } else {
+                            sc[mI][0] = bf16_to_f32(__ldg(sr[mI][0] + (kbase + ku) / 64));
+                            sc[mI][1] = bf16_to_f32(__ldg(sr[mI][1] + (kbase + ku) / 64));
+                        }
+                    }
 #pragma unroll
                     for (int j = 0; j < NT; ++j) {
                         const unsigned char* xr = j == 0 ? xs0 : xs1;
                         const bool xk = j == 0 ? xok0 : xok1;
-                        const int kk = k - xbase + (W4 ? t * 16 : t * 8);
-                        xb[u][j][0] = xk ? *(const uint4*)(xr + (size_t)kk * 2) : make_uint4(0, 0, 0, 0);
-                        if (W4) xb[u][j][W4 ? 1 : 0] = xk ? *(const uint4*)(xr + (size_t)(kk + 8) * 2) : make_uint4(0, 0, 0, 0);
-                    }
-                    if (W4) {
+                        const uint4 xa = xk ? *(const uint4*)(xr + (size_t)(kx + t * 16) * 2) : make_uint4(0, 0, 0, 0);
+                        const uint4 xc = xk ? *(const uint4*)(xr + (size_t)(kx + t * 16 + 8) * 2) : make_uint4(0, 0, 0, 0);
+                        // activation pairs matching the nibble pairing (n_i, n_{i+4})
+                        const uint32_t bA0 = prmt(xa.x, xa.z, 0x5410), bA1 = prmt(xa.x, xa.z, 0x7632);
+                        const uint32_t bA2 = prmt(xa.y, xa.w, 0x5410), bA3 = prmt(xa.y, xa.w, 0x7632);
+                        const uint32_t bC0 = prmt(xc.x, xc.z, 0x5410), bC1 = prmt(xc.x, xc.z, 0x7632);
+                        const uint32_t bC2 = prmt(xc.y, xc.w, 0x5410), bC3 = prmt(xc.y, xc.w, 0x7632);
+                        float c1[4] = {0, 0, 0, 0};
+                        mma_bf16_16816(c1, ONES, ONES, ONES, ONES, bA0, bA1);
+                        mma_bf16_16816(c1, ONES, ONES, ONES, ONES, bA2, bA3);
+                        mma_bf16_16816(c1, ONES, ONES, ONES, ONES, bC0, bC1);
+                        mma_bf16_16816(c1, ONES, ONES, ONES, ONES, bC2, bC3);
 #pragma unroll
                         for (int mI = 0; mI < NM; ++mI) {
-                            sc[u][mI][0] = bf16_to_f32(__ldg(sr[mI][0] + k / 64));
-                            sc[u][mI][1] = bf16_to_f32(__ldg(sr[mI][1] + k / 64));
-                        }
-                    }
-                }
-            }
-            ok = mbar_wait(&ring.full[slot], parity, gbar, err, 32);
-            if (!ok) break;
-            const unsigned char* sb = ring.ptr + (size_t)slot * SLOT_BYTES;
-#pragma unroll
-            for (int u = 0; u < MAXU; ++u) {
-                if (u0 + u < u1) {
-                    const int ku = (u0 + u) * UNIT;          // offset inside the stage
-                    if (!W4) {
-#pragma unroll
-                        for (int mI = 0; mI < NM; ++mI) {
-                            const uint4 r0 = *(const uint4*)(sb + (size_t)(mI * 16 + g) * G.pitch + (ku + t * 8) * 2);
-                            const uint4 r1 = *(const uint4*)(sb + (size_t)(mI * 16 + g + 8) * G.pitch + (ku + t * 8) * 2);
-#pragma unroll
-                            for (int j = 0; j < NT; ++j) {
-                                const uint4& xv = xb[u][j][0];
-                                mma_bf16_16816(acc[mI][j], r0.x, r1.x, r0.y, r1.y, xv.x, xv.y);
-                                mma_bf16_16816(acc[mI][j], r0.z, r1.z, r0.w, r1.w, xv.z, xv.w);
-                            }
-                        }
-                    } else {
-                        const uint32_t ONES = 0x3F803F80u;
-#pragma unroll
-                        for (int j = 0; j < NT; ++j) {
-                            const uint4 xa = xb[u][j][0], xc = xb[u][j][W4 ? 1 : 0];
-                            // activation pairs matching the nibble pairing (n_i, n_{i+4})
-                            const uint32_t bA0 = prmt(xa.x, xa.z, 0x5410), bA1 = prmt(xa.x, xa.z, 0x7632);
-                            const uint32_t bA2 = prmt(xa.y, xa.w, 0x5410), bA3 = prmt(xa.y, xa.w, 0x7632);
-                            const uint32_t bC0 = prmt(xc.x, xc.z, 0x5410), bC1 = prmt(xc.x, xc.z, 0x7632);
-                            const uint32_t bC2 = prmt(xc.y, xc.w, 0x5410), bC3 = prmt(xc.y, xc.w, 0x7632);
-                            float c1[4] = {0, 0, 0, 0};
-                            mma_bf16_16816(c1, ONES, ONES, ONES, ONES, bA0, bA1);
-                            mma_bf16_16816(c1, ONES, ONES, ONES, ONES, bA2, bA3);
-                            mma_bf16_16816(c1, ONES, ONES, ONES, ONES, bC0, bC1);
-                            mma_bf16_16816(c1, ONES, ONES, ONES, ONES, bC2, bC3);
-#pragma unroll
-                            for (int mI = 0; mI < NM; ++mI) {
-                                const uint2 w0 = *(const uint2*)(sb + (size_t)(mI * 16 + g) * G.pitch + ku / 2 + t * 8);
-                                const uint2 w1 = *(const uint2*)(sb + (size_t)(mI * 16 + g + 8) * G.pitch + ku / 2 + t * 8);
-                                float c[4] = {0, 0, 0, 0};
-                                mma_bf16_16816(c, nib_pair(w0.x), nib_pair(w1.x), nib_pair(w0.x >> 4), nib_pair(w1.x >> 4), bA0, bA1);
-                                mma_bf16_16816(c, nib_pair(w0.x >> 8), nib_pair(w1.x >> 8), nib_pair(w0.x >> 12), nib_pair(w1.x >> 12), bA2, bA3);
-                                mma_bf16_16816(c, nib_pair(w0.y), nib_pair(w1.y), nib_pair(w0.y >> 4), nib_pair(w1.y >> 4), bC0, bC1);
-                                mma_bf16_16816(c, nib_pair(w0.y >> 8), nib_pair(w1.y >> 8), nib_pair(w0.y >> 12), nib_pair(w1.y >> 12), bC2, bC3);
-                                acc[mI][j][0] = fmaf(sc[u][mI][0], fmaf(-136.0f, c1[0], c[0]), acc[mI][j][0]);
-                                acc[mI][j][1] = fmaf(sc[u][mI][0], fmaf(-136.0f, c1[1], c[1]), acc[mI][j][1]);
-                                acc[mI][j][2] = fmaf(sc[u][mI][1], fmaf(-136.0f, c1[2], c[2]), acc[mI][j][2]);
-                                acc[mI][j][3] = fmaf(sc[u][mI][1], fmaf(-136.0f, c1[3], c[3]), acc[mI][j][3]);
-                            }
+                            const uint2 w0 = *(const uint2*)(sb + (size_t)(mI * 16 + g) * G.pitch + ku / 2 + t * 8);
+                            const uint2 w1 = *(const uint2*)(sb + (size_t)(mI * 16 + g + 8) * G.pitch + ku / 2 + t * 8);
+                            float c[4] = {0, 0, 0, 0};
+                            mma_bf16_16816(c, nib_pair(w0.x), nib_pair(w1.x), nib_pair(w0.x >> 4), nib_pair(w1.x >> 4), bA0, bA1);
+                            mma_bf16_16816(c, nib_pair(w0.x >> 8), nib_pair(w1.x >> 8), nib_pair(w0.x >> 12), nib_pair(w1.x >> 12), bA2, bA3);
+                            mma_bf16_16816(c, nib_pair(w0.y), nib_pair(w1.y), nib_pair(w0.y >> 4), nib_pair(w1.y >> 4), bC0, bC1);
+                            mma_bf16_16816(c, nib_pair(w0.y >> 8), nib_pair(w1.y >> 8), nib_pair(w0.y >> 12), nib_pair(w1.y >> 12), bC2, bC3);
+                            acc[mI][j][0] = fmaf(sc[mI][0], fmaf(-136.0f, c1[0], c[0]), acc[mI][j][0]);
+                            acc[mI][j][1] = fmaf(sc[mI][0], fmaf(-136.0f, c1[1], c[1]), acc[mI][j][1]);
+                            acc[mI][j][2] = fmaf(sc[mI][1], fmaf(-136.0f, c1[2], c[2]), acc[mI][j][2]);
+                            acc[mI][j][3] = fmaf(sc[mI][1], fmaf(-136.0f, c1[3], c[3]), acc[mI][j][3]);
                         }
                     }
                 }
@@ -330,7 +327,7 @@ decode_step_kernel(const Phase* __restrict__ phases, int n_phases, unsigned* bar
         // ── producer warp: streams the weights of every contraction phase, in the order the consumers will want
         //    them, as far ahead as the ring allows. Weights never change, so it may run ahead of the grid barriers;
         //    HBM keeps streaming while the consumers wait for activations. ──
-        const int lane = tid - CONSUMERS;
+        const int lane = tid & 31, pw = (tid - CONSUMERS) >> 5;
         unsigned fill = 0;
         bool ok = true;
         for (int i = 0; i < n_phases && ok; ++i) {
@@ -343,25 +340,36 @@ decode_step_kernel(const Phase* __restrict__ phases, int n_phases, unsigned* bar
                 int seg, tile;
                 seg_of_tile(P.segs, P.n_segments, dual, gt, seg, tile);
                 const char* src_row = nullptr;
+                const char* src_scale = nullptr;
                 if (lane < G.rows) {
                     const int mI = lane >> 4, r = lane & 15;
                     const int si = dual ? mI : seg;
                     const char* W = (const char*)(si == 0 ? P.segs.w[0] : (si == 1 ? P.segs.w[1] : P.segs.w[2]));
-                    src_row = W + (size_t)weight_row(P.epilogue, P.fz, tile, r) * full_row;
+                    const int wr = weight_row(P.epilogue, P.fz, tile, r);
+                    src_row = W + (size_t)wr * full_row;
+                    if (G.scale_row_bytes) {
+                        const char* S = (const char*)(si == 0 ? P.segs.scales[0] : (si == 1 ? P.segs.scales[1] : P.segs.scales[2]));
+                        src_scale = S + (size_t)wr * (P.K / 64) * 2;
+                    }
                 }
                 for (int s = 0; s < G.n_stages && ok; ++s, ++fill) {
+                    if ((int)(fill % PRODUCERS) != pw) continue;
                     const int slot = fill % SLOTS;
                     if (lane == 0) {
                         ok = mbar_wait(&s_empty[slot], ((fill / SLOTS) & 1) ^ 1, bar, err, 33);
-                        if (ok) mbar_expect_tx(&s_full[slot], (uint32_t)(G.rows * G.row_bytes));
+                        if (ok) mbar_expect_tx(&s_full[slot], (uint32_t)(G.rows * (G.row_bytes + G.scale_row_bytes)));
                     }
                     ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-                    if (ok && lane < G.rows)
+                    if (ok && lane < G.rows) {
                         bulk_load(ring.base + slot * SLOT_BYTES + lane * G.pitch, src_row + (size_t)s * G.row_bytes, (uint32_t)G.row_bytes, &s_full[slot]);
+                        if (G.scale_row_bytes)
+                            bulk_load(ring.base + slot * SLOT_BYTES + G.scale_off + lane * G.scale_row_bytes,
+                                      src_scale + (size_t)s * G.scale_row_bytes, (uint32_t)G.scale_row_bytes, &s_full[slot]);
+                    }
                 }
             }
         }
-        if (lane == 0) s_produced = fill;
+        if (lane == 0 && pw == 0) s_produced = fill;
     } else {
         // ── consumers: walk the phases ──
         uint32_t drained = 0;
@@ -379,10 +387,10 @@ decode_step_kernel(const Phase* __restrict__ phases, int n_phases, unsigned* bar
                         case 1: if (ANY_I4) ok = consume_gemv<true, NT, false, false>(P, ring, drained, scratch, bar, err); break;
                         case 2: ok = consume_gemv<false, NT, true, false>(P, ring, drained, scratch, bar, err); break;
                         case 3: if (ANY_I4) ok = consume_gemv<true, NT, true, false>(P, ring, drained, scratch, bar, err); break;
-                        case 4: if (NT == 1) ok = consume_gemv<false, 1, false, true>(P, ring, drained, scratch, bar, err); break;
-                        case 5: if (NT == 1 && ANY_I4) ok = consume_gemv<true, 1, false, true>(P, ring, drained, scratch, bar, err); break;
-                        case 6: if (NT == 1) ok = consume_gemv<false, 1, true, true>(P, ring, drained, scratch, bar, err); break;
-                        case 7: if (NT == 1 && ANY_I4) ok = consume_gemv<true, 1, true, true>(P, ring, drained, scratch, bar, err); break;
+                        case 4: ok = consume_gemv<false, NT, false, true>(P, ring, drained, scratch, bar, err); break;
+                        case 5: if (ANY_I4) ok = consume_gemv<true, NT, false, true>(P, ring, drained, scratch, bar, err); break;
+                        case 6: ok = consume_gemv<false, NT, true, true>(P, ring, drained, scratch, bar, err); break;
+                        case 7: if (ANY_I4) ok = consume_gemv<true, NT, true, true>(P, ring, drained, scratch, bar, err); break;
                     }
                     break;
                 }
@@ -544,7 +552,6 @@ int32_t build(sanic_ctx* ctx, const std::vector<sanic_stage_desc>& stages, Plan*
                 if (rc != SANIC_OK) return rc;
                 const bool w4 = g.weight_dtype == SANIC_I4, wide = g.batch > 8, dual = g.epilogue == SANIC_EPI_SILU_MUL,
                            norm = g.norm_x != nullptr;
-                if (norm && wide) return SANIC_ERR_UNSUPPORTED;
                 if (group >= 0 && group != (wide ? 1 : 0)) return SANIC_ERR_UNSUPPORTED;
                 group = wide ? 1 : 0;
                 any_i4 = any_i4 || w4;

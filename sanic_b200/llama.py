@@ -133,9 +133,9 @@ class LlamaMachine:
         self.partials = z((dev.lib.sanic_attn_decode_scratch_bytes(B, Hq, D, self.n_splits) // 4,), torch.float32)
         self.amax_scratch = z((B * 2 * 256,), torch.float32)
         self.stream = torch.cuda.Stream(device=td)
+        self.persistent = persistent
         self._build()
         self.captured = False
-        self.persistent = persistent
         if capture:
             self.capture()
 
@@ -173,7 +173,9 @@ class LlamaMachine:
         cfg, B = self.cfg, self.batch
         Hq, Hkv, D = cfg["q_heads"], cfg["kv_heads"], cfg["head_dim"]
         fused = self.fused
-        inline_norm = fused and B <= 4    # at larger batch every CTA re-deriving the normalised rows costs more than a launch
+        # as separate launches, every CTA re-deriving the normalised rows costs more than a launch at larger batch;
+        # the single-kernel step derives them once per stage, so it inlines the norm at any batch
+        inline_norm = fused and (B <= 4 or self.persistent)
         st = []
         s = abi.StageDesc()
         s.stage_kind, s.op = abi.STAGE_GATHER, abi.OP_EMBED

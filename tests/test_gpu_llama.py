@@ -93,6 +93,7 @@ def test_single_kernel_step(dev, batch, w4):
     assert m.kernel_count == 1
     times = m.step_stage_times()
     assert len(times) == m.n_stages + 1 and all(t >= 0.0 for t in times)      # argmax is two phases
+    assert m.n_stages == 1 + 5 * SMALL["layers"] + 3       # norms ride the projections at any batch in this form
 
 
 def test_batch16_and_replay_equals_eager(dev):
