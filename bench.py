@@ -149,7 +149,7 @@ def time_events(fn, steps, warmup, torch):
     return ts[len(ts) // 2] * 1e-3, ts[0] * 1e-3
 
 
-def suite(dev, torch, hbm_peak, tf_peak, quick, only=None, c2_shape=(4096, 2048, 8192), c3_shape=(8, 4096), fused=True, persistent=False):
+def suite(dev, torch, hbm_peak, tf_peak, quick, only=None, c2_shape=(4096, 2048, 8192), c3_shape=(8, 4096), fused=True, form="auto"):
     import numpy as np
     from sanic_b200 import llama
     out = {}
@@ -204,6 +204,8 @@ def suite(dev, torch, hbm_peak, tf_peak, quick, only=None, c2_shape=(4096, 2048,
         if not want("c4_" + name):
             continue
         w = llama.random_weights(cfg, 11, td, w4=w4)
+        # the step as one cooperative kernel wins at small batch, the captured launch list at batch 16 (measured)
+        persistent = fused and (form == "persistent" or (form == "auto" and batch <= 4))
         m = llama.LlamaMachine(dev, cfg, w, ctx=1088, batch=batch, w4=w4, fused=fused, persistent=persistent)
         rng = np.random.default_rng(3)
         # prefill 1024 positions from random token ids by decoding on the device
@@ -222,6 +224,7 @@ def suite(dev, torch, hbm_peak, tf_peak, quick, only=None, c2_shape=(4096, 2048,
         wb = m.weight_bytes()
         out[f"c4_llama_decode_{name}"] = {
             "tok_per_s": batch / sec, "ms_per_step": sec * 1e3, "launches_per_step": m.kernel_count,
+            "form": "one cooperative kernel" if persistent else "captured launch list",
             "algorithmic_bytes": wb + kv_bytes, "achieved_gbs": (wb + kv_bytes) / sec / 1e9,
             "frac_of_hbm_peak": (wb + kv_bytes) / sec / 1e9 / hbm_peak}
         del m, w
@@ -353,7 +356,7 @@ def run_ours(args):
     if rank == 0 and world == 1 and not args.no_suite:
         try:
             line["suite"] = suite(dev, torch, hbm_peak, tf_peak, args.quick, args.only.split(",") if args.only else None,
-                                  tuple(int(t) for t in args.c2_shape.split(",")), tuple(int(t) for t in args.c3_shape.split(",")), not args.llama_unfused, args.llama_persistent)
+                                  tuple(int(t) for t in args.c2_shape.split(",")), tuple(int(t) for t in args.c3_shape.split(",")), not args.llama_unfused, args.llama_form)
         except Exception as e:  # the headline line must still print
             line["suite"] = {"error": repr(e)}
     if rank == 0:
@@ -382,7 +385,8 @@ def main():
     ap.add_argument("--only", default="", help="comma-separated substrings of suite entries to run (c1,c2,c3,c4_bf16_b1,...)")
     ap.add_argument("--c2-shape", default="4096,2048,8192", help="M,K,N of the suite's GEMM (small cases for profiling)")
     ap.add_argument("--llama-unfused", action="store_true", help="one stage per graph cone in the decode step")
-    ap.add_argument("--llama-persistent", action="store_true", help="replay the decode step as one cooperative kernel instead of the launch list")
+    ap.add_argument("--llama-form", default="auto", choices=["auto", "list", "persistent"],
+                    help="decode step as the captured launch list, as one cooperative kernel, or whichever measured faster for the batch")
     ap.add_argument("--c3-shape", default="8,4096", help="batch,sequence of the suite's prefill attention")
     args = ap.parse_args()
     if args.warmup < 3:
