@@ -174,68 +174,8 @@ __device__ __forceinline__ bool consume_gemv(const Phase& P, const Ring& ring, u
             *(uint4*)(xs + (size_t)n * xpitch + c * 16) = v;
         }
     };
-    // Inlined norm at small batch: ONE pass over the f32 rows feeds both the sum of squares and the staged bf16
-    // activations (each thread keeps its chunks in registers across the block-wide sum), so the phase starts
-    // after one L2 round trip instead of two.
-    const int cpr_all = P.K / 8;
-    const bool one_pass = NORM && whole && (cpr_all % CONSUMERS == 0) && P.batch * (cpr_all / CONSUMERS) <= 4;
-    if (one_pass) {
-        const int per_row = cpr_all / CONSUMERS, cnt = P.batch * per_row;
-        float (*s_part)[GW] = reinterpret_cast<float (*)[GW]>(scratch + 16);
-        float4 va[4], vb[4];
-        float ssr[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            if (i < cnt) {
-                const float* src = P.fz.norm_x + (size_t)(i / per_row) * P.K + ((size_t)(i % per_row) * CONSUMERS + tid) * 8;
-                va[i] = __ldcg((const float4*)src); vb[i] = __ldcg((const float4*)(src + 4));
-            }
-        }
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            if (i < cnt) {
-                float ss = va[i].x * va[i].x;
-                ss = fmaf(va[i].y, va[i].y, ss); ss = fmaf(va[i].z, va[i].z, ss); ss = fmaf(va[i].w, va[i].w, ss);
-                ss = fmaf(vb[i].x, vb[i].x, ss); ss = fmaf(vb[i].y, vb[i].y, ss); ss = fmaf(vb[i].z, vb[i].z, ss); ss = fmaf(vb[i].w, vb[i].w, ss);
-                const int n = i / per_row;
-#pragma unroll
-                for (int r = 0; r < 4; ++r) if (r == n) ssr[r] += ss;
-            }
-        }
-#pragma unroll
-        for (int r = 0; r < 4; ++r) {
-            if (r < P.batch) {
-                const float tot = warp_sum(ssr[r]);
-                if (lane == 0) s_part[r][warp] = tot;
-            }
-        }
-        consumer_sync();
-        if (tid < P.batch) {
-            float tot = 0.0f;
-#pragma unroll
-            for (int w = 0; w < GW; ++w) tot += s_part[tid][w];
-            scratch[tid] = 1.0f / sqrtf(tot * (1.0f / (float)P.K) + P.fz.norm_eps);
-        }
-        consumer_sync();
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            if (i < cnt) {
-                const int n = i / per_row, c = (i % per_row) * CONSUMERS + tid;
-                const float den = scratch[n];
-                const uint4 gq = __ldg((const uint4*)(P.fz.norm_gamma + (size_t)c * 8));
-                uint4 v;
-                v.x = pack_bf16x2((va[i].x * bf16lo(gq.x)) * den, (va[i].y * bf16hi(gq.x)) * den);
-                v.y = pack_bf16x2((va[i].z * bf16lo(gq.y)) * den, (va[i].w * bf16hi(gq.y)) * den);
-                v.z = pack_bf16x2((vb[i].x * bf16lo(gq.z)) * den, (vb[i].y * bf16hi(gq.z)) * den);
-                v.w = pack_bf16x2((vb[i].z * bf16lo(gq.w)) * den, (vb[i].w * bf16hi(gq.w)) * den);
-                *(uint4*)(xs + (size_t)n * xpitch + c * 16) = v;
-            }
-        }
-        consumer_sync();
-    } else {
-        if (NORM) row_norms<true>(P.fz, P.batch, P.K, scratch);   // once per phase
-        if (whole) { stage_x(0); consumer_sync(); }
-    }
+    if (NORM) row_norms<true>(P.fz, P.batch, P.K, scratch);   // once per phase
+    if (whole) { stage_x(0); consumer_sync(); }
     // this thread's activation rows (batch columns g and g + 8); a column beyond the batch reads zeros
     const bool xok0 = g < P.batch, xok1 = NT > 1 && (g + 8) < P.batch;
     const unsigned char* xs0 = xs + (size_t)(xok0 ? g : 0) * xpitch;
