@@ -482,6 +482,29 @@ def test_flash_fwd_sliding_window(dev, window):
     _flash_case(dev, 1, 4, 2, 700, 700, "window", window=window)
 
 
+@pytest.mark.parametrize("mode", ["plain", "causal", "window"])
+def test_flash_fwd_many_items_equals_single_round_calls(dev, mode):
+    # The forward kernel is persistent: one block per SM walks a list of (query block, head, batch) items,
+    # double-buffering the query tiles and reusing its tensor memory from item to item. A call with several
+    # items per block must give, bit for bit, what the same rows give when every (batch, kv head) is its own
+    # small call (at most one item per block).
+    B, Hq, Hkv, L = 3, 16, 4, 1100
+    g = torch.Generator(device=dev.torch_device); g.manual_seed(23)
+    q = torch.randn(B, Hq, L, 64, generator=g, device=dev.torch_device).to(torch.bfloat16)
+    k = torch.randn(B, Hkv, L, 64, generator=g, device=dev.torch_device).to(torch.bfloat16)
+    v = torch.randn(B, Hkv, L, 64, generator=g, device=dev.torch_device).to(torch.bfloat16)
+    kw = dict(causal=(mode != "plain"), window=(200 if mode == "window" else 0))
+    big = dev.attn_fwd_bf16(q, k, v, **kw)       # 5 query blocks x 16 heads x 3 = 240 items on 148 blocks
+    dev.sync()
+    grp = Hq // Hkv
+    for b in range(B):
+        for hk in range(Hkv):
+            small = dev.attn_fwd_bf16(q[b:b + 1, hk * grp:(hk + 1) * grp].contiguous(), k[b:b + 1, hk:hk + 1].contiguous(),
+                                      v[b:b + 1, hk:hk + 1].contiguous(), **kw)
+            dev.sync()
+            assert torch.equal(small[0], big[b, hk * grp:(hk + 1) * grp]), (b, hk)
+
+
 def test_flash_fwd_rope_pipeline_long(dev):
     # size-independent checks at a longer sequence: causal row 0 equals V row 0, and the output is
     # unchanged when keys beyond the causal edge are replaced (they must never be read into a result)
