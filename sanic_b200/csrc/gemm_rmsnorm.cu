@@ -5,16 +5,19 @@
 // The derived carrier has two Plain(Add) slots over the same K stream and a project that
 // divides once at the end (reference tests/laws.rs:620-646, src/partition.rs:2591-2608), so
 // the main loop is a plain tensor-core GEMM on A' = bf16(x * g) and the epilogue scales each
-// row by 1/sqrt(.). The fusion lives in the prologue of each K stage: the A tile that TMA
-// brought into shared memory is rewritten in place (x * g) by a transform warpgroup, which also
-// accumulates sum x^2 per row from the same bytes; x is read from HBM exactly once.
+// row by 1/sqrt(.). The fusion lives in the prologue of each K stage: a transform warpgroup reads
+// the A tile that TMA brought into shared memory, multiplies by g, accumulates sum x^2 per row from
+// the same bytes, and hands the tile to the tensor core THROUGH TENSOR MEMORY (the MMA takes its A
+// operand from TMEM). x is read from HBM exactly once, and shared memory carries each operand byte
+// once in and once out: rewriting A in place instead cost 32 KB more shared-memory traffic per k-block,
+// and shared-memory bandwidth is what bounds a one-CTA 128x256 tile.
 //
 // Persistent kernel, one CTA per SM, 128x256 output tile, BK = 64, 4-stage TMA ring.
 //   warp 0      TMA producer (cp.async.bulk.tensor, 128B swizzle, mbarrier complete_tx)
-//   warp 1      MMA issuer (tcgen05.mma cta_group::1 kind::f16, M=128 N=256 K=16 per instruction)
-//   warp 2      TMEM allocator (512 columns = two 128x256 f32 accumulators, double buffered)
-//   warps 4-11  A transform: x*g in place + sum x^2 (two threads per row)
-//   warps 12-15 epilogue: tcgen05.ld, * rsqrt, bf16/f32 stores, overlapped with the next tile
+//   warp 1      MMA issuer (tcgen05.mma cta_group::1 kind::f16, A from TMEM, M=128 N=256 K=16 per instruction)
+//   warp 2      TMEM allocator (256 accumulator columns + 4 x 32 columns of A stages)
+//   warps 4-11  A transform: shared memory -> x*g -> TMEM, + sum x^2 (two threads per row)
+//   warps 12-15 epilogue: tcgen05.ld, * rsqrt, bf16/f32 stores
 // Every mbarrier wait is bounded; on expiry the kernel records an error code in the context's
 // status word, drains and frees its TMEM, and the next sanic_sync returns SANIC_ERR_TIMEOUT.
 //
@@ -34,10 +37,11 @@ constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int MAX_K = 8192;
 constexpr int NTHREADS = 512;
 constexpr uint32_t SPIN_LIMIT = 1u << 24;
+constexpr int TM_A = BN;                      // tensor-memory columns: [0, BN) accumulator, then STAGES x 32 columns of A
 
 struct Shared {
     uint64_t full[STAGES], ready[STAGES], empty[STAGES];
-    uint64_t tmem_full[2], tmem_empty[2], ss_full[2], ss_empty[2];
+    uint64_t tmem_full, tmem_empty, ss_full[2], ss_empty[2];
     uint32_t tmem_base;
     volatile int abort_flag;
     float ss[2][2][BM];   // [accumulator slot][row half][row]
@@ -74,6 +78,22 @@ __device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64
     asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
                  "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
                  ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// The same with the A operand in tensor memory: lane = row, each 32-bit column holds two consecutive K
+// elements, so one K=16 step reads 8 columns starting at a_tmem.
+__device__ __forceinline__ void umma_f16_ts(uint32_t tmem_d, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+                 ::"r"(tmem_d), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// 32 lanes x 16 columns: thread i of the warp writes 16 consecutive columns of lane (base lane + i).
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+          "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+        : "memory");
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
@@ -127,10 +147,8 @@ gemm_rmsnorm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(&sh->full[s], 1); mbar_init(&sh->ready[s], 8); mbar_init(&sh->empty[s], 1); }
-        for (int a = 0; a < 2; ++a) {
-            mbar_init(&sh->tmem_full[a], 1); mbar_init(&sh->tmem_empty[a], 4);
-            mbar_init(&sh->ss_full[a], 8); mbar_init(&sh->ss_empty[a], 4);
-        }
+        mbar_init(&sh->tmem_full, 1); mbar_init(&sh->tmem_empty, 4);
+        for (int a = 0; a < 2; ++a) { mbar_init(&sh->ss_full[a], 8); mbar_init(&sh->ss_empty[a], 4); }
         sh->abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -178,35 +196,35 @@ gemm_rmsnorm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             int use = 0;
             bool ok = true;
             for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x, ++use) {
-                const int a = use & 1;
-                ok = mbar_wait(&sh->tmem_empty[a], ((use >> 1) & 1) ^ 1, sh, err, 2);
+                ok = mbar_wait(&sh->tmem_empty, (use & 1) ^ 1, sh, err, 2);     // the epilogue has read the previous tile
                 if (!ok) break;
                 tc_fence_after();
-                const uint32_t acc = tmem + a * BN;
+                const uint32_t acc = tmem;
                 for (int kb = 0; kb < kblocks; ++kb) {
                     ok = mbar_wait(&sh->ready[p.stage], p.phase, sh, err, 3);
                     if (!ok) break;
                     tc_fence_after();
-                    const uint32_t sa = base + p.stage * STAGE_BYTES, sb = sa + A_BYTES;
-                    const uint64_t adesc = make_desc(sa, 16, 1024);
+                    const uint32_t sb = base + p.stage * STAGE_BYTES + A_BYTES;
+                    const uint32_t a_tmem = tmem + TM_A + p.stage * (BK / 2);
                     const uint64_t bdesc = w_is_nk ? make_desc(sb, 16, 1024) : make_desc(sb, 64 * BK * 2, 1024);
 #pragma unroll
                     for (int k = 0; k < BK / 16; ++k) {
-                        // K-major: 16 elements = 32 bytes along the swizzled row; MN-major: 16 k-rows = 2048 bytes
-                        const uint64_t ad = adesc + (uint64_t)(k * 2);
+                        // A: 16 elements = 8 tensor-memory columns; B K-major: 32 bytes along the swizzled row; MN-major: 16 k-rows = 2048 bytes
                         const uint64_t bd = bdesc + (uint64_t)(w_is_nk ? k * 2 : k * 128);
-                        umma_f16(acc, ad, bd, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                        umma_f16_ts(acc, a_tmem + 8 * k, bd, idesc, (kb > 0 || k > 0) ? 1u : 0u);
                     }
                     umma_commit(&sh->empty[p.stage]);      // stage reusable once these MMAs have read it
                     p.advance();
                 }
-                if (ok) umma_commit(&sh->tmem_full[a]);
+                if (ok) umma_commit(&sh->tmem_full);
             }
         }
     } else if (warp >= 4 && warp < 12) {
-        // ── A transform: x*g in place, sum x^2 ──
+        // ── A transform: shared memory -> x*g -> tensor memory, sum x^2 ──
         const int idx = threadIdx.x - 128;
         const int row = idx & (BM - 1), half = idx >> 7;   // half 0: chunks 0-3, half 1: chunks 4-7
+        // this warp may touch tensor-memory lanes 32*(warp%4)..+31, which are exactly its rows
+        const uint32_t a_lane = tmem + ((uint32_t)(row & ~31) << 16) + TM_A + half * (BK / 4);
         Pipe p;
         int use = 0;
         bool ok = true;
@@ -216,12 +234,12 @@ gemm_rmsnorm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             for (int kb = 0; kb < kblocks; ++kb) {
                 ok = mbar_wait(&sh->full[p.stage], p.phase, sh, err, 4);
                 if (!ok) break;
-                unsigned char* arow = aligned + p.stage * STAGE_BYTES + row * 128;
+                const unsigned char* arow = aligned + p.stage * STAGE_BYTES + row * 128;
+                uint32_t av[16];
 #pragma unroll
                 for (int c4 = 0; c4 < 4; ++c4) {
                     const int c = half * 4 + c4;
-                    uint4* ptr = (uint4*)(arow + ((c ^ (row & 7)) << 4));
-                    uint4 v = *ptr;
+                    const uint4 v = *(const uint4*)(arow + ((c ^ (row & 7)) << 4));
                     const uint4 gv = *(const uint4*)(gsm + kb * BK + c * 8);
                     uint32_t xs[4] = {v.x, v.y, v.z, v.w};
                     const uint32_t gs[4] = {gv.x, gv.y, gv.z, gv.w};
@@ -233,9 +251,12 @@ gemm_rmsnorm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                         // of the exact product) equals bf16(float(x) * float(g)) bit for bit
                         asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(xs[j]) : "r"(xs[j]), "r"(gs[j]));
                     }
-                    *ptr = make_uint4(xs[0], xs[1], xs[2], xs[3]);
+                    av[4 * c4] = xs[0]; av[4 * c4 + 1] = xs[1]; av[4 * c4 + 2] = xs[2]; av[4 * c4 + 3] = xs[3];
                 }
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic writes -> visible to the MMA
+                // 32 k values = 16 columns of this row's lane in the stage's A slot (free: the stage's previous MMAs
+                // retired before the producer refilled the stage this thread just read)
+                tmem_st16(a_lane + p.stage * (BK / 2), av);
+                tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&sh->ready[p.stage]);
                 p.advance();
@@ -261,14 +282,14 @@ gemm_rmsnorm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             if (!ok) break;
             const float ssv = sh->ss[a][0][row] + sh->ss[a][1][row];
             const float rstd = 1.0f / sqrtf(ssv * inv_k + eps);
-            ok = mbar_wait(&sh->tmem_full[a], (use >> 1) & 1, sh, err, 7);
+            ok = mbar_wait(&sh->tmem_full, use & 1, sh, err, 7);
             if (!ok) break;
             tc_fence_after();
             const int gr = m0 + row;
 #pragma unroll 1
             for (int c = 0; c < BN / 32; ++c) {
                 uint32_t r[32];
-                tmem_ld32(tmem + ((uint32_t)(q * 32) << 16) + a * BN + c * 32, r);
+                tmem_ld32(tmem + ((uint32_t)(q * 32) << 16) + c * 32, r);
                 const int gc = n0 + c * 32;
                 if (gr < M && gc < N) {
                     if (out_dtype == SANIC_BF16) {
@@ -300,7 +321,7 @@ gemm_rmsnorm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             }
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) { mbar_arrive(&sh->tmem_empty[a]); mbar_arrive(&sh->ss_empty[a]); }
+            if (lane == 0) { mbar_arrive(&sh->tmem_empty); mbar_arrive(&sh->ss_empty[a]); }
         }
     }
     // teardown: every role has left its loop (normally or after a bounded wait ran out)
