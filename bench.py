@@ -268,6 +268,24 @@ def run_ours(args):
     q_dev = q_host.to(td)
     out_host = torch.empty((B, HQ, D), dtype=torch.bfloat16).pin_memory()
     dec = SplitKVDecoder(dev, k, v)
+    # N > 1: the exchange either as an NCCL all-gather followed by the merge kernel, or as one kernel over peer memory
+    # (accumulators stored into every peer's buffer over NVLink, flags, merge). The peer form is used when it can be
+    # set up and gives, bit for bit, the NCCL form's output on a first step.
+    exchange, exchange_note = ("nccl" if world > 1 else "none"), ""
+    if world > 1 and args.exchange != "nccl":
+        try:
+            dec_peer = SplitKVDecoder(dev, k, v, n_splits=dec.n_splits, init_nccl=False, exchange="peer")
+            o_ref = dec.step(q_dev[0]).clone()
+            o_peer = dec_peer.step(q_dev[0]).clone()
+            torch.cuda.synchronize()
+            same = torch.tensor([1 if torch.equal(o_ref, o_peer) else 0], dtype=torch.int32, device=td)
+            dist.all_reduce(same, op=dist.ReduceOp.MIN)
+            if int(same.item()) == 1:
+                dec_nccl, dec, exchange = dec, dec_peer, "peer"
+            else:
+                exchange_note = "peer exchange disagreed with the NCCL form; NCCL used"
+        except RuntimeError as e:
+            exchange_note = f"peer exchange unavailable ({e}); NCCL used"
 
     def barrier():
         if world > 1:
@@ -335,7 +353,9 @@ def run_ours(args):
                                    f"sharded over {world} GPU(s) on the sequence axis",
                        "kv_bytes_total": bytes_total, "n_splits_per_gpu": dec.n_splits,
                        "l2": "inputs larger than L2 (>= 2 GB per GPU per step), no flush needed",
-                       "exchange": "NCCL all-gather of (m,l,o) carriers + derived combine" if world > 1 else "none (1 GPU)"},
+                       "exchange": {"none": "none (1 GPU)", "nccl": "NCCL all-gather of (m,l,o) carriers + derived combine",
+                                    "peer": "one kernel: peer stores of (m,l,o) carriers over NVLink + flags + derived combine (bit-identical to the NCCL form)"}[exchange],
+                       **({"exchange_note": exchange_note} if exchange_note else {})},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
                          "frac": achieved / hbm_peak, "traffic": TRAFFIC_RATIO_DECODE * bytes_local if TRAFFIC_RATIO_DECODE else None,
                          "kernel": "attn_decode_kernel<128,false>", "peak_kind": f"of {peak_kind}",
@@ -385,6 +405,7 @@ def main():
     ap.add_argument("--only", default="", help="comma-separated substrings of suite entries to run (c1,c2,c3,c4_bf16_b1,...)")
     ap.add_argument("--c2-shape", default="4096,2048,8192", help="M,K,N of the suite's GEMM (small cases for profiling)")
     ap.add_argument("--llama-unfused", action="store_true", help="one stage per graph cone in the decode step")
+    ap.add_argument("--exchange", default="auto", choices=["auto", "nccl", "peer"], help="how N > 1 ranks exchange their accumulators")
     ap.add_argument("--llama-form", default="auto", choices=["auto", "list", "persistent"],
                     help="decode step as the captured launch list, as one cooperative kernel, or whichever measured faster for the batch")
     ap.add_argument("--c3-shape", default="8,4096", help="batch,sequence of the suite's prefill attention")

@@ -286,6 +286,26 @@ int32_t sanic_nccl_shutdown(sanic_ctx* ctx);
 int32_t sanic_splitkv_decode_step(sanic_ctx* ctx, const sanic_decode_params* p, float* gathered, void* out,
                                   int32_t out_dtype, void* stream);
 
+/* The same step with the exchange and the merge in one kernel over peer memory instead of NCCL: every device
+ * stores its accumulators into each peer's exchange buffer over NVLink, publishes a flag, waits (bounded) for the
+ * others' flags and merges in rank order. The reference has no multi-device path; this is the device-level split
+ * of src/interp.rs:597-640 with shared memory between devices as the exchange medium.
+ * Set-up: every rank allocates sanic_peer_exchange_bytes() with sanic_alloc, zero-fills it, exports it with
+ * sanic_ipc_export, sends the 64 bytes to the other ranks by any side channel, and opens theirs with
+ * sanic_ipc_open; buffers[rank] is the local allocation itself. All ranks must have zero-filled before the first
+ * step (host barrier). `epoch` starts at 1 and increases by 1 every step on every rank. */
+typedef struct {
+    int32_t rank, nranks;        /* 1..8 */
+    void* buffers[8];            /* every rank's exchange buffer as mapped in this process */
+    uint32_t epoch;
+} sanic_peer_exchange;
+size_t sanic_peer_exchange_bytes(int32_t rows /* batch * q_heads */, int32_t head_dim, int32_t nranks);
+int32_t sanic_ipc_export(sanic_ctx* ctx, const void* dptr, uint8_t handle_out[64]);
+int32_t sanic_ipc_open(sanic_ctx* ctx, const uint8_t handle[64], void** dptr_out);
+int32_t sanic_ipc_close(sanic_ctx* ctx, void* dptr);
+int32_t sanic_splitkv_decode_step_peer(sanic_ctx* ctx, const sanic_decode_params* p, const sanic_peer_exchange* x, void* out,
+                                       int32_t out_dtype, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -40,6 +40,10 @@ class AttnParams(C.Structure):
                 ("scale", f32), ("mask", vp), ("out_dtype", i32)]
 
 
+class PeerExchange(C.Structure):
+    _fields_ = [("rank", i32), ("nranks", i32), ("buffers", vp * 8), ("epoch", C.c_uint32)]
+
+
 class DecodeParams(C.Structure):
     _fields_ = [("q", vp), ("k", vp), ("v", vp),
                 ("k_batch_stride", i64), ("k_head_stride", i64), ("k_seq_stride", i64),
@@ -138,6 +142,11 @@ PROTOTYPES = {
     "sanic_nccl_init": (i32, [vp, i32, i32, C.POINTER(C.c_uint8)]),
     "sanic_nccl_shutdown": (i32, [vp]),
     "sanic_splitkv_decode_step": (i32, [vp, C.POINTER(DecodeParams), vp, vp, i32, vp]),
+    "sanic_peer_exchange_bytes": (C.c_size_t, [i32, i32, i32]),
+    "sanic_ipc_export": (i32, [vp, vp, C.POINTER(C.c_uint8)]),
+    "sanic_ipc_open": (i32, [vp, C.POINTER(C.c_uint8), C.POINTER(vp)]),
+    "sanic_ipc_close": (i32, [vp, vp]),
+    "sanic_splitkv_decode_step_peer": (i32, [vp, C.POINTER(DecodeParams), C.POINTER(PeerExchange), vp, i32, vp]),
 }
 
 _lib = None

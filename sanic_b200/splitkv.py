@@ -38,14 +38,19 @@ def exchange_and_merge(local_carrier, merge_fn, group=None):
 class SplitKVDecoder:
     """One rank of a sequence-sharded decode. `k`, `v` are this rank's slices [B, Hkv, n_local, D] bf16."""
 
-    def __init__(self, dev, k, v, n_splits=None, init_nccl=True):
+    def __init__(self, dev, k, v, n_splits=None, init_nccl=True, exchange="nccl"):
+        """`exchange`: "nccl" (all-gather, then a merge kernel) or "peer" (one kernel stores the accumulators into
+        every peer's buffer over NVLink, waits for the others' flags and merges)."""
         self.dev, self.k, self.v = dev, k, v
+        self.exchange = exchange
+        self.epoch = 0
+        self._peer = None
         self.rank = dist.get_rank() if dist.is_initialized() else 0
         self.world = dist.get_world_size() if dist.is_initialized() else 1
         B, Hkv, n_local, D = k.shape
         self.n_local = n_local
         self.n_splits = n_splits or dev.suggest_splits(B, Hkv, D, n_local)
-        if self.world > 1 and init_nccl:
+        if self.world > 1 and init_nccl and exchange == "nccl":
             ident = torch.zeros(128, dtype=torch.uint8)
             if self.rank == 0:
                 buf = (C.c_uint8 * 128)()
@@ -67,12 +72,84 @@ class SplitKVDecoder:
                               out=torch.empty((B, Hq, D), dtype=torch.bfloat16, device=td))
         return self._bufs
 
+    def _peer_setup(self, rows, D):
+        """Allocate this rank's exchange buffer, trade IPC handles over torch.distributed, map the peers' buffers.
+
+        Every rank takes the same collective calls whether or not its own part succeeded; the ranks then agree
+        on the outcome, so a rank that cannot export or map raises on all of them instead of leaving the others
+        waiting."""
+        lib, dev = self.dev.lib, self.dev
+        ok, why = 1, ""
+        local = C.c_void_p()
+        handle = (C.c_uint8 * 64)()
+        try:
+            nbytes = int(lib.sanic_peer_exchange_bytes(rows, D, self.world))
+            dev._check(lib.sanic_alloc(dev.h, nbytes, C.byref(local)), "alloc")
+            dev._check(lib.sanic_memset(dev.h, local, 0, nbytes, dev.stream()), "memset")
+            dev.sync()
+            dev._check(lib.sanic_ipc_export(dev.h, local, handle), "ipc_export")
+        except Exception as e:      # noqa: BLE001 - reported below, on every rank
+            ok, why = 0, str(e)
+        mine = torch.tensor(list(handle), dtype=torch.uint8, device=dev.torch_device)
+        theirs = [torch.empty_like(mine) for _ in range(self.world)]
+        if self.world > 1:
+            dist.all_gather(theirs, mine)
+        x = abi.PeerExchange()
+        x.rank, x.nranks = self.rank, self.world
+        opened = []
+        if ok:
+            try:
+                for r in range(self.world):
+                    if r == self.rank:
+                        x.buffers[r] = local.value
+                        continue
+                    h = (C.c_uint8 * 64)(*theirs[r].cpu().tolist())
+                    ptr = C.c_void_p()
+                    dev._check(lib.sanic_ipc_open(dev.h, h, C.byref(ptr)), "ipc_open")
+                    x.buffers[r] = ptr.value
+                    opened.append(ptr)
+            except Exception as e:  # noqa: BLE001
+                ok, why = 0, str(e)
+        if self.world > 1:
+            agreed = torch.tensor([ok], dtype=torch.int32, device=dev.torch_device)
+            dist.all_reduce(agreed, op=dist.ReduceOp.MIN)      # also the barrier: every buffer is zero-filled and mapped
+            all_ok = int(agreed.item())
+        else:
+            all_ok = ok
+        if not all_ok:
+            for ptr in opened:
+                lib.sanic_ipc_close(dev.h, ptr)
+            if local.value:
+                lib.sanic_free(dev.h, local)
+            raise RuntimeError("peer exchange set-up failed" + (f": {why}" if why else " on another rank"))
+        self._peer = dict(x=x, local=local, opened=opened)
+
+    def close(self):
+        if self._peer is not None:
+            self.dev.sync()
+            if self.world > 1:
+                dist.barrier()      # nobody is still storing into a buffer that is about to go away
+            for ptr in self._peer["opened"]:
+                self.dev.lib.sanic_ipc_close(self.dev.h, ptr)
+            self.dev.lib.sanic_free(self.dev.h, self._peer["local"])
+            self._peer = None
+
     def step(self, q, scale=None):
         """q [B, Hq, D] bf16 (replicated on every rank) -> attention output [B, Hq, D] bf16 on every rank."""
         B, Hq, D = q.shape
         b = self._buffers(B, Hq, D)
         p, _keep = self.dev.decode_params(q, self.k, self.v, self.n_local, n_splits=self.n_splits, scale=scale,
                                           carrier_out=b["carrier"], out=None)
+        if self.exchange == "peer":
+            if self._peer is None:
+                self._peer_setup(B * Hq, D)
+            self.epoch += 1
+            x = self._peer["x"]
+            x.epoch = self.epoch
+            rc = self.dev.lib.sanic_splitkv_decode_step_peer(self.dev.h, C.byref(p), C.byref(x), C.c_void_p(b["out"].data_ptr()),
+                                                         abi.BF16, self.dev.stream())
+            self.dev._check(rc, "splitkv_decode_step_peer")
+            return b["out"]
         rc = self.dev.lib.sanic_splitkv_decode_step(self.dev.h, C.byref(p), C.c_void_p(b["gathered"].data_ptr()),
                                                     C.c_void_p(b["out"].data_ptr()), abi.BF16, self.dev.stream())
         self.dev._check(rc, "splitkv_decode_step")

@@ -529,3 +529,25 @@ def test_flash_fwd_rope_pipeline_long(dev):
     exp = orc.sdpa(qr[0, :4].float().cpu().numpy().astype(np.float64), kr[0, :1].float().cpu().numpy().astype(np.float64),
                    v[0, :1].float().cpu().numpy().astype(np.float64), is_causal=True, enable_gqa=True)
     assert nerr(out[0, :4].float().cpu().numpy(), exp) <= BF16_TOL
+
+
+def test_splitkv_peer_exchange_single_rank(dev):
+    # world size 1: the peer-memory exchange kernel stores into its own buffer, flags itself and merges one
+    # accumulator set; three steps cover both buffer parities. Output equals the NCCL-form call (which at one
+    # rank is fold + merge) bit for bit.
+    from sanic_b200.splitkv import SplitKVDecoder
+    B, Hq, Hkv, D, n = 2, 8, 2, 128, 1000
+    g = torch.Generator(device=dev.torch_device); g.manual_seed(31)
+    k = torch.randn(B, Hkv, n, D, generator=g, device=dev.torch_device).to(torch.bfloat16)
+    v = torch.randn(B, Hkv, n, D, generator=g, device=dev.torch_device).to(torch.bfloat16)
+    a = SplitKVDecoder(dev, k, v, n_splits=4, init_nccl=False)
+    b = SplitKVDecoder(dev, k, v, n_splits=4, init_nccl=False, exchange="peer")
+    for step in range(3):
+        q = torch.randn(B, Hq, D, generator=g, device=dev.torch_device).to(torch.bfloat16)
+        oa = a.step(q).clone(); ob = b.step(q).clone()
+        dev.sync()
+        assert torch.equal(oa, ob), step
+    exp = orc.sdpa(q.float().cpu().numpy().astype(np.float64)[:, :, None, :], k.float().cpu().numpy().astype(np.float64),
+                   v.float().cpu().numpy().astype(np.float64), enable_gqa=True)[:, :, 0, :]
+    assert nerr(ob.float().cpu().numpy(), exp) <= BF16_TOL
+    b.close()
