@@ -1,12 +1,16 @@
 // Online-softmax fold in f32 storage and f32 CUDA-core arithmetic.
 //
-// One CTA of 8 warps per query row. The key axis is streamed lane-split (the 256 threads
-// take keys j, j+256, ...); each lane keeps its own (m, l, o[Ev]) accumulator in registers,
-// the 32 lane accumulators of a warp are merged with a shuffle butterfly and the 8 warp
-// accumulators through shared memory, every merge applying the carrier's own combine,
-// the -inf guard included (reference src/derive.rs:1700-1713). This is the lane_stream x
-// sgs schedule of the reference's cooperative fold (src/emit_metal.rs:760-1101,
-// src/plan.rs:434-455), written for 32-wide warps.
+// One CTA of 256 threads folds a block of BQ = 256 / DV query rows of one (batch, head) over the key axis in
+// chunks of 256 keys, so K and V are read once per BQ rows instead of once per row. Per chunk:
+//   scores   thread j takes key j of the chunk: one pass over its K row gives the BQ scores (q rows broadcast
+//            from shared memory); masked or out-of-range keys lift to the identity (-inf, 0, 0)
+//   combine  per row, the chunk maximum (warp shuffles, then the 8 warps through shared memory) is combined into
+//            the running (m, l, o) with the carrier's own rule, the -inf guard included (reference
+//            src/derive.rs:1700-1713): m' = max(m, c), everything carried so far scales by exp(m - m')
+//   values   thread (row, e) adds sum_j exp(s_j - m') * V[j][e] over the chunk (V rows read coalesced across e) and,
+//            redundantly across e, sum_j exp(s_j - m') into l
+// Chunks are folded left to right, which is the lane_stream x sgs schedule of the reference's cooperative fold
+// (src/emit_metal.rs:760-1101, src/plan.rs:434-455) with the CTA as the lane group; project o / l at the end.
 //
 // A tensor-core TF32 contraction has a 10-bit mantissa and cannot hold the 1e-5
 // relative bound this path is checked at, so the contraction runs as FP32 FMAs and
@@ -16,99 +20,135 @@
 namespace {
 using namespace sanic;
 
-constexpr int FW = 8;   // warps (simdgroups) per query row
+constexpr int NT = 256;      // threads per CTA = keys per chunk
 
 template <int DV>
-__global__ void __launch_bounds__(FW * 32) attn_fwd_f32_kernel(sanic_attn_params p) {
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int row = blockIdx.x;
+__global__ void __launch_bounds__(NT) attn_fwd_f32_kernel(sanic_attn_params p) {
+    constexpr int BQ = NT / DV;                   // query rows per CTA
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int r0 = blockIdx.x * BQ;
     const int bh = blockIdx.y;
     const int b = bh / p.q_heads, h = bh % p.q_heads;
     const int hk = h / (p.q_heads / p.kv_heads);
     const int E = p.head_dim, Ev = p.v_dim, S = p.kv_len, L = p.q_len;
 
     extern __shared__ float smem[];
-    float* qs = smem;                 // [E]
-    float* ws = smem + E;             // [FW][DV + 2] warp accumulators
-    const float* Q = (const float*)p.q + ((size_t)bh * L + row) * E;
-    for (int d = threadIdx.x; d < E; d += FW * 32) qs[d] = Q[d];
+    float* qs = smem;                     // [BQ][E]
+    float* ps = qs + BQ * E;              // [BQ][NT] weights exp(s - m') of the current chunk
+    float* red = ps + BQ * NT;            // [BQ][8] warp maxima
+    float* mrow = red + BQ * 8;           // [BQ] running max
+    float* arow = mrow + BQ;              // [BQ] rescale factor of the current chunk
+    for (int i = tid; i < BQ * E; i += NT) {
+        const int r = i / E, d = i % E;
+        qs[i] = (r0 + r < L) ? ((const float*)p.q)[((size_t)bh * L + r0 + r) * E + d] : 0.0f;
+    }
+    if (tid < BQ) mrow[tid] = -INFINITY;
     __syncthreads();
 
     const float* K = (const float*)p.k + ((size_t)(b * p.kv_heads + hk) * S) * E;
     const float* V = (const float*)p.v + ((size_t)(b * p.kv_heads + hk) * S) * Ev;
 
-    // Visible key range. A causal / window prefix mask contributes exact zeros outside
-    // it, so stopping the stream at the edge is bit-identical (src/emit_metal.rs:442-456).
-    int lo = 0, hi = S;
-    if (p.causal) hi = min(S, row + 1);
-    if (p.window > 0) { hi = min(S, row + 1); lo = max(0, row - p.window + 1); }
+    // Visible key range of each row. A causal / window prefix mask contributes exact zeros outside it, so
+    // stopping the stream at the edge is bit-identical (src/emit_metal.rs:442-456).
+    auto row_lo = [&](int row) { return (p.window > 0) ? max(0, row - p.window + 1) : 0; };
+    auto row_hi = [&](int row) { return (row >= L) ? 0 : ((p.causal || p.window > 0) ? min(S, row + 1) : S); };
+    const int last_row = min(r0 + BQ, L) - 1;
+    const int j_lo = row_lo(r0), j_hi = row_hi(last_row);        // both are monotone in the row
 
-    float m = -INFINITY, l = 0.0f;
-    float o[DV];
-#pragma unroll
-    for (int e = 0; e < DV; ++e) o[e] = 0.0f;
+    const int rq = tid / DV, e = tid % DV;       // the (row, output column) this thread accumulates
+    float l = 0.0f, o = 0.0f;
 
-    for (int j = lo + threadIdx.x; j < hi; j += FW * 32) {
-        float s = 0.0f;
-        if ((E & 3) == 0) {
-            const float4* kr = (const float4*)(K + (size_t)j * E);
-            for (int d4 = 0; d4 < E / 4; ++d4) {
-                float4 kv = kr[d4];
-                s = fmaf(qs[4 * d4 + 0], kv.x, s);
-                s = fmaf(qs[4 * d4 + 1], kv.y, s);
-                s = fmaf(qs[4 * d4 + 2], kv.z, s);
-                s = fmaf(qs[4 * d4 + 3], kv.w, s);
+    for (int c0 = (j_lo / NT) * NT; c0 < j_hi; c0 += NT) {
+        // ── scores of key j against the BQ rows ──
+        const int j = c0 + tid;
+        {   // the chunk's V rows are read 256 FMAs from now: start them towards L1 (one 128-byte line per request)
+            const int n_keys = min(NT, S - c0);
+            const char* vb = (const char*)(V + (size_t)c0 * Ev);
+            const int lines = (n_keys * Ev * 4 + 127) / 128;
+            for (int i = tid; i < lines; i += NT) asm volatile("prefetch.global.L1 [%0];" ::"l"(vb + (size_t)i * 128));
+        }
+        float sc[BQ];
+#pragma unroll
+        for (int r = 0; r < BQ; ++r) sc[r] = 0.0f;
+        if (j < S) {
+            if ((E & 3) == 0) {
+                const float4* kr = (const float4*)(K + (size_t)j * E);
+                // eight independent 16-byte loads of the key row in flight before their FMAs: one round trip per 32 dims
+                for (int d0 = 0; d0 < E / 4; d0 += 8) {
+                    float4 kv[8];
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) kv[u] = (d0 + u < E / 4) ? __ldg(kr + d0 + u) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) {
+                        if (d0 + u < E / 4) {
+#pragma unroll
+                            for (int r = 0; r < BQ; ++r) {
+                                const float4 q = *(const float4*)(qs + r * E + 4 * (d0 + u));
+                                sc[r] = fmaf(q.x, kv[u].x, sc[r]); sc[r] = fmaf(q.y, kv[u].y, sc[r]);
+                                sc[r] = fmaf(q.z, kv[u].z, sc[r]); sc[r] = fmaf(q.w, kv[u].w, sc[r]);
+                            }
+                        }
+                    }
+                }
+            } else {
+                for (int d = 0; d < E; ++d) {
+                    const float kv = __ldg(K + (size_t)j * E + d);
+#pragma unroll
+                    for (int r = 0; r < BQ; ++r) sc[r] = fmaf(qs[r * E + d], kv, sc[r]);
+                }
             }
-        } else {
-            for (int d = 0; d < E; ++d) s = fmaf(qs[d], K[(size_t)j * E + d], s);
         }
-        s *= p.scale;
-        if (p.mask) s += p.mask[(size_t)row * S + j];
-        // element lift (s, 1, v) combined into the running accumulator
-        float mn = fmaxf(m, s);
-        float ra = (m > -INFINITY) ? expf(m - mn) : 0.0f;
-        float rb = (s > -INFINITY) ? expf(s - mn) : 0.0f;
-        l = l * ra + rb;
-        const float* vr = V + (size_t)j * Ev;
 #pragma unroll
-        for (int e = 0; e < DV; ++e)
-            if (e < Ev) o[e] = o[e] * ra + rb * vr[e];
-        m = mn;
-    }
-    // butterfly merge of the lane accumulators with the derived combine
+        for (int r = 0; r < BQ; ++r) {
+            const int row = r0 + r;
+            float s = sc[r] * p.scale;
+            if (p.mask && row < L && j < S) s += p.mask[(size_t)row * S + j];
+            if (!(j >= row_lo(row) && j < row_hi(row))) s = -INFINITY;      // outside the row's range: the identity
+            sc[r] = s;
+            float mx = s;
 #pragma unroll
-    for (int off = 16; off > 0; off >>= 1) {
-        float mo = __shfl_xor_sync(0xffffffffu, m, off);
-        float lo_ = __shfl_xor_sync(0xffffffffu, l, off);
-        MloScale sc = mlo_rescale(m, mo);
-        l = l * sc.ra + lo_ * sc.rb;
-#pragma unroll
-        for (int e = 0; e < DV; ++e) {
-            float oo = __shfl_xor_sync(0xffffffffu, o[e], off);
-            o[e] = o[e] * sc.ra + oo * sc.rb;
+            for (int off = 16; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+            if (lane == 0) red[r * 8 + warp] = mx;
         }
-        m = sc.m;
-    }
-    // merge the warp accumulators left to right, then project: o / l
-    if (lane == 0) { ws[warp * (DV + 2)] = m; ws[warp * (DV + 2) + 1] = l; }
+        __syncthreads();
+        // ── combine the chunk maximum into the running maximum ──
+        if (tid < BQ) {
+            float cm = red[tid * 8];
 #pragma unroll
-    for (int e = 0; e < DV; ++e)
-        if ((e & 31) == lane) ws[warp * (DV + 2) + 2 + e] = o[e];
-    __syncthreads();
-    if (warp == 0) {
-        float* out = (float*)p.out + ((size_t)bh * L + row) * Ev;
-        for (int e = lane; e < Ev; e += 32) {
-            float mm = ws[0], ll = ws[1], oo = ws[2 + e];
+            for (int w = 1; w < 8; ++w) cm = fmaxf(cm, red[tid * 8 + w]);
+            const float m_old = mrow[tid], m_new = fmaxf(m_old, cm);
+            arow[tid] = (m_old > -INFINITY) ? expf(m_old - m_new) : 0.0f;     // a side at -inf carries weight 0
+            mrow[tid] = m_new;
+        }
+        __syncthreads();
 #pragma unroll
-            for (int w = 1; w < FW; ++w) {
-                MloScale sc = mlo_rescale(mm, ws[w * (DV + 2)]);
-                ll = ll * sc.ra + ws[w * (DV + 2) + 1] * sc.rb;
-                oo = oo * sc.ra + ws[w * (DV + 2) + 2 + e] * sc.rb;
-                mm = sc.m;
+        for (int r = 0; r < BQ; ++r) ps[r * NT + tid] = (sc[r] > -INFINITY) ? expf(sc[r] - mrow[r]) : 0.0f;
+        __syncthreads();
+        // ── values: (row rq, column e) ──
+        {
+            const float alpha = arow[rq];
+            o *= alpha; l *= alpha;
+            const int n = min(NT, min(j_hi, S) - c0);      // keys of this chunk that exist and any row can see
+            const float* pr = ps + rq * NT;
+            const float* vr = V + (size_t)c0 * Ev + e;
+            if (e < Ev) {
+                // 32 independent loads in flight per round trip; weights of masked keys are exact zeros
+                for (int jj0 = 0; jj0 < n; jj0 += 32) {
+                    float vv[32];
+#pragma unroll
+                    for (int u = 0; u < 32; ++u) vv[u] = (jj0 + u < n) ? __ldg(vr + (size_t)(jj0 + u) * Ev) : 0.0f;
+#pragma unroll
+                    for (int u = 0; u < 32; ++u) {
+                        const float w = pr[jj0 + u];
+                        o = fmaf(w, vv[u], o);
+                        l += w;
+                    }
+                }
             }
-            out[e] = oo / ll;
         }
+        __syncthreads();      // ps, red and arow are rewritten by the next chunk
     }
+    if (e < Ev && r0 + rq < L) ((float*)p.out)[((size_t)bh * L + r0 + rq) * Ev + e] = o / l;
 }
 }  // namespace
 
@@ -123,9 +163,10 @@ extern "C" int32_t sanic_attn_fwd_f32(sanic_ctx* ctx, const sanic_attn_params* p
     SANIC_REQUIRE(ctx, p->out_dtype == SANIC_F32, "attn_fwd_f32: output is f32");
     SANIC_REQUIRE(ctx, !(p->causal && p->mask), "attn_fwd_f32: attn_mask and is_causal cannot both be set");
     sanic_set_device(ctx);
-    dim3 grid(p->q_len, p->batch * p->q_heads), block(FW * 32);
     const int dv = p->v_dim <= 32 ? 32 : (p->v_dim <= 64 ? 64 : 128);
-    size_t smem = ((size_t)p->head_dim + (size_t)FW * (dv + 2)) * sizeof(float);
+    const int bq = NT / dv;
+    dim3 grid((p->q_len + bq - 1) / bq, p->batch * p->q_heads), block(NT);
+    size_t smem = ((size_t)bq * p->head_dim + (size_t)bq * NT + (size_t)bq * 10) * sizeof(float);
     if (dv == 32) attn_fwd_f32_kernel<32><<<grid, block, smem, (cudaStream_t)stream>>>(*p);
     else if (dv == 64) attn_fwd_f32_kernel<64><<<grid, block, smem, (cudaStream_t)stream>>>(*p);
     else attn_fwd_f32_kernel<128><<<grid, block, smem, (cudaStream_t)stream>>>(*p);
