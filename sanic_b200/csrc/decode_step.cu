@@ -1,19 +1,30 @@
-// One decode step as one persistent, cooperatively launched kernel.
+// One decode step as one persistent, cooperatively launched, warp-specialised kernel.
 //
 // A captured launch list pays a fixed cost per kernel (launch, ramp-up, drain) that is several times
 // the HBM time of a decode-step stage: a 2048x2048 bf16 projection is 8 MB, 1.3 us of bandwidth. Here
-// the stage list (reference src/partition.rs:101-127) is lowered once into a table of phases; a grid of
-// co-resident CTAs walks the table, each phase strided over the CTAs, with a grid-wide barrier where the
-// launch list had a kernel boundary. While a CTA waits at the barrier, the weights of its first tile of
-// the next phase are already on their way into L2, so HBM keeps streaming across the boundary.
+// the stage list (reference src/partition.rs:101-127) is lowered once into a table of phases; one block
+// per SM walks the table, each phase strided over the blocks, with a grid-wide barrier where the launch
+// list had a kernel boundary.
 //
-// The phases reuse the device bodies of the stand-alone kernels (gemv_body.cuh, attn_decode_body.cuh), so
-// both paths compute bit-identical results. Data written in one phase and read in a later one crosses SMs
-// inside one kernel: those reads go to L2 (ld.global.cg), never through the non-coherent L1.
+//   warps 0-7   consumers: run the phase bodies. A contraction takes its weight fragments from a
+//               shared-memory ring and its activations from a per-phase shared-memory copy (RMSNorm applied
+//               while staging), then sums the warps and runs the epilogue exactly as the stand-alone kernel
+//               does (gemv_body.cuh: tile_finish). Attention phases run the stand-alone fold body
+//               (attn_decode_body.cuh) on a named barrier.
+//   warps 8-11  producers: stream the weights of EVERY contraction phase, in consumption order, into the ring
+//               with cp.async.bulk row copies that complete on mbarriers (ring slots dealt round-robin to the
+//               four warps: one warp cannot issue copies fast enough). Weights are constant within a step, so
+//               the producers run ahead of the grid barriers: HBM keeps streaming while the consumers wait for
+//               activations, which a launch list cannot do.
 //
-// The barrier is a monotonic arrival counter (cleared on the stream before the launch). Every spin is
-// bounded: a CTA that gives up raises the abort word, records a code in the context's status word and
-// leaves; the others see the abort word or run out of spins themselves, so the kernel always ends.
+// Both forms of a step compute the same values (same fragment layout, same summation order per tile). Data
+// written in one phase and read in a later one crosses SMs inside one kernel: those reads go to L2
+// (ld.global.cg), never through the non-coherent L1.
+//
+// The grid barrier is a monotonic arrival counter (cleared on the stream before the launch): release-add,
+// acquire-poll. Every spin (grid barrier, ring mbarriers) is bounded: a block that gives up raises the abort
+// word, records a code in the context's status word and leaves; the others see the abort word or run out of
+// spins themselves, and no block exits while a bulk copy into its shared memory is still in flight.
 #include "decode_step.cuh"
 
 #include <new>
