@@ -380,6 +380,13 @@ def run_ours(args):
             line["cpu_baseline"] = {"value": gbs, "unit": "GB/s", "cores": threads, "kind": "port",
                                     "sample": f"{args.cpu_sample_keys} of {L} keys per sequence, all {B}x{HQ} heads, "
                                               f"dense f64 oracle, {csec:.2f} s"}
+            # the reference's interpreter is single-threaded: the same path on one thread, on a quarter of the sample
+            from oracle import oracle as orc
+            orc.set_num_threads(1)
+            gbs1, csec1, _ = cpu_sample(max(256, args.cpu_sample_keys // 4), 1)
+            orc.set_num_threads(threads)
+            line["cpu_baseline"]["single_thread"] = {"value": gbs1, "unit": "GB/s", "cores": 1,
+                                                     "sample": f"{max(256, args.cpu_sample_keys // 4)} keys per sequence, {csec1:.2f} s"}
     del dec, k, v
     torch.cuda.empty_cache()
     if rank == 0 and world == 1 and not args.no_suite:

@@ -99,6 +99,12 @@ int32_t sanic_splitkv_decode_step(sanic_ctx* ctx, const sanic_decode_params* p, 
     if (!ctx || !p) return SANIC_ERR_INVALID;
     SANIC_REQUIRE(ctx, p->carrier_out && gathered && out, "splitkv_decode_step: carrier_out, gathered and out are required");
     sanic_decode_params local = *p;
+    const int nranks_now = ctx->nccl_comm ? ctx->nccl_nranks : 1;
+    if (nranks_now == 1) {   // one device: the fold's own last-arriver merge projects straight into `out` (one launch)
+        local.out = out;
+        local.out_dtype = out_dtype;
+        return sanic_attn_decode_splitkv(ctx, &local, stream);
+    }
     local.out = nullptr;  // the local projection is meaningless before the cross-device merge
     int32_t rc = sanic_attn_decode_splitkv(ctx, &local, stream);
     if (rc != SANIC_OK) return rc;
