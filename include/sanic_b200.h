@@ -237,12 +237,71 @@ int32_t sanic_round_to_bf16(sanic_ctx* ctx, const float* x, size_t n, uint16_t* 
 int32_t sanic_store_u32_saturating(sanic_ctx* ctx, const float* x, size_t n, uint32_t* out, void* stream);
 int32_t sanic_w4_unpack(sanic_ctx* ctx, const uint8_t* packed, size_t n_elems, float* out, void* stream);
 
+/* ── K1 / K2 / K3 generic: any carrier, given as expression programs, rendered to CUDA C and compiled at run
+ *    time for sm_100a. The fallback for carriers no specialised kernel matches and the pointwise kernel of
+ *    elementwise cones: the role of emit_fused_metal_with (scalar fold, src/emit_metal.rs:626-736), the
+ *    cooperative fold (:760-1101) and the pointwise kernel (:1118-1178) over the node -> code recursion of
+ *    src/codegen.rs:283-443. The carrier is the reference's own: leaves, into, combine, identity, project
+ *    (src/derive.rs:262-287) over the closed scalar basis (src/scalar.rs:45-69, Expr src/derive.rs:96-118). ── */
+#define SANIC_MAX_AXES 6
+#define SANIC_MAX_SLOTS 8
+enum { SANIC_X_CONST = 1,   /* value */
+       SANIC_X_LOAD = 2,    /* arg = operand index: a typed, strided read at the current point */
+       SANIC_X_COORD = 3,   /* arg = grid axis, or n_axes for the streamed coordinate; as a float (Iota / Coordinate) */
+       SANIC_X_ITEM = 4,    /* arg = leaf index (into, and project for stream-invariant leaves is not needed: use LOAD) */
+       SANIC_X_A = 5, SANIC_X_B = 6,   /* arg = slot of the left / right accumulator (combine) */
+       SANIC_X_F = 7,       /* arg = slot of the final accumulator (project) */
+       SANIC_X_RESULT = 8,  /* the projected value (epilogue) */
+       SANIC_X_ADD = 16, SANIC_X_SUB, SANIC_X_MUL, SANIC_X_DIV, SANIC_X_MAX, SANIC_X_MIN,
+       SANIC_X_LT,          /* a < b as 1.0 / 0.0 */
+       SANIC_X_NEG, SANIC_X_RECIP, SANIC_X_EXP, SANIC_X_LOG, SANIC_X_SQRT, SANIC_X_TANH, SANIC_X_SIN, SANIC_X_COS,
+       SANIC_X_WHERE,       /* cond != 0 ? a : b; operands pushed cond, a, b */
+       SANIC_X_ROUND };     /* arg = SANIC_BF16 / SANIC_F32: round to a storage width and widen back */
+typedef struct { int32_t op; int32_t arg; double value; } sanic_expr_op;   /* one postfix instruction */
+typedef struct { int32_t first, count; } sanic_expr;                        /* a slice of the op array */
+typedef struct {
+    int32_t dtype;                      /* SANIC_F32 / SANIC_BF16 / SANIC_U32 / SANIC_I4 (unsigned nibble q+8, low nibble = even element) */
+    int32_t buffer;                     /* which of the buffers bound at launch, 0..15 */
+    int64_t offset;                     /* elements */
+    int64_t stride[SANIC_MAX_AXES];     /* elements per step of each grid axis; 0 broadcasts */
+    int64_t stream_stride;              /* elements per step of the streamed axis */
+} sanic_operand;
+typedef struct {
+    int32_t n_axes;                     /* output grid, row-major, last axis fastest */
+    int64_t extent[SANIC_MAX_AXES];
+    int64_t stream;                     /* streamed extent; 0 = pointwise kernel: out[point] = project */
+    int32_t lanes;                      /* 1: one thread per output point; 32: a warp per point (cooperative fold) */
+    int32_t interleave;                 /* lanes == 32 only. 0: lane b folds the contiguous chunk [b*n/B, (b+1)*n/B), B = min(32, n),
+                                           merged in lane order (run_carrier_split, src/interp.rs:597-640): legal for every carrier.
+                                           1: lane b folds s = b, b+32, ...: needs a carrier that merges out of order (src/plan.rs:481-488) */
+    int32_t n_operands; const sanic_operand* operands;
+    int32_t n_ops; const sanic_expr_op* ops;
+    int32_t n_leaves; const sanic_expr* leaves;           /* value of leaf i at (point, s): LOAD / COORD / CONST and the basis */
+    int32_t n_slots; const double* identity;
+    const sanic_expr* into;                               /* per slot, over ITEM */
+    const sanic_expr* combine;                            /* per slot, over A and B; all slots read the old accumulator */
+    sanic_expr project;                                   /* over F (and LOAD / COORD at the grid point) */
+    sanic_expr epilogue;                                  /* count 0 = none; over RESULT and LOAD / COORD at the grid point */
+    int32_t out_dtype;                                    /* SANIC_F32 / SANIC_BF16 (RNE) / SANIC_U32 (saturating) */
+} sanic_generic_desc;
+typedef struct sanic_generic_kernel sanic_generic_kernel;
+/* The generated CUDA C text (MetalKernel::msl). ctx may be NULL. *needed receives the size including the terminator. */
+int32_t sanic_generic_source(sanic_ctx* ctx, const sanic_generic_desc* d, char* buf, size_t cap, size_t* needed);
+/* Renders and compiles for sm_100a without loading: the "does the generated code compile" check; needs no device. ctx may be NULL. */
+int32_t sanic_generic_cubin_size(sanic_ctx* ctx, const sanic_generic_desc* d, size_t* bytes);
+/* Renders, compiles and loads (MetalDevice::compile, src/metal.rs:160-180; a compile failure is a status, not a panic). */
+int32_t sanic_generic_compile(sanic_ctx* ctx, const sanic_generic_desc* d, sanic_generic_kernel** out);
+/* out holds one element per grid point at the descriptor's out_dtype. */
+int32_t sanic_generic_launch(sanic_ctx* ctx, sanic_generic_kernel* k, const void* const* buffers, int32_t n_buffers, void* out,
+                             void* stream);
+int32_t sanic_generic_destroy(sanic_generic_kernel* k);
+
 /* ── stateful stepping: Graph::compile_for / StepProgram::instantiate / Machine::step
  *    (src/graph.rs:231-356) with capture/replay (src/compile.rs:820-1035, src/metal.rs:634-705) ── */
 typedef struct sanic_program sanic_program;
 enum { SANIC_STAGE_FUSED = 1, SANIC_STAGE_ELEMENTWISE = 2, SANIC_STAGE_GATHER = 3 };  /* src/partition.rs:44-98 */
 enum { SANIC_OP_GEMV = 1, SANIC_OP_DECODE_ATTN = 2, SANIC_OP_ARGMAX = 3, SANIC_OP_RMSNORM = 4, SANIC_OP_EMBED = 5,
-       SANIC_OP_ROPE_CACHE = 6, SANIC_OP_ADVANCE = 7 };
+       SANIC_OP_ROPE_CACHE = 6, SANIC_OP_ADVANCE = 7, SANIC_OP_GENERIC = 8 };
 typedef struct {
     int32_t stage_kind;          /* SANIC_STAGE_* */
     int32_t op;                  /* SANIC_OP_* */
@@ -255,6 +314,7 @@ typedef struct {
         struct { const void* table; const int32_t* tokens; int32_t batch, hidden, vocab; float* out; } embed;
         sanic_rope_cache_params rope_cache;
         struct { int32_t* position; } advance;
+        struct { sanic_generic_kernel* kernel; const void* buffers[16]; int32_t n_buffers; void* out; } generic;   /* a compiled fallback kernel */
     } u;
 } sanic_stage_desc;
 int32_t sanic_program_create(sanic_ctx* ctx, const sanic_stage_desc* stages, int32_t n_stages, sanic_program** out);

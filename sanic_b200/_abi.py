@@ -18,7 +18,11 @@ KERNEL_NONE, KERNEL_ONLINE_SOFTMAX_FOLD, KERNEL_DEFERRED_NORM_CONTRACTION, KERNE
     KERNEL_GROUPED_I4_CONTRACTION, KERNEL_EXTREMUM_INDEX = range(6)
 EPI_STORE, EPI_RESIDUAL_ADD, EPI_SILU_MUL, EPI_ROPE_CACHE = 0, 1, 2, 3
 STAGE_FUSED, STAGE_ELEMENTWISE, STAGE_GATHER = 1, 2, 3
-OP_GEMV, OP_DECODE_ATTN, OP_ARGMAX, OP_RMSNORM, OP_EMBED, OP_ROPE_CACHE, OP_ADVANCE = 1, 2, 3, 4, 5, 6, 7
+OP_GEMV, OP_DECODE_ATTN, OP_ARGMAX, OP_RMSNORM, OP_EMBED, OP_ROPE_CACHE, OP_ADVANCE, OP_GENERIC = 1, 2, 3, 4, 5, 6, 7, 8
+MAX_AXES, MAX_SLOTS = 6, 8
+X_CONST, X_LOAD, X_COORD, X_ITEM, X_A, X_B, X_F, X_RESULT = 1, 2, 3, 4, 5, 6, 7, 8
+(X_ADD, X_SUB, X_MUL, X_DIV, X_MAX, X_MIN, X_LT, X_NEG, X_RECIP, X_EXP, X_LOG, X_SQRT, X_TANH, X_SIN, X_COS, X_WHERE,
+ X_ROUND) = range(16, 33)
 
 vp, i32, i64, f32 = C.c_void_p, C.c_int32, C.c_int64, C.c_float
 
@@ -87,13 +91,38 @@ class _AdvanceStage(C.Structure):
     _fields_ = [("position", vp)]
 
 
+class _GenericStage(C.Structure):
+    _fields_ = [("kernel", vp), ("buffers", vp * 16), ("n_buffers", i32), ("out", vp)]
+
+
 class _StageUnion(C.Union):
     _fields_ = [("gemv", GemvParams), ("decode", DecodeParams), ("argmax", _ArgmaxStage), ("rmsnorm", _RmsnormStage),
-                ("embed", _EmbedStage), ("rope_cache", RopeCacheParams), ("advance", _AdvanceStage)]
+                ("embed", _EmbedStage), ("rope_cache", RopeCacheParams), ("advance", _AdvanceStage),
+                ("generic", _GenericStage)]
 
 
 class StageDesc(C.Structure):
     _fields_ = [("stage_kind", i32), ("op", i32), ("carrier", CarrierDesc), ("u", _StageUnion)]
+
+
+class ExprOp(C.Structure):
+    _fields_ = [("op", i32), ("arg", i32), ("value", C.c_double)]
+
+
+class Expr(C.Structure):
+    _fields_ = [("first", i32), ("count", i32)]
+
+
+class Operand(C.Structure):
+    _fields_ = [("dtype", i32), ("buffer", i32), ("offset", i64), ("stride", i64 * MAX_AXES), ("stream_stride", i64)]
+
+
+class GenericDesc(C.Structure):
+    _fields_ = [("n_axes", i32), ("extent", i64 * MAX_AXES), ("stream", i64), ("lanes", i32), ("interleave", i32),
+                ("n_operands", i32), ("operands", C.POINTER(Operand)), ("n_ops", i32), ("ops", C.POINTER(ExprOp)),
+                ("n_leaves", i32), ("leaves", C.POINTER(Expr)), ("n_slots", i32), ("identity", C.POINTER(C.c_double)),
+                ("into", C.POINTER(Expr)), ("combine", C.POINTER(Expr)), ("project", Expr), ("epilogue", Expr),
+                ("out_dtype", i32)]
 
 
 # name -> (restype, argtypes); every symbol the header declares
@@ -130,6 +159,11 @@ PROTOTYPES = {
     "sanic_round_to_bf16": (i32, [vp, vp, C.c_size_t, vp, vp]),
     "sanic_store_u32_saturating": (i32, [vp, vp, C.c_size_t, vp, vp]),
     "sanic_w4_unpack": (i32, [vp, vp, C.c_size_t, vp, vp]),
+    "sanic_generic_source": (i32, [vp, C.POINTER(GenericDesc), C.c_char_p, C.c_size_t, C.POINTER(C.c_size_t)]),
+    "sanic_generic_cubin_size": (i32, [vp, C.POINTER(GenericDesc), C.POINTER(C.c_size_t)]),
+    "sanic_generic_compile": (i32, [vp, C.POINTER(GenericDesc), C.POINTER(vp)]),
+    "sanic_generic_launch": (i32, [vp, vp, C.POINTER(vp), i32, vp, vp]),
+    "sanic_generic_destroy": (i32, [vp]),
     "sanic_program_create": (i32, [vp, C.POINTER(StageDesc), i32, C.POINTER(vp)]),
     "sanic_program_destroy": (i32, [vp]),
     "sanic_program_kernel_count": (i32, [vp]),

@@ -1,0 +1,459 @@
+// The generic emitter: any carrier, given as expression programs, becomes CUDA C text that is compiled at
+// run time for sm_100a. This is the fallback for carriers no specialised kernel matches, and the pointwise
+// kernel for elementwise cones.
+//
+// It plays the role of the reference's generated-source kernels (src/emit_metal.rs):
+//   scalar fold       one thread per output point, the streamed axis folded serially in registers
+//                     (x = leaves, el = into(x), acc = combine(acc, el), then project, optional elementwise
+//                     epilogue, narrowed store)                                        :626-736
+//   cooperative fold  the streamed axis split over the 32 lanes of a warp, lane partials merged with the
+//                     carrier's OWN combine                                            :760-1101
+//   pointwise         value per output point                                           :1118-1178
+// and of the shared node -> code recursion (src/codegen.rs:283-443): here a node is a postfix program over
+// strided loads, coordinates and the closed scalar basis (src/scalar.rs:45-69; Expr, src/derive.rs:96-118).
+//
+// Arithmetic is f32 in registers, loads and stores are typed (bf16 widen, int4 nibble q+8, bf16 RNE store, u32
+// saturating store: src/emit_metal.rs:119-232). Lane split: lane b of B = min(32, stream) folds the contiguous
+// chunk [b*n/B, (b+1)*n/B) and the partials merge left to right in lane order, which is the chunking and the
+// merge order of run_carrier_split (src/interp.rs:597-640), so it is legal for every associative carrier; the
+// interleaved split (lane b takes s = b, b+32, ...: coalesced for a unit stream stride) needs a carrier that
+// merges out of order (src/plan.rs:481-488) and is the caller's choice.
+#include <cuda.h>
+#include <dlfcn.h>
+#include <nvrtc.h>
+
+#include <cmath>
+#include <cstdio>
+#include <cstring>
+#include <sstream>
+#include <vector>
+
+#include "common.cuh"
+
+namespace {
+
+// ── NVRTC, resolved at run time so that the library has no link-time dependency on it ──
+struct Nvrtc {
+    void* lib = nullptr;
+    nvrtcResult (*create)(nvrtcProgram*, const char*, const char*, int, const char* const*, const char* const*) = nullptr;
+    nvrtcResult (*compile)(nvrtcProgram, int, const char* const*) = nullptr;
+    nvrtcResult (*cubin_size)(nvrtcProgram, size_t*) = nullptr;
+    nvrtcResult (*cubin)(nvrtcProgram, char*) = nullptr;
+    nvrtcResult (*log_size)(nvrtcProgram, size_t*) = nullptr;
+    nvrtcResult (*log)(nvrtcProgram, char*) = nullptr;
+    nvrtcResult (*destroy)(nvrtcProgram*) = nullptr;
+    const char* (*err)(nvrtcResult) = nullptr;
+    bool ok = false;
+};
+Nvrtc& nvrtc() {
+    static Nvrtc n = [] {
+        Nvrtc r;
+        const char* names[] = {"libnvrtc.so.12", "/usr/local/cuda/lib64/libnvrtc.so.12", "libnvrtc.so"};
+        for (const char* nm : names) {
+            r.lib = dlopen(nm, RTLD_NOW | RTLD_LOCAL);
+            if (r.lib) break;
+        }
+        if (!r.lib) return r;
+        r.create = (decltype(r.create))dlsym(r.lib, "nvrtcCreateProgram");
+        r.compile = (decltype(r.compile))dlsym(r.lib, "nvrtcCompileProgram");
+        r.cubin_size = (decltype(r.cubin_size))dlsym(r.lib, "nvrtcGetCUBINSize");
+        r.cubin = (decltype(r.cubin))dlsym(r.lib, "nvrtcGetCUBIN");
+        r.log_size = (decltype(r.log_size))dlsym(r.lib, "nvrtcGetProgramLogSize");
+        r.log = (decltype(r.log))dlsym(r.lib, "nvrtcGetProgramLog");
+        r.destroy = (decltype(r.destroy))dlsym(r.lib, "nvrtcDestroyProgram");
+        r.err = (decltype(r.err))dlsym(r.lib, "nvrtcGetErrorString");
+        r.ok = r.create && r.compile && r.cubin_size && r.cubin && r.log_size && r.log && r.destroy && r.err;
+        return r;
+    }();
+    return n;
+}
+
+// ── driver entry points for loading and launching the compiled module ──
+struct Driver {
+    CUresult (*module_load)(CUmodule*, const void*) = nullptr;
+    CUresult (*module_unload)(CUmodule) = nullptr;
+    CUresult (*get_function)(CUfunction*, CUmodule, const char*) = nullptr;
+    CUresult (*launch)(CUfunction, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned, CUstream, void**, void**) = nullptr;
+    bool ok = false;
+};
+template <typename F>
+bool entry(const char* name, F& fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint(name, &p, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess || !p) return false;
+    fn = (F)p;
+    return true;
+}
+Driver& driver() {
+    static Driver d = [] {
+        Driver r;
+        r.ok = entry("cuModuleLoadData", r.module_load) && entry("cuModuleUnload", r.module_unload) &&
+               entry("cuModuleGetFunction", r.get_function) && entry("cuLaunchKernel", r.launch);
+        return r;
+    }();
+    return d;
+}
+
+// ── code generation ──
+struct Gen {
+    const sanic_generic_desc* d;
+    std::ostringstream out;
+    int fresh = 0;
+    std::string err;
+
+    std::string tmp() { return "t" + std::to_string(fresh++); }
+
+    static std::string lit(double v) {
+        const float f = (float)v;
+        uint32_t bits;
+        memcpy(&bits, &f, 4);
+        char buf[48];
+        snprintf(buf, sizeof buf, "__uint_as_float(0x%08xu)", bits);
+        return buf;
+    }
+
+    // element index of operand k at the current point; `s` is the name of the stream variable ("" outside the loop)
+    std::string address(int k, const std::string& s) {
+        const sanic_operand& o = d->operands[k];
+        std::ostringstream a;
+        a << "(" << (long long)o.offset << "LL";
+        for (int ax = 0; ax < d->n_axes; ++ax)
+            if (o.stride[ax] != 0) a << " + c" << ax << " * " << (long long)o.stride[ax] << "LL";
+        if (!s.empty() && o.stream_stride != 0) a << " + " << s << " * " << (long long)o.stream_stride << "LL";
+        a << ")";
+        return a.str();
+    }
+
+    std::string load(int k, const std::string& s, const std::string& indent) {
+        const sanic_operand& o = d->operands[k];
+        const std::string t = tmp(), idx = address(k, s), base = "bufs.p[" + std::to_string(o.buffer) + "]";
+        switch (o.dtype) {
+            case SANIC_F32: out << indent << "const float " << t << " = ((const float*)" << base << ")[" << idx << "];\n"; break;
+            case SANIC_BF16: out << indent << "const float " << t << " = widen_bf16(((const unsigned short*)" << base << ")[" << idx << "]);\n"; break;
+            case SANIC_U32: out << indent << "const float " << t << " = (float)((const unsigned*)" << base << ")[" << idx << "];\n"; break;
+            case SANIC_I4: out << indent << "const float " << t << " = load_i4((const unsigned char*)" << base << ", " << idx << ");\n"; break;
+            default: err = "generic emitter: operand dtype not supported"; out << indent << "const float " << t << " = 0.0f;\n";
+        }
+        return t;
+    }
+
+    // Renders one postfix program; returns the name of the value. `s`: stream variable or "".
+    std::string program(const sanic_expr& e, const std::string& s, const std::string& indent, const char* item, const char* a,
+                        const char* b, const char* f, const char* result) {
+        std::vector<std::string> st;
+        auto pop = [&]() -> std::string {
+            if (st.empty()) { err = "generic emitter: expression stack underflow"; return "0.0f"; }
+            std::string v = st.back(); st.pop_back(); return v;
+        };
+        auto named = [&](const char* base, int i, const char* what) {
+            if (!base) { err = std::string("generic emitter: ") + what + " read outside its program"; st.push_back("0.0f"); }
+            else st.push_back(std::string(base) + std::to_string(i));
+        };
+        if (e.first < 0 || e.count < 0 || e.first + e.count > d->n_ops) { err = "generic emitter: program outside the op array"; return "0.0f"; }
+        for (int i = e.first; i < e.first + e.count; ++i) {
+            const sanic_expr_op& op = d->ops[i];
+            auto unary = [&](const char* fn) { std::string x = pop(), t = tmp(); out << indent << "const float " << t << " = " << fn << "(" << x << ");\n"; st.push_back(t); };
+            auto binary = [&](const char* l, const char* m, const char* r) {
+                std::string y = pop(), x = pop(), t = tmp();
+                out << indent << "const float " << t << " = " << l << x << m << y << r << ";\n"; st.push_back(t);
+            };
+            switch (op.op) {
+                case SANIC_X_CONST: st.push_back(lit(op.value)); break;
+                case SANIC_X_LOAD:
+                    if (op.arg < 0 || op.arg >= d->n_operands) { err = "generic emitter: operand index out of range"; st.push_back("0.0f"); }
+                    else st.push_back(load(op.arg, s, indent));
+                    break;
+                case SANIC_X_COORD:
+                    if (op.arg == d->n_axes) {
+                        if (s.empty()) { err = "generic emitter: stream coordinate read outside the fold body"; st.push_back("0.0f"); }
+                        else st.push_back("(float)" + s);
+                    } else if (op.arg >= 0 && op.arg < d->n_axes) st.push_back("(float)c" + std::to_string(op.arg));
+                    else { err = "generic emitter: coordinate axis out of range"; st.push_back("0.0f"); }
+                    break;
+                case SANIC_X_ITEM: named(item, op.arg, "Item"); break;
+                case SANIC_X_A: named(a, op.arg, "A"); break;
+                case SANIC_X_B: named(b, op.arg, "B"); break;
+                case SANIC_X_F: named(f, op.arg, "F"); break;
+                case SANIC_X_RESULT: if (!result) { err = "generic emitter: Result read outside the epilogue"; st.push_back("0.0f"); } else st.push_back(result); break;
+                case SANIC_X_ADD: binary("", " + ", ""); break;
+                case SANIC_X_SUB: binary("", " - ", ""); break;
+                case SANIC_X_MUL: binary("", " * ", ""); break;
+                case SANIC_X_DIV: binary("", " / ", ""); break;
+                case SANIC_X_MAX: binary("fmaxf(", ", ", ")"); break;
+                case SANIC_X_MIN: binary("fminf(", ", ", ")"); break;
+                case SANIC_X_LT: binary("((", " < ", ") ? 1.0f : 0.0f)"); break;
+                case SANIC_X_NEG: unary("-"); break;
+                case SANIC_X_RECIP: unary("1.0f / "); break;
+                case SANIC_X_EXP: unary("expf"); break;
+                case SANIC_X_LOG: unary("logf"); break;
+                case SANIC_X_SQRT: unary("sqrtf"); break;
+                case SANIC_X_TANH: unary("tanhf"); break;
+                case SANIC_X_SIN: unary("sinf"); break;
+                case SANIC_X_COS: unary("cosf"); break;
+                case SANIC_X_WHERE: {
+                    std::string bb = pop(), aa = pop(), c = pop(), t = tmp();
+                    out << indent << "const float " << t << " = (" << c << " != 0.0f) ? " << aa << " : " << bb << ";\n";
+                    st.push_back(t);
+                    break;
+                }
+                case SANIC_X_ROUND:
+                    if (op.arg == SANIC_BF16) unary("round_bf16");
+                    else if (op.arg != SANIC_F32) err = "generic emitter: RoundTo width not supported";
+                    break;
+                default: err = "generic emitter: unknown op";
+            }
+        }
+        if (st.size() != 1) { err = "generic emitter: a program must leave exactly one value"; return "0.0f"; }
+        return st.back();
+    }
+};
+
+constexpr const char* PRELUDE = R"(
+struct Bufs { const void* p[16]; };
+__device__ __forceinline__ float widen_bf16(unsigned short h) { return __uint_as_float(((unsigned)h) << 16); }
+__device__ __forceinline__ unsigned short narrow_bf16(float f) {
+    unsigned b = __float_as_uint(f);
+    if (f != f) return (unsigned short)((b >> 16) | 0x0040u);
+    return (unsigned short)((b + 0x7FFFu + ((b >> 16) & 1u)) >> 16);
+}
+__device__ __forceinline__ float round_bf16(float f) { return widen_bf16(narrow_bf16(f)); }
+__device__ __forceinline__ float load_i4(const unsigned char* p, long long i) {
+    const unsigned byte = p[i >> 1];
+    return (float)(int)((i & 1) ? (byte >> 4) : (byte & 15u)) - 8.0f;
+}
+__device__ __forceinline__ unsigned store_u32(float f) {
+    if (!(f > 0.0f)) return 0u;
+    if (f >= 4294967296.0f) return 0xFFFFFFFFu;
+    return (unsigned)f;
+}
+)";
+
+int64_t grid_points(const sanic_generic_desc* d) {
+    int64_t n = 1;
+    for (int a = 0; a < d->n_axes; ++a) n *= d->extent[a];
+    return n;
+}
+
+int32_t validate(sanic_ctx* ctx, const sanic_generic_desc* d) {
+    if (!d) return sanic_fail(ctx, SANIC_ERR_INVALID, "generic emitter: null descriptor");
+    SANIC_REQUIRE(ctx, d->n_axes >= 0 && d->n_axes <= SANIC_MAX_AXES, "generic emitter: 0..6 grid axes");
+    for (int a = 0; a < d->n_axes; ++a) SANIC_REQUIRE(ctx, d->extent[a] > 0, "generic emitter: grid extents must be positive");
+    SANIC_REQUIRE(ctx, d->n_operands >= 0 && d->n_operands <= 64 && (d->n_operands == 0 || d->operands), "generic emitter: bad operand table");
+    for (int k = 0; k < d->n_operands; ++k)
+        SANIC_REQUIRE(ctx, d->operands[k].buffer >= 0 && d->operands[k].buffer < 16, "generic emitter: buffer index 0..15");
+    SANIC_REQUIRE(ctx, d->n_ops >= 0 && (d->n_ops == 0 || d->ops), "generic emitter: bad op array");
+    SANIC_REQUIRE(ctx, d->out_dtype == SANIC_F32 || d->out_dtype == SANIC_BF16 || d->out_dtype == SANIC_U32, "generic emitter: bad output dtype");
+    SANIC_REQUIRE(ctx, d->stream >= 0, "generic emitter: negative stream extent");
+    if (d->stream > 0) {
+        SANIC_REQUIRE(ctx, d->n_slots >= 1 && d->n_slots <= SANIC_MAX_SLOTS && d->identity && d->into && d->combine, "generic emitter: 1..8 slots with identity, into and combine");
+        SANIC_REQUIRE(ctx, d->n_leaves >= 0 && d->n_leaves <= 16 && (d->n_leaves == 0 || d->leaves), "generic emitter: 0..16 leaves");
+        SANIC_REQUIRE(ctx, d->lanes == 1 || d->lanes == 32, "generic emitter: lanes is 1 (one thread per point) or 32 (a warp per point)");
+    }
+    return SANIC_OK;
+}
+
+// The whole kernel as CUDA C text.
+int32_t render(sanic_ctx* ctx, const sanic_generic_desc* d, std::string* text) {
+    int32_t rc = validate(ctx, d);
+    if (rc != SANIC_OK) return rc;
+    Gen g{d};
+    std::ostringstream& o = g.out;
+    const int64_t points = grid_points(d);
+    const bool fold = d->stream > 0;
+    const bool coop = fold && d->lanes == 32;
+    o << PRELUDE;
+    o << "extern \"C\" __global__ void __launch_bounds__(256) sanic_generic(Bufs bufs, void* outp) {\n";
+    if (coop) {
+        o << "    const long long gid = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;\n";
+        o << "    const int lane = threadIdx.x & 31;\n";
+    } else {
+        o << "    const long long gid = blockIdx.x * (long long)blockDim.x + threadIdx.x;\n";
+    }
+    o << "    if (gid >= " << (long long)points << "LL) return;\n";
+    // row-major decode of the grid point, last axis fastest (src/codegen.rs grid decode)
+    o << "    long long rem = gid;\n";
+    for (int a = d->n_axes - 1; a >= 0; --a) {
+        o << "    const long long c" << a << " = rem % " << (long long)d->extent[a] << "LL; rem /= " << (long long)d->extent[a] << "LL;\n";
+    }
+    o << "    (void)rem;\n";
+    std::string result;
+    if (fold) {
+        const int S = d->n_slots;
+        for (int i = 0; i < S; ++i) o << "    float acc" << i << " = " << Gen::lit(d->identity[i]) << ";\n";
+        const long long n = (long long)d->stream;
+        if (coop) {
+            const long long B = n < 32 ? n : 32;
+            if (d->interleave) {
+                o << "    for (long long s = lane; s < " << n << "LL; s += 32) {\n";
+            } else {
+                o << "    const long long s_lo = (lane < " << B << ") ? (lane * " << n << "LL) / " << B << " : 0;\n";
+                o << "    const long long s_hi = (lane < " << B << ") ? ((lane + 1) * " << n << "LL) / " << B << " : 0;\n";
+                o << "    for (long long s = s_lo; s < s_hi; ++s) {\n";
+            }
+        } else {
+            o << "    for (long long s = 0; s < " << n << "LL; ++s) {\n";
+        }
+        const std::string in2 = "        ";
+        for (int l = 0; l < d->n_leaves; ++l) {
+            const std::string v = g.program(d->leaves[l], "s", in2, nullptr, nullptr, nullptr, nullptr, nullptr);
+            o << in2 << "const float x" << l << " = " << v << ";\n";
+        }
+        for (int i = 0; i < S; ++i) {
+            const std::string v = g.program(d->into[i], "s", in2, "x", nullptr, nullptr, nullptr, nullptr);
+            o << in2 << "const float el" << i << " = " << v << ";\n";
+        }
+        // every new slot is computed from the OLD accumulator before any slot is overwritten
+        for (int i = 0; i < S; ++i) {
+            const std::string v = g.program(d->combine[i], "s", in2, nullptr, "acc", "el", nullptr, nullptr);
+            o << in2 << "const float na" << i << " = " << v << ";\n";
+        }
+        for (int i = 0; i < S; ++i) o << in2 << "acc" << i << " = na" << i << ";\n";
+        o << "    }\n";
+        if (coop) {
+            // ordered tree over the lanes: the lower lane is the left operand, lanes without a chunk never take part
+            const long long B = d->interleave ? 32 : (n < 32 ? n : 32);
+            o << "    #pragma unroll\n    for (int off = 1; off < 32; off <<= 1) {\n";
+            for (int i = 0; i < S; ++i) o << "        const float pb" << i << " = __shfl_down_sync(0xffffffffu, acc" << i << ", off);\n";
+            o << "        const bool take = ((lane & (2 * off - 1)) == 0) && (lane + off < " << B << ");\n";
+            const std::string in2b = "        ";
+            for (int i = 0; i < S; ++i) {
+                const std::string v = g.program(d->combine[i], "", in2b, nullptr, "acc", "pb", nullptr, nullptr);
+                o << in2b << "const float ma" << i << " = " << v << ";\n";
+            }
+            for (int i = 0; i < S; ++i) o << in2b << "if (take) acc" << i << " = ma" << i << ";\n";
+            o << "    }\n";
+            o << "    if (lane != 0) return;\n";
+        }
+        result = g.program(d->project, "", "    ", nullptr, nullptr, nullptr, "acc", nullptr);
+    } else {
+        result = g.program(d->project, "", "    ", nullptr, nullptr, nullptr, nullptr, nullptr);
+    }
+    if (d->epilogue.count > 0) {
+        o << "    const float fv = " << result << ";\n";
+        result = g.program(d->epilogue, "", "    ", nullptr, nullptr, nullptr, nullptr, "fv");
+    }
+    switch (d->out_dtype) {
+        case SANIC_F32: o << "    ((float*)outp)[gid] = " << result << ";\n"; break;
+        case SANIC_BF16: o << "    ((unsigned short*)outp)[gid] = narrow_bf16(" << result << ");\n"; break;
+        default: o << "    ((unsigned*)outp)[gid] = store_u32(" << result << ");\n"; break;
+    }
+    o << "}\n";
+    if (!g.err.empty()) return sanic_fail(ctx, SANIC_ERR_INVALID, g.err);
+    *text = o.str();
+    return SANIC_OK;
+}
+
+int32_t compile_cubin(sanic_ctx* ctx, const std::string& text, std::vector<char>* cubin) {
+    Nvrtc& n = nvrtc();
+    if (!n.ok) return sanic_fail(ctx, SANIC_ERR_UNSUPPORTED, "generic emitter: the NVRTC library could not be loaded");
+    nvrtcProgram prog;
+    nvrtcResult r = n.create(&prog, text.c_str(), "sanic_generic.cu", 0, nullptr, nullptr);
+    if (r != NVRTC_SUCCESS) return sanic_fail(ctx, SANIC_ERR_CUDA, std::string("nvrtcCreateProgram: ") + n.err(r));
+    const char* opts[] = {"--gpu-architecture=sm_100a", "-lineinfo", "--fmad=true"};
+    r = n.compile(prog, 3, opts);
+    if (r != NVRTC_SUCCESS) {
+        size_t ls = 0;
+        n.log_size(prog, &ls);
+        std::string log(ls, '\0');
+        if (ls) n.log(prog, &log[0]);
+        n.destroy(&prog);
+        return sanic_fail(ctx, SANIC_ERR_CUDA, std::string("generated kernel failed to compile: ") + n.err(r) + "\n" + log);
+    }
+    size_t sz = 0;
+    n.cubin_size(prog, &sz);
+    cubin->resize(sz);
+    if (sz) n.cubin(prog, cubin->data());
+    n.destroy(&prog);
+    if (!sz) return sanic_fail(ctx, SANIC_ERR_CUDA, "generated kernel: empty cubin");
+    return SANIC_OK;
+}
+
+}  // namespace
+
+struct sanic_generic_kernel {
+    CUmodule module = nullptr;
+    CUfunction fn = nullptr;
+    int64_t points = 0;
+    int lanes = 1;
+    int n_buffers = 0;
+};
+
+extern "C" {
+
+int32_t sanic_generic_source(sanic_ctx* ctx, const sanic_generic_desc* d, char* buf, size_t cap, size_t* needed) {
+    std::string text;
+    int32_t rc = render(ctx, d, &text);
+    if (rc != SANIC_OK) return rc;
+    if (needed) *needed = text.size() + 1;
+    if (buf && cap) {
+        const size_t n = text.size() < cap - 1 ? text.size() : cap - 1;
+        memcpy(buf, text.data(), n);
+        buf[n] = '\0';
+    }
+    return SANIC_OK;
+}
+
+int32_t sanic_generic_cubin_size(sanic_ctx* ctx, const sanic_generic_desc* d, size_t* bytes) {
+    std::string text;
+    int32_t rc = render(ctx, d, &text);
+    if (rc != SANIC_OK) return rc;
+    std::vector<char> cubin;
+    rc = compile_cubin(ctx, text, &cubin);
+    if (rc != SANIC_OK) return rc;
+    if (bytes) *bytes = cubin.size();
+    return SANIC_OK;
+}
+
+int32_t sanic_generic_compile(sanic_ctx* ctx, const sanic_generic_desc* d, sanic_generic_kernel** out) {
+    if (!ctx || !out) return SANIC_ERR_INVALID;
+    *out = nullptr;
+    std::string text;
+    int32_t rc = render(ctx, d, &text);
+    if (rc != SANIC_OK) return rc;
+    std::vector<char> cubin;
+    rc = compile_cubin(ctx, text, &cubin);
+    if (rc != SANIC_OK) return rc;
+    sanic_set_device(ctx);
+    SANIC_CUDA_CHECK(ctx, cudaFree(nullptr));   // the primary context exists and is current
+    Driver& dr = driver();
+    if (!dr.ok) return sanic_fail(ctx, SANIC_ERR_CUDA, "generic emitter: driver entry points for module loading not found");
+    sanic_generic_kernel* k = new sanic_generic_kernel();
+    CUresult cr = dr.module_load(&k->module, cubin.data());
+    if (cr != CUDA_SUCCESS) { delete k; return sanic_fail(ctx, SANIC_ERR_CUDA, "cuModuleLoadData failed with code " + std::to_string((int)cr)); }
+    cr = dr.get_function(&k->fn, k->module, "sanic_generic");
+    if (cr != CUDA_SUCCESS) { dr.module_unload(k->module); delete k; return sanic_fail(ctx, SANIC_ERR_CUDA, "cuModuleGetFunction failed with code " + std::to_string((int)cr)); }
+    k->points = grid_points(d);
+    k->lanes = (d->stream > 0 && d->lanes == 32) ? 32 : 1;
+    for (int i = 0; i < d->n_operands; ++i) if (d->operands[i].buffer + 1 > k->n_buffers) k->n_buffers = d->operands[i].buffer + 1;
+    *out = k;
+    return SANIC_OK;
+}
+
+int32_t sanic_generic_launch(sanic_ctx* ctx, sanic_generic_kernel* k, const void* const* buffers, int32_t n_buffers, void* out,
+                             void* stream) {
+    if (!ctx || !k) return SANIC_ERR_INVALID;
+    SANIC_REQUIRE(ctx, out, "generic launch: null output");
+    SANIC_REQUIRE(ctx, n_buffers >= k->n_buffers && n_buffers <= 16, "generic launch: the kernel reads more buffers than were bound");
+    struct { const void* p[16]; } bufs = {};
+    for (int i = 0; i < n_buffers; ++i) {
+        SANIC_REQUIRE(ctx, buffers && (buffers[i] || i >= k->n_buffers), "generic launch: unbound buffer");
+        bufs.p[i] = buffers[i];
+    }
+    const int64_t threads = k->points * k->lanes;
+    const int64_t blocks = (threads + 255) / 256;
+    SANIC_REQUIRE(ctx, blocks <= 0x7FFFFFFFLL, "generic launch: grid too large");
+    void* args[] = {&bufs, &out};
+    sanic_set_device(ctx);
+    CUresult cr = driver().launch(k->fn, (unsigned)blocks, 1, 1, 256, 1, 1, 0, (CUstream)stream, args, nullptr);
+    if (cr != CUDA_SUCCESS) return sanic_fail(ctx, SANIC_ERR_CUDA, "cuLaunchKernel failed with code " + std::to_string((int)cr));
+    return SANIC_OK;
+}
+
+int32_t sanic_generic_destroy(sanic_generic_kernel* k) {
+    if (!k) return SANIC_ERR_INVALID;
+    if (k->module && driver().ok) driver().module_unload(k->module);
+    delete k;
+    return SANIC_OK;
+}
+
+}  // extern "C"

@@ -26,6 +26,14 @@ struct sanic_program {
 
 namespace {
 int32_t check_stage(sanic_ctx* ctx, const sanic_stage_desc& s) {
+    if (s.op == SANIC_OP_GENERIC) {
+        // a compiled fallback kernel stands for any stage kind: a carrier no specialised kernel matches, a cone, a gather
+        if (s.stage_kind != SANIC_STAGE_FUSED && s.stage_kind != SANIC_STAGE_ELEMENTWISE && s.stage_kind != SANIC_STAGE_GATHER)
+            return sanic_fail(ctx, SANIC_ERR_INVALID, "program: unknown stage kind");
+        if (!s.u.generic.kernel || !s.u.generic.out || s.u.generic.n_buffers < 0 || s.u.generic.n_buffers > 16)
+            return sanic_fail(ctx, SANIC_ERR_INVALID, "program: a generic stage needs a compiled kernel, its buffers and an output");
+        return SANIC_OK;
+    }
     if (s.stage_kind == SANIC_STAGE_FUSED) {
         int32_t family = 0;
         int32_t rc = sanic_emit_select(&s.carrier, &family);
@@ -66,6 +74,8 @@ int32_t run_stage(sanic_ctx* ctx, const sanic_stage_desc& s, void* stream) {
                                       s.u.embed.vocab, s.u.embed.out, stream);
         case SANIC_OP_ROPE_CACHE: return sanic_rope_cache_write(ctx, &s.u.rope_cache, stream);
         case SANIC_OP_ADVANCE: return sanic_advance_position(ctx, s.u.advance.position, stream);
+        case SANIC_OP_GENERIC:
+            return sanic_generic_launch(ctx, s.u.generic.kernel, s.u.generic.buffers, s.u.generic.n_buffers, s.u.generic.out, stream);
         default: return sanic_fail(ctx, SANIC_ERR_INVALID, "program: unknown op");
     }
 }

@@ -1,0 +1,241 @@
+"""Host side of the generic emitter: carriers as expression programs -> generated CUDA kernels.
+
+A carrier here is the reference's own (src/derive.rs:262-287 of the reference project): `leaves` (the
+per-element inputs of the fold), `into` (lift one element), `combine` (the associative merge over two
+accumulators), `identity`, `project`. Expressions are trees over the closed scalar basis
+(src/scalar.rs:45-69; Expr, src/derive.rs:96-118), built with the operators and functions of this
+module and flattened to the postfix programs of the C ABI. The generated kernel is the fallback for
+carriers no specialised kernel matches (scalar fold / cooperative fold) and the pointwise kernel for
+elementwise cones (src/emit_metal.rs:626-1178).
+
+Nothing here computes: `describe` only packs a descriptor, `source` and `compiles` render and compile
+without a device, `GenericKernel` compiles, loads and launches through libsanic_b200.so.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass, field
+from typing import Sequence
+
+from . import _abi as abi
+
+
+class E:
+    """An expression node. Build with the helpers below; Python operators map onto the scalar basis."""
+    __slots__ = ("op", "arg", "value", "kids")
+
+    def __init__(self, op, arg=0, value=0.0, kids=()):
+        self.op, self.arg, self.value, self.kids = op, arg, float(value), tuple(kids)
+
+    @staticmethod
+    def of(x) -> "E":
+        return x if isinstance(x, E) else const(x)
+
+    def __add__(self, o): return E(abi.X_ADD, kids=(self, E.of(o)))
+    def __radd__(self, o): return E(abi.X_ADD, kids=(E.of(o), self))
+    def __sub__(self, o): return E(abi.X_SUB, kids=(self, E.of(o)))
+    def __rsub__(self, o): return E(abi.X_SUB, kids=(E.of(o), self))
+    def __mul__(self, o): return E(abi.X_MUL, kids=(self, E.of(o)))
+    def __rmul__(self, o): return E(abi.X_MUL, kids=(E.of(o), self))
+    def __truediv__(self, o): return E(abi.X_DIV, kids=(self, E.of(o)))
+    def __rtruediv__(self, o): return E(abi.X_DIV, kids=(E.of(o), self))
+    def __neg__(self): return E(abi.X_NEG, kids=(self,))
+    def __lt__(self, o): return E(abi.X_LT, kids=(self, E.of(o)))      # 1.0 / 0.0
+    def __gt__(self, o): return E(abi.X_LT, kids=(E.of(o), self))
+
+    def flatten(self, out: list):
+        for k in self.kids:
+            k.flatten(out)
+        out.append((self.op, self.arg, self.value))
+
+
+def const(v) -> E: return E(abi.X_CONST, value=v)
+def load(operand: int) -> E: return E(abi.X_LOAD, arg=operand)
+def coord(axis: int) -> E: return E(abi.X_COORD, arg=axis)
+def item(i: int) -> E: return E(abi.X_ITEM, arg=i)
+def A(i: int) -> E: return E(abi.X_A, arg=i)
+def B(i: int) -> E: return E(abi.X_B, arg=i)
+def F(i: int) -> E: return E(abi.X_F, arg=i)
+def result() -> E: return E(abi.X_RESULT)
+def maximum(a, b) -> E: return E(abi.X_MAX, kids=(E.of(a), E.of(b)))
+def minimum(a, b) -> E: return E(abi.X_MIN, kids=(E.of(a), E.of(b)))
+def recip(a) -> E: return E(abi.X_RECIP, kids=(E.of(a),))
+def exp(a) -> E: return E(abi.X_EXP, kids=(E.of(a),))
+def log(a) -> E: return E(abi.X_LOG, kids=(E.of(a),))
+def sqrt(a) -> E: return E(abi.X_SQRT, kids=(E.of(a),))
+def tanh(a) -> E: return E(abi.X_TANH, kids=(E.of(a),))
+def sin(a) -> E: return E(abi.X_SIN, kids=(E.of(a),))
+def cos(a) -> E: return E(abi.X_COS, kids=(E.of(a),))
+def where(c, a, b) -> E: return E(abi.X_WHERE, kids=(E.of(c), E.of(a), E.of(b)))
+def round_to(a, dtype: int) -> E: return E(abi.X_ROUND, arg=dtype, kids=(E.of(a),))
+
+
+@dataclass
+class Operand:
+    """A typed, strided view of one bound buffer: element index = offset + sum(coord * stride) + s * stream_stride."""
+    buffer: int
+    dtype: int
+    strides: Sequence[int]
+    stream_stride: int = 0
+    offset: int = 0
+
+
+@dataclass
+class Carrier:
+    """leaves / into / combine / identity / project, as in the reference's `Carrier`."""
+    leaves: Sequence[E]
+    into: Sequence[E]
+    combine: Sequence[E]
+    identity: Sequence[float]
+    project: E
+
+
+# ── the carriers the reference's laws pin (tests/laws.rs:107-126,620-646; tests/compile.rs:139-171) ──
+def carrier_sum(leaf: E) -> Carrier:
+    return Carrier([leaf], [item(0)], [A(0) + B(0)], [0.0], F(0))
+
+
+def carrier_max(leaf: E) -> Carrier:
+    return Carrier([leaf], [item(0)], [maximum(A(0), B(0))], [float("-inf")], F(0))
+
+
+def _shift(side, m):
+    """exp(side - m), forced to 0 when the side's maximum is -inf (src/derive.rs:1700-1713)."""
+    return where(const(float("-inf")) < side, exp(side - m), 0.0)
+
+
+def carrier_online_softmax(score: E, value: E) -> Carrier:
+    """(m, l, o): Plain(Max), ExpShifted{0}, ExpShifted{0}; project o / l."""
+    m = maximum(A(0), B(0))
+    return Carrier([score, value], [item(0), const(1.0), item(1)],
+                   [m, A(1) * _shift(A(0), m) + B(1) * _shift(B(0), m), A(2) * _shift(A(0), m) + B(2) * _shift(B(0), m)],
+                   [float("-inf"), 0.0, 0.0], F(2) / F(1))
+
+
+def carrier_logsumexp(leaf: E) -> Carrier:
+    m = maximum(A(0), B(0))
+    return Carrier([leaf], [item(0), const(1.0)], [m, A(1) * _shift(A(0), m) + B(1) * _shift(B(0), m)],
+                   [float("-inf"), 0.0], F(0) + log(F(1)))
+
+
+def carrier_deferred_norm(x: E, gamma_w: E, n: int, eps: float) -> Carrier:
+    """2 x Plain(Add): sum x^2 and sum x*gamma*w; project dot / sqrt(sum x^2 / n + eps) (defer-div)."""
+    return Carrier([x, gamma_w], [item(0) * item(0), item(0) * item(1)], [A(0) + B(0), A(1) + B(1)], [0.0, 0.0],
+                   F(1) / sqrt(F(0) * (1.0 / n) + eps))
+
+
+def carrier_first_argmax(leaf: E, index: E) -> Carrier:
+    """(Plain(Max), AtExtremum{key 0, Max, ties Min}): the first maximal index (src/ir.rs:1415-1433)."""
+    key = maximum(A(0), B(0))
+    idx = where(A(0) < B(0), B(1), where(B(0) < A(0), A(1), minimum(A(1), B(1))))
+    return Carrier([leaf, index], [item(0), item(1)], [key, idx], [float("-inf"), float("inf")], F(1))
+
+
+class Description:
+    """A packed sanic_generic_desc with the ctypes arrays it points into kept alive."""
+
+    def __init__(self, grid: Sequence[int], operands: Sequence[Operand], *, carrier: Carrier | None = None, stream: int = 0,
+                 value: E | None = None, epilogue: E | None = None, out_dtype: int = abi.F32, lanes: int = 1,
+                 interleave: bool = False):
+        if len(grid) > abi.MAX_AXES:
+            raise ValueError(f"at most {abi.MAX_AXES} grid axes")
+        if (carrier is None) == (value is None):
+            raise ValueError("give a carrier (a fold) or a value (a pointwise kernel), not both")
+        if carrier is not None and stream <= 0:
+            raise ValueError("a fold needs a positive streamed extent")
+        ops: list = []
+
+        def prog(e: E) -> abi.Expr:
+            first = len(ops)
+            e.flatten(ops)
+            return abi.Expr(first, len(ops) - first)
+
+        d = abi.GenericDesc()
+        d.n_axes = len(grid)
+        for i, g in enumerate(grid):
+            d.extent[i] = int(g)
+        d.stream = int(stream) if carrier is not None else 0
+        d.lanes, d.interleave = int(lanes), int(bool(interleave))
+        self._operands = (abi.Operand * max(1, len(operands)))()
+        for i, o in enumerate(operands):
+            if len(o.strides) != len(grid):
+                raise ValueError("an operand needs one stride per grid axis")
+            self._operands[i].dtype, self._operands[i].buffer = int(o.dtype), int(o.buffer)
+            self._operands[i].offset, self._operands[i].stream_stride = int(o.offset), int(o.stream_stride)
+            for a, s in enumerate(o.strides):
+                self._operands[i].stride[a] = int(s)
+        d.n_operands, d.operands = len(operands), self._operands
+        if carrier is not None:
+            n = len(carrier.into)
+            if not (len(carrier.combine) == len(carrier.identity) == n):
+                raise ValueError("into, combine and identity must have one entry per slot")
+            self._leaves = (abi.Expr * max(1, len(carrier.leaves)))(*[prog(e) for e in carrier.leaves])
+            self._into = (abi.Expr * n)(*[prog(e) for e in carrier.into])
+            self._combine = (abi.Expr * n)(*[prog(e) for e in carrier.combine])
+            self._identity = (C.c_double * n)(*[float(v) for v in carrier.identity])
+            d.n_leaves, d.leaves, d.n_slots = len(carrier.leaves), self._leaves, n
+            d.identity, d.into, d.combine = self._identity, self._into, self._combine
+            d.project = prog(carrier.project)
+        else:
+            d.project = prog(value)
+        d.epilogue = prog(epilogue) if epilogue is not None else abi.Expr(0, 0)
+        d.out_dtype = int(out_dtype)
+        self._ops = (abi.ExprOp * max(1, len(ops)))(*[abi.ExprOp(o, a, v) for o, a, v in ops])
+        d.n_ops, d.ops = len(ops), self._ops
+        self.desc = d
+        self.points = 1
+        for g in grid:
+            self.points *= int(g)
+        self.n_buffers = 1 + max((o.buffer for o in operands), default=-1)
+
+
+def source(desc: Description) -> str:
+    """The generated CUDA C text. Needs the library, not a device."""
+    lib = abi.load()
+    need = C.c_size_t()
+    rc = lib.sanic_generic_source(None, C.byref(desc.desc), None, 0, C.byref(need))
+    if rc != abi.OK:
+        raise ValueError(f"the descriptor does not render (status {rc})")
+    buf = C.create_string_buffer(need.value)
+    lib.sanic_generic_source(None, C.byref(desc.desc), buf, need.value, None)
+    return buf.value.decode()
+
+
+def compiles(desc: Description) -> int:
+    """Compiles the generated text for sm_100a without loading it; returns the cubin size. Needs no device."""
+    lib = abi.load()
+    n = C.c_size_t()
+    rc = lib.sanic_generic_cubin_size(None, C.byref(desc.desc), C.byref(n))
+    if rc != abi.OK:
+        raise RuntimeError(f"the generated kernel does not compile (status {rc})")
+    return n.value
+
+
+class GenericKernel:
+    """A compiled and loaded generic kernel on one device (the Executable of one stage)."""
+
+    def __init__(self, device, desc: Description):
+        self.device, self.desc = device, desc
+        h = C.c_void_p()
+        device._check(device.lib.sanic_generic_compile(device.h, C.byref(desc.desc), C.byref(h)), "generic_compile")
+        self.h = h
+
+    def __call__(self, buffers, out):
+        """buffers: torch tensors on the device, in buffer-index order; out: a tensor of grid size at the output dtype."""
+        if out.numel() != self.desc.points:
+            raise ValueError("the output must hold one element per grid point")
+        arr = (C.c_void_p * max(1, len(buffers)))(*[C.c_void_p(b.data_ptr()) for b in buffers])
+        self.device._check(self.device.lib.sanic_generic_launch(self.device.h, self.h, arr, len(buffers), C.c_void_p(out.data_ptr()),
+                                                                self.device.stream()), "generic_launch")
+        return out
+
+    def close(self):
+        if getattr(self, "h", None):
+            self.device.lib.sanic_generic_destroy(self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
