@@ -252,6 +252,9 @@ enum { SANIC_X_CONST = 1,   /* value */
        SANIC_X_A = 5, SANIC_X_B = 6,   /* arg = slot of the left / right accumulator (combine) */
        SANIC_X_F = 7,       /* arg = slot of the final accumulator (project) */
        SANIC_X_RESULT = 8,  /* the projected value (epilogue) */
+       SANIC_X_GATHER = 9,  /* arg = operand index; pops the index value: reads the operand at round(index) along its gather
+                               axis (Gather: round, then a bounds check, src/interp.rs:378-379). An index out of range reads 0
+                               and the next sanic_sync fails with SANIC_ERR_INVALID */
        SANIC_X_ADD = 16, SANIC_X_SUB, SANIC_X_MUL, SANIC_X_DIV, SANIC_X_MAX, SANIC_X_MIN,
        SANIC_X_LT,          /* a < b as 1.0 / 0.0 */
        SANIC_X_NEG, SANIC_X_RECIP, SANIC_X_EXP, SANIC_X_LOG, SANIC_X_SQRT, SANIC_X_TANH, SANIC_X_SIN, SANIC_X_COS,
@@ -265,12 +268,17 @@ typedef struct {
     int64_t offset;                     /* elements */
     int64_t stride[SANIC_MAX_AXES];     /* elements per step of each grid axis; 0 broadcasts */
     int64_t stream_stride;              /* elements per step of the streamed axis */
+    int64_t gather_stride;              /* elements per step of the gathered index (SANIC_X_GATHER only) */
+    int64_t gather_extent;              /* valid indices are 0 .. gather_extent-1 */
 } sanic_operand;
 typedef struct {
     int32_t n_axes;                     /* output grid, row-major, last axis fastest */
     int64_t extent[SANIC_MAX_AXES];
     int64_t stream;                     /* streamed extent; 0 = pointwise kernel: out[point] = project */
     int32_t lanes;                      /* 1: one thread per output point; 32: a warp per point (cooperative fold) */
+    int32_t warps;                      /* lanes == 32 only: 0 or 1 = one warp per point; 2..8 = a block of that many warps per
+                                           point, the chunking below taken over all its threads (B = min(32*warps, n)), warp
+                                           partials merged in warp order through shared memory */
     int32_t interleave;                 /* lanes == 32 only. 0: lane b folds the contiguous chunk [b*n/B, (b+1)*n/B), B = min(32, n),
                                            merged in lane order (run_carrier_split, src/interp.rs:597-640): legal for every carrier.
                                            1: lane b folds s = b, b+32, ...: needs a carrier that merges out of order (src/plan.rs:481-488) */
@@ -282,6 +290,9 @@ typedef struct {
     const sanic_expr* combine;                            /* per slot, over A and B; all slots read the old accumulator */
     sanic_expr project;                                   /* over F (and LOAD / COORD at the grid point) */
     sanic_expr epilogue;                                  /* count 0 = none; over RESULT and LOAD / COORD at the grid point */
+    sanic_expr store_if;                                  /* count 0 = always; else the point is stored only where this is != 0:
+                                                             the in-place form of where(c, x, s) writing s's own buffer, which
+                                                             never loads s (src/emit_metal.rs:1118-1178) */
     int32_t out_dtype;                                    /* SANIC_F32 / SANIC_BF16 (RNE) / SANIC_U32 (saturating) */
 } sanic_generic_desc;
 typedef struct sanic_generic_kernel sanic_generic_kernel;

@@ -34,6 +34,7 @@ def _run(prog, env):
         if name == "const": st.append(np.float64(value))
         elif name == "load": st.append(env["load"](arg))
         elif name == "coord": st.append(env["coord"](arg))
+        elif name == "gather": st.append(env["gather"](arg, st.pop()))
         elif name in ("item", "a", "b", "f"): st.append(env[name][arg])
         elif name == "result": st.append(env["result"])
         elif name in ("neg", "recip", "exp", "log", "sqrt", "tanh", "sin", "cos", "round_bf16", "round_f32"):
@@ -86,7 +87,15 @@ class _Point:
                     raise ValueError("stream coordinate outside the fold body")
                 return np.full(self.grid, float(s))
             return self.coords[a].astype(np.float64)
-        return {"load": load, "coord": coord}
+        def gather(k, index):
+            # index = round() (half away from zero), then a bounds check (src/interp.rs:378-379)
+            o = self.operands[k]
+            gi = np.broadcast_to(np.trunc(np.asarray(index, np.float64) + np.copysign(0.5, index)), self.grid).astype(np.int64)
+            if np.any(gi < 0) or np.any(gi >= int(o["gather_extent"])):
+                raise IndexError("gather index out of range")
+            idx = self.base[k] + (0 if s is None else s * int(o["stream_stride"])) + gi * int(o["gather_stride"])
+            return self.buffers[int(o["buffer"])][idx]
+        return {"load": load, "coord": coord, "gather": gather}
 
 
 def pointwise(grid, operands, buffers, value, epilogue=None) -> np.ndarray:

@@ -20,7 +20,7 @@ EPI_STORE, EPI_RESIDUAL_ADD, EPI_SILU_MUL, EPI_ROPE_CACHE = 0, 1, 2, 3
 STAGE_FUSED, STAGE_ELEMENTWISE, STAGE_GATHER = 1, 2, 3
 OP_GEMV, OP_DECODE_ATTN, OP_ARGMAX, OP_RMSNORM, OP_EMBED, OP_ROPE_CACHE, OP_ADVANCE, OP_GENERIC = 1, 2, 3, 4, 5, 6, 7, 8
 MAX_AXES, MAX_SLOTS = 6, 8
-X_CONST, X_LOAD, X_COORD, X_ITEM, X_A, X_B, X_F, X_RESULT = 1, 2, 3, 4, 5, 6, 7, 8
+X_CONST, X_LOAD, X_COORD, X_ITEM, X_A, X_B, X_F, X_RESULT, X_GATHER = 1, 2, 3, 4, 5, 6, 7, 8, 9
 (X_ADD, X_SUB, X_MUL, X_DIV, X_MAX, X_MIN, X_LT, X_NEG, X_RECIP, X_EXP, X_LOG, X_SQRT, X_TANH, X_SIN, X_COS, X_WHERE,
  X_ROUND) = range(16, 33)
 
@@ -114,15 +114,16 @@ class Expr(C.Structure):
 
 
 class Operand(C.Structure):
-    _fields_ = [("dtype", i32), ("buffer", i32), ("offset", i64), ("stride", i64 * MAX_AXES), ("stream_stride", i64)]
+    _fields_ = [("dtype", i32), ("buffer", i32), ("offset", i64), ("stride", i64 * MAX_AXES), ("stream_stride", i64),
+                ("gather_stride", i64), ("gather_extent", i64)]
 
 
 class GenericDesc(C.Structure):
-    _fields_ = [("n_axes", i32), ("extent", i64 * MAX_AXES), ("stream", i64), ("lanes", i32), ("interleave", i32),
+    _fields_ = [("n_axes", i32), ("extent", i64 * MAX_AXES), ("stream", i64), ("lanes", i32), ("warps", i32), ("interleave", i32),
                 ("n_operands", i32), ("operands", C.POINTER(Operand)), ("n_ops", i32), ("ops", C.POINTER(ExprOp)),
                 ("n_leaves", i32), ("leaves", C.POINTER(Expr)), ("n_slots", i32), ("identity", C.POINTER(C.c_double)),
                 ("into", C.POINTER(Expr)), ("combine", C.POINTER(Expr)), ("project", Expr), ("epilogue", Expr),
-                ("out_dtype", i32)]
+                ("store_if", Expr), ("out_dtype", i32)]
 
 
 # name -> (restype, argtypes); every symbol the header declares

@@ -163,6 +163,27 @@ struct Gen {
                     if (op.arg < 0 || op.arg >= d->n_operands) { err = "generic emitter: operand index out of range"; st.push_back("0.0f"); }
                     else st.push_back(load(op.arg, s, indent));
                     break;
+                case SANIC_X_GATHER: {
+                    // index = round(value), half away from zero, then a bounds check (src/interp.rs:378-379); an index out
+                    // of range reads 0 and leaves code 51 in the status word
+                    if (op.arg < 0 || op.arg >= d->n_operands) { err = "generic emitter: operand index out of range"; st.push_back("0.0f"); break; }
+                    const sanic_operand& o = d->operands[op.arg];
+                    if (o.gather_extent <= 0) { err = "generic emitter: a gathered operand needs a gather extent"; st.push_back("0.0f"); break; }
+                    if (o.dtype == SANIC_I4) { err = "generic emitter: gather of an int4 operand is not supported"; st.push_back("0.0f"); break; }
+                    const std::string idx = pop(), gi = tmp(), t = tmp();
+                    const std::string base = "bufs.p[" + std::to_string(o.buffer) + "]";
+                    const std::string at = "[" + address(op.arg, s) + " + " + gi + " * " + std::to_string((long long)o.gather_stride) + "LL]";
+                    out << indent << "const long long " << gi << " = (long long)roundf(" << idx << ");\n";
+                    out << indent << "float " << t << " = 0.0f;\n";
+                    out << indent << "if (" << gi << " >= 0 && " << gi << " < " << (long long)o.gather_extent << "LL) " << t << " = ";
+                    if (o.dtype == SANIC_F32) out << "((const float*)" << base << ")" << at;
+                    else if (o.dtype == SANIC_BF16) out << "widen_bf16(((const unsigned short*)" << base << ")" << at << ")";
+                    else if (o.dtype == SANIC_U32) out << "(float)((const unsigned*)" << base << ")" << at;
+                    else err = "generic emitter: operand dtype not supported";
+                    out << "; else atomicCAS(status, 0, 51);\n";
+                    st.push_back(t);
+                    break;
+                }
                 case SANIC_X_COORD:
                     if (op.arg == d->n_axes) {
                         if (s.empty()) { err = "generic emitter: stream coordinate read outside the fold body"; st.push_back("0.0f"); }
@@ -248,6 +269,8 @@ int32_t validate(sanic_ctx* ctx, const sanic_generic_desc* d) {
         SANIC_REQUIRE(ctx, d->n_slots >= 1 && d->n_slots <= SANIC_MAX_SLOTS && d->identity && d->into && d->combine, "generic emitter: 1..8 slots with identity, into and combine");
         SANIC_REQUIRE(ctx, d->n_leaves >= 0 && d->n_leaves <= 16 && (d->n_leaves == 0 || d->leaves), "generic emitter: 0..16 leaves");
         SANIC_REQUIRE(ctx, d->lanes == 1 || d->lanes == 32, "generic emitter: lanes is 1 (one thread per point) or 32 (a warp per point)");
+        SANIC_REQUIRE(ctx, d->warps >= 0 && d->warps <= 8 && (d->warps <= 1 || d->lanes == 32),
+                      "generic emitter: 1..8 warps per point, more than one only with lanes = 32");
     }
     return SANIC_OK;
 }
@@ -261,9 +284,15 @@ int32_t render(sanic_ctx* ctx, const sanic_generic_desc* d, std::string* text) {
     const int64_t points = grid_points(d);
     const bool fold = d->stream > 0;
     const bool coop = fold && d->lanes == 32;
+    const int W = (coop && d->warps > 1) ? d->warps : 1;      // warps per output point
+    const long long T = 32LL * W;                             // threads per output point
     o << PRELUDE;
-    o << "extern \"C\" __global__ void __launch_bounds__(256) sanic_generic(Bufs bufs, void* outp) {\n";
-    if (coop) {
+    o << "extern \"C\" __global__ void __launch_bounds__(256) sanic_generic(Bufs bufs, void* outp, int* status) {\n";
+    if (coop && W > 1) {
+        // a block per output point; `lane` numbers its threads across the warps, in chunk order
+        o << "    const long long gid = blockIdx.x;\n";
+        o << "    const int lane = threadIdx.x;\n";
+    } else if (coop) {
         o << "    const long long gid = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;\n";
         o << "    const int lane = threadIdx.x & 31;\n";
     } else {
@@ -282,9 +311,9 @@ int32_t render(sanic_ctx* ctx, const sanic_generic_desc* d, std::string* text) {
         for (int i = 0; i < S; ++i) o << "    float acc" << i << " = " << Gen::lit(d->identity[i]) << ";\n";
         const long long n = (long long)d->stream;
         if (coop) {
-            const long long B = n < 32 ? n : 32;
+            const long long B = n < T ? n : T;
             if (d->interleave) {
-                o << "    for (long long s = lane; s < " << n << "LL; s += 32) {\n";
+                o << "    for (long long s = lane; s < " << n << "LL; s += " << T << ") {\n";
             } else {
                 o << "    const long long s_lo = (lane < " << B << ") ? (lane * " << n << "LL) / " << B << " : 0;\n";
                 o << "    const long long s_hi = (lane < " << B << ") ? ((lane + 1) * " << n << "LL) / " << B << " : 0;\n";
@@ -311,7 +340,7 @@ int32_t render(sanic_ctx* ctx, const sanic_generic_desc* d, std::string* text) {
         o << "    }\n";
         if (coop) {
             // ordered tree over the lanes: the lower lane is the left operand, lanes without a chunk never take part
-            const long long B = d->interleave ? 32 : (n < 32 ? n : 32);
+            const long long B = n < T ? n : T;
             o << "    #pragma unroll\n    for (int off = 1; off < 32; off <<= 1) {\n";
             for (int i = 0; i < S; ++i) o << "        const float pb" << i << " = __shfl_down_sync(0xffffffffu, acc" << i << ", off);\n";
             o << "        const bool take = ((lane & (2 * off - 1)) == 0) && (lane + off < " << B << ");\n";
@@ -322,7 +351,29 @@ int32_t render(sanic_ctx* ctx, const sanic_generic_desc* d, std::string* text) {
             }
             for (int i = 0; i < S; ++i) o << in2b << "if (take) acc" << i << " = ma" << i << ";\n";
             o << "    }\n";
-            o << "    if (lane != 0) return;\n";
+            if (W > 1) {
+                // warp partials meet in shared memory and merge left to right in warp order (the threadgroup-memory
+                // merge rounds of the reference's cooperative fold)
+                o << "    __shared__ float part[" << W << "][" << S << "];\n";
+                o << "    if ((lane & 31) == 0) {";
+                for (int i = 0; i < S; ++i) o << " part[lane >> 5][" << i << "] = acc" << i << ";";
+                o << " }\n    __syncthreads();\n";
+                o << "    if (lane != 0) return;\n";
+                for (int w = 1; w < W; ++w) {
+                    if (32LL * w >= B) break;      // that warp and the ones after it had no chunk
+                    o << "    {\n";
+                    const std::string in3 = "        ";
+                    for (int i = 0; i < S; ++i) o << in3 << "const float pw" << i << " = part[" << w << "][" << i << "];\n";
+                    for (int i = 0; i < S; ++i) {
+                        const std::string v = g.program(d->combine[i], "", in3, nullptr, "acc", "pw", nullptr, nullptr);
+                        o << in3 << "const float mw" << i << " = " << v << ";\n";
+                    }
+                    for (int i = 0; i < S; ++i) o << in3 << "acc" << i << " = mw" << i << ";\n";
+                    o << "    }\n";
+                }
+            } else {
+                o << "    if (lane != 0) return;\n";
+            }
         }
         result = g.program(d->project, "", "    ", nullptr, nullptr, nullptr, "acc", nullptr);
     } else {
@@ -331,6 +382,12 @@ int32_t render(sanic_ctx* ctx, const sanic_generic_desc* d, std::string* text) {
     if (d->epilogue.count > 0) {
         o << "    const float fv = " << result << ";\n";
         result = g.program(d->epilogue, "", "    ", nullptr, nullptr, nullptr, nullptr, "fv");
+    }
+    if (d->store_if.count > 0) {
+        // the in-place form: where(c, x, s) written into s's own buffer stores only where c != 0 and never loads s
+        // (src/emit_metal.rs:1118-1178)
+        const std::string c = g.program(d->store_if, "", "    ", nullptr, nullptr, nullptr, nullptr, nullptr);
+        o << "    if (!(" << c << " != 0.0f)) return;\n";
     }
     switch (d->out_dtype) {
         case SANIC_F32: o << "    ((float*)outp)[gid] = " << result << ";\n"; break;
@@ -374,7 +431,8 @@ struct sanic_generic_kernel {
     CUmodule module = nullptr;
     CUfunction fn = nullptr;
     int64_t points = 0;
-    int lanes = 1;
+    int lanes = 1;          // threads per output point
+    int block = 256;
     int n_buffers = 0;
 };
 
@@ -423,7 +481,8 @@ int32_t sanic_generic_compile(sanic_ctx* ctx, const sanic_generic_desc* d, sanic
     cr = dr.get_function(&k->fn, k->module, "sanic_generic");
     if (cr != CUDA_SUCCESS) { dr.module_unload(k->module); delete k; return sanic_fail(ctx, SANIC_ERR_CUDA, "cuModuleGetFunction failed with code " + std::to_string((int)cr)); }
     k->points = grid_points(d);
-    k->lanes = (d->stream > 0 && d->lanes == 32) ? 32 : 1;
+    k->lanes = (d->stream > 0 && d->lanes == 32) ? 32 * (d->warps > 1 ? d->warps : 1) : 1;
+    k->block = k->lanes > 32 ? k->lanes : 256;      // several warps per point: one block per point
     for (int i = 0; i < d->n_operands; ++i) if (d->operands[i].buffer + 1 > k->n_buffers) k->n_buffers = d->operands[i].buffer + 1;
     *out = k;
     return SANIC_OK;
@@ -440,11 +499,12 @@ int32_t sanic_generic_launch(sanic_ctx* ctx, sanic_generic_kernel* k, const void
         bufs.p[i] = buffers[i];
     }
     const int64_t threads = k->points * k->lanes;
-    const int64_t blocks = (threads + 255) / 256;
+    const int64_t blocks = (threads + k->block - 1) / k->block;
     SANIC_REQUIRE(ctx, blocks <= 0x7FFFFFFFLL, "generic launch: grid too large");
-    void* args[] = {&bufs, &out};
+    int* status = ctx->status_dev;
+    void* args[] = {&bufs, &out, &status};
     sanic_set_device(ctx);
-    CUresult cr = driver().launch(k->fn, (unsigned)blocks, 1, 1, 256, 1, 1, 0, (CUstream)stream, args, nullptr);
+    CUresult cr = driver().launch(k->fn, (unsigned)blocks, 1, 1, (unsigned)k->block, 1, 1, 0, (CUstream)stream, args, nullptr);
     if (cr != CUDA_SUCCESS) return sanic_fail(ctx, SANIC_ERR_CUDA, "cuLaunchKernel failed with code " + std::to_string((int)cr));
     return SANIC_OK;
 }

@@ -107,6 +107,7 @@ int32_t sanic_sync(sanic_ctx* ctx, void* stream) {
     int code = *(volatile int*)ctx->status_host;
     if (code != 0) {
         *ctx->status_host = 0;
+        if (code == 51) return sanic_fail(ctx, SANIC_ERR_INVALID, "a gather index was out of range (code 51)");
         return sanic_fail(ctx, SANIC_ERR_TIMEOUT, "a bounded device-side wait ran out (code " + std::to_string(code) + ")");
     }
     return SANIC_OK;

@@ -8,13 +8,13 @@ module and flattened to the postfix programs of the C ABI. The generated kernel 
 carriers no specialised kernel matches (scalar fold / cooperative fold) and the pointwise kernel for
 elementwise cones (src/emit_metal.rs:626-1178).
 
-Nothing here computes: `describe` only packs a descriptor, `source` and `compiles` render and compile
+Nothing here computes: `Description` only packs a descriptor, `source` and `compiles` render and compile
 without a device, `GenericKernel` compiles, loads and launches through libsanic_b200.so.
 """
 from __future__ import annotations
 
 import ctypes as C
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Sequence
 
 from . import _abi as abi
@@ -52,6 +52,7 @@ class E:
 def const(v) -> E: return E(abi.X_CONST, value=v)
 def load(operand: int) -> E: return E(abi.X_LOAD, arg=operand)
 def coord(axis: int) -> E: return E(abi.X_COORD, arg=axis)
+def gather(operand: int, index) -> E: return E(abi.X_GATHER, arg=operand, kids=(E.of(index),))
 def item(i: int) -> E: return E(abi.X_ITEM, arg=i)
 def A(i: int) -> E: return E(abi.X_A, arg=i)
 def B(i: int) -> E: return E(abi.X_B, arg=i)
@@ -78,6 +79,8 @@ class Operand:
     strides: Sequence[int]
     stream_stride: int = 0
     offset: int = 0
+    gather_stride: int = 0     # for `gather`: elements per step of the gathered index, and the number of valid indices
+    gather_extent: int = 0
 
 
 @dataclass
@@ -135,8 +138,8 @@ class Description:
     """A packed sanic_generic_desc with the ctypes arrays it points into kept alive."""
 
     def __init__(self, grid: Sequence[int], operands: Sequence[Operand], *, carrier: Carrier | None = None, stream: int = 0,
-                 value: E | None = None, epilogue: E | None = None, out_dtype: int = abi.F32, lanes: int = 1,
-                 interleave: bool = False):
+                 value: E | None = None, epilogue: E | None = None, store_if: E | None = None, out_dtype: int = abi.F32,
+                 lanes: int = 1, warps: int = 1, interleave: bool = False):
         if len(grid) > abi.MAX_AXES:
             raise ValueError(f"at most {abi.MAX_AXES} grid axes")
         if (carrier is None) == (value is None):
@@ -155,13 +158,14 @@ class Description:
         for i, g in enumerate(grid):
             d.extent[i] = int(g)
         d.stream = int(stream) if carrier is not None else 0
-        d.lanes, d.interleave = int(lanes), int(bool(interleave))
+        d.lanes, d.warps, d.interleave = int(lanes), int(warps), int(bool(interleave))
         self._operands = (abi.Operand * max(1, len(operands)))()
         for i, o in enumerate(operands):
             if len(o.strides) != len(grid):
                 raise ValueError("an operand needs one stride per grid axis")
             self._operands[i].dtype, self._operands[i].buffer = int(o.dtype), int(o.buffer)
             self._operands[i].offset, self._operands[i].stream_stride = int(o.offset), int(o.stream_stride)
+            self._operands[i].gather_stride, self._operands[i].gather_extent = int(o.gather_stride), int(o.gather_extent)
             for a, s in enumerate(o.strides):
                 self._operands[i].stride[a] = int(s)
         d.n_operands, d.operands = len(operands), self._operands
@@ -179,6 +183,7 @@ class Description:
         else:
             d.project = prog(value)
         d.epilogue = prog(epilogue) if epilogue is not None else abi.Expr(0, 0)
+        d.store_if = prog(store_if) if store_if is not None else abi.Expr(0, 0)
         d.out_dtype = int(out_dtype)
         self._ops = (abi.ExprOp * max(1, len(ops)))(*[abi.ExprOp(o, a, v) for o, a, v in ops])
         d.n_ops, d.ops = len(ops), self._ops

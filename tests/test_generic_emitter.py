@@ -24,7 +24,8 @@ BF16_TOL = 2e-2
 _NAMES = {abi.X_CONST: "const", abi.X_LOAD: "load", abi.X_COORD: "coord", abi.X_ITEM: "item", abi.X_A: "a", abi.X_B: "b",
           abi.X_F: "f", abi.X_RESULT: "result", abi.X_ADD: "add", abi.X_SUB: "sub", abi.X_MUL: "mul", abi.X_DIV: "div",
           abi.X_MAX: "max", abi.X_MIN: "min", abi.X_LT: "lt", abi.X_NEG: "neg", abi.X_RECIP: "recip", abi.X_EXP: "exp",
-          abi.X_LOG: "log", abi.X_SQRT: "sqrt", abi.X_TANH: "tanh", abi.X_SIN: "sin", abi.X_COS: "cos", abi.X_WHERE: "where"}
+          abi.X_LOG: "log", abi.X_SQRT: "sqrt", abi.X_TANH: "tanh", abi.X_SIN: "sin", abi.X_COS: "cos", abi.X_WHERE: "where",
+          abi.X_GATHER: "gather"}
 
 
 def prog(e):
@@ -40,15 +41,20 @@ def prog(e):
     return out
 
 
+def _ops(operands):
+    return [dict(buffer=o.buffer, strides=list(o.strides), stream_stride=o.stream_stride, offset=o.offset,
+                 gather_stride=o.gather_stride, gather_extent=o.gather_extent) for o in operands]
+
+
 def oracle_fold(grid, stream, operands, buffers, carrier, epilogue=None, blocks=1):
-    ops = [dict(buffer=o.buffer, strides=list(o.strides), stream_stride=o.stream_stride, offset=o.offset) for o in operands]
+    ops = _ops(operands)
     return ce.carrier_fold(grid, stream, ops, buffers, [prog(l) for l in carrier.leaves], [prog(e) for e in carrier.into],
                            [prog(e) for e in carrier.combine], list(carrier.identity), prog(carrier.project),
                            prog(epilogue) if epilogue is not None else None, blocks)
 
 
 def oracle_map(grid, operands, buffers, value):
-    ops = [dict(buffer=o.buffer, strides=list(o.strides), stream_stride=o.stream_stride, offset=o.offset) for o in operands]
+    ops = _ops(operands)
     return ce.pointwise(grid, ops, buffers, prog(value))
 
 
@@ -137,6 +143,7 @@ def all_descriptions():
     out["scalar fold"] = em.Description(grid, ops, carrier=car, stream=k, out_dtype=abi.BF16)
     out["cooperative fold"] = em.Description(grid, ops, carrier=car, stream=k, lanes=32)
     out["interleaved fold"] = em.Description(grid, ops, carrier=car, stream=k, lanes=32, interleave=True)
+    out["four warps per point"] = em.Description(grid, ops, carrier=car, stream=k, lanes=32, warps=4)
     grid, n, ops, car = attention_case(6, 40, 1, 8, 0.5, causal=True)
     out["online softmax"] = em.Description(grid, ops, carrier=car, stream=n, lanes=32)
     ops = [em.Operand(0, abi.F32, [1], 0), em.Operand(1, abi.BF16, [1], 0)]
@@ -146,7 +153,23 @@ def all_descriptions():
     out["argmax"] = em.Description((), ops, carrier=em.carrier_first_argmax(em.load(0), em.coord(0)), stream=100, out_dtype=abi.U32)
     ops = [em.Operand(0, abi.I4, [128], 1), em.Operand(1, abi.BF16, [2], 0), em.Operand(2, abi.BF16, [0], 1)]
     out["int4 leaf"] = em.Description((4,), ops, carrier=em.carrier_sum(em.load(0) * em.load(1) * em.load(2)), stream=128)
+    ops = [em.Operand(0, abi.BF16, [0, 1], gather_stride=32, gather_extent=100), em.Operand(1, abi.F32, [1, 0])]
+    out["gather"] = em.Description((4, 32), ops, value=em.gather(0, em.load(1)))
+    ops = [em.Operand(0, abi.F32, [0, 1]), em.Operand(1, abi.F32, [0, 0])]
+    hit = (em.coord(0) < em.load(1) + 1.0) * (em.load(1) < em.coord(0) + 1.0)
+    out["in-place row write"] = em.Description((16, 8), ops, value=em.load(0), store_if=hit, out_dtype=abi.BF16)
     return out
+
+
+def test_oracle_gather_rounds_then_checks_bounds():
+    # src/interp.rs:378-379: the index is round()ed (half away from zero), then bounds-checked
+    table = np.arange(12.0).reshape(4, 3)
+    idx = np.array([0.4, 2.5, 1.49, 3.0])
+    ops = [em.Operand(0, abi.F32, [0, 1], gather_stride=3, gather_extent=4), em.Operand(1, abi.F32, [1, 0])]
+    got = oracle_map((4, 3), ops, [table, idx], em.gather(0, em.load(1)))
+    assert got.tolist() == [[0, 1, 2], [9, 10, 11], [3, 4, 5], [9, 10, 11]]
+    with pytest.raises(IndexError):
+        oracle_map((4, 3), ops, [table, np.array([0.0, 3.5, 0.0, 0.0])], em.gather(0, em.load(1)))
 
 
 def test_every_description_renders():
@@ -245,6 +268,28 @@ def test_generic_online_softmax_fold(dev, lanes, interleave, stream):
     d = em.Description(grid, ops, carrier=car, stream=n, lanes=lanes, interleave=interleave)
     got = run_kernel(dev, d, [on_device(dev, x, abi.F32) for x in (q, k, v)], grid)
     assert nerr(got, want) <= F32_TOL
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("warps,interleave", [(2, False), (8, False), (4, True)])
+@pytest.mark.parametrize("stream", [5, 40, 257, 3000])
+def test_generic_block_level_split(dev, warps, interleave, stream):
+    # the streamed axis split over the threads of a block: lanes, then warps (src/plan.rs:434-488); the answer is the
+    # straight fold's, for the online-softmax carrier and for the first-argmax carrier (bit-exact)
+    L, Ev = 7, 8
+    g = orc.Xorshift(0x5B17)
+    q, k, v = (orc.round_to(orc.DT_F32, x) for x in (g.normal(L, 1), g.normal(stream, 1) * 2.0, g.normal(stream, Ev)))
+    grid, n, ops, car = attention_case(L, stream, 1, Ev, 0.8, causal=True)
+    want = oracle_fold(grid, n, ops, [q, k, v], car)
+    d = em.Description(grid, ops, carrier=car, stream=n, lanes=32, warps=warps, interleave=interleave)
+    got = run_kernel(dev, d, [on_device(dev, x, abi.F32) for x in (q, k, v)], grid)
+    assert nerr(got, want) <= F32_TOL
+    x = np.round(g.normal(3, stream) * 2.0) / 2.0
+    ops = [em.Operand(0, abi.F32, [stream], 1)]
+    car = em.carrier_first_argmax(em.load(0), em.coord(1))
+    d = em.Description((3,), ops, carrier=car, stream=stream, lanes=32, warps=warps, interleave=interleave, out_dtype=abi.U32)
+    got = run_kernel(dev, d, [on_device(dev, x, abi.F32)], (3,), abi.U32)
+    assert got.tolist() == np.argmax(x, axis=1).tolist()
 
 
 @pytest.mark.gpu
@@ -357,6 +402,58 @@ def test_generic_pointwise_cone_and_stores(dev):
     want = oracle_map((n,), ops, [gate], value)
     got = run_kernel(dev, em.Description((n,), ops, value=value), [on_device(dev, gate, abi.F32)], (n,))
     assert nerr(got, want) <= F32_TOL
+
+
+@pytest.mark.gpu
+def test_generic_gather_stage(dev):
+    # the embedding: token ids travel as floats, Gather rounds them (src/interp.rs:378-379, examples/llama3_2.rs:112-121)
+    import torch
+    vocab, hidden, batch = 300, 64, 5
+    g = orc.Xorshift(0xE3B)
+    table = orc.round_to(orc.DT_BF16, g.normal(vocab, hidden))
+    tokens = np.array([0.0, 299.0, 17.4, 17.5, 123.0])          # 17.4 -> 17, 17.5 -> 18
+    ops = [em.Operand(0, abi.BF16, [0, 1], gather_stride=hidden, gather_extent=vocab), em.Operand(1, abi.F32, [1, 0])]
+    value = em.gather(0, em.load(1))
+    want = oracle_map((batch, hidden), ops, [table, tokens], value)
+    assert np.array_equal(want, table[[0, 299, 17, 18, 123]])
+    d = em.Description((batch, hidden), ops, value=value)
+    got = run_kernel(dev, d, [on_device(dev, table, abi.BF16), on_device(dev, tokens, abi.F32)], (batch, hidden))
+    assert np.array_equal(got, want)
+    # an index out of range reads 0 and the next synchronisation reports it; the context stays usable
+    from sanic_b200.backend import RunError
+    bad = on_device(dev, np.array([0.0, 300.0, 1.0, 2.0, 3.0]), abi.F32)
+    out = torch.empty(batch * hidden, device=dev.torch_device)
+    k = em.GenericKernel(dev, d)
+    k([on_device(dev, table, abi.BF16), bad], out)
+    with pytest.raises(RunError):
+        dev.sync()
+    assert float(out.view(batch, hidden)[1].abs().max()) == 0.0
+    k([on_device(dev, table, abi.BF16), on_device(dev, tokens, abi.F32)], out)
+    dev.sync()
+    assert np.array_equal(out.cpu().numpy().reshape(batch, hidden).astype(np.float64), want)
+    k.close()
+
+
+@pytest.mark.gpu
+def test_generic_in_place_row_write(dev):
+    # update_cache = where((idx < pos+1) * (pos < idx+1), current, cache) written into the cache's own buffer: only row
+    # `pos` is stored, the rest of the cache is neither loaded nor written (src/nn.rs:208-212, src/emit_metal.rs:1118-1178)
+    import torch
+    ctx_len, d_head, pos = 40, 16, 23
+    g = orc.Xorshift(0xCAC4E)
+    cache = orc.round_to(orc.DT_BF16, g.normal(ctx_len, d_head))
+    cur = orc.round_to(orc.DT_F32, g.normal(d_head))
+    ops = [em.Operand(0, abi.F32, [0, 1]), em.Operand(1, abi.F32, [0, 0])]
+    hit = (em.coord(0) < em.load(1) + 1.0) * (em.load(1) < em.coord(0) + 1.0)
+    d = em.Description((ctx_len, d_head), ops, value=em.load(0), store_if=hit, out_dtype=abi.BF16)
+    t_cache = on_device(dev, cache, abi.BF16).reshape(-1)
+    k = em.GenericKernel(dev, d)
+    k([on_device(dev, cur, abi.F32), on_device(dev, np.array([float(pos)]), abi.F32)], t_cache)
+    dev.sync()
+    k.close()
+    want = cache.copy()
+    want[pos] = orc.round_to(orc.DT_BF16, cur)
+    assert np.array_equal(t_cache.float().cpu().numpy().reshape(ctx_len, d_head).astype(np.float64), want)
 
 
 @pytest.mark.gpu
