@@ -173,6 +173,22 @@ def suite(dev, torch, hbm_peak, tf_peak, quick, only=None, c2_shape=(4096, 2048,
         med, best = time_events(c1_batch, 10, 3, torch)
         med_call, _ = time_events(lambda: dev.attn_fwd_f32(q, k, v, scale=0.125), 20, 3, torch)
         out["c1_attn_f32_us"] = {"median": med / 20 * 1e6, "min": best / 20 * 1e6, "through_python_wrapper": med_call * 1e6}
+        # the same config through the generic emitter (the fallback for carriers no hand-written kernel matches): one
+        # generated kernel that reads only Q, K, V, as a scalar fold and as a cooperative fold with the value-feature axis
+        # over the lanes and the key axis over 4 warps
+        from sanic_b200 import emitter as em
+        grid, n_keys, operands, carrier = em.attention(1, 1, 1, 256, 1024, 64, 64, 0.125)
+        og = torch.empty(256 * 64, device=td)
+        for label, kw in (("generated_scalar_fold", dict(lanes=1)), ("generated_cooperative_fold", dict(lanes=32, warps=4, lane_axis=True))):
+            kern = em.GenericKernel(dev, em.Description(grid, operands, carrier=carrier, stream=n_keys, **kw))
+            bufs = (C.c_void_p * 3)(q.data_ptr(), k.data_ptr(), v.data_ptr())
+            def gen_batch():
+                for _ in range(20):
+                    dev.lib.sanic_generic_launch(dev.h, kern.h, bufs, 3, C.c_void_p(og.data_ptr()), dev.stream())
+            med_g, _ = time_events(gen_batch, 5, 2, torch)
+            out["c1_attn_f32_us"][label] = med_g / 20 * 1e6
+            out["c1_attn_f32_us"][label + "_max_abs_diff"] = float((og.view(256, 64) - o1.view(256, 64)).abs().max())
+            kern.close()
     # config 2: RMSNorm-fused GEMM, x[4096x2048] g[2048] W[2048x8192] bf16, f32 accumulation, bf16 output
     M, K, N = c2_shape
     x = torch.randn(M, K, generator=g, device=td).to(torch.bfloat16)

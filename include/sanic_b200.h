@@ -247,7 +247,8 @@ int32_t sanic_w4_unpack(sanic_ctx* ctx, const uint8_t* packed, size_t n_elems, f
 #define SANIC_MAX_SLOTS 8
 enum { SANIC_X_CONST = 1,   /* value */
        SANIC_X_LOAD = 2,    /* arg = operand index: a typed, strided read at the current point */
-       SANIC_X_COORD = 3,   /* arg = grid axis, or n_axes for the streamed coordinate; as a float (Iota / Coordinate) */
+       SANIC_X_COORD = 3,   /* arg = grid axis, n_axes for the streamed coordinate, n_axes + 1 for the inner coordinate of a
+                               contracted leaf; as a float (Iota / Coordinate) */
        SANIC_X_ITEM = 4,    /* arg = leaf index (into, and project for stream-invariant leaves is not needed: use LOAD) */
        SANIC_X_A = 5, SANIC_X_B = 6,   /* arg = slot of the left / right accumulator (combine) */
        SANIC_X_F = 7,       /* arg = slot of the final accumulator (project) */
@@ -268,6 +269,7 @@ typedef struct {
     int64_t offset;                     /* elements */
     int64_t stride[SANIC_MAX_AXES];     /* elements per step of each grid axis; 0 broadcasts */
     int64_t stream_stride;              /* elements per step of the streamed axis */
+    int64_t inner_stride;               /* elements per step of a contracted leaf's inner axis */
     int64_t gather_stride;              /* elements per step of the gathered index (SANIC_X_GATHER only) */
     int64_t gather_extent;              /* valid indices are 0 .. gather_extent-1 */
 } sanic_operand;
@@ -279,12 +281,20 @@ typedef struct {
     int32_t warps;                      /* lanes == 32 only: 0 or 1 = one warp per point; 2..8 = a block of that many warps per
                                            point, the chunking below taken over all its threads (B = min(32*warps, n)), warp
                                            partials merged in warp order through shared memory */
+    int32_t lane_axis;                  /* lanes == 32 only. 1: the LAST grid axis is spread over the lanes (FoldSched::lane_axis,
+                                           src/plan.rs:434-455): a warp owns 32 neighbouring points, each lane its own accumulator; a
+                                           contracted leaf that does not read that axis is computed once per warp (inner axis split over
+                                           the lanes, butterfly sum); with warps > 1 the streamed axis is split over the warps instead
+                                           of over the lanes */
     int32_t interleave;                 /* lanes == 32 only. 0: lane b folds the contiguous chunk [b*n/B, (b+1)*n/B), B = min(32, n),
                                            merged in lane order (run_carrier_split, src/interp.rs:597-640): legal for every carrier.
                                            1: lane b folds s = b, b+32, ...: needs a carrier that merges out of order (src/plan.rs:481-488) */
     int32_t n_operands; const sanic_operand* operands;
     int32_t n_ops; const sanic_expr_op* ops;
     int32_t n_leaves; const sanic_expr* leaves;           /* value of leaf i at (point, s): LOAD / COORD / CONST and the basis */
+    const int64_t* leaf_inner;                            /* NULL, or per leaf: an extent R > 1 makes the leaf the sum over r < R of
+                                                             its program (operands step by inner_stride; COORD n_axes+1 reads r):
+                                                             a contraction computed in the fold body (src/codegen.rs:27-36) */
     int32_t n_slots; const double* identity;
     const sanic_expr* into;                               /* per slot, over ITEM */
     const sanic_expr* combine;                            /* per slot, over A and B; all slots read the old accumulator */

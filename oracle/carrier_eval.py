@@ -76,9 +76,11 @@ class _Point:
                 idx = idx + self.coords[a] * int(s)
             self.base.append(idx)
 
-    def env(self, s):
+    def env(self, s, r=None):
         def load(k):
             idx = self.base[k] + (0 if s is None else s * int(self.operands[k]["stream_stride"]))
+            if r is not None:
+                idx = idx + r * int(self.operands[k].get("inner_stride", 0))
             return self.buffers[int(self.operands[k]["buffer"])][idx]
 
         def coord(a):
@@ -86,6 +88,10 @@ class _Point:
                 if s is None:
                     raise ValueError("stream coordinate outside the fold body")
                 return np.full(self.grid, float(s))
+            if a == len(self.grid) + 1:
+                if r is None:
+                    raise ValueError("inner coordinate outside a contracted leaf")
+                return np.full(self.grid, float(r))
             return self.coords[a].astype(np.float64)
         def gather(k, index):
             # index = round() (half away from zero), then a bounds check (src/interp.rs:378-379)
@@ -109,8 +115,10 @@ def pointwise(grid, operands, buffers, value, epilogue=None) -> np.ndarray:
     return r
 
 
-def carrier_fold(grid, stream, operands, buffers, leaves, into, combine, identity, project, epilogue=None, blocks=1) -> np.ndarray:
-    """run_carrier (blocks == 1) / run_carrier_split (blocks > 1) of one carrier over every grid point."""
+def carrier_fold(grid, stream, operands, buffers, leaves, into, combine, identity, project, epilogue=None, blocks=1,
+                 leaf_inner=()) -> np.ndarray:
+    """run_carrier (blocks == 1) / run_carrier_split (blocks > 1) of one carrier over every grid point. leaf_inner[l] = R > 1
+    makes leaf l a Reduce(Add) over an inner axis: a left fold from 0.0 in index order (src/interp.rs:355-363)."""
     pt = _Point(grid, operands, buffers)
     n, nb = int(stream), int(blocks)
     if not (1 <= nb <= n):
@@ -124,7 +132,17 @@ def carrier_fold(grid, stream, operands, buffers, leaves, into, combine, identit
         acc = [np.full(pt.grid, float(v)) for v in identity]
         for s in range(lo, hi):
             env = pt.env(s)
-            env["item"] = [np.broadcast_to(_run(l, env), pt.grid) for l in leaves]
+            items = []
+            for li, l in enumerate(leaves):
+                R = int(leaf_inner[li]) if li < len(leaf_inner) else 0
+                if R > 1:
+                    tot = np.zeros(pt.grid)
+                    for r in range(R):
+                        tot = tot + np.broadcast_to(_run(l, pt.env(s, r)), pt.grid)
+                    items.append(tot)
+                else:
+                    items.append(np.broadcast_to(_run(l, env), pt.grid))
+            env["item"] = items
             el = [np.broadcast_to(_run(e, env), pt.grid).astype(np.float64) for e in into]
             acc = merge(acc, el)
         return acc

@@ -100,6 +100,7 @@ struct Gen {
     std::ostringstream out;
     int fresh = 0;
     std::string err;
+    std::string inner;      // name of the inner contraction variable while a contracted leaf is rendered, else empty
 
     std::string tmp() { return "t" + std::to_string(fresh++); }
 
@@ -120,6 +121,7 @@ struct Gen {
         for (int ax = 0; ax < d->n_axes; ++ax)
             if (o.stride[ax] != 0) a << " + c" << ax << " * " << (long long)o.stride[ax] << "LL";
         if (!s.empty() && o.stream_stride != 0) a << " + " << s << " * " << (long long)o.stream_stride << "LL";
+        if (!inner.empty() && o.inner_stride != 0) a << " + " << inner << " * " << (long long)o.inner_stride << "LL";
         a << ")";
         return a.str();
     }
@@ -188,6 +190,9 @@ struct Gen {
                     if (op.arg == d->n_axes) {
                         if (s.empty()) { err = "generic emitter: stream coordinate read outside the fold body"; st.push_back("0.0f"); }
                         else st.push_back("(float)" + s);
+                    } else if (op.arg == d->n_axes + 1) {
+                        if (inner.empty()) { err = "generic emitter: inner coordinate read outside a contracted leaf"; st.push_back("0.0f"); }
+                        else st.push_back("(float)" + inner);
                     } else if (op.arg >= 0 && op.arg < d->n_axes) st.push_back("(float)c" + std::to_string(op.arg));
                     else { err = "generic emitter: coordinate axis out of range"; st.push_back("0.0f"); }
                     break;
@@ -269,10 +274,129 @@ int32_t validate(sanic_ctx* ctx, const sanic_generic_desc* d) {
         SANIC_REQUIRE(ctx, d->n_slots >= 1 && d->n_slots <= SANIC_MAX_SLOTS && d->identity && d->into && d->combine, "generic emitter: 1..8 slots with identity, into and combine");
         SANIC_REQUIRE(ctx, d->n_leaves >= 0 && d->n_leaves <= 16 && (d->n_leaves == 0 || d->leaves), "generic emitter: 0..16 leaves");
         SANIC_REQUIRE(ctx, d->lanes == 1 || d->lanes == 32, "generic emitter: lanes is 1 (one thread per point) or 32 (a warp per point)");
+        SANIC_REQUIRE(ctx, !d->lane_axis || (d->lanes == 32 && d->n_axes >= 1 && !d->interleave),
+                      "generic emitter: a lane-distributed output axis needs lanes = 32, a grid axis, and no interleave");
         SANIC_REQUIRE(ctx, d->warps >= 0 && d->warps <= 8 && (d->warps <= 1 || d->lanes == 32),
                       "generic emitter: 1..8 warps per point, more than one only with lanes = 32");
     }
     return SANIC_OK;
+}
+
+// Does a program read the given grid axis (through a coordinate or through an operand that steps along it)?
+bool reads_axis(const sanic_generic_desc* d, const sanic_expr& e, int axis) {
+    for (int i = e.first; i < e.first + e.count && i < d->n_ops; ++i) {
+        const sanic_expr_op& op = d->ops[i];
+        if (op.op == SANIC_X_COORD && op.arg == axis) return true;
+        if ((op.op == SANIC_X_LOAD || op.op == SANIC_X_GATHER) && op.arg >= 0 && op.arg < d->n_operands &&
+            d->operands[op.arg].stride[axis] != 0) return true;
+    }
+    return false;
+}
+
+// The tail every schedule shares: epilogue, conditional store, narrowed store at `index`.
+void render_store(Gen& g, const sanic_generic_desc* d, std::string result, const std::string& index) {
+    std::ostringstream& o = g.out;
+    if (d->epilogue.count > 0) {
+        o << "    const float fv = " << result << ";\n";
+        result = g.program(d->epilogue, "", "    ", nullptr, nullptr, nullptr, nullptr, "fv");
+    }
+    if (d->store_if.count > 0) {
+        // the in-place form: where(c, x, s) written into s's own buffer stores only where c != 0 and never loads s
+        // (src/emit_metal.rs:1118-1178)
+        const std::string c = g.program(d->store_if, "", "    ", nullptr, nullptr, nullptr, nullptr, nullptr);
+        o << "    if (!(" << c << " != 0.0f)) return;\n";
+    }
+    switch (d->out_dtype) {
+        case SANIC_F32: o << "    ((float*)outp)[" << index << "] = " << result << ";\n"; break;
+        case SANIC_BF16: o << "    ((unsigned short*)outp)[" << index << "] = narrow_bf16(" << result << ");\n"; break;
+        default: o << "    ((unsigned*)outp)[" << index << "] = store_u32(" << result << ");\n"; break;
+    }
+    o << "}\n";
+}
+
+// Cooperative fold with a lane-distributed output axis (FoldSched::lane_axis, src/plan.rs:434-455): the last grid axis
+// is spread over the 32 lanes of a warp, so a warp owns 32 neighbouring output points that share everything not
+// spanning that axis. Each lane carries its own accumulator; a contracted leaf that does not read the lane axis (the
+// score of an attention fold) is computed ONCE per warp, its inner axis split over the lanes and summed with a
+// butterfly, instead of once per output point. With several warps the streamed axis is split over them in contiguous
+// chunks and the warp partials merge in warp order through shared memory.
+void render_lane_axis(Gen& g, const sanic_generic_desc* d) {
+    std::ostringstream& o = g.out;
+    const int S = d->n_slots, last = d->n_axes - 1;
+    const int W = d->warps > 1 ? d->warps : 1;
+    const long long ext = (long long)d->extent[last], passes = (ext + 31) / 32, n = (long long)d->stream;
+    long long outer = 1;
+    for (int a = 0; a < last; ++a) outer *= d->extent[a];
+    const long long units = outer * passes;       // one warp (or one block of W warps) per 32 points of the lane axis
+    o << PRELUDE;
+    o << "extern \"C\" __global__ void __launch_bounds__(256) sanic_generic(Bufs bufs, void* outp, int* status) {\n";
+    o << "    const int lane = threadIdx.x & 31;\n";
+    if (W > 1) o << "    const int warp = threadIdx.x >> 5;\n    const long long unit = blockIdx.x;\n";
+    else o << "    const long long unit = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;\n";
+    o << "    if (unit >= " << units << "LL) return;\n";
+    o << "    long long rem = unit / " << passes << "LL;\n";
+    o << "    const long long cl = (unit % " << passes << "LL) * 32 + lane;\n";
+    o << "    const bool active = cl < " << ext << "LL;\n";
+    o << "    const long long c" << last << " = active ? cl : " << (ext - 1) << "LL;   // idle lanes shadow the last point and never store\n";
+    o << "    const long long outer = rem;\n";
+    for (int a = last - 1; a >= 0; --a)
+        o << "    const long long c" << a << " = rem % " << (long long)d->extent[a] << "LL; rem /= " << (long long)d->extent[a] << "LL;\n";
+    o << "    (void)rem;\n";
+    for (int i = 0; i < S; ++i) o << "    float acc" << i << " = " << Gen::lit(d->identity[i]) << ";\n";
+    const long long B = n < W ? n : W;            // chunks of the streamed axis, one per warp
+    if (W > 1) {
+        o << "    const long long s_lo = (warp < " << B << ") ? (warp * " << n << "LL) / " << B << " : 0;\n";
+        o << "    const long long s_hi = (warp < " << B << ") ? ((warp + 1) * " << n << "LL) / " << B << " : 0;\n";
+        o << "    for (long long s = s_lo; s < s_hi; ++s) {\n";
+    } else {
+        o << "    for (long long s = 0; s < " << n << "LL; ++s) {\n";
+    }
+    const std::string in2 = "        ";
+    for (int l = 0; l < d->n_leaves; ++l) {
+        const long long R = d->leaf_inner ? (long long)d->leaf_inner[l] : 0;
+        if (R > 1) {
+            const bool shared = !reads_axis(d, d->leaves[l], last);
+            o << in2 << "float x" << l << " = 0.0f;\n";
+            if (shared) o << in2 << "for (long long r" << l << " = lane; r" << l << " < " << R << "LL; r" << l << " += 32) {\n";
+            else o << in2 << "for (long long r" << l << " = 0; r" << l << " < " << R << "LL; ++r" << l << ") {\n";
+            g.inner = "r" + std::to_string(l);
+            const std::string v = g.program(d->leaves[l], "s", in2 + "    ", nullptr, nullptr, nullptr, nullptr, nullptr);
+            g.inner.clear();
+            o << in2 << "    x" << l << " += " << v << ";\n" << in2 << "}\n";
+            if (shared) o << in2 << "for (int off = 16; off > 0; off >>= 1) x" << l << " += __shfl_xor_sync(0xffffffffu, x" << l << ", off);\n";
+        } else {
+            const std::string v = g.program(d->leaves[l], "s", in2, nullptr, nullptr, nullptr, nullptr, nullptr);
+            o << in2 << "const float x" << l << " = " << v << ";\n";
+        }
+    }
+    for (int i = 0; i < S; ++i) {
+        const std::string v = g.program(d->into[i], "s", in2, "x", nullptr, nullptr, nullptr, nullptr);
+        o << in2 << "const float el" << i << " = " << v << ";\n";
+    }
+    for (int i = 0; i < S; ++i) {
+        const std::string v = g.program(d->combine[i], "s", in2, nullptr, "acc", "el", nullptr, nullptr);
+        o << in2 << "const float na" << i << " = " << v << ";\n";
+    }
+    for (int i = 0; i < S; ++i) o << in2 << "acc" << i << " = na" << i << ";\n";
+    o << "    }\n";
+    if (W > 1) {
+        o << "    __shared__ float part[" << W << "][" << S << "][32];\n";
+        for (int i = 0; i < S; ++i) o << "    part[warp][" << i << "][lane] = acc" << i << ";\n";
+        o << "    __syncthreads();\n    if (warp != 0) return;\n";
+        for (int w = 1; w < W && w < B; ++w) {
+            o << "    {\n";
+            for (int i = 0; i < S; ++i) o << in2 << "const float pw" << i << " = part[" << w << "][" << i << "][lane];\n";
+            for (int i = 0; i < S; ++i) {
+                const std::string v = g.program(d->combine[i], "", in2, nullptr, "acc", "pw", nullptr, nullptr);
+                o << in2 << "const float mw" << i << " = " << v << ";\n";
+            }
+            for (int i = 0; i < S; ++i) o << in2 << "acc" << i << " = mw" << i << ";\n";
+            o << "    }\n";
+        }
+    }
+    o << "    if (!active) return;\n";
+    const std::string result = g.program(d->project, "", "    ", nullptr, nullptr, nullptr, "acc", nullptr);
+    render_store(g, d, result, "outer * " + std::to_string(ext) + "LL + cl");
 }
 
 // The whole kernel as CUDA C text.
@@ -281,6 +405,12 @@ int32_t render(sanic_ctx* ctx, const sanic_generic_desc* d, std::string* text) {
     if (rc != SANIC_OK) return rc;
     Gen g{d};
     std::ostringstream& o = g.out;
+    if (d->stream > 0 && d->lanes == 32 && d->lane_axis) {
+        render_lane_axis(g, d);
+        if (!g.err.empty()) return sanic_fail(ctx, SANIC_ERR_INVALID, g.err);
+        *text = o.str();
+        return SANIC_OK;
+    }
     const int64_t points = grid_points(d);
     const bool fold = d->stream > 0;
     const bool coop = fold && d->lanes == 32;
@@ -324,8 +454,21 @@ int32_t render(sanic_ctx* ctx, const sanic_generic_desc* d, std::string* text) {
         }
         const std::string in2 = "        ";
         for (int l = 0; l < d->n_leaves; ++l) {
-            const std::string v = g.program(d->leaves[l], "s", in2, nullptr, nullptr, nullptr, nullptr, nullptr);
-            o << in2 << "const float x" << l << " = " << v << ";\n";
+            const long long R = d->leaf_inner ? (long long)d->leaf_inner[l] : 0;
+            if (R > 1) {
+                // a leaf that is itself a contraction: sum over the inner axis in the fold body (the in-body QK^T of
+                // the online-softmax fold, src/codegen.rs:27-36,328-351), a left fold from 0 in index order
+                o << in2 << "float x" << l << " = 0.0f;\n";
+                o << in2 << "for (long long r" << l << " = 0; r" << l << " < " << R << "LL; ++r" << l << ") {\n";
+                g.inner = "r" + std::to_string(l);
+                const std::string v = g.program(d->leaves[l], "s", in2 + "    ", nullptr, nullptr, nullptr, nullptr, nullptr);
+                g.inner.clear();
+                o << in2 << "    x" << l << " += " << v << ";\n";
+                o << in2 << "}\n";
+            } else {
+                const std::string v = g.program(d->leaves[l], "s", in2, nullptr, nullptr, nullptr, nullptr, nullptr);
+                o << in2 << "const float x" << l << " = " << v << ";\n";
+            }
         }
         for (int i = 0; i < S; ++i) {
             const std::string v = g.program(d->into[i], "s", in2, "x", nullptr, nullptr, nullptr, nullptr);
@@ -379,22 +522,7 @@ int32_t render(sanic_ctx* ctx, const sanic_generic_desc* d, std::string* text) {
     } else {
         result = g.program(d->project, "", "    ", nullptr, nullptr, nullptr, nullptr, nullptr);
     }
-    if (d->epilogue.count > 0) {
-        o << "    const float fv = " << result << ";\n";
-        result = g.program(d->epilogue, "", "    ", nullptr, nullptr, nullptr, nullptr, "fv");
-    }
-    if (d->store_if.count > 0) {
-        // the in-place form: where(c, x, s) written into s's own buffer stores only where c != 0 and never loads s
-        // (src/emit_metal.rs:1118-1178)
-        const std::string c = g.program(d->store_if, "", "    ", nullptr, nullptr, nullptr, nullptr, nullptr);
-        o << "    if (!(" << c << " != 0.0f)) return;\n";
-    }
-    switch (d->out_dtype) {
-        case SANIC_F32: o << "    ((float*)outp)[gid] = " << result << ";\n"; break;
-        case SANIC_BF16: o << "    ((unsigned short*)outp)[gid] = narrow_bf16(" << result << ");\n"; break;
-        default: o << "    ((unsigned*)outp)[gid] = store_u32(" << result << ");\n"; break;
-    }
-    o << "}\n";
+    render_store(g, d, result, "gid");
     if (!g.err.empty()) return sanic_fail(ctx, SANIC_ERR_INVALID, g.err);
     *text = o.str();
     return SANIC_OK;
@@ -430,8 +558,8 @@ int32_t compile_cubin(sanic_ctx* ctx, const std::string& text, std::vector<char>
 struct sanic_generic_kernel {
     CUmodule module = nullptr;
     CUfunction fn = nullptr;
-    int64_t points = 0;
-    int lanes = 1;          // threads per output point
+    int64_t points = 0;     // launch units
+    int lanes = 1;          // threads per launch unit
     int block = 256;
     int n_buffers = 0;
 };
@@ -481,6 +609,10 @@ int32_t sanic_generic_compile(sanic_ctx* ctx, const sanic_generic_desc* d, sanic
     cr = dr.get_function(&k->fn, k->module, "sanic_generic");
     if (cr != CUDA_SUCCESS) { dr.module_unload(k->module); delete k; return sanic_fail(ctx, SANIC_ERR_CUDA, "cuModuleGetFunction failed with code " + std::to_string((int)cr)); }
     k->points = grid_points(d);
+    if (d->stream > 0 && d->lanes == 32 && d->lane_axis) {      // a unit = 32 points of the last axis
+        const int64_t ext = d->extent[d->n_axes - 1];
+        k->points = k->points / ext * ((ext + 31) / 32);
+    }
     k->lanes = (d->stream > 0 && d->lanes == 32) ? 32 * (d->warps > 1 ? d->warps : 1) : 1;
     k->block = k->lanes > 32 ? k->lanes : 256;      // several warps per point: one block per point
     for (int i = 0; i < d->n_operands; ++i) if (d->operands[i].buffer + 1 > k->n_buffers) k->n_buffers = d->operands[i].buffer + 1;

@@ -79,6 +79,7 @@ class Operand:
     strides: Sequence[int]
     stream_stride: int = 0
     offset: int = 0
+    inner_stride: int = 0      # for a contracted leaf: elements per step of its inner axis
     gather_stride: int = 0     # for `gather`: elements per step of the gathered index, and the number of valid indices
     gather_extent: int = 0
 
@@ -91,6 +92,7 @@ class Carrier:
     combine: Sequence[E]
     identity: Sequence[float]
     project: E
+    leaf_inner: Sequence[int] = ()     # per leaf: an extent R > 1 makes the leaf the sum over r < R of its expression
 
 
 # ── the carriers the reference's laws pin (tests/laws.rs:107-126,620-646; tests/compile.rs:139-171) ──
@@ -107,12 +109,15 @@ def _shift(side, m):
     return where(const(float("-inf")) < side, exp(side - m), 0.0)
 
 
-def carrier_online_softmax(score: E, value: E) -> Carrier:
-    """(m, l, o): Plain(Max), ExpShifted{0}, ExpShifted{0}; project o / l."""
+def carrier_online_softmax(score: E, value: E, contraction: int = 0, post: "callable | None" = None) -> Carrier:
+    """(m, l, o): Plain(Max), ExpShifted{0}, ExpShifted{0}; project o / l. With `contraction` = E > 1 the score leaf is
+    the sum of `score` over an inner axis of that extent, computed in the fold body; `post` maps the contracted leaf to
+    the score that is lifted (scale, additive mask)."""
     m = maximum(A(0), B(0))
-    return Carrier([score, value], [item(0), const(1.0), item(1)],
+    s = item(0) if post is None else post(item(0))
+    return Carrier([score, value], [s, const(1.0), item(1)],
                    [m, A(1) * _shift(A(0), m) + B(1) * _shift(B(0), m), A(2) * _shift(A(0), m) + B(2) * _shift(B(0), m)],
-                   [float("-inf"), 0.0, 0.0], F(2) / F(1))
+                   [float("-inf"), 0.0, 0.0], F(2) / F(1), leaf_inner=(contraction, 0) if contraction > 1 else ())
 
 
 def carrier_logsumexp(leaf: E) -> Carrier:
@@ -134,12 +139,31 @@ def carrier_first_argmax(leaf: E, index: E) -> Carrier:
     return Carrier([leaf, index], [item(0), item(1)], [key, idx], [float("-inf"), float("inf")], F(1))
 
 
+def attention(batch, q_heads, kv_heads, q_len, kv_len, head_dim, v_dim, scale, dtype=abi.F32, causal=False):
+    """softmax(Q K^T * scale [+ causal mask]) V as ONE fused stage that reads only Q, K and V (the shape the reference's
+    partitioner pins, src/partition.rs:2491-2513): grid (batch, kv head, repeat, query, value feature), stream = key, the
+    QK^T contraction over head_dim computed in the fold body. Grouped-query attention is the reindex-expand of the kv
+    heads: the repeat axis has stride 0 in K and V (src/nn.rs:107-151). The computed mask is where(i < j, -1e30, 0)
+    (src/ir.rs:1511-1526). Returns (grid, stream, operands, carrier); buffers are Q [B,Hq,L,E], K [B,Hkv,S,E], V [B,Hkv,S,Ev]."""
+    rep = q_heads // kv_heads
+    L, S, E, Ev = q_len, kv_len, head_dim, v_dim
+    q = Operand(0, dtype, [q_heads * L * E, rep * L * E, L * E, E, 0], 0, inner_stride=1)
+    k = Operand(1, dtype, [kv_heads * S * E, S * E, 0, 0, 0], E, inner_stride=1)
+    v = Operand(2, dtype, [kv_heads * S * Ev, S * Ev, 0, 0, 1], Ev)
+
+    def post(x):
+        x = x * scale
+        return x + where(coord(3) < coord(5), -1e30, 0.0) if causal else x
+    car = carrier_online_softmax(load(0) * load(1), load(2), contraction=E, post=post)
+    return (batch, kv_heads, rep, L, Ev), S, [q, k, v], car
+
+
 class Description:
     """A packed sanic_generic_desc with the ctypes arrays it points into kept alive."""
 
     def __init__(self, grid: Sequence[int], operands: Sequence[Operand], *, carrier: Carrier | None = None, stream: int = 0,
                  value: E | None = None, epilogue: E | None = None, store_if: E | None = None, out_dtype: int = abi.F32,
-                 lanes: int = 1, warps: int = 1, interleave: bool = False):
+                 lanes: int = 1, warps: int = 1, interleave: bool = False, lane_axis: bool = False):
         if len(grid) > abi.MAX_AXES:
             raise ValueError(f"at most {abi.MAX_AXES} grid axes")
         if (carrier is None) == (value is None):
@@ -159,6 +183,7 @@ class Description:
             d.extent[i] = int(g)
         d.stream = int(stream) if carrier is not None else 0
         d.lanes, d.warps, d.interleave = int(lanes), int(warps), int(bool(interleave))
+        d.lane_axis = int(bool(lane_axis))
         self._operands = (abi.Operand * max(1, len(operands)))()
         for i, o in enumerate(operands):
             if len(o.strides) != len(grid):
@@ -166,6 +191,7 @@ class Description:
             self._operands[i].dtype, self._operands[i].buffer = int(o.dtype), int(o.buffer)
             self._operands[i].offset, self._operands[i].stream_stride = int(o.offset), int(o.stream_stride)
             self._operands[i].gather_stride, self._operands[i].gather_extent = int(o.gather_stride), int(o.gather_extent)
+            self._operands[i].inner_stride = int(o.inner_stride)
             for a, s in enumerate(o.strides):
                 self._operands[i].stride[a] = int(s)
         d.n_operands, d.operands = len(operands), self._operands
@@ -178,6 +204,11 @@ class Description:
             self._combine = (abi.Expr * n)(*[prog(e) for e in carrier.combine])
             self._identity = (C.c_double * n)(*[float(v) for v in carrier.identity])
             d.n_leaves, d.leaves, d.n_slots = len(carrier.leaves), self._leaves, n
+            if carrier.leaf_inner:
+                if len(carrier.leaf_inner) != len(carrier.leaves):
+                    raise ValueError("leaf_inner needs one extent per leaf")
+                self._inner = (abi.i64 * len(carrier.leaves))(*[int(r) for r in carrier.leaf_inner])
+                d.leaf_inner = self._inner
             d.identity, d.into, d.combine = self._identity, self._into, self._combine
             d.project = prog(carrier.project)
         else:

@@ -43,14 +43,14 @@ def prog(e):
 
 def _ops(operands):
     return [dict(buffer=o.buffer, strides=list(o.strides), stream_stride=o.stream_stride, offset=o.offset,
-                 gather_stride=o.gather_stride, gather_extent=o.gather_extent) for o in operands]
+                 inner_stride=o.inner_stride, gather_stride=o.gather_stride, gather_extent=o.gather_extent) for o in operands]
 
 
 def oracle_fold(grid, stream, operands, buffers, carrier, epilogue=None, blocks=1):
     ops = _ops(operands)
     return ce.carrier_fold(grid, stream, ops, buffers, [prog(l) for l in carrier.leaves], [prog(e) for e in carrier.into],
                            [prog(e) for e in carrier.combine], list(carrier.identity), prog(carrier.project),
-                           prog(epilogue) if epilogue is not None else None, blocks)
+                           prog(epilogue) if epilogue is not None else None, blocks, list(carrier.leaf_inner))
 
 
 def oracle_map(grid, operands, buffers, value):
@@ -73,6 +73,10 @@ def attention_case(L, S, E, Ev, scale, dtype=abi.F32, causal=False):
     if causal:   # where(i < j, -1e30, 0) added to the score (src/ir.rs:1511-1526)
         score = score + em.where(em.coord(0) < em.coord(2), -1e30, 0.0)
     return (L, Ev), S, operands, em.carrier_online_softmax(score, em.load(2))
+
+
+def full_attention_case(B, Hq, Hkv, L, S, E, Ev, scale, dtype=abi.F32, causal=False):
+    return em.attention(B, Hq, Hkv, L, S, E, Ev, scale, dtype, causal)
 
 
 # ───────────────────────── CPU: oracle pins ─────────────────────────
@@ -124,6 +128,20 @@ def test_oracle_split_law_and_cpp_oracle_agree():
     assert np.allclose(oracle_fold(grid, n, ops, [q, k, v], car), orc.sdpa(q, k, v, scale=0.7, is_causal=True), rtol=0, atol=1e-13)
 
 
+def test_oracle_fused_attention_reads_only_qkv():
+    # tests/oracle.rs:90-151 shapes (2,3,5,7,4,6) seed 0xA11CE, and the GQA 4/2 known answer of tests/nn.rs:108-137
+    g = orc.Xorshift(0xA11CE)
+    B, H, L, S, E, Ev = 2, 3, 5, 7, 4, 6
+    q, k, v = g.normal(B, H, L, E), g.normal(B, H, S, E), g.normal(B, H, S, Ev)
+    for causal in (False, True):
+        grid, n, ops, car = full_attention_case(B, H, H, L, S, E, Ev, 0.5, causal=causal)
+        got = oracle_fold(grid, n, ops, [q, k, v], car, blocks=3).reshape(B, H, L, Ev)
+        assert np.allclose(got, orc.sdpa(q, k, v, scale=0.5, is_causal=causal), rtol=0, atol=1e-13)
+    q = np.ones((1, 4, 1, 1)); k = np.ones((1, 2, 1, 1)); v = np.array([10.0, 20.0]).reshape(1, 2, 1, 1)
+    grid, n, ops, car = full_attention_case(1, 4, 2, 1, 1, 1, 1, 1.0)
+    assert oracle_fold(grid, n, ops, [q, k, v], car).ravel().tolist() == [10.0, 10.0, 20.0, 20.0]
+
+
 def test_oracle_overflow_magnitude_carriers_stay_finite():
     # tests/laws.rs:444-505: scores centred far outside exp's range fold to the same answer as centred ones
     g = orc.Xorshift(0x0F10)
@@ -143,6 +161,10 @@ def all_descriptions():
     out["scalar fold"] = em.Description(grid, ops, carrier=car, stream=k, out_dtype=abi.BF16)
     out["cooperative fold"] = em.Description(grid, ops, carrier=car, stream=k, lanes=32)
     out["interleaved fold"] = em.Description(grid, ops, carrier=car, stream=k, lanes=32, interleave=True)
+    g5, n5, o5, c5 = full_attention_case(2, 4, 2, 8, 24, 16, 8, 0.25, abi.BF16, causal=True)
+    out["fused attention"] = em.Description(g5, o5, carrier=c5, stream=n5, lanes=32, out_dtype=abi.BF16)
+    out["lane-distributed output axis"] = em.Description(g5, o5, carrier=c5, stream=n5, lanes=32, lane_axis=True)
+    out["lane axis, stream over 4 warps"] = em.Description(g5, o5, carrier=c5, stream=n5, lanes=32, warps=4, lane_axis=True)
     out["four warps per point"] = em.Description(grid, ops, carrier=car, stream=k, lanes=32, warps=4)
     grid, n, ops, car = attention_case(6, 40, 1, 8, 0.5, causal=True)
     out["online softmax"] = em.Description(grid, ops, carrier=car, stream=n, lanes=32)
@@ -178,7 +200,9 @@ def test_every_description_renders():
         assert 'extern "C" __global__' in text and "sanic_generic" in text, name
         if d.desc.stream > 0:
             assert "for (long long s" in text, name
-        if d.desc.lanes == 32:
+        if d.desc.lanes == 32 and d.desc.lane_axis:
+            assert "__shfl_xor_sync" in text and "const bool active" in text, name    # the shared score, summed over lanes
+        elif d.desc.lanes == 32:
             assert "__shfl_down_sync" in text, name
         else:
             assert "__shfl" not in text.split("sanic_generic(")[1], name
@@ -290,6 +314,59 @@ def test_generic_block_level_split(dev, warps, interleave, stream):
     d = em.Description((3,), ops, carrier=car, stream=stream, lanes=32, warps=warps, interleave=interleave, out_dtype=abi.U32)
     got = run_kernel(dev, d, [on_device(dev, x, abi.F32)], (3,), abi.U32)
     assert got.tolist() == np.argmax(x, axis=1).tolist()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("lanes,warps", [(1, 1), (32, 1), (32, 4)])
+def test_generic_fused_attention_reads_only_qkv(dev, causal, lanes, warps):
+    # one generated kernel for softmax(QK^T * scale + mask) V with grouped-query heads, against the C++ oracle
+    B, Hq, Hkv, L, S, E, Ev = 2, 4, 2, 9, 70, 16, 8
+    g = orc.Xorshift(0xF1A5)
+    q, k, v = (orc.round_to(orc.DT_F32, t) for t in (g.normal(B, Hq, L, E), g.normal(B, Hkv, S, E), g.normal(B, Hkv, S, Ev)))
+    grid, n, ops, car = full_attention_case(B, Hq, Hkv, L, S, E, Ev, 0.25, causal=causal)
+    want = orc.sdpa(q, k, v, scale=0.25, is_causal=causal, enable_gqa=True)
+    d = em.Description(grid, ops, carrier=car, stream=n, lanes=lanes, warps=warps)
+    got = run_kernel(dev, d, [on_device(dev, t, abi.F32) for t in (q, k, v)], grid).reshape(B, Hq, L, Ev)
+    assert nerr(got, want) <= F32_TOL
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("warps", [1, 3, 8])
+@pytest.mark.parametrize("Ev,S", [(8, 70), (40, 5), (64, 200)])
+def test_generic_lane_distributed_output_axis(dev, warps, Ev, S):
+    # the value-feature axis over the lanes: the score is computed once per warp, each lane owns o[e]
+    B, Hq, Hkv, L, E = 1, 4, 2, 6, 48
+    g = orc.Xorshift(0x1A2E)
+    q, k, v = (orc.round_to(orc.DT_F32, t) for t in (g.normal(B, Hq, L, E), g.normal(B, Hkv, S, E), g.normal(B, Hkv, S, Ev)))
+    grid, n, ops, car = full_attention_case(B, Hq, Hkv, L, S, E, Ev, 0.2, causal=True)
+    want = orc.sdpa(q, k, v, scale=0.2, is_causal=True, enable_gqa=True)
+    d = em.Description(grid, ops, carrier=car, stream=n, lanes=32, warps=warps, lane_axis=True)
+    got = run_kernel(dev, d, [on_device(dev, t, abi.F32) for t in (q, k, v)], grid).reshape(B, Hq, L, Ev)
+    assert nerr(got, want) <= F32_TOL
+    # a carrier without a contracted leaf on the same schedule: row-wise matmul, the output column over the lanes
+    m, kk = 5, 90
+    a, b = (orc.round_to(orc.DT_F32, t) for t in (g.normal(m, kk), g.normal(kk, Ev)))
+    grid, stream, ops, car = matmul_case(m, kk, Ev)
+    d = em.Description(grid, ops, carrier=car, stream=stream, lanes=32, warps=warps, lane_axis=True)
+    got = run_kernel(dev, d, [on_device(dev, a, abi.F32), on_device(dev, b, abi.F32)], grid)
+    assert nerr(got, oracle_fold(grid, stream, ops, [a, b], car)) <= F32_TOL
+
+
+@pytest.mark.gpu
+def test_generic_attention_at_the_first_config_matches_the_specialised_kernel(dev):
+    # Q[256, 64], K, V[1024, 64] f32, scale 1/8, no mask: the generated kernel, the hand-written f32 fold and the oracle
+    import torch
+    g = orc.Xorshift(0xC1)
+    q, k, v = (orc.round_to(orc.DT_F32, t) for t in (g.normal(1, 1, 256, 64), g.normal(1, 1, 1024, 64), g.normal(1, 1, 1024, 64)))
+    grid, n, ops, car = full_attention_case(1, 1, 1, 256, 1024, 64, 64, 0.125)
+    want = orc.sdpa(q, k, v, scale=0.125)
+    tq, tk, tv = (on_device(dev, t, abi.F32) for t in (q, k, v))
+    for kw in (dict(interleave=True), dict(lane_axis=True, warps=4)):
+        got = run_kernel(dev, em.Description(grid, ops, carrier=car, stream=n, lanes=32, **kw), [tq, tk, tv], grid)
+        assert nerr(got.reshape(1, 1, 256, 64), want) <= F32_TOL
+    hand = dev.attn_fwd_f32(tq, tk, tv, scale=0.125).cpu().numpy().astype(np.float64)
+    assert nerr(hand, want) <= F32_TOL
 
 
 @pytest.mark.gpu
