@@ -175,11 +175,11 @@ def suite(dev, torch, hbm_peak, tf_peak, quick, only=None, c2_shape=(4096, 2048,
         out["c1_attn_f32_us"] = {"median": med / 20 * 1e6, "min": best / 20 * 1e6, "through_python_wrapper": med_call * 1e6}
         # the same config through the generic emitter (the fallback for carriers no hand-written kernel matches): one
         # generated kernel that reads only Q, K, V, as a scalar fold and as a cooperative fold with the value-feature axis
-        # over the lanes and the key axis over 4 warps
+        # over the lanes and the key axis over 8 warps
         from sanic_b200 import emitter as em
         grid, n_keys, operands, carrier = em.attention(1, 1, 1, 256, 1024, 64, 64, 0.125)
         og = torch.empty(256 * 64, device=td)
-        for label, kw in (("generated_scalar_fold", dict(lanes=1)), ("generated_cooperative_fold", dict(lanes=32, warps=4, lane_axis=True))):
+        for label, kw in (("generated_scalar_fold", dict(lanes=1)), ("generated_cooperative_fold", dict(lanes=32, warps=8, lane_axis=True))):
             kern = em.GenericKernel(dev, em.Description(grid, operands, carrier=carrier, stream=n_keys, **kw))
             bufs = (C.c_void_p * 3)(q.data_ptr(), k.data_ptr(), v.data_ptr())
             def gen_batch():

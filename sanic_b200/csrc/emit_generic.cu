@@ -347,9 +347,9 @@ void render_lane_axis(Gen& g, const sanic_generic_desc* d) {
     if (W > 1) {
         o << "    const long long s_lo = (warp < " << B << ") ? (warp * " << n << "LL) / " << B << " : 0;\n";
         o << "    const long long s_hi = (warp < " << B << ") ? ((warp + 1) * " << n << "LL) / " << B << " : 0;\n";
-        o << "    for (long long s = s_lo; s < s_hi; ++s) {\n";
+        o << "    #pragma unroll 4\n    for (long long s = s_lo; s < s_hi; ++s) {\n";
     } else {
-        o << "    for (long long s = 0; s < " << n << "LL; ++s) {\n";
+        o << "    #pragma unroll 4\n    for (long long s = 0; s < " << n << "LL; ++s) {\n";
     }
     const std::string in2 = "        ";
     for (int l = 0; l < d->n_leaves; ++l) {
@@ -443,14 +443,14 @@ int32_t render(sanic_ctx* ctx, const sanic_generic_desc* d, std::string* text) {
         if (coop) {
             const long long B = n < T ? n : T;
             if (d->interleave) {
-                o << "    for (long long s = lane; s < " << n << "LL; s += " << T << ") {\n";
+                o << "    #pragma unroll 4\n    for (long long s = lane; s < " << n << "LL; s += " << T << ") {\n";
             } else {
                 o << "    const long long s_lo = (lane < " << B << ") ? (lane * " << n << "LL) / " << B << " : 0;\n";
                 o << "    const long long s_hi = (lane < " << B << ") ? ((lane + 1) * " << n << "LL) / " << B << " : 0;\n";
-                o << "    for (long long s = s_lo; s < s_hi; ++s) {\n";
+                o << "    #pragma unroll 4\n    for (long long s = s_lo; s < s_hi; ++s) {\n";
             }
         } else {
-            o << "    for (long long s = 0; s < " << n << "LL; ++s) {\n";
+            o << "    #pragma unroll 4\n    for (long long s = 0; s < " << n << "LL; ++s) {\n";
         }
         const std::string in2 = "        ";
         for (int l = 0; l < d->n_leaves; ++l) {
