@@ -24,6 +24,7 @@
 // Roofline: tensor-bound. FLOPs = 2*M*N*K; HBM bytes = x + W + y (about 117 MB at
 // 4096x2048x8192, 61 us at 2.25 PFLOP/s).
 #include <cuda.h>
+#include <cstdio>
 
 #include "common.cuh"
 
@@ -37,6 +38,7 @@ constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int MAX_K = 8192;
 constexpr int NTHREADS = 512;
 constexpr uint32_t SPIN_LIMIT = 1u << 24;
+constexpr uint32_t P_SPIN_LIMIT = 1u << 22;   // the pair kernel: waits that cross CTAs, kept short
 constexpr int TM_A = BN;                      // tensor-memory columns: [0, BN) accumulator, then STAGES x 32 columns of A
 
 struct Shared {
@@ -333,6 +335,319 @@ gemm_rmsnorm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     }
 }
 
+// ───────────────────────── the same contraction on a pair of SMs ─────────────────────────
+// Two CTAs of a cluster share one 256x256 output tile: CTA r holds rows [128r, 128r+128) of A (transformed into its own
+// tensor memory as above) and columns [128r, 128r+128) of B in its shared memory, and ONE thread of the leader CTA
+// issues tcgen05.mma.cta_group::2 (M = 256): each SM multiplies its half of A with the whole of B, reading the other
+// half of B from its peer. Per k-block a CTA now brings 32 KB through L2 -> shared memory instead of 48 KB for the same
+// tensor work, which is what bounds the one-CTA tile. Six 32 KB stages.
+// Synchronisation across the pair: the transform warps of both CTAs arrive on the LEADER's ready barrier (relaxed
+// cluster-scope arrivals: a release fence on that path costs about 0.9 us each); the leader's commits arrive on the stage-empty and accumulator-full barriers of BOTH CTAs (one commit per
+// destination); the epilogue warps of both CTAs arrive on the leader's accumulator-empty barrier.
+constexpr int P_STAGES = 6;
+constexpr int PB_BYTES = (BN / 2) * BK * 2;            // 16 KB: this CTA's half of the B tile
+constexpr int P_STAGE_BYTES = A_BYTES + PB_BYTES;      // 32 KB
+constexpr int P_NTHREADS = 640;                        // warps 0-3 single-thread roles, 4-11 A transform, 12-19 epilogue
+
+struct PShared {
+    uint64_t full[P_STAGES], ready[P_STAGES], empty[P_STAGES];
+    uint64_t tmem_full, tmem_empty, ss_full[2], ss_empty[2];
+    uint32_t tmem_base;
+    volatile int abort_flag;
+    float ss[2][2][BM];
+};
+
+__device__ __forceinline__ uint32_t cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// the shared::cluster address of the same shared-memory location in CTA `rank` of this cluster
+__device__ __forceinline__ uint32_t map_to_rank(uint32_t addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// The same without the release fence, for a thread that only passes on an event it has itself acquired (the facts it
+// forwards are completed tensor-core reads or tcgen05.st / TMA writes that their issuers already waited for).
+__device__ __forceinline__ void mbar_arrive_cluster_relaxed(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Bounded wait. CLUSTER: acquire at cluster scope, for barriers whose arrivals may come from the peer CTA (it costs more
+// than the CTA-scope form, so only the roles that need it use it).
+template <bool CLUSTER>
+__device__ __forceinline__ bool mbar_wait_p(uint64_t* bar, uint32_t parity, PShared* sh, int* err, int code) {
+    uint32_t addr = smem_u32(bar);
+    for (uint32_t it = 0; it < P_SPIN_LIMIT; ++it) {
+        uint32_t done;
+        if (CLUSTER)
+            asm volatile("{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                         : "=r"(done) : "r"(addr), "r"(parity) : "memory");
+        else
+            asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                         : "=r"(done) : "r"(addr), "r"(parity) : "memory");
+        if (done) return true;
+        if ((it & 1023u) == 1023u && sh->abort_flag) return false;
+    }
+    sh->abort_flag = 1;
+    atomicCAS(err, 0, code);
+    return false;
+}
+__device__ __forceinline__ void umma2_f16_ts(uint32_t tmem_d, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::2.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+                 ::"r"(tmem_d), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// arrives on ONE barrier, given by its shared::cluster address (this CTA's or the peer's), when the pair's MMAs so far retire
+__device__ __forceinline__ void umma2_commit(uint32_t cluster_addr) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_addr) : "memory");
+}
+
+__global__ void __launch_bounds__(P_NTHREADS, 1)
+gemm_rmsnorm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                         const uint16_t* __restrict__ gamma, void* __restrict__ y, int M, int N, int K, int w_is_nk,
+                         float eps, int out_dtype, int* err, int dbg, unsigned long long* trace) {
+    extern __shared__ unsigned char smem_dyn[];
+    const uint32_t raw = smem_u32(smem_dyn);
+    const uint32_t base = (raw + 1023u) & ~1023u;
+    unsigned char* aligned = smem_dyn + (base - raw);
+    uint16_t* gsm = (uint16_t*)(aligned + P_STAGES * P_STAGE_BYTES);
+    PShared* sh = (PShared*)(aligned + P_STAGES * P_STAGE_BYTES + MAX_K * 2);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_rank();                  // 0 = the leader, which issues every MMA
+#define PTRACE(role, kb) do { if (trace && blockIdx.x < 2 && (kb) < 64) { unsigned long long _t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(_t)); trace[(role) * 64 + (kb)] = _t; } } while (0)
+    const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+    const int kblocks = (K + BK - 1) / BK;
+    const int m_tiles = (M + 2 * BM - 1) / (2 * BM), n_tiles = (N + BN - 1) / BN;
+    const int tiles = m_tiles * n_tiles;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < P_STAGES; ++s) { mbar_init(&sh->full[s], 1); mbar_init(&sh->ready[s], 16); mbar_init(&sh->empty[s], 1); }
+        mbar_init(&sh->tmem_full, 1); mbar_init(&sh->tmem_empty, 16);
+        for (int a = 0; a < 2; ++a) { mbar_init(&sh->ss_full[a], 8); mbar_init(&sh->ss_empty[a], 8); }
+        sh->abort_flag = 0;
+        sh->tmem_base = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    for (int i = threadIdx.x; i < kblocks * BK; i += P_NTHREADS) gsm[i] = (i < K) ? gamma[i] : (uint16_t)0;
+    __syncthreads();
+    if (warp == 2) {
+        // one warp of EACH CTA of the pair allocates (all 512 columns, so both get base 0)
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sh->tmem_base)), "r"(512));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;");
+    }
+    tc_fence_before();
+    cluster_sync_all();
+    tc_fence_after();
+    const uint32_t tmem = sh->tmem_base;
+
+    if (warp == 0) {
+        // ── TMA producer: this CTA's 128 rows of A and its 128 columns of B ──
+        if (lane == 0) {
+            int stage = 0; uint32_t phase = 1;
+            bool ok = true;
+            for (int t = pair; t < tiles && ok; t += n_pairs) {
+                const int m0 = (t % m_tiles) * (2 * BM) + (int)rank * BM, n0 = (t / m_tiles) * BN + (int)rank * (BN / 2);
+                for (int kb = 0; kb < kblocks; ++kb) {
+                    ok = mbar_wait_p<true>(&sh->empty[stage], phase, sh, err, 21);
+                    if (!ok) break;
+                    if (t < pair + 2 * n_pairs && kblocks == 32) PTRACE(0 + rank, kb + 32 * (t != pair));
+                    const uint32_t sa = base + stage * P_STAGE_BYTES, sb = sa + A_BYTES;
+                    mbar_expect_tx(&sh->full[stage], P_STAGE_BYTES);
+                    tma_load_2d(sa, &map_a, &sh->full[stage], kb * BK, m0);
+                    if (w_is_nk) {
+                        tma_load_2d(sb, &map_b, &sh->full[stage], kb * BK, n0);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < BN / 128; ++j)
+                            tma_load_2d(sb + j * (64 * BK * 2), &map_b, &sh->full[stage], n0 + 64 * j, kb * BK);
+                    }
+                    if (++stage == P_STAGES) { stage = 0; phase ^= 1; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ── MMA issuer: the leader CTA only ──
+        if (lane == 0 && rank == 0) {
+            const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((w_is_nk ? 0u : 1u) << 16) |
+                                   ((uint32_t)(BN >> 3) << 17) | ((uint32_t)((2 * BM) >> 4) << 24);
+            int stage = 0; uint32_t phase = 0;
+            int use = 0;
+            bool ok = true;
+            for (int t = pair; t < tiles && ok; t += n_pairs, ++use) {
+                ok = mbar_wait_p<true>(&sh->tmem_empty, (use & 1) ^ 1, sh, err, 22);    // both epilogues have read the previous tile
+                if (!ok) break;
+                tc_fence_after();
+                for (int kb = 0; kb < kblocks; ++kb) {
+                    ok = mbar_wait_p<true>(&sh->ready[stage], phase, sh, err, 23);      // both CTAs' A halves are in tensor memory, both B halves landed
+                    if (!ok) break;
+                    if (t < pair + 2 * n_pairs && kblocks == 32) PTRACE(5, kb + 32 * (t != pair));
+                    tc_fence_after();
+                    const uint32_t sb = base + stage * P_STAGE_BYTES + A_BYTES;
+                    const uint32_t a_tmem = tmem + TM_A + stage * (BK / 2);
+                    const uint64_t bdesc = w_is_nk ? make_desc(sb, 16, 1024) : make_desc(sb, 64 * BK * 2, 1024);
+#pragma unroll
+                    for (int k = 0; k < BK / 16; ++k) {
+                        const uint64_t bd = bdesc + (uint64_t)(w_is_nk ? k * 2 : k * 128);
+                        if (!(dbg & 1)) umma2_f16_ts(tmem, a_tmem + 8 * k, bd, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                    }
+                    // one commit per stage, to the leader's own barrier; warp 3 relays it to the peer
+                    umma2_commit(map_to_rank(smem_u32(&sh->empty[stage]), 0));
+                    if (++stage == P_STAGES) { stage = 0; phase ^= 1; }
+                }
+                if (ok) {
+                    const uint32_t f = smem_u32(&sh->tmem_full);
+                    umma2_commit(map_to_rank(f, 0));
+                    umma2_commit(map_to_rank(f, 1));
+                }
+            }
+        }
+    } else if (warp == 3) {
+        // ── leader only: relay "stage free" to the peer's producer (a second commit per stage would cost the issuer more) ──
+        if (lane == 0 && rank == 0) {
+            int stage = 0; uint32_t phase = 0;
+            bool ok = true;
+            for (int t = pair; t < tiles && ok; t += n_pairs) {
+                for (int kb = 0; kb < kblocks; ++kb) {
+                    ok = mbar_wait_p<true>(&sh->empty[stage], phase, sh, err, 29);
+                    if (!ok) break;
+                    if (t < pair + 2 * n_pairs && kblocks == 32) PTRACE(6, kb + 32 * (t != pair));
+                    mbar_arrive_cluster_relaxed(map_to_rank(smem_u32(&sh->empty[stage]), 1));
+                    if (++stage == P_STAGES) { stage = 0; phase ^= 1; }
+                }
+            }
+        }
+    } else if (warp >= 4 && warp < 12) {
+        // ── A transform (both CTAs): shared memory -> x*g -> this CTA's tensor memory, sum x^2 ──
+        const int idx = threadIdx.x - 128;
+        const int row = idx & (BM - 1), half = idx >> 7;
+        const uint32_t a_lane = tmem + ((uint32_t)(row & ~31) << 16) + TM_A + half * (BK / 4);
+        int stage = 0; uint32_t phase = 0;
+        int use = 0;
+        bool ok = true;
+        for (int t = pair; t < tiles && ok; t += n_pairs, ++use) {
+            const int a = use & 1;
+            float ss = 0.0f;
+            for (int kb = 0; kb < kblocks; ++kb) {
+                ok = mbar_wait_p<false>(&sh->full[stage], phase, sh, err, 24);
+                if (!ok) break;
+                if (t < pair + 2 * n_pairs && kblocks == 32 && idx == 0) PTRACE(2 + rank, kb + 32 * (t != pair));
+                const unsigned char* arow = aligned + stage * P_STAGE_BYTES + row * 128;
+                uint32_t av[16];
+#pragma unroll
+                for (int c4 = 0; c4 < 4; ++c4) {
+                    const int c = half * 4 + c4;
+                    const uint4 v = *(const uint4*)(arow + ((c ^ (row & 7)) << 4));
+                    const uint4 gv = *(const uint4*)(gsm + kb * BK + c * 8);
+                    uint32_t xs[4] = {v.x, v.y, v.z, v.w};
+                    const uint32_t gs[4] = {gv.x, gv.y, gv.z, gv.w};
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        float x0 = bf16lo(xs[j]), x1 = bf16hi(xs[j]);
+                        ss = fmaf(x0, x0, ss); ss = fmaf(x1, x1, ss);
+                        asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(xs[j]) : "r"(xs[j]), "r"(gs[j]));
+                    }
+                    av[4 * c4] = xs[0]; av[4 * c4 + 1] = xs[1]; av[4 * c4 + 2] = xs[2]; av[4 * c4 + 3] = xs[3];
+                }
+                if (!(dbg & 2)) tmem_st16(a_lane + stage * (BK / 2), av);
+                tc_fence_before();
+                __syncwarp();
+                // having seen this CTA's `full`, the arrival also says that this CTA's half of B has landed. The peer's
+                // warps arrive on the leader's barrier directly: no release fence is needed (the tcgen05.st above has
+                // been waited for, the TMA bytes were observed through `full`) and with one it cost about 0.9 us per arrival
+                if (lane == 0) mbar_arrive_cluster_relaxed(map_to_rank(smem_u32(&sh->ready[stage]), 0));
+                if (++stage == P_STAGES) { stage = 0; phase ^= 1; }
+            }
+            if (!ok) break;
+            ok = mbar_wait_p<false>(&sh->ss_empty[a], ((use >> 1) & 1) ^ 1, sh, err, 25);
+            if (!ok) break;
+            sh->ss[a][half][row] = ss;
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&sh->ss_full[a]);
+        }
+    } else if (warp >= 12) {
+        // ── epilogue (both CTAs): this CTA's 128 rows of the 256 x 256 tile; two warps per lane quarter, 128 columns each ──
+        const int q = warp & 3;
+        const int row = q * 32 + lane;
+        const int c_begin = ((warp - 12) >> 2) * (BN / 64);
+        const bool wide_ok = (N % 16 == 0) && (((uintptr_t)y & 31) == 0);     // 32-byte stores need 32-byte aligned rows
+        int use = 0;
+        bool ok = true;
+        const float inv_k = 1.0f / (float)K;
+        for (int t = pair; t < tiles && ok; t += n_pairs, ++use) {
+            const int a = use & 1;
+            const int m0 = (t % m_tiles) * (2 * BM) + (int)rank * BM, n0 = (t / m_tiles) * BN;
+            ok = mbar_wait_p<false>(&sh->ss_full[a], (use >> 1) & 1, sh, err, 26);
+            if (!ok) break;
+            const float ssv = sh->ss[a][0][row] + sh->ss[a][1][row];
+            const float rstd = 1.0f / sqrtf(ssv * inv_k + eps);
+            ok = mbar_wait_p<true>(&sh->tmem_full, use & 1, sh, err, 27);
+            if (!ok) break;
+            if (use < 4 && warp == 12 && lane == 0 && rank == 0) PTRACE(4, use);
+            tc_fence_after();
+            const int gr = m0 + row;
+#pragma unroll 1
+            for (int c = c_begin; c < c_begin + BN / 64; ++c) {
+                uint32_t r[32];
+                if (!(dbg & 8)) tmem_ld32(tmem + ((uint32_t)(q * 32) << 16) + c * 32, r);
+                else { for (int j = 0; j < 32; ++j) r[j] = j; }
+                const int gc = n0 + c * 32;
+                if (gr < M && gc < N && !(dbg & 4)) {
+                    if (out_dtype == SANIC_BF16) {
+                        uint32_t pk[16];
+#pragma unroll
+                        for (int j = 0; j < 16; ++j)
+                            pk[j] = pack_bf16x2(__uint_as_float(r[2 * j]) * rstd, __uint_as_float(r[2 * j + 1]) * rstd);
+                        uint16_t* dst = (uint16_t*)y + (size_t)gr * N + gc;
+                        if (gc + 32 <= N && wide_ok) {
+#pragma unroll
+                            for (int j = 0; j < 2; ++j)      // 32-byte stores: every lane writes whole sectors
+                                asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(dst + 16 * j), "r"(pk[8 * j]),
+                                             "r"(pk[8 * j + 1]), "r"(pk[8 * j + 2]), "r"(pk[8 * j + 3]), "r"(pk[8 * j + 4]),
+                                             "r"(pk[8 * j + 5]), "r"(pk[8 * j + 6]), "r"(pk[8 * j + 7]) : "memory");
+                        } else if (gc + 32 <= N) {
+#pragma unroll
+                            for (int j = 0; j < 4; ++j)
+                                *(uint4*)(dst + 8 * j) = make_uint4(pk[4 * j], pk[4 * j + 1], pk[4 * j + 2], pk[4 * j + 3]);
+                        } else {
+                            for (int j = 0; j < 32 && gc + j < N; ++j)
+                                dst[j] = (uint16_t)((j & 1) ? (pk[j >> 1] >> 16) : (pk[j >> 1] & 0xFFFF));
+                        }
+                    } else {
+                        float* dst = (float*)y + (size_t)gr * N + gc;
+                        if (gc + 32 <= N) {
+#pragma unroll
+                            for (int j = 0; j < 8; ++j)
+                                *(float4*)(dst + 4 * j) = make_float4(__uint_as_float(r[4 * j]) * rstd, __uint_as_float(r[4 * j + 1]) * rstd,
+                                                                      __uint_as_float(r[4 * j + 2]) * rstd, __uint_as_float(r[4 * j + 3]) * rstd);
+                        } else {
+                            for (int j = 0; j < 32 && gc + j < N; ++j) dst[j] = __uint_as_float(r[j]) * rstd;
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) { mbar_arrive_cluster_relaxed(map_to_rank(smem_u32(&sh->tmem_empty), 0)); mbar_arrive(&sh->ss_empty[a]); }
+            if (use < 4 && warp == 12 && lane == 0 && rank == 0) PTRACE(4, 8 + use);
+        }
+    }
+    // teardown: neither CTA may leave (or free tensor memory) while the other can still reach into it
+    tc_fence_before();
+    cluster_sync_all();
+    if (warp == 2) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512));
+    }
+}
+
 typedef CUresult (*encode_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                               const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                               CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -377,6 +692,36 @@ extern "C" int32_t sanic_gemm_rmsnorm(sanic_ctx* ctx, const sanic_gemm_rmsnorm_p
     if (rc != SANIC_OK) return rc;
 
     cudaStream_t st = (cudaStream_t)stream;
+    static const bool use_pair = (getenv("SANIC_GEMM_PAIR") != nullptr && getenv("SANIC_GEMM_PAIR")[0] == '1');
+    if (use_pair) {
+        // the 256 x 256 tile on a pair of SMs: B's map has a 128-row box (this CTA's half)
+        if (p->w_is_nk) {
+            rc = encode_2d(ctx, &map_b, p->w, (uint64_t)p->K, (uint64_t)p->N, BK, BN / 2);
+            if (rc != SANIC_OK) return rc;
+        }
+        const int psmem = P_STAGES * P_STAGE_BYTES + MAX_K * 2 + (int)sizeof(PShared) + 1024;
+        SANIC_CUDA_CHECK(ctx, cudaFuncSetAttribute(gemm_rmsnorm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, psmem));
+        const int ptiles = ((p->M + 2 * BM - 1) / (2 * BM)) * ((p->N + BN - 1) / BN);
+        cudaLaunchConfig_t cfg = {};
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+        cfg.blockDim = dim3(P_NTHREADS); cfg.dynamicSmemBytes = psmem; cfg.stream = st; cfg.attrs = attr; cfg.numAttrs = 1;
+        cfg.gridDim = dim3(2 * (ctx->sm_count / 2));
+        int max_clusters = 0;
+        SANIC_CUDA_CHECK(ctx, cudaOccupancyMaxActiveClusters(&max_clusters, gemm_rmsnorm_pair_kernel, &cfg));
+        SANIC_REQUIRE(ctx, max_clusters >= 1, "gemm_rmsnorm: no SM pair can hold the kernel");
+        int pairs = ptiles < max_clusters ? ptiles : max_clusters;
+        if (pairs > ctx->sm_count / 2) pairs = ctx->sm_count / 2;
+        cfg.gridDim = dim3(2 * pairs);
+        if (getenv("SANIC_DEBUG_PAIR")) fprintf(stderr, "pair gemm: max_clusters %d pairs %d tiles %d smem %d\n", max_clusters, pairs, ptiles, psmem);
+        cudaError_t le = cudaLaunchKernelEx(&cfg, gemm_rmsnorm_pair_kernel, map_a, map_b, (const uint16_t*)p->gamma, p->y, (int)p->M,
+                                            (int)p->N, (int)p->K, (int)p->w_is_nk, p->eps, (int)p->out_dtype, ctx->status_dev,
+                                            getenv("SANIC_PAIR_DBG") ? atoi(getenv("SANIC_PAIR_DBG")) : 0,
+                                            (unsigned long long*)(getenv("SANIC_PAIR_TRACE") ? (void*)strtoull(getenv("SANIC_PAIR_TRACE"), nullptr, 0) : nullptr));
+        if (le != cudaSuccess) return sanic_fail(ctx, SANIC_ERR_CUDA, std::string("gemm_rmsnorm (pair): ") + cudaGetErrorString(le));
+        return SANIC_OK;
+    }
     const int smem = STAGES * STAGE_BYTES + MAX_K * 2 + (int)sizeof(Shared) + 1024;
     SANIC_CUDA_CHECK(ctx, cudaFuncSetAttribute(gemm_rmsnorm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     const int tiles = ((p->M + BM - 1) / BM) * ((p->N + BN - 1) / BN);
