@@ -340,21 +340,25 @@ gemm_rmsnorm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 // tensor memory as above) and columns [128r, 128r+128) of B in its shared memory, and ONE thread of the leader CTA
 // issues tcgen05.mma.cta_group::2 (M = 256): each SM multiplies its half of A with the whole of B, reading the other
 // half of B from its peer. Per k-block a CTA now brings 32 KB through L2 -> shared memory instead of 48 KB for the same
-// tensor work, which is what bounds the one-CTA tile. Six 32 KB stages.
+// tensor work, which is what bounds the one-CTA tile. Two rings: 4 A tiles (a slot is free as soon as the transform has
+// read it) and 8 B half-tiles, matched by 8 transformed-A slots in tensor memory (512 columns in all).
 // Synchronisation across the pair: the transform warps of both CTAs arrive on the LEADER's ready barrier (relaxed
 // cluster-scope arrivals: a release fence on that path costs about 0.9 us each); the leader's commits arrive on the stage-empty and accumulator-full barriers of BOTH CTAs (one commit per
 // destination); the epilogue warps of both CTAs arrive on the leader's accumulator-empty barrier.
-constexpr int P_STAGES = 6;
+constexpr int PA_SLOTS = 4;                            // A tiles in shared memory: free again as soon as the transform has read them
+constexpr int PB_SLOTS = 8;                            // B half-tiles in shared memory, and transformed A tiles in tensor memory
 constexpr int PB_BYTES = (BN / 2) * BK * 2;            // 16 KB: this CTA's half of the B tile
-constexpr int P_STAGE_BYTES = A_BYTES + PB_BYTES;      // 32 KB
-constexpr int P_NTHREADS = 640;                        // warps 0-3 single-thread roles, 4-11 A transform, 12-19 epilogue
+constexpr int P_RING_BYTES = PA_SLOTS * A_BYTES + PB_SLOTS * PB_BYTES;    // 192 KB
+constexpr int P_OUT_BYTES = 8 * 2048;                  // store staging: one 32 x 32 bf16 block per epilogue warp
+constexpr int P_NTHREADS = 896;                        // warps 0-3 single-thread roles, 4-19 A transform (two groups), 20-27 epilogue
 
 struct PShared {
-    uint64_t full[P_STAGES], ready[P_STAGES], empty[P_STAGES];
+    uint64_t full_a[PA_SLOTS], empty_a[PA_SLOTS];
+    uint64_t full_b[PB_SLOTS], ready[PB_SLOTS], empty[PB_SLOTS];
     uint64_t tmem_full, tmem_empty, ss_full[2], ss_empty[2];
     uint32_t tmem_base;
     volatile int abort_flag;
-    float ss[2][2][BM];
+    float ss[2][4][BM];   // [accumulator use parity][transform group * 2 + row half][row]
 };
 
 __device__ __forceinline__ uint32_t cluster_rank() {
@@ -411,14 +415,18 @@ __device__ __forceinline__ void umma2_commit(uint32_t cluster_addr) {
 
 __global__ void __launch_bounds__(P_NTHREADS, 1)
 gemm_rmsnorm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                         const uint16_t* __restrict__ gamma, void* __restrict__ y, int M, int N, int K, int w_is_nk,
-                         float eps, int out_dtype, int* err, int dbg, unsigned long long* trace) {
+                         const __grid_constant__ CUtensorMap map_y, const uint16_t* __restrict__ gamma, void* __restrict__ y,
+                         int M, int N, int K, int w_is_nk, float eps, int out_dtype, int* err, int dbg,
+                         unsigned long long* trace, int gamma_bytes, int bulk_store) {
     extern __shared__ unsigned char smem_dyn[];
     const uint32_t raw = smem_u32(smem_dyn);
     const uint32_t base = (raw + 1023u) & ~1023u;
     unsigned char* aligned = smem_dyn + (base - raw);
-    uint16_t* gsm = (uint16_t*)(aligned + P_STAGES * P_STAGE_BYTES);
-    PShared* sh = (PShared*)(aligned + P_STAGES * P_STAGE_BYTES + MAX_K * 2);
+    uint16_t* gsm = (uint16_t*)(aligned + P_RING_BYTES);
+    const uint32_t b_ring = base + PA_SLOTS * A_BYTES;
+    // after gamma: 8 x 2 KB of store staging (one 32 x 32 bf16 block per epilogue warp) when bulk_store, then the barriers
+    const uint32_t stage_out = base + P_RING_BYTES + gamma_bytes;
+    PShared* sh = (PShared*)(aligned + P_RING_BYTES + gamma_bytes + (bulk_store ? P_OUT_BYTES : 0));
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_rank();                  // 0 = the leader, which issues every MMA
@@ -429,16 +437,17 @@ gemm_rmsnorm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
     const int tiles = m_tiles * n_tiles;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < P_STAGES; ++s) { mbar_init(&sh->full[s], 1); mbar_init(&sh->ready[s], 16); mbar_init(&sh->empty[s], 1); }
+        for (int s = 0; s < PA_SLOTS; ++s) { mbar_init(&sh->full_a[s], 1); mbar_init(&sh->empty_a[s], 8); }
+        for (int s = 0; s < PB_SLOTS; ++s) { mbar_init(&sh->full_b[s], 1); mbar_init(&sh->ready[s], 16); mbar_init(&sh->empty[s], 1); }
         mbar_init(&sh->tmem_full, 1); mbar_init(&sh->tmem_empty, 16);
-        for (int a = 0; a < 2; ++a) { mbar_init(&sh->ss_full[a], 8); mbar_init(&sh->ss_empty[a], 8); }
+        for (int a = 0; a < 2; ++a) { mbar_init(&sh->ss_full[a], 16); mbar_init(&sh->ss_empty[a], 8); }
         sh->abort_flag = 0;
         sh->tmem_base = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     for (int i = threadIdx.x; i < kblocks * BK; i += P_NTHREADS) gsm[i] = (i < K) ? gamma[i] : (uint16_t)0;
     __syncthreads();
-    if (warp == 2) {
+    if (warp == 3) {
         // one warp of EACH CTA of the pair allocates (all 512 columns, so both get base 0)
         asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sh->tmem_base)), "r"(512));
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;");
@@ -449,27 +458,42 @@ gemm_rmsnorm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
     const uint32_t tmem = sh->tmem_base;
 
     if (warp == 0) {
-        // ── TMA producer: this CTA's 128 rows of A and its 128 columns of B ──
+        // ── TMA producer for A: this CTA's 128 rows; a slot is free again once the 8 transform warps have read it ──
         if (lane == 0) {
             int stage = 0; uint32_t phase = 1;
             bool ok = true;
             for (int t = pair; t < tiles && ok; t += n_pairs) {
-                const int m0 = (t % m_tiles) * (2 * BM) + (int)rank * BM, n0 = (t / m_tiles) * BN + (int)rank * (BN / 2);
+                const int m0 = (t % m_tiles) * (2 * BM) + (int)rank * BM;
+                for (int kb = 0; kb < kblocks; ++kb) {
+                    ok = mbar_wait_p<false>(&sh->empty_a[stage], phase, sh, err, 20);
+                    if (!ok) break;
+                    if (t < pair + 2 * n_pairs && kblocks == 32) PTRACE(0 + rank, kb + 32 * (t != pair));
+                    mbar_expect_tx(&sh->full_a[stage], A_BYTES);
+                    tma_load_2d(base + stage * A_BYTES, &map_a, &sh->full_a[stage], kb * BK, m0);
+                    if (++stage == PA_SLOTS) { stage = 0; phase ^= 1; }
+                }
+            }
+        }
+    } else if (warp == 2) {
+        // ── TMA producer for B: this CTA's 128 columns; a slot is free again once the pair's MMAs on it retire ──
+        if (lane == 0) {
+            int stage = 0; uint32_t phase = 1;
+            bool ok = true;
+            for (int t = pair; t < tiles && ok; t += n_pairs) {
+                const int n0 = (t / m_tiles) * BN + (int)rank * (BN / 2);
                 for (int kb = 0; kb < kblocks; ++kb) {
                     ok = mbar_wait_p<true>(&sh->empty[stage], phase, sh, err, 21);
                     if (!ok) break;
-                    if (t < pair + 2 * n_pairs && kblocks == 32) PTRACE(0 + rank, kb + 32 * (t != pair));
-                    const uint32_t sa = base + stage * P_STAGE_BYTES, sb = sa + A_BYTES;
-                    mbar_expect_tx(&sh->full[stage], P_STAGE_BYTES);
-                    tma_load_2d(sa, &map_a, &sh->full[stage], kb * BK, m0);
+                    const uint32_t sb = b_ring + stage * PB_BYTES;
+                    mbar_expect_tx(&sh->full_b[stage], PB_BYTES);
                     if (w_is_nk) {
-                        tma_load_2d(sb, &map_b, &sh->full[stage], kb * BK, n0);
+                        tma_load_2d(sb, &map_b, &sh->full_b[stage], kb * BK, n0);
                     } else {
 #pragma unroll
                         for (int j = 0; j < BN / 128; ++j)
-                            tma_load_2d(sb + j * (64 * BK * 2), &map_b, &sh->full[stage], n0 + 64 * j, kb * BK);
+                            tma_load_2d(sb + j * (64 * BK * 2), &map_b, &sh->full_b[stage], n0 + 64 * j, kb * BK);
                     }
-                    if (++stage == P_STAGES) { stage = 0; phase ^= 1; }
+                    if (++stage == PB_SLOTS) { stage = 0; phase ^= 1; }
                 }
             }
         }
@@ -490,7 +514,7 @@ gemm_rmsnorm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                     if (!ok) break;
                     if (t < pair + 2 * n_pairs && kblocks == 32) PTRACE(5, kb + 32 * (t != pair));
                     tc_fence_after();
-                    const uint32_t sb = base + stage * P_STAGE_BYTES + A_BYTES;
+                    const uint32_t sb = b_ring + stage * PB_BYTES;
                     const uint32_t a_tmem = tmem + TM_A + stage * (BK / 2);
                     const uint64_t bdesc = w_is_nk ? make_desc(sb, 16, 1024) : make_desc(sb, 64 * BK * 2, 1024);
 #pragma unroll
@@ -500,7 +524,7 @@ gemm_rmsnorm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                     }
                     // one commit per stage, to the leader's own barrier; warp 3 relays it to the peer
                     umma2_commit(map_to_rank(smem_u32(&sh->empty[stage]), 0));
-                    if (++stage == P_STAGES) { stage = 0; phase ^= 1; }
+                    if (++stage == PB_SLOTS) { stage = 0; phase ^= 1; }
                 }
                 if (ok) {
                     const uint32_t f = smem_u32(&sh->tmem_full);
@@ -520,26 +544,31 @@ gemm_rmsnorm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                     if (!ok) break;
                     if (t < pair + 2 * n_pairs && kblocks == 32) PTRACE(6, kb + 32 * (t != pair));
                     mbar_arrive_cluster_relaxed(map_to_rank(smem_u32(&sh->empty[stage]), 1));
-                    if (++stage == P_STAGES) { stage = 0; phase ^= 1; }
+                    if (++stage == PB_SLOTS) { stage = 0; phase ^= 1; }
                 }
             }
         }
-    } else if (warp >= 4 && warp < 12) {
+    } else if (warp >= 4 && warp < 20) {
         // ── A transform (both CTAs): shared memory -> x*g -> this CTA's tensor memory, sum x^2 ──
-        const int idx = threadIdx.x - 128;
+        // Two groups of 8 warps take alternate k-blocks: one k-block costs a warp about 1000 clocks of mostly latency
+        // (barrier wake-ups, shared-memory loads, the tensor-memory store and its wait), twice what the tensor core needs.
+        const int idx = (threadIdx.x - 128) & 255, group = (threadIdx.x - 128) >> 8;
         const int row = idx & (BM - 1), half = idx >> 7;
         const uint32_t a_lane = tmem + ((uint32_t)(row & ~31) << 16) + TM_A + half * (BK / 4);
-        int stage = 0; uint32_t phase = 0;
         int use = 0;
+        uint32_t gk = 0;                     // k-blocks since the start, over all tiles: ring positions derive from it
         bool ok = true;
         for (int t = pair; t < tiles && ok; t += n_pairs, ++use) {
             const int a = use & 1;
             float ss = 0.0f;
-            for (int kb = 0; kb < kblocks; ++kb) {
-                ok = mbar_wait_p<false>(&sh->full[stage], phase, sh, err, 24);
+            for (int kb = 0; kb < kblocks; ++kb, ++gk) {
+                if ((int)(gk & 1u) != group) continue;
+                const int sa = gk % PA_SLOTS; const uint32_t pa = (gk / PA_SLOTS) & 1u;          // A ring (shared memory)
+                const int stage = gk % PB_SLOTS; const uint32_t phase = (gk / PB_SLOTS) & 1u;    // B ring = tensor-memory A slots
+                ok = mbar_wait_p<false>(&sh->full_a[sa], pa, sh, err, 24);
                 if (!ok) break;
                 if (t < pair + 2 * n_pairs && kblocks == 32 && idx == 0) PTRACE(2 + rank, kb + 32 * (t != pair));
-                const unsigned char* arow = aligned + stage * P_STAGE_BYTES + row * 128;
+                const unsigned char* arow = aligned + sa * A_BYTES + row * 128;
                 uint32_t av[16];
 #pragma unroll
                 for (int c4 = 0; c4 < 4; ++c4) {
@@ -556,27 +585,35 @@ gemm_rmsnorm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                     }
                     av[4 * c4] = xs[0]; av[4 * c4 + 1] = xs[1]; av[4 * c4 + 2] = xs[2]; av[4 * c4 + 3] = xs[3];
                 }
+                // the A tile is in registers: hand its shared-memory slot back
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&sh->empty_a[sa]);
+                // the tensor-memory slot is free once the MMAs of its previous use retired (the same event that frees the B
+                // slot of that index), and the arrival below also vouches for this CTA's half of B
+                ok = mbar_wait_p<false>(&sh->empty[stage], phase ^ 1, sh, err, 30);
+                if (!ok) break;
+                ok = mbar_wait_p<false>(&sh->full_b[stage], phase, sh, err, 31);
+                if (!ok) break;
+                tc_fence_after();
                 if (!(dbg & 2)) tmem_st16(a_lane + stage * (BK / 2), av);
                 tc_fence_before();
                 __syncwarp();
-                // having seen this CTA's `full`, the arrival also says that this CTA's half of B has landed. The peer's
-                // warps arrive on the leader's barrier directly: no release fence is needed (the tcgen05.st above has
-                // been waited for, the TMA bytes were observed through `full`) and with one it cost about 0.9 us per arrival
+                // The peer's warps arrive on the leader's barrier directly: no release fence is needed (the tcgen05.st above
+                // has been waited for, the TMA bytes were observed through full_b) and with one it cost about 0.9 us per arrival
                 if (lane == 0) mbar_arrive_cluster_relaxed(map_to_rank(smem_u32(&sh->ready[stage]), 0));
-                if (++stage == P_STAGES) { stage = 0; phase ^= 1; }
             }
             if (!ok) break;
             ok = mbar_wait_p<false>(&sh->ss_empty[a], ((use >> 1) & 1) ^ 1, sh, err, 25);
             if (!ok) break;
-            sh->ss[a][half][row] = ss;
+            sh->ss[a][group * 2 + half][row] = ss;
             __syncwarp();
             if (lane == 0) mbar_arrive(&sh->ss_full[a]);
         }
-    } else if (warp >= 12) {
+    } else if (warp >= 20) {
         // ── epilogue (both CTAs): this CTA's 128 rows of the 256 x 256 tile; two warps per lane quarter, 128 columns each ──
         const int q = warp & 3;
         const int row = q * 32 + lane;
-        const int c_begin = ((warp - 12) >> 2) * (BN / 64);
+        const int c_begin = ((warp - 20) >> 2) * (BN / 64);
         const bool wide_ok = (N % 16 == 0) && (((uintptr_t)y & 31) == 0);     // 32-byte stores need 32-byte aligned rows
         int use = 0;
         bool ok = true;
@@ -586,11 +623,11 @@ gemm_rmsnorm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
             const int m0 = (t % m_tiles) * (2 * BM) + (int)rank * BM, n0 = (t / m_tiles) * BN;
             ok = mbar_wait_p<false>(&sh->ss_full[a], (use >> 1) & 1, sh, err, 26);
             if (!ok) break;
-            const float ssv = sh->ss[a][0][row] + sh->ss[a][1][row];
+            const float ssv = (sh->ss[a][0][row] + sh->ss[a][1][row]) + (sh->ss[a][2][row] + sh->ss[a][3][row]);
             const float rstd = 1.0f / sqrtf(ssv * inv_k + eps);
             ok = mbar_wait_p<true>(&sh->tmem_full, use & 1, sh, err, 27);
             if (!ok) break;
-            if (use < 4 && warp == 12 && lane == 0 && rank == 0) PTRACE(4, use);
+            if (use < 4 && warp == 20 && lane == 0 && rank == 0) PTRACE(4, use);
             tc_fence_after();
             const int gr = m0 + row;
 #pragma unroll 1
@@ -599,7 +636,31 @@ gemm_rmsnorm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                 if (!(dbg & 8)) tmem_ld32(tmem + ((uint32_t)(q * 32) << 16) + c * 32, r);
                 else { for (int j = 0; j < 32; ++j) r[j] = j; }
                 const int gc = n0 + c * 32;
-                if (gr < M && gc < N && !(dbg & 4)) {
+                if (bulk_store) {
+                    // bf16 through shared memory and one bulk tensor store per 32 x 32 block: the warp hands 2 KB to the copy
+                    // engine instead of issuing 32-row scattered stores (which cost 4 us of a 20 us tile); the engine clips
+                    // the block at the edges of y
+                    const uint32_t mine = stage_out + (uint32_t)(warp - 20) * 2048u;
+                    if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");    // the previous block has been read out
+                    __syncwarp();
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const uint32_t p0 = pack_bf16x2(__uint_as_float(r[8 * j]) * rstd, __uint_as_float(r[8 * j + 1]) * rstd);
+                        const uint32_t p1 = pack_bf16x2(__uint_as_float(r[8 * j + 2]) * rstd, __uint_as_float(r[8 * j + 3]) * rstd);
+                        const uint32_t p2 = pack_bf16x2(__uint_as_float(r[8 * j + 4]) * rstd, __uint_as_float(r[8 * j + 5]) * rstd);
+                        const uint32_t p3 = pack_bf16x2(__uint_as_float(r[8 * j + 6]) * rstd, __uint_as_float(r[8 * j + 7]) * rstd);
+                        // 64-byte rows: the 16-byte chunk index is XORed with (row / 2) % 4, the copy engine's 64-byte swizzle
+                        const uint32_t at = mine + (uint32_t)lane * 64u + (uint32_t)((j ^ ((lane >> 1) & 3)) << 4);
+                        asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(at), "r"(p0), "r"(p1), "r"(p2), "r"(p3) : "memory");
+                    }
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    __syncwarp();
+                    if (lane == 0 && gc < N && m0 + q * 32 < M) {
+                        asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];"
+                                     ::"l"((uint64_t)&map_y), "r"(gc), "r"(m0 + q * 32), "r"(mine) : "memory");
+                        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                    }
+                } else if (gr < M && gc < N && !(dbg & 4)) {
                     if (out_dtype == SANIC_BF16) {
                         uint32_t pk[16];
 #pragma unroll
@@ -636,13 +697,14 @@ gemm_rmsnorm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
             tc_fence_before();
             __syncwarp();
             if (lane == 0) { mbar_arrive_cluster_relaxed(map_to_rank(smem_u32(&sh->tmem_empty), 0)); mbar_arrive(&sh->ss_empty[a]); }
-            if (use < 4 && warp == 12 && lane == 0 && rank == 0) PTRACE(4, 8 + use);
+            if (use < 4 && warp == 20 && lane == 0 && rank == 0) PTRACE(4, 8 + use);
         }
     }
+    if (bulk_store && warp >= 20 && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");   // every block of y has been written
     // teardown: neither CTA may leave (or free tensor memory) while the other can still reach into it
     tc_fence_before();
     cluster_sync_all();
-    if (warp == 2) {
+    if (warp == 3) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512));
     }
@@ -653,7 +715,7 @@ typedef CUresult (*encode_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, voi
                               CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
 int32_t encode_2d(sanic_ctx* ctx, CUtensorMap* map, const void* ptr, uint64_t inner, uint64_t outer, uint32_t box_inner,
-                  uint32_t box_outer) {
+                  uint32_t box_outer, CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B) {
     if (!ctx->encode_tiled) {
         void* fn = nullptr;
         cudaDriverEntryPointQueryResult q;
@@ -667,7 +729,7 @@ int32_t encode_2d(sanic_ctx* ctx, CUtensorMap* map, const void* ptr, uint64_t in
     cuuint32_t estr[2] = {1, 1};
     CUresult r = ((encode_fn)ctx->encode_tiled)(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims,
                                                 strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                                                CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                                swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                                                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return sanic_fail(ctx, SANIC_ERR_CUDA, "cuTensorMapEncodeTiled failed (" + std::to_string((int)r) + ")");
     return SANIC_OK;
@@ -699,7 +761,18 @@ extern "C" int32_t sanic_gemm_rmsnorm(sanic_ctx* ctx, const sanic_gemm_rmsnorm_p
             rc = encode_2d(ctx, &map_b, p->w, (uint64_t)p->K, (uint64_t)p->N, BK, BN / 2);
             if (rc != SANIC_OK) return rc;
         }
-        const int psmem = P_STAGES * P_STAGE_BYTES + MAX_K * 2 + (int)sizeof(PShared) + 1024;
+        const int kb = (p->K + BK - 1) / BK;
+        const int gamma_bytes = ((kb * BK * 2 + 1023) / 1024) * 1024;
+        int psmem = P_RING_BYTES + gamma_bytes + (int)sizeof(PShared) + 1024;
+        // bf16 output goes through staging and bulk tensor stores when shared memory has room for it (K up to 7168)
+        static const bool no_bulk = getenv("SANIC_PAIR_NO_BULK") != nullptr;
+        const int bulk_store = (p->out_dtype == SANIC_BF16 && psmem + P_OUT_BYTES <= ctx->max_smem && !no_bulk) ? 1 : 0;
+        CUtensorMap map_y = map_a;
+        if (bulk_store) {
+            psmem += P_OUT_BYTES;
+            rc = encode_2d(ctx, &map_y, p->y, (uint64_t)p->N, (uint64_t)p->M, 32, 32, CU_TENSOR_MAP_SWIZZLE_64B);
+            if (rc != SANIC_OK) return rc;
+        }
         SANIC_CUDA_CHECK(ctx, cudaFuncSetAttribute(gemm_rmsnorm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, psmem));
         const int ptiles = ((p->M + 2 * BM - 1) / (2 * BM)) * ((p->N + BN - 1) / BN);
         cudaLaunchConfig_t cfg = {};
@@ -715,10 +788,11 @@ extern "C" int32_t sanic_gemm_rmsnorm(sanic_ctx* ctx, const sanic_gemm_rmsnorm_p
         if (pairs > ctx->sm_count / 2) pairs = ctx->sm_count / 2;
         cfg.gridDim = dim3(2 * pairs);
         if (getenv("SANIC_DEBUG_PAIR")) fprintf(stderr, "pair gemm: max_clusters %d pairs %d tiles %d smem %d\n", max_clusters, pairs, ptiles, psmem);
-        cudaError_t le = cudaLaunchKernelEx(&cfg, gemm_rmsnorm_pair_kernel, map_a, map_b, (const uint16_t*)p->gamma, p->y, (int)p->M,
+        cudaError_t le = cudaLaunchKernelEx(&cfg, gemm_rmsnorm_pair_kernel, map_a, map_b, map_y, (const uint16_t*)p->gamma, p->y, (int)p->M,
                                             (int)p->N, (int)p->K, (int)p->w_is_nk, p->eps, (int)p->out_dtype, ctx->status_dev,
                                             getenv("SANIC_PAIR_DBG") ? atoi(getenv("SANIC_PAIR_DBG")) : 0,
-                                            (unsigned long long*)(getenv("SANIC_PAIR_TRACE") ? (void*)strtoull(getenv("SANIC_PAIR_TRACE"), nullptr, 0) : nullptr));
+                                            (unsigned long long*)(getenv("SANIC_PAIR_TRACE") ? (void*)strtoull(getenv("SANIC_PAIR_TRACE"), nullptr, 0) : nullptr),
+                                            gamma_bytes, bulk_store);
         if (le != cudaSuccess) return sanic_fail(ctx, SANIC_ERR_CUDA, std::string("gemm_rmsnorm (pair): ") + cudaGetErrorString(le));
         return SANIC_OK;
     }
