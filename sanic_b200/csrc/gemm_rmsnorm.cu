@@ -416,8 +416,7 @@ __device__ __forceinline__ void umma2_commit(uint32_t cluster_addr) {
 __global__ void __launch_bounds__(P_NTHREADS, 1)
 gemm_rmsnorm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                          const __grid_constant__ CUtensorMap map_y, const uint16_t* __restrict__ gamma, void* __restrict__ y,
-                         int M, int N, int K, int w_is_nk, float eps, int out_dtype, int* err, int dbg,
-                         unsigned long long* trace, int gamma_bytes, int bulk_store) {
+                         int M, int N, int K, int w_is_nk, float eps, int out_dtype, int* err, int gamma_bytes, int bulk_store) {
     extern __shared__ unsigned char smem_dyn[];
     const uint32_t raw = smem_u32(smem_dyn);
     const uint32_t base = (raw + 1023u) & ~1023u;
@@ -430,7 +429,6 @@ gemm_rmsnorm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_rank();                  // 0 = the leader, which issues every MMA
-#define PTRACE(role, kb) do { if (trace && blockIdx.x < 2 && (kb) < 64) { unsigned long long _t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(_t)); trace[(role) * 64 + (kb)] = _t; } } while (0)
     const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
     const int kblocks = (K + BK - 1) / BK;
     const int m_tiles = (M + 2 * BM - 1) / (2 * BM), n_tiles = (N + BN - 1) / BN;
@@ -467,7 +465,6 @@ gemm_rmsnorm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                 for (int kb = 0; kb < kblocks; ++kb) {
                     ok = mbar_wait_p<false>(&sh->empty_a[stage], phase, sh, err, 20);
                     if (!ok) break;
-                    if (t < pair + 2 * n_pairs && kblocks == 32) PTRACE(0 + rank, kb + 32 * (t != pair));
                     mbar_expect_tx(&sh->full_a[stage], A_BYTES);
                     tma_load_2d(base + stage * A_BYTES, &map_a, &sh->full_a[stage], kb * BK, m0);
                     if (++stage == PA_SLOTS) { stage = 0; phase ^= 1; }
@@ -512,7 +509,6 @@ gemm_rmsnorm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                 for (int kb = 0; kb < kblocks; ++kb) {
                     ok = mbar_wait_p<true>(&sh->ready[stage], phase, sh, err, 23);      // both CTAs' A halves are in tensor memory, both B halves landed
                     if (!ok) break;
-                    if (t < pair + 2 * n_pairs && kblocks == 32) PTRACE(5, kb + 32 * (t != pair));
                     tc_fence_after();
                     const uint32_t sb = b_ring + stage * PB_BYTES;
                     const uint32_t a_tmem = tmem + TM_A + stage * (BK / 2);
@@ -520,7 +516,7 @@ gemm_rmsnorm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
 #pragma unroll
                     for (int k = 0; k < BK / 16; ++k) {
                         const uint64_t bd = bdesc + (uint64_t)(w_is_nk ? k * 2 : k * 128);
-                        if (!(dbg & 1)) umma2_f16_ts(tmem, a_tmem + 8 * k, bd, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                        umma2_f16_ts(tmem, a_tmem + 8 * k, bd, idesc, (kb > 0 || k > 0) ? 1u : 0u);
                     }
                     // one commit per stage, to the leader's own barrier; warp 3 relays it to the peer
                     umma2_commit(map_to_rank(smem_u32(&sh->empty[stage]), 0));
@@ -542,7 +538,6 @@ gemm_rmsnorm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                 for (int kb = 0; kb < kblocks; ++kb) {
                     ok = mbar_wait_p<true>(&sh->empty[stage], phase, sh, err, 29);
                     if (!ok) break;
-                    if (t < pair + 2 * n_pairs && kblocks == 32) PTRACE(6, kb + 32 * (t != pair));
                     mbar_arrive_cluster_relaxed(map_to_rank(smem_u32(&sh->empty[stage]), 1));
                     if (++stage == PB_SLOTS) { stage = 0; phase ^= 1; }
                 }
@@ -567,7 +562,6 @@ gemm_rmsnorm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                 const int stage = gk % PB_SLOTS; const uint32_t phase = (gk / PB_SLOTS) & 1u;    // B ring = tensor-memory A slots
                 ok = mbar_wait_p<false>(&sh->full_a[sa], pa, sh, err, 24);
                 if (!ok) break;
-                if (t < pair + 2 * n_pairs && kblocks == 32 && idx == 0) PTRACE(2 + rank, kb + 32 * (t != pair));
                 const unsigned char* arow = aligned + sa * A_BYTES + row * 128;
                 uint32_t av[16];
 #pragma unroll
@@ -595,7 +589,7 @@ gemm_rmsnorm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                 ok = mbar_wait_p<false>(&sh->full_b[stage], phase, sh, err, 31);
                 if (!ok) break;
                 tc_fence_after();
-                if (!(dbg & 2)) tmem_st16(a_lane + stage * (BK / 2), av);
+                tmem_st16(a_lane + stage * (BK / 2), av);
                 tc_fence_before();
                 __syncwarp();
                 // The peer's warps arrive on the leader's barrier directly: no release fence is needed (the tcgen05.st above
@@ -627,14 +621,12 @@ gemm_rmsnorm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
             const float rstd = 1.0f / sqrtf(ssv * inv_k + eps);
             ok = mbar_wait_p<true>(&sh->tmem_full, use & 1, sh, err, 27);
             if (!ok) break;
-            if (use < 4 && warp == 20 && lane == 0 && rank == 0) PTRACE(4, use);
             tc_fence_after();
             const int gr = m0 + row;
 #pragma unroll 1
             for (int c = c_begin; c < c_begin + BN / 64; ++c) {
                 uint32_t r[32];
-                if (!(dbg & 8)) tmem_ld32(tmem + ((uint32_t)(q * 32) << 16) + c * 32, r);
-                else { for (int j = 0; j < 32; ++j) r[j] = j; }
+                tmem_ld32(tmem + ((uint32_t)(q * 32) << 16) + c * 32, r);
                 const int gc = n0 + c * 32;
                 if (bulk_store) {
                     // bf16 through shared memory and one bulk tensor store per 32 x 32 block: the warp hands 2 KB to the copy
@@ -660,7 +652,7 @@ gemm_rmsnorm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                                      ::"l"((uint64_t)&map_y), "r"(gc), "r"(m0 + q * 32), "r"(mine) : "memory");
                         asm volatile("cp.async.bulk.commit_group;" ::: "memory");
                     }
-                } else if (gr < M && gc < N && !(dbg & 4)) {
+                } else if (gr < M && gc < N) {
                     if (out_dtype == SANIC_BF16) {
                         uint32_t pk[16];
 #pragma unroll
@@ -697,7 +689,6 @@ gemm_rmsnorm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
             tc_fence_before();
             __syncwarp();
             if (lane == 0) { mbar_arrive_cluster_relaxed(map_to_rank(smem_u32(&sh->tmem_empty), 0)); mbar_arrive(&sh->ss_empty[a]); }
-            if (use < 4 && warp == 20 && lane == 0 && rank == 0) PTRACE(4, 8 + use);
         }
     }
     if (bulk_store && warp >= 20 && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");   // every block of y has been written
@@ -754,7 +745,11 @@ extern "C" int32_t sanic_gemm_rmsnorm(sanic_ctx* ctx, const sanic_gemm_rmsnorm_p
     if (rc != SANIC_OK) return rc;
 
     cudaStream_t st = (cudaStream_t)stream;
-    static const bool use_pair = (getenv("SANIC_GEMM_PAIR") != nullptr && getenv("SANIC_GEMM_PAIR")[0] == '1');
+    // The 256 x 256 tile on SM pairs wins (5-7 % at 4096 x 2048 x 8192) once there are enough of those tiles to fill the
+    // pairs; smaller problems keep the one-CTA 128 x 256 tile. SANIC_GEMM_PAIR=0/1 forces the choice (tests, A/B timing).
+    const int pair_tiles = ((p->M + 2 * BM - 1) / (2 * BM)) * ((p->N + BN - 1) / BN);
+    const char* force = getenv("SANIC_GEMM_PAIR");
+    const bool use_pair = force ? (force[0] == '1') : (p->M >= 4 * BM && pair_tiles >= ctx->sm_count / 2);
     if (use_pair) {
         // the 256 x 256 tile on a pair of SMs: B's map has a 128-row box (this CTA's half)
         if (p->w_is_nk) {
@@ -765,8 +760,7 @@ extern "C" int32_t sanic_gemm_rmsnorm(sanic_ctx* ctx, const sanic_gemm_rmsnorm_p
         const int gamma_bytes = ((kb * BK * 2 + 1023) / 1024) * 1024;
         int psmem = P_RING_BYTES + gamma_bytes + (int)sizeof(PShared) + 1024;
         // bf16 output goes through staging and bulk tensor stores when shared memory has room for it (K up to 7168)
-        static const bool no_bulk = getenv("SANIC_PAIR_NO_BULK") != nullptr;
-        const int bulk_store = (p->out_dtype == SANIC_BF16 && psmem + P_OUT_BYTES <= ctx->max_smem && !no_bulk) ? 1 : 0;
+        const int bulk_store = (p->out_dtype == SANIC_BF16 && psmem + P_OUT_BYTES <= ctx->max_smem) ? 1 : 0;
         CUtensorMap map_y = map_a;
         if (bulk_store) {
             psmem += P_OUT_BYTES;
@@ -787,11 +781,8 @@ extern "C" int32_t sanic_gemm_rmsnorm(sanic_ctx* ctx, const sanic_gemm_rmsnorm_p
         int pairs = ptiles < max_clusters ? ptiles : max_clusters;
         if (pairs > ctx->sm_count / 2) pairs = ctx->sm_count / 2;
         cfg.gridDim = dim3(2 * pairs);
-        if (getenv("SANIC_DEBUG_PAIR")) fprintf(stderr, "pair gemm: max_clusters %d pairs %d tiles %d smem %d\n", max_clusters, pairs, ptiles, psmem);
         cudaError_t le = cudaLaunchKernelEx(&cfg, gemm_rmsnorm_pair_kernel, map_a, map_b, map_y, (const uint16_t*)p->gamma, p->y, (int)p->M,
                                             (int)p->N, (int)p->K, (int)p->w_is_nk, p->eps, (int)p->out_dtype, ctx->status_dev,
-                                            getenv("SANIC_PAIR_DBG") ? atoi(getenv("SANIC_PAIR_DBG")) : 0,
-                                            (unsigned long long*)(getenv("SANIC_PAIR_TRACE") ? (void*)strtoull(getenv("SANIC_PAIR_TRACE"), nullptr, 0) : nullptr),
                                             gamma_bytes, bulk_store);
         if (le != cudaSuccess) return sanic_fail(ctx, SANIC_ERR_CUDA, std::string("gemm_rmsnorm (pair): ") + cudaGetErrorString(le));
         return SANIC_OK;

@@ -447,6 +447,20 @@ def test_gemm_rmsnorm_many_tiles_per_cta(dev):
     assert got.shape == (2048, 8192)
 
 
+@pytest.mark.parametrize("form", ["0", "1"])
+def test_gemm_rmsnorm_both_tile_forms(dev, form, monkeypatch):
+    # SANIC_GEMM_PAIR forces the one-CTA 128 x 256 tile ("0") or the 256 x 256 tile on a pair of SMs ("1": two CTAs of a
+    # cluster, tcgen05 cta_group::2, bulk tensor stores); without it the library picks by problem size
+    monkeypatch.setenv("SANIC_GEMM_PAIR", form)
+    for nk in (True, False):
+        _gemm_case(dev, 128, 256, 256, nk)                                  # one CTA of the pair has no rows at all
+        _gemm_case(dev, 384, 512, 768, nk, out_dtype=torch.float32)         # direct f32 stores
+        _gemm_case(dev, 200, 320, 264, nk)                                  # ragged M, K, N: the bulk stores clip at the edges
+    got, exp = _gemm_case(dev, 2048, 256, 8192, True)                       # several tiles per pair: ring and accumulator phases
+    assert got.shape == (2048, 8192)
+    _gemm_case(dev, 512, 8192, 256, True)                                   # the longest K: staging does not fit, direct stores
+
+
 # ───────────────────────── prefill online-softmax fold (tcgen05) ─────────────────────────
 def _flash_case(dev, B, Hq, Hkv, Lq, Lk, mode, window=0, seed=91):
     q, qv = bf16t(normal(seed, B, Hq, Lq, 64), dev)
