@@ -13,11 +13,21 @@
 // strided loads, coordinates and the closed scalar basis (src/scalar.rs:45-69; Expr, src/derive.rs:96-118).
 //
 // Arithmetic is f32 in registers, loads and stores are typed (bf16 widen, int4 nibble q+8, bf16 RNE store, u32
-// saturating store: src/emit_metal.rs:119-232). Lane split: lane b of B = min(32, stream) folds the contiguous
-// chunk [b*n/B, (b+1)*n/B) and the partials merge left to right in lane order, which is the chunking and the
-// merge order of run_carrier_split (src/interp.rs:597-640), so it is legal for every associative carrier; the
-// interleaved split (lane b takes s = b, b+32, ...: coalesced for a unit stream stride) needs a carrier that
-// merges out of order (src/plan.rs:481-488) and is the caller's choice.
+// saturating store: src/emit_metal.rs:119-232). A leaf may be a contraction computed in the fold body (sum over an
+// inner axis) or a gather (index rounded half away from zero, then bounds-checked: an index out of range reads 0 and
+// leaves code 51 in the context's status word). A store may be conditional (the in-place where(c, x, s)).
+// Schedules (FoldSched, src/plan.rs:434-488):
+//   lanes = 1                one thread per output point.
+//   lanes = 32               the streamed axis over the lanes of a warp: lane b of B = min(32, stream) folds the
+//                            contiguous chunk [b*n/B, (b+1)*n/B) and the partials merge left to right in lane order, the
+//                            chunking and merge order of run_carrier_split (src/interp.rs:597-640), legal for every
+//                            associative carrier; `interleave` (lane b takes s = b, b+32, ...: coalesced for a unit
+//                            stream stride) needs a carrier that merges out of order (src/plan.rs:481-488).
+//   warps = 2..8             the same split over all threads of a block, warp partials merged in warp order through
+//                            shared memory.
+//   lane_axis                the LAST grid axis over the lanes instead: a warp owns 32 neighbouring output points, a
+//                            contracted leaf that does not read that axis is computed once per warp (inner axis over
+//                            the lanes, butterfly sum), and with warps > 1 the streamed axis is split over the warps.
 #include <cuda.h>
 #include <dlfcn.h>
 #include <nvrtc.h>

@@ -72,10 +72,12 @@ def test_struct_sizes_match_the_header():
 #include <stddef.h>
 #include "sanic_b200.h"
 int main(void) {
-  printf("%zu %zu %zu %zu %zu %zu %zu %zu %zu %zu %zu\n", sizeof(sanic_device_specs), sizeof(sanic_carrier_desc),
+  printf("%zu %zu %zu %zu %zu %zu %zu %zu %zu %zu %zu %zu %zu %zu %zu %zu %zu\n", sizeof(sanic_device_specs), sizeof(sanic_carrier_desc),
          sizeof(sanic_attn_params), sizeof(sanic_decode_params), sizeof(sanic_gemm_rmsnorm_params),
          sizeof(sanic_gemv_params), sizeof(sanic_rope_cache_params), sizeof(sanic_stage_desc),
-         offsetof(sanic_stage_desc, u), sizeof(sanic_peer_exchange), offsetof(sanic_peer_exchange, epoch));
+         offsetof(sanic_stage_desc, u), sizeof(sanic_peer_exchange), offsetof(sanic_peer_exchange, epoch),
+         sizeof(sanic_expr_op), sizeof(sanic_operand), offsetof(sanic_operand, gather_extent), sizeof(sanic_generic_desc),
+         offsetof(sanic_generic_desc, project), offsetof(sanic_generic_desc, out_dtype));
   return 0; }
 '''
     with tempfile.TemporaryDirectory() as d:
@@ -86,7 +88,9 @@ int main(void) {
         got = [int(t) for t in subprocess.run([exe], capture_output=True, text=True, check=True).stdout.split()]
     want = [C.sizeof(abi.DeviceSpecs), C.sizeof(abi.CarrierDesc), C.sizeof(abi.AttnParams), C.sizeof(abi.DecodeParams),
             C.sizeof(abi.GemmRmsnormParams), C.sizeof(abi.GemvParams), C.sizeof(abi.RopeCacheParams),
-            C.sizeof(abi.StageDesc), abi.StageDesc.u.offset, C.sizeof(abi.PeerExchange), abi.PeerExchange.epoch.offset]
+            C.sizeof(abi.StageDesc), abi.StageDesc.u.offset, C.sizeof(abi.PeerExchange), abi.PeerExchange.epoch.offset,
+            C.sizeof(abi.ExprOp), C.sizeof(abi.Operand), abi.Operand.gather_extent.offset, C.sizeof(abi.GenericDesc),
+            abi.GenericDesc.project.offset, abi.GenericDesc.out_dtype.offset]
     assert got == want
 
 
