@@ -619,7 +619,7 @@ gemm_rmsnorm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
             if (!ok) break;
             const float ssv = (sh->ss[a][0][row] + sh->ss[a][1][row]) + (sh->ss[a][2][row] + sh->ss[a][3][row]);
             const float rstd = 1.0f / sqrtf(ssv * inv_k + eps);
-            ok = mbar_wait_p<true>(&sh->tmem_full, use & 1, sh, err, 27);
+            ok = mbar_wait_p<false>(&sh->tmem_full, use & 1, sh, err, 27);     // parked, not polling: 256 threads wait here for a whole tile
             if (!ok) break;
             tc_fence_after();
             const int gr = m0 + row;
