@@ -345,17 +345,17 @@ gemm_rmsnorm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 // Synchronisation across the pair: the transform warps of both CTAs arrive on the LEADER's ready barrier (relaxed
 // cluster-scope arrivals: a release fence on that path costs about 0.9 us each); the leader's commits arrive on the stage-empty and accumulator-full barriers of BOTH CTAs (one commit per
 // destination); the epilogue warps of both CTAs arrive on the leader's accumulator-empty barrier.
-constexpr int PA_SLOTS = 4;                            // A tiles in shared memory: free again as soon as the transform has read them
-constexpr int PB_SLOTS = 8;                            // B half-tiles in shared memory, and transformed A tiles in tensor memory
+constexpr int PA_SLOTS = 6;                            // A tiles in shared memory, transformed in place, read by the MMA from there
+constexpr int PB_SLOTS = 6;                            // B half-tiles in shared memory; stage s = A slot s + B slot s
 constexpr int PB_BYTES = (BN / 2) * BK * 2;            // 16 KB: this CTA's half of the B tile
 constexpr int P_RING_BYTES = PA_SLOTS * A_BYTES + PB_SLOTS * PB_BYTES;    // 192 KB
 constexpr int P_OUT_BYTES = 8 * 2048;                  // store staging: one 32 x 32 bf16 block per epilogue warp
 constexpr int P_NTHREADS = 896;                        // warps 0-3 single-thread roles, 4-19 A transform (two groups), 20-27 epilogue
 
 struct PShared {
-    uint64_t full_a[PA_SLOTS], empty_a[PA_SLOTS];
+    uint64_t full_a[PA_SLOTS];
     uint64_t full_b[PB_SLOTS], ready[PB_SLOTS], empty[PB_SLOTS];
-    uint64_t tmem_full, tmem_empty, ss_full[2], ss_empty[2];
+    uint64_t tmem_full[2], tmem_empty[2], ss_full[2], ss_empty[2];
     uint32_t tmem_base;
     volatile int abort_flag;
     float ss[2][4][BM];   // [accumulator use parity][transform group * 2 + row half][row]
@@ -403,10 +403,10 @@ __device__ __forceinline__ bool mbar_wait_p(uint64_t* bar, uint32_t parity, PSha
     atomicCAS(err, 0, code);
     return false;
 }
-__device__ __forceinline__ void umma2_f16_ts(uint32_t tmem_d, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+__device__ __forceinline__ void umma2_f16_ss(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
     asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-                 "tcgen05.mma.cta_group::2.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
-                 ::"r"(tmem_d), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+                 "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                 ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
 }
 // arrives on ONE barrier, given by its shared::cluster address (this CTA's or the peer's), when the pair's MMAs so far retire
 __device__ __forceinline__ void umma2_commit(uint32_t cluster_addr) {
@@ -435,10 +435,12 @@ gemm_rmsnorm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
     const int tiles = m_tiles * n_tiles;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < PA_SLOTS; ++s) { mbar_init(&sh->full_a[s], 1); mbar_init(&sh->empty_a[s], 8); }
+        for (int s = 0; s < PA_SLOTS; ++s) mbar_init(&sh->full_a[s], 1);
         for (int s = 0; s < PB_SLOTS; ++s) { mbar_init(&sh->full_b[s], 1); mbar_init(&sh->ready[s], 16); mbar_init(&sh->empty[s], 1); }
-        mbar_init(&sh->tmem_full, 1); mbar_init(&sh->tmem_empty, 16);
-        for (int a = 0; a < 2; ++a) { mbar_init(&sh->ss_full[a], 16); mbar_init(&sh->ss_empty[a], 8); }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(&sh->tmem_full[a], 1); mbar_init(&sh->tmem_empty[a], 16);
+            mbar_init(&sh->ss_full[a], 16); mbar_init(&sh->ss_empty[a], 8);
+        }
         sh->abort_flag = 0;
         sh->tmem_base = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -456,14 +458,14 @@ gemm_rmsnorm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
     const uint32_t tmem = sh->tmem_base;
 
     if (warp == 0) {
-        // ── TMA producer for A: this CTA's 128 rows; a slot is free again once the 8 transform warps have read it ──
+        // ── TMA producer for A: this CTA's 128 rows; a slot is free again once the pair's MMAs on it retire ──
         if (lane == 0) {
             int stage = 0; uint32_t phase = 1;
             bool ok = true;
             for (int t = pair; t < tiles && ok; t += n_pairs) {
                 const int m0 = (t % m_tiles) * (2 * BM) + (int)rank * BM;
                 for (int kb = 0; kb < kblocks; ++kb) {
-                    ok = mbar_wait_p<false>(&sh->empty_a[stage], phase, sh, err, 20);
+                    ok = mbar_wait_p<true>(&sh->empty[stage], phase, sh, err, 20);
                     if (!ok) break;
                     mbar_expect_tx(&sh->full_a[stage], A_BYTES);
                     tma_load_2d(base + stage * A_BYTES, &map_a, &sh->full_a[stage], kb * BK, m0);
@@ -503,27 +505,29 @@ gemm_rmsnorm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
             int use = 0;
             bool ok = true;
             for (int t = pair; t < tiles && ok; t += n_pairs, ++use) {
-                ok = mbar_wait_p<true>(&sh->tmem_empty, (use & 1) ^ 1, sh, err, 22);    // both epilogues have read the previous tile
+                const int ab = use & 1;                                                   // accumulator buffer: 256 columns each
+                ok = mbar_wait_p<true>(&sh->tmem_empty[ab], ((use >> 1) & 1) ^ 1, sh, err, 22);    // both epilogues have read its previous tile
                 if (!ok) break;
                 tc_fence_after();
+                const uint32_t acc = tmem + (uint32_t)ab * BN;
                 for (int kb = 0; kb < kblocks; ++kb) {
                     ok = mbar_wait_p<true>(&sh->ready[stage], phase, sh, err, 23);      // both CTAs' A halves are in tensor memory, both B halves landed
                     if (!ok) break;
                     tc_fence_after();
                     const uint32_t sb = b_ring + stage * PB_BYTES;
-                    const uint32_t a_tmem = tmem + TM_A + stage * (BK / 2);
+                    const uint64_t adesc = make_desc(base + stage * A_BYTES, 16, 1024);
                     const uint64_t bdesc = w_is_nk ? make_desc(sb, 16, 1024) : make_desc(sb, 64 * BK * 2, 1024);
 #pragma unroll
                     for (int k = 0; k < BK / 16; ++k) {
                         const uint64_t bd = bdesc + (uint64_t)(w_is_nk ? k * 2 : k * 128);
-                        umma2_f16_ts(tmem, a_tmem + 8 * k, bd, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                        umma2_f16_ss(acc, adesc + (uint64_t)(k * 2), bd, idesc, (kb > 0 || k > 0) ? 1u : 0u);
                     }
                     // one commit per stage, to the leader's own barrier; warp 3 relays it to the peer
                     umma2_commit(map_to_rank(smem_u32(&sh->empty[stage]), 0));
                     if (++stage == PB_SLOTS) { stage = 0; phase ^= 1; }
                 }
                 if (ok) {
-                    const uint32_t f = smem_u32(&sh->tmem_full);
+                    const uint32_t f = smem_u32(&sh->tmem_full[ab]);
                     umma2_commit(map_to_rank(f, 0));
                     umma2_commit(map_to_rank(f, 1));
                 }
@@ -549,7 +553,6 @@ gemm_rmsnorm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
         // (barrier wake-ups, shared-memory loads, the tensor-memory store and its wait), twice what the tensor core needs.
         const int idx = (threadIdx.x - 128) & 255, group = (threadIdx.x - 128) >> 8;
         const int row = idx & (BM - 1), half = idx >> 7;
-        const uint32_t a_lane = tmem + ((uint32_t)(row & ~31) << 16) + TM_A + half * (BK / 4);
         int use = 0;
         uint32_t gk = 0;                     // k-blocks since the start, over all tiles: ring positions derive from it
         bool ok = true;
@@ -558,12 +561,10 @@ gemm_rmsnorm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
             float ss = 0.0f;
             for (int kb = 0; kb < kblocks; ++kb, ++gk) {
                 if ((int)(gk & 1u) != group) continue;
-                const int sa = gk % PA_SLOTS; const uint32_t pa = (gk / PA_SLOTS) & 1u;          // A ring (shared memory)
-                const int stage = gk % PB_SLOTS; const uint32_t phase = (gk / PB_SLOTS) & 1u;    // B ring = tensor-memory A slots
-                ok = mbar_wait_p<false>(&sh->full_a[sa], pa, sh, err, 24);
+                const int stage = gk % PB_SLOTS; const uint32_t phase = (gk / PB_SLOTS) & 1u;
+                ok = mbar_wait_p<false>(&sh->full_a[stage], phase, sh, err, 24);
                 if (!ok) break;
-                const unsigned char* arow = aligned + sa * A_BYTES + row * 128;
-                uint32_t av[16];
+                unsigned char* arow = aligned + stage * A_BYTES + row * 128;
 #pragma unroll
                 for (int c4 = 0; c4 < 4; ++c4) {
                     const int c = half * 4 + c4;
@@ -577,23 +578,16 @@ gemm_rmsnorm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                         ss = fmaf(x0, x0, ss); ss = fmaf(x1, x1, ss);
                         asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(xs[j]) : "r"(xs[j]), "r"(gs[j]));
                     }
-                    av[4 * c4] = xs[0]; av[4 * c4 + 1] = xs[1]; av[4 * c4 + 2] = xs[2]; av[4 * c4 + 3] = xs[3];
+                    // back to the same (swizzled) place: the MMA reads x*g from shared memory
+                    *(uint4*)(arow + ((c ^ (row & 7)) << 4)) = make_uint4(xs[0], xs[1], xs[2], xs[3]);
                 }
-                // the A tile is in registers: hand its shared-memory slot back
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&sh->empty_a[sa]);
-                // the tensor-memory slot is free once the MMAs of its previous use retired (the same event that frees the B
-                // slot of that index), and the arrival below also vouches for this CTA's half of B
-                ok = mbar_wait_p<false>(&sh->empty[stage], phase ^ 1, sh, err, 30);
-                if (!ok) break;
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // generic writes -> visible to the tensor core's reads
+                // the arrival below also vouches for this CTA's half of B
                 ok = mbar_wait_p<false>(&sh->full_b[stage], phase, sh, err, 31);
                 if (!ok) break;
-                tc_fence_after();
-                tmem_st16(a_lane + stage * (BK / 2), av);
-                tc_fence_before();
                 __syncwarp();
-                // The peer's warps arrive on the leader's barrier directly: no release fence is needed (the tcgen05.st above
-                // has been waited for, the TMA bytes were observed through full_b) and with one it cost about 0.9 us per arrival
+                // The peer's warps arrive on the leader's barrier directly, without a release fence (it cost about 0.9 us per
+                // arrival): the writes above were ordered by the proxy fence, the TMA bytes were observed through full_b
                 if (lane == 0) mbar_arrive_cluster_relaxed(map_to_rank(smem_u32(&sh->ready[stage]), 0));
             }
             if (!ok) break;
@@ -619,14 +613,14 @@ gemm_rmsnorm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
             if (!ok) break;
             const float ssv = (sh->ss[a][0][row] + sh->ss[a][1][row]) + (sh->ss[a][2][row] + sh->ss[a][3][row]);
             const float rstd = 1.0f / sqrtf(ssv * inv_k + eps);
-            ok = mbar_wait_p<false>(&sh->tmem_full, use & 1, sh, err, 27);     // parked, not polling: 256 threads wait here for a whole tile
+            ok = mbar_wait_p<false>(&sh->tmem_full[a], (use >> 1) & 1, sh, err, 27);     // parked, not polling: 256 threads wait here for a whole tile
             if (!ok) break;
             tc_fence_after();
             const int gr = m0 + row;
 #pragma unroll 1
             for (int c = c_begin; c < c_begin + BN / 64; ++c) {
                 uint32_t r[32];
-                tmem_ld32(tmem + ((uint32_t)(q * 32) << 16) + c * 32, r);
+                tmem_ld32(tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)a * BN + c * 32, r);
                 const int gc = n0 + c * 32;
                 if (bulk_store) {
                     // bf16 through shared memory and one bulk tensor store per 32 x 32 block: the warp hands 2 KB to the copy
@@ -688,7 +682,7 @@ gemm_rmsnorm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
             }
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) { mbar_arrive_cluster_relaxed(map_to_rank(smem_u32(&sh->tmem_empty), 0)); mbar_arrive(&sh->ss_empty[a]); }
+            if (lane == 0) { mbar_arrive_cluster_relaxed(map_to_rank(smem_u32(&sh->tmem_empty[a]), 0)); mbar_arrive(&sh->ss_empty[a]); }
         }
     }
     if (bulk_store && warp >= 20 && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");   // every block of y has been written
