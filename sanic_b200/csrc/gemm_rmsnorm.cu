@@ -336,15 +336,21 @@ gemm_rmsnorm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 }
 
 // ───────────────────────── the same contraction on a pair of SMs ─────────────────────────
-// Two CTAs of a cluster share one 256x256 output tile: CTA r holds rows [128r, 128r+128) of A (transformed into its own
-// tensor memory as above) and columns [128r, 128r+128) of B in its shared memory, and ONE thread of the leader CTA
-// issues tcgen05.mma.cta_group::2 (M = 256): each SM multiplies its half of A with the whole of B, reading the other
-// half of B from its peer. Per k-block a CTA now brings 32 KB through L2 -> shared memory instead of 48 KB for the same
-// tensor work, which is what bounds the one-CTA tile. Two rings: 4 A tiles (a slot is free as soon as the transform has
-// read it) and 8 B half-tiles, matched by 8 transformed-A slots in tensor memory (512 columns in all).
-// Synchronisation across the pair: the transform warps of both CTAs arrive on the LEADER's ready barrier (relaxed
-// cluster-scope arrivals: a release fence on that path costs about 0.9 us each); the leader's commits arrive on the stage-empty and accumulator-full barriers of BOTH CTAs (one commit per
-// destination); the epilogue warps of both CTAs arrive on the leader's accumulator-empty barrier.
+// Two CTAs of a cluster share one 256x256 output tile: CTA r holds rows [128r, 128r+128) of A and columns
+// [128r, 128r+128) of B in its shared memory, and ONE thread of the leader CTA issues tcgen05.mma.cta_group::2 (M = 256):
+// each SM multiplies its half of A with the whole of B, reading the other half of B from its peer. Per k-block a CTA
+// brings 32 KB through L2 -> shared memory instead of 48 KB for the same tensor work, which is what bounds the one-CTA
+// tile. With B's shared-memory traffic halved there is room to rewrite A in place (x*g back to the same swizzled
+// bytes) and feed the MMA from shared memory; tensor memory then holds TWO 256-column accumulators and the epilogue
+// of a tile overlaps the main loop of the next. (Fed from tensor memory instead, the MMAs paid a fixed cost per
+// instruction and left room for one accumulator only: same speed, epilogue exposed.)
+// Six stages of (A 16 KB + B half 16 KB); A and B have their own producer threads and full barriers, one empty barrier.
+// Two groups of 8 transform warps take alternate k-blocks. bf16 output leaves through shared-memory staging and one
+// bulk tensor store per 32 x 32 block.
+// Synchronisation across the pair: the transform warps of both CTAs arrive on the LEADER's ready barrier with relaxed
+// cluster-scope arrivals (a release fence on that path costs about 0.9 us per arrival); the leader commits each stage
+// to its own empty barrier and a relay thread forwards it to the peer's; the accumulator-full commits go to both CTAs
+// (one commit per destination); the epilogue warps of both CTAs arrive on the leader's accumulator-empty barrier.
 constexpr int PA_SLOTS = 6;                            // A tiles in shared memory, transformed in place, read by the MMA from there
 constexpr int PB_SLOTS = 6;                            // B half-tiles in shared memory; stage s = A slot s + B slot s
 constexpr int PB_BYTES = (BN / 2) * BK * 2;            // 16 KB: this CTA's half of the B tile
