@@ -274,6 +274,7 @@ gemm_rmsnorm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         // ── epilogue ──
         const int q = warp & 3;                      // TMEM lane quarter this warp may read
         const int row = q * 32 + lane;
+        const bool wide_ok = (N % 16 == 0) && (((uintptr_t)y & 31) == 0);     // 32-byte stores need 32-byte aligned rows
         int use = 0;
         bool ok = true;
         const float inv_k = 1.0f / (float)K;
@@ -300,7 +301,13 @@ gemm_rmsnorm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                         for (int j = 0; j < 16; ++j)
                             pk[j] = pack_bf16x2(__uint_as_float(r[2 * j]) * rstd, __uint_as_float(r[2 * j + 1]) * rstd);
                         uint16_t* dst = (uint16_t*)y + (size_t)gr * N + gc;
-                        if (gc + 32 <= N) {
+                        if (gc + 32 <= N && wide_ok) {
+#pragma unroll
+                            for (int j = 0; j < 2; ++j)      // 32-byte stores: every lane writes whole sectors
+                                asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(dst + 16 * j), "r"(pk[8 * j]),
+                                             "r"(pk[8 * j + 1]), "r"(pk[8 * j + 2]), "r"(pk[8 * j + 3]), "r"(pk[8 * j + 4]),
+                                             "r"(pk[8 * j + 5]), "r"(pk[8 * j + 6]), "r"(pk[8 * j + 7]) : "memory");
+                        } else if (gc + 32 <= N) {
 #pragma unroll
                             for (int j = 0; j < 4; ++j)
                                 *(uint4*)(dst + 8 * j) = make_uint4(pk[4 * j], pk[4 * j + 1], pk[4 * j + 2], pk[4 * j + 3]);
