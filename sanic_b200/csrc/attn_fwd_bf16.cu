@@ -369,13 +369,26 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                 if (grow < p.q_len) {
                     const float inv = 1.0f / l;
                     uint16_t* dst = (uint16_t*)p.out + ((size_t)(w.b * p.q_heads + w.h) * p.q_len + grow) * D;
+                    if (((uintptr_t)p.out & 31) == 0) {
+                        // a 128-byte row per thread as four 32-byte stores: every lane writes whole sectors
 #pragma unroll
-                    for (int q = 0; q < D / 8; ++q) {
-                        uint32_t w0 = pack_bf16x2(__uint_as_float(o[8 * q]) * inv, __uint_as_float(o[8 * q + 1]) * inv);
-                        uint32_t w1 = pack_bf16x2(__uint_as_float(o[8 * q + 2]) * inv, __uint_as_float(o[8 * q + 3]) * inv);
-                        uint32_t w2 = pack_bf16x2(__uint_as_float(o[8 * q + 4]) * inv, __uint_as_float(o[8 * q + 5]) * inv);
-                        uint32_t w3 = pack_bf16x2(__uint_as_float(o[8 * q + 6]) * inv, __uint_as_float(o[8 * q + 7]) * inv);
-                        *(uint4*)(dst + q * 8) = make_uint4(w0, w1, w2, w3);
+                        for (int q = 0; q < D / 16; ++q) {
+                            uint32_t wv[8];
+#pragma unroll
+                            for (int j = 0; j < 8; ++j)
+                                wv[j] = pack_bf16x2(__uint_as_float(o[16 * q + 2 * j]) * inv, __uint_as_float(o[16 * q + 2 * j + 1]) * inv);
+                            asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(dst + q * 16), "r"(wv[0]), "r"(wv[1]),
+                                         "r"(wv[2]), "r"(wv[3]), "r"(wv[4]), "r"(wv[5]), "r"(wv[6]), "r"(wv[7]) : "memory");
+                        }
+                    } else {
+#pragma unroll
+                        for (int q = 0; q < D / 8; ++q) {
+                            uint32_t w0 = pack_bf16x2(__uint_as_float(o[8 * q]) * inv, __uint_as_float(o[8 * q + 1]) * inv);
+                            uint32_t w1 = pack_bf16x2(__uint_as_float(o[8 * q + 2]) * inv, __uint_as_float(o[8 * q + 3]) * inv);
+                            uint32_t w2 = pack_bf16x2(__uint_as_float(o[8 * q + 4]) * inv, __uint_as_float(o[8 * q + 5]) * inv);
+                            uint32_t w3 = pack_bf16x2(__uint_as_float(o[8 * q + 6]) * inv, __uint_as_float(o[8 * q + 7]) * inv);
+                            *(uint4*)(dst + q * 8) = make_uint4(w0, w1, w2, w3);
+                        }
                     }
                 }
             }
