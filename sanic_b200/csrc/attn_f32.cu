@@ -12,6 +12,11 @@
 // Chunks are folded left to right, which is the lane_stream x sgs schedule of the reference's cooperative fold
 // (src/emit_metal.rs:760-1101, src/plan.rs:434-455) with the CTA as the lane group; project o / l at the end.
 //
+// When the (row block, batch * head) grid alone would leave SMs idle, the key axis is also split over the CTAs of a
+// thread-block cluster (up to 8): CTA z folds the contiguous chunk range [z*n/Z, (z+1)*n/Z), leaves its raw (m, l, o)
+// in its own shared memory, and CTA 0 merges the partials in rank order through distributed shared memory with the
+// carrier's combine: run_carrier_split (src/interp.rs:597-640) with the cluster as the device, no scratch in HBM.
+//
 // A tensor-core TF32 contraction has a 10-bit mantissa and cannot hold the 1e-5
 // relative bound this path is checked at, so the contraction runs as FP32 FMAs and
 // exp / division are the full-precision library routines.
@@ -28,6 +33,7 @@ __global__ void __launch_bounds__(NT) attn_fwd_f32_kernel(sanic_attn_params p) {
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int r0 = blockIdx.x * BQ;
     const int bh = blockIdx.y;
+    const int z = blockIdx.z, Z = gridDim.z;      // this CTA's share of the key chunks; the cluster spans z
     const int b = bh / p.q_heads, h = bh % p.q_heads;
     const int hk = h / (p.q_heads / p.kv_heads);
     const int E = p.head_dim, Ev = p.v_dim, S = p.kv_len, L = p.q_len;
@@ -38,6 +44,7 @@ __global__ void __launch_bounds__(NT) attn_fwd_f32_kernel(sanic_attn_params p) {
     float* red = ps + BQ * NT;            // [BQ][8] warp maxima
     float* mrow = red + BQ * 8;           // [BQ] running max
     float* arow = mrow + BQ;              // [BQ] rescale factor of the current chunk
+    float* part = arow + BQ;              // [BQ][2 + DV] this CTA's raw (m, l, o), read by CTA 0 of the cluster
     for (int i = tid; i < BQ * E; i += NT) {
         const int r = i / E, d = i % E;
         qs[i] = (r0 + r < L) ? ((const float*)p.q)[((size_t)bh * L + r0 + r) * E + d] : 0.0f;
@@ -58,7 +65,9 @@ __global__ void __launch_bounds__(NT) attn_fwd_f32_kernel(sanic_attn_params p) {
     const int rq = tid / DV, e = tid % DV;       // the (row, output column) this thread accumulates
     float l = 0.0f, o = 0.0f;
 
-    for (int c0 = (j_lo / NT) * NT; c0 < j_hi; c0 += NT) {
+    const int c_first = j_lo / NT, n_chunks = (j_hi > j_lo) ? (j_hi + NT - 1) / NT - c_first : 0;
+    const int c_begin = c_first + (z * n_chunks) / Z, c_end = c_first + ((z + 1) * n_chunks) / Z;
+    for (int c0 = c_begin * NT; c0 < c_end * NT; c0 += NT) {
         // ── scores of key j against the BQ rows ──
         const int j = c0 + tid;
         {   // the chunk's V rows are read 256 FMAs from now: start them towards L1 (one 128-byte line per request)
@@ -148,6 +157,28 @@ __global__ void __launch_bounds__(NT) attn_fwd_f32_kernel(sanic_attn_params p) {
         }
         __syncthreads();      // ps, red and arow are rewritten by the next chunk
     }
+    if (Z > 1) {
+        // partials meet in CTA 0 of the cluster, merged left to right in rank (= chunk) order
+        part[rq * (2 + DV) + 2 + e] = o;
+        if (e == 0) { part[rq * (2 + DV)] = mrow[rq]; part[rq * (2 + DV) + 1] = l; }
+        asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+        if (z == 0) {
+            float m = mrow[rq];
+            for (int q = 1; q < Z; ++q) {
+                uint32_t remote;
+                asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(part + rq * (2 + DV))), "r"(q));
+                float mb, lb, ob;
+                asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(mb) : "r"(remote) : "memory");
+                asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(lb) : "r"(remote + 4) : "memory");
+                asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(ob) : "r"(remote + 8 + 4 * e) : "memory");
+                const MloScale sc = mlo_rescale(m, mb);
+                l = l * sc.ra + lb * sc.rb; o = o * sc.ra + ob * sc.rb; m = sc.m;
+            }
+        }
+        // the other CTAs' shared memory must outlive CTA 0's reads
+        asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+        if (z != 0) return;
+    }
     if (e < Ev && r0 + rq < L) ((float*)p.out)[((size_t)bh * L + r0 + rq) * Ev + e] = o / l;
 }
 }  // namespace
@@ -166,10 +197,25 @@ extern "C" int32_t sanic_attn_fwd_f32(sanic_ctx* ctx, const sanic_attn_params* p
     const int dv = p->v_dim <= 32 ? 32 : (p->v_dim <= 64 ? 64 : 128);
     const int bq = NT / dv;
     dim3 grid((p->q_len + bq - 1) / bq, p->batch * p->q_heads), block(NT);
-    size_t smem = ((size_t)bq * p->head_dim + (size_t)bq * NT + (size_t)bq * 10) * sizeof(float);
-    if (dv == 32) attn_fwd_f32_kernel<32><<<grid, block, smem, (cudaStream_t)stream>>>(*p);
-    else if (dv == 64) attn_fwd_f32_kernel<64><<<grid, block, smem, (cudaStream_t)stream>>>(*p);
-    else attn_fwd_f32_kernel<128><<<grid, block, smem, (cudaStream_t)stream>>>(*p);
-    SANIC_LAUNCH_CHECK(ctx, "attn_fwd_f32");
+    // split the key axis over a cluster when the grid alone would not give every SM two CTAs
+    const long long ctas = (long long)grid.x * grid.y;
+    const int chunks = (p->kv_len + NT - 1) / NT;
+    int splits = (int)((2LL * ctx->sm_count + ctas - 1) / ctas);
+    if (splits > 8) splits = 8;
+    if (splits > chunks) splits = chunks;
+    if (splits < 1 || grid.y > 65535) splits = 1;
+    grid.z = splits;
+    size_t smem = ((size_t)bq * p->head_dim + (size_t)bq * NT + (size_t)bq * 10 + (size_t)bq * (2 + dv)) * sizeof(float);
+    cudaLaunchConfig_t cfg = {};
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = splits;
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = (cudaStream_t)stream;
+    cfg.attrs = attr; cfg.numAttrs = 1;
+    cudaError_t e;
+    if (dv == 32) e = cudaLaunchKernelEx(&cfg, attn_fwd_f32_kernel<32>, *p);
+    else if (dv == 64) e = cudaLaunchKernelEx(&cfg, attn_fwd_f32_kernel<64>, *p);
+    else e = cudaLaunchKernelEx(&cfg, attn_fwd_f32_kernel<128>, *p);
+    if (e != cudaSuccess) return sanic_fail(ctx, SANIC_ERR_CUDA, std::string("attn_fwd_f32: ") + cudaGetErrorString(e));
     return SANIC_OK;
 }
