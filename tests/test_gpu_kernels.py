@@ -116,6 +116,38 @@ def test_attn_f32_shapes_and_masks(dev, shape, mode):
     assert nerr(got.cpu().numpy(), exp) <= F32_TOL
 
 
+@pytest.mark.parametrize("mode", ["plain", "causal", "window", "mask"])
+@pytest.mark.parametrize("L,S", [(37, 1000), (600, 600), (5, 2100)])
+def test_attn_f32_keys_split_over_a_cluster(dev, mode, L, S):
+    # few (row block, head) CTAs and several 256-key chunks: the key axis is split over a cluster of up to 8 CTAs and the
+    # partial (m, l, o) merge in rank order through distributed shared memory; ragged last chunk, rows whose visible
+    # range ends before a CTA's share (its partial is the identity), a window that starts inside a later chunk
+    if mode in ("causal", "window"):
+        S = L if L > 256 else 600
+        L = S
+    E, Ev = 24, 40
+    q = orc.round_to(orc.DT_F32, normal(11 + L, 1, 2, L, E))
+    k = orc.round_to(orc.DT_F32, normal(12 + S, 1, 1, S, E))
+    v = orc.round_to(orc.DT_F32, normal(13 + S, 1, 1, S, Ev))
+    scale = 0.3
+    tq, tk, tv = f32t(q, dev), f32t(k, dev), f32t(v, dev)
+    if mode == "plain":
+        exp = orc.sdpa(q, k, v, scale=scale, enable_gqa=True)
+        got = dev.attn_fwd_f32(tq, tk, tv, scale=scale)
+    elif mode == "causal":
+        exp = orc.sdpa(q, k, v, is_causal=True, scale=scale, enable_gqa=True)
+        got = dev.attn_fwd_f32(tq, tk, tv, causal=True, scale=scale)
+    elif mode == "window":
+        exp = orc.sdpa_window(q, k, v, 300, scale=scale)
+        got = dev.attn_fwd_f32(tq, tk, tv, window=300, scale=scale)
+    else:
+        m = orc.round_to(orc.DT_F32, normal(14 + S, L, S))
+        m[:, S // 2:S // 2 + 300] = -np.inf            # a whole chunk's worth of keys masked out for every row
+        exp = orc.sdpa(q, k, v, mask=m, scale=scale, enable_gqa=True)
+        got = dev.attn_fwd_f32(tq, tk, tv, mask=f32t(m, dev), scale=scale)
+    assert nerr(got.cpu().numpy(), exp) <= F32_TOL
+
+
 def test_attn_f32_rejects_bad_arguments(dev):
     from sanic_b200 import RunError
     q = torch.zeros(1, 3, 2, 4, device=dev.torch_device)
