@@ -286,7 +286,7 @@ __device__ __forceinline__ void gemv_tile(const uint16_t* __restrict__ x, int ba
             wr[mI][0] = W + (size_t)wrow0 * K;
             wr[mI][1] = W + (size_t)wrow1 * K;
         }
-        constexpr int U = DUAL ? 2 : 4;
+        constexpr int U = (DUAL || NT == 2) ? 2 : 4;     // 64-blocks in flight per warp: what 128 registers hold without spilling
         for (int blk = b0; blk < b1; blk += U) {
             const int nb = min(U, b1 - blk);      // uniform across the warp
             uint4 a[U][NM][2][2];
@@ -299,8 +299,10 @@ __device__ __forceinline__ void gemv_tile(const uint16_t* __restrict__ x, int ba
                     for (int mI = 0; mI < NM; ++mI)
 #pragma unroll
                         for (int r = 0; r < 2; ++r) {
-                            a[u][mI][r][0] = ldg_stream16(wr[mI][r] + kb + t * 8);
-                            a[u][mI][r][1] = ldg_stream16(wr[mI][r] + kb + 32 + t * 8);
+                            // k permutation: thread t owns 16 consecutive k of the 64-block (two 16-byte loads side by side),
+                            // so the four threads of a row read one whole 128-byte line; the activations use the same one
+                            a[u][mI][r][0] = ldg_stream16(wr[mI][r] + kb + t * 16);
+                            a[u][mI][r][1] = ldg_stream16(wr[mI][r] + kb + t * 16 + 8);
                         }
                 }
             }
@@ -310,8 +312,8 @@ __device__ __forceinline__ void gemv_tile(const uint16_t* __restrict__ x, int ba
                     int kb = (blk + u) * 64;
 #pragma unroll
                     for (int j = 0; j < NT; ++j) {
-                        xb[u][j][0] = load_x8<NORM, PERSIST>(xrow[j], xf[j], gam, den[j], kb + t * 8, xok[j]);
-                        xb[u][j][1] = load_x8<NORM, PERSIST>(xrow[j], xf[j], gam, den[j], kb + 32 + t * 8, xok[j]);
+                        xb[u][j][0] = load_x8<NORM, PERSIST>(xrow[j], xf[j], gam, den[j], kb + t * 16, xok[j]);
+                        xb[u][j][1] = load_x8<NORM, PERSIST>(xrow[j], xf[j], gam, den[j], kb + t * 16 + 8, xok[j]);
                     }
                 }
             }
