@@ -273,6 +273,33 @@ class LlamaMachine:
         self.dev._check(self.dev.lib.sanic_program_stage_times(self.prog, st, buf, cap, C.byref(n)), "program_stage_times")
         return [buf[i] for i in range(n.value)]
 
+    def generate(self, prompts, new_tokens: int):
+        """Greedy decoding (the loop of examples/llama3_2.rs:577-664): `prompts` is one equal-length list of token ids per
+        batch row. The prompt is consumed one position per step through the same decode step (decode equals prefill,
+        tests/decode.rs:121-204: the model's prediction is simply replaced by the next prompt token), then `new_tokens`
+        steps run back to back on the device, each feeding its argmax to the next with no host round trip.
+        Returns an int array [batch, new_tokens]."""
+        import numpy as np
+        prompts = np.asarray(prompts, dtype=np.int32)
+        if prompts.ndim != 2 or prompts.shape[0] != self.batch or prompts.shape[1] < 1:
+            raise RunError("generate: one equal-length, non-empty prompt per batch row")
+        n = prompts.shape[1]
+        if n + new_tokens > self.ctx:
+            raise RunError(f"generate: {n} prompt + {new_tokens} new tokens exceed the cache extent {self.ctx}")
+        for pos in range(n - 1):
+            self.set_state(prompts[:, pos], pos)
+            self.step()
+        self.set_state(prompts[:, n - 1], n - 1)
+        out = np.zeros((self.batch, new_tokens), dtype=np.int32)
+        history = torch.empty(new_tokens, self.batch, dtype=torch.int32, device=self.dev.torch_device)
+        with torch.cuda.stream(self.stream):
+            for i in range(new_tokens):
+                self.step()
+                history[i].copy_(self.tokens, non_blocking=True)      # same stream: ordered after the step that wrote it
+        self.sync()
+        out[:] = history.cpu().numpy().T
+        return out
+
     def sync(self):
         self.stream.synchronize()
 

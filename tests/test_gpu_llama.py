@@ -128,3 +128,24 @@ def test_full_architecture_decode_steps(dev):
     """Llama-3.2-1B architecture (16 layers, hidden 2048, vocab 128256): a few greedy steps against the oracle."""
     from sanic_b200 import llama
     run_pair(dev, llama.LLAMA_3_2_1B, ctx=64, batch=1, w4=False, steps=3, prefill=8, seed=9)
+
+
+def test_generate_matches_manual_stepping(dev):
+    # the greedy loop: prompt consumed through the decode step, then device-side feedback only
+    from sanic_b200 import llama
+    w = llama.random_weights(SMALL, 21, dev.torch_device)
+    prompts = np.array([[5, 17, 900, 3], [1, 2, 3, 4]], dtype=np.int32)
+    m = llama.LlamaMachine(dev, SMALL, w, ctx=64, batch=2)
+    got = m.generate(prompts, 10)
+    m2 = llama.LlamaMachine(dev, SMALL, w, ctx=64, batch=2)
+    for pos in range(3):
+        m2.set_state(prompts[:, pos], pos)
+        m2.step()
+    m2.set_state(prompts[:, 3], 3)
+    want = []
+    for _ in range(10):
+        m2.step()
+        want.append(m2.read_tokens())
+    assert got.tolist() == np.array(want).T.tolist()
+    with pytest.raises(llama.RunError):
+        m.generate(prompts, 100)
