@@ -249,6 +249,9 @@ class LlamaMachine:
     def set_state(self, tokens, position: int):
         if position < 0 or position >= self.ctx:
             raise RunError(f"position {position} is outside the cache extent {self.ctx}")
+        # steps are asynchronous on the machine's own stream: a step still in flight would write its token and its
+        # advanced position AFTER the values set here
+        self.sync()
         self.tokens.copy_(torch.as_tensor(tokens, dtype=torch.int32).to(self.dev.torch_device))
         self.position.fill_(position)
         torch.cuda.synchronize(self.dev.torch_device)
@@ -308,6 +311,7 @@ class LlamaMachine:
         return self.tokens.cpu().numpy().copy()
 
     def load_caches(self, k_list, v_list):
+        self.sync()      # a step in flight still writes its cache row
         for l in range(self.cfg["layers"]):
             self.kcache[l].copy_(k_list[l])
             self.vcache[l].copy_(v_list[l])
