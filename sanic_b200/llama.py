@@ -126,9 +126,11 @@ class LlamaMachine:
                                     [math.exp(i * (-math.log(cfg.get("theta", ROPE_THETA)) / (D // 2))) for i in range(D // 2)],
                                     ctx)
         tiles = (ctx + 63) // 64
-        # chunks of the key axis per (batch, kv head): about 64 CTAs in all (measured best at ctx ~1k: 8 chunks at
-        # batch 1, 1 at batch 16), at least 2 tiles of 64 keys per chunk
-        self.n_splits = max(1, min(max(1, tiles // 2), -(-64 // (B * Hkv))))
+        # chunks of the key axis per (batch, kv head): about 64 CTAs in all, and two chunks while the (batch, kv head)
+        # pairs alone do not fill the SMs (measured at ctx ~1k: 8 chunks best at batch 1; at batch 16 two chunks give
+        # 1.251 ms/step against 1.298 with one and 1.303 with four); at least 2 tiles of 64 keys per chunk
+        want = max(-(-64 // (B * Hkv)), 2 if B * Hkv <= 148 else 1)
+        self.n_splits = max(1, min(max(1, tiles // 2), want))
         # the machine owns its scratch: two machines stepping on different streams must not share one
         self.partials = z((dev.lib.sanic_attn_decode_scratch_bytes(B, Hq, D, self.n_splits) // 4,), torch.float32)
         self.amax_scratch = z((B * 2 * 256,), torch.float32)
