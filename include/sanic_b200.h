@@ -165,6 +165,12 @@ typedef struct {
     int32_t out_dtype;  /* SANIC_BF16 or SANIC_F32 */
 } sanic_gemm_rmsnorm_params;
 int32_t sanic_gemm_rmsnorm(sanic_ctx* ctx, const sanic_gemm_rmsnorm_params* p, void* stream);
+/* For weights that are bound once (a stateful program, src/graph.rs:231-356): w_out = bf16(W * g) along K, the
+ * rewrite sum (x*g)*W = sum x*(g*W). sanic_gemm_rmsnorm with gamma == NULL then takes w_out as W: the activations go
+ * to the tensor core as loaded and only sum x^2 is taken from them, which removes the per-stage transform from the
+ * pipeline's latency. One factor is rounded to bf16 either way (x*g there, g*W here). */
+int32_t sanic_gemm_prescale_weights(sanic_ctx* ctx, const void* gamma, const void* w, void* w_out, int32_t N, int32_t K,
+                                    int32_t w_is_nk, void* stream);
 
 /* ── K2c / plain contraction at decode batch sizes: y[b,o] = sum_k x[b,k] * W[o,k].
  *    Weights bf16, or int4 nibbles (q+8, low nibble = even element, src/emit_metal.rs:179-181)

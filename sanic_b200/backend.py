@@ -193,16 +193,28 @@ class CudaDevice:
         return (out, car) if return_carrier else out
 
     # ── K2b: deferred-normaliser contraction ──
+    def gemm_prescale_weights(self, gamma, w, w_is_nk=True):
+        """bf16(W * g) along K, for weights that are bound once; pass the result to gemm_rmsnorm with gamma=None."""
+        for n, t in (("gamma", gamma), ("w", w)):
+            self._on_device(n, t, torch.bfloat16)
+        N, K = (w.shape[0], w.shape[1]) if w_is_nk else (w.shape[1], w.shape[0])
+        if gamma.shape[0] != K:
+            raise RunError("gemm_prescale_weights: gamma must have one entry per contraction index")
+        out = torch.empty_like(w)
+        self._check(self.lib.sanic_gemm_prescale_weights(self.h, _ptr(gamma), _ptr(w), _ptr(out), N, K, int(w_is_nk), self.stream()),
+                    "gemm_prescale_weights")
+        return out
+
     def gemm_rmsnorm(self, x, gamma, w, eps=1e-5, w_is_nk=True, out_dtype=torch.bfloat16):
-        for n, t in (("x", x), ("gamma", gamma), ("w", w)):
+        for n, t in (("x", x), ("w", w)) + ((("gamma", gamma),) if gamma is not None else ()):
             self._on_device(n, t, torch.bfloat16)
         M, K = x.shape
         N = w.shape[0] if w_is_nk else w.shape[1]
-        if (w.shape[1] if w_is_nk else w.shape[0]) != K or gamma.shape[0] != K:
+        if (w.shape[1] if w_is_nk else w.shape[0]) != K or (gamma is not None and gamma.shape[0] != K):
             raise RunError("gemm_rmsnorm: contraction extents must match")
         y = self.empty((M, N), out_dtype)
         p = abi.GemmRmsnormParams()
-        p.x, p.gamma, p.w, p.y = x.data_ptr(), gamma.data_ptr(), w.data_ptr(), y.data_ptr()
+        p.x, p.gamma, p.w, p.y = x.data_ptr(), (gamma.data_ptr() if gamma is not None else None), w.data_ptr(), y.data_ptr()
         p.M, p.N, p.K, p.w_is_nk, p.eps = M, N, K, int(w_is_nk), float(eps)
         p.out_dtype = abi.BF16 if out_dtype == torch.bfloat16 else abi.F32
         self._check(self.lib.sanic_gemm_rmsnorm(self.h, C.byref(p), self.stream()), "gemm_rmsnorm")

@@ -429,7 +429,8 @@ __device__ __forceinline__ void umma2_commit(uint32_t cluster_addr) {
 __global__ void __launch_bounds__(P_NTHREADS, 1)
 gemm_rmsnorm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                          const __grid_constant__ CUtensorMap map_y, const uint16_t* __restrict__ gamma, void* __restrict__ y,
-                         int M, int N, int K, int w_is_nk, float eps, int out_dtype, int* err, int gamma_bytes, int bulk_store) {
+                         int M, int N, int K, int w_is_nk, float eps, int out_dtype, int* err, int gamma_bytes, int bulk_store,
+                         int prescaled) {
     extern __shared__ unsigned char smem_dyn[];
     const uint32_t raw = smem_u32(smem_dyn);
     const uint32_t base = (raw + 1023u) & ~1023u;
@@ -449,7 +450,7 @@ gemm_rmsnorm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < PA_SLOTS; ++s) mbar_init(&sh->full_a[s], 1);
-        for (int s = 0; s < PB_SLOTS; ++s) { mbar_init(&sh->full_b[s], 1); mbar_init(&sh->ready[s], 16); mbar_init(&sh->empty[s], 1); }
+        for (int s = 0; s < PB_SLOTS; ++s) { mbar_init(&sh->full_b[s], 1); mbar_init(&sh->ready[s], 16); mbar_init(&sh->empty[s], prescaled ? 9 : 1); }
         for (int a = 0; a < 2; ++a) {
             mbar_init(&sh->tmem_full[a], 1); mbar_init(&sh->tmem_empty[a], 16);
             mbar_init(&sh->ss_full[a], 16); mbar_init(&sh->ss_empty[a], 8);
@@ -458,7 +459,8 @@ gemm_rmsnorm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
         sh->tmem_base = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    for (int i = threadIdx.x; i < kblocks * BK; i += P_NTHREADS) gsm[i] = (i < K) ? gamma[i] : (uint16_t)0;
+    if (!prescaled)
+        for (int i = threadIdx.x; i < kblocks * BK; i += P_NTHREADS) gsm[i] = (i < K) ? gamma[i] : (uint16_t)0;
     __syncthreads();
     if (warp == 3) {
         // one warp of EACH CTA of the pair allocates (all 512 columns, so both get base 0)
@@ -578,6 +580,29 @@ gemm_rmsnorm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                 ok = mbar_wait_p<false>(&sh->full_a[stage], phase, sh, err, 24);
                 if (!ok) break;
                 unsigned char* arow = aligned + stage * A_BYTES + row * 128;
+                if (prescaled) {
+                    // The weights already carry g: the MMA reads x as the TMA left it, so the stage is vouched for BEFORE
+                    // this warp reads it (the transform leaves the ring's latency cycle); what remains here is sum x^2,
+                    // and the stage's empty barrier also counts these 8 warps so the producer cannot overtake the read.
+                    ok = mbar_wait_p<false>(&sh->full_b[stage], phase, sh, err, 31);
+                    if (!ok) break;
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive_cluster_relaxed(map_to_rank(smem_u32(&sh->ready[stage]), 0));
+#pragma unroll
+                    for (int c4 = 0; c4 < 4; ++c4) {
+                        const int c = half * 4 + c4;
+                        const uint4 v = *(const uint4*)(arow + ((c ^ (row & 7)) << 4));
+                        const uint32_t xs[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            const float x0 = bf16lo(xs[j]), x1 = bf16hi(xs[j]);
+                            ss = fmaf(x0, x0, ss); ss = fmaf(x1, x1, ss);
+                        }
+                    }
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&sh->empty[stage]);
+                    continue;
+                }
 #pragma unroll
                 for (int c4 = 0; c4 < 4; ++c4) {
                     const int c = half * 4 + c4;
@@ -734,9 +759,48 @@ int32_t encode_2d(sanic_ctx* ctx, CUtensorMap* map, const void* ptr, uint64_t in
 }
 }  // namespace
 
+namespace {
+// W'[n, k] = bf16(W[n, k] * g[k]) (bf16 x bf16 is exact in f32, one rounding): eight elements per thread.
+__global__ void __launch_bounds__(256) prescale_kernel(const uint4* __restrict__ w, const uint16_t* __restrict__ gamma, uint4* __restrict__ out,
+                                                       size_t n8, int K, int N, int w_is_nk) {
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n8; i += (size_t)gridDim.x * blockDim.x) {
+        const uint4 v = w[i];
+        uint32_t xs[4] = {v.x, v.y, v.z, v.w};
+        if (w_is_nk) {                       // [N, K]: eight consecutive k of one row
+            const int k = (int)((i * 8) % (size_t)K);
+            const uint4 g = *(const uint4*)(gamma + k);
+            const uint32_t gs[4] = {g.x, g.y, g.z, g.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(xs[j]) : "r"(xs[j]), "r"(gs[j]));
+        } else {                             // [K, N]: eight consecutive n of one k
+            const int k = (int)((i * 8) / (size_t)N);
+            const uint32_t g2 = (uint32_t)gamma[k] * 0x00010001u;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(xs[j]) : "r"(xs[j]), "r"(g2));
+        }
+        out[i] = make_uint4(xs[0], xs[1], xs[2], xs[3]);
+    }
+}
+}  // namespace
+
+extern "C" int32_t sanic_gemm_prescale_weights(sanic_ctx* ctx, const void* gamma, const void* w, void* w_out, int32_t N, int32_t K,
+                                               int32_t w_is_nk, void* stream) {
+    if (!ctx) return SANIC_ERR_INVALID;
+    SANIC_REQUIRE(ctx, gamma && w && w_out && N > 0 && K > 0, "gemm_prescale_weights: bad arguments");
+    SANIC_REQUIRE(ctx, K % 8 == 0 && N % 8 == 0, "gemm_prescale_weights: K and N must be multiples of 8");
+    SANIC_REQUIRE(ctx, ((uintptr_t)w % 16) == 0 && ((uintptr_t)w_out % 16) == 0 && ((uintptr_t)gamma % 16) == 0,
+                  "gemm_prescale_weights: tensors must be 16-byte aligned");
+    sanic_set_device(ctx);
+    const size_t n8 = (size_t)N * K / 8;
+    const int blocks = (int)((n8 + 255) / 256 < (size_t)(8 * ctx->sm_count) ? (n8 + 255) / 256 : (size_t)(8 * ctx->sm_count));
+    prescale_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>((const uint4*)w, (const uint16_t*)gamma, (uint4*)w_out, n8, K, N, w_is_nk);
+    SANIC_LAUNCH_CHECK(ctx, "gemm_prescale_weights");
+    return SANIC_OK;
+}
+
 extern "C" int32_t sanic_gemm_rmsnorm(sanic_ctx* ctx, const sanic_gemm_rmsnorm_params* p, void* stream) {
     if (!ctx || !p) return SANIC_ERR_INVALID;
-    SANIC_REQUIRE(ctx, p->x && p->gamma && p->w && p->y, "gemm_rmsnorm: null tensor");
+    SANIC_REQUIRE(ctx, p->x && p->w && p->y, "gemm_rmsnorm: null tensor");
     SANIC_REQUIRE(ctx, p->M > 0 && p->N > 0 && p->K > 0, "gemm_rmsnorm: empty extent");
     SANIC_REQUIRE(ctx, p->K % 8 == 0 && p->N % 8 == 0, "gemm_rmsnorm: K and N must be multiples of 8 (16-byte rows)");
     SANIC_REQUIRE(ctx, p->K <= MAX_K, "gemm_rmsnorm: K is limited to 8192");
@@ -756,7 +820,9 @@ extern "C" int32_t sanic_gemm_rmsnorm(sanic_ctx* ctx, const sanic_gemm_rmsnorm_p
     // pairs; smaller problems keep the one-CTA 128 x 256 tile. SANIC_GEMM_PAIR=0/1 forces the choice (tests, A/B timing).
     const int pair_tiles = ((p->M + 2 * BM - 1) / (2 * BM)) * ((p->N + BN - 1) / BN);
     const char* force = getenv("SANIC_GEMM_PAIR");
-    const bool use_pair = force ? (force[0] == '1') : (p->M >= 4 * BM && pair_tiles >= ctx->sm_count / 2);
+    // gamma == NULL: the weights were pre-scaled with sanic_gemm_prescale_weights (only the pair kernel has that form)
+    const bool prescaled = (p->gamma == nullptr);
+    const bool use_pair = prescaled || (force ? (force[0] == '1') : (p->M >= 4 * BM && pair_tiles >= ctx->sm_count / 2));
     if (use_pair) {
         // the 256 x 256 tile on a pair of SMs: B's map has a 128-row box (this CTA's half)
         if (p->w_is_nk) {
@@ -790,7 +856,7 @@ extern "C" int32_t sanic_gemm_rmsnorm(sanic_ctx* ctx, const sanic_gemm_rmsnorm_p
         cfg.gridDim = dim3(2 * pairs);
         cudaError_t le = cudaLaunchKernelEx(&cfg, gemm_rmsnorm_pair_kernel, map_a, map_b, map_y, (const uint16_t*)p->gamma, p->y, (int)p->M,
                                             (int)p->N, (int)p->K, (int)p->w_is_nk, p->eps, (int)p->out_dtype, ctx->status_dev,
-                                            gamma_bytes, bulk_store);
+                                            gamma_bytes, bulk_store, prescaled ? 1 : 0);
         if (le != cudaSuccess) return sanic_fail(ctx, SANIC_ERR_CUDA, std::string("gemm_rmsnorm (pair): ") + cudaGetErrorString(le));
         return SANIC_OK;
     }

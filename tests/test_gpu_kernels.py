@@ -493,6 +493,26 @@ def test_gemm_rmsnorm_both_tile_forms(dev, form, monkeypatch):
     _gemm_case(dev, 512, 8192, 256, True)                                   # the longest K: staging does not fit, direct stores
 
 
+@pytest.mark.parametrize("w_is_nk", [True, False])
+def test_gemm_rmsnorm_with_prescaled_weights(dev, w_is_nk):
+    # weights bound once: W' = bf16(W * g) along K, then the contraction with gamma = None; the rewrite
+    # sum (x*g)*W = sum x*(g*W) rounds g*W instead of x*g, the same one bf16 rounding per term
+    for M, K, N in ((128, 256, 256), (200, 320, 264), (1024, 512, 2048)):
+        x, xv = bf16t(normal(91, M, K), dev)
+        g, gv = bf16t(1.0 + 0.1 * normal(92, K), dev)
+        w, wv = bf16t(0.02 * normal(93, *((N, K) if w_is_nk else (K, N))), dev)
+        ws = dev.gemm_prescale_weights(g, w, w_is_nk=w_is_nk)
+        scaled = orc.round_to(orc.DT_BF16, wv * (gv[None, :] if w_is_nk else gv[:, None]))
+        assert np.array_equal(ws.float().cpu().numpy().astype(np.float64), scaled)          # the pre-scale is one exact RNE
+        y = dev.gemm_rmsnorm(x, None, ws, eps=1e-5, w_is_nk=w_is_nk)
+        dev.sync()
+        exp = orc.rmsnorm_gemm(xv, gv, wv, eps=1e-5, w_is_nk=w_is_nk)
+        assert nerr(y.float().cpu().numpy(), exp) <= BF16_TOL
+        # against the oracle fed the pre-scaled weights (gamma = 1) the only differences are accumulation order and the output rounding
+        exp2 = orc.rmsnorm_gemm(xv, np.ones(K), scaled, eps=1e-5, w_is_nk=w_is_nk)
+        assert nerr(y.float().cpu().numpy(), exp2) <= 2.0 ** -7
+
+
 # ───────────────────────── prefill online-softmax fold (tcgen05) ─────────────────────────
 def _flash_case(dev, B, Hq, Hkv, Lq, Lk, mode, window=0, seed=91):
     q, qv = bf16t(normal(seed, B, Hq, Lq, 64), dev)
