@@ -39,7 +39,8 @@ enum {
 };
 
 /* Storage widths (src/scalar.rs:181-201). */
-enum { SANIC_F32 = 1, SANIC_F16 = 2, SANIC_BF16 = 3, SANIC_U32 = 4, SANIC_I4 = 5 };
+enum { SANIC_F32 = 1, SANIC_F16 = 2, SANIC_BF16 = 3, SANIC_U32 = 4, SANIC_I4 = 5,
+       SANIC_F64 = 6 /* an arithmetic width only (accum_dtype); no buffer is stored at it */ };
 
 /* ── context and memory: replaces MetalDevice open/alloc/read (src/metal.rs:149-490) ── */
 int32_t sanic_cuda_open(int32_t ordinal, sanic_ctx** out);
@@ -66,6 +67,12 @@ int32_t sanic_upload(sanic_ctx* ctx, void* dst_dev, const void* src_host, size_t
 int32_t sanic_download(sanic_ctx* ctx, void* dst_host, const void* src_dev, size_t bytes, void* stream);
 int32_t sanic_memset(sanic_ctx* ctx, void* dptr, int32_t byte, size_t bytes, void* stream);
 int32_t sanic_sync(sanic_ctx* ctx, void* stream);
+/* Host-side failure injection (the reference surfaces device failures as Err(String) from run_graph_timed,
+ * src/metal.rs:686-705; there is no device-side injector here): writes `code` into the context's status word exactly as a
+ * kernel whose bounded wait ran out would, so the next sanic_sync returns the matching error and clears the word.
+ * Codes: 1-29 mbarrier waits of the tensor-core kernels, 31-33 persistent step (grid barrier, ring full, ring empty),
+ * 41+q peer flag of rank q, 51 gather index, 52 decode length clamp. No kernel is launched and nothing on the device is disturbed. */
+int32_t sanic_status_inject(sanic_ctx* ctx, int32_t code);
 
 /* ── carrier structure: what the emitter keys kernel choice on (src/derive.rs:519-530) ── */
 enum { SANIC_SLOT_PLAIN_ADD = 1, SANIC_SLOT_PLAIN_MAX = 2, SANIC_SLOT_PLAIN_MIN = 3,
@@ -97,6 +104,10 @@ typedef struct {
     float scale;
     const float* mask;                     /* optional additive mask [q_len, kv_len] (f32 path only) */
     int32_t out_dtype;                     /* SANIC_F32 or SANIC_BF16 */
+    int32_t accum_dtype;                   /* f32 path only. 0 / SANIC_F32: f32 arithmetic. SANIC_F64: scores, exponentials and
+                                              the (m, l, o) carrier in f64, rounded once at the store: the plain relative error
+                                              against the f64 interpreter (src/interp.rs:270-518) stays at f32 rounding level even
+                                              where an output is a near cancellation of its terms */
 } sanic_attn_params;
 /* f32 storage, f32 CUDA-core arithmetic: q [B,Hq,L,E], k [B,Hkv,S,E], v [B,Hkv,S,Ev], out [B,Hq,L,Ev]. */
 int32_t sanic_attn_fwd_f32(sanic_ctx* ctx, const sanic_attn_params* p, void* stream);
@@ -125,6 +136,10 @@ typedef struct {
     float* carrier_out;       /* optional [B*Hq, 2 + D] f32: merged raw accumulator (m natural-log units, l, o) */
     void* out;                /* optional projected output [B, Hq, D] */
     int32_t out_dtype;        /* SANIC_F32 or SANIC_BF16 */
+    int32_t kv_cap;           /* extent of the key axis of k and v (the cache's sequence extent). Required (>= 1) with
+                                 kv_len_dev, checked against the strides on the host; the kernel never reads a key at or
+                                 beyond it: a device-side length outside [1, kv_cap] is clamped and the next sanic_sync
+                                 fails with SANIC_ERR_INVALID (code 52). 0 with a host kv_len = unchecked */
 } sanic_decode_params;
 int32_t sanic_attn_decode_splitkv(sanic_ctx* ctx, const sanic_decode_params* p, void* stream);
 size_t sanic_attn_decode_scratch_bytes(int32_t batch, int32_t q_heads, int32_t head_dim, int32_t n_splits);
@@ -215,6 +230,11 @@ int32_t sanic_rmsnorm(sanic_ctx* ctx, const float* x, const void* gamma_bf16, in
 /* Embedding gather: out[b,:] = widen(table[token[b],:]) (Stage::Gather, src/partition.rs:2938-2946). */
 int32_t sanic_embed_gather(sanic_ctx* ctx, const void* table_bf16, const int32_t* tokens, int32_t batch, int32_t hidden,
                            int32_t vocab, float* out, void* stream);
+/* The same gather from an int4 group-quantised table (config 4's int4 variant quantises the tied embedding too):
+ * table [vocab, hidden/2] nibbles (q + 8, low nibble = even element, src/emit_metal.rs:179-181), scales [vocab,
+ * hidden/group] bf16; out[b, i] = (nibble - 8) * scale[token[b], i / group] (the widened value an I4 input means). */
+int32_t sanic_embed_gather_w4(sanic_ctx* ctx, const void* table_i4, const void* scales_bf16, const int32_t* tokens, int32_t batch,
+                              int32_t hidden, int32_t vocab, int32_t group, float* out, void* stream);
 /* cos/sin table for RoPE: table[pos][f] = (cos(pos*inv_freq[f]), sin(pos*inv_freq[f])), angles and
  * sincos evaluated in f64 on the device, stored f32. inv_freq is a HOST array of n_freq doubles: the
  * schedule (plain theta^(-i/F) of src/nn.rs:197-199, or the llama3 blend of examples/llama3_2.rs:95-107)
@@ -338,7 +358,8 @@ typedef struct {
         sanic_decode_params decode;
         struct { const float* x; int32_t rows, n; uint32_t* out; float* scratch; } argmax;
         struct { const float* x; const void* gamma; int32_t rows, n; float eps; void* out; } rmsnorm;
-        struct { const void* table; const int32_t* tokens; int32_t batch, hidden, vocab; float* out; } embed;
+        struct { const void* table; const int32_t* tokens; int32_t batch, hidden, vocab; float* out;
+                 const void* scales; int32_t table_dtype /* 0 / SANIC_BF16, or SANIC_I4 with scales */, group; } embed;
         sanic_rope_cache_params rope_cache;
         struct { int32_t* position; } advance;
         struct { sanic_generic_kernel* kernel; const void* buffers[16]; int32_t n_buffers; void* out; } generic;   /* a compiled fallback kernel */
@@ -385,6 +406,10 @@ typedef struct {
     int32_t rank, nranks;        /* 1..8 */
     void* buffers[8];            /* every rank's exchange buffer as mapped in this process */
     uint32_t epoch;
+    uint32_t spin_limit;         /* polls of a peer's flag before the wait gives up with SANIC_ERR_TIMEOUT (code 41 + rank);
+                                    0 = the default, about one second. Ranks are assumed to launch their steps within that
+                                    skew of each other; a serving loop with long host-side gaps raises it or runs a host
+                                    barrier first */
 } sanic_peer_exchange;
 size_t sanic_peer_exchange_bytes(int32_t rows /* batch * q_heads */, int32_t head_dim, int32_t nranks);
 int32_t sanic_ipc_export(sanic_ctx* ctx, const void* dptr, uint8_t handle_out[64]);

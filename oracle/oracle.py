@@ -295,7 +295,7 @@ class _LlamaCfg(C.Structure):
     _fields_ = [(n, C.c_uint64) for n in ("vocab", "layers", "hidden", "q_heads", "kv_heads", "head_dim", "ffn",
                                           "ctx", "batch")] + \
                [("w4", C.c_int32), ("group", C.c_int32), ("round_acts", C.c_int32), ("llama3_rope", C.c_int32),
-                ("eps", C.c_double), ("theta", C.c_double)]
+                ("w4_head", C.c_int32), ("norm_store", C.c_int32), ("eps", C.c_double), ("theta", C.c_double)]
 
 
 _PP = C.POINTER(C.c_void_p)
@@ -304,7 +304,7 @@ _PP = C.POINTER(C.c_void_p)
 class _LlamaWeights(C.Structure):
     _fields_ = [("embed", C.c_void_p), ("final_norm", C.c_void_p), ("attn_norm", _PP), ("mlp_norm", _PP)] + \
                [(n, _PP) for n in ("wq", "wk", "wv", "wo", "wgate", "wup", "wdown",
-                                   "sq", "sk", "sv", "so", "sgate", "sup", "sdown")]
+                                   "sq", "sk", "sv", "so", "sgate", "sup", "sdown")] + [("sembed", C.c_void_p)]
 
 
 class Llama:
@@ -313,6 +313,8 @@ class Llama:
     `weights` maps names to numpy arrays: 'embed' [vocab, hidden] uint16 (bf16 bits), 'final_norm',
     and per layer lists 'attn_norm', 'mlp_norm', 'wq', 'wk', 'wv', 'wo', 'wgate', 'wup', 'wdown'
     (uint16 bf16 bits [out, in], or uint8 packed int4 when w4) and 'sq' ... 'sdown' (bf16 bits scales).
+    cfg['w4_head'] = 1: 'embed' is packed int4 [vocab, hidden/2] with 'sembed' [vocab, hidden/group] scales.
+    cfg['norm_store'] = 1: stored(bf16) sits on x*g and the RMSNorm division is deferred past each contraction.
     """
 
     def __init__(self, cfg: dict, weights: dict):
@@ -324,6 +326,8 @@ class Llama:
         c.group = int(cfg.get("group", 64))
         c.round_acts = int(cfg.get("round_acts", 1))
         c.llama3_rope = int(cfg.get("llama3_rope", 1))
+        c.w4_head = int(cfg.get("w4_head", 0))
+        c.norm_store = int(cfg.get("norm_store", 0))
         c.eps = float(cfg.get("eps", 1e-5))
         c.theta = float(cfg.get("theta", 500000.0))
         self.cfg = cfg
@@ -341,6 +345,8 @@ class Llama:
 
         w.embed = ptr(weights["embed"])
         w.final_norm = ptr(weights["final_norm"])
+        if c.w4_head:
+            w.sembed = ptr(weights["sembed"])
         for name in ("attn_norm", "mlp_norm", "wq", "wk", "wv", "wo", "wgate", "wup", "wdown"):
             setattr(w, name, ptrs(weights[name]))
         if c.w4:

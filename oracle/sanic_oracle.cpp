@@ -550,17 +550,29 @@ int orc_rmsnorm_gemm_carrier_split(const double* x, const double* gamma, const d
 void orc_w4_gemv(const uint8_t* packed, const double* scales, const double* x, size_t batch, size_t n_out, size_t K,
                  size_t group, double* y) {
     size_t G = K / group;
+    // Every (o, b) output adds its K terms in index order, as the interpreter's left fold does. The batch rows of
+    // one weight row are independent chains, so eight of them advance together: same values, shorter wall time.
 #pragma omp parallel for schedule(static)
-    for (size_t o = 0; o < n_out; ++o)
-        for (size_t b = 0; b < batch; ++b) {
-            double acc = 0.0;
-            for (size_t c = 0; c < K; ++c) {
-                size_t i = o * K + c;
-                double qv = (double)(int)((packed[i / 2] >> ((i & 1) * 4)) & 0xF) - 8.0;
-                acc = acc + (qv * x[b * K + c]) * scales[o * G + c / group];
-            }
-            y[b * n_out + o] = acc;
+    for (size_t o = 0; o < n_out; ++o) {
+        std::vector<double> qrow(K), srow(K);
+        for (size_t c = 0; c < K; ++c) {
+            size_t i = o * K + c;
+            qrow[c] = (double)(int)((packed[i / 2] >> ((i & 1) * 4)) & 0xF) - 8.0;
+            srow[c] = scales[o * G + c / group];
         }
+        for (size_t b0 = 0; b0 < batch; b0 += 8) {
+            size_t nb = batch - b0 < 8 ? batch - b0 : 8;
+            double acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+            if (nb == 8) {
+                for (size_t c = 0; c < K; ++c)
+                    for (size_t bb = 0; bb < 8; ++bb) acc[bb] = acc[bb] + (qrow[c] * x[(b0 + bb) * K + c]) * srow[c];
+            } else {
+                for (size_t c = 0; c < K; ++c)
+                    for (size_t bb = 0; bb < nb; ++bb) acc[bb] = acc[bb] + (qrow[c] * x[(b0 + bb) * K + c]) * srow[c];
+            }
+            for (size_t bb = 0; bb < nb; ++bb) y[(b0 + bb) * n_out + o] = acc[bb];
+        }
+    }
 }
 int orc_w4_gemv_carrier_split(const uint8_t* packed, const double* scales, const double* x, size_t batch, size_t n_out,
                               size_t K, size_t group, size_t blocks, double* y) {
@@ -582,13 +594,24 @@ int orc_w4_gemv_carrier_split(const uint8_t* packed, const double* scales, const
 
 // Dense bf16-weight matvec: y[b,o] = sum_k x[b,k] * W[o,k], weights given as bf16 bits.
 void orc_gemv_bf16w(const uint16_t* w, const double* x, size_t batch, size_t n_out, size_t K, double* y) {
+    // per (o, b): the K terms added in index order; eight batch rows advance together (independent chains)
 #pragma omp parallel for schedule(static)
-    for (size_t o = 0; o < n_out; ++o)
-        for (size_t b = 0; b < batch; ++b) {
-            double acc = 0.0;
-            for (size_t c = 0; c < K; ++c) acc = acc + x[b * K + c] * bf16_widen(w[o * K + c]);
-            y[b * n_out + o] = acc;
+    for (size_t o = 0; o < n_out; ++o) {
+        std::vector<double> wrow(K);
+        for (size_t c = 0; c < K; ++c) wrow[c] = bf16_widen(w[o * K + c]);
+        for (size_t b0 = 0; b0 < batch; b0 += 8) {
+            size_t nb = batch - b0 < 8 ? batch - b0 : 8;
+            double acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+            if (nb == 8) {
+                for (size_t c = 0; c < K; ++c)
+                    for (size_t bb = 0; bb < 8; ++bb) acc[bb] = acc[bb] + x[(b0 + bb) * K + c] * wrow[c];
+            } else {
+                for (size_t c = 0; c < K; ++c)
+                    for (size_t bb = 0; bb < nb; ++bb) acc[bb] = acc[bb] + x[(b0 + bb) * K + c] * wrow[c];
+            }
+            for (size_t bb = 0; bb < nb; ++bb) y[(b0 + bb) * n_out + o] = acc[bb];
         }
+    }
 }
 
 // eval(argmax(x, -1)) for rows x n: first maximal index (src/ir.rs:1402-1433).
@@ -657,6 +680,11 @@ struct OrcLlamaCfg {
     int32_t group;       // int4 group size along K
     int32_t round_acts;  // 1: stored(bf16) at projection inputs and q
     int32_t llama3_rope; // 1: llama3 frequency blend; 0: plain theta schedule
+    int32_t w4_head;     // 1: the tied embedding / lm_head table is int4 + bf16 scales too (`embed` packed, `sembed` scales)
+    int32_t norm_store;  // where stored(bf16) sits on a normed projection input (round_acts = 1):
+                         //   0: on rms_norm(x) itself, bf16((x*g)/sqrt(mean(x^2)+eps));
+                         //   1: on x*g, with the division deferred past the contraction (the defer-div carrier of
+                         //      tests/laws.rs:620-646: slots sum x^2 and sum bf16(x*g)*W, project = dot / sqrt(ss/n + eps))
     double eps, theta;
 };
 struct OrcLlamaWeights {  // per layer arrays of pointers
@@ -668,6 +696,7 @@ struct OrcLlamaWeights {  // per layer arrays of pointers
     const void* const* wgate; const void* const* wup; const void* const* wdown;
     const uint16_t* const* sq; const uint16_t* const* sk; const uint16_t* const* sv; const uint16_t* const* so;
     const uint16_t* const* sgate; const uint16_t* const* sup; const uint16_t* const* sdown;
+    const uint16_t* sembed;                // [vocab, hidden/group] bf16 scales of an int4 table (w4_head)
 };
 struct OrcLlama {
     OrcLlamaCfg cfg;
@@ -678,9 +707,9 @@ struct OrcLlama {
 };
 
 static void project(const OrcLlama* m, const void* w, const uint16_t* s, const std::vector<double>& x, size_t batch,
-                    size_t n_out, size_t K, std::vector<double>& y) {
+                    size_t n_out, size_t K, std::vector<double>& y, int force_w4 = -1) {
     y.assign(batch * n_out, 0.0);
-    if (m->cfg.w4) {
+    if (force_w4 >= 0 ? force_w4 != 0 : m->cfg.w4 != 0) {
         std::vector<double> sc((n_out * K) / m->cfg.group);
         orc_from_bf16_bits(s, sc.data(), sc.size());
         orc_w4_gemv((const uint8_t*)w, sc.data(), x.data(), batch, n_out, K, m->cfg.group, y.data());
@@ -690,6 +719,29 @@ static void project(const OrcLlama* m, const void* w, const uint16_t* s, const s
 }
 static void maybe_round(const OrcLlama* m, std::vector<double>& v) {
     if (m->cfg.round_acts) for (double& x : v) x = round_bf16(x);
+}
+// The normed input of a projection and the factor its outputs are still to be divided by.
+// norm_store 0: xn = stored(rms_norm(x, g)), den = 1. norm_store 1: xn = stored(x * g), den[b] = sqrt(mean(x^2) + eps):
+// the contraction runs on x*g and each output row is divided once afterwards (defer-div).
+static void normed_input(const OrcLlama* m, const std::vector<double>& x, const std::vector<double>& gamma, size_t B, size_t Hd,
+                         std::vector<double>& xn, std::vector<double>& den) {
+    xn.resize(B * Hd);
+    den.assign(B, 1.0);
+    if (m->cfg.norm_store == 0) {
+        orc_rms_norm(x.data(), gamma.data(), B, Hd, m->cfg.eps, xn.data());
+    } else {
+        for (size_t b = 0; b < B; ++b) {
+            double ss = 0.0;
+            for (size_t i = 0; i < Hd; ++i) ss = ss + x[b * Hd + i] * x[b * Hd + i];
+            den[b] = std::sqrt(ss * (1.0 / (double)Hd) + m->cfg.eps);
+            for (size_t i = 0; i < Hd; ++i) xn[b * Hd + i] = x[b * Hd + i] * gamma[i];
+        }
+    }
+    maybe_round(m, xn);
+}
+static void divide_rows(std::vector<double>& y, const std::vector<double>& den, size_t B, size_t n) {
+    for (size_t b = 0; b < B; ++b)
+        if (den[b] != 1.0) for (size_t i = 0; i < n; ++i) y[b * n + i] = y[b * n + i] / den[b];
 }
 
 OrcLlama* orc_llama_create(const OrcLlamaCfg* cfg, const OrcLlamaWeights* w) {
@@ -713,21 +765,29 @@ int orc_llama_step(OrcLlama* m, const int32_t* tokens_in, int64_t position, int3
     size_t B = c.batch, Hd = c.hidden, D = c.head_dim, Hq = c.q_heads, Hk = c.kv_heads, F = c.ffn, T = c.ctx;
     size_t rep = Hq / Hk;
     if ((size_t)position >= T) return 1;
-    std::vector<double> x(B * Hd), gamma(Hd), xn, q, k, v, tmp, att(B * Hd), proj, gate, up, h;
+    std::vector<double> x(B * Hd), gamma(Hd), xn, den, q, k, v, tmp, att(B * Hd), proj, gate, up, h;
     for (size_t b = 0; b < B; ++b) {  // Gather rounds its index (src/interp.rs:378-379)
         size_t tok = (size_t)std::llround((double)tokens_in[b]);
         if (tok >= c.vocab) return 2;
-        orc_from_bf16_bits(m->w.embed + tok * Hd, &x[b * Hd], Hd);
+        if (c.w4_head) {   // an I4 input means its widened values: (nibble - 8) * scale of its group
+            const uint8_t* packed = (const uint8_t*)m->w.embed;
+            for (size_t i = 0; i < Hd; ++i) {
+                size_t e = tok * Hd + i;
+                double qv = (double)(int)((packed[e / 2] >> ((e & 1) * 4)) & 0xF) - 8.0;
+                x[b * Hd + i] = qv * bf16_widen(m->w.sembed[tok * (Hd / c.group) + i / c.group]);
+            }
+        } else {
+            orc_from_bf16_bits(m->w.embed + tok * Hd, &x[b * Hd], Hd);
+        }
     }
     std::vector<double> pos(1, (double)position);
     for (size_t l = 0; l < c.layers; ++l) {
         orc_from_bf16_bits(m->w.attn_norm[l], gamma.data(), Hd);
-        xn.resize(B * Hd);
-        orc_rms_norm(x.data(), gamma.data(), B, Hd, c.eps, xn.data());
-        maybe_round(m, xn);
+        normed_input(m, x, gamma, B, Hd, xn, den);
         project(m, m->w.wq[l], c.w4 ? m->w.sq[l] : nullptr, xn, B, Hq * D, Hd, q);
         project(m, m->w.wk[l], c.w4 ? m->w.sk[l] : nullptr, xn, B, Hk * D, Hd, k);
         project(m, m->w.wv[l], c.w4 ? m->w.sv[l] : nullptr, xn, B, Hk * D, Hd, v);
+        divide_rows(q, den, B, Hq * D); divide_rows(k, den, B, Hk * D); divide_rows(v, den, B, Hk * D);
         // rope on q and k: rows are (batch, head), all at the shared position
         std::vector<double> posq(B * Hq, (double)position), posk(B * Hk, (double)position);
         tmp.resize(q.size()); orc_rope(q.data(), posq.data(), m->inv_freq.data(), B * Hq, D, tmp.data()); q = tmp;
@@ -773,10 +833,10 @@ int orc_llama_step(OrcLlama* m, const int32_t* tokens_in, int64_t position, int3
         project(m, m->w.wo[l], c.w4 ? m->w.so[l] : nullptr, attr, B, Hd, Hd, proj);
         for (size_t i = 0; i < B * Hd; ++i) x[i] = x[i] + proj[i];
         orc_from_bf16_bits(m->w.mlp_norm[l], gamma.data(), Hd);
-        orc_rms_norm(x.data(), gamma.data(), B, Hd, c.eps, xn.data());
-        maybe_round(m, xn);
+        normed_input(m, x, gamma, B, Hd, xn, den);
         project(m, m->w.wgate[l], c.w4 ? m->w.sgate[l] : nullptr, xn, B, F, Hd, gate);
         project(m, m->w.wup[l], c.w4 ? m->w.sup[l] : nullptr, xn, B, F, Hd, up);
+        divide_rows(gate, den, B, F); divide_rows(up, den, B, F);
         h.resize(B * F);
         for (size_t i = 0; i < B * F; ++i) {  // silu(g) * up  (src/ir.rs:1500-1509)
             double sig = 1.0 / (1.0 + std::exp(-gate[i]));
@@ -787,11 +847,9 @@ int orc_llama_step(OrcLlama* m, const int32_t* tokens_in, int64_t position, int3
         for (size_t i = 0; i < B * Hd; ++i) x[i] = x[i] + proj[i];
     }
     orc_from_bf16_bits(m->w.final_norm, gamma.data(), Hd);
-    xn.resize(B * Hd);
-    orc_rms_norm(x.data(), gamma.data(), B, Hd, c.eps, xn.data());
-    maybe_round(m, xn);
-    m->logits.assign(B * c.vocab, 0.0);
-    orc_gemv_bf16w(m->w.embed, xn.data(), B, c.vocab, Hd, m->logits.data());
+    normed_input(m, x, gamma, B, Hd, xn, den);
+    project(m, m->w.embed, c.w4_head ? m->w.sembed : nullptr, xn, B, c.vocab, Hd, m->logits, c.w4_head ? 1 : 0);
+    divide_rows(m->logits, den, B, c.vocab);
     std::vector<double> idx(B);
     orc_argmax(m->logits.data(), B, c.vocab, idx.data());
     for (size_t b = 0; b < B; ++b) tokens_out[b] = (int32_t)idx[b];

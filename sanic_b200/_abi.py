@@ -12,7 +12,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libsanic_b200.so")
 
 OK, ERR_INVALID, ERR_CUDA, ERR_UNSUPPORTED, ERR_TIMEOUT, ERR_NCCL, ERR_DTYPE, ERR_NOMEM = range(8)
-F32, F16, BF16, U32, I4 = 1, 2, 3, 4, 5
+F32, F16, BF16, U32, I4, F64 = 1, 2, 3, 4, 5, 6
 SLOT_PLAIN_ADD, SLOT_PLAIN_MAX, SLOT_PLAIN_MIN, SLOT_EXP_SHIFTED, SLOT_AT_EXTREMUM = 1, 2, 3, 4, 5
 KERNEL_NONE, KERNEL_ONLINE_SOFTMAX_FOLD, KERNEL_DEFERRED_NORM_CONTRACTION, KERNEL_PLAIN_CONTRACTION, \
     KERNEL_GROUPED_I4_CONTRACTION, KERNEL_EXTREMUM_INDEX = range(6)
@@ -41,11 +41,11 @@ class CarrierDesc(C.Structure):
 class AttnParams(C.Structure):
     _fields_ = [("q", vp), ("k", vp), ("v", vp), ("out", vp), ("batch", i32), ("q_heads", i32), ("kv_heads", i32),
                 ("q_len", i32), ("kv_len", i32), ("head_dim", i32), ("v_dim", i32), ("causal", i32), ("window", i32),
-                ("scale", f32), ("mask", vp), ("out_dtype", i32)]
+                ("scale", f32), ("mask", vp), ("out_dtype", i32), ("accum_dtype", i32)]
 
 
 class PeerExchange(C.Structure):
-    _fields_ = [("rank", i32), ("nranks", i32), ("buffers", vp * 8), ("epoch", C.c_uint32)]
+    _fields_ = [("rank", i32), ("nranks", i32), ("buffers", vp * 8), ("epoch", C.c_uint32), ("spin_limit", C.c_uint32)]
 
 
 class DecodeParams(C.Structure):
@@ -54,7 +54,7 @@ class DecodeParams(C.Structure):
                 ("v_batch_stride", i64), ("v_head_stride", i64), ("v_row_stride", i64),
                 ("v_transposed", i32), ("batch", i32), ("q_heads", i32), ("kv_heads", i32), ("head_dim", i32),
                 ("kv_len", i32), ("kv_len_dev", vp), ("window", i32), ("n_splits", i32), ("scale", f32),
-                ("partials", vp), ("carrier_out", vp), ("out", vp), ("out_dtype", i32)]
+                ("partials", vp), ("carrier_out", vp), ("out", vp), ("out_dtype", i32), ("kv_cap", i32)]
 
 
 class GemmRmsnormParams(C.Structure):
@@ -84,7 +84,8 @@ class _RmsnormStage(C.Structure):
 
 
 class _EmbedStage(C.Structure):
-    _fields_ = [("table", vp), ("tokens", vp), ("batch", i32), ("hidden", i32), ("vocab", i32), ("out", vp)]
+    _fields_ = [("table", vp), ("tokens", vp), ("batch", i32), ("hidden", i32), ("vocab", i32), ("out", vp),
+                ("scales", vp), ("table_dtype", i32), ("group", i32)]
 
 
 class _AdvanceStage(C.Structure):
@@ -142,6 +143,8 @@ PROTOTYPES = {
     "sanic_emit_select": (i32, [C.POINTER(CarrierDesc), C.POINTER(i32)]),
     "sanic_attn_fwd_f32": (i32, [vp, C.POINTER(AttnParams), vp]),
     "sanic_attn_fwd_bf16": (i32, [vp, C.POINTER(AttnParams), vp]),
+    "sanic_status_inject": (i32, [vp, i32]),
+    "sanic_embed_gather_w4": (i32, [vp, vp, vp, vp, i32, i32, i32, i32, vp, vp]),
     "sanic_attn_decode_splitkv": (i32, [vp, C.POINTER(DecodeParams), vp]),
     "sanic_attn_decode_splitkv_static": (i32, [vp, C.POINTER(DecodeParams), vp]),
     "sanic_attn_decode_static_scratch_capacity": (C.c_size_t, []),

@@ -79,12 +79,15 @@ class CudaDevice:
     def empty(self, shape, dtype):
         return torch.empty(shape, dtype=dtype, device=self.torch_device)
 
-    def _on_device(self, name, t, dtype=None):
+    def _on_device(self, name, t, dtype=None, strided=False):
         if not isinstance(t, torch.Tensor) or t.device != self.torch_device:
             raise RunError(f"input `{name}` is not a tensor on {self.torch_device}")
         if dtype is not None and t.dtype != dtype:
             raise RunError(f"input `{name}` has dtype {t.dtype}; expected {dtype}")
-        if not t.is_contiguous():
+        if strided:      # the entry point takes element strides; only the innermost axis must be dense
+            if t.stride(-1) != 1:
+                raise RunError(f"input `{name}` must be contiguous along its last axis")
+        elif not t.is_contiguous():
             raise RunError(f"input `{name}` must be contiguous")
         return t
 
@@ -113,14 +116,16 @@ class CudaDevice:
         p.out_dtype = out_dtype
         return p
 
-    def attn_fwd_f32(self, q, k, v, causal=False, window=0, scale=None, mask=None):
-        """q [B,Hq,L,E], k [B,Hkv,S,E], v [B,Hkv,S,Ev] f32 -> [B,Hq,L,Ev] f32."""
+    def attn_fwd_f32(self, q, k, v, causal=False, window=0, scale=None, mask=None, f64_accumulate=False):
+        """q [B,Hq,L,E], k [B,Hkv,S,E], v [B,Hkv,S,Ev] f32 -> [B,Hq,L,Ev] f32. `f64_accumulate` keeps scores,
+        exponentials and the carrier in f64 (one rounding, at the store)."""
         for n, t in (("q", q), ("k", k), ("v", v)):
             self._on_device(n, t, torch.float32)
         if mask is not None:
             self._on_device("mask", mask, torch.float32)
         out = self.empty((q.shape[0], q.shape[1], q.shape[2], v.shape[-1]), torch.float32)
         p = self._attn_params(q, k, v, out, causal, window, scale, mask, abi.F32)
+        p.accum_dtype = abi.F64 if f64_accumulate else abi.F32
         self._check(self.lib.sanic_attn_fwd_f32(self.h, C.byref(p), self.stream()), "attn_fwd_f32")
         return out
 
@@ -145,8 +150,9 @@ class CudaDevice:
         return int(self.lib.sanic_attn_decode_suggest_splits(self.h, batch, kv_heads, head_dim, kv_len))
 
     def decode_params(self, q, k, v, kv_len, v_transposed=False, n_splits=None, window=0, scale=None,
-                      kv_len_dev=None, out=None, carrier_out=None, partials=None, out_dtype=abi.BF16):
-        """Fill a DecodeParams. q [B,Hq,D] bf16; k [B,Hkv,S,D]; v [B,Hkv,S,D] or [B,Hkv,D,S] when v_transposed."""
+                      kv_len_dev=None, out=None, carrier_out=None, partials=None, out_dtype=abi.BF16, kv_cap=None):
+        """Fill a DecodeParams. q [B,Hq,D] bf16; k [B,Hkv,S,D]; v [B,Hkv,S,D] or [B,Hkv,D,S] when v_transposed.
+        `kv_cap` (default: the key extent of k) bounds what a device-side length may make the kernel read."""
         B, Hq, D = q.shape
         Hkv = k.shape[1]
         if n_splits is None:
@@ -167,12 +173,14 @@ class CudaDevice:
         p.carrier_out = carrier_out.data_ptr() if carrier_out is not None else None
         p.out = out.data_ptr() if out is not None else None
         p.out_dtype = out_dtype
+        p.kv_cap = int(kv_cap if kv_cap is not None else k.shape[2])
         return p, partials
 
     def attn_decode(self, q, k, v, kv_len, v_transposed=False, n_splits=None, window=0, scale=None,
                     return_carrier=False, out_dtype=torch.bfloat16):
-        for n, t in (("q", q), ("k", k), ("v", v)):
-            self._on_device(n, t, torch.bfloat16)
+        self._on_device("q", q, torch.bfloat16)
+        self._on_device("k", k, torch.bfloat16, strided=True)      # slices of a longer cache are read in place
+        self._on_device("v", v, torch.bfloat16, strided=True)
         B, Hq, D = q.shape
         out = self.empty((B, Hq, D), out_dtype)
         car = self.empty((B * Hq, D + 2), torch.float32) if return_carrier else None
@@ -285,6 +293,18 @@ class CudaDevice:
         rc = self.lib.sanic_embed_gather(self.h, _ptr(table), _ptr(tokens), tokens.shape[0], table.shape[1],
                                          table.shape[0], _ptr(out), self.stream())
         self._check(rc, "embed_gather")
+        return out
+
+    def embed_gather_w4(self, table, scales, tokens, group=64):
+        """table [vocab, hidden/2] uint8 nibbles, scales [vocab, hidden/group] bf16 -> widened rows [batch, hidden] f32."""
+        self._on_device("table", table, torch.uint8)
+        self._on_device("scales", scales, torch.bfloat16)
+        self._on_device("tokens", tokens, torch.int32)
+        hidden = table.shape[1] * 2
+        out = self.empty((tokens.shape[0], hidden), torch.float32)
+        rc = self.lib.sanic_embed_gather_w4(self.h, _ptr(table), _ptr(scales), _ptr(tokens), tokens.shape[0], hidden,
+                                            table.shape[0], group, _ptr(out), self.stream())
+        self._check(rc, "embed_gather_w4")
         return out
 
     def rope_table(self, inv_freq, n_pos):

@@ -13,6 +13,8 @@
 // projects o / l, or exports the merged raw accumulator for a cross-device merge.
 //
 // HBM-bound: algorithmic bytes = 2 * kv_len * D * 2 per (batch, kv head).
+#include <atomic>
+
 #include "common.cuh"
 
 #include "attn_decode_body.cuh"
@@ -22,9 +24,9 @@ using namespace sanic;
 using namespace sanic::decode;
 
 template <int D, bool VT>
-__global__ void __launch_bounds__(128) attn_decode_kernel(sanic_decode_params p, int* counters) {
+__global__ void __launch_bounds__(128) attn_decode_kernel(sanic_decode_params p, int* counters, int* err) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
-    attn_decode_tile<D, VT>(p, counters, (int)blockIdx.x, (int)blockIdx.y, (int)blockIdx.z, smem_raw, (int)threadIdx.x, true, 0);
+    attn_decode_tile<D, VT>(p, counters, (int)blockIdx.x, (int)blockIdx.y, (int)blockIdx.z, smem_raw, (int)threadIdx.x, true, 0, err);
 }
 
 // Stage 2 on its own: merge n_parts raw accumulators and project.
@@ -59,7 +61,7 @@ int32_t launch_decode(sanic_ctx* ctx, const sanic_decode_params& p, cudaStream_t
     SANIC_CUDA_CHECK(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<D>::SMEM));
     int* counters = (int*)(p.partials + (size_t)p.batch * p.q_heads * p.n_splits * (D + 2));
     dim3 grid(p.n_splits, p.kv_heads, p.batch);
-    cudaError_t le = launch_pdl(kern, grid, dim3(128), (size_t)Cfg<D>::SMEM, st, p, counters);
+    cudaError_t le = launch_pdl(kern, grid, dim3(128), (size_t)Cfg<D>::SMEM, st, p, counters, ctx->status_dev);
     if (le != cudaSuccess) return sanic_fail(ctx, SANIC_ERR_CUDA, std::string("attn_decode_splitkv: ") + cudaGetErrorString(le));
     return SANIC_OK;
 }
@@ -109,29 +111,40 @@ int32_t sanic_attn_decode_splitkv_static(sanic_ctx* ctx, const sanic_decode_para
     SANIC_REQUIRE(ctx, p->batch > 0 && p->q_heads > 0 && p->kv_heads > 0 && p->n_splits >= 1 && p->head_dim > 0,
                   "attn_decode_static: bad shape");
     const size_t need = (size_t)p->batch * p->q_heads * p->n_splits * (p->head_dim + 2);
-    if (need > SANIC_STATIC_SCRATCH_FLOATS || (size_t)p->batch * p->kv_heads > SANIC_STATIC_SCRATCH_COUNTERS)
+    if (need > SANIC_STATIC_SCRATCH_FLOATS)
         return sanic_fail(ctx, SANIC_ERR_INVALID,
                           "attn_decode_static: batch*q_heads*n_splits*(head_dim+2) = " + std::to_string(need) +
                           " floats exceeds the built-in scratch of " + std::to_string(SANIC_STATIC_SCRATCH_FLOATS) +
                           " floats; use fewer splits or sanic_attn_decode_splitkv with caller scratch");
+    if ((size_t)p->batch * p->kv_heads > SANIC_STATIC_SCRATCH_COUNTERS)
+        return sanic_fail(ctx, SANIC_ERR_INVALID,
+                          "attn_decode_static: batch*kv_heads = " + std::to_string((size_t)p->batch * p->kv_heads) +
+                          " exceeds the built-in " + std::to_string(SANIC_STATIC_SCRATCH_COUNTERS) +
+                          " ticket counters; use sanic_attn_decode_splitkv with caller scratch");
     sanic_set_device(ctx);
     // In host code the array's name is only a handle. Its device address is looked up once per
     // device, with that device current; the kernel is given that address, never the name.
-    static float* dev_addr[64] = {nullptr};
+    // Two host threads may both find the slot empty and both look the address up: they store the
+    // same value, so the slots are atomics only to make that overlap well defined.
+    static std::atomic<float*> dev_addr[64];
     SANIC_REQUIRE(ctx, ctx->device >= 0 && ctx->device < 64, "attn_decode_static: device ordinal out of range");
-    if (!dev_addr[ctx->device]) {
+    float* scratch = dev_addr[ctx->device].load(std::memory_order_acquire);
+    if (!scratch) {
         void* ptr = nullptr;
         cudaError_t e = cudaGetSymbolAddress(&ptr, g_decode_scratch);
         if (e != cudaSuccess || !ptr)
             return sanic_fail(ctx, SANIC_ERR_CUDA, std::string("attn_decode_static: cudaGetSymbolAddress: ") + cudaGetErrorString(e));
-        dev_addr[ctx->device] = (float*)ptr;
+        scratch = (float*)ptr;
+        dev_addr[ctx->device].store(scratch, std::memory_order_release);
     }
-    float* scratch = dev_addr[ctx->device];
+    sanic_decode_params local = *p;
+    local.partials = scratch;
+    // an invalid call must not touch the shared array: validate first, then clear the counters
+    int32_t rc = host_validate(ctx, &local);
+    if (rc != SANIC_OK) return rc;
     // The ticket counters must start at zero. They sit right after this call's partials; the array
     // keeps whatever the previous call left, so clear them on the stream (no allocation involved).
     SANIC_CUDA_CHECK(ctx, cudaMemsetAsync(scratch + need, 0, (size_t)p->batch * p->kv_heads * sizeof(int), (cudaStream_t)stream));
-    sanic_decode_params local = *p;
-    local.partials = scratch;
     return decode_validate_and_launch(ctx, &local, stream);
 }
 

@@ -57,7 +57,9 @@ __device__ __forceinline__ void load_tile(const sanic_decode_params& p, const ui
             bool ok = gk < hi;
             const uint16_t* src = Vb + (size_t)d * p.v_row_stride + (ok ? gk : 0);
             uint32_t dst = vaddr + d * 128 + ((c ^ (d & 7)) << 4);
-            cp_async16(dst, src, ok ? 16 : 0);
+            // the chunk that straddles the visible edge copies only its visible keys; the rest of the 16 bytes is
+            // zero-filled, so whatever the cache holds beyond the edge (NaN bit patterns included) never meets P = 0
+            cp_async16(dst, src, ok ? min(16, (hi - gk) * 2) : 0);
         }
     }
 }
@@ -70,7 +72,7 @@ __device__ __forceinline__ void tile_sync(int id) { asm volatile("bar.sync %0, 1
 // named barrier the 128 threads meet on.
 template <int D, bool VT>
 __device__ __forceinline__ void attn_decode_tile(const sanic_decode_params& p, int* counters, int split, int hk, int b,
-                                                 unsigned char* smem_raw, int tid, bool pdl, int bar_id) {
+                                                 unsigned char* smem_raw, int tid, bool pdl, int bar_id, int* err) {
     const int warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, t = lane & 3;
     const int group = p.q_heads / p.kv_heads;
@@ -78,7 +80,13 @@ __device__ __forceinline__ void attn_decode_tile(const sanic_decode_params& p, i
     constexpr int NT = D / 8;    // n-tiles of the output
 
     if (pdl) { griddep_launch(); griddep_wait(); }   // q, the caches and the position come from the previous kernels of the step
-    const int kv_len = p.kv_len_dev ? (*p.kv_len_dev + 1) : p.kv_len;
+    // A visible length read from the device is never trusted beyond the cache extent the host vouched for: it is
+    // clamped into [1, kv_cap] and the clamp is reported through the status word (the host turns code 52 into an error).
+    int kv_len = p.kv_len_dev ? (*p.kv_len_dev + 1) : p.kv_len;
+    if (p.kv_cap > 0 && (kv_len > p.kv_cap || kv_len < 1)) {
+        kv_len = kv_len < 1 ? 1 : p.kv_cap;
+        if (tid == 0 && err) atomicCAS(err, 0, 52);
+    }
     const int hi = kv_len;
     const int lo = (p.window > 0) ? max(0, kv_len - p.window) : 0;
     const int T0 = lo / KT, T1 = (hi + KT - 1) / KT;
@@ -294,6 +302,24 @@ inline int32_t host_validate(sanic_ctx* ctx, const sanic_decode_params* p) {
                   p->q_heads / p->kv_heads <= 16, "attn_decode: GQA group must divide and be <= 16");
     SANIC_REQUIRE(ctx, p->n_splits >= 1, "attn_decode: n_splits must be >= 1");
     SANIC_REQUIRE(ctx, p->kv_len_dev || p->kv_len >= 1, "attn_decode: empty key axis");
+    SANIC_REQUIRE(ctx, p->kv_cap >= 0 && (!p->kv_len_dev || p->kv_cap >= 1),
+                  "attn_decode: a device-side length needs kv_cap, the key extent of the cache");
+    SANIC_REQUIRE(ctx, p->kv_cap == 0 || p->kv_len_dev || p->kv_len <= p->kv_cap, "attn_decode: kv_len exceeds kv_cap");
+    if (p->kv_cap > 0) {
+        // kv_cap keys must fit inside one (batch, kv head) slice as the strides describe it
+        const int64_t k_span = (int64_t)p->kv_cap * p->k_seq_stride;
+        const bool k_head_major = p->k_head_stride >= p->k_seq_stride;      // [.., head, seq, D]; else [.., seq, head, D]
+        SANIC_REQUIRE(ctx, !k_head_major || ((p->kv_heads == 1 || k_span <= p->k_head_stride) && (p->batch == 1 || k_span <= p->k_batch_stride)),
+                      "attn_decode: kv_cap keys do not fit the K strides");
+        if (p->v_transposed) {
+            SANIC_REQUIRE(ctx, p->kv_cap <= p->v_row_stride, "attn_decode: kv_cap keys do not fit a row of the transposed V");
+        } else {
+            const int64_t v_span = (int64_t)p->kv_cap * p->v_row_stride;
+            const bool v_head_major = p->v_head_stride >= p->v_row_stride;
+            SANIC_REQUIRE(ctx, !v_head_major || ((p->kv_heads == 1 || v_span <= p->v_head_stride) && (p->batch == 1 || v_span <= p->v_batch_stride)),
+                          "attn_decode: kv_cap keys do not fit the V strides");
+        }
+    }
     SANIC_REQUIRE(ctx, p->k_seq_stride % 8 == 0 && p->k_head_stride % 8 == 0 && p->k_batch_stride % 8 == 0 &&
                   p->v_row_stride % 8 == 0 && p->v_head_stride % 8 == 0 && p->v_batch_stride % 8 == 0 &&
                   ((uintptr_t)p->k % 16) == 0 && ((uintptr_t)p->v % 16) == 0 && ((uintptr_t)p->q % 4) == 0,

@@ -298,10 +298,10 @@ __device__ __forceinline__ bool consume_gemv(const Phase& P, const Ring& ring, u
 }
 
 template <bool VT>
-__device__ __forceinline__ void run_decode(const Phase& P, int per_b, unsigned char* shared, int tid) {
+__device__ __forceinline__ void run_decode(const Phase& P, int per_b, unsigned char* shared, int tid, int* err) {
     for (int it = blockIdx.x; it < P.n_blocks; it += gridDim.x) {
         const int b = it / per_b, hk = (it % per_b) / P.dec.n_splits, split = it % P.dec.n_splits;
-        decode::attn_decode_tile<64, VT>(P.dec, P.counters, split, hk, b, shared, tid, false, 1);
+        decode::attn_decode_tile<64, VT>(P.dec, P.counters, split, hk, b, shared, tid, false, 1, err);
         decode::tile_sync(1);
     }
 }
@@ -409,20 +409,27 @@ decode_step_kernel(const Phase* __restrict__ phases, int n_phases, unsigned* bar
                     // one item = (chunk, kv head, batch) on the first 128 threads; its K/V ring is the shared region
                     const int per_b = P.dec.n_splits * P.dec.kv_heads;
                     if (tid < 128) {
-                        if (P.variant & 1) run_decode<true>(P, per_b, shared, tid);
-                        else run_decode<false>(P, per_b, shared, tid);
+                        if (P.variant & 1) run_decode<true>(P, per_b, shared, tid, err);
+                        else run_decode<false>(P, per_b, shared, tid, err);
                     }
                     break;
                 }
-                case PH_EMBED: {   // out[b,:] = widen(table[token[b],:])
-                    const uint16_t* table = (const uint16_t*)P.a;
+                case PH_EMBED: {   // out[b,:] = widen(table[token[b],:]); variant 1: int4 nibbles times the group scale
                     const int32_t* tokens = (const int32_t*)P.b;
                     float* out = (float*)P.c;
                     const int hidden = P.i1, vocab = P.i2;
                     for (int b = blockIdx.x; b < P.n_blocks; b += gridDim.x) {
                         int tok = __ldcg(tokens + b);
                         tok = tok < 0 ? 0 : (tok >= vocab ? vocab - 1 : tok);
-                        for (int k = tid; k < hidden; k += CONSUMERS) out[(size_t)b * hidden + k] = bf16_to_f32(table[(size_t)tok * hidden + k]);
+                        if (P.variant & 1) {
+                            const uint8_t* row = (const uint8_t*)P.a + (size_t)tok * (hidden / 2);
+                            const uint16_t* srow = (const uint16_t*)P.scratch + (size_t)tok * (hidden / P.i0);
+                            for (int k = tid; k < hidden; k += CONSUMERS)
+                                out[(size_t)b * hidden + k] = (float)(((row[k >> 1] >> ((k & 1) * 4)) & 0xF) - 8) * bf16_to_f32(srow[k / P.i0]);
+                        } else {
+                            const uint16_t* table = (const uint16_t*)P.a;
+                            for (int k = tid; k < hidden; k += CONSUMERS) out[(size_t)b * hidden + k] = bf16_to_f32(table[(size_t)tok * hidden + k]);
+                        }
                     }
                     break;
                 }
@@ -592,6 +599,11 @@ int32_t build(sanic_ctx* ctx, const std::vector<sanic_stage_desc>& stages, Plan*
                 SANIC_REQUIRE(ctx, s.u.embed.table && s.u.embed.tokens && s.u.embed.out && s.u.embed.batch > 0, "step: bad embed stage");
                 P.op = PH_EMBED; P.n_blocks = s.u.embed.batch;
                 P.a = s.u.embed.table; P.b = s.u.embed.tokens; P.c = s.u.embed.out; P.i1 = s.u.embed.hidden; P.i2 = s.u.embed.vocab;
+                if (s.u.embed.table_dtype == SANIC_I4) {
+                    SANIC_REQUIRE(ctx, s.u.embed.scales && s.u.embed.group > 0 && s.u.embed.group % 2 == 0 && s.u.embed.hidden % s.u.embed.group == 0,
+                                  "step: an int4 embed stage needs scales and an even group size dividing hidden");
+                    P.variant = 1; P.i0 = s.u.embed.group; P.scratch = (float*)s.u.embed.scales;
+                }
                 break;
             case SANIC_OP_RMSNORM:
                 SANIC_REQUIRE(ctx, s.u.rmsnorm.x && s.u.rmsnorm.gamma && s.u.rmsnorm.out && s.u.rmsnorm.rows > 0 && s.u.rmsnorm.n > 0,

@@ -39,8 +39,8 @@ __device__ __forceinline__ void st_release_sys(unsigned* p, unsigned v) {
 }
 
 __global__ void __launch_bounds__(256) peer_push_merge_kernel(const float* __restrict__ local, int rows, int D, int rank, int nranks,
-                                                            Peers peers, unsigned epoch, int* ticket, void* out, int out_dtype,
-                                                            int* err) {
+                                                            Peers peers, unsigned epoch, unsigned spin_limit, int* ticket, void* out,
+                                                            int out_dtype, int* err) {
     const int W = D + 2;
     const int parity = epoch & 1;
     const size_t set_floats = (size_t)rows * W;                       // one rank's accumulators
@@ -73,7 +73,7 @@ __global__ void __launch_bounds__(256) peer_push_merge_kernel(const float* __res
         for (int q = 0; q < nranks && ok; ++q) {
             unsigned spins = 0;
             while (ld_acquire_sys(flags + q) != epoch) {
-                if (++spins > PEER_SPIN_LIMIT) { atomicCAS(err, 0, 41 + q); ok = 0; break; }
+                if (++spins > spin_limit) { atomicCAS(err, 0, 41 + q); ok = 0; break; }
             }
         }
         s_ok = ok;
@@ -160,7 +160,8 @@ int32_t sanic_splitkv_decode_step_peer(sanic_ctx* ctx, const sanic_decode_params
     if (grid < 1) grid = 1;
     cudaError_t e = launch_pdl(peer_push_merge_kernel, dim3(grid), dim3(256), (size_t)0, (cudaStream_t)stream,
                                (const float*)p->carrier_out, rows, (int)p->head_dim, (int)x->rank, (int)x->nranks, peers,
-                               (unsigned)x->epoch, ticket, out, (int)out_dtype, ctx->status_dev);
+                               (unsigned)x->epoch, (unsigned)(x->spin_limit ? x->spin_limit : PEER_SPIN_LIMIT), ticket, out, (int)out_dtype,
+                               ctx->status_dev);
     if (e != cudaSuccess) return sanic_fail(ctx, SANIC_ERR_CUDA, std::string("splitkv_decode_step_peer: ") + cudaGetErrorString(e));
     return SANIC_OK;
 }

@@ -42,6 +42,23 @@ __global__ void embed_gather_kernel(const uint16_t* table, const int32_t* tokens
         out[(size_t)b * hidden + i] = bf16_to_f32(table[(size_t)tok * hidden + i]);
 }
 
+// The same gather from an int4 group-quantised table: out[b, i] = (nibble - 8) * scale[tok, i / group], the widened
+// value an I4 input means (unsigned q + 8 nibbles, low nibble = even element; exact in f32: 4 bits times 8 bits).
+__global__ void embed_gather_w4_kernel(const uint8_t* table, const uint16_t* scales, const int32_t* tokens, int hidden, int vocab,
+                                       int group, float* out) {
+    griddep_launch();
+    griddep_wait();
+    int b = blockIdx.x;
+    int tok = tokens[b];
+    tok = tok < 0 ? 0 : (tok >= vocab ? vocab - 1 : tok);
+    const uint8_t* row = table + (size_t)tok * (hidden / 2);
+    const uint16_t* srow = scales + (size_t)tok * (hidden / group);
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        const int nib = (row[i >> 1] >> ((i & 1) * 4)) & 0xF;
+        out[(size_t)b * hidden + i] = (float)(nib - 8) * bf16_to_f32(srow[i / group]);
+    }
+}
+
 __global__ void rope_table_kernel(const double* inv_freq, int n_freq, int n_pos, float* table) {
     int idx = blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= n_freq * n_pos) return;
@@ -216,6 +233,17 @@ int32_t sanic_embed_gather(sanic_ctx* ctx, const void* table, const int32_t* tok
     SANIC_REQUIRE(ctx, table && tokens && out && batch > 0 && hidden > 0 && vocab > 0, "embed_gather: bad arguments");
     sanic_set_device(ctx);
     SANIC_CUDA_CHECK(ctx, launch_pdl(embed_gather_kernel, dim3(batch), dim3(256), 0, (cudaStream_t)stream, (const uint16_t*)table, tokens, hidden, vocab, out));
+    return SANIC_OK;
+}
+
+int32_t sanic_embed_gather_w4(sanic_ctx* ctx, const void* table, const void* scales, const int32_t* tokens, int32_t batch,
+                              int32_t hidden, int32_t vocab, int32_t group, float* out, void* stream) {
+    if (!ctx) return SANIC_ERR_INVALID;
+    SANIC_REQUIRE(ctx, table && scales && tokens && out && batch > 0 && hidden > 0 && vocab > 0, "embed_gather_w4: bad arguments");
+    SANIC_REQUIRE(ctx, group > 0 && group % 2 == 0 && hidden % group == 0, "embed_gather_w4: hidden must be a multiple of the even group size");
+    sanic_set_device(ctx);
+    SANIC_CUDA_CHECK(ctx, launch_pdl(embed_gather_w4_kernel, dim3(batch), dim3(256), 0, (cudaStream_t)stream, (const uint8_t*)table,
+                                     (const uint16_t*)scales, tokens, hidden, vocab, group, out));
     return SANIC_OK;
 }
 

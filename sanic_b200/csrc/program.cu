@@ -70,6 +70,9 @@ int32_t run_stage(sanic_ctx* ctx, const sanic_stage_desc& s, void* stream) {
             return sanic_rmsnorm(ctx, s.u.rmsnorm.x, s.u.rmsnorm.gamma, s.u.rmsnorm.rows, s.u.rmsnorm.n, s.u.rmsnorm.eps,
                                  s.u.rmsnorm.out, stream);
         case SANIC_OP_EMBED:
+            if (s.u.embed.table_dtype == SANIC_I4)
+                return sanic_embed_gather_w4(ctx, s.u.embed.table, s.u.embed.scales, s.u.embed.tokens, s.u.embed.batch,
+                                             s.u.embed.hidden, s.u.embed.vocab, s.u.embed.group, s.u.embed.out, stream);
             return sanic_embed_gather(ctx, s.u.embed.table, s.u.embed.tokens, s.u.embed.batch, s.u.embed.hidden,
                                       s.u.embed.vocab, s.u.embed.out, stream);
         case SANIC_OP_ROPE_CACHE: return sanic_rope_cache_write(ctx, &s.u.rope_cache, stream);

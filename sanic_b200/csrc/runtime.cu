@@ -108,8 +108,17 @@ int32_t sanic_sync(sanic_ctx* ctx, void* stream) {
     if (code != 0) {
         *ctx->status_host = 0;
         if (code == 51) return sanic_fail(ctx, SANIC_ERR_INVALID, "a gather index was out of range (code 51)");
+        if (code == 52)
+            return sanic_fail(ctx, SANIC_ERR_INVALID, "a device-side key length was outside [1, kv_cap] and was clamped: the decode "
+                                                      "position ran past the cache extent (code 52)");
         return sanic_fail(ctx, SANIC_ERR_TIMEOUT, "a bounded device-side wait ran out (code " + std::to_string(code) + ")");
     }
+    return SANIC_OK;
+}
+
+int32_t sanic_status_inject(sanic_ctx* ctx, int32_t code) {
+    if (!ctx || !ctx->status_host) return SANIC_ERR_INVALID;
+    *(volatile int*)ctx->status_host = code;
     return SANIC_OK;
 }
 

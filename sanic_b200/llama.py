@@ -40,9 +40,12 @@ def llama3_inv_freq(n_freq: int):
     return out
 
 
-def random_weights(cfg: dict, seed: int, device, w4: bool = False):
+def random_weights(cfg: dict, seed: int, device, w4: bool = False, w4_head: bool | None = None):
     """Random-init weights of the architecture: N(0, 0.02) bf16, norms N(1, 0.1); the int4 variant draws
-    integers uniform in [-8, 7] with a positive bf16 scale per 64 inputs."""
+    integers uniform in [-8, 7] with a positive bf16 scale per 64 inputs. `w4_head` (default: as `w4`) quantises
+    the tied embedding / lm_head table the same way ('embed' packed, 'sembed' scales); False keeps it bf16."""
+    if w4_head is None:
+        w4_head = w4
     g = torch.Generator(device=device)
     g.manual_seed(seed)
     H, F, V = cfg["hidden"], cfg["ffn"], cfg["vocab"]
@@ -61,7 +64,11 @@ def random_weights(cfg: dict, seed: int, device, w4: bool = False):
         s = 0.02 / 4.6 * (1.0 + 0.25 * torch.rand(rows, cols // 64, generator=g, device=device, dtype=torch.float32))
         return packed, s.to(torch.bfloat16).contiguous()
 
-    w = dict(embed=dense(V, H), final_norm=norm(), attn_norm=[], mlp_norm=[])
+    w = dict(final_norm=norm(), attn_norm=[], mlp_norm=[])
+    if w4_head:
+        w["embed"], w["sembed"] = quant(V, H)
+    else:
+        w["embed"] = dense(V, H)
     shapes = dict(wq=(Hq * D, H), wk=(Hkv * D, H), wv=(Hkv * D, H), wo=(H, Hq * D), wgate=(F, H), wup=(F, H), wdown=(H, F))
     for name in shapes:
         w[name] = []
@@ -78,20 +85,6 @@ def random_weights(cfg: dict, seed: int, device, w4: bool = False):
             else:
                 w[name].append(dense(r, c))
     return w
-
-
-def weights_to_oracle(w: dict, w4: bool):
-    """Host copies in the layout oracle.Llama takes (bf16 bits as uint16, packed int4 as uint8)."""
-    def bits(t):
-        return t.view(torch.int16).cpu().numpy().view("uint16")
-
-    out = dict(embed=bits(w["embed"]), final_norm=bits(w["final_norm"]),
-               attn_norm=[bits(t) for t in w["attn_norm"]], mlp_norm=[bits(t) for t in w["mlp_norm"]])
-    for name in ("wq", "wk", "wv", "wo", "wgate", "wup", "wdown"):
-        out[name] = [t.cpu().numpy() if w4 else bits(t) for t in w[name]]
-        if w4:
-            out["s" + name[1:]] = [bits(t) for t in w["s" + name[1:]]]
-    return out
 
 
 class LlamaMachine:
@@ -135,6 +128,7 @@ class LlamaMachine:
         self.partials = z((dev.lib.sanic_attn_decode_scratch_bytes(B, Hq, D, self.n_splits) // 4,), torch.float32)
         self.amax_scratch = z((B * 2 * 256,), torch.float32)
         self.stream = torch.cuda.Stream(device=td)
+        self._host_position = 0
         self.persistent = persistent
         self._build()
         self.captured = False
@@ -145,7 +139,10 @@ class LlamaMachine:
     def _gemv(self, x, names, layer, outs, epilogue=abi.EPI_STORE, residual=None, out_dtype=abi.F32, norm=None,
               rope_layer=None):
         ws = [self.w[n][layer] if layer is not None else self.w[n] for n in names]
-        sc = [self.w["s" + n[1:]][layer] for n in names] if (self.w4 and layer is not None) else None
+        if layer is not None:
+            sc = [self.w["s" + n[1:]][layer] for n in names] if self.w4 else None
+        else:       # the tied table: quantised when it came with scales
+            sc = [self.w["s" + n] for n in names] if ws[0].dtype == torch.uint8 else None
         s = abi.StageDesc()
         s.stage_kind, s.op = abi.STAGE_FUSED, abi.OP_GEMV
         s.carrier = carrier_contraction(abi.I4 if sc is not None else abi.BF16)
@@ -184,6 +181,8 @@ class LlamaMachine:
         s.u.embed.table, s.u.embed.tokens = self.w["embed"].data_ptr(), self.tokens.data_ptr()
         s.u.embed.batch, s.u.embed.hidden, s.u.embed.vocab = B, cfg["hidden"], cfg["vocab"]
         s.u.embed.out = self.x.data_ptr()
+        if self.w["embed"].dtype == torch.uint8:
+            s.u.embed.scales, s.u.embed.table_dtype, s.u.embed.group = self.w["sembed"].data_ptr(), abi.I4, 64
         st.append(s)
         for l in range(cfg["layers"]):
             if fused:
@@ -256,10 +255,16 @@ class LlamaMachine:
         self.sync()
         self.tokens.copy_(torch.as_tensor(tokens, dtype=torch.int32).to(self.dev.torch_device))
         self.position.fill_(position)
+        self._host_position = int(position)
         torch.cuda.synchronize(self.dev.torch_device)
 
     def step(self, timed: bool = False):
         """One decode step: token <- argmax(logits(token, position)); position += 1. Returns device seconds if timed."""
+        # the position lives on the device; the host keeps its own count so that a step whose cache row would fall
+        # outside the cache is refused here instead of being clamped (and reported) by the kernels
+        if self._host_position >= self.ctx:
+            raise RunError(f"step: position {self._host_position} is outside the cache extent {self.ctx}")
+        self._host_position += 1
         st = C.c_void_p(self.stream.cuda_stream)
         if self.captured:
             sec = C.c_double(0.0)
@@ -271,6 +276,9 @@ class LlamaMachine:
 
     def step_stage_times(self):
         """One decode step with a device time per stage (MetalDevice::run_kernel_timed): list of seconds."""
+        if self._host_position >= self.ctx:
+            raise RunError(f"step: position {self._host_position} is outside the cache extent {self.ctx}")
+        self._host_position += 1
         st = C.c_void_p(self.stream.cuda_stream)
         cap = 4 * self.n_stages + 8
         buf = (C.c_double * cap)()
@@ -306,7 +314,10 @@ class LlamaMachine:
         return out
 
     def sync(self):
-        self.stream.synchronize()
+        """Wait for the steps in flight and surface the device status word: a step whose bounded wait ran out, or
+        whose position ran past the cache, left partial writes, and a decode loop must not continue on them
+        (src/metal.rs:686-705 returns Err for the same reason). Raises RunError."""
+        self.dev._check(self.dev.lib.sanic_sync(self.dev.h, C.c_void_p(self.stream.cuda_stream)), "machine sync")
 
     def read_tokens(self):
         self.sync()

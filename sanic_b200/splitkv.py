@@ -134,8 +134,15 @@ class SplitKVDecoder:
             self.dev.lib.sanic_free(self.dev.h, self._peer["local"])
             self._peer = None
 
+    def sync(self):
+        """Wait for the steps in flight on the current stream and raise RunError if a peer's flag never arrived
+        (status codes 41 + rank) or any other bounded wait ran out. The tensor `step` returned is valid only after
+        this returns."""
+        self.dev.sync()
+
     def step(self, q, scale=None):
-        """q [B, Hq, D] bf16 (replicated on every rank) -> attention output [B, Hq, D] bf16 on every rank."""
+        """q [B, Hq, D] bf16 (replicated on every rank) -> attention output [B, Hq, D] bf16 on every rank.
+        Asynchronous: call sync() before reading the result."""
         B, Hq, D = q.shape
         b = self._buffers(B, Hq, D)
         p, _keep = self.dev.decode_params(q, self.k, self.v, self.n_local, n_splits=self.n_splits, scale=scale,

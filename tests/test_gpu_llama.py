@@ -11,6 +11,7 @@ import pytest
 import torch
 
 from oracle import oracle as orc
+from llama_util import run_pair
 
 pytestmark = pytest.mark.gpu
 
@@ -21,56 +22,6 @@ SMALL = dict(vocab=1024, layers=2, hidden=256, q_heads=4, kv_heads=2, head_dim=6
 def dev():
     from sanic_b200 import CudaDevice
     return CudaDevice(0)
-
-
-def run_pair(dev, cfg, ctx, batch, w4, steps, prefill, seed=5, fused=True, persistent=False):
-    from sanic_b200 import llama
-    w = llama.random_weights(cfg, seed, dev.torch_device, w4=w4)
-    m = llama.LlamaMachine(dev, cfg, w, ctx=ctx, batch=batch, w4=w4, fused=fused, persistent=persistent)
-    ocfg = dict(cfg, ctx=ctx, batch=batch, w4=int(w4), group=64, round_acts=1, llama3_rope=1)
-    o = orc.Llama(ocfg, llama.weights_to_oracle(w, w4))
-    rng = np.random.default_rng(seed)
-    # prefill the caches by decoding random token ids on the device, then hand the bf16 cache
-    # contents to the oracle so both sides start the compared steps from identical state
-    toks = rng.integers(0, cfg["vocab"], size=(prefill, batch)).astype(np.int32)
-    for p in range(prefill):
-        m.set_state(toks[p], p)
-        m.step()
-    m.sync()
-    for l in range(cfg["layers"]):
-        o.kcache[l] = m.kcache[l].float().cpu().numpy().astype(np.float64)
-        o.vcache[l] = m.vcache[l].float().cpu().numpy().astype(np.float64)
-    cur = rng.integers(0, cfg["vocab"], size=batch).astype(np.int32)
-    m.set_state(cur, prefill)
-    ocur = cur.copy()
-    ties = 0
-    for s in range(steps):
-        m.step()
-        got = m.read_tokens()
-        ocur = o.step(ocur, prefill + s)
-        lg = m.logits.cpu().numpy().astype(np.float64)
-        ol = o.logits()
-        # bf16 bound of one kernel is 2e-2; independent rounding noise of a deeper stack grows with the
-        # square root of its depth (the 2-layer model is held to the single-kernel bound)
-        tol_logits = 2e-2 * max(1.0, (cfg["layers"] / 2.0) ** 0.5)
-        err = np.max(np.abs(lg - ol) / (1.0 + np.abs(ol)))
-        assert err <= tol_logits, f"step {s}: logits differ by {err}"
-        rms = np.linalg.norm(lg - ol) / np.linalg.norm(ol)
-        assert rms <= 2e-2, f"step {s}: logits differ by {rms} in relative rms"
-        bad = np.nonzero(got != ocur)[0]
-        if bad.size:
-            # A different token is an error unless the oracle's own top-2 gap on that row is inside
-            # the bf16 bound: then both indices are maxima to within the storage precision (a tie).
-            top = np.sort(ol[bad], axis=1)
-            gaps = top[:, -1] - top[:, -2]
-            tol = 2e-2 * (1.0 + np.abs(top[:, -1]))
-            assert np.all(gaps <= tol), f"step {s}: tokens {got[bad]} vs oracle {ocur[bad]}, oracle top-2 gaps {gaps}"
-            assert np.all(np.abs(ol[bad, got[bad]] - top[:, -1]) <= tol)
-            ties += int(bad.size)
-            m.tokens.copy_(torch.as_tensor(ocur).to(m.tokens.device))   # continue both sides from the same token
-            torch.cuda.synchronize()
-    assert ties <= max(1, steps * batch // 16), f"{ties} near-tie steps out of {steps * batch}"
-    return m
 
 
 @pytest.mark.parametrize("batch", [1, 3])
@@ -121,13 +72,6 @@ def test_machine_refuses_bad_state(dev):
         m.set_state([0], 64)
     with pytest.raises(CompileError):
         llama.LlamaMachine(dev, dict(SMALL, hidden=128), w, ctx=64, batch=1)
-
-
-@pytest.mark.slow
-def test_full_architecture_decode_steps(dev):
-    """Llama-3.2-1B architecture (16 layers, hidden 2048, vocab 128256): a few greedy steps against the oracle."""
-    from sanic_b200 import llama
-    run_pair(dev, llama.LLAMA_3_2_1B, ctx=64, batch=1, w4=False, steps=3, prefill=8, seed=9)
 
 
 def test_generate_matches_manual_stepping(dev):

@@ -52,6 +52,11 @@ def test_static_scratch_decode_matches_caller_scratch_twice():
         assert _nerr(got, ref) <= BF16_TOL, f"call {call}"
         assert _nerr(got_car[:, 1:], ref_car[:, 1:]) <= BF16_TOL, f"call {call}"
         assert torch.equal(got, ref), f"call {call}: the two entry points run the same deterministic kernel"
+        # and both agree with the CPU oracle on one (batch, kv head)
+        from oracle import oracle as orc
+        f64 = lambda t: t.float().cpu().numpy().astype(np.float64)
+        exp = orc.sdpa(f64(q[1:, 12:]).reshape(1, 4, 1, D), f64(k[1:, 3:, :kv_len]), f64(v[1:, 3:, :kv_len]), enable_gqa=True)
+        assert np.max(np.abs(f64(got[1, 12:]) - exp.reshape(4, D)) / (1.0 + np.abs(exp.reshape(4, D)))) <= BF16_TOL
 
 
 def test_static_scratch_rejects_oversized_requests():
@@ -70,3 +75,11 @@ def test_static_scratch_rejects_oversized_requests():
     rc = dev.lib.sanic_attn_decode_splitkv_static(dev.h, C.byref(p), dev.stream())
     assert rc == abi.ERR_INVALID
     assert b"exceeds the built-in scratch" in dev.lib.sanic_last_error(dev.h)
+    # the other limit, one ticket counter per (batch, kv head), has its own message
+    B2, H2 = 4100, 1
+    q2 = torch.zeros(B2, H2, 64, dtype=torch.bfloat16, device=td)
+    k2 = torch.zeros(B2, H2, 8, 64, dtype=torch.bfloat16, device=td)
+    p2, _keep = dev.decode_params(q2, k2, k2, 8, n_splits=1, out=dev.empty((B2, H2, 64), torch.float32), out_dtype=abi.F32,
+                                  partials=torch.zeros(1, device=td))
+    assert dev.lib.sanic_attn_decode_splitkv_static(dev.h, C.byref(p2), dev.stream()) == abi.ERR_INVALID
+    assert b"ticket counters" in dev.lib.sanic_last_error(dev.h)
