@@ -35,7 +35,12 @@ enum {
     SANIC_ERR_TIMEOUT = 4,      /* a bounded device-side wait ran out */
     SANIC_ERR_NCCL = 5,
     SANIC_ERR_DTYPE = 6,        /* RunError::Dtype */
-    SANIC_ERR_NOMEM = 7
+    SANIC_ERR_NOMEM = 7,
+    SANIC_ERR_MISSING_INPUT = 8,    /* RunError::MissingInput */
+    SANIC_ERR_UNKNOWN_INPUT = 9,    /* RunError::UnknownInput */
+    SANIC_ERR_DUPLICATE_INPUT = 10, /* RunError::DuplicateInput */
+    SANIC_ERR_SHAPE = 11,           /* RunError::Shape */
+    SANIC_ERR_FEEDBACK = 12         /* RunError::Feedback */
 };
 
 /* Storage widths (src/scalar.rs:181-201). */
@@ -383,6 +388,82 @@ int32_t sanic_program_step(sanic_program* prog, void* stream, double* gpu_second
  * receives min(cap, stages) entries and *n_out their count; a program captured in its single-kernel form
  * reports one entry per phase (argmax is two). The step is a real one: state advances. Synchronises `stream`. */
 int32_t sanic_program_stage_times(sanic_program* prog, void* stream, double* seconds, int32_t cap, int32_t* n_out);
+
+/* ── schedules over a buffer table: binding by name on every run, replays with state feedback, machines ──
+ *
+ * What the reference's emitter hands its runtime is a program whose stages NAME their buffers
+ * (MetalProgram{stages[{kernel, inputs, output, ..}], inputs, dtypes, buffers[(name, elements)]},
+ * src/emit_metal.rs:1183-1212). A schedule here is the stage list above plus that buffer table and a relocation
+ * list: each pointer field of a stage that refers to a table buffer is given as (stage, byte offset of the field
+ * inside sanic_stage_desc, buffer index, byte offset into the buffer). Binding fills those fields and nothing else,
+ * so binding other buffers never recompiles anything. Every check runs on the host before any CUDA call; a
+ * schedule compiled with ctx == NULL checks bindings and feedback without a device and refuses to run. */
+enum { SANIC_BUF_INPUT = 1,    /* bound by the caller, by name (InputSpec, src/compile.rs:114-121) */
+       SANIC_BUF_SCRATCH = 2 };/* allocated by the runtime, zero-filled: intermediates and outputs (program.buffers) */
+typedef struct {
+    const char* name;                   /* unique; inputs are bound under this name */
+    int32_t kind;                       /* SANIC_BUF_* */
+    int32_t dtype;                      /* declared storage: SANIC_F32 / F16 / BF16 / U32 / I4 */
+    int32_t rank;
+    int64_t shape[SANIC_MAX_AXES];      /* concrete extents (dynamic shapes are refused) */
+} sanic_buffer_decl;
+typedef struct { int32_t stage; int32_t field_offset; int32_t buffer; int64_t byte_offset; } sanic_reloc;
+typedef struct {
+    const sanic_stage_desc* stages; int32_t n_stages;   /* pointer fields named by a relocation are filled at bind time */
+    const sanic_buffer_decl* buffers; int32_t n_buffers;
+    const sanic_reloc* relocs; int32_t n_relocs;
+    const int32_t* outputs; int32_t n_outputs;          /* buffer index of every root, in compilation-root order */
+    /* roots compiled in place (compile_roots_in_place, src/compile.rs:408; the law is Graph::overwritable_states,
+     * src/graph.rs:127-160): root in_place_root[i] writes the buffer of input in_place_input[i] (a buffer index) instead
+     * of one of its own */
+    const int32_t* in_place_root; const int32_t* in_place_input; int32_t n_in_place;
+} sanic_schedule_desc;
+/* A bound buffer as the runtime sees one: Buffer::shape() and Buffer::dtype() (src/compile.rs:81-84) plus its address. */
+typedef struct { const char* name; const void* dptr; int32_t dtype; int32_t rank; int64_t shape[SANIC_MAX_AXES]; } sanic_binding;
+typedef struct { void* dptr; int32_t dtype; int32_t rank; int64_t shape[SANIC_MAX_AXES]; size_t bytes; } sanic_buffer_view;
+typedef struct sanic_schedule sanic_schedule;
+typedef struct sanic_replay sanic_replay;
+/* Backend::prepare (src/compile.rs:94-99): validates the table, the relocations, the roots and the in-place pairs. */
+int32_t sanic_schedule_compile(sanic_ctx* ctx, const sanic_schedule_desc* desc, sanic_schedule** out);
+int32_t sanic_schedule_destroy(sanic_schedule* s);
+const char* sanic_schedule_last_error(sanic_schedule* s);   /* also set when the schedule has no context */
+int32_t sanic_schedule_input_count(sanic_schedule* s);      /* Program::input_names (src/compile.rs:138-140) */
+const char* sanic_schedule_input_name(sanic_schedule* s, int32_t i);
+int32_t sanic_schedule_output_count(sanic_schedule* s);
+/* The checks of Program::ordered_bindings (src/compile.rs:190-229), alone: SANIC_ERR_UNKNOWN_INPUT, _DUPLICATE_INPUT,
+ * _MISSING_INPUT, _SHAPE, _DTYPE in that order of discovery. */
+int32_t sanic_schedule_check_bindings(sanic_schedule* s, const sanic_binding* bindings, int32_t n);
+/* Program::try_run / Backend::execute (src/compile.rs:101-107,175-187): bind by name, launch every stage on `stream`,
+ * return the roots in order. The views point into storage the schedule owns: valid until its next execute or destroy. */
+int32_t sanic_schedule_execute(sanic_schedule* s, const sanic_binding* bindings, int32_t n, void* stream,
+                               sanic_buffer_view* outputs, int32_t n_outputs);
+/* Program::capture(bindings, feedback) (src/compile.rs:820-960): freeze the step over these bindings. Each feedback pair
+ * (root index, input name) must name a real root and a real input of equal shape and storage, each at most once
+ * (SANIC_ERR_FEEDBACK otherwise). A pair whose root was compiled in place is ONE buffer; any other pair makes the replay
+ * two frozen steps whose buffers trade places (ping-pong). persistent != 0 lowers each step into the single cooperative
+ * kernel (sanic_program_capture_persistent). */
+int32_t sanic_schedule_capture(sanic_schedule* s, const sanic_binding* bindings, int32_t n, const int32_t* feedback_output,
+                               const char* const* feedback_input, int32_t n_feedback, int32_t persistent, void* stream,
+                               sanic_replay** out);
+int32_t sanic_replay_step(sanic_replay* r, void* stream, double* gpu_seconds);           /* MetalReplay::step_timed */
+int32_t sanic_replay_stage_times(sanic_replay* r, void* stream, double* seconds, int32_t cap, int32_t* n_out);
+int32_t sanic_replay_output(sanic_replay* r, int32_t root, sanic_buffer_view* out);       /* MetalReplay::last_outputs */
+int32_t sanic_replay_kernel_count(sanic_replay* r);
+int32_t sanic_replay_parities(sanic_replay* r);                                           /* 1, or 2 when feedback swaps */
+int32_t sanic_replay_destroy(sanic_replay* r);
+/* Graph::compile_for + StepProgram::instantiate (src/graph.rs:231-341). A state is an input whose successor is root
+ * `root`; its buffer is allocated here, zero-filled, and owned by the machine; the caller binds the other inputs only
+ * (binding a state is SANIC_ERR_DUPLICATE_INPUT). A state declared at another width than `boundary_dtype`, the
+ * compilation's boundary policy, is refused with SANIC_ERR_UNSUPPORTED unless `pinned` (src/graph.rs:236-245,
+ * Graph::output_at :113-125). The machine is a replay: step it with sanic_replay_step. */
+typedef struct { const char* input_name; int32_t root; int32_t pinned; } sanic_state_decl;
+int32_t sanic_machine_instantiate(sanic_schedule* s, const sanic_state_decl* states, int32_t n_states, int32_t boundary_dtype,
+                                  const sanic_binding* bindings, int32_t n, const char* const* output_names,
+                                  const int32_t* output_roots, int32_t n_named_outputs, int32_t persistent, void* stream,
+                                  sanic_replay** out);
+int32_t sanic_machine_output(sanic_replay* m, const char* name, sanic_buffer_view* out);  /* Machine::output (src/graph.rs:343-356) */
+/* The buffer state `name` will be read from by the NEXT step (to load a prefilled cache, or to read a state back). */
+int32_t sanic_machine_state(sanic_replay* m, const char* name, sanic_buffer_view* out);
 
 /* ── multi-device split-KV: each device folds its slice of the key axis, the carriers are
  *    exchanged and merged with the derived combine (src/interp.rs:538-554) ── */

@@ -11,7 +11,9 @@ import os
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libsanic_b200.so")
 
-OK, ERR_INVALID, ERR_CUDA, ERR_UNSUPPORTED, ERR_TIMEOUT, ERR_NCCL, ERR_DTYPE, ERR_NOMEM = range(8)
+(OK, ERR_INVALID, ERR_CUDA, ERR_UNSUPPORTED, ERR_TIMEOUT, ERR_NCCL, ERR_DTYPE, ERR_NOMEM, ERR_MISSING_INPUT, ERR_UNKNOWN_INPUT,
+ ERR_DUPLICATE_INPUT, ERR_SHAPE, ERR_FEEDBACK) = range(13)
+BUF_INPUT, BUF_SCRATCH = 1, 2
 F32, F16, BF16, U32, I4, F64 = 1, 2, 3, 4, 5, 6
 SLOT_PLAIN_ADD, SLOT_PLAIN_MAX, SLOT_PLAIN_MIN, SLOT_EXP_SHIFTED, SLOT_AT_EXTREMUM = 1, 2, 3, 4, 5
 KERNEL_NONE, KERNEL_ONLINE_SOFTMAX_FOLD, KERNEL_DEFERRED_NORM_CONTRACTION, KERNEL_PLAIN_CONTRACTION, \
@@ -127,6 +129,36 @@ class GenericDesc(C.Structure):
                 ("store_if", Expr), ("out_dtype", i32)]
 
 
+class BufferDecl(C.Structure):
+    _fields_ = [("name", C.c_char_p), ("kind", i32), ("dtype", i32), ("rank", i32), ("shape", i64 * MAX_AXES)]
+
+
+class Reloc(C.Structure):
+    _fields_ = [("stage", i32), ("field_offset", i32), ("buffer", i32), ("byte_offset", i64)]
+
+
+class ScheduleDesc(C.Structure):
+    _fields_ = [("stages", vp), ("n_stages", i32), ("buffers", vp), ("n_buffers", i32), ("relocs", vp), ("n_relocs", i32),
+                ("outputs", vp), ("n_outputs", i32), ("in_place_root", vp), ("in_place_input", vp), ("n_in_place", i32)]
+
+
+class Binding(C.Structure):
+    _fields_ = [("name", C.c_char_p), ("dptr", vp), ("dtype", i32), ("rank", i32), ("shape", i64 * MAX_AXES)]
+
+
+class BufferView(C.Structure):
+    _fields_ = [("dptr", vp), ("dtype", i32), ("rank", i32), ("shape", i64 * MAX_AXES), ("bytes", C.c_size_t)]
+
+
+class StateDecl(C.Structure):
+    _fields_ = [("input_name", C.c_char_p), ("root", i32), ("pinned", i32)]
+
+
+def dtype_of_torch(dt):
+    import torch
+    return {torch.float32: F32, torch.float16: F16, torch.bfloat16: BF16, torch.int32: U32, torch.uint8: I4}[dt]
+
+
 # name -> (restype, argtypes); every symbol the header declares
 PROTOTYPES = {
     "sanic_cuda_open": (i32, [i32, C.POINTER(vp)]),
@@ -177,6 +209,25 @@ PROTOTYPES = {
     "sanic_program_capture_persistent": (i32, [vp, vp]),
     "sanic_program_step": (i32, [vp, vp, C.POINTER(C.c_double)]),
     "sanic_program_stage_times": (i32, [vp, vp, C.POINTER(C.c_double), i32, C.POINTER(i32)]),
+    "sanic_schedule_compile": (i32, [vp, C.POINTER(ScheduleDesc), C.POINTER(vp)]),
+    "sanic_schedule_destroy": (i32, [vp]),
+    "sanic_schedule_last_error": (C.c_char_p, [vp]),
+    "sanic_schedule_input_count": (i32, [vp]),
+    "sanic_schedule_input_name": (C.c_char_p, [vp, i32]),
+    "sanic_schedule_output_count": (i32, [vp]),
+    "sanic_schedule_check_bindings": (i32, [vp, C.POINTER(Binding), i32]),
+    "sanic_schedule_execute": (i32, [vp, C.POINTER(Binding), i32, vp, C.POINTER(BufferView), i32]),
+    "sanic_schedule_capture": (i32, [vp, C.POINTER(Binding), i32, C.POINTER(i32), C.POINTER(C.c_char_p), i32, i32, vp, C.POINTER(vp)]),
+    "sanic_replay_step": (i32, [vp, vp, C.POINTER(C.c_double)]),
+    "sanic_replay_stage_times": (i32, [vp, vp, C.POINTER(C.c_double), i32, C.POINTER(i32)]),
+    "sanic_replay_output": (i32, [vp, i32, C.POINTER(BufferView)]),
+    "sanic_replay_kernel_count": (i32, [vp]),
+    "sanic_replay_parities": (i32, [vp]),
+    "sanic_replay_destroy": (i32, [vp]),
+    "sanic_machine_instantiate": (i32, [vp, C.POINTER(StateDecl), i32, i32, C.POINTER(Binding), i32, C.POINTER(C.c_char_p), C.POINTER(i32),
+                                        i32, i32, vp, C.POINTER(vp)]),
+    "sanic_machine_output": (i32, [vp, C.c_char_p, C.POINTER(BufferView)]),
+    "sanic_machine_state": (i32, [vp, C.c_char_p, C.POINTER(BufferView)]),
     "sanic_nccl_unique_id": (i32, [C.POINTER(C.c_uint8)]),
     "sanic_nccl_init": (i32, [vp, i32, i32, C.POINTER(C.c_uint8)]),
     "sanic_nccl_shutdown": (i32, [vp]),

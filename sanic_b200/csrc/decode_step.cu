@@ -78,6 +78,14 @@ __host__ __device__ inline Geom geom_of(bool w4, bool dual, int K) {
     return g;
 }
 
+// k values per staged activation row when a phase's activations do not fit the staging area whole: a ring stage,
+// halved until `batch` rows of it (plus the row padding) fit
+__host__ __device__ inline int stage_span(int batch, int stage_k) {
+    int span = stage_k;
+    while (span > 64 && (size_t)batch * (span * 2 + 64) > (size_t)XS_BYTES) span >>= 1;
+    return span;
+}
+
 // weight row (within its matrix) of fragment row r (0..15) of row tile `tile`
 __device__ __forceinline__ int weight_row(int epilogue, const gemv::Fused& fz, int tile, int r) {
     if (epilogue == SANIC_EPI_ROPE_CACHE) {      // rotate-half partners d = 8*sub + r and d + D/2 of one head
@@ -168,14 +176,18 @@ __device__ __forceinline__ bool consume_gemv(const Phase& P, const Ring& ring, u
     constexpr int UNIT = W4 ? 64 : 32;       // k values one pass of a warp covers
     const Geom G = geom_of(W4, DUAL, P.K);
     const int units = G.stage_k / UNIT;
-    const int u0 = (warp * units) / GW, u1 = ((warp + 1) * units) / GW;
     // The phase's activations (norm applied) are the same for every tile: they are staged in shared memory, as a
     // whole when batch x K fits (one L2 round trip per phase), else one ring stage's K range at a time. Rows sit
     // 4 bank groups apart, like the weight rows. The inner loop reads activations from shared memory only.
     unsigned char* xs = (unsigned char*)scratch + SCRATCH_BYTES;
     const bool whole = (size_t)P.batch * (P.K * 2 + 64) <= (size_t)XS_BYTES;
-    const int xspan = whole ? P.K : G.stage_k;       // k values per staged row
+    // k values per staged row: the whole K, else a ring stage, else (a stage of 16 rows can exceed the staging area:
+    // 16 x 4096 int4 inputs are 132 KB of bf16) the largest power-of-two part of a stage that fits
+    const int xspan = whole ? P.K : stage_span(P.batch, G.stage_k);
     const int xpitch = xspan * 2 + 64;
+    const int units_x = xspan / UNIT;                 // units per staged span; the warps split these
+    const int ux0 = (warp * units_x) / GW, ux1 = ((warp + 1) * units_x) / GW;
+    const int spans_per_stage = whole ? 1 : G.stage_k / xspan;
     auto stage_x = [&](int k_begin) {
         const int cpr = xspan / 8;       // 16-byte chunks per row
         for (int idx = tid; idx < P.batch * cpr; idx += CONSUMERS) {
@@ -215,11 +227,15 @@ __device__ __forceinline__ bool consume_gemv(const Phase& P, const Ring& ring, u
             const int slot = drained % SLOTS;
             const uint32_t parity = (drained / SLOTS) & 1;
             const int kbase = s * G.stage_k;
-            const int xbase = whole ? 0 : kbase;
-            if (!whole) { consumer_sync(); stage_x(kbase); consumer_sync(); }
             ok = mbar_wait(&ring.full[slot], parity, gbar, err, 32);
             if (!ok) break;
             const unsigned char* sb = ring.ptr + (size_t)slot * SLOT_BYTES;
+            for (int sp = 0; sp < spans_per_stage; ++sp) {
+            const int xbase = whole ? 0 : kbase + sp * xspan;
+            if (!whole) { consumer_sync(); stage_x(xbase); consumer_sync(); }
+            // this warp's units of the span (of the whole stage when everything is staged at once)
+            const int u0 = whole ? (warp * units) / GW : sp * units_x + ux0;
+            const int u1 = whole ? ((warp + 1) * units) / GW : sp * units_x + ux1;
 #pragma unroll 2
             for (int u = u0; u < u1; ++u) {
                 const int ku = u * UNIT;                 // offset inside the stage
@@ -287,6 +303,7 @@ __device__ __forceinline__ bool consume_gemv(const Phase& P, const Ring& ring, u
                     }
                 }
             }
+            }   // spans of the stage
             __syncwarp();
             if (lane == 0) mbar_arrive(&ring.empty[slot]);     // this warp is done reading the slot
         }

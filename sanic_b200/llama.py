@@ -1,11 +1,13 @@
-"""Llama-3.2-1B-architecture decode step as a captured launch list.
+"""Llama-3.2-1B-architecture decode step as a schedule over named buffers, instantiated as a machine.
 
-Mirrors the stateful-stepping API of the reference (`Graph::compile_for` ->
-`StepProgram::instantiate` -> `Machine::step`, src/graph.rs:231-356 of the reference project)
-for the decode graph of examples/llama3_2.rs:112-253, with a leading batch axis and a shared
-scalar position. The emitter's product is an ordered stage list (Fused / Elementwise / Gather,
-src/partition.rs:44-98); state (KV caches, position, token) lives in device buffers owned by
-the machine, and a step is one CUDA-graph replay with no host writes.
+The decode graph of examples/llama3_2.rs:112-253 of the reference project, with a leading batch axis and a
+shared scalar position, is written down the way the reference's emitter hands a step to its runtime: a buffer
+table (weights under their checkpoint names, states, intermediates), an ordered stage list (Fused / Elementwise /
+Gather, src/partition.rs:44-98) whose pointer fields name table buffers, the roots (state successors first,
+src/graph.rs:164-177) and which roots were compiled in place. `Graph::compile_for` -> `StepProgram::instantiate`
+-> `Machine::step` (src/graph.rs:231-356) are then the generic `sanic_b200.schedule` calls: the machine
+allocates the states (KV caches, token, position) zero-filled, binds the weights by name, wires every state's
+successor to the next step's input, and a step is one CUDA-graph replay with no host writes.
 
 Storage declarations (the graph's, not the kernels'): weights bf16 or int4+bf16 scales; caches
 bf16; the residual stream is pinned f32; every activation a projection reads, and q, are
@@ -21,6 +23,8 @@ import torch
 from . import _abi as abi
 from .backend import (CompileError, CudaDevice, RunError, carrier_contraction, carrier_extremum_index,
                       carrier_online_softmax)
+from .checkpoint import _LAYER
+from .schedule import ScheduleBuilder, view_tensor
 
 LLAMA_3_2_1B = dict(vocab=128256, layers=16, hidden=2048, q_heads=32, kv_heads=8, head_dim=64, ffn=8192)
 
@@ -87,34 +91,32 @@ def random_weights(cfg: dict, seed: int, device, w4: bool = False, w4_head: bool
     return w
 
 
+def weight_bindings(cfg: dict, w: dict) -> dict:
+    """The weight dictionary under the graph's input names (the checkpoint's tensor names; int4 scales under
+    `<name>.scales`)."""
+    out = {"model.embed_tokens.weight": w["embed"], "model.norm.weight": w["final_norm"]}
+    if "sembed" in w:
+        out["model.embed_tokens.weight.scales"] = w["sembed"]
+    for l in range(cfg["layers"]):
+        for key, suffix in _LAYER.items():
+            out[f"model.layers.{l}.{suffix}"] = w[key][l]
+            if key.startswith("w") and ("s" + key[1:]) in w:
+                out[f"model.layers.{l}.{suffix}.scales"] = w["s" + key[1:]][l]
+    return out
+
+
 class LlamaMachine:
-    """The instantiated step program: owns state buffers, replays one captured graph per step."""
+    """The decode step as a machine: owns the state buffers, replays one captured step per call."""
 
     def __init__(self, dev: CudaDevice, cfg: dict, weights: dict, ctx: int, batch: int, w4: bool = False,
                  capture: bool = True, fused: bool = True, persistent: bool = False):
         self.dev, self.cfg, self.ctx, self.batch, self.w4, self.fused = dev, dict(cfg), ctx, batch, w4, fused
-        H, F, V, L = cfg["hidden"], cfg["ffn"], cfg["vocab"], cfg["layers"]
-        Hq, Hkv, D = cfg["q_heads"], cfg["kv_heads"], cfg["head_dim"]
+        H, Hq, Hkv, D = cfg["hidden"], cfg["q_heads"], cfg["kv_heads"], cfg["head_dim"]
         if H != Hq * D or Hq % Hkv or D not in (64, 128):
             raise CompileError("invalid graph: hidden must equal q_heads*head_dim and head_dim must be 64 or 128")
         if ctx % 8:
             raise CompileError("invalid input declaration: the cache sequence extent must be a multiple of 8")
-        td, B = dev.torch_device, batch
-        z = lambda shape, dt: torch.zeros(shape, dtype=dt, device=td)
         self.w = weights
-        self.tokens = z((B,), torch.int32)
-        self.position = z((1,), torch.int32)
-        self.x = z((B, H), torch.float32)
-        self.xn = z((B, H), torch.bfloat16)
-        self.q = z((B, Hq * D), torch.float32)
-        self.k = z((B, Hkv * D), torch.float32)
-        self.v = z((B, Hkv * D), torch.float32)
-        self.qb = z((B, Hq, D), torch.bfloat16)
-        self.att = z((B, Hq, D), torch.bfloat16)
-        self.h = z((B, F), torch.bfloat16)
-        self.logits = z((B, V), torch.float32)
-        self.kcache = [z((B, Hkv, ctx, D), torch.bfloat16) for _ in range(L)]   # [kv, seq, hd]
-        self.vcache = [z((B, Hkv, D, ctx), torch.bfloat16) for _ in range(L)]   # [kv, hd, seq]
         self.table = dev.rope_table(llama3_inv_freq(D // 2) if cfg.get("llama3_rope", 1) else
                                     [math.exp(i * (-math.log(cfg.get("theta", ROPE_THETA)) / (D // 2))) for i in range(D // 2)],
                                     ctx)
@@ -122,129 +124,202 @@ class LlamaMachine:
         # chunks of the key axis per (batch, kv head): about 64 CTAs in all, and two chunks while the (batch, kv head)
         # pairs alone do not fill the SMs (measured at ctx ~1k: 8 chunks best at batch 1; at batch 16 two chunks give
         # 1.251 ms/step against 1.298 with one and 1.303 with four); at least 2 tiles of 64 keys per chunk
-        want = max(-(-64 // (B * Hkv)), 2 if B * Hkv <= 148 else 1)
+        want = max(-(-64 // (batch * Hkv)), 2 if batch * Hkv <= 148 else 1)
         self.n_splits = max(1, min(max(1, tiles // 2), want))
-        # the machine owns its scratch: two machines stepping on different streams must not share one
-        self.partials = z((dev.lib.sanic_attn_decode_scratch_bytes(B, Hq, D, self.n_splits) // 4,), torch.float32)
-        self.amax_scratch = z((B * 2 * 256,), torch.float32)
-        self.stream = torch.cuda.Stream(device=td)
+        self.stream = torch.cuda.Stream(device=dev.torch_device)
         self._host_position = 0
         self.persistent = persistent
+        self.captured = bool(capture)
         self._build()
-        self.captured = False
-        if capture:
-            self.capture()
+        self._instantiate()
 
-    # ── stage list ──
-    def _gemv(self, x, names, layer, outs, epilogue=abi.EPI_STORE, residual=None, out_dtype=abi.F32, norm=None,
+    # ── the schedule: buffer table, stages, roots ──
+    def _names(self, l, key):
+        name = f"model.layers.{l}.{_LAYER[key]}" if l is not None else {"embed": "model.embed_tokens.weight"}[key]
+        return name
+
+    def _gemv(self, b, x, keys, layer, outs, K, rows, epilogue=abi.EPI_STORE, residual=None, out_dtype=abi.F32, norm=None,
               rope_layer=None):
-        ws = [self.w[n][layer] if layer is not None else self.w[n] for n in names]
-        if layer is not None:
-            sc = [self.w["s" + n[1:]][layer] for n in names] if self.w4 else None
-        else:       # the tied table: quantised when it came with scales
-            sc = [self.w["s" + n] for n in names] if ws[0].dtype == torch.uint8 else None
+        """One contraction stage: activations `x` against the weight matrices `keys` of `layer` (None: the tied table)."""
+        names = [self._names(layer, k) for k in keys]
+        quant = self.w[keys[0]][layer].dtype == torch.uint8 if layer is not None else self.w["embed"].dtype == torch.uint8
         s = abi.StageDesc()
         s.stage_kind, s.op = abi.STAGE_FUSED, abi.OP_GEMV
-        s.carrier = carrier_contraction(abi.I4 if sc is not None else abi.BF16)
-        g = self.dev.gemv_params(x, ws, outs, sc, epilogue, residual, out_dtype)
+        s.carrier = carrier_contraction(abi.I4 if quant else abi.BF16)
+        g = s.u.gemv
+        g.batch, g.K, g.weight_dtype, g.group, g.n_segments = self.batch, K, (abi.I4 if quant else abi.BF16), 64, len(keys)
+        refs = {}
+        for i, n in enumerate(names):
+            g.rows[i] = rows[i]
+            refs[f"gemv.w[{i}]"] = n
+            if quant:
+                refs[f"gemv.scales[{i}]"] = n + ".scales"
+        for i, o in enumerate(outs):
+            refs[f"gemv.out[{i}]"] = o
+        g.out_dtype, g.epilogue = out_dtype, epilogue
+        if residual is not None:
+            refs["gemv.residual"] = residual
         if norm is not None:      # the RMSNorm cone of the residual stream is inlined into the fold's leaf
-            g.norm_x, g.norm_gamma, g.norm_eps = self.x.data_ptr(), norm.data_ptr(), float(self.cfg.get("eps", 1e-5))
+            refs["gemv.norm_x"], refs["gemv.norm_gamma"] = "x", norm
+            g.norm_eps = float(self.cfg.get("eps", 1e-5))
+        else:
+            refs["gemv.x"] = x
         if rope_layer is not None:
             cfg = self.cfg
-            g.rope_table, g.rope_position = self.table.data_ptr(), self.position.data_ptr()
-            g.rope_q_out = self.qb.data_ptr()
-            g.rope_k_cache, g.rope_v_cache = self.kcache[rope_layer].data_ptr(), self.vcache[rope_layer].data_ptr()
+            refs["gemv.rope_table"], refs["gemv.rope_position"], refs["gemv.rope_q_out"] = "rope_table", "position", "q_rope"
+            refs["gemv.rope_k_cache"], refs["gemv.rope_v_cache"] = f"cache.{rope_layer}.key.next", f"cache.{rope_layer}.value.next"
             g.rope_q_heads, g.rope_kv_heads, g.rope_head_dim, g.rope_ctx = cfg["q_heads"], cfg["kv_heads"], cfg["head_dim"], self.ctx
-        s.u.gemv = g
-        return s
+        b.stage(s, refs)
 
-    def _rmsnorm(self, gamma):
+    def _rmsnorm(self, b, gamma):
         s = abi.StageDesc()
         s.stage_kind, s.op = abi.STAGE_ELEMENTWISE, abi.OP_RMSNORM
-        s.u.rmsnorm.x, s.u.rmsnorm.gamma = self.x.data_ptr(), gamma.data_ptr()
         s.u.rmsnorm.rows, s.u.rmsnorm.n, s.u.rmsnorm.eps = self.batch, self.cfg["hidden"], float(self.cfg.get("eps", 1e-5))
-        s.u.rmsnorm.out = self.xn.data_ptr()
-        return s
+        b.stage(s, {"rmsnorm.x": "x", "rmsnorm.gamma": gamma, "rmsnorm.out": "xn"})
 
     def _build(self):
-        """The launch list. fused=True: 5 launches per layer (norm and RoPE/cache write ride the projections);
-        fused=False: one stage per graph cone (9 per layer), kept for comparison and tests."""
-        cfg, B = self.cfg, self.batch
-        Hq, Hkv, D = cfg["q_heads"], cfg["kv_heads"], cfg["head_dim"]
+        """fused=True: 5 stages per layer (norm and RoPE/cache write ride the projections); fused=False: one stage per
+        graph cone (8 per layer), kept for comparison and tests."""
+        cfg, B, dev = self.cfg, self.batch, self.dev
+        H, F, V, L = cfg["hidden"], cfg["ffn"], cfg["vocab"], cfg["layers"]
+        Hq, Hkv, D, ctx = cfg["q_heads"], cfg["kv_heads"], cfg["head_dim"], self.ctx
         fused = self.fused
         # as separate launches, every CTA re-deriving the normalised rows costs more than a launch at larger batch;
         # the single-kernel step derives them once per stage, so it inlines the norm at any batch
         inline_norm = fused and (B <= 4 or self.persistent)
-        st = []
+        b = ScheduleBuilder()
+        # inputs: the weights under their checkpoint names, the RoPE table, and the states
+        self.bindings = weight_bindings(cfg, self.w)
+        for name, t in self.bindings.items():
+            shape = tuple(t.shape)
+            if t.dtype == torch.uint8:
+                shape = shape[:-1] + (shape[-1] * 2,)      # declared in elements, stored two per byte
+            b.input(name, abi.dtype_of_torch(t.dtype), shape)
+        b.input("rope_table", abi.F32, tuple(self.table.shape))
+        self.bindings["rope_table"] = self.table
+        b.input("tokens", abi.U32, (B,))
+        b.input("position", abi.U32, (1,))
+        for l in range(L):
+            b.input(f"cache.{l}.key", abi.BF16, (B, Hkv, ctx, D))      # [kv, seq, hd]
+            b.input(f"cache.{l}.value", abi.BF16, (B, Hkv, D, ctx))    # [kv, hd, seq]
+        # state successors: every one of them overwrites its predecessor (the cache row write is the conditional store
+        # of where(coord == position, new, cache); token and position are read before they are written within a step)
+        for l in range(L):
+            b.scratch(f"cache.{l}.key.next", abi.BF16, (B, Hkv, ctx, D))
+            b.scratch(f"cache.{l}.value.next", abi.BF16, (B, Hkv, D, ctx))
+        b.scratch("tokens.next", abi.U32, (B,))
+        b.scratch("position.next", abi.U32, (1,))
+        # intermediates
+        b.scratch("x", abi.F32, (B, H))
+        b.scratch("xn", abi.BF16, (B, H))
+        if not fused:
+            b.scratch("q", abi.F32, (B, Hq * D)); b.scratch("k", abi.F32, (B, Hkv * D)); b.scratch("v", abi.F32, (B, Hkv * D))
+        b.scratch("q_rope", abi.BF16, (B, Hq, D))
+        b.scratch("attended", abi.BF16, (B, Hq, D))
+        b.scratch("h", abi.BF16, (B, F))
+        b.scratch("logits", abi.F32, (B, V))
+        b.scratch("attn.partials", abi.F32, (dev.lib.sanic_attn_decode_scratch_bytes(B, Hq, D, self.n_splits) // 4,))
+        b.scratch("argmax.scratch", abi.F32, (B * 2 * 256,))
+
+        quant_table = self.w["embed"].dtype == torch.uint8
         s = abi.StageDesc()
         s.stage_kind, s.op = abi.STAGE_GATHER, abi.OP_EMBED
-        s.u.embed.table, s.u.embed.tokens = self.w["embed"].data_ptr(), self.tokens.data_ptr()
-        s.u.embed.batch, s.u.embed.hidden, s.u.embed.vocab = B, cfg["hidden"], cfg["vocab"]
-        s.u.embed.out = self.x.data_ptr()
-        if self.w["embed"].dtype == torch.uint8:
-            s.u.embed.scales, s.u.embed.table_dtype, s.u.embed.group = self.w["sembed"].data_ptr(), abi.I4, 64
-        st.append(s)
-        for l in range(cfg["layers"]):
+        s.u.embed.batch, s.u.embed.hidden, s.u.embed.vocab = B, H, V
+        refs = {"embed.table": "model.embed_tokens.weight", "embed.tokens": "tokens", "embed.out": "x"}
+        if quant_table:
+            s.u.embed.table_dtype, s.u.embed.group = abi.I4, 64
+            refs["embed.scales"] = "model.embed_tokens.weight.scales"
+        b.stage(s, refs)
+        qkv_rows = [Hq * D, Hkv * D, Hkv * D]
+        for l in range(L):
+            attn_norm, mlp_norm = self._names(l, "attn_norm"), self._names(l, "mlp_norm")
             if fused:
                 if not inline_norm:
-                    st.append(self._rmsnorm(self.w["attn_norm"][l]))
-                st.append(self._gemv(self.xn, ["wq", "wk", "wv"], l, [], abi.EPI_ROPE_CACHE,
-                                     norm=self.w["attn_norm"][l] if inline_norm else None, rope_layer=l))
+                    self._rmsnorm(b, attn_norm)
+                self._gemv(b, "xn", ["wq", "wk", "wv"], l, [], H, qkv_rows, abi.EPI_ROPE_CACHE,
+                           norm=attn_norm if inline_norm else None, rope_layer=l)
             else:
-                st.append(self._rmsnorm(self.w["attn_norm"][l]))
-                st.append(self._gemv(self.xn, ["wq", "wk", "wv"], l, [self.q, self.k, self.v]))
+                self._rmsnorm(b, attn_norm)
+                self._gemv(b, "xn", ["wq", "wk", "wv"], l, ["q", "k", "v"], H, qkv_rows)
                 s = abi.StageDesc()
                 s.stage_kind, s.op = abi.STAGE_ELEMENTWISE, abi.OP_ROPE_CACHE
                 r = s.u.rope_cache
-                r.q, r.k, r.v = self.q.data_ptr(), self.k.data_ptr(), self.v.data_ptr()
-                r.q_out, r.k_cache, r.v_cache = self.qb.data_ptr(), self.kcache[l].data_ptr(), self.vcache[l].data_ptr()
-                r.table, r.position = self.table.data_ptr(), self.position.data_ptr()
-                r.batch, r.q_heads, r.kv_heads, r.head_dim, r.ctx = B, Hq, Hkv, D, self.ctx
-                st.append(s)
+                r.batch, r.q_heads, r.kv_heads, r.head_dim, r.ctx = B, Hq, Hkv, D, ctx
+                b.stage(s, {"rope_cache.q": "q", "rope_cache.k": "k", "rope_cache.v": "v", "rope_cache.q_out": "q_rope",
+                            "rope_cache.k_cache": f"cache.{l}.key.next", "rope_cache.v_cache": f"cache.{l}.value.next",
+                            "rope_cache.table": "rope_table", "rope_cache.position": "position"})
             s = abi.StageDesc()
             s.stage_kind, s.op = abi.STAGE_FUSED, abi.OP_DECODE_ATTN
             s.carrier = carrier_online_softmax(abi.BF16)
-            s.u.decode, _ = self.dev.decode_params(self.qb, self.kcache[l], self.vcache[l], 1, v_transposed=True,
-                                                   n_splits=self.n_splits, kv_len_dev=self.position, out=self.att,
-                                                   partials=self.partials, out_dtype=abi.BF16)
-            st.append(s)
-            st.append(self._gemv(self.att.view(B, Hq * D), ["wo"], l, [self.x], abi.EPI_RESIDUAL_ADD, self.x))
+            p = s.u.decode
+            p.k_batch_stride, p.k_head_stride, p.k_seq_stride = Hkv * ctx * D, ctx * D, D
+            p.v_batch_stride, p.v_head_stride, p.v_row_stride = Hkv * D * ctx, D * ctx, ctx
+            p.v_transposed, p.batch, p.q_heads, p.kv_heads, p.head_dim = 1, B, Hq, Hkv, D
+            p.kv_len, p.window, p.n_splits, p.scale = 1, 0, self.n_splits, 1.0 / math.sqrt(D)
+            p.out_dtype, p.kv_cap = abi.BF16, ctx
+            b.stage(s, {"decode.q": "q_rope", "decode.k": f"cache.{l}.key.next", "decode.v": f"cache.{l}.value.next",
+                        "decode.kv_len_dev": "position", "decode.partials": "attn.partials", "decode.out": "attended"})
+            self._gemv(b, "attended", ["wo"], l, ["x"], Hq * D, [H], abi.EPI_RESIDUAL_ADD, "x")
             if inline_norm:
-                st.append(self._gemv(self.xn, ["wgate", "wup"], l, [self.h], abi.EPI_SILU_MUL, None, abi.BF16,
-                                     norm=self.w["mlp_norm"][l]))
+                self._gemv(b, "xn", ["wgate", "wup"], l, ["h"], H, [F, F], abi.EPI_SILU_MUL, None, abi.BF16, norm=mlp_norm)
             else:
-                st.append(self._rmsnorm(self.w["mlp_norm"][l]))
-                st.append(self._gemv(self.xn, ["wgate", "wup"], l, [self.h], abi.EPI_SILU_MUL, None, abi.BF16))
-            st.append(self._gemv(self.h, ["wdown"], l, [self.x], abi.EPI_RESIDUAL_ADD, self.x))
+                self._rmsnorm(b, mlp_norm)
+                self._gemv(b, "xn", ["wgate", "wup"], l, ["h"], H, [F, F], abi.EPI_SILU_MUL, None, abi.BF16)
+            self._gemv(b, "h", ["wdown"], l, ["x"], F, [H], abi.EPI_RESIDUAL_ADD, "x")
         if inline_norm:
-            st.append(self._gemv(self.xn, ["embed"], None, [self.logits], norm=self.w["final_norm"]))
+            self._gemv(b, "xn", ["embed"], None, ["logits"], H, [V], norm="model.norm.weight")
         else:
-            st.append(self._rmsnorm(self.w["final_norm"]))
-            st.append(self._gemv(self.xn, ["embed"], None, [self.logits]))
+            self._rmsnorm(b, "model.norm.weight")
+            self._gemv(b, "xn", ["embed"], None, ["logits"], H, [V])
         s = abi.StageDesc()
         s.stage_kind, s.op = abi.STAGE_FUSED, abi.OP_ARGMAX
         s.carrier = carrier_extremum_index()
-        s.u.argmax.x, s.u.argmax.rows, s.u.argmax.n = self.logits.data_ptr(), B, cfg["vocab"]
-        s.u.argmax.out, s.u.argmax.scratch = self.tokens.data_ptr(), self.amax_scratch.data_ptr()
-        st.append(s)
+        s.u.argmax.rows, s.u.argmax.n = B, V
+        b.stage(s, {"argmax.x": "logits", "argmax.out": "tokens.next", "argmax.scratch": "argmax.scratch"})
         s = abi.StageDesc()
         s.stage_kind, s.op = abi.STAGE_ELEMENTWISE, abi.OP_ADVANCE
-        s.u.advance.position = self.position.data_ptr()
-        st.append(s)
-        arr = (abi.StageDesc * len(st))(*st)
-        h = C.c_void_p()
-        self.dev._check(self.dev.lib.sanic_program_create(self.dev.h, arr, len(st), C.byref(h)), "program_create")
-        self.prog = h
-        self.n_stages = len(st)
-        self.kernel_count = int(self.dev.lib.sanic_program_kernel_count(h))
+        b.stage(s, {"advance.position": "position.next"})
+        # roots: state successors first (src/graph.rs:164-177), then the outputs
+        self.state_roots = []
+        for l in range(L):
+            self.state_roots.append((f"cache.{l}.key", b.root(f"cache.{l}.key.next", in_place_of=f"cache.{l}.key")))
+            self.state_roots.append((f"cache.{l}.value", b.root(f"cache.{l}.value.next", in_place_of=f"cache.{l}.value")))
+        self.token_root = b.root("tokens.next", in_place_of="tokens")
+        self.state_roots.append(("tokens", self.token_root, 1))          # indices are exact or wrong: pinned at u32
+        self.state_roots.append(("position", b.root("position.next", in_place_of="position"), 1))
+        self.logits_root = b.root("logits")
+        self.n_stages = len(b.stages)
+        self.prog = b.compile(dev)
 
-    def capture(self):
-        torch.cuda.synchronize(self.dev.torch_device)
-        fn = self.dev.lib.sanic_program_capture_persistent if self.persistent else self.dev.lib.sanic_program_capture
-        rc = fn(self.prog, C.c_void_p(self.stream.cuda_stream))
-        self.dev._check(rc, "program_capture")
-        self.captured = True
-        self.kernel_count = int(self.dev.lib.sanic_program_kernel_count(self.prog))   # kernels one replay starts
+    def _instantiate(self):
+        td, L = self.dev.torch_device, self.cfg["layers"]
+        torch.cuda.synchronize(td)
+        st = C.c_void_p(self.stream.cuda_stream)
+        if self.captured:
+            self.machine = self.prog.instantiate(self.state_roots, self.bindings, abi.BF16,
+                                                 outputs=[("token", self.token_root), ("logits", self.logits_root)],
+                                                 persistent=self.persistent, stream=st)
+            state = lambda name: view_tensor(self.machine.state(name), td)
+            self.kernel_count = self.machine.kernel_count       # kernels one replay starts
+            self.logits = view_tensor(self.machine.output("logits"), td)
+            self._states = None
+        else:
+            # no frozen step: every step is a run of the schedule with the states bound like any other input
+            # (Program::try_run); the in-place roots still write their predecessors' buffers
+            z = lambda d: torch.zeros(d[3], dtype={abi.BF16: torch.bfloat16, abi.U32: torch.int32}[d[2]], device=td)
+            decl = {d[0]: d for d in self.prog.buffer_decls}
+            self._states = {name: z(decl[name]) for name, *_ in self.state_roots}
+            state = lambda name: self._states[name]
+            self.machine = None
+            self.kernel_count = self.n_stages + 1
+            outs = self.prog.try_run(dict(self.bindings, **self._states), stream=st)     # also allocates the scratch
+            self.stream.synchronize()
+            for t in self._states.values():
+                t.zero_()
+            self.logits = view_tensor(outs[self.logits_root], td)
+        self.kcache = [state(f"cache.{l}.key") for l in range(L)]
+        self.vcache = [state(f"cache.{l}.value") for l in range(L)]
+        self.tokens, self.position = state("tokens"), state("position")
 
     # ── Machine::step ──
     def set_state(self, tokens, position: int):
@@ -258,33 +333,28 @@ class LlamaMachine:
         self._host_position = int(position)
         torch.cuda.synchronize(self.dev.torch_device)
 
-    def step(self, timed: bool = False):
-        """One decode step: token <- argmax(logits(token, position)); position += 1. Returns device seconds if timed."""
+    def _guard(self):
         # the position lives on the device; the host keeps its own count so that a step whose cache row would fall
         # outside the cache is refused here instead of being clamped (and reported) by the kernels
         if self._host_position >= self.ctx:
             raise RunError(f"step: position {self._host_position} is outside the cache extent {self.ctx}")
         self._host_position += 1
+
+    def step(self, timed: bool = False):
+        """One decode step: token <- argmax(logits(token, position)); position += 1. Returns device seconds if timed."""
+        self._guard()
         st = C.c_void_p(self.stream.cuda_stream)
-        if self.captured:
-            sec = C.c_double(0.0)
-            rc = self.dev.lib.sanic_program_step(self.prog, st, C.byref(sec) if timed else None)
-            self.dev._check(rc, "program_step")
-            return sec.value if timed else None
-        self.dev._check(self.dev.lib.sanic_program_run(self.prog, st), "program_run")
+        if self.machine is not None:
+            return self.machine.step(stream=st, timed=timed)
+        self.prog.try_run(dict(self.bindings, **self._states), stream=st)
         return None
 
     def step_stage_times(self):
         """One decode step with a device time per stage (MetalDevice::run_kernel_timed): list of seconds."""
-        if self._host_position >= self.ctx:
-            raise RunError(f"step: position {self._host_position} is outside the cache extent {self.ctx}")
-        self._host_position += 1
-        st = C.c_void_p(self.stream.cuda_stream)
-        cap = 4 * self.n_stages + 8
-        buf = (C.c_double * cap)()
-        n = C.c_int32(0)
-        self.dev._check(self.dev.lib.sanic_program_stage_times(self.prog, st, buf, cap, C.byref(n)), "program_stage_times")
-        return [buf[i] for i in range(n.value)]
+        if self.machine is None:
+            raise RunError("step_stage_times needs a captured machine")
+        self._guard()
+        return self.machine.stage_times(stream=C.c_void_p(self.stream.cuda_stream), cap=4 * self.n_stages + 8)
 
     def generate(self, prompts, new_tokens: int):
         """Greedy decoding (the loop of examples/llama3_2.rs:577-664): `prompts` is one equal-length list of token ids per
@@ -337,8 +407,16 @@ class LlamaMachine:
                 n += t.numel() * t.element_size()
         return n
 
+    def close(self):
+        if getattr(self, "machine", None) is not None:
+            self.machine.close()
+            self.machine = None
+        if getattr(self, "prog", None) is not None:
+            self.prog.close()
+            self.prog = None
+
     def __del__(self):
         try:
-            self.dev.lib.sanic_program_destroy(self.prog)
+            self.close()
         except Exception:
             pass

@@ -84,7 +84,8 @@ def lockstep(machines, o, cfg, prefill, steps, rng, label=""):
                 assert np.all(np.abs(ol[bad, got[bad]] - top[bad, -1]) <= tol)
                 st["ties"] += int(bad.size)
                 st["worst_gap"] = min(st["worst_gap"], float(gaps.min()))
-                m.set_state(ocur, prefill + s + 1)      # continue both sides from the same token
+                if s + 1 < steps:
+                    m.set_state(ocur, prefill + s + 1)      # continue both sides from the same token
     return stats
 
 

@@ -72,6 +72,9 @@ def test_struct_sizes_match_the_header():
 #include <stddef.h>
 #include "sanic_b200.h"
 int main(void) {
+  printf("%zu %zu %zu %zu %zu %zu %zu %zu %zu %zu ", sizeof(sanic_buffer_decl), sizeof(sanic_reloc), sizeof(sanic_schedule_desc),
+         sizeof(sanic_binding), sizeof(sanic_buffer_view), sizeof(sanic_state_decl), offsetof(sanic_stage_desc, u.embed.scales),
+         offsetof(sanic_decode_params, kv_cap), offsetof(sanic_attn_params, accum_dtype), offsetof(sanic_peer_exchange, spin_limit));
   printf("%zu %zu %zu %zu %zu %zu %zu %zu %zu %zu %zu %zu %zu %zu %zu %zu %zu\n", sizeof(sanic_device_specs), sizeof(sanic_carrier_desc),
          sizeof(sanic_attn_params), sizeof(sanic_decode_params), sizeof(sanic_gemm_rmsnorm_params),
          sizeof(sanic_gemv_params), sizeof(sanic_rope_cache_params), sizeof(sanic_stage_desc),
@@ -86,7 +89,10 @@ int main(void) {
         exe = os.path.join(d, "p")
         subprocess.run(["gcc", "-I", os.path.join(ROOT, "include"), c, "-o", exe], check=True)
         got = [int(t) for t in subprocess.run([exe], capture_output=True, text=True, check=True).stdout.split()]
-    want = [C.sizeof(abi.DeviceSpecs), C.sizeof(abi.CarrierDesc), C.sizeof(abi.AttnParams), C.sizeof(abi.DecodeParams),
+    want = [C.sizeof(abi.BufferDecl), C.sizeof(abi.Reloc), C.sizeof(abi.ScheduleDesc), C.sizeof(abi.Binding), C.sizeof(abi.BufferView),
+            C.sizeof(abi.StateDecl), abi.StageDesc.u.offset + abi._StageUnion.embed.offset + abi._EmbedStage.scales.offset,
+            abi.DecodeParams.kv_cap.offset, abi.AttnParams.accum_dtype.offset, abi.PeerExchange.spin_limit.offset,
+            C.sizeof(abi.DeviceSpecs), C.sizeof(abi.CarrierDesc), C.sizeof(abi.AttnParams), C.sizeof(abi.DecodeParams),
             C.sizeof(abi.GemmRmsnormParams), C.sizeof(abi.GemvParams), C.sizeof(abi.RopeCacheParams),
             C.sizeof(abi.StageDesc), abi.StageDesc.u.offset, C.sizeof(abi.PeerExchange), abi.PeerExchange.epoch.offset,
             C.sizeof(abi.ExprOp), C.sizeof(abi.Operand), abi.Operand.gather_extent.offset, C.sizeof(abi.GenericDesc),

@@ -1,0 +1,154 @@
+"""Schedules over a buffer table on the device: bind-by-name runs, rebinding without rebuilding, replays whose
+fed-back state is one buffer (a root compiled in place) or two that trade places (ping-pong), and machines
+(reference src/compile.rs:132-229,820-1035, src/graph.rs:231-356; its tests: tests/graph.rs, tests/compile.rs).
+Every value is checked against the CPU oracle."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import oracle as orc
+from test_schedule_cpu import gemv_stage
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def dev():
+    from sanic_b200 import CudaDevice
+    return CudaDevice(0)
+
+
+def bf16t(a, dev):
+    bits = orc.to_bf16_bits(a)
+    return torch.tensor(bits.view(np.int16), device=dev.torch_device).view(torch.bfloat16), orc.from_bf16_bits(bits)
+
+
+def nerr(got, exp):
+    got, exp = np.asarray(got, dtype=np.float64), np.asarray(exp, dtype=np.float64)
+    assert got.shape == exp.shape and np.all(np.isfinite(got))
+    return float(np.max(np.abs(got - exp) / (1.0 + np.abs(exp))))
+
+
+def accumulate_schedule(in_place):
+    """acc' = acc + W x: one contraction with the residual-add epilogue; the root is fed back into `acc`."""
+    from sanic_b200 import abi
+    from sanic_b200.schedule import ScheduleBuilder
+    b = ScheduleBuilder()
+    b.input("w", abi.BF16, (64, 128))
+    b.input("x", abi.BF16, (2, 128))
+    b.input("acc", abi.F32, (2, 64))
+    b.scratch("acc.next", abi.F32, (2, 64))
+    s = gemv_stage(128, 64, batch=2)
+    s.u.gemv.epilogue = abi.EPI_RESIDUAL_ADD
+    b.stage(s, {"gemv.x": "x", "gemv.w[0]": "w", "gemv.out[0]": "acc.next", "gemv.residual": "acc"})
+    b.root("acc.next", in_place_of="acc" if in_place else None)
+    return b
+
+
+def test_run_binds_by_name_and_rebinding_does_not_rebuild(dev):
+    from sanic_b200.schedule import view_tensor
+    rng = orc.Xorshift(0x5C4ED)
+    prog = accumulate_schedule(in_place=False).compile(dev)
+    w1, w1v = bf16t(0.1 * rng.normal(64, 128), dev)
+    w2, w2v = bf16t(0.1 * rng.normal(64, 128), dev)
+    x, xv = bf16t(rng.normal(2, 128), dev)
+    acc = torch.tensor(rng.normal(2, 64), dtype=torch.float32, device=dev.torch_device)
+    accv = acc.cpu().numpy().astype(np.float64)
+    for w, wv in ((w1, w1v), (w2, w2v), (w1, w1v)):       # other buffers under the same names: no recompilation
+        (out,) = prog.try_run({"x": x, "acc": acc, "w": w})      # any order: binding is by name
+        dev.sync()
+        got = view_tensor(out, dev.torch_device).cpu().numpy()
+        assert nerr(got, accv + orc.gemv_bf16w(orc.to_bf16_bits(wv), xv)) <= 1e-5
+        assert tuple(out.shape[i] for i in range(out.rank)) == (2, 64)
+    assert torch.equal(acc.cpu(), torch.tensor(accv, dtype=torch.float32))      # a plain run never writes its inputs
+
+
+@pytest.mark.parametrize("in_place", [True, False])
+@pytest.mark.parametrize("persistent", [False])
+def test_replay_feedback_in_place_and_ping_pong(dev, in_place, persistent):
+    from sanic_b200.schedule import view_tensor
+    rng = orc.Xorshift(0xFEED)
+    prog = accumulate_schedule(in_place).compile(dev)
+    w, wv = bf16t(0.1 * rng.normal(64, 128), dev)
+    x, xv = bf16t(rng.normal(2, 128), dev)
+    acc = torch.zeros(2, 64, dtype=torch.float32, device=dev.torch_device)
+    st = torch.cuda.Stream(device=dev.torch_device)
+    import ctypes as C
+    rep = prog.capture({"w": w, "x": x, "acc": acc}, [(0, "acc")], persistent=persistent, stream=C.c_void_p(st.cuda_stream))
+    # one buffer when the root overwrites its predecessor, two frozen steps trading buffers otherwise
+    assert rep.parities == (1 if in_place else 2)
+    step_val = orc.gemv_bf16w(orc.to_bf16_bits(wv), xv)
+    exp = np.zeros((2, 64))
+    for n in range(1, 6):
+        sec = rep.step(stream=C.c_void_p(st.cuda_stream), timed=True)
+        assert sec > 0.0
+        exp = (exp.astype(np.float32) + step_val.astype(np.float32)).astype(np.float64)     # f32 accumulation, as the device stores it
+        got = view_tensor(rep.last_output(0), dev.torch_device).cpu().numpy()
+        assert nerr(got, exp) <= 1e-5, n
+    if in_place:
+        assert view_tensor(rep.last_output(0), dev.torch_device).data_ptr() == acc.data_ptr()
+    rep.close()
+
+
+def test_machine_allocates_zeroed_states_and_names_outputs(dev):
+    from sanic_b200 import abi
+    from sanic_b200.schedule import ProgramError, view_tensor
+    import ctypes as C
+    rng = orc.Xorshift(0x3AC)
+    prog = accumulate_schedule(in_place=True).compile(dev)
+    w, wv = bf16t(0.1 * rng.normal(64, 128), dev)
+    x, xv = bf16t(rng.normal(2, 128), dev)
+    st = torch.cuda.Stream(device=dev.torch_device)
+    sp = C.c_void_p(st.cuda_stream)
+    m = prog.instantiate([("acc", 0)], {"w": w, "x": x}, abi.F32, outputs=[("total", 0)], stream=sp)
+    state = view_tensor(m.state("acc"), dev.torch_device)
+    assert torch.count_nonzero(state) == 0                       # StepProgram::instantiate zero-fills the states
+    for _ in range(3):
+        m.step(stream=sp)
+    st.synchronize()
+    exp = 3.0 * orc.gemv_bf16w(orc.to_bf16_bits(wv), xv)
+    assert nerr(view_tensor(m.output("total"), dev.torch_device).cpu().numpy(), exp) <= 1e-5
+    with pytest.raises(ProgramError, match="no output named `nope`"):
+        m.output("nope")
+    # host-written inputs are read by the next replay: change x in place, the frozen step sees it
+    x.zero_()
+    torch.cuda.synchronize()
+    m.step(stream=sp)
+    st.synchronize()
+    assert nerr(view_tensor(m.output("total"), dev.torch_device).cpu().numpy(), exp) <= 1e-5
+    m.close()
+
+
+def test_generated_kernel_as_a_schedule_stage(dev):
+    """A carrier no specialised kernel matches runs as a generated stage whose operands are table buffers:
+    row sums of x (the reference's `[3, 7]` pin, tests/compile.rs:13-40, at another size) feeding a second
+    generated stage that adds a bias: two stages, one intermediate, all through the buffer table."""
+    from sanic_b200 import abi, emitter as em
+    from sanic_b200.schedule import ScheduleBuilder, view_tensor
+    rows, n = 5, 300
+    rng = orc.Xorshift(0x6E4)
+    xv = orc.round_to(orc.DT_F32, rng.normal(rows, n))
+    bv = orc.round_to(orc.DT_F32, rng.normal(rows))
+    x = torch.tensor(xv, dtype=torch.float32, device=dev.torch_device)
+    bias = torch.tensor(bv, dtype=torch.float32, device=dev.torch_device)
+    d1 = em.Description((rows,), [em.Operand(0, abi.F32, [n], 1)], carrier=em.carrier_sum(em.load(0)), stream=n, lanes=32)
+    d2 = em.Description((rows,), [em.Operand(0, abi.F32, [1]), em.Operand(1, abi.F32, [1])], value=em.load(0) + em.load(1))
+    k1, k2 = em.GenericKernel(dev, d1), em.GenericKernel(dev, d2)
+    b = ScheduleBuilder()
+    b.input("x", abi.F32, (rows, n))
+    b.input("bias", abi.F32, (rows,))
+    b.scratch("sums", abi.F32, (rows,))
+    b.scratch("y", abi.F32, (rows,))
+    for kern, refs in ((k1, {"generic.buffers[0]": "x", "generic.out": "sums"}),
+                       (k2, {"generic.buffers[0]": "sums", "generic.buffers[1]": "bias", "generic.out": "y"})):
+        s = abi.StageDesc()
+        s.stage_kind, s.op = abi.STAGE_FUSED, abi.OP_GENERIC
+        s.u.generic.kernel, s.u.generic.n_buffers = kern.h, len(refs) - 1
+        b.stage(s, refs)
+    b.root("y")
+    prog = b.compile(dev)
+    (out,) = prog.try_run({"x": x, "bias": bias})
+    dev.sync()
+    exp = orc.round_to(orc.DT_F32, np.array([np.sum(xv[r]) for r in range(rows)])) + bv
+    assert nerr(view_tensor(out, dev.torch_device).cpu().numpy(), exp) <= 1e-5
+    prog.close(); k1.close(); k2.close()
