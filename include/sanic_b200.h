@@ -66,6 +66,16 @@ typedef struct {
 } sanic_device_specs;
 int32_t sanic_specs(sanic_ctx* ctx, sanic_device_specs* out);
 
+/* Measured facts next to the datasheet ones: what a fitted DeviceSpecs carries (src/cost.rs:62-119) and what the
+ * reference's in-context timing measures (src/compile.rs:1348-1630). Both probes are tiny, bounded kernels.
+ * sanic_probe_sfu: `ex2.approx` per clock per SM with `warps_per_sm` resident warps (one CTA per SM); mode 0 = the
+ * exponentials alone, 1 = + the scale-and-shift FMA per element, 2 = + the row-sum add, 3 = + the bf16x2 pack: the inner
+ * loop of the online-softmax warps. *clk_per_128_per_warp (optional) is the raw figure: clocks per 128 elements per lane.
+ * sanic_probe_stream: GB/s of a read-only sweep of `buffer` (best of `repeats`), the rate an HBM-bound fold is held to. */
+int32_t sanic_probe_sfu(sanic_ctx* ctx, int32_t warps_per_sm, int32_t mode, int32_t iters, void* stream, double* exp_per_clk_per_sm,
+                        double* clk_per_128_per_warp);
+int32_t sanic_probe_stream(sanic_ctx* ctx, const void* buffer, size_t bytes, int32_t repeats, void* stream, double* gb_per_s);
+
 int32_t sanic_alloc(sanic_ctx* ctx, size_t bytes, void** dptr);
 int32_t sanic_free(sanic_ctx* ctx, void* dptr);
 int32_t sanic_upload(sanic_ctx* ctx, void* dst_dev, const void* src_host, size_t bytes, void* stream);
@@ -388,6 +398,12 @@ int32_t sanic_program_step(sanic_program* prog, void* stream, double* gpu_second
  * receives min(cap, stages) entries and *n_out their count; a program captured in its single-kernel form
  * reports one entry per phase (argmax is two). The step is a real one: state advances. Synchronises `stream`. */
 int32_t sanic_program_stage_times(sanic_program* prog, void* stream, double* seconds, int32_t cap, int32_t* n_out);
+/* A finer view of one step of a program captured in its single-kernel form (the per-kernel breakdown of the
+ * reference's SANIC_DEBUG=4 replay, src/compile.rs:1147-1346, inside one kernel): per phase, seconds from the phase's
+ * start to (0) its activations staged in shared memory, (1) its last contraction done, (2) its sums and epilogue done,
+ * (3) the grid barrier that ends it released, as block 0 saw them; phases that are not contractions report 0, 0, 0 and
+ * their whole time. `out` receives 4 * min(cap, phases) numbers. The step is a real one. Synchronises `stream`. */
+int32_t sanic_program_phase_profile(sanic_program* prog, void* stream, double* out, int32_t cap, int32_t* n_out);
 
 /* ── schedules over a buffer table: binding by name on every run, replays with state feedback, machines ──
  *
@@ -447,6 +463,7 @@ int32_t sanic_schedule_capture(sanic_schedule* s, const sanic_binding* bindings,
                                sanic_replay** out);
 int32_t sanic_replay_step(sanic_replay* r, void* stream, double* gpu_seconds);           /* MetalReplay::step_timed */
 int32_t sanic_replay_stage_times(sanic_replay* r, void* stream, double* seconds, int32_t cap, int32_t* n_out);
+int32_t sanic_replay_phase_profile(sanic_replay* r, void* stream, double* out, int32_t cap, int32_t* n_out);
 int32_t sanic_replay_output(sanic_replay* r, int32_t root, sanic_buffer_view* out);       /* MetalReplay::last_outputs */
 int32_t sanic_replay_kernel_count(sanic_replay* r);
 int32_t sanic_replay_parities(sanic_replay* r);                                           /* 1, or 2 when feedback swaps */

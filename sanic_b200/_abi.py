@@ -166,6 +166,8 @@ PROTOTYPES = {
     "sanic_last_error": (C.c_char_p, [vp]),
     "sanic_version": (C.c_char_p, []),
     "sanic_specs": (i32, [vp, C.POINTER(DeviceSpecs)]),
+    "sanic_probe_sfu": (i32, [vp, i32, i32, i32, vp, C.POINTER(C.c_double), C.POINTER(C.c_double)]),
+    "sanic_probe_stream": (i32, [vp, vp, C.c_size_t, i32, vp, C.POINTER(C.c_double)]),
     "sanic_alloc": (i32, [vp, C.c_size_t, C.POINTER(vp)]),
     "sanic_free": (i32, [vp, vp]),
     "sanic_upload": (i32, [vp, vp, vp, C.c_size_t, vp]),
@@ -228,6 +230,8 @@ PROTOTYPES = {
                                         i32, i32, vp, C.POINTER(vp)]),
     "sanic_machine_output": (i32, [vp, C.c_char_p, C.POINTER(BufferView)]),
     "sanic_machine_state": (i32, [vp, C.c_char_p, C.POINTER(BufferView)]),
+    "sanic_program_phase_profile": (i32, [vp, vp, C.POINTER(C.c_double), i32, C.POINTER(i32)]),
+    "sanic_replay_phase_profile": (i32, [vp, vp, C.POINTER(C.c_double), i32, C.POINTER(i32)]),
     "sanic_nccl_unique_id": (i32, [C.POINTER(C.c_uint8)]),
     "sanic_nccl_init": (i32, [vp, i32, i32, C.POINTER(C.c_uint8)]),
     "sanic_nccl_shutdown": (i32, [vp]),

@@ -142,6 +142,15 @@ __device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_
 
 __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 2, 256;" ::: "memory"); }
 
+// Block 0 leaves a clock stamp (profile of the phase it is in; null = off)
+__device__ __forceinline__ void stamp(unsigned long long* prof, int slot) {
+    if (prof && blockIdx.x == 0 && threadIdx.x == 0) {
+        unsigned long long g;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(g));
+        prof[slot] = g;
+    }
+}
+
 __device__ __forceinline__ bool grid_barrier(unsigned* bar, unsigned target, int* err, int* s_ok) {
     consumer_sync();
     if (threadIdx.x == 0) {
@@ -168,7 +177,8 @@ struct Ring {
 
 // The consumers' half of a contraction phase: weights come out of the ring, activations from L2.
 template <bool W4, int NT, bool DUAL, bool NORM>
-__device__ __forceinline__ bool consume_gemv(const Phase& P, const Ring& ring, uint32_t& drained, float* scratch, unsigned* gbar, int* err) {
+__device__ __forceinline__ bool consume_gemv(const Phase& P, const Ring& ring, uint32_t& drained, float* scratch, unsigned* gbar, int* err,
+                                             unsigned long long* prof) {
     using namespace gemv;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, t = lane & 3;
@@ -199,6 +209,7 @@ __device__ __forceinline__ bool consume_gemv(const Phase& P, const Ring& ring, u
     };
     if (NORM) row_norms<true>(P.fz, P.batch, P.K, scratch);   // once per phase
     if (whole) { stage_x(0); consumer_sync(); }
+    stamp(prof, 0);      // activations staged
     // this thread's activation rows (batch columns g and g + 8); a column beyond the batch reads zeros
     const bool xok0 = g < P.batch, xok1 = NT > 1 && (g + 8) < P.batch;
     const unsigned char* xs0 = xs + (size_t)(xok0 ? g : 0) * xpitch;
@@ -308,9 +319,11 @@ __device__ __forceinline__ bool consume_gemv(const Phase& P, const Ring& ring, u
             if (lane == 0) mbar_arrive(&ring.empty[slot]);     // this warp is done reading the slot
         }
         if (!ok) break;
+        stamp(prof, 1);      // the last tile's contraction is done (overwritten per tile)
         tile_finish<NT, DUAL, true>(acc, P.batch, P.segs, P.out_dtype, P.epilogue, P.residual, P.fz, 1, 0, seg, tile, scratch);
         consumer_sync();   // the scratch is reused by the next tile
     }
+    stamp(prof, 2);          // sums and epilogue done: the block is ready for the grid barrier
     return ok;
 }
 
@@ -332,7 +345,8 @@ __device__ __forceinline__ void amax_merge(float& v, int& i, float v2, int i2) {
 // ANY_I4 = false leaves the int4 bodies out for programs that have none.
 template <int NT, bool ANY_I4>
 __global__ void __launch_bounds__(THREADS, 1)
-decode_step_kernel(const Phase* __restrict__ phases, int n_phases, unsigned* bar, int* err, unsigned long long* stamps) {
+decode_step_kernel(const Phase* __restrict__ phases, int n_phases, unsigned* bar, int* err, unsigned long long* stamps,
+                   unsigned long long* prof) {
     extern __shared__ __align__(128) unsigned char dyn[];       // [weight ring][shared region]
     __shared__ Phase ph[2];
     __shared__ __align__(8) uint64_t s_full[SLOTS], s_empty[SLOTS];
@@ -411,14 +425,14 @@ decode_step_kernel(const Phase* __restrict__ phases, int n_phases, unsigned* bar
                 case PH_GEMV: {
                     float* scratch = (float*)shared;
                     switch (((P.variant >> 1) & 6) | (P.variant & 1)) {      // bit0: int4, bit1: silu-mul pair, bit2: inlined norm
-                        case 0: ok = consume_gemv<false, NT, false, false>(P, ring, drained, scratch, bar, err); break;
-                        case 1: if (ANY_I4) ok = consume_gemv<true, NT, false, false>(P, ring, drained, scratch, bar, err); break;
-                        case 2: ok = consume_gemv<false, NT, true, false>(P, ring, drained, scratch, bar, err); break;
-                        case 3: if (ANY_I4) ok = consume_gemv<true, NT, true, false>(P, ring, drained, scratch, bar, err); break;
-                        case 4: ok = consume_gemv<false, NT, false, true>(P, ring, drained, scratch, bar, err); break;
-                        case 5: if (ANY_I4) ok = consume_gemv<true, NT, false, true>(P, ring, drained, scratch, bar, err); break;
-                        case 6: ok = consume_gemv<false, NT, true, true>(P, ring, drained, scratch, bar, err); break;
-                        case 7: if (ANY_I4) ok = consume_gemv<true, NT, true, true>(P, ring, drained, scratch, bar, err); break;
+                        case 0: ok = consume_gemv<false, NT, false, false>(P, ring, drained, scratch, bar, err, prof ? prof + 3 * i : nullptr); break;
+                        case 1: if (ANY_I4) ok = consume_gemv<true, NT, false, false>(P, ring, drained, scratch, bar, err, prof ? prof + 3 * i : nullptr); break;
+                        case 2: ok = consume_gemv<false, NT, true, false>(P, ring, drained, scratch, bar, err, prof ? prof + 3 * i : nullptr); break;
+                        case 3: if (ANY_I4) ok = consume_gemv<true, NT, true, false>(P, ring, drained, scratch, bar, err, prof ? prof + 3 * i : nullptr); break;
+                        case 4: ok = consume_gemv<false, NT, false, true>(P, ring, drained, scratch, bar, err, prof ? prof + 3 * i : nullptr); break;
+                        case 5: if (ANY_I4) ok = consume_gemv<true, NT, false, true>(P, ring, drained, scratch, bar, err, prof ? prof + 3 * i : nullptr); break;
+                        case 6: ok = consume_gemv<false, NT, true, true>(P, ring, drained, scratch, bar, err, prof ? prof + 3 * i : nullptr); break;
+                        case 7: if (ANY_I4) ok = consume_gemv<true, NT, true, true>(P, ring, drained, scratch, bar, err, prof ? prof + 3 * i : nullptr); break;
                     }
                     break;
                 }
@@ -557,6 +571,7 @@ struct Plan {
     Phase* d_phases = nullptr;
     unsigned* d_bar = nullptr;
     unsigned long long* d_stamps = nullptr;
+    unsigned long long* d_prof = nullptr;     // 3 stamps per phase, taken by block 0 inside contraction phases
     int n = 0;
     int grid = 0;
     size_t smem = 0;
@@ -569,6 +584,7 @@ void destroy(Plan* plan) {
     if (plan->d_phases) cudaFree(plan->d_phases);
     if (plan->d_bar) cudaFree(plan->d_bar);
     if (plan->d_stamps) cudaFree(plan->d_stamps);
+    if (plan->d_prof) cudaFree(plan->d_prof);
     delete plan;
 }
 
@@ -669,6 +685,8 @@ int32_t build(sanic_ctx* ctx, const std::vector<sanic_stage_desc>& stages, Plan*
     if (e == cudaSuccess) e = cudaMalloc(&plan->d_bar, 2 * sizeof(unsigned));
     if (e == cudaSuccess) e = cudaMalloc(&plan->d_stamps, (ph.size() + 1) * sizeof(unsigned long long));
     if (e == cudaSuccess) e = cudaMemset(plan->d_stamps, 0, (ph.size() + 1) * sizeof(unsigned long long));
+    if (e == cudaSuccess) e = cudaMalloc(&plan->d_prof, 3 * ph.size() * sizeof(unsigned long long));
+    if (e == cudaSuccess) e = cudaMemset(plan->d_prof, 0, 3 * ph.size() * sizeof(unsigned long long));
     if (e == cudaSuccess) e = cudaMemcpy(plan->d_phases, ph.data(), ph.size() * sizeof(Phase), cudaMemcpyHostToDevice);
     if (e != cudaSuccess) { destroy(plan); return sanic_fail(ctx, SANIC_ERR_CUDA, std::string("step: ") + cudaGetErrorString(e)); }
     *out = plan;
@@ -683,7 +701,8 @@ int32_t launch(sanic_ctx* ctx, Plan* plan, cudaStream_t stream) {
     unsigned* bar = plan->d_bar;
     int* err = ctx->status_dev;
     unsigned long long* stamps = plan->d_stamps;
-    void* args[] = {(void*)&phases_arg, (void*)&n, (void*)&bar, (void*)&err, (void*)&stamps};
+    unsigned long long* prof = plan->d_prof;
+    void* args[] = {(void*)&phases_arg, (void*)&n, (void*)&bar, (void*)&err, (void*)&stamps, (void*)&prof};
     cudaError_t e = cudaLaunchCooperativeKernel(plan->kernel, dim3(plan->grid), dim3(THREADS), args, plan->smem, stream);
     if (e != cudaSuccess) return sanic_fail(ctx, SANIC_ERR_CUDA, std::string("step: ") + cudaGetErrorString(e));
     return SANIC_OK;
@@ -697,6 +716,25 @@ int32_t phase_times(sanic_ctx* ctx, Plan* plan, double* seconds, int cap) {
     SANIC_CUDA_CHECK(ctx, cudaMemcpy(h.data(), plan->d_stamps, h.size() * sizeof(unsigned long long), cudaMemcpyDeviceToHost));
     int n = std::min(cap, plan->n);
     for (int i = 0; i < n; ++i) seconds[i] = (double)(h[i + 1] - h[i]) * 1e-9;
+    return n;
+}
+
+// The same step in finer grain, for contraction phases (block 0's view): seconds from the phase's start to its
+// activations being staged, to the end of its last tile's contraction, to the end of its sums and epilogue, and to the
+// release of the grid barrier that ends it. Four numbers per phase; a phase that is not a contraction reports 0, 0, 0
+// and its whole time. Returns the number of phases written.
+int32_t phase_profile(sanic_ctx* ctx, Plan* plan, double* out, int cap) {
+    std::vector<unsigned long long> h(plan->n + 1), pr(3 * (size_t)plan->n);
+    SANIC_CUDA_CHECK(ctx, cudaMemcpy(h.data(), plan->d_stamps, h.size() * sizeof(unsigned long long), cudaMemcpyDeviceToHost));
+    SANIC_CUDA_CHECK(ctx, cudaMemcpy(pr.data(), plan->d_prof, pr.size() * sizeof(unsigned long long), cudaMemcpyDeviceToHost));
+    int n = std::min(cap, plan->n);
+    for (int i = 0; i < n; ++i) {
+        for (int k = 0; k < 3; ++k) {
+            const unsigned long long t = pr[3 * (size_t)i + k];
+            out[4 * i + k] = (t >= h[i] && t <= h[i + 1]) ? (double)(t - h[i]) * 1e-9 : 0.0;
+        }
+        out[4 * i + 3] = (double)(h[i + 1] - h[i]) * 1e-9;
+    }
     return n;
 }
 

@@ -17,6 +17,8 @@ int32_t build(sanic_ctx* ctx, const std::vector<sanic_stage_desc>& stages, Plan*
 int32_t launch(sanic_ctx* ctx, Plan* plan, cudaStream_t stream);
 int phases(const Plan* plan);
 int32_t phase_times(sanic_ctx* ctx, Plan* plan, double* seconds, int cap);
+// Four numbers per phase of the last completed step: staged / contracted / finished / barrier released, in seconds from the phase's start.
+int32_t phase_profile(sanic_ctx* ctx, Plan* plan, double* out, int cap);
 void destroy(Plan* plan);
 
 }  // namespace step

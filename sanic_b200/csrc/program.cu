@@ -225,4 +225,18 @@ int32_t sanic_program_stage_times(sanic_program* p, void* stream, double* second
     return rc;
 }
 
+// A finer view of one step of a program captured in its single-kernel form: per phase, seconds from the phase's start to
+// (0) activations staged, (1) last contraction done, (2) sums and epilogue done, (3) the grid barrier released, as one
+// block saw them. `out` receives 4 * min(cap, phases) numbers. The step is a real one. Synchronises `stream`.
+int32_t sanic_program_phase_profile(sanic_program* p, void* stream, double* out, int32_t cap, int32_t* n_out) {
+    if (!p || !out || !n_out || cap < 0) return SANIC_ERR_INVALID;
+    sanic_ctx* ctx = p->ctx;
+    SANIC_REQUIRE(ctx, p->exec && p->plan, "program_phase_profile: capture the program in its single-kernel form first");
+    sanic_set_device(ctx);
+    SANIC_CUDA_CHECK(ctx, cudaGraphLaunch(p->exec, (cudaStream_t)stream));
+    SANIC_CUDA_CHECK(ctx, cudaStreamSynchronize((cudaStream_t)stream));
+    *n_out = sanic::step::phase_profile(ctx, p->plan, out, cap);
+    return SANIC_OK;
+}
+
 }  // extern "C"

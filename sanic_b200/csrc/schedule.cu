@@ -377,6 +377,15 @@ int32_t sanic_replay_stage_times(sanic_replay* r, void* stream, double* seconds,
     return rc;
 }
 
+int32_t sanic_replay_phase_profile(sanic_replay* r, void* stream, double* out, int32_t cap, int32_t* n_out) {
+    if (!r || r->parity.empty()) return SANIC_ERR_INVALID;
+    const int par = r->next;
+    r->next = (par + 1) % (int)r->parity.size();
+    int32_t rc = sanic_program_phase_profile(r->parity[par], stream, out, cap, n_out);
+    if (rc == SANIC_OK) ++r->steps; else r->sch->err = r->sch->ctx->err;
+    return rc;
+}
+
 int32_t sanic_replay_kernel_count(sanic_replay* r) { return (r && !r->parity.empty()) ? sanic_program_kernel_count(r->parity[0]) : -1; }
 int32_t sanic_replay_parities(sanic_replay* r) { return r ? (int32_t)r->parity.size() : -1; }
 

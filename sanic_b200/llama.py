@@ -356,6 +356,13 @@ class LlamaMachine:
         self._guard()
         return self.machine.stage_times(stream=C.c_void_p(self.stream.cuda_stream), cap=4 * self.n_stages + 8)
 
+    def step_phase_profile(self):
+        """One decode step of the single-kernel form with four clock stamps per phase (see Replay.phase_profile)."""
+        if self.machine is None or not self.persistent:
+            raise RunError("step_phase_profile needs a machine captured in its single-kernel form")
+        self._guard()
+        return self.machine.phase_profile(stream=C.c_void_p(self.stream.cuda_stream), cap=4 * self.n_stages + 8)
+
     def generate(self, prompts, new_tokens: int):
         """Greedy decoding (the loop of examples/llama3_2.rs:577-664): `prompts` is one equal-length list of token ids per
         batch row. The prompt is consumed one position per step through the same decode step (decode equals prefill,

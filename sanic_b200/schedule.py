@@ -253,6 +253,16 @@ class Replay:
             self.program._raise(rc, "stage_times")
         return [buf[i] for i in range(n.value)]
 
+    def phase_profile(self, stream=None, cap=4096):
+        """One step of a single-kernel replay, per phase: [staged, contracted, finished, barrier released] seconds."""
+        buf = (C.c_double * (4 * cap))()
+        n = C.c_int32(0)
+        st = stream if stream is not None else self.program.dev.stream()
+        rc = self.lib.sanic_replay_phase_profile(self.h, st, buf, cap, C.byref(n))
+        if rc != abi.OK:
+            self.program._raise(rc, "phase_profile")
+        return [[buf[4 * i + k] for k in range(4)] for i in range(n.value)]
+
     def last_output(self, root: int):
         v = abi.BufferView()
         rc = self.lib.sanic_replay_output(self.h, root, C.byref(v))
