@@ -193,7 +193,8 @@ def time_events(fn, steps, warmup, torch):
     return ts[len(ts) // 2] * 1e-3, ts[0] * 1e-3
 
 
-def suite(dev, torch, hbm_peak, tf_peak, quick, only=None, c2_shape=(4096, 2048, 8192), c3_shape=(8, 4096), fused=True, form="auto"):
+def suite(dev, torch, hbm_peak, tf_peak, quick, only=None, c2_shape=(4096, 2048, 8192), c3_shape=(8, 4096), fused=True, form="auto",
+          c4_layers=0):
     import numpy as np
     from sanic_b200 import llama
     out = {}
@@ -280,11 +281,12 @@ def suite(dev, torch, hbm_peak, tf_peak, quick, only=None, c2_shape=(4096, 2048,
     del q3, k3, v3, qr, kr
     torch.cuda.empty_cache()
     if want("probe"):
+      try:
         # measured device facts behind the bounds quoted for config 3 (exponentials per clock per SM, and what the softmax
         # warps' other instructions add) and for the HBM-bound folds (a read-only sweep of 4 GiB)
         import ctypes as C
         pr = {}
-        for warps in (4, 8, 16):
+        for warps in (4, 8):       # 16 warps of this probe (128 live values per lane) do not fit one SM's register file
             for mode, label in enumerate(("ex2", "ex2+fma", "ex2+fma+sum", "ex2+fma+sum+pack")):
                 rate, clk = C.c_double(0.0), C.c_double(0.0)
                 dev._check(dev.lib.sanic_probe_sfu(dev.h, warps, mode, 200, dev.stream(), C.byref(rate), C.byref(clk)), "probe_sfu")
@@ -297,8 +299,12 @@ def suite(dev, torch, hbm_peak, tf_peak, quick, only=None, c2_shape=(4096, 2048,
         del buf
         torch.cuda.empty_cache()
         out["probe"] = pr
+      except Exception as e:      # a probe must not take the rest of the suite with it
+        out["probe"] = {"error": repr(e)}
     # config 4: Llama-3.2-1B-architecture decode step, ctx 1024 (+32 steps), CUDA-graph replays
-    cfg = llama.LLAMA_3_2_1B
+    cfg = dict(llama.LLAMA_3_2_1B)
+    if c4_layers:       # a shallower stack of the same layers (small cases for profiling)
+        cfg["layers"] = c4_layers
     for name, batch, w4 in (("bf16_b1", 1, False), ("bf16_b16", 16, False), ("int4_b1", 1, True), ("int4_b16", 16, True)):
         if not want("c4_" + name):
             continue
@@ -512,7 +518,7 @@ def run_ours(args):
     if rank == 0 and world == 1 and not args.no_suite:
         try:
             line["suite"] = suite(dev, torch, hbm_peak, tf_peak, args.quick, args.only.split(",") if args.only else None,
-                                  tuple(int(t) for t in args.c2_shape.split(",")), tuple(int(t) for t in args.c3_shape.split(",")), not args.llama_unfused, args.llama_form)
+                                  tuple(int(t) for t in args.c2_shape.split(",")), tuple(int(t) for t in args.c3_shape.split(",")), not args.llama_unfused, args.llama_form, args.c4_layers)
         except Exception as e:  # the headline line must still print
             line["suite"] = {"error": repr(e)}
     if rank == 0:
@@ -546,6 +552,7 @@ def main():
     ap.add_argument("--exchange", default="auto", choices=["auto", "nccl", "peer"], help="how N > 1 ranks exchange their accumulators")
     ap.add_argument("--llama-form", default="auto", choices=["auto", "list", "persistent"],
                     help="decode step as the captured launch list, as one cooperative kernel, or whichever measured faster for the batch")
+    ap.add_argument("--c4-layers", type=int, default=0, help="layers of the suite's decode-step model (0: the architecture's 16)")
     ap.add_argument("--c3-shape", default="8,4096", help="batch,sequence of the suite's prefill attention")
     args = ap.parse_args()
     if args.warmup < 3:

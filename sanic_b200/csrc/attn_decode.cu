@@ -23,10 +23,10 @@ namespace {
 using namespace sanic;
 using namespace sanic::decode;
 
-template <int D, bool VT>
+template <int D, bool VT, bool SPLITP>
 __global__ void __launch_bounds__(128) attn_decode_kernel(sanic_decode_params p, int* counters, int* err) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
-    attn_decode_tile<D, VT>(p, counters, (int)blockIdx.x, (int)blockIdx.y, (int)blockIdx.z, smem_raw, (int)threadIdx.x, true, 0, err);
+    attn_decode_tile<D, VT, SPLITP>(p, counters, (int)blockIdx.x, (int)blockIdx.y, (int)blockIdx.z, smem_raw, (int)threadIdx.x, true, 0, err);
 }
 
 // Stage 2 on its own: merge n_parts raw accumulators and project.
@@ -57,7 +57,9 @@ __global__ void carrier_merge_kernel(const float* parts, int n_parts, int rows, 
 
 template <int D, bool VT>
 int32_t launch_decode(sanic_ctx* ctx, const sanic_decode_params& p, cudaStream_t st) {
-    auto kern = attn_decode_kernel<D, VT>;
+    // SANIC_DECODE_SPLIT_P=1: the bf16 remainder of P goes through a second MMA (error measurements, A/B timing)
+    static const bool split_p = getenv("SANIC_DECODE_SPLIT_P") && getenv("SANIC_DECODE_SPLIT_P")[0] == '1';
+    auto kern = split_p ? attn_decode_kernel<D, VT, true> : attn_decode_kernel<D, VT, false>;
     SANIC_CUDA_CHECK(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<D>::SMEM));
     int* counters = (int*)(p.partials + (size_t)p.batch * p.q_heads * p.n_splits * (D + 2));
     dim3 grid(p.n_splits, p.kv_heads, p.batch);
