@@ -175,6 +175,48 @@ struct Ring {
     unsigned char* ptr;                  // generic pointer to slot 0
 };
 
+// RMSNorm of up to two rows of 2048 values, staged as bf16 in shared memory, in one pass: thread t holds 8 consecutive
+// values of every row, so the sum of squares and the normalised row come from the same loads (one L2 round trip, not
+// two). Kept out of line: its live registers must not add to the contraction loop's.
+__device__ __noinline__ void stage_normed_rows(const Phase& P, float* scratch, unsigned char* xs, int xpitch) {
+    using namespace gemv;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+        float (*s_part)[GW] = reinterpret_cast<float (*)[GW]>(scratch + 16);
+        float4 xa[2], xb[2];
+        const uint4 gm = __ldg((const uint4*)(P.fz.norm_gamma + tid * 8));
+#pragma unroll
+        for (int n = 0; n < 2; ++n) {
+            if (n >= P.batch) break;
+            xa[n] = __ldcg((const float4*)(P.fz.norm_x + (size_t)n * P.K + tid * 8));
+            xb[n] = __ldcg((const float4*)(P.fz.norm_x + (size_t)n * P.K + tid * 8 + 4));
+        }
+#pragma unroll
+        for (int n = 0; n < 2; ++n) {
+            if (n >= P.batch) break;
+            float ss = xa[n].x * xa[n].x;
+            ss = fmaf(xa[n].y, xa[n].y, ss); ss = fmaf(xa[n].z, xa[n].z, ss); ss = fmaf(xa[n].w, xa[n].w, ss);
+            ss = fmaf(xb[n].x, xb[n].x, ss); ss = fmaf(xb[n].y, xb[n].y, ss); ss = fmaf(xb[n].z, xb[n].z, ss); ss = fmaf(xb[n].w, xb[n].w, ss);
+            ss = warp_sum(ss);
+            if (lane == 0) s_part[n][warp] = ss;
+        }
+        consumer_sync();
+#pragma unroll
+        for (int n = 0; n < 2; ++n) {
+            if (n >= P.batch) break;
+            float tot = 0.0f;
+#pragma unroll
+            for (int w = 0; w < GW; ++w) tot += s_part[n][w];
+            const float den = 1.0f / sqrtf(tot * (1.0f / (float)P.K) + P.fz.norm_eps);
+            uint4 r;
+            r.x = pack_bf16x2((xa[n].x * bf16lo(gm.x)) * den, (xa[n].y * bf16hi(gm.x)) * den);
+            r.y = pack_bf16x2((xa[n].z * bf16lo(gm.y)) * den, (xa[n].w * bf16hi(gm.y)) * den);
+            r.z = pack_bf16x2((xb[n].x * bf16lo(gm.z)) * den, (xb[n].y * bf16hi(gm.z)) * den);
+            r.w = pack_bf16x2((xb[n].z * bf16lo(gm.w)) * den, (xb[n].w * bf16hi(gm.w)) * den);
+            *(uint4*)(xs + (size_t)n * xpitch + tid * 16) = r;
+        }
+        consumer_sync();
+}
+
 // The consumers' half of a contraction phase: weights come out of the ring, activations from L2.
 template <bool W4, int NT, bool DUAL, bool NORM>
 __device__ __forceinline__ bool consume_gemv(const Phase& P, const Ring& ring, uint32_t& drained, float* scratch, unsigned* gbar, int* err,
@@ -207,8 +249,12 @@ __device__ __forceinline__ bool consume_gemv(const Phase& P, const Ring& ring, u
             *(uint4*)(xs + (size_t)n * xpitch + c * 16) = v;
         }
     };
-    if (NORM) row_norms<true>(P.fz, P.batch, P.K, scratch);   // once per phase
-    if (whole) { stage_x(0); consumer_sync(); }
+    if (NT == 1 && NORM && P.K == CONSUMERS * 8 && P.batch <= 2) {
+        stage_normed_rows(P, scratch, xs, xpitch);
+    } else {
+        if (NORM) row_norms<true>(P.fz, P.batch, P.K, scratch);   // once per phase
+        if (whole) { stage_x(0); consumer_sync(); }
+    }
     stamp(prof, 0);      // activations staged
     // this thread's activation rows (batch columns g and g + 8); a column beyond the batch reads zeros
     const bool xok0 = g < P.batch, xok1 = NT > 1 && (g + 8) < P.batch;
@@ -223,6 +269,10 @@ __device__ __forceinline__ bool consume_gemv(const Phase& P, const Ring& ring, u
         for (int mI = 0; mI < NM; ++mI)
 #pragma unroll
             for (int j = 0; j < NT; ++j) acc[mI][j][0] = acc[mI][j][1] = acc[mI][j][2] = acc[mI][j][3] = 0.0f;
+        // the residual this thread's epilogue will add: loaded now, so that its L2 round trip runs under the contraction
+        float res_pre = 0.0f;
+        const bool have_res = P.epilogue == SANIC_EPI_RESIDUAL_ADD && tid < 16 * P.batch;
+        if (have_res) res_pre = __ldcg(P.residual + (size_t)(tid / 16) * P.segs.rows[0] + tile * 16 + (tid % 16));
         // int4 with stages too short to carry their scales: scale rows of fragment rows g and g+8 in global memory
         const uint16_t* sr[NM][2];
         if (W4 && G.scale_row_bytes == 0) {
@@ -320,7 +370,7 @@ __device__ __forceinline__ bool consume_gemv(const Phase& P, const Ring& ring, u
         }
         if (!ok) break;
         stamp(prof, 1);      // the last tile's contraction is done (overwritten per tile)
-        tile_finish<NT, DUAL, true>(acc, P.batch, P.segs, P.out_dtype, P.epilogue, P.residual, P.fz, 1, 0, seg, tile, scratch);
+        tile_finish<NT, DUAL, true>(acc, P.batch, P.segs, P.out_dtype, P.epilogue, P.residual, P.fz, 1, 0, seg, tile, scratch, have_res, res_pre);
         consumer_sync();   // the scratch is reused by the next tile
     }
     stamp(prof, 2);          // sums and epilogue done: the block is ready for the grid barrier
@@ -378,6 +428,11 @@ decode_step_kernel(const Phase* __restrict__ phases, int n_phases, unsigned* bar
             const bool w4 = P.variant & 1, dual = (P.variant & 4) != 0;
             const Geom G = geom_of(w4, dual, P.K);
             const size_t full_row = w4 ? (size_t)P.K / 2 : (size_t)P.K * 2;
+            // The norm weight of an inlined RMSNorm is read once per step: cold in L2 by the time its phase starts
+            // (gigabytes have streamed through since) and on the consumers' critical path. The producers reach the phase
+            // a ring's depth early: ask L2 for it now.
+            if ((P.variant & 8) && lane == 0 && pw == 0)
+                asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(P.fz.norm_gamma), "r"(P.K * 2) : "memory");
             for (int gt = blockIdx.x; gt < P.n_blocks && ok; gt += gridDim.x) {
                 int seg, tile;
                 seg_of_tile(P.segs, P.n_segments, dual, gt, seg, tile);
@@ -419,8 +474,11 @@ decode_step_kernel(const Phase* __restrict__ phases, int n_phases, unsigned* bar
         if (blockIdx.x == 0 && tid == 0) { unsigned long long g; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(g)); stamps[0] = g; }
         for (int i = 0; i < n_phases && ok; ++i) {
             const Phase& P = ph[i & 1];
-            if (i + 1 < n_phases)   // next descriptor: in shared memory by the time the barrier releases
-                for (int w = tid; w < PW; w += CONSUMERS) ((int*)&ph[(i + 1) & 1])[w] = __ldg((const int*)&phases[i + 1] + w);
+            // The next descriptor: the table is cold in L2 (it is read once per step), so its load is issued now, into a
+            // register, and stored to shared memory only when the phase body is done: the miss runs under the phase.
+            static_assert(PW <= CONSUMERS, "one descriptor word per consumer thread");
+            int next_word = 0;
+            if (i + 1 < n_phases && tid < PW) next_word = __ldg((const int*)&phases[i + 1] + tid);
             switch (P.op) {
                 case PH_GEMV: {
                     float* scratch = (float*)shared;
@@ -545,6 +603,7 @@ decode_step_kernel(const Phase* __restrict__ phases, int n_phases, unsigned* bar
                     break;
                 default: break;
             }
+            if (i + 1 < n_phases && tid < PW) ((int*)&ph[(i + 1) & 1])[tid] = next_word;     // visible after the barrier's block syncs
             if (ok && i + 1 < n_phases) ok = grid_barrier(bar, (unsigned)(i + 1) * gridDim.x, err, &s_ok);
             if (blockIdx.x == 0 && tid == 0) { unsigned long long g; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(g)); stamps[i + 1] = g; }
         }

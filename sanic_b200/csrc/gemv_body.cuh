@@ -102,7 +102,7 @@ __host__ __device__ constexpr int scratch_floats() {
 template <int NT, bool DUAL, bool PERSIST>
 __device__ __forceinline__ void tile_finish(float (&acc)[DUAL ? 2 : 1][NT][4], int batch, const SegTable& segs, int out_dtype,
                                             int epilogue, const float* residual, const Fused& fz, int KS, int krank, int seg,
-                                            int tile, float* scratch) {
+                                            int tile, float* scratch, bool have_res = false, float res_pre = 0.0f) {
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, t = lane & 3;
     constexpr int NM = DUAL ? 2 : 1, RW = 8 * NT + 1;
@@ -150,13 +150,9 @@ __device__ __forceinline__ void tile_finish(float (&acc)[DUAL ? 2 : 1][NT][4], i
         asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
         if (krank != 0) return;
         block_sync<PERSIST>();
-    } else {
-        for (int idx = tid; idx < NM * 16 * 8 * NT; idx += GW * 32) {
-            const int n = idx % (8 * NT), r = (idx / (8 * NT)) % 16, mI = idx / (8 * NT * 16);
-            red[0][mI][r][n] = csum[mI][r][n];
-        }
-        block_sync<PERSIST>();
     }
+    // the epilogue reads the cluster total rank 0 published, or, without a K split, the block sum where it lies
+    const float (*fin)[16][RW] = (KS > 1) ? red[0] : csum;
     if (rope) {
         // thread (r < 8, n): partners a = row r (d0 = 8*sub + r) and b = row r + 8 (d0 + D/2)
         const int D = fz.head_dim, F = D / 2, tph = D / 16;
@@ -164,7 +160,7 @@ __device__ __forceinline__ void tile_finish(float (&acc)[DUAL ? 2 : 1][NT][4], i
         const int pos = *fz.rope_position;
         for (int idx = tid; idx < 8 * batch; idx += GW * 32) {
             const int n = idx / 8, r = idx % 8;
-            const float a = red[0][0][r][n], b = red[0][0][r + 8][n];
+            const float a = fin[0][r][n], b = fin[0][r + 8][n];
             const int d0 = 8 * sub + r;
             if (pos < 0 || pos >= fz.ctx) continue;
             if (seg < 2) {
@@ -187,14 +183,15 @@ __device__ __forceinline__ void tile_finish(float (&acc)[DUAL ? 2 : 1][NT][4], i
     void* outp = seg == 0 ? segs.out[0] : (seg == 1 ? segs.out[1] : segs.out[2]);
     for (int idx = tid; idx < 16 * batch; idx += GW * 32) {
         int n = idx / 16, r = idx % 16;  // consecutive threads -> consecutive rows (contiguous in out[n][row])
-        float y = red[0][0][r][n];
+        float y = fin[0][r][n];
         if (DUAL) {  // silu(a) * b = (a * 1/(1+exp(-a))) * b  (reference src/ir.rs:1500-1509)
-            const float ga = y, up = red[0][NM - 1][r][n];
+            const float ga = y, up = fin[NM - 1][r][n];
             float sig = 1.0f / (1.0f + expf(-ga));
             y = (ga * sig) * up;
         }
         size_t oi = (size_t)n * rows + row0 + r;
-        if (epilogue == SANIC_EPI_RESIDUAL_ADD) y = (PERSIST ? __ldcg(residual + oi) : residual[oi]) + y;
+        // `res_pre` is this thread's residual value when the caller loaded it ahead of the contraction (idx == tid then)
+        if (epilogue == SANIC_EPI_RESIDUAL_ADD) y = ((have_res && idx == tid) ? res_pre : (PERSIST ? __ldcg(residual + oi) : residual[oi])) + y;
         if (out_dtype == SANIC_BF16) ((uint16_t*)outp)[oi] = f32_to_bf16_bits(y);
         else ((float*)outp)[oi] = y;
     }
