@@ -161,6 +161,14 @@ size_t sanic_attn_decode_scratch_bytes(int32_t batch, int32_t q_heads, int32_t h
 /* Suggested number of chunks for this device and shape (a multiple of the SM count in CTAs). */
 int32_t sanic_attn_decode_suggest_splits(sanic_ctx* ctx, int32_t batch, int32_t kv_heads, int32_t head_dim, int64_t kv_len);
 
+/* The same fold with the (batch, kv head, key tile) space cut into one contiguous range per CTA of an exactly resident
+ * grid (stream-K), so that no partial last wave is paid when the key axis is short for the device (a per-device slice of a
+ * sharded cache). p->n_splits is the number of partial slots per row of `partials`: at least
+ * sanic_attn_decode_streamk_slots(); the scratch layout and size are those of sanic_attn_decode_splitkv for that n_splits.
+ * The chunk boundaries differ from the fixed-chunk form's; any chunking merges to the same value (src/interp.rs:538-554). */
+int32_t sanic_attn_decode_streamk(sanic_ctx* ctx, const sanic_decode_params* p, void* stream);
+int32_t sanic_attn_decode_streamk_slots(sanic_ctx* ctx, int32_t batch, int32_t kv_heads, int32_t head_dim);
+
 /* Same fold for callers that cannot allocate device memory. This entry point has no counterpart in
  * the reference. Some hosts of this library may not call cudaMalloc at the point where they decode:
  * a latency-critical serving loop where an allocation would synchronise the device, plugins that are handed a fixed arena by their framework, and
@@ -515,6 +523,15 @@ int32_t sanic_ipc_open(sanic_ctx* ctx, const uint8_t handle[64], void** dptr_out
 int32_t sanic_ipc_close(sanic_ctx* ctx, void* dptr);
 int32_t sanic_splitkv_decode_step_peer(sanic_ctx* ctx, const sanic_decode_params* p, const sanic_peer_exchange* x, void* out,
                                        int32_t out_dtype, void* stream);
+
+/* The multi-device step as ONE launch: the stream-K fold above whose stage 2, per (batch, kv head) group, stores the
+ * group's merged accumulators into every device's exchange buffer, publishes a per-group flag, and, after the CTA has
+ * finished its own range, waits (bounded; status 41 + rank on expiry) for the other devices' flags of that group, merges
+ * in rank order and projects into `out`. No second kernel, no collective. Buffers: sanic_peer_exchange_bytes_fused()
+ * bytes each, zero-filled, exchanged as for sanic_splitkv_decode_step_peer; p->out and p->carrier_out are not needed. */
+size_t sanic_peer_exchange_bytes_fused(int32_t rows /* batch * q_heads */, int32_t head_dim, int32_t nranks, int32_t groups /* batch * kv_heads */);
+int32_t sanic_splitkv_decode_step_fused(sanic_ctx* ctx, const sanic_decode_params* p, const sanic_peer_exchange* x, void* out,
+                                        int32_t out_dtype, void* stream);
 
 #ifdef __cplusplus
 }

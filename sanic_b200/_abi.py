@@ -180,6 +180,10 @@ PROTOTYPES = {
     "sanic_status_inject": (i32, [vp, i32]),
     "sanic_embed_gather_w4": (i32, [vp, vp, vp, vp, i32, i32, i32, i32, vp, vp]),
     "sanic_attn_decode_splitkv": (i32, [vp, C.POINTER(DecodeParams), vp]),
+    "sanic_attn_decode_streamk": (i32, [vp, C.POINTER(DecodeParams), vp]),
+    "sanic_attn_decode_streamk_slots": (i32, [vp, i32, i32, i32]),
+    "sanic_peer_exchange_bytes_fused": (C.c_size_t, [i32, i32, i32, i32]),
+    "sanic_splitkv_decode_step_fused": (i32, [vp, C.POINTER(DecodeParams), C.POINTER(PeerExchange), vp, i32, vp]),
     "sanic_attn_decode_splitkv_static": (i32, [vp, C.POINTER(DecodeParams), vp]),
     "sanic_attn_decode_static_scratch_capacity": (C.c_size_t, []),
     "sanic_attn_decode_scratch_bytes": (C.c_size_t, [i32, i32, i32, i32]),

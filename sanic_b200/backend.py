@@ -176,17 +176,25 @@ class CudaDevice:
         p.kv_cap = int(kv_cap if kv_cap is not None else k.shape[2])
         return p, partials
 
+    def streamk_slots(self, batch, kv_heads, head_dim):
+        return int(self.lib.sanic_attn_decode_streamk_slots(self.h, batch, kv_heads, head_dim))
+
     def attn_decode(self, q, k, v, kv_len, v_transposed=False, n_splits=None, window=0, scale=None,
-                    return_carrier=False, out_dtype=torch.bfloat16):
+                    return_carrier=False, out_dtype=torch.bfloat16, streamk=False, kv_len_dev=None):
+        """Split-KV decode fold. `streamk`: one contiguous range of the (batch, kv head, key tile) space per resident CTA
+        instead of n_splits fixed chunks per (batch, kv head)."""
         self._on_device("q", q, torch.bfloat16)
         self._on_device("k", k, torch.bfloat16, strided=True)      # slices of a longer cache are read in place
         self._on_device("v", v, torch.bfloat16, strided=True)
         B, Hq, D = q.shape
         out = self.empty((B, Hq, D), out_dtype)
         car = self.empty((B * Hq, D + 2), torch.float32) if return_carrier else None
+        if streamk:
+            n_splits = self.streamk_slots(B, k.shape[1], D)
         p, _keep = self.decode_params(q, k, v, kv_len, v_transposed, n_splits, window, scale, out=out, carrier_out=car,
-                                      out_dtype=abi.BF16 if out_dtype == torch.bfloat16 else abi.F32)
-        self._check(self.lib.sanic_attn_decode_splitkv(self.h, C.byref(p), self.stream()), "attn_decode_splitkv")
+                                      out_dtype=abi.BF16 if out_dtype == torch.bfloat16 else abi.F32, kv_len_dev=kv_len_dev)
+        fn = self.lib.sanic_attn_decode_streamk if streamk else self.lib.sanic_attn_decode_splitkv
+        self._check(fn(self.h, C.byref(p), self.stream()), "attn_decode")
         return (out, car) if return_carrier else out
 
     def carrier_merge(self, parts, out_dtype=torch.float32, return_carrier=False):

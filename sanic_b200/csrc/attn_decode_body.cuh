@@ -67,19 +67,30 @@ __device__ __forceinline__ void load_tile(const sanic_decode_params& p, const ui
 // Barrier over the 128 threads of one item (named barrier `id`; id 0 in a 128-thread CTA is the CTA barrier).
 __device__ __forceinline__ void tile_sync(int id) { asm volatile("bar.sync %0, 128;" ::"r"(id) : "memory"); }
 
-// One (chunk, kv head, batch) item of the fold, executed by 128 threads (tid in [0, 128)). `smem_raw` is the
-// caller's dynamic shared memory (Cfg<D>::SMEM bytes, 128-byte aligned); `pdl` as in gemv_tile; `bar_id` is the
-// named barrier the 128 threads meet on.
-template <int D, bool VT, bool SPLITP = false>
-__device__ __forceinline__ void attn_decode_tile(const sanic_decode_params& p, int* counters, int split, int hk, int b,
-                                                 unsigned char* smem_raw, int tid, bool pdl, int bar_id, int* err) {
-    const int warp = tid >> 5, lane = tid & 31;
-    const int g = lane >> 2, t = lane & 3;
-    const int group = p.q_heads / p.kv_heads;
-    constexpr int KS = D / 16;   // k-steps of the QK^T contraction
-    constexpr int NT = D / 8;    // n-tiles of the output
+// Cross-device exchange folded into the fold's own last arrivers (the fused form of the multi-device step): where the
+// merged raw accumulators of a (batch, kv head) group go besides carrier_out. Null pointer = single device.
+struct Exchange {
+    float* buf[8];               // every rank's exchange buffer as mapped here (buf[rank] is the local one)
+    int rank, nranks, groups;
+    unsigned epoch, spin_limit;
+    void* out; int out_dtype;    // the final projected output [B, Hq, D]
+};
+// Layout of a fused exchange buffer, in 4-byte words: flags [2 parities][8 ranks][groups], then data
+// [2 parities][nranks][rows][2 + D] (offsets are multiples of 4 words when groups is).
+__host__ __device__ inline size_t xchg_flag_words(int groups) { return (size_t)2 * 8 * ((groups + 3) / 4 * 4); }
 
-    if (pdl) { griddep_launch(); griddep_wait(); }   // q, the caches and the position come from the previous kernels of the step
+__device__ __forceinline__ unsigned ld_acquire_sys_u32(const unsigned* p) {
+    unsigned v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_release_sys_u32(unsigned* p, unsigned v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+// The visible tile range of the key axis: [T0, T1) in tiles of KT keys, keys [lo, hi).
+struct KeyRange { int lo, hi, T0, T1; };
+__device__ __forceinline__ KeyRange key_range(const sanic_decode_params& p, int tid, int* err) {
     // A visible length read from the device is never trusted beyond the cache extent the host vouched for: it is
     // clamped into [1, kv_cap] and the clamp is reported through the status word (the host turns code 52 into an error).
     int kv_len = p.kv_len_dev ? (*p.kv_len_dev + 1) : p.kv_len;
@@ -87,17 +98,40 @@ __device__ __forceinline__ void attn_decode_tile(const sanic_decode_params& p, i
         kv_len = kv_len < 1 ? 1 : p.kv_cap;
         if (tid == 0 && err) atomicCAS(err, 0, 52);
     }
-    const int hi = kv_len;
-    const int lo = (p.window > 0) ? max(0, kv_len - p.window) : 0;
-    const int T0 = lo / KT, T1 = (hi + KT - 1) / KT;
-    const int nT = T1 - T0;
-    const int t_begin = T0 + (int)(((long long)split * nT) / p.n_splits);
-    const int t_end = T0 + (int)(((long long)(split + 1) * nT) / p.n_splits);
+    KeyRange r;
+    r.hi = kv_len;
+    r.lo = (p.window > 0) ? max(0, kv_len - p.window) : 0;
+    r.T0 = r.lo / KT;
+    r.T1 = (r.hi + KT - 1) / KT;
+    return r;
+}
+
+// Stage 1 of one segment: tiles [t_begin, t_end) of the key axis of (batch b, kv head hk), folded by 128 threads
+// (tid in [0, 128)) into one raw accumulator per query head of the group, written to partial slot `slot` of the row.
+// Then the group's ticket: returns true in the CTA that is the last of the group's `n_parts` segments to arrive (the
+// partials of the whole group are then complete and visible to it). `smem_raw` is the caller's dynamic shared memory
+// (Cfg<D>::SMEM bytes, 128-byte aligned); `bar_id` is the named barrier the 128 threads meet on.
+template <int D, bool VT, bool SPLITP = false>
+__device__ __forceinline__ bool fold_segment(const sanic_decode_params& p, int* counters, int b, int hk, int t_begin, int t_end,
+                                             int lo, int hi, int slot, int n_parts, unsigned char* smem_raw, int tid, int bar_id) {
+    const int warp = tid >> 5, lane = tid & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int group = p.q_heads / p.kv_heads;
+    constexpr int KS = D / 16;   // k-steps of the QK^T contraction
+    constexpr int NT = D / 8;    // n-tiles of the output
     const int n_tiles = t_end - t_begin;
 
     const uint16_t* Kb = (const uint16_t*)p.k + (size_t)b * p.k_batch_stride + (size_t)hk * p.k_head_stride;
     const uint16_t* Vb = (const uint16_t*)p.v + (size_t)b * p.v_batch_stride + (size_t)hk * p.v_head_stride;
     const uint32_t smem_base = smem_u32(smem_raw);
+
+    // The first tiles do not depend on q: their copies are issued before q is read, so the two latencies overlap.
+    constexpr int STAGES = Cfg<D>::STAGES;
+#pragma unroll
+    for (int s = 0; s < STAGES - 1; ++s) {
+        if (s < n_tiles) load_tile<D, VT>(p, Kb, Vb, smem_base + s * Cfg<D>::STAGE_BYTES, (t_begin + s) * KT, hi, tid);
+        cp_async_commit();
+    }
 
     // Q fragments (read from L2: another SM may have written q earlier in the same kernel): row r = query head hk*group + r, zero beyond the group.
     uint32_t qa[KS][2];  // [ks][0] = (a0,a1) cols 2t,2t+1 ; [ks][1] = (a4,a5) cols 8+2t,+1 ; rows g (rows g+8 via qb)
@@ -118,14 +152,6 @@ __device__ __forceinline__ void attn_decode_tile(const sanic_decode_params& p, i
     for (int i = 0; i < NT; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f; }
     float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.0f, l1 = 0.0f;  // rows g and g+8 (log2 units)
     const float sl2 = p.scale * LOG2E;
-
-    constexpr int STAGES = Cfg<D>::STAGES;
-#pragma unroll
-    for (int s = 0; s < STAGES - 1; ++s) {
-        if (s < n_tiles) load_tile<D, VT>(p, Kb, Vb, smem_base + s * Cfg<D>::STAGE_BYTES, (t_begin + s) * KT, hi, tid);
-        cp_async_commit();
-    }
-
     for (int it = 0; it < n_tiles; ++it) {
         cp_async_wait<STAGES - 2>();
         tile_sync(bar_id);
@@ -259,23 +285,37 @@ __device__ __forceinline__ void attn_decode_tile(const sanic_decode_params& p, i
             float ra = (m > -INFINITY) ? exp2f(m - M) : 0.0f, rb = (mb > -INFINITY) ? exp2f(mb - M) : 0.0f;
             l = l * ra + lb * rb; ov = ov * ra + ob * rb; m = M;
         }
-        float* part = p.partials + (((size_t)b * p.q_heads + (size_t)hk * group + r) * p.n_splits + split) * W;
+        float* part = p.partials + (((size_t)b * p.q_heads + (size_t)hk * group + r) * p.n_splits + slot) * W;
         part[2 + d] = ov;
         if (d == 0) { part[0] = m * LN2; part[1] = l; }  // m back in natural-log units
     }
 
-    // stage 2 by the last CTA of this (batch, kv head)
+    // the group's ticket: the last of its n_parts segments to arrive owns stage 2
     __shared__ int s_last;
     __threadfence();
     tile_sync(bar_id);
     if (tid == 0) {
         int ticket = atomicAdd(&counters[b * p.kv_heads + hk], 1);
-        s_last = (ticket == p.n_splits - 1);
+        s_last = (ticket == n_parts - 1);
         if (s_last) counters[b * p.kv_heads + hk] = 0;  // ready for the next launch
     }
     tile_sync(bar_id);
-    if (!s_last) return;
-    __threadfence();
+    const bool last = s_last != 0;
+    tile_sync(bar_id);      // s_last may be rewritten by this CTA's next segment
+    if (last) __threadfence();
+    return last;
+}
+
+// Stage 2 of one (batch, kv head) group, by the CTA that arrived last: merges the group's n_parts partials left to right
+// with the derived combine, exports the merged raw accumulator and/or projects o / l. With an exchange, the merged raw
+// accumulators are also stored into slot `rank` of every device's exchange buffer and the group's flag is published
+// there (system-scope release); the cross-device merge is merge_group_remote, once the other devices' flags are in.
+template <int D>
+__device__ __forceinline__ void merge_group(const sanic_decode_params& p, int b, int hk, int n_parts, int tid, int bar_id,
+                                            const Exchange* x) {
+    const int group = p.q_heads / p.kv_heads;
+    const int W = D + 2;
+    const int rows = p.batch * p.q_heads;
     for (int idx = tid; idx < group * D; idx += 128) {
         int r = idx / D, d = idx % D;
         size_t row = (size_t)b * p.q_heads + (size_t)hk * group + r;
@@ -284,11 +324,11 @@ __device__ __forceinline__ void attn_decode_tile(const sanic_decode_params& p, i
         // independent of the combine chain so their latencies overlap. The combine itself runs
         // left to right over the chunks, as stage 2 of the split reduction does.
         float m = __ldcg(part), l = __ldcg(part + 1), ov = __ldcg(part + 2 + d);
-        for (int s0 = 1; s0 < p.n_splits; s0 += 8) {
+        for (int s0 = 1; s0 < n_parts; s0 += 8) {
             float mb[8], lb[8], ob[8];
 #pragma unroll
             for (int u = 0; u < 8; ++u) {
-                const bool in = s0 + u < p.n_splits;
+                const bool in = s0 + u < n_parts;
                 const float* pb = part + (size_t)(in ? s0 + u : 0) * W;
                 mb[u] = in ? __ldcg(pb) : -INFINITY; lb[u] = in ? __ldcg(pb + 1) : 0.0f; ob[u] = in ? __ldcg(pb + 2 + d) : 0.0f;
             }
@@ -303,12 +343,85 @@ __device__ __forceinline__ void attn_decode_tile(const sanic_decode_params& p, i
             c[2 + d] = ov;
             if (d == 0) { c[0] = m; c[1] = l; }
         }
-        if (p.out) {
+        if (x) {
+            const size_t data_off = xchg_flag_words(x->groups) + (size_t)(x->epoch & 1) * x->nranks * rows * W;
+            for (int q = 0; q < x->nranks; ++q) {
+                float* c = x->buf[q] + data_off + ((size_t)x->rank * rows + row) * W;
+                c[2 + d] = ov;
+                if (d == 0) { c[0] = m; c[1] = l; }
+            }
+        } else if (p.out) {
             float v = ov / l;  // project
             if (p.out_dtype == SANIC_BF16) ((uint16_t*)p.out)[row * D + d] = f32_to_bf16_bits(v);
             else ((float*)p.out)[row * D + d] = v;
         }
     }
+    if (x) {
+        // every thread's peer stores are fenced before the flag that vouches for them
+        __threadfence_system();
+        tile_sync(bar_id);
+        const int gi = b * p.kv_heads + hk;
+        if (tid < x->nranks)
+            st_release_sys_u32((unsigned*)x->buf[tid] + ((size_t)(x->epoch & 1) * 8 + x->rank) * ((x->groups + 3) / 4 * 4) + gi, x->epoch);
+    }
+}
+
+// The cross-device half of stage 2 for one group: waits (bounded) for every device's flag of this group in the local
+// exchange buffer, merges the devices' accumulators in rank order (= chunk order of the device-level split) and projects.
+// Returns false when a flag never arrived (status code 41 + rank of the missing device).
+template <int D>
+__device__ __forceinline__ bool merge_group_remote(const sanic_decode_params& p, int b, int hk, int tid, int bar_id, const Exchange* x,
+                                                   int* err) {
+    const int group = p.q_heads / p.kv_heads;
+    const int W = D + 2;
+    const int rows = p.batch * p.q_heads;
+    const int gi = b * p.kv_heads + hk;
+    __shared__ int s_ok;
+    if (tid == 0) {
+        const unsigned* flags = (const unsigned*)x->buf[x->rank] + (size_t)(x->epoch & 1) * 8 * ((x->groups + 3) / 4 * 4);
+        int ok = 1;
+        for (int q = 0; q < x->nranks && ok; ++q) {
+            unsigned spins = 0;
+            while (ld_acquire_sys_u32(flags + (size_t)q * ((x->groups + 3) / 4 * 4) + gi) != x->epoch) {
+                if (++spins > x->spin_limit) { if (err) atomicCAS(err, 0, 41 + q); ok = 0; break; }
+            }
+        }
+        s_ok = ok;
+    }
+    tile_sync(bar_id);
+    const bool ok = s_ok != 0;
+    tile_sync(bar_id);
+    if (!ok) return false;
+    const float* data = x->buf[x->rank] + xchg_flag_words(x->groups) + (size_t)(x->epoch & 1) * x->nranks * rows * W;
+    for (int idx = tid; idx < group * D; idx += 128) {
+        int r = idx / D, d = idx % D;
+        size_t row = (size_t)b * p.q_heads + (size_t)hk * group + r;
+        const float* pa = data + row * W;
+        float m = __ldcg(pa), l = __ldcg(pa + 1), ov = __ldcg(pa + 2 + d);
+        for (int q = 1; q < x->nranks; ++q) {
+            const float* pb = data + ((size_t)q * rows + row) * W;
+            const MloScale sc = mlo_rescale(m, __ldcg(pb));
+            l = l * sc.ra + __ldcg(pb + 1) * sc.rb; ov = ov * sc.ra + __ldcg(pb + 2 + d) * sc.rb; m = sc.m;
+        }
+        const float v = ov / l;
+        if (x->out_dtype == SANIC_BF16) ((uint16_t*)x->out)[row * D + d] = f32_to_bf16_bits(v);
+        else ((float*)x->out)[row * D + d] = v;
+    }
+    return true;
+}
+
+// One (chunk, kv head, batch) item of the fold in its fixed-chunk form: chunk `split` of n_splits equal tile ranges,
+// executed by 128 threads (tid in [0, 128)); `pdl` as in gemv_tile.
+template <int D, bool VT, bool SPLITP = false>
+__device__ __forceinline__ void attn_decode_tile(const sanic_decode_params& p, int* counters, int split, int hk, int b,
+                                                 unsigned char* smem_raw, int tid, bool pdl, int bar_id, int* err) {
+    if (pdl) { griddep_launch(); griddep_wait(); }   // q, the caches and the position come from the previous kernels of the step
+    const KeyRange kr = key_range(p, tid, err);
+    const int nT = kr.T1 - kr.T0;
+    const int t_begin = kr.T0 + (int)(((long long)split * nT) / p.n_splits);
+    const int t_end = kr.T0 + (int)(((long long)(split + 1) * nT) / p.n_splits);
+    if (fold_segment<D, VT, SPLITP>(p, counters, b, hk, t_begin, t_end, kr.lo, kr.hi, split, p.n_splits, smem_raw, tid, bar_id))
+        merge_group<D>(p, b, hk, p.n_splits, tid, bar_id, nullptr);
 }
 
 // Host side: the argument checks of one split-KV fold.

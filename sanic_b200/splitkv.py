@@ -38,11 +38,13 @@ def exchange_and_merge(local_carrier, merge_fn, group=None):
 class SplitKVDecoder:
     """One rank of a sequence-sharded decode. `k`, `v` are this rank's slices [B, Hkv, n_local, D] bf16."""
 
-    def __init__(self, dev, k, v, n_splits=None, init_nccl=True, exchange="nccl"):
-        """`exchange`: "nccl" (all-gather, then a merge kernel) or "peer" (one kernel stores the accumulators into
-        every peer's buffer over NVLink, waits for the others' flags and merges)."""
+    def __init__(self, dev, k, v, n_splits=None, init_nccl=True, exchange="nccl", force_exchange=False):
+        """`exchange`: "nccl" (all-gather, then a merge kernel), "peer" (a second kernel stores the accumulators into
+        every peer's buffer over NVLink, waits for the others' flags and merges) or "fused" (the whole step is one
+        launch: the stream-K fold whose last arrivers store, flag, wait and merge per (batch, kv head) group)."""
         self.dev, self.k, self.v = dev, k, v
         self.exchange = exchange
+        self.force_exchange = force_exchange      # run the exchange path even with one rank (tests)
         self.epoch = 0
         self._peer = None
         self.rank = dist.get_rank() if dist.is_initialized() else 0
@@ -50,6 +52,8 @@ class SplitKVDecoder:
         B, Hkv, n_local, D = k.shape
         self.n_local = n_local
         self.n_splits = n_splits or dev.suggest_splits(B, Hkv, D, n_local)
+        if exchange == "fused":
+            self.n_splits = dev.streamk_slots(B, Hkv, D)
         if self.world > 1 and init_nccl and exchange == "nccl":
             ident = torch.zeros(128, dtype=torch.uint8)
             if self.rank == 0:
@@ -72,7 +76,7 @@ class SplitKVDecoder:
                               out=torch.empty((B, Hq, D), dtype=torch.bfloat16, device=td))
         return self._bufs
 
-    def _peer_setup(self, rows, D):
+    def _peer_setup(self, rows, D, groups=0):
         """Allocate this rank's exchange buffer, trade IPC handles over torch.distributed, map the peers' buffers.
 
         Every rank takes the same collective calls whether or not its own part succeeded; the ranks then agree
@@ -83,7 +87,8 @@ class SplitKVDecoder:
         local = C.c_void_p()
         handle = (C.c_uint8 * 64)()
         try:
-            nbytes = int(lib.sanic_peer_exchange_bytes(rows, D, self.world))
+            nbytes = int(lib.sanic_peer_exchange_bytes_fused(rows, D, self.world, groups) if groups
+                         else lib.sanic_peer_exchange_bytes(rows, D, self.world))
             dev._check(lib.sanic_alloc(dev.h, nbytes, C.byref(local)), "alloc")
             dev._check(lib.sanic_memset(dev.h, local, 0, nbytes, dev.stream()), "memset")
             dev.sync()
@@ -147,6 +152,22 @@ class SplitKVDecoder:
         b = self._buffers(B, Hq, D)
         p, _keep = self.dev.decode_params(q, self.k, self.v, self.n_local, n_splits=self.n_splits, scale=scale,
                                           carrier_out=b["carrier"], out=None)
+        if self.exchange == "fused" and self.world == 1 and not self.force_exchange:
+            # one device: nothing to exchange, the stream-K fold projects straight into the output
+            p.out, p.out_dtype, p.carrier_out = b["out"].data_ptr(), abi.BF16, None
+            self.dev._check(self.dev.lib.sanic_attn_decode_streamk(self.dev.h, C.byref(p), self.dev.stream()), "attn_decode_streamk")
+            return b["out"]
+        if self.exchange == "fused":
+            if self._peer is None:
+                self._peer_setup(B * Hq, D, groups=B * self.k.shape[1])
+            self.epoch += 1
+            x = self._peer["x"]
+            x.epoch = self.epoch
+            p.carrier_out = None
+            rc = self.dev.lib.sanic_splitkv_decode_step_fused(self.dev.h, C.byref(p), C.byref(x), C.c_void_p(b["out"].data_ptr()),
+                                                          abi.BF16, self.dev.stream())
+            self.dev._check(rc, "splitkv_decode_step_fused")
+            return b["out"]
         if self.exchange == "peer":
             if self._peer is None:
                 self._peer_setup(B * Hq, D)

@@ -617,3 +617,68 @@ def test_splitkv_peer_exchange_single_rank(dev):
                    v.float().cpu().numpy().astype(np.float64), enable_gqa=True)[:, :, 0, :]
     assert nerr(ob.float().cpu().numpy(), exp) <= BF16_TOL
     b.close()
+
+
+# ───────────────────────── stream-K form of the decode fold, and the fused multi-device step ─────────────────────────
+@pytest.mark.parametrize("D,vt", [(64, True), (128, False), (64, False)])
+@pytest.mark.parametrize("kv_len,window", [(1, 0), (63, 0), (65, 0), (1000, 0), (5000, 0), (5000, 700), (40000, 0)])
+def test_decode_streamk_matches_the_oracle_and_the_chunked_form(dev, D, vt, kv_len, window):
+    B, Hq, Hkv, S = 2, 8, 2, 40000 if kv_len > 5000 else 5056
+    g = torch.Generator(device=dev.torch_device); g.manual_seed(kv_len + D)
+    q = torch.randn(B, Hq, D, generator=g, device=dev.torch_device).to(torch.bfloat16)
+    k = torch.randn(B, Hkv, S, D, generator=g, device=dev.torch_device).to(torch.bfloat16)
+    v = torch.randn(B, Hkv, S, D, generator=g, device=dev.torch_device).to(torch.bfloat16)
+    vdev = v.transpose(2, 3).contiguous() if vt else v
+    out, car = dev.attn_decode(q, k, vdev, kv_len, v_transposed=vt, window=window, streamk=True, return_carrier=True,
+                               out_dtype=torch.float32)
+    ref = dev.attn_decode(q, k, vdev, kv_len, v_transposed=vt, window=window, n_splits=3, out_dtype=torch.float32)
+    dev.sync()
+    assert nerr(out.cpu().numpy(), ref.cpu().numpy()) <= 2e-3            # another chunking of the same fold
+    lo = max(0, kv_len - window) if window else 0
+    f64 = lambda t: t.float().cpu().numpy().astype(np.float64)
+    exp = orc.sdpa(f64(q[:1]).reshape(1, Hq, 1, D), f64(k[:1, :, lo:kv_len]), f64(v[:1, :, lo:kv_len]), enable_gqa=True).reshape(Hq, D)
+    assert nerr(out[0].cpu().numpy(), exp) <= BF16_TOL
+    c = car.cpu().numpy().reshape(B, Hq, D + 2)
+    assert nerr(c[0, :, 2:] / c[0, :, 1:2], exp) <= BF16_TOL
+    # a second launch on the same scratch: the group tickets were reset by the first
+    out2 = dev.attn_decode(q, k, vdev, kv_len, v_transposed=vt, window=window, streamk=True, out_dtype=torch.float32)
+    dev.sync()
+    assert torch.equal(out, out2)
+
+
+def test_decode_streamk_many_groups_and_device_side_length(dev):
+    # more (batch, kv head) groups than resident CTAs can split finely, and a length read from the device
+    B, Hq, Hkv, D, S = 16, 32, 8, 64, 1056
+    g = torch.Generator(device=dev.torch_device); g.manual_seed(5)
+    q = torch.randn(B, Hq, D, generator=g, device=dev.torch_device).to(torch.bfloat16)
+    k = torch.randn(B, Hkv, S, D, generator=g, device=dev.torch_device).to(torch.bfloat16)
+    v = torch.randn(B, Hkv, D, S, generator=g, device=dev.torch_device).to(torch.bfloat16)
+    pos = torch.tensor([1029], dtype=torch.int32, device=dev.torch_device)
+    out = dev.attn_decode(q, k, v, 1, v_transposed=True, streamk=True, out_dtype=torch.float32, kv_len_dev=pos)
+    ref = dev.attn_decode(q, k, v, 1030, v_transposed=True, n_splits=2, out_dtype=torch.float32)
+    dev.sync()
+    assert nerr(out.cpu().numpy(), ref.cpu().numpy()) <= 2e-3
+    f64 = lambda t: t.float().cpu().numpy().astype(np.float64)
+    exp = orc.sdpa(f64(q[15:, 28:]).reshape(1, 4, 1, D), f64(k[15:, 7:, :1030]), f64(v[15:, 7:, :, :1030]).transpose(0, 1, 3, 2), enable_gqa=True)
+    assert nerr(out[15, 28:].cpu().numpy(), exp.reshape(4, D)) <= BF16_TOL
+
+
+def test_splitkv_fused_exchange_single_rank(dev):
+    # world size 1: the fused step's last arrivers store into the rank's own buffer, flag themselves and merge one
+    # accumulator set; three steps cover both buffer parities
+    from sanic_b200.splitkv import SplitKVDecoder
+    B, Hq, Hkv, D, n = 2, 8, 2, 128, 3000
+    g = torch.Generator(device=dev.torch_device); g.manual_seed(32)
+    k = torch.randn(B, Hkv, n, D, generator=g, device=dev.torch_device).to(torch.bfloat16)
+    v = torch.randn(B, Hkv, n, D, generator=g, device=dev.torch_device).to(torch.bfloat16)
+    a = SplitKVDecoder(dev, k, v, n_splits=4, init_nccl=False)
+    b = SplitKVDecoder(dev, k, v, init_nccl=False, exchange="fused", force_exchange=True)
+    for step in range(3):
+        q = torch.randn(B, Hq, D, generator=g, device=dev.torch_device).to(torch.bfloat16)
+        oa = a.step(q).clone(); ob = b.step(q).clone()
+        b.sync()
+        assert nerr(ob.float().cpu().numpy(), oa.float().cpu().numpy()) <= 2.0 ** -7, step     # another chunking, one bf16 rounding
+    exp = orc.sdpa(q.float().cpu().numpy().astype(np.float64)[:, :, None, :], k.float().cpu().numpy().astype(np.float64),
+                   v.float().cpu().numpy().astype(np.float64), enable_gqa=True)[:, :, 0, :]
+    assert nerr(ob.float().cpu().numpy(), exp) <= BF16_TOL
+    b.close()

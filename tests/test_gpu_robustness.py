@@ -192,3 +192,44 @@ def test_peer_flag_that_never_arrives_times_out_and_returns(dev):
     exp = orc.sdpa(q.float().cpu().numpy().astype(np.float64)[:, :, None, :], k.float().cpu().numpy().astype(np.float64),
                    v.float().cpu().numpy().astype(np.float64), enable_gqa=True)[:, :, 0, :]
     assert nerr(out.cpu().numpy(), exp) <= BF16_TOL
+
+
+def test_fused_step_times_out_when_a_device_never_publishes(dev):
+    """The one-launch multi-device step with two 'ranks' of which only rank 0 runs: its last arrivers store and flag
+    every group into both buffers, then wait for rank 1's group flags, which nobody writes. The bounded wait gives up,
+    the kernel returns, sanic_sync reports code 41 + 1, the output is untouched and the context keeps working."""
+    import time
+    from sanic_b200 import RunError, abi
+    lib = dev.lib
+    B, Hq, Hkv, D, n = 1, 8, 2, 128, 2048
+    g = torch.Generator(device=dev.torch_device); g.manual_seed(78)
+    q = torch.randn(B, Hq, D, generator=g, device=dev.torch_device).to(torch.bfloat16)
+    k = torch.randn(B, Hkv, n, D, generator=g, device=dev.torch_device).to(torch.bfloat16)
+    v = torch.randn(B, Hkv, n, D, generator=g, device=dev.torch_device).to(torch.bfloat16)
+    rows, groups = B * Hq, B * Hkv
+    nbytes = int(lib.sanic_peer_exchange_bytes_fused(rows, D, 2, groups))
+    bufs = [torch.zeros(nbytes // 4 + 4, dtype=torch.float32, device=dev.torch_device) for _ in range(2)]
+    out = torch.full((B, Hq, D), 7.0, dtype=torch.float32, device=dev.torch_device)
+    p, _keep = dev.decode_params(q, k, v, n, n_splits=dev.streamk_slots(B, Hkv, D), out=None)
+    x = abi.PeerExchange()
+    x.rank, x.nranks, x.epoch, x.spin_limit = 0, 2, 1, 1 << 12
+    x.buffers[0], x.buffers[1] = bufs[0].data_ptr(), bufs[1].data_ptr()
+    t0 = time.time()
+    dev._check(lib.sanic_splitkv_decode_step_fused(dev.h, C.byref(p), C.byref(x), C.c_void_p(out.data_ptr()), abi.F32, dev.stream()),
+               "fused step")
+    with pytest.raises(RunError, match="code 42"):
+        dev.sync()
+    assert time.time() - t0 < 5.0
+    assert torch.all(out == 7.0)
+    flags = bufs[1][:64].view(torch.int32).cpu().numpy()       # [2 parities][8 ranks][4 (groups padded)]
+    assert list(flags[32:34]) == [1, 1] and list(flags[36:38]) == [0, 0]      # parity 1: rank 0's two groups set, rank 1's never
+    x1 = abi.PeerExchange()
+    x1.rank, x1.nranks, x1.epoch = 0, 1, 1
+    buf1 = torch.zeros(int(lib.sanic_peer_exchange_bytes_fused(rows, D, 1, groups)) // 4 + 4, dtype=torch.float32, device=dev.torch_device)
+    x1.buffers[0] = buf1.data_ptr()
+    dev._check(lib.sanic_splitkv_decode_step_fused(dev.h, C.byref(p), C.byref(x1), C.c_void_p(out.data_ptr()), abi.F32, dev.stream()),
+               "fused step")
+    dev.sync()
+    exp = orc.sdpa(q.float().cpu().numpy().astype(np.float64)[:, :, None, :], k.float().cpu().numpy().astype(np.float64),
+                   v.float().cpu().numpy().astype(np.float64), enable_gqa=True)[:, :, 0, :]
+    assert nerr(out.cpu().numpy(), exp) <= BF16_TOL
