@@ -490,6 +490,50 @@ int32_t sanic_machine_output(sanic_replay* m, const char* name, sanic_buffer_vie
 /* The buffer state `name` will be read from by the NEXT step (to load a prefilled cache, or to read a state back). */
 int32_t sanic_machine_state(sanic_replay* m, const char* name, sanic_buffer_view* out);
 
+/* ── planning facts, the device-level split, measured tuning ──
+ * sanic_fitted_specs is the reference's DeviceSpecs (src/cost.rs:33-60: sram_bytes ... mem_latency_s, same meaning) with
+ * what this device adds. sanic_specs_b200 is the counterpart of DeviceSpecs::m1_pro (src/cost.rs:93-119): constants fitted
+ * from this library's own measured kernels on B200. sanic_specs_measure re-measures the ones a probe can give. */
+typedef struct {
+    double sram_bytes, regfile_bytes, hbm_bandwidth, peak_flops, launch_overhead, dtype_bytes;
+    int32_t compute_dtype, boundary_dtype;      /* DeviceSpecs::compute, Policy::boundary */
+    double min_blocks, mem_latency_s;
+    /* beyond the reference's fields */
+    double hbm_read_bandwidth;                  /* a read-only sweep (folds read, they do not copy) */
+    double launch_overhead_empty;               /* measured floor: an empty kernel after an empty kernel in a replayed graph */
+    double exp_per_clk_per_sm, sm_clock_hz;     /* the SFU rate that bounds the online-softmax fold at small head_dim */
+    double grid_barrier_s;                      /* device-wide barrier inside the single-kernel step */
+    double exchange_latency_s, link_bandwidth;  /* cross-device carrier exchange: fixed latency, bytes/s per direction */
+    double l2_bytes;
+    int32_t sm_count, reserved;
+} sanic_fitted_specs;
+int32_t sanic_specs_b200(sanic_fitted_specs* out);
+int32_t sanic_specs_measure(sanic_ctx* ctx, void* stream, sanic_fitted_specs* out);
+/* mergeable_out_of_order (src/plan.rs:478-488): 1 when every slot kind re-associates, so the streamed axis may be split. */
+int32_t sanic_mergeable_out_of_order(const sanic_carrier_desc* carrier);
+/* The chunking of run_carrier_split (src/interp.rs:603) at any level: part `part` of `parts` owns [lo, hi). */
+int32_t sanic_shard_range(int64_t extent, int32_t part, int32_t parts, int64_t* lo, int64_t* hi);
+/* FoldSched (src/plan.rs:434-476) with the device-level factor on the streamed axis above the kernel: legal for every
+ * carrier sanic_mergeable_out_of_order accepts, the carriers being the exchanged state. sanic_plan_fold prices a fold of
+ * `points` outputs in `streams` independent operand streams ((batch, kv head) groups), `bytes_per_step` / `flops_per_step`
+ * summed over all streams, for device counts 1, 2, 4, 8 (up to max_devices): roofline with the Little's-law bandwidth
+ * floor, launch overhead, and for d > 1 the fixed exchange latency plus (d - 1) carriers over the link. Cheapest wins. */
+typedef struct {
+    int32_t devices;            /* parts of the streamed axis, one per device (1 = no device-level split) */
+    int32_t ctas;               /* resident CTAs per device the axis is cut over */
+    int32_t warps, lanes;       /* FoldSched::sgs and the lane width inside a CTA */
+    double seconds, hbm_seconds, flop_seconds, launch_seconds, exchange_seconds;
+} sanic_fold_plan;
+int32_t sanic_plan_fold(const sanic_fitted_specs* specs, const sanic_carrier_desc* carrier, int64_t points, int64_t streams,
+                        int64_t stream_extent, double bytes_per_step, double flops_per_step, int32_t carrier_floats_per_point,
+                        int32_t max_devices, sanic_fold_plan* out);
+/* In-context timing of schedule candidates (the reference's SANIC_TUNE path, src/compile.rs:1348-1630) for the decode
+ * fold, on the caller's own buffers: candidates[i] > 0 = that many fixed chunks per (batch, kv head), 0 = the stream-K
+ * form. p->n_splits must be the largest slot count among them (it sizes p->partials). seconds (optional) receives the best
+ * of `repeats` timed launches per candidate, *best_index the fastest. */
+int32_t sanic_tune_decode(sanic_ctx* ctx, const sanic_decode_params* p, const int32_t* candidates, int32_t n, int32_t repeats,
+                          void* stream, int32_t* best_index, double* seconds);
+
 /* ── multi-device split-KV: each device folds its slice of the key axis, the carriers are
  *    exchanged and merged with the derived combine (src/interp.rs:538-554) ── */
 int32_t sanic_nccl_unique_id(uint8_t out_id[128]);

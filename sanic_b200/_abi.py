@@ -154,6 +154,19 @@ class StateDecl(C.Structure):
     _fields_ = [("input_name", C.c_char_p), ("root", i32), ("pinned", i32)]
 
 
+class FittedSpecs(C.Structure):
+    _fields_ = [(n, C.c_double) for n in ("sram_bytes", "regfile_bytes", "hbm_bandwidth", "peak_flops", "launch_overhead", "dtype_bytes")] + \
+               [("compute_dtype", i32), ("boundary_dtype", i32)] + \
+               [(n, C.c_double) for n in ("min_blocks", "mem_latency_s", "hbm_read_bandwidth", "launch_overhead_empty", "exp_per_clk_per_sm",
+                                          "sm_clock_hz", "grid_barrier_s", "exchange_latency_s", "link_bandwidth", "l2_bytes")] + \
+               [("sm_count", i32), ("reserved", i32)]
+
+
+class FoldPlan(C.Structure):
+    _fields_ = [("devices", i32), ("ctas", i32), ("warps", i32), ("lanes", i32)] + \
+               [(n, C.c_double) for n in ("seconds", "hbm_seconds", "flop_seconds", "launch_seconds", "exchange_seconds")]
+
+
 def dtype_of_torch(dt):
     import torch
     return {torch.float32: F32, torch.float16: F16, torch.bfloat16: BF16, torch.int32: U32, torch.uint8: I4}[dt]
@@ -236,6 +249,12 @@ PROTOTYPES = {
     "sanic_machine_state": (i32, [vp, C.c_char_p, C.POINTER(BufferView)]),
     "sanic_program_phase_profile": (i32, [vp, vp, C.POINTER(C.c_double), i32, C.POINTER(i32)]),
     "sanic_replay_phase_profile": (i32, [vp, vp, C.POINTER(C.c_double), i32, C.POINTER(i32)]),
+    "sanic_specs_b200": (i32, [C.POINTER(FittedSpecs)]),
+    "sanic_specs_measure": (i32, [vp, vp, C.POINTER(FittedSpecs)]),
+    "sanic_mergeable_out_of_order": (i32, [C.POINTER(CarrierDesc)]),
+    "sanic_shard_range": (i32, [i64, i32, i32, C.POINTER(i64), C.POINTER(i64)]),
+    "sanic_plan_fold": (i32, [C.POINTER(FittedSpecs), C.POINTER(CarrierDesc), i64, i64, i64, C.c_double, C.c_double, i32, i32, C.POINTER(FoldPlan)]),
+    "sanic_tune_decode": (i32, [vp, C.POINTER(DecodeParams), C.POINTER(i32), i32, i32, vp, C.POINTER(i32), C.POINTER(C.c_double)]),
     "sanic_nccl_unique_id": (i32, [C.POINTER(C.c_uint8)]),
     "sanic_nccl_init": (i32, [vp, i32, i32, C.POINTER(C.c_uint8)]),
     "sanic_nccl_shutdown": (i32, [vp]),

@@ -17,10 +17,12 @@ from . import _abi as abi
 
 
 def shard_range(n: int, rank: int, world: int):
-    """[lo, hi) of rank's slice; every slice is non-empty when world <= n (src/interp.rs:570-574)."""
+    """[lo, hi) of rank's slice; every slice is non-empty when world <= n (src/interp.rs:570-574). The device-level
+    chunking is the library's (sanic_shard_range), the same one every other level of the split uses."""
+    from .plan import shard_range as _lib_range
     if not (1 <= world <= n):
         raise ValueError(f"world must be in [1, extent = {n}]")
-    return rank * n // world, (rank + 1) * n // world
+    return _lib_range(n, rank, world)
 
 
 def exchange_and_merge(local_carrier, merge_fn, group=None):

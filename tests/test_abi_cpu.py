@@ -72,6 +72,7 @@ def test_struct_sizes_match_the_header():
 #include <stddef.h>
 #include "sanic_b200.h"
 int main(void) {
+  printf("%zu %zu %zu %zu ", sizeof(sanic_fitted_specs), offsetof(sanic_fitted_specs, sm_count), sizeof(sanic_fold_plan), offsetof(sanic_fold_plan, seconds));
   printf("%zu %zu %zu %zu %zu %zu %zu %zu %zu %zu ", sizeof(sanic_buffer_decl), sizeof(sanic_reloc), sizeof(sanic_schedule_desc),
          sizeof(sanic_binding), sizeof(sanic_buffer_view), sizeof(sanic_state_decl), offsetof(sanic_stage_desc, u.embed.scales),
          offsetof(sanic_decode_params, kv_cap), offsetof(sanic_attn_params, accum_dtype), offsetof(sanic_peer_exchange, spin_limit));
@@ -89,7 +90,8 @@ int main(void) {
         exe = os.path.join(d, "p")
         subprocess.run(["gcc", "-I", os.path.join(ROOT, "include"), c, "-o", exe], check=True)
         got = [int(t) for t in subprocess.run([exe], capture_output=True, text=True, check=True).stdout.split()]
-    want = [C.sizeof(abi.BufferDecl), C.sizeof(abi.Reloc), C.sizeof(abi.ScheduleDesc), C.sizeof(abi.Binding), C.sizeof(abi.BufferView),
+    want = [C.sizeof(abi.FittedSpecs), abi.FittedSpecs.sm_count.offset, C.sizeof(abi.FoldPlan), abi.FoldPlan.seconds.offset,
+            C.sizeof(abi.BufferDecl), C.sizeof(abi.Reloc), C.sizeof(abi.ScheduleDesc), C.sizeof(abi.Binding), C.sizeof(abi.BufferView),
             C.sizeof(abi.StateDecl), abi.StageDesc.u.offset + abi._StageUnion.embed.offset + abi._EmbedStage.scales.offset,
             abi.DecodeParams.kv_cap.offset, abi.AttnParams.accum_dtype.offset, abi.PeerExchange.spin_limit.offset,
             C.sizeof(abi.DeviceSpecs), C.sizeof(abi.CarrierDesc), C.sizeof(abi.AttnParams), C.sizeof(abi.DecodeParams),

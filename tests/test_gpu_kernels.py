@@ -682,3 +682,29 @@ def test_splitkv_fused_exchange_single_rank(dev):
                    v.float().cpu().numpy().astype(np.float64), enable_gqa=True)[:, :, 0, :]
     assert nerr(ob.float().cpu().numpy(), exp) <= BF16_TOL
     b.close()
+
+
+def test_measured_specs_and_in_context_tuning_of_the_decode_fold(dev):
+    from sanic_b200 import abi, plan
+    s = plan.measure_specs(dev)
+    assert 4.0e12 < s.hbm_read_bandwidth < 9.0e12          # a read-only sweep of 1 GiB
+    assert 8.0 < s.exp_per_clk_per_sm < 16.5               # 16 is the datasheet rate
+    assert 0.0 < s.launch_overhead_empty < 2e-5
+    B, Hq, Hkv, D, S = 4, 32, 8, 128, 16384
+    g = torch.Generator(device=dev.torch_device); g.manual_seed(8)
+    q = torch.randn(B, Hq, D, generator=g, device=dev.torch_device).to(torch.bfloat16)
+    k = torch.randn(B, Hkv, S, D, generator=g, device=dev.torch_device).to(torch.bfloat16)
+    v = torch.randn(B, Hkv, S, D, generator=g, device=dev.torch_device).to(torch.bfloat16)
+    out = dev.empty((B, Hq, D), torch.float32)
+    slots = max(64, dev.streamk_slots(B, Hkv, D))
+    p, _keep = dev.decode_params(q, k, v, S, n_splits=slots, out=out, out_dtype=abi.F32)
+    cands = [1, 4, 16, 64, 0]                              # fixed chunks per (batch, kv head); 0 = stream-K
+    best, secs = plan.tune_decode(dev, p, cands, repeats=3)
+    assert best in cands and len(secs) == len(cands) and all(0.0 < t < 1.0 for t in secs)
+    assert secs[cands.index(best)] == min(secs)
+    assert secs[cands.index(1)] > min(secs)                # one chunk per (batch, kv head) leaves most SMs idle
+    # the buffers hold the last candidate's result, and it is right
+    dev.sync()
+    f64 = lambda t: t.float().cpu().numpy().astype(np.float64)
+    exp = orc.sdpa(f64(q[:1, :4]).reshape(1, 4, 1, D), f64(k[:1, :1]), f64(v[:1, :1]), enable_gqa=True).reshape(4, D)
+    assert nerr(out[0, :4].cpu().numpy(), exp) <= BF16_TOL
