@@ -281,6 +281,12 @@ int32_t sanic_rope_cache_write(sanic_ctx* ctx, const sanic_rope_cache_params* p,
 /* position += 1 on the device, so a captured step replays without host writes. */
 int32_t sanic_advance_position(sanic_ctx* ctx, int32_t* position, void* stream);
 
+/* Non-finite values (NaN, +-inf) of a float buffer, counted: the check behind SANIC_NANSCAN=1, under which every run and
+ * replayed step of a schedule scans the float buffers the runtime owns and names the first offender in its error
+ * (the reference's pass: src/compile.rs:1261-1275). Synchronises `stream`. SANIC_DEBUG=1/2/3 (read once, as
+ * src/lib.rs:38-46): one line per captured replay / per replayed step with its device time / the stage list. */
+int32_t sanic_count_nonfinite(sanic_ctx* ctx, const void* dptr, size_t n, int32_t dtype, void* stream, uint32_t* count);
+
 /* ── K4: typed load/store helpers exposed for bit-exactness tests (src/emit_metal.rs:123-232) ── */
 int32_t sanic_round_to_bf16(sanic_ctx* ctx, const float* x, size_t n, uint16_t* out_bits, void* stream);
 int32_t sanic_store_u32_saturating(sanic_ctx* ctx, const float* x, size_t n, uint32_t* out, void* stream);
@@ -539,6 +545,11 @@ int32_t sanic_tune_decode(sanic_ctx* ctx, const sanic_decode_params* p, const in
 int32_t sanic_nccl_unique_id(uint8_t out_id[128]);
 int32_t sanic_nccl_init(sanic_ctx* ctx, int32_t rank, int32_t nranks, const uint8_t id[128]);
 int32_t sanic_nccl_shutdown(sanic_ctx* ctx);
+/* Host-side bounded wait for work on `stream` that includes a collective: polls the stream and ncclCommGetAsyncError.
+ * When `timeout_ms` passes with the stream still busy (a rank never joined: such a collective cannot be waited out on the
+ * device) or the communicator reports an error, the communicator is aborted and dropped from the context and the call
+ * fails with SANIC_ERR_TIMEOUT / SANIC_ERR_NCCL. Without a communicator, or with timeout_ms <= 0, this is sanic_sync. */
+int32_t sanic_nccl_wait(sanic_ctx* ctx, void* stream, int32_t timeout_ms);
 /* Runs the local split-KV fold (p->carrier_out must be set, p->out ignored), all-gathers the
  * [rows, 2+D] carriers into `gathered` [nranks, rows, 2+D] and merges them into `out` on every rank. */
 int32_t sanic_splitkv_decode_step(sanic_ctx* ctx, const sanic_decode_params* p, float* gathered, void* out,

@@ -191,6 +191,7 @@ PROTOTYPES = {
     "sanic_attn_fwd_f32": (i32, [vp, C.POINTER(AttnParams), vp]),
     "sanic_attn_fwd_bf16": (i32, [vp, C.POINTER(AttnParams), vp]),
     "sanic_status_inject": (i32, [vp, i32]),
+    "sanic_count_nonfinite": (i32, [vp, vp, C.c_size_t, i32, vp, C.POINTER(C.c_uint32)]),
     "sanic_embed_gather_w4": (i32, [vp, vp, vp, vp, i32, i32, i32, i32, vp, vp]),
     "sanic_attn_decode_splitkv": (i32, [vp, C.POINTER(DecodeParams), vp]),
     "sanic_attn_decode_streamk": (i32, [vp, C.POINTER(DecodeParams), vp]),
@@ -258,6 +259,7 @@ PROTOTYPES = {
     "sanic_nccl_unique_id": (i32, [C.POINTER(C.c_uint8)]),
     "sanic_nccl_init": (i32, [vp, i32, i32, C.POINTER(C.c_uint8)]),
     "sanic_nccl_shutdown": (i32, [vp]),
+    "sanic_nccl_wait": (i32, [vp, vp, i32]),
     "sanic_splitkv_decode_step": (i32, [vp, C.POINTER(DecodeParams), vp, vp, i32, vp]),
     "sanic_peer_exchange_bytes": (C.c_size_t, [i32, i32, i32]),
     "sanic_ipc_export": (i32, [vp, vp, C.POINTER(C.c_uint8)]),

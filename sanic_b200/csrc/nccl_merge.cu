@@ -8,7 +8,9 @@
 // torch ships) so the single-device library has no link-time dependency on it.
 #include <dlfcn.h>
 
+#include <chrono>
 #include <cstring>
+#include <thread>
 
 #include "common.cuh"
 
@@ -20,6 +22,7 @@ typedef int (*fn_destroy)(void*);
 typedef int (*fn_allgather)(const void*, void*, size_t, int, void*, cudaStream_t);
 typedef const char* (*fn_errstr)(int);
 typedef int (*fn_async_err)(void*, int*);
+typedef int (*fn_abort)(void*);
 
 struct NcclApi {
     void* lib = nullptr;
@@ -29,6 +32,7 @@ struct NcclApi {
     fn_allgather allgather = nullptr;
     fn_errstr errstr = nullptr;
     fn_async_err async_err = nullptr;
+    fn_abort abort = nullptr;
 };
 NcclApi g_api;
 
@@ -47,6 +51,7 @@ bool load_api() {
     g_api.allgather = (fn_allgather)dlsym(h, "ncclAllGather");
     g_api.errstr = (fn_errstr)dlsym(h, "ncclGetErrorString");
     g_api.async_err = (fn_async_err)dlsym(h, "ncclCommGetAsyncError");
+    g_api.abort = (fn_abort)dlsym(h, "ncclCommAbort");
     if (!g_api.get_uid || !g_api.init_rank || !g_api.destroy || !g_api.allgather) return false;
     g_api.lib = h;
     return true;
@@ -92,6 +97,36 @@ int32_t sanic_nccl_shutdown(sanic_ctx* ctx) {
     ctx->nccl_nranks = 1;
     ctx->nccl_rank = 0;
     return SANIC_OK;
+}
+
+// Host-side bounded wait for the work on `stream` when it includes a collective: polls the stream and the communicator's
+// asynchronous error state. A collective that a rank never joined does not complete and cannot be waited out on the
+// device; when `timeout_ms` passes with the stream still busy, or the communicator reports an error, the communicator is
+// aborted (its kernels stop), the context's communicator is dropped, and the call fails. With no communicator this is
+// sanic_sync.
+int32_t sanic_nccl_wait(sanic_ctx* ctx, void* stream, int32_t timeout_ms) {
+    if (!ctx) return SANIC_ERR_INVALID;
+    if (!ctx->nccl_comm || timeout_ms <= 0) return sanic_sync(ctx, stream);
+    sanic_set_device(ctx);
+    const auto t0 = std::chrono::steady_clock::now();
+    for (;;) {
+        cudaError_t q = cudaStreamQuery((cudaStream_t)stream);
+        if (q == cudaSuccess) return sanic_sync(ctx, stream);
+        if (q != cudaErrorNotReady) return sanic_fail(ctx, SANIC_ERR_CUDA, std::string("nccl_wait: ") + cudaGetErrorString(q));
+        int async = 0;
+        const int rc = g_api.async_err ? g_api.async_err(ctx->nccl_comm, &async) : 0;
+        const bool failed = rc != 0 || (async != 0 && async != 7 /* ncclInProgress */);
+        const bool late = std::chrono::duration_cast<std::chrono::milliseconds>(std::chrono::steady_clock::now() - t0).count() > timeout_ms;
+        if (failed || late) {
+            if (g_api.abort) g_api.abort(ctx->nccl_comm);
+            ctx->nccl_comm = nullptr; ctx->nccl_nranks = 1; ctx->nccl_rank = 0;
+            return failed ? sanic_fail(ctx, SANIC_ERR_NCCL, std::string("nccl_wait: the communicator reported ") +
+                                                             (g_api.errstr ? g_api.errstr(rc != 0 ? rc : async) : "an error") + "; aborted")
+                          : sanic_fail(ctx, SANIC_ERR_TIMEOUT, "nccl_wait: the collective did not complete within " + std::to_string(timeout_ms) +
+                                                                " ms (a rank did not take part); the communicator was aborted");
+        }
+        std::this_thread::sleep_for(std::chrono::microseconds(50));
+    }
 }
 
 int32_t sanic_splitkv_decode_step(sanic_ctx* ctx, const sanic_decode_params* p, float* gathered, void* out,

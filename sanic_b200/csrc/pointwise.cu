@@ -3,6 +3,10 @@
 // reference emitter (src/emit_metal.rs:123-232, 1118-1178 in the reference project).
 #include <vector>
 
+#include <cuda_fp16.h>
+
+#include <algorithm>
+
 #include "common.cuh"
 
 namespace {
@@ -57,6 +61,20 @@ __global__ void embed_gather_w4_kernel(const uint8_t* table, const uint16_t* sca
         const int nib = (row[i >> 1] >> ((i & 1) * 4)) & 0xF;
         out[(size_t)b * hidden + i] = (float)(nib - 8) * bf16_to_f32(srow[i / group]);
     }
+}
+
+// Non-finite values of a buffer, counted (the reference's SANIC_NANSCAN pass, src/compile.rs:1261-1275).
+__global__ void count_nonfinite_kernel(const void* p, size_t n, int dtype, unsigned* count) {
+    unsigned local = 0;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        float v;
+        if (dtype == SANIC_F32) v = ((const float*)p)[i];
+        else if (dtype == SANIC_BF16) v = bf16_to_f32(((const uint16_t*)p)[i]);
+        else v = __half2float(((const __half*)p)[i]);
+        if (!(fabsf(v) <= 3.4028234664e38f)) ++local;      // NaN and +-inf both fail the comparison
+    }
+    local = __reduce_add_sync(0xffffffffu, local);
+    if ((threadIdx.x & 31) == 0 && local) atomicAdd(count, local);
 }
 
 __global__ void rope_table_kernel(const double* inv_freq, int n_freq, int n_pos, float* table) {
@@ -233,6 +251,25 @@ int32_t sanic_embed_gather(sanic_ctx* ctx, const void* table, const int32_t* tok
     SANIC_REQUIRE(ctx, table && tokens && out && batch > 0 && hidden > 0 && vocab > 0, "embed_gather: bad arguments");
     sanic_set_device(ctx);
     SANIC_CUDA_CHECK(ctx, launch_pdl(embed_gather_kernel, dim3(batch), dim3(256), 0, (cudaStream_t)stream, (const uint16_t*)table, tokens, hidden, vocab, out));
+    return SANIC_OK;
+}
+
+int32_t sanic_count_nonfinite(sanic_ctx* ctx, const void* dptr, size_t n, int32_t dtype, void* stream, uint32_t* count) {
+    if (!ctx || !dptr || !count) return SANIC_ERR_INVALID;
+    if (dtype != SANIC_F32 && dtype != SANIC_BF16 && dtype != SANIC_F16) return sanic_fail(ctx, SANIC_ERR_DTYPE, "count_nonfinite: f32, bf16 or f16");
+    sanic_set_device(ctx);
+    unsigned* d = nullptr;
+    SANIC_CUDA_CHECK(ctx, cudaMalloc(&d, sizeof(unsigned)));
+    cudaError_t e = cudaMemsetAsync(d, 0, sizeof(unsigned), (cudaStream_t)stream);
+    if (e == cudaSuccess && n) {
+        const int blocks = (int)std::min<size_t>((n + 255) / 256, 1184);
+        count_nonfinite_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(dptr, n, dtype, d);
+        e = cudaGetLastError();
+    }
+    if (e == cudaSuccess) e = cudaMemcpyAsync(count, d, sizeof(unsigned), cudaMemcpyDeviceToHost, (cudaStream_t)stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize((cudaStream_t)stream);
+    cudaFree(d);
+    if (e != cudaSuccess) return sanic_fail(ctx, SANIC_ERR_CUDA, std::string("count_nonfinite: ") + cudaGetErrorString(e));
     return SANIC_OK;
 }
 

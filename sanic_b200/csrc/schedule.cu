@@ -14,6 +14,8 @@
 // All validation happens on the host before any CUDA call, and a schedule compiled with a NULL
 // context validates bindings without a device (the refusals are testable anywhere).
 #include <algorithm>
+#include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <map>
 #include <new>
@@ -137,6 +139,37 @@ int32_t alloc_zeroed(sanic_schedule* s, size_t bytes, void** out) {
     cudaError_t e = cudaMalloc(out, bytes);
     if (e == cudaSuccess) e = cudaMemset(*out, 0, bytes);
     if (e != cudaSuccess) return fail(s, e == cudaErrorMemoryAllocation ? SANIC_ERR_NOMEM : SANIC_ERR_CUDA, std::string("buffer allocation: ") + cudaGetErrorString(e));
+    return SANIC_OK;
+}
+
+// SANIC_DEBUG (read once, as src/lib.rs:38-46 does): 1 = one line per compiled schedule and captured replay,
+// 2 = also one line per replayed step with its device time, 3 = also the stage list once per replay.
+// SANIC_NANSCAN=1: after every run or replayed step, every float buffer the runtime owns is scanned for non-finite values
+// and the first offender is named in the error (src/compile.rs:1261-1275).
+int debug_level() {
+    static const int level = [] { const char* e = getenv("SANIC_DEBUG"); return e ? atoi(e) : 0; }();
+    return level;
+}
+bool nan_scan_on() {
+    static const bool on = [] { const char* e = getenv("SANIC_NANSCAN"); return e && e[0] != '0'; }();
+    return on;
+}
+const char* op_name(int op) {
+    switch (op) {
+        case SANIC_OP_GEMV: return "contraction"; case SANIC_OP_DECODE_ATTN: return "online-softmax fold"; case SANIC_OP_ARGMAX: return "extremum index";
+        case SANIC_OP_RMSNORM: return "rmsnorm"; case SANIC_OP_EMBED: return "gather"; case SANIC_OP_ROPE_CACHE: return "rope + cache write";
+        case SANIC_OP_ADVANCE: return "advance"; case SANIC_OP_GENERIC: return "generated"; default: return "?";
+    }
+}
+int32_t nan_scan(sanic_schedule* s, const std::vector<void*>& base, void* stream) {
+    for (size_t i = 0; i < s->bufs.size(); ++i) {
+        const Buf& d = s->bufs[i];
+        if (d.kind != SANIC_BUF_SCRATCH || !base[i] || !(d.dtype == SANIC_F32 || d.dtype == SANIC_BF16 || d.dtype == SANIC_F16)) continue;
+        uint32_t bad = 0;
+        int32_t rc = sanic_count_nonfinite(s->ctx, base[i], d.elements(), d.dtype, stream, &bad);
+        if (rc != SANIC_OK) return rc;
+        if (bad) return fail(s, SANIC_ERR_INVALID, "nan scan: buffer `" + d.name + "` holds " + std::to_string(bad) + " non-finite value(s)");
+    }
     return SANIC_OK;
 }
 
@@ -278,6 +311,7 @@ int32_t sanic_schedule_execute(sanic_schedule* s, const sanic_binding* b, int32_
     }
     rc = sanic_program_run(s->prog, stream);
     if (rc != SANIC_OK) { s->err = s->ctx->err; return rc; }
+    if (nan_scan_on()) { rc = nan_scan(s, base, stream); if (rc != SANIC_OK) return rc; }
     if (outputs)
         for (size_t i = 0; i < s->outputs.size(); ++i) fill_view(s->bufs[s->outputs[i]], base[s->outputs[i]], &outputs[i]);
     return SANIC_OK;
@@ -352,6 +386,12 @@ int32_t sanic_schedule_capture(sanic_schedule* s, const sanic_binding* b, int32_
         if (rc != SANIC_OK) { s->err = s->ctx->err; free_replay(r); return rc; }
         r->base.push_back(bufs);
     }
+    if (debug_level() >= 1)
+        fprintf(stderr, "sanic: captured %zu stage(s) over %zu buffer(s) as %d frozen step(s), %d kernel(s) each%s\n", s->stages.size(),
+                s->bufs.size(), parities, sanic_program_kernel_count(r->parity[0]), persistent ? " (one cooperative kernel)" : "");
+    if (debug_level() >= 3)
+        for (size_t i = 0; i < s->stages.size(); ++i)
+            fprintf(stderr, "sanic:   stage %3zu  %-20s kind %d\n", i, op_name(s->stages[i].op), s->stages[i].stage_kind);
     *out = r;
     return SANIC_OK;
 }
@@ -362,8 +402,15 @@ int32_t sanic_replay_step(sanic_replay* r, void* stream, double* gpu_seconds) {
     if (!r || r->parity.empty()) return SANIC_ERR_INVALID;
     const int par = r->next;
     r->next = (par + 1) % (int)r->parity.size();
-    int32_t rc = sanic_program_step(r->parity[par], stream, gpu_seconds);
+    double sec = 0.0;
+    const bool want = gpu_seconds || debug_level() >= 2;
+    int32_t rc = sanic_program_step(r->parity[par], stream, want ? &sec : nullptr);
+    if (gpu_seconds) *gpu_seconds = sec;
     if (rc == SANIC_OK) ++r->steps; else r->sch->err = r->sch->ctx->err;
+    if (rc == SANIC_OK && debug_level() >= 2)
+        fprintf(stderr, "sanic: step %ld (frozen step %d of %zu, %d kernel(s)) %.3f ms on the device\n", r->steps, par, r->parity.size(),
+                sanic_program_kernel_count(r->parity[par]), sec * 1e3);
+    if (rc == SANIC_OK && nan_scan_on()) rc = nan_scan(r->sch, r->base[par], stream);
     return rc;
 }
 

@@ -31,9 +31,15 @@ def exchange_and_merge(local_carrier, merge_fn, group=None):
     `merge_fn(parts[world, rows, 2+D])` applies the derived combine and projects. Works on any
     backend torch.distributed offers; the GPU path below uses NCCL from inside the C library.
     """
+    from .backend import RunError
     world = dist.get_world_size(group)
     parts = [torch.empty_like(local_carrier) for _ in range(world)]
-    dist.all_gather(parts, local_carrier, group=group)
+    try:
+        dist.all_gather(parts, local_carrier, group=group)
+    except (RuntimeError, dist.DistBackendError) as e:
+        # a rank that never joined (it raised, exited, or was never started) ends the collective with the process
+        # group's timeout: the step's output does not exist, and the caller must not continue on it
+        raise RunError(f"carrier exchange failed: a rank did not take part within the process group's timeout ({e})") from e
     return merge_fn(torch.stack(parts))
 
 
@@ -141,10 +147,16 @@ class SplitKVDecoder:
             self.dev.lib.sanic_free(self.dev.h, self._peer["local"])
             self._peer = None
 
-    def sync(self):
+    def sync(self, timeout_s: float = 0.0):
         """Wait for the steps in flight on the current stream and raise RunError if a peer's flag never arrived
         (status codes 41 + rank) or any other bounded wait ran out. The tensor `step` returned is valid only after
-        this returns."""
+        this returns. With the NCCL exchange and `timeout_s` > 0 the wait is bounded on the host as well: the
+        communicator's asynchronous error state is polled, and when the deadline passes with the collective still in
+        flight (a rank that never joined) the communicator is aborted and RunError raised."""
+        if timeout_s > 0.0 and self.exchange == "nccl" and self.world > 1:
+            rc = self.dev.lib.sanic_nccl_wait(self.dev.h, self.dev.stream(), int(timeout_s * 1000))
+            self.dev._check(rc, "nccl_wait")
+            return
         self.dev.sync()
 
     def step(self, q, scale=None):

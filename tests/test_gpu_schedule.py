@@ -152,3 +152,48 @@ def test_generated_kernel_as_a_schedule_stage(dev):
     exp = orc.round_to(orc.DT_F32, np.array([np.sum(xv[r]) for r in range(rows)])) + bv
     assert nerr(view_tensor(out, dev.torch_device).cpu().numpy(), exp) <= 1e-5
     prog.close(); k1.close(); k2.close()
+
+
+def test_nan_scan_names_the_buffer_and_debug_levels_print(dev):
+    """SANIC_NANSCAN and SANIC_DEBUG are read once per process, so the run happens in a child process."""
+    import os
+    import subprocess
+    import sys
+    import ctypes as C
+    from sanic_b200 import abi
+    bad = torch.tensor([1.0, float("nan"), float("inf"), 2.0, -float("inf")], device=dev.torch_device)
+    n = C.c_uint32(0)
+    dev._check(dev.lib.sanic_count_nonfinite(dev.h, C.c_void_p(bad.data_ptr()), bad.numel(), abi.F32, dev.stream(), C.byref(n)), "count")
+    assert n.value == 3
+    dev._check(dev.lib.sanic_count_nonfinite(dev.h, C.c_void_p(bad.to(torch.bfloat16).data_ptr()), bad.numel(), abi.BF16, dev.stream(), C.byref(n)), "count")
+    assert n.value == 3
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    code = r'''
+import sys, ctypes as C
+sys.path.insert(0, %r); sys.path.insert(0, %r + "/tests")
+import torch
+from sanic_b200 import CudaDevice
+from sanic_b200.schedule import ProgramError
+from test_gpu_schedule import accumulate_schedule
+dev = CudaDevice(0)
+prog = accumulate_schedule(in_place=False).compile(dev)
+w = torch.full((64, 128), 0.01, dtype=torch.bfloat16, device=dev.torch_device)
+x = torch.ones(2, 128, dtype=torch.bfloat16, device=dev.torch_device)
+acc = torch.zeros(2, 64, dtype=torch.float32, device=dev.torch_device)
+st = torch.cuda.Stream(device=dev.torch_device)
+rep = prog.capture({"w": w, "x": x, "acc": acc}, [(0, "acc")], stream=C.c_void_p(st.cuda_stream))
+rep.step(stream=C.c_void_p(st.cuda_stream))
+w[3, 5] = float("nan")
+torch.cuda.synchronize()
+try:
+    rep.step(stream=C.c_void_p(st.cuda_stream))
+    print("NO ERROR")
+except ProgramError as e:
+    print("ERROR:", e)
+''' % (root, root)
+    env = dict(os.environ, SANIC_NANSCAN="1", SANIC_DEBUG="3")
+    r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, env=env, timeout=300)
+    assert "ERROR:" in r.stdout and "non-finite" in r.stdout and "`acc" in r.stdout, r.stdout + r.stderr
+    assert "sanic: captured 1 stage(s)" in r.stderr and "2 frozen step(s)" in r.stderr
+    assert "sanic: step 1" in r.stderr and "ms on the device" in r.stderr
+    assert "stage   0  contraction" in r.stderr

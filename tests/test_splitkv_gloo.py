@@ -62,6 +62,39 @@ def test_two_rank_shard_exchange_merge(masked_tail):
     assert len(ret) == world and all(e < 1e-12 for e in ret.values()), dict(ret)
 
 
+def _withheld_worker(rank, world, port, ret):
+    import datetime
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=4))
+    from sanic_b200.backend import RunError
+    if rank == 1:
+        ret[rank] = "left"          # this rank leaves between steps without joining the exchange
+        return
+    local = torch.zeros(4, 10, dtype=torch.float64)
+    try:
+        exchange_and_merge(local, lambda parts: parts.sum(0))
+        ret[rank] = "completed"
+    except RunError as e:
+        ret[rank] = "RunError" if "did not take part" in str(e) else f"other: {e}"
+
+
+def test_exchange_with_a_rank_that_never_joins_raises_instead_of_hanging():
+    # failure made on the host: rank 1 never takes part; rank 0's collective ends with the process group's timeout and
+    # the helper turns that into a RunError (the step has no output)
+    world = 2
+    ctx = mp.get_context("spawn")
+    ret = ctx.Manager().dict()
+    port = _free_port()
+    procs = [ctx.Process(target=_withheld_worker, args=(r, world, port, ret)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(60)
+        if p.is_alive():
+            p.kill()
+    assert ret.get(1) == "left" and ret.get(0) == "RunError", dict(ret)
+
+
 def test_shard_range_is_the_reference_chunking():
     n = 1048576
     for world in (1, 2, 4, 8, 3, 7):
