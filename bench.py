@@ -287,7 +287,7 @@ def suite(dev, torch, hbm_peak, tf_peak, quick, only=None, c2_shape=(4096, 2048,
         import ctypes as C
         pr = {}
         for warps in (4, 8):       # 16 warps of this probe (128 live values per lane) do not fit one SM's register file
-            for mode, label in enumerate(("ex2", "ex2+fma", "ex2+fma+sum", "ex2+fma+sum+pack")):
+            for mode, label in enumerate(("ex2", "ex2+fma", "ex2+fma+sum", "ex2+fma+sum+pack", "quarter_on_fma_pipe", "half_on_fma_pipe")):
                 rate, clk = C.c_double(0.0), C.c_double(0.0)
                 dev._check(dev.lib.sanic_probe_sfu(dev.h, warps, mode, 200, dev.stream(), C.byref(rate), C.byref(clk)), "probe_sfu")
                 pr[f"warps{warps}_{label}"] = {"exp_per_clk_per_sm": round(rate.value, 2), "clk_per_128_per_lane": clk.value}
@@ -537,9 +537,9 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
-# dram bytes (read + write) / algorithmic bytes of attn_decode_kernel, from the ncu capture summarised in
-# profiles/attn_decode_splitkv.md (a 65,536-key case; traffic grows in proportion to the keys streamed)
-TRAFFIC_RATIO_DECODE = 1.0067
+# dram bytes (read + write) / algorithmic bytes of the decode fold, from one ncu capture of a 65,536-key case (1.0740 GB read
+# + 7.9 MB written for 1.0737 GB of K and V); the traffic grows in proportion to the keys streamed
+TRAFFIC_RATIO_DECODE = 1.0076
 
 
 def main():

@@ -70,7 +70,7 @@ int32_t sanic_specs(sanic_ctx* ctx, sanic_device_specs* out);
  * reference's in-context timing measures (src/compile.rs:1348-1630). Both probes are tiny, bounded kernels.
  * sanic_probe_sfu: `ex2.approx` per clock per SM with `warps_per_sm` resident warps (one CTA per SM); mode 0 = the
  * exponentials alone, 1 = + the scale-and-shift FMA per element, 2 = + the row-sum add, 3 = + the bf16x2 pack: the inner
- * loop of the online-softmax warps. *clk_per_128_per_warp (optional) is the raw figure: clocks per 128 elements per lane.
+ * loop of the online-softmax warps; 4 / 5 = mode 3 with every fourth / second pair of exponentials on the FMA pipe (cubic). *clk_per_128_per_warp (optional) is the raw figure: clocks per 128 elements per lane.
  * sanic_probe_stream: GB/s of a read-only sweep of `buffer` (best of `repeats`), the rate an HBM-bound fold is held to. */
 int32_t sanic_probe_sfu(sanic_ctx* ctx, int32_t warps_per_sm, int32_t mode, int32_t iters, void* stream, double* exp_per_clk_per_sm,
                         double* clk_per_128_per_warp);

@@ -6,7 +6,9 @@
 //           tile next to 512 clocks of tensor-core work, so this rate, and how much of the warps' other instructions
 //           (scale, row sum, bf16 pack) the SM overlaps with it, is the bound of the prefill kernel. Mode 0 issues only
 //           the exponentials from registers; modes 1-3 add, per element, the FMA that scales and shifts the score, the
-//           add of the row sum and the bf16x2 pack of the result: exactly the softmax warp's inner loop.
+//           add of the row sum and the bf16x2 pack of the result: exactly the softmax warp's inner loop. Modes 4 and 5 are
+//           mode 3 with every fourth / every second pair of exponentials computed on the FMA pipe (a cubic after range
+//           reduction) instead of the SFU: what moving part of the load off the SFU buys.
 //   stream  a plain read-only sweep of a buffer (16-byte loads, every SM): the HBM read rate a fold can be held to.
 #include "common.cuh"
 
@@ -14,6 +16,29 @@ namespace {
 using namespace sanic;
 
 __device__ __forceinline__ float ex2(float x) { float y; asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x)); return y; }
+
+// exp2 of a pair on the FMA pipe: round to the nearest integer with the 1.5 * 2^23 trick, a cubic on the remainder in
+// [-0.5, 0.5] (relative error 1e-4: inside the bf16 rounding the result gets anyway), and the integer part added into
+// the exponent field. Packed f32x2 arithmetic: 3 adds and 3 FMAs per pair, plus one integer multiply-add per element.
+__device__ __forceinline__ void ex2_poly2(float& p0, float& p1, float x0, float x1) {
+    const float MAGIC = 12582912.0f;     // 1.5 * 2^23
+    float t0, t1, r0, r1, f0, f1, q0, q1;
+    asm("{\n\t.reg .b64 a, b, d;\n\tmov.b64 a, {%2, %3};\n\tmov.b64 b, {%4, %4};\n\tadd.rn.f32x2 d, a, b;\n\tmov.b64 {%0, %1}, d;\n\t}"
+        : "=f"(t0), "=f"(t1) : "f"(x0), "f"(x1), "f"(MAGIC));
+    asm("{\n\t.reg .b64 a, b, d;\n\tmov.b64 a, {%2, %3};\n\tmov.b64 b, {%4, %4};\n\tadd.rn.f32x2 d, a, b;\n\tmov.b64 {%0, %1}, d;\n\t}"
+        : "=f"(r0), "=f"(r1) : "f"(t0), "f"(t1), "f"(-MAGIC));
+    asm("{\n\t.reg .b64 a, b, d;\n\tmov.b64 a, {%2, %3};\n\tmov.b64 b, {%4, %5};\n\tsub.rn.f32x2 d, a, b;\n\tmov.b64 {%0, %1}, d;\n\t}"
+        : "=f"(f0), "=f"(f1) : "f"(x0), "f"(x1), "f"(r0), "f"(r1));
+    const float C3 = 0.0555041087f, C2 = 0.2402265069f, C1 = 0.6931471806f;
+    asm("{\n\t.reg .b64 a, b, c, d;\n\tmov.b64 a, {%2, %3};\n\tmov.b64 b, {%4, %4};\n\tmov.b64 c, {%5, %5};\n\tfma.rn.f32x2 d, a, b, c;\n\tmov.b64 {%0, %1}, d;\n\t}"
+        : "=f"(q0), "=f"(q1) : "f"(f0), "f"(f1), "f"(C3), "f"(C2));
+    asm("{\n\t.reg .b64 a, b, c, d;\n\tmov.b64 a, {%2, %3};\n\tmov.b64 b, {%4, %5};\n\tmov.b64 c, {%6, %6};\n\tfma.rn.f32x2 d, a, b, c;\n\tmov.b64 {%0, %1}, d;\n\t}"
+        : "=f"(q0), "=f"(q1) : "f"(q0), "f"(q1), "f"(f0), "f"(f1), "f"(C1));
+    asm("{\n\t.reg .b64 a, b, c, d;\n\tmov.b64 a, {%2, %3};\n\tmov.b64 b, {%4, %5};\n\tmov.b64 c, {%6, %6};\n\tfma.rn.f32x2 d, a, b, c;\n\tmov.b64 {%0, %1}, d;\n\t}"
+        : "=f"(q0), "=f"(q1) : "f"(q0), "f"(q1), "f"(f0), "f"(f1), "f"(1.0f));
+    p0 = __uint_as_float(__float_as_uint(q0) + (__float_as_uint(t0) << 23));
+    p1 = __uint_as_float(__float_as_uint(q1) + (__float_as_uint(t1) << 23));
+}
 
 template <int MODE>
 __global__ void probe_sfu_kernel(float* out, const float* in, long long* clk, int iters) {
@@ -29,7 +54,10 @@ __global__ void probe_sfu_kernel(float* out, const float* in, long long* clk, in
         for (int i = 0; i < 64; ++i) {
             float a = r[2 * i], b = r[2 * i + 1];
             if (MODE >= 1) { a = fmaf(a, sl2, -msub); b = fmaf(b, sl2, -msub); }
-            const float p0 = ex2(a), p1 = ex2(b);
+            float p0, p1;
+            // modes 4 and 5: every fourth / every second pair takes its exponentials on the FMA pipe instead of the SFU
+            if ((MODE == 4 && (i & 3) == 3) || (MODE == 5 && (i & 1) == 1)) ex2_poly2(p0, p1, a, b);
+            else { p0 = ex2(a); p1 = ex2(b); }
             if (MODE >= 2) { sums[(2 * i) & 7] += p0; sums[(2 * i + 1) & 7] += p1; }
             pk[i] = (MODE >= 3) ? pack_bf16x2(p0, p1) : (__float_as_uint(p0) ^ __float_as_uint(p1));
         }
@@ -60,8 +88,8 @@ extern "C" {
 int32_t sanic_probe_sfu(sanic_ctx* ctx, int32_t warps_per_sm, int32_t mode, int32_t iters, void* stream, double* exp_per_clk_per_sm,
                         double* clk_per_128_per_warp) {
     if (!ctx || !exp_per_clk_per_sm) return SANIC_ERR_INVALID;
-    SANIC_REQUIRE(ctx, warps_per_sm >= 1 && warps_per_sm <= 32 && mode >= 0 && mode <= 3 && iters >= 1 && iters <= 10000,
-                  "probe_sfu: warps per SM in [1, 32], mode in [0, 3], iterations in [1, 10000]");
+    SANIC_REQUIRE(ctx, warps_per_sm >= 1 && warps_per_sm <= 32 && mode >= 0 && mode <= 5 && iters >= 1 && iters <= 10000,
+                  "probe_sfu: warps per SM in [1, 32], mode in [0, 5], iterations in [1, 10000]");
     sanic_set_device(ctx);
     cudaStream_t st = (cudaStream_t)stream;
     float *out = nullptr, *in = nullptr;
@@ -76,7 +104,9 @@ int32_t sanic_probe_sfu(sanic_ctx* ctx, int32_t warps_per_sm, int32_t mode, int3
         if (mode == 0) probe_sfu_kernel<0><<<g, b, 0, st>>>(out, in, clk, iters);
         else if (mode == 1) probe_sfu_kernel<1><<<g, b, 0, st>>>(out, in, clk, iters);
         else if (mode == 2) probe_sfu_kernel<2><<<g, b, 0, st>>>(out, in, clk, iters);
-        else probe_sfu_kernel<3><<<g, b, 0, st>>>(out, in, clk, iters);
+        else if (mode == 3) probe_sfu_kernel<3><<<g, b, 0, st>>>(out, in, clk, iters);
+        else if (mode == 4) probe_sfu_kernel<4><<<g, b, 0, st>>>(out, in, clk, iters);
+        else probe_sfu_kernel<5><<<g, b, 0, st>>>(out, in, clk, iters);
         e = cudaGetLastError();
         if (e == cudaSuccess) e = cudaStreamSynchronize(st);
     }
