@@ -126,7 +126,8 @@ typedef struct {
 } sanic_attn_params;
 /* f32 storage, f32 CUDA-core arithmetic: q [B,Hq,L,E], k [B,Hkv,S,E], v [B,Hkv,S,Ev], out [B,Hq,L,Ev]. */
 int32_t sanic_attn_fwd_f32(sanic_ctx* ctx, const sanic_attn_params* p, void* stream);
-/* bf16 storage, tensor-core contractions, f32 carrier in registers. E = Ev in {64, 128}. */
+/* bf16 storage, tcgen05 contractions with accumulators in tensor memory, f32 carrier in registers. E = Ev = 64 (the
+ * head size of the prefill configuration); any other head size is refused with SANIC_ERR_UNSUPPORTED. */
 int32_t sanic_attn_fwd_bf16(sanic_ctx* ctx, const sanic_attn_params* p, void* stream);
 
 /* Split-KV decode (one query token per sequence). Stage 1 folds contiguous chunks of

@@ -589,3 +589,40 @@ def test_generic_stage_in_a_program(dev):
     assert nerr(out.cpu().numpy().reshape(L, Ev), want) <= F32_TOL
     dev.lib.sanic_program_destroy(prog_h)
     k1.close(); k2.close()
+
+
+@pytest.mark.gpu
+def test_hand_written_merge_equals_the_carriers_own_combine(dev):
+    """The (m, l, o) merge the hand-written kernels use (`sanic_carrier_merge`, the stage 2 of every split fold and of the
+    multi-device step) against the SAME carrier's combine rendered from its expression programs: the generic emitter folds
+    the axis of partial accumulators with into = identity, combine = the derived one (src/derive.rs:1700-1713), project =
+    o / l. Equal to f32 rounding, including sides whose maximum is -inf (identity partials)."""
+    import torch
+    n_parts, rows, D = 7, 24, 16
+    g = orc.Xorshift(0x3E26E)
+    parts = np.empty((n_parts, rows, D + 2))
+    parts[..., 0] = g.uniform(n_parts, rows) * 30.0
+    parts[..., 1] = np.abs(g.uniform(n_parts, rows)) * 40.0 + 0.1
+    parts[..., 2:] = g.uniform(n_parts, rows, D) * 25.0
+    parts[2, :, 0] = -np.inf; parts[2, :, 1] = 0.0; parts[2, :, 2:] = 0.0          # an all-masked part
+    parts[0, 5, 0] = -np.inf; parts[0, 5, 1] = 0.0; parts[0, 5, 2:] = 0.0          # ... also as the leftmost one
+    parts = orc.round_to(orc.DT_F32, parts)
+    tp = on_device(dev, parts, abi.F32)
+    hand = dev.carrier_merge(tp.view(n_parts, rows, D + 2)).cpu().numpy()
+    # the carrier over partial accumulators: leaves (m, l, o[e]) of part s at row r; lift = the item itself
+    W = D + 2
+    ops = [em.Operand(0, abi.F32, [W, 0], rows * W, offset=0), em.Operand(0, abi.F32, [W, 0], rows * W, offset=1),
+           em.Operand(0, abi.F32, [W, 1], rows * W, offset=2)]
+    m = em.maximum(em.A(0), em.B(0))
+    car = em.Carrier([em.load(0), em.load(1), em.load(2)], [em.item(0), em.item(1), em.item(2)],
+                     [m, em.A(1) * em._shift(em.A(0), m) + em.B(1) * em._shift(em.B(0), m),
+                      em.A(2) * em._shift(em.A(0), m) + em.B(2) * em._shift(em.B(0), m)],
+                     [float("-inf"), 0.0, 0.0], em.F(2) / em.F(1))
+    kern = em.GenericKernel(dev, em.Description((rows, D), ops, carrier=car, stream=n_parts))
+    out = torch.empty(rows * D, device=dev.torch_device)
+    kern([tp], out)
+    dev.sync()
+    gen = out.cpu().numpy().reshape(rows, D)
+    assert nerr(gen, hand) <= 2e-6
+    assert nerr(hand, orc.carrier_merge_mlo(parts)) <= F32_TOL
+    kern.close()
