@@ -27,6 +27,7 @@
 // spins themselves, and no block exits while a bulk copy into its shared memory is still in flight.
 #include "decode_step.cuh"
 
+#include <algorithm>
 #include <new>
 
 #include "attn_decode_body.cuh"
@@ -128,9 +129,9 @@ __device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, unsigned* gbar, int* err, int code) {
     for (unsigned it = 0; it < SPIN_LIMIT; ++it) {
         if (mbar_test(bar, parity)) return true;
-        if ((it & 4095u) == 4095u && ld_acquire(gbar + 1) != 0) return false;
+        if (gbar && (it & 4095u) == 4095u && ld_acquire(gbar + 1) != 0) return false;
     }
-    atomicExch(gbar + 1, 1u);
+    if (gbar) atomicExch(gbar + 1, 1u);
     atomicCAS(err, 0, code);
     return false;
 }
@@ -218,7 +219,10 @@ __device__ __noinline__ void stage_normed_rows(const Phase& P, float* scratch, u
 }
 
 // The consumers' half of a contraction phase: weights come out of the ring, activations from L2.
-template <bool W4, int NT, bool DUAL, bool NORM>
+// DIRECT: the activations are not staged in shared memory; every use reads them from global memory through L1 (the
+// stand-alone ring-fed contraction: a kernel of its own starts with a clean L1, and its activations were written by an
+// earlier kernel, so the non-coherent path is safe there and 64 KB of them stay resident).
+template <bool W4, int NT, bool DUAL, bool NORM, bool DIRECT = false>
 __device__ __forceinline__ bool consume_gemv(const Phase& P, const Ring& ring, uint32_t& drained, float* scratch, unsigned* gbar, int* err,
                                              unsigned long long* prof) {
     using namespace gemv;
@@ -232,7 +236,7 @@ __device__ __forceinline__ bool consume_gemv(const Phase& P, const Ring& ring, u
     // whole when batch x K fits (one L2 round trip per phase), else one ring stage's K range at a time. Rows sit
     // 4 bank groups apart, like the weight rows. The inner loop reads activations from shared memory only.
     unsigned char* xs = (unsigned char*)scratch + SCRATCH_BYTES;
-    const bool whole = (size_t)P.batch * (P.K * 2 + 64) <= (size_t)XS_BYTES;
+    const bool whole = DIRECT || (size_t)P.batch * (P.K * 2 + 64) <= (size_t)XS_BYTES;
     // k values per staged row: the whole K, else a ring stage, else (a stage of 16 rows can exceed the staging area:
     // 16 x 4096 int4 inputs are 132 KB of bf16) the largest power-of-two part of a stage that fits
     const int xspan = whole ? P.K : stage_span(P.batch, G.stage_k);
@@ -242,14 +246,22 @@ __device__ __forceinline__ bool consume_gemv(const Phase& P, const Ring& ring, u
     const int spans_per_stage = whole ? 1 : G.stage_k / xspan;
     auto stage_x = [&](int k_begin) {
         const int cpr = xspan / 8;       // 16-byte chunks per row
-        for (int idx = tid; idx < P.batch * cpr; idx += CONSUMERS) {
+        const int total = P.batch * cpr;
+        // Every block stages the same bytes. Walking them from a block-dependent offset keeps the 148 blocks from asking
+        // the same L2 slice for the same line at the same moment.
+        const int rot = (int)(((long long)blockIdx.x * total) / gridDim.x) & ~7;
+        for (int i = tid; i < total; i += CONSUMERS) {
+            int idx = i + rot;
+            if (idx >= total) idx -= total;
             const int n = idx / cpr, c = idx % cpr;
             const uint4 v = load_x8<NORM, true>(P.x + (size_t)n * P.K, NORM ? P.fz.norm_x + (size_t)n * P.K : nullptr, P.fz.norm_gamma,
                                                 NORM ? scratch[n] : 1.0f, k_begin + c * 8, true);
             *(uint4*)(xs + (size_t)n * xpitch + c * 16) = v;
         }
     };
-    if (NT == 1 && NORM && P.K == CONSUMERS * 8 && P.batch <= 2) {
+    if (DIRECT) {
+        // nothing to stage
+    } else if (NT == 1 && NORM && P.K == CONSUMERS * 8 && P.batch <= 2) {
         stage_normed_rows(P, scratch, xs, xpitch);
     } else {
         if (NORM) row_norms<true>(P.fz, P.batch, P.K, scratch);   // once per phase
@@ -258,8 +270,9 @@ __device__ __forceinline__ bool consume_gemv(const Phase& P, const Ring& ring, u
     stamp(prof, 0);      // activations staged
     // this thread's activation rows (batch columns g and g + 8); a column beyond the batch reads zeros
     const bool xok0 = g < P.batch, xok1 = NT > 1 && (g + 8) < P.batch;
-    const unsigned char* xs0 = xs + (size_t)(xok0 ? g : 0) * xpitch;
-    const unsigned char* xs1 = xs + (size_t)(xok1 ? g + 8 : 0) * xpitch;
+    const unsigned char* xs0 = DIRECT ? (const unsigned char*)(P.x + (size_t)(xok0 ? g : 0) * P.K) : xs + (size_t)(xok0 ? g : 0) * xpitch;
+    const unsigned char* xs1 = DIRECT ? (const unsigned char*)(P.x + (size_t)(xok1 ? g + 8 : 0) * P.K) : xs + (size_t)(xok1 ? g + 8 : 0) * xpitch;
+    auto ldx = [](const unsigned char* p) { return DIRECT ? __ldg((const uint4*)p) : *(const uint4*)p; };
     bool ok = true;
     for (int gt = blockIdx.x; gt < P.n_blocks && ok; gt += gridDim.x) {
         int seg, tile;
@@ -306,7 +319,7 @@ __device__ __forceinline__ bool consume_gemv(const Phase& P, const Ring& ring, u
 #pragma unroll
                     for (int j = 0; j < NT; ++j) {
                         const unsigned char* xr = j == 0 ? xs0 : xs1;
-                        xv[j] = (j == 0 ? xok0 : xok1) ? *(const uint4*)(xr + (size_t)(kx + t * 8) * 2) : make_uint4(0, 0, 0, 0);
+                        xv[j] = (j == 0 ? xok0 : xok1) ? ldx(xr + (size_t)(kx + t * 8) * 2) : make_uint4(0, 0, 0, 0);
                     }
 #pragma unroll
                     for (int mI = 0; mI < NM; ++mI) {
@@ -335,8 +348,8 @@ __device__ __forceinline__ bool consume_gemv(const Phase& P, const Ring& ring, u
                     for (int j = 0; j < NT; ++j) {
                         const unsigned char* xr = j == 0 ? xs0 : xs1;
                         const bool xk = j == 0 ? xok0 : xok1;
-                        const uint4 xa = xk ? *(const uint4*)(xr + (size_t)(kx + t * 16) * 2) : make_uint4(0, 0, 0, 0);
-                        const uint4 xc = xk ? *(const uint4*)(xr + (size_t)(kx + t * 16 + 8) * 2) : make_uint4(0, 0, 0, 0);
+                        const uint4 xa = xk ? ldx(xr + (size_t)(kx + t * 16) * 2) : make_uint4(0, 0, 0, 0);
+                        const uint4 xc = xk ? ldx(xr + (size_t)(kx + t * 16 + 8) * 2) : make_uint4(0, 0, 0, 0);
                         // activation pairs matching the nibble pairing (n_i, n_{i+4})
                         const uint32_t bA0 = prmt(xa.x, xa.z, 0x5410), bA1 = prmt(xa.x, xa.z, 0x7632);
                         const uint32_t bA2 = prmt(xa.y, xa.w, 0x5410), bA3 = prmt(xa.y, xa.w, 0x7632);
@@ -390,6 +403,56 @@ __device__ __forceinline__ void amax_merge(float& v, int& i, float v2, int i2) {
     if (v2 > v || (v2 == v && i2 < i)) { v = v2; i = i2; }
 }
 
+// The producers' half of one contraction phase: this block's tiles, stage by stage, into the ring. `fill` counts the ring
+// stages issued so far by all producer warps together; warp `pw` issues the stages with fill % PRODUCERS == pw.
+__device__ __forceinline__ bool produce_phase(const Phase& P, const Ring& ring, uint64_t* s_full, uint64_t* s_empty, unsigned& fill, int lane,
+                                              int pw, unsigned* bar, int* err) {
+    bool ok = true;
+    {
+        const bool w4 = P.variant & 1, dual = (P.variant & 4) != 0;
+        const Geom G = geom_of(w4, dual, P.K);
+        const size_t full_row = w4 ? (size_t)P.K / 2 : (size_t)P.K * 2;
+        // The norm weight of an inlined RMSNorm is read once per step: cold in L2 by the time its phase starts
+        // (gigabytes have streamed through since) and on the consumers' critical path. The producers reach the phase
+        // a ring's depth early: ask L2 for it now.
+        if ((P.variant & 8) && lane == 0 && pw == 0)
+            asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(P.fz.norm_gamma), "r"(P.K * 2) : "memory");
+        for (int gt = blockIdx.x; gt < P.n_blocks && ok; gt += gridDim.x) {
+            int seg, tile;
+            seg_of_tile(P.segs, P.n_segments, dual, gt, seg, tile);
+            const char* src_row = nullptr;
+            const char* src_scale = nullptr;
+            if (lane < G.rows) {
+                const int mI = lane >> 4, r = lane & 15;
+                const int si = dual ? mI : seg;
+                const char* W = (const char*)(si == 0 ? P.segs.w[0] : (si == 1 ? P.segs.w[1] : P.segs.w[2]));
+                const int wr = weight_row(P.epilogue, P.fz, tile, r);
+                src_row = W + (size_t)wr * full_row;
+                if (G.scale_row_bytes) {
+                    const char* S = (const char*)(si == 0 ? P.segs.scales[0] : (si == 1 ? P.segs.scales[1] : P.segs.scales[2]));
+                    src_scale = S + (size_t)wr * (P.K / 64) * 2;
+                }
+            }
+            for (int s = 0; s < G.n_stages && ok; ++s, ++fill) {
+                if ((int)(fill % PRODUCERS) != pw) continue;
+                const int slot = fill % SLOTS;
+                if (lane == 0) {
+                    ok = mbar_wait(&s_empty[slot], ((fill / SLOTS) & 1) ^ 1, bar, err, 33);
+                    if (ok) mbar_expect_tx(&s_full[slot], (uint32_t)(G.rows * (G.row_bytes + G.scale_row_bytes)));
+                }
+                ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+                if (ok && lane < G.rows) {
+                    bulk_load(ring.base + slot * SLOT_BYTES + lane * G.pitch, src_row + (size_t)s * G.row_bytes, (uint32_t)G.row_bytes, &s_full[slot]);
+                    if (G.scale_row_bytes)
+                        bulk_load(ring.base + slot * SLOT_BYTES + G.scale_off + lane * G.scale_row_bytes,
+                                  src_scale + (size_t)s * G.scale_row_bytes, (uint32_t)G.scale_row_bytes, &s_full[slot]);
+                }
+            }
+        }
+    }
+    return ok;
+}
+
 // One instantiation per batch width (a program's contractions share it): fewer bodies per kernel keep the
 // register allocation of each one clean. Weight storage may differ per stage (int4 layers, bf16 lm_head);
 // ANY_I4 = false leaves the int4 bodies out for programs that have none.
@@ -425,46 +488,7 @@ decode_step_kernel(const Phase* __restrict__ phases, int n_phases, unsigned* bar
         for (int i = 0; i < n_phases && ok; ++i) {
             const Phase& P = phases[i];
             if (P.op != PH_GEMV) continue;
-            const bool w4 = P.variant & 1, dual = (P.variant & 4) != 0;
-            const Geom G = geom_of(w4, dual, P.K);
-            const size_t full_row = w4 ? (size_t)P.K / 2 : (size_t)P.K * 2;
-            // The norm weight of an inlined RMSNorm is read once per step: cold in L2 by the time its phase starts
-            // (gigabytes have streamed through since) and on the consumers' critical path. The producers reach the phase
-            // a ring's depth early: ask L2 for it now.
-            if ((P.variant & 8) && lane == 0 && pw == 0)
-                asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(P.fz.norm_gamma), "r"(P.K * 2) : "memory");
-            for (int gt = blockIdx.x; gt < P.n_blocks && ok; gt += gridDim.x) {
-                int seg, tile;
-                seg_of_tile(P.segs, P.n_segments, dual, gt, seg, tile);
-                const char* src_row = nullptr;
-                const char* src_scale = nullptr;
-                if (lane < G.rows) {
-                    const int mI = lane >> 4, r = lane & 15;
-                    const int si = dual ? mI : seg;
-                    const char* W = (const char*)(si == 0 ? P.segs.w[0] : (si == 1 ? P.segs.w[1] : P.segs.w[2]));
-                    const int wr = weight_row(P.epilogue, P.fz, tile, r);
-                    src_row = W + (size_t)wr * full_row;
-                    if (G.scale_row_bytes) {
-                        const char* S = (const char*)(si == 0 ? P.segs.scales[0] : (si == 1 ? P.segs.scales[1] : P.segs.scales[2]));
-                        src_scale = S + (size_t)wr * (P.K / 64) * 2;
-                    }
-                }
-                for (int s = 0; s < G.n_stages && ok; ++s, ++fill) {
-                    if ((int)(fill % PRODUCERS) != pw) continue;
-                    const int slot = fill % SLOTS;
-                    if (lane == 0) {
-                        ok = mbar_wait(&s_empty[slot], ((fill / SLOTS) & 1) ^ 1, bar, err, 33);
-                        if (ok) mbar_expect_tx(&s_full[slot], (uint32_t)(G.rows * (G.row_bytes + G.scale_row_bytes)));
-                    }
-                    ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-                    if (ok && lane < G.rows) {
-                        bulk_load(ring.base + slot * SLOT_BYTES + lane * G.pitch, src_row + (size_t)s * G.row_bytes, (uint32_t)G.row_bytes, &s_full[slot]);
-                        if (G.scale_row_bytes)
-                            bulk_load(ring.base + slot * SLOT_BYTES + G.scale_off + lane * G.scale_row_bytes,
-                                      src_scale + (size_t)s * G.scale_row_bytes, (uint32_t)G.scale_row_bytes, &s_full[slot]);
-                    }
-                }
-            }
+            ok = produce_phase(P, ring, s_full, s_empty, fill, lane, pw, bar, err);
         }
         if (lane == 0 && pw == 0) s_produced = fill;
     } else {
@@ -623,6 +647,48 @@ decode_step_kernel(const Phase* __restrict__ phases, int n_phases, unsigned* bar
     __syncthreads();
 }
 
+// One contraction as a kernel of its own, fed like a phase of the step kernel: producer warps stream the weights through
+// the shared-memory ring with bulk copies, consumer warps take their activations from global memory through L1. Used by
+// the launch-list form at batch > 8, where the register-staged loads of gemv_mma_kernel (two 64-blocks per warp: what 128
+// registers hold beside two accumulator tiles) keep about 10 MB in flight and 19 MB saturate HBM; the ring holds
+// 4 x 32 KB per SM in flight whatever the consumers' registers do. The weights do not depend on the stream predecessor,
+// so the producers start before the programmatic-launch wait; the consumers wait before they touch activations.
+template <bool W4, bool DUAL>
+__global__ void __launch_bounds__(THREADS, 1) gemv_ring_kernel(const __grid_constant__ Phase P, int* err) {
+    extern __shared__ __align__(128) unsigned char dyn[];       // [weight ring][contraction scratch]
+    __shared__ __align__(8) uint64_t s_full[SLOTS], s_empty[SLOTS];
+    __shared__ unsigned s_produced;
+    const int tid = threadIdx.x;
+    Ring ring{s_full, s_empty, smem_u32(dyn), dyn};
+    if (tid == 0) {
+        for (int i = 0; i < SLOTS; ++i) { mbar_init(&s_full[i], 1); mbar_init(&s_empty[i], gemv::GW); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        s_produced = 0;
+    }
+    __syncthreads();
+    if (tid >= CONSUMERS) {
+        const int lane = tid & 31, pw = (tid - CONSUMERS) >> 5;
+        unsigned fill = 0;
+        produce_phase(P, ring, s_full, s_empty, fill, lane, pw, nullptr, err);
+        if (lane == 0 && pw == 0) s_produced = fill;
+    } else {
+        griddep_launch();
+        griddep_wait();
+        uint32_t drained = 0;
+        consume_gemv<W4, 2, DUAL, false, true>(P, ring, drained, (float*)(dyn + RING_BYTES), nullptr, err, nullptr);
+    }
+    __syncthreads();
+    if (tid == 0) {      // no copy into this CTA's shared memory may still be in flight when it exits
+        const unsigned produced = s_produced;
+        const unsigned first = produced > SLOTS ? produced - SLOTS : 0;
+        for (unsigned f = first; f < produced; ++f) {
+            bool done = false;
+            for (unsigned it = 0; it < SPIN_LIMIT && !done; ++it) done = mbar_test(&s_full[f % SLOTS], (f / SLOTS) & 1);
+        }
+    }
+    __syncthreads();
+}
+
 }  // namespace
 
 struct Plan {
@@ -645,6 +711,33 @@ void destroy(Plan* plan) {
     if (plan->d_stamps) cudaFree(plan->d_stamps);
     if (plan->d_prof) cudaFree(plan->d_prof);
     delete plan;
+}
+
+// The ring-fed contraction for one stage of a launch list (batch > 8, no inlined norm). SANIC_ERR_UNSUPPORTED when the shape
+// has no ring geometry; the caller then uses the register-staged kernel.
+int32_t gemv_ring(sanic_ctx* ctx, const sanic_gemv_params* g, cudaStream_t stream) {
+    Phase P{};
+    int tiles = 0;
+    int32_t rc = gemv::host_prepare(ctx, g, P.segs, P.fz, tiles);
+    if (rc != SANIC_OK) return rc;
+    const bool w4 = g->weight_dtype == SANIC_I4, dual = g->epilogue == SANIC_EPI_SILU_MUL;
+    if (g->batch <= 8 || g->norm_x) return SANIC_ERR_UNSUPPORTED;
+    const Geom G = geom_of(w4, dual, g->K);
+    if (G.stage_k < 256 || g->K % G.stage_k != 0) return SANIC_ERR_UNSUPPORTED;
+    P.op = PH_GEMV; P.n_blocks = tiles;
+    P.variant = (w4 ? 1 : 0) | 2 | (dual ? 4 : 0);
+    P.x = (const uint16_t*)g->x; P.batch = g->batch; P.K = g->K; P.n_segments = g->n_segments;
+    P.out_dtype = g->out_dtype; P.epilogue = g->epilogue; P.residual = g->residual;
+    const size_t smem = RING_BYTES + SCRATCH_BYTES;
+    sanic_set_device(ctx);
+    auto go = [&](auto kern) -> int32_t {
+        SANIC_CUDA_CHECK(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        cudaError_t e = launch_pdl(kern, dim3(std::min(tiles, ctx->sm_count)), dim3(THREADS), smem, stream, P, ctx->status_dev);
+        if (e != cudaSuccess) return sanic_fail(ctx, SANIC_ERR_CUDA, std::string("gemv (ring): ") + cudaGetErrorString(e));
+        return SANIC_OK;
+    };
+    if (w4) return dual ? go(gemv_ring_kernel<true, true>) : go(gemv_ring_kernel<true, false>);
+    return dual ? go(gemv_ring_kernel<false, true>) : go(gemv_ring_kernel<false, false>);
 }
 
 int32_t build(sanic_ctx* ctx, const std::vector<sanic_stage_desc>& stages, Plan** out) {

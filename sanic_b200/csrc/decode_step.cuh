@@ -20,6 +20,9 @@ int32_t phase_times(sanic_ctx* ctx, Plan* plan, double* seconds, int cap);
 // Four numbers per phase of the last completed step: staged / contracted / finished / barrier released, in seconds from the phase's start.
 int32_t phase_profile(sanic_ctx* ctx, Plan* plan, double* out, int cap);
 void destroy(Plan* plan);
+// One contraction stage fed through a shared-memory ring by bulk copies (batch > 8): see gemv_ring_kernel.
+// SANIC_ERR_UNSUPPORTED when the shape has no ring geometry (no error text is set).
+int32_t gemv_ring(sanic_ctx* ctx, const sanic_gemv_params* p, cudaStream_t stream);
 
 }  // namespace step
 }  // namespace sanic

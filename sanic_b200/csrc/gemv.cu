@@ -29,6 +29,7 @@
 //     partners (d, d + D/2) of one head, so the epilogue rotates them and writes q, the K
 //     cache row and the V cache column of the current position in place.
 // Launched with programmatic dependent launch: weight prefetch runs before the wait.
+#include "decode_step.cuh"
 #include "gemv_body.cuh"
 
 namespace {
@@ -82,6 +83,13 @@ extern "C" int32_t sanic_gemv(sanic_ctx* ctx, const sanic_gemv_params* p, void* 
     cudaStream_t st = (cudaStream_t)stream;
     const bool w4 = p->weight_dtype == SANIC_I4;
     const bool wide = p->batch > 8;
+    // batch > 8: the contraction fed through a shared-memory ring by bulk copies keeps twice the bytes in flight
+    // (SANIC_GEMV_RING=0 keeps the register-staged kernel, for A/B timing)
+    static const bool ring = !(getenv("SANIC_GEMV_RING") && getenv("SANIC_GEMV_RING")[0] == '0');
+    if (wide && ring && !p->norm_x) {
+        rc = sanic::step::gemv_ring(ctx, p, st);
+        if (rc != SANIC_ERR_UNSUPPORTED) return rc;
+    }
     if (dual) {
         if (w4) return wide ? launch_n<true, 2, true>(ctx, *p, segs, fz, tiles, st) : launch_n<true, 1, true>(ctx, *p, segs, fz, tiles, st);
         return wide ? launch_n<false, 2, true>(ctx, *p, segs, fz, tiles, st) : launch_n<false, 1, true>(ctx, *p, segs, fz, tiles, st);
