@@ -733,6 +733,397 @@ gemm_rmsnorm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
     }
 }
 
+// ───────────────────────── the pair tile with A brought in through registers ─────────────────────────
+// Same 256x256 tile on a pair of SMs, same accumulators and epilogue; selected with SANIC_GEMM_PAIR=2. It moves fewer
+// bytes through shared memory than the kernel above (per k-block and SM: 16 KB of A stored once from registers instead of
+// copied in, read, multiplied and written back) and measures the same (131 against 128 us at 4096 x 2048 x 8192), which
+// is why the kernel above stays the default: at this tile neither form is bound by bytes but by chains of shared-memory
+// and barrier latencies that the tensor core's own operand reads stretch (measured in this kernel with clock counters, on
+// the thread concerned, while the MMAs run: a satisfied mbarrier wait 210 clocks, a shared-memory load 55, a tcgen05.mma
+// issue 60-130, sixteen bytes stored per lane 30, dependent ALU instructions of a transform warp 4.5 each).
+//   * A never waits in shared memory for data: four groups of transform warps take every fourth k-block; a warp loads x
+//     from global memory into REGISTERS one of its k-blocks ahead, multiplies by g and takes sum x^2 while the slot may
+//     still be busy, and stores the swizzled tile when the slot frees (a slot's life starts at the store);
+//   * both CTAs' B copies complete on the LEADER's barrier (cp.async.bulk.tensor.cta_group::2 with the leader's mbarrier),
+//     so no warp has to vouch for B;
+//   * one tcgen05.commit per stage frees the slot in both CTAs (mbarrier multicast of the commit), no relay;
+//   * the MMA thread waits on no barrier inside a tile: watcher threads turn barrier completions into counters (the
+//     peer's through one posted store into the leader's shared memory per k-block), and one read of the counters often
+//     covers several k-blocks.
+// With gamma == NULL (weights scaled beforehand) the same path runs without the multiply.
+constexpr int P2_GROUPS = 4;          // groups of transform warps; each takes every P2_GROUPS-th k-block
+struct P2Shared {
+    uint64_t full_b[PB_SLOTS], ready[PB_SLOTS], empty[PB_SLOTS];
+    uint64_t tmem_full[2], tmem_empty[2], ss_full[2], ss_empty[2];
+    uint32_t tmem_base;
+    volatile int abort_flag;
+    // k-blocks (of the pair's sequence) whose B halves have landed / whose A half is stored in this CTA / in the peer
+    // (the leader's copies are the ones read; the peer writes seen_a_peer into the leader's shared memory)
+    uint32_t seen_b, seen_a, seen_a_peer;
+    float ss[2][P2_GROUPS][BM];   // [accumulator use parity][transform group][row]
+};
+template <bool CLUSTER>
+__device__ __forceinline__ bool mbar_wait_p2(uint64_t* bar, uint32_t parity, P2Shared* sh, int* err, int code) {
+    uint32_t addr = smem_u32(bar);
+    for (uint32_t it = 0; it < P_SPIN_LIMIT; ++it) {
+        uint32_t done;
+        if (CLUSTER)
+            asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                         : "=r"(done) : "r"(addr), "r"(parity) : "memory");
+        else
+            asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                         : "=r"(done) : "r"(addr), "r"(parity) : "memory");
+        if (done) return true;
+        if ((it & 1023u) == 1023u && sh->abort_flag) return false;
+    }
+    sh->abort_flag = 1;
+    atomicCAS(err, 0, code);
+    return false;
+}
+// one lane waits for the warp: 31 fewer pollers on the barrier per warp
+template <bool CLUSTER>
+__device__ __forceinline__ bool warp_wait_p2(uint64_t* bar, uint32_t parity, P2Shared* sh, int* err, int code, int lane) {
+    int ok = 1;
+    if (lane == 0) ok = mbar_wait_p2<CLUSTER>(bar, parity, sh, err, code) ? 1 : 0;
+    return __shfl_sync(0xffffffffu, ok, 0) != 0;
+}
+// this CTA's copy, completion counted on the mbarrier at `bar_cluster_addr` (the leader's)
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, uint32_t bar_cluster_addr, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                 ::"r"(dst), "l"((uint64_t)map), "r"(bar_cluster_addr), "r"(x), "r"(y) : "memory");
+}
+// arrives on the barrier at this offset in BOTH CTAs of the pair when the pair's MMAs so far retire
+__device__ __forceinline__ void umma2_commit_both(uint64_t* bar) {
+    const uint16_t mask = 3;
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(smem_u32(bar)), "h"(mask) : "memory");
+}
+
+__global__ void __launch_bounds__(P_NTHREADS, 1)
+gemm_rmsnorm_pair_reg_kernel(const __grid_constant__ CUtensorMap map_b, const __grid_constant__ CUtensorMap map_y,
+                             const uint16_t* __restrict__ x, const uint16_t* __restrict__ gamma, void* __restrict__ y,
+                             int M, int N, int K, int w_is_nk, float eps, int out_dtype, int* err, int gamma_bytes, int bulk_store) {
+    extern __shared__ unsigned char smem_dyn[];
+    const uint32_t raw = smem_u32(smem_dyn);
+    const uint32_t base = (raw + 1023u) & ~1023u;
+    unsigned char* aligned = smem_dyn + (base - raw);
+    uint16_t* gsm = (uint16_t*)(aligned + P_RING_BYTES);
+    const uint32_t b_ring = base + PA_SLOTS * A_BYTES;
+    const uint32_t stage_out = base + P_RING_BYTES + gamma_bytes;
+    P2Shared* sh = (P2Shared*)(aligned + P_RING_BYTES + gamma_bytes + (bulk_store ? P_OUT_BYTES : 0));
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_rank();
+    const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+    const int kblocks = (K + BK - 1) / BK;
+    const int m_tiles = (M + 2 * BM - 1) / (2 * BM), n_tiles = (N + BN - 1) / BN;
+    const int tiles = m_tiles * n_tiles;
+    const bool scaled = gamma != nullptr;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < PB_SLOTS; ++s) { mbar_init(&sh->full_b[s], 1); mbar_init(&sh->ready[s], 16 / P2_GROUPS); mbar_init(&sh->empty[s], 1); }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(&sh->tmem_full[a], 1); mbar_init(&sh->tmem_empty[a], 16);
+            mbar_init(&sh->ss_full[a], 16); mbar_init(&sh->ss_empty[a], 8);
+        }
+        sh->abort_flag = 0;
+        sh->tmem_base = 0;
+        sh->seen_a = 0; sh->seen_b = 0; sh->seen_a_peer = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (scaled)
+        for (int i = threadIdx.x; i < kblocks * BK; i += P_NTHREADS) gsm[i] = (i < K) ? gamma[i] : (uint16_t)0;
+    __syncthreads();
+    if (warp == 3) {
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sh->tmem_base)), "r"(512));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;");
+    }
+    tc_fence_before();
+    cluster_sync_all();
+    tc_fence_after();
+    const uint32_t tmem = sh->tmem_base;
+
+    if (warp == 0) {
+        // ── TMA producer for B: this CTA's 128 columns into its own shared memory, bytes counted on the leader's barrier ──
+        if (lane == 0) {
+            int stage = 0; uint32_t phase = 1;
+            bool ok = true;
+            for (int t = pair; t < tiles && ok; t += n_pairs) {
+                const int n0 = (t / m_tiles) * BN + (int)rank * (BN / 2);
+                for (int kb = 0; kb < kblocks; ++kb) {
+                    ok = mbar_wait_p2<false>(&sh->empty[stage], phase, sh, err, 21);
+                    if (!ok) break;
+                    const uint32_t sb = b_ring + stage * PB_BYTES;
+                    const uint32_t bar = map_to_rank(smem_u32(&sh->full_b[stage]), 0);
+                    if (rank == 0) mbar_expect_tx(&sh->full_b[stage], 2 * PB_BYTES);      // both halves
+                    if (w_is_nk) {
+                        tma_load_2d_pair(sb, &map_b, bar, kb * BK, n0);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < BN / 128; ++j)
+                            tma_load_2d_pair(sb + j * (64 * BK * 2), &map_b, bar, n0 + 64 * j, kb * BK);
+                    }
+                    if (++stage == PB_SLOTS) { stage = 0; phase ^= 1; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ── MMA issuer: the leader CTA only ──
+        if (lane == 0 && rank == 0) {
+            const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((w_is_nk ? 0u : 1u) << 16) |
+                                   ((uint32_t)(BN >> 3) << 17) | ((uint32_t)((2 * BM) >> 4) << 24);
+            int stage = 0; uint32_t phase = 0;
+            int use = 0;
+            bool ok = true;
+            uint32_t q = 0, avail = 0;
+            for (int t = pair; t < tiles && ok; t += n_pairs, ++use) {
+                const int ab = use & 1;
+                ok = mbar_wait_p2<true>(&sh->tmem_empty[ab], ((use >> 1) & 1) ^ 1, sh, err, 22);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t acc = tmem + (uint32_t)ab * BN;
+                for (int kb = 0; kb < kblocks; ++kb) {
+                    if (q >= avail) {
+                        // one plain shared-memory read per counter instead of two mbarrier waits (a satisfied mbarrier wait costs
+                        // this thread about 210 clocks, a shared-memory load 55): the watcher threads below turn barrier
+                        // completions into counters, and one read often covers several k-blocks
+                        uint32_t it = 0;
+                        for (;;) {
+                            uint32_t pa, pp, pb;
+                            asm volatile("ld.acquire.cta.shared.u32 %0, [%1];" : "=r"(pa) : "r"(smem_u32(&sh->seen_a)) : "memory");
+                            asm volatile("ld.acquire.cluster.shared.u32 %0, [%1];" : "=r"(pp) : "r"(smem_u32(&sh->seen_a_peer)) : "memory");
+                            asm volatile("ld.acquire.cta.shared.u32 %0, [%1];" : "=r"(pb) : "r"(smem_u32(&sh->seen_b)) : "memory");
+                            avail = pa < pb ? pa : pb;
+                            avail = avail < pp ? avail : pp;
+                            if (q < avail) break;
+                            if (++it > P_SPIN_LIMIT || ((it & 1023u) == 0 && sh->abort_flag)) { if (it > P_SPIN_LIMIT) { sh->abort_flag = 1; atomicCAS(err, 0, 23); } ok = false; break; }
+                        }
+                        if (!ok) break;
+                    }
+                    const uint32_t sb = b_ring + stage * PB_BYTES;
+                    const uint64_t adesc = make_desc(base + stage * A_BYTES, 16, 1024);
+                    const uint64_t bdesc = w_is_nk ? make_desc(sb, 16, 1024) : make_desc(sb, 64 * BK * 2, 1024);
+#pragma unroll
+                    for (int k = 0; k < BK / 16; ++k) {
+                        const uint64_t bd = bdesc + (uint64_t)(w_is_nk ? k * 2 : k * 128);
+                        umma2_f16_ss(acc, adesc + (uint64_t)(k * 2), bd, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                    }
+                    umma2_commit_both(&sh->empty[stage]);
+                    ++q;
+                    if (++stage == PB_SLOTS) { stage = 0; phase ^= 1; }
+                }
+                if (ok) umma2_commit_both(&sh->tmem_full[ab]);
+            }
+        }
+    } else if (warp == 2 || warp == 3) {
+        // ── watchers: turn barrier completions into counters in the LEADER's shared memory. Leader warp 2: B landed (both
+        // halves, counted by the copies themselves); warp 3 of each CTA: this CTA's A half stored (the peer writes its
+        // counter across the cluster: one posted store per k-block instead of a remote barrier arrival per warp, which
+        // held each arriving warp for about 800 clocks) ──
+        if (lane == 0 && (rank == 0 || warp == 3)) {
+            uint64_t* bars = warp == 2 ? sh->full_b : sh->ready;
+            const uint32_t out = map_to_rank(smem_u32(warp == 2 ? &sh->seen_b : (rank == 0 ? &sh->seen_a : &sh->seen_a_peer)), 0);
+            int stage = 0; uint32_t phase = 0;
+            const int my_tiles = pair < tiles ? (tiles - pair + n_pairs - 1) / n_pairs : 0;
+            const uint32_t total = (uint32_t)(my_tiles * kblocks);
+            for (uint32_t q = 0; q < total; ++q) {
+                if (!mbar_wait_p2<false>(&bars[stage], phase, sh, err, warp == 2 ? 28 : 29)) break;
+                if (rank == 0) asm volatile("st.release.cta.shared::cluster.u32 [%0], %1;" ::"r"(out), "r"(q + 1) : "memory");
+                else asm volatile("st.relaxed.cluster.shared::cluster.u32 [%0], %1;" ::"r"(out), "r"(q + 1) : "memory");
+                if (++stage == PB_SLOTS) { stage = 0; phase ^= 1; }
+            }
+        }
+    } else if (warp >= 4 && warp < 20) {
+        // ── A (both CTAs): global memory -> registers -> x*g -> swizzled shared memory, sum x^2 ──
+        // P2_GROUPS groups of warps take every P2_GROUPS-th k-block of the pair's sequence (over all its tiles): a k-block costs
+        // a warp a chain of latencies (barrier wake-up, the loads' arrival, stores, the proxy fence, the arrival at the
+        // leader) of about 900 clocks, and the tensor cores want one every 512. A warp covers rows 4w..4w+3 of each 16-row
+        // band: 8 lanes per row, 16 bytes each, so a load instruction reads four whole 128-byte rows.
+        constexpr int WPG = 16 / P2_GROUPS, RPT = 32 / WPG;          // warps per group; rows per thread
+        const int group = (warp - 4) / WPG, wg = (warp - 4) % WPG;
+        const int c = lane & 7;                        // 16-byte chunk of the row
+        const int r0 = wg * 4 + (lane >> 3);           // row within a (4 * WPG)-row band; rows r0 + 4 * WPG * j
+        const uint32_t swz = (uint32_t)((c ^ (r0 & 7)) << 4);
+        const int my_tiles = pair < tiles ? (tiles - pair + n_pairs - 1) / n_pairs : 0;
+        float ss[RPT];
+#pragma unroll
+        for (int j = 0; j < RPT; ++j) ss[j] = 0.0f;
+        bool ok = true;
+        // the load stream runs one of this group's k-blocks ahead of the store stream; both walk (tile use, k-block) by P2_GROUPS
+        int f_use = 0, f_kb = group, s_use = 0, s_kb = group, stage = group % PA_SLOTS;
+        uint32_t phase = 1;                            // producer parity: the first pass over the ring does not wait
+        while (f_kb >= kblocks && f_use < my_tiles) { f_kb -= kblocks; ++f_use; }
+        while (s_kb >= kblocks && s_use < my_tiles) { s_kb -= kblocks; ++s_use; }
+        auto row_base = [&](int use) { const int t = pair + use * n_pairs; return (t % m_tiles) * (2 * BM) + (int)rank * BM + r0; };
+        int f_row = f_use < my_tiles ? row_base(f_use) : 0;
+        uint4 buf[RPT];
+        auto fetch = [&]() {
+            if (f_use >= my_tiles) return;
+            const int k0 = f_kb * BK + c * 8;
+#pragma unroll
+            for (int j = 0; j < RPT; ++j) {
+                const int gr = f_row + 4 * WPG * j;
+                buf[j] = (gr < M && k0 < K) ? __ldg((const uint4*)(x + (size_t)gr * K + k0)) : make_uint4(0, 0, 0, 0);
+            }
+            f_kb += P2_GROUPS;
+            if (f_kb >= kblocks) {
+                do { f_kb -= kblocks; ++f_use; } while (f_kb >= kblocks);
+                if (f_use < my_tiles) f_row = row_base(f_use);
+            }
+        };
+        auto flush = [&](int use) -> bool {            // this group's sum x^2 of tile `use` to the epilogue
+            const int a = use & 1;
+            if (!warp_wait_p2<false>(&sh->ss_empty[a], ((use >> 1) & 1) ^ 1, sh, err, 25, lane)) return false;
+#pragma unroll
+            for (int j = 0; j < RPT; ++j) {
+                float v = ss[j];
+                v += __shfl_xor_sync(0xffffffffu, v, 1);
+                v += __shfl_xor_sync(0xffffffffu, v, 2);
+                v += __shfl_xor_sync(0xffffffffu, v, 4);
+                if (c == 0) sh->ss[a][group][r0 + 4 * WPG * j] = v;
+                ss[j] = 0.0f;
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&sh->ss_full[a]);
+            return true;
+        };
+        int flushed = 0;
+        fetch();
+        while (s_use < my_tiles && ok) {
+            while (flushed < s_use && ok) { ok = flush(flushed); ++flushed; }
+            if (!ok) break;
+            // multiply and square while the slot may still be busy: only the stores wait for it
+            uint4 gv = make_uint4(0, 0, 0, 0);
+            if (scaled) gv = *(const uint4*)(gsm + s_kb * BK + c * 8);
+            const uint32_t gs[4] = {gv.x, gv.y, gv.z, gv.w};
+#pragma unroll
+            for (int j = 0; j < RPT; ++j) {
+                uint32_t xs[4] = {buf[j].x, buf[j].y, buf[j].z, buf[j].w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float x0 = bf16lo(xs[e]), x1 = bf16hi(xs[e]);
+                    ss[j] = fmaf(x0, x0, ss[j]); ss[j] = fmaf(x1, x1, ss[j]);
+                    // bf16 x bf16 is exact in f32, so the packed multiply equals bf16(float(x) * float(g)) bit for bit
+                    if (scaled) asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(xs[e]) : "r"(xs[e]), "r"(gs[e]));
+                }
+                buf[j] = make_uint4(xs[0], xs[1], xs[2], xs[3]);
+            }
+            ok = warp_wait_p2<false>(&sh->empty[stage], phase, sh, err, 24, lane);      // the pair's MMAs on this slot retired
+            if (!ok) break;
+            const uint32_t slot = base + stage * A_BYTES + (uint32_t)r0 * 128u + swz;
+#pragma unroll
+            for (int j = 0; j < RPT; ++j)
+                asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(slot + (uint32_t)(4 * WPG * j) * 128u),
+                             "r"(buf[j].x), "r"(buf[j].y), "r"(buf[j].z), "r"(buf[j].w) : "memory");
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // generic writes -> visible to the tensor core's reads
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&sh->ready[stage]);       // this CTA's barrier; its watcher tells the leader
+            fetch();                                   // the next of this group's k-blocks, in flight until its slot frees
+            s_kb += P2_GROUPS;
+            while (s_kb >= kblocks) { s_kb -= kblocks; ++s_use; }
+            stage += P2_GROUPS;
+            if (stage >= PA_SLOTS) { stage -= PA_SLOTS; phase ^= 1; }
+        }
+        while (ok && flushed < my_tiles) { ok = flush(flushed); ++flushed; }
+    } else if (warp >= 20) {
+        // ── epilogue (both CTAs): this CTA's 128 rows of the 256 x 256 tile; two warps per lane quarter, 128 columns each ──
+        const int q = warp & 3;
+        const int row = q * 32 + lane;
+        const int c_begin = ((warp - 20) >> 2) * (BN / 64);
+        const bool wide_ok = (N % 16 == 0) && (((uintptr_t)y & 31) == 0);
+        int use = 0;
+        bool ok = true;
+        const float inv_k = 1.0f / (float)K;
+        for (int t = pair; t < tiles && ok; t += n_pairs, ++use) {
+            const int a = use & 1;
+            const int m0 = (t % m_tiles) * (2 * BM) + (int)rank * BM, n0 = (t / m_tiles) * BN;
+            ok = mbar_wait_p2<false>(&sh->ss_full[a], (use >> 1) & 1, sh, err, 26);
+            if (!ok) break;
+            float ssv = 0.0f;
+#pragma unroll
+            for (int gI = 0; gI < P2_GROUPS; ++gI) ssv += sh->ss[a][gI][row];
+            const float rstd = 1.0f / sqrtf(ssv * inv_k + eps);
+            ok = mbar_wait_p2<false>(&sh->tmem_full[a], (use >> 1) & 1, sh, err, 27);
+            if (!ok) break;
+            tc_fence_after();
+            const int gr = m0 + row;
+#pragma unroll 1
+            for (int cc = c_begin; cc < c_begin + BN / 64; ++cc) {
+                uint32_t r[32];
+                tmem_ld32(tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)a * BN + cc * 32, r);
+                const int gc = n0 + cc * 32;
+                if (bulk_store) {
+                    // bf16 through shared memory and one bulk tensor store per 32 x 32 block; the copy engine clips the
+                    // block at the edges of y
+                    const uint32_t mine = stage_out + (uint32_t)(warp - 20) * 2048u;
+                    if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");    // the previous block has been read out
+                    __syncwarp();
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const uint32_t p0 = pack_bf16x2(__uint_as_float(r[8 * j]) * rstd, __uint_as_float(r[8 * j + 1]) * rstd);
+                        const uint32_t p1 = pack_bf16x2(__uint_as_float(r[8 * j + 2]) * rstd, __uint_as_float(r[8 * j + 3]) * rstd);
+                        const uint32_t p2 = pack_bf16x2(__uint_as_float(r[8 * j + 4]) * rstd, __uint_as_float(r[8 * j + 5]) * rstd);
+                        const uint32_t p3 = pack_bf16x2(__uint_as_float(r[8 * j + 6]) * rstd, __uint_as_float(r[8 * j + 7]) * rstd);
+                        // 64-byte rows: the 16-byte chunk index is XORed with (row / 2) % 4, the copy engine's 64-byte swizzle
+                        const uint32_t at = mine + (uint32_t)lane * 64u + (uint32_t)((j ^ ((lane >> 1) & 3)) << 4);
+                        asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(at), "r"(p0), "r"(p1), "r"(p2), "r"(p3) : "memory");
+                    }
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    __syncwarp();
+                    if (lane == 0 && gc < N && m0 + q * 32 < M) {
+                        asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];"
+                                     ::"l"((uint64_t)&map_y), "r"(gc), "r"(m0 + q * 32), "r"(mine) : "memory");
+                        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                    }
+                } else if (gr < M && gc < N) {
+                    if (out_dtype == SANIC_BF16) {
+                        uint32_t pk[16];
+#pragma unroll
+                        for (int j = 0; j < 16; ++j)
+                            pk[j] = pack_bf16x2(__uint_as_float(r[2 * j]) * rstd, __uint_as_float(r[2 * j + 1]) * rstd);
+                        uint16_t* dst = (uint16_t*)y + (size_t)gr * N + gc;
+                        if (gc + 32 <= N && wide_ok) {
+#pragma unroll
+                            for (int j = 0; j < 2; ++j)
+                                asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(dst + 16 * j), "r"(pk[8 * j]),
+                                             "r"(pk[8 * j + 1]), "r"(pk[8 * j + 2]), "r"(pk[8 * j + 3]), "r"(pk[8 * j + 4]),
+                                             "r"(pk[8 * j + 5]), "r"(pk[8 * j + 6]), "r"(pk[8 * j + 7]) : "memory");
+                        } else if (gc + 32 <= N) {
+#pragma unroll
+                            for (int j = 0; j < 4; ++j)
+                                *(uint4*)(dst + 8 * j) = make_uint4(pk[4 * j], pk[4 * j + 1], pk[4 * j + 2], pk[4 * j + 3]);
+                        } else {
+                            for (int j = 0; j < 32 && gc + j < N; ++j)
+                                dst[j] = (uint16_t)((j & 1) ? (pk[j >> 1] >> 16) : (pk[j >> 1] & 0xFFFF));
+                        }
+                    } else {
+                        float* dst = (float*)y + (size_t)gr * N + gc;
+                        if (gc + 32 <= N) {
+#pragma unroll
+                            for (int j = 0; j < 8; ++j)
+                                *(float4*)(dst + 4 * j) = make_float4(__uint_as_float(r[4 * j]) * rstd, __uint_as_float(r[4 * j + 1]) * rstd,
+                                                                      __uint_as_float(r[4 * j + 2]) * rstd, __uint_as_float(r[4 * j + 3]) * rstd);
+                        } else {
+                            for (int j = 0; j < 32 && gc + j < N; ++j) dst[j] = __uint_as_float(r[j]) * rstd;
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) { mbar_arrive_cluster_relaxed(map_to_rank(smem_u32(&sh->tmem_empty[a]), 0)); mbar_arrive(&sh->ss_empty[a]); }
+        }
+    }
+    if (bulk_store && warp >= 20 && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+    // teardown: neither CTA may leave (or free tensor memory) while the other can still reach into it
+    tc_fence_before();
+    cluster_sync_all();
+    if (warp == 3) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512));
+    }
+}
+
 typedef CUresult (*encode_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                               const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                               CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -822,7 +1213,7 @@ extern "C" int32_t sanic_gemm_rmsnorm(sanic_ctx* ctx, const sanic_gemm_rmsnorm_p
     const char* force = getenv("SANIC_GEMM_PAIR");
     // gamma == NULL: the weights were pre-scaled with sanic_gemm_prescale_weights (only the pair kernel has that form)
     const bool prescaled = (p->gamma == nullptr);
-    const bool use_pair = prescaled || (force ? (force[0] == '1') : (p->M >= 4 * BM && pair_tiles >= ctx->sm_count / 2));
+    const bool use_pair = prescaled || (force ? (force[0] == '1' || force[0] == '2') : (p->M >= 4 * BM && pair_tiles >= ctx->sm_count / 2));
     if (use_pair) {
         // the 256 x 256 tile on a pair of SMs: B's map has a 128-row box (this CTA's half)
         if (p->w_is_nk) {
@@ -840,6 +1231,10 @@ extern "C" int32_t sanic_gemm_rmsnorm(sanic_ctx* ctx, const sanic_gemm_rmsnorm_p
             rc = encode_2d(ctx, &map_y, p->y, (uint64_t)p->N, (uint64_t)p->M, 32, 32, CU_TENSOR_MAP_SWIZZLE_64B);
             if (rc != SANIC_OK) return rc;
         }
+        const bool reg_path = force && force[0] == '2';
+        if (reg_path) {
+            SANIC_CUDA_CHECK(ctx, cudaFuncSetAttribute(gemm_rmsnorm_pair_reg_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, psmem));
+        }
         SANIC_CUDA_CHECK(ctx, cudaFuncSetAttribute(gemm_rmsnorm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, psmem));
         const int ptiles = ((p->M + 2 * BM - 1) / (2 * BM)) * ((p->N + BN - 1) / BN);
         cudaLaunchConfig_t cfg = {};
@@ -854,6 +1249,13 @@ extern "C" int32_t sanic_gemm_rmsnorm(sanic_ctx* ctx, const sanic_gemm_rmsnorm_p
         int pairs = ptiles < max_clusters ? ptiles : max_clusters;
         if (pairs > ctx->sm_count / 2) pairs = ctx->sm_count / 2;
         cfg.gridDim = dim3(2 * pairs);
+        if (reg_path) {
+            cudaError_t le = cudaLaunchKernelEx(&cfg, gemm_rmsnorm_pair_reg_kernel, map_b, map_y, (const uint16_t*)p->x, (const uint16_t*)p->gamma, p->y,
+                                                (int)p->M, (int)p->N, (int)p->K, (int)p->w_is_nk, p->eps, (int)p->out_dtype, ctx->status_dev,
+                                                gamma_bytes, bulk_store);
+            if (le != cudaSuccess) return sanic_fail(ctx, SANIC_ERR_CUDA, std::string("gemm_rmsnorm (pair, registers): ") + cudaGetErrorString(le));
+            return SANIC_OK;
+        }
         cudaError_t le = cudaLaunchKernelEx(&cfg, gemm_rmsnorm_pair_kernel, map_a, map_b, map_y, (const uint16_t*)p->gamma, p->y, (int)p->M,
                                             (int)p->N, (int)p->K, (int)p->w_is_nk, p->eps, (int)p->out_dtype, ctx->status_dev,
                                             gamma_bytes, bulk_store, prescaled ? 1 : 0);
@@ -869,3 +1271,7 @@ extern "C" int32_t sanic_gemm_rmsnorm(sanic_ctx* ctx, const sanic_gemm_rmsnorm_p
     SANIC_LAUNCH_CHECK(ctx, "gemm_rmsnorm");
     return SANIC_OK;
 }
+
+
+
+

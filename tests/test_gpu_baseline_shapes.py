@@ -70,7 +70,7 @@ def test_c2_full_shape_sampled_rows(dev, monkeypatch):
     rows[0], rows[-1] = 0, M - 1
     exp = orc.rmsnorm_gemm(orc.from_bf16_bits(xb[rows]), orc.from_bf16_bits(gb), orc.from_bf16_bits(wb), eps=1e-5, w_is_nk=False)
     worst = {}
-    for form in ("0", "1"):                  # one-CTA 128x256 tile, and the 256x256 tile on SM pairs
+    for form in ("0", "1", "2"):                # one-CTA 128x256 tile, and the 256x256 tile on SM pairs
         monkeypatch.setenv("SANIC_GEMM_PAIR", form)
         for nk, w in ((False, w_kn), (True, w_nk)):
             y = dev.gemm_rmsnorm(x, g, w, eps=1e-5, w_is_nk=nk)

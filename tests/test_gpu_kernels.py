@@ -479,7 +479,7 @@ def test_gemm_rmsnorm_many_tiles_per_cta(dev):
     assert got.shape == (2048, 8192)
 
 
-@pytest.mark.parametrize("form", ["0", "1"])
+@pytest.mark.parametrize("form", ["0", "1", "2"])
 def test_gemm_rmsnorm_both_tile_forms(dev, form, monkeypatch):
     # SANIC_GEMM_PAIR forces the one-CTA 128 x 256 tile ("0") or the 256 x 256 tile on a pair of SMs ("1": two CTAs of a
     # cluster, tcgen05 cta_group::2, bulk tensor stores); without it the library picks by problem size
