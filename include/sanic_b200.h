@@ -378,7 +378,11 @@ int32_t sanic_generic_destroy(sanic_generic_kernel* k);
 typedef struct sanic_program sanic_program;
 enum { SANIC_STAGE_FUSED = 1, SANIC_STAGE_ELEMENTWISE = 2, SANIC_STAGE_GATHER = 3 };  /* src/partition.rs:44-98 */
 enum { SANIC_OP_GEMV = 1, SANIC_OP_DECODE_ATTN = 2, SANIC_OP_ARGMAX = 3, SANIC_OP_RMSNORM = 4, SANIC_OP_EMBED = 5,
-       SANIC_OP_ROPE_CACHE = 6, SANIC_OP_ADVANCE = 7, SANIC_OP_GENERIC = 8 };
+       SANIC_OP_ROPE_CACHE = 6, SANIC_OP_ADVANCE = 7, SANIC_OP_GENERIC = 8,
+       SANIC_OP_ATTN_FWD = 9,      /* the online-softmax fold over many queries: prefill and plain attention (FUSED) */
+       SANIC_OP_GEMM_RMSNORM = 10, /* the deferred-normaliser contraction (FUSED) */
+       SANIC_OP_ROPE = 11 };       /* rotate-half RoPE of whole [rows, seq, D] operands, the cut the reference makes in front
+                                      of a fold over projected operands (src/partition.rs:1295-1311) (ELEMENTWISE) */
 typedef struct {
     int32_t stage_kind;          /* SANIC_STAGE_* */
     int32_t op;                  /* SANIC_OP_* */
@@ -393,6 +397,9 @@ typedef struct {
         sanic_rope_cache_params rope_cache;
         struct { int32_t* position; } advance;
         struct { sanic_generic_kernel* kernel; const void* buffers[16]; int32_t n_buffers; void* out; } generic;   /* a compiled fallback kernel */
+        struct { sanic_attn_params p; int32_t storage; /* SANIC_F32: CUDA-core path; SANIC_BF16: tensor-core path */ } attn;
+        sanic_gemm_rmsnorm_params gemm;
+        struct { const void* x; void* out; int64_t rows; int32_t seq, head_dim; const float* table; int32_t pos0; } rope;
     } u;
 } sanic_stage_desc;
 int32_t sanic_program_create(sanic_ctx* ctx, const sanic_stage_desc* stages, int32_t n_stages, sanic_program** out);
@@ -454,10 +461,12 @@ typedef struct { const char* name; const void* dptr; int32_t dtype; int32_t rank
 typedef struct { void* dptr; int32_t dtype; int32_t rank; int64_t shape[SANIC_MAX_AXES]; size_t bytes; } sanic_buffer_view;
 typedef struct sanic_schedule sanic_schedule;
 typedef struct sanic_replay sanic_replay;
-/* Backend::prepare (src/compile.rs:94-99): validates the table, the relocations, the roots and the in-place pairs. */
+/* Backend::prepare (src/compile.rs:94-99): validates the table, every stage's structure (kind, op, carrier family, leaf
+ * storage), the relocations, the roots and the in-place pairs. */
 int32_t sanic_schedule_compile(sanic_ctx* ctx, const sanic_schedule_desc* desc, sanic_schedule** out);
 int32_t sanic_schedule_destroy(sanic_schedule* s);
-const char* sanic_schedule_last_error(sanic_schedule* s);   /* also set when the schedule has no context */
+const char* sanic_schedule_last_error(sanic_schedule* s);   /* also set when the schedule has no context; with s == NULL: why
+                                                               this thread's last sanic_schedule_compile failed */
 int32_t sanic_schedule_input_count(sanic_schedule* s);      /* Program::input_names (src/compile.rs:138-140) */
 const char* sanic_schedule_input_name(sanic_schedule* s, int32_t i);
 int32_t sanic_schedule_output_count(sanic_schedule* s);

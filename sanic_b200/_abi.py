@@ -21,6 +21,7 @@ KERNEL_NONE, KERNEL_ONLINE_SOFTMAX_FOLD, KERNEL_DEFERRED_NORM_CONTRACTION, KERNE
 EPI_STORE, EPI_RESIDUAL_ADD, EPI_SILU_MUL, EPI_ROPE_CACHE = 0, 1, 2, 3
 STAGE_FUSED, STAGE_ELEMENTWISE, STAGE_GATHER = 1, 2, 3
 OP_GEMV, OP_DECODE_ATTN, OP_ARGMAX, OP_RMSNORM, OP_EMBED, OP_ROPE_CACHE, OP_ADVANCE, OP_GENERIC = 1, 2, 3, 4, 5, 6, 7, 8
+OP_ATTN_FWD, OP_GEMM_RMSNORM, OP_ROPE = 9, 10, 11
 MAX_AXES, MAX_SLOTS = 6, 8
 X_CONST, X_LOAD, X_COORD, X_ITEM, X_A, X_B, X_F, X_RESULT, X_GATHER = 1, 2, 3, 4, 5, 6, 7, 8, 9
 (X_ADD, X_SUB, X_MUL, X_DIV, X_MAX, X_MIN, X_LT, X_NEG, X_RECIP, X_EXP, X_LOG, X_SQRT, X_TANH, X_SIN, X_COS, X_WHERE,
@@ -98,10 +99,18 @@ class _GenericStage(C.Structure):
     _fields_ = [("kernel", vp), ("buffers", vp * 16), ("n_buffers", i32), ("out", vp)]
 
 
+class _AttnStage(C.Structure):
+    _fields_ = [("p", AttnParams), ("storage", i32)]
+
+
+class _RopeStage(C.Structure):
+    _fields_ = [("x", vp), ("out", vp), ("rows", i64), ("seq", i32), ("head_dim", i32), ("table", vp), ("pos0", i32)]
+
+
 class _StageUnion(C.Union):
     _fields_ = [("gemv", GemvParams), ("decode", DecodeParams), ("argmax", _ArgmaxStage), ("rmsnorm", _RmsnormStage),
                 ("embed", _EmbedStage), ("rope_cache", RopeCacheParams), ("advance", _AdvanceStage),
-                ("generic", _GenericStage)]
+                ("generic", _GenericStage), ("attn", _AttnStage), ("gemm", GemmRmsnormParams), ("rope", _RopeStage)]
 
 
 class StageDesc(C.Structure):

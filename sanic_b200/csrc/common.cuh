@@ -28,6 +28,10 @@ struct sanic_ctx {
     int* status_dev = nullptr;
 };
 
+namespace sanic {
+// device-free structure checks of one stage (program.cu); `why` receives the refusal
+int32_t stage_check(const sanic_stage_desc& s, std::string* why, bool pointers);
+}
 static inline int32_t sanic_fail(sanic_ctx* ctx, int32_t code, const std::string& msg) {
     if (ctx) ctx->err = msg;
     return code;

@@ -24,39 +24,53 @@ struct sanic_program {
     sanic::step::Plan* plan = nullptr;   // the persistent single-kernel form of the step, when the list allows it
 };
 
-namespace {
-int32_t check_stage(sanic_ctx* ctx, const sanic_stage_desc& s) {
+namespace sanic {
+// Structure checks of one stage that need no device: stage kind against op, op against the carrier's kernel family, leaf
+// storage against the weight buffer. Shared by program creation and by schedule compilation (which may run without a context,
+// and before any buffer is bound: `pointers` = false leaves the fields a binding fills out of the check).
+int32_t stage_check(const sanic_stage_desc& s, std::string* why, bool pointers) {
+    auto fail = [&](int32_t code, const char* msg) { if (why) *why = msg; return code; };
     if (s.op == SANIC_OP_GENERIC) {
         // a compiled fallback kernel stands for any stage kind: a carrier no specialised kernel matches, a cone, a gather
         if (s.stage_kind != SANIC_STAGE_FUSED && s.stage_kind != SANIC_STAGE_ELEMENTWISE && s.stage_kind != SANIC_STAGE_GATHER)
-            return sanic_fail(ctx, SANIC_ERR_INVALID, "program: unknown stage kind");
-        if (!s.u.generic.kernel || !s.u.generic.out || s.u.generic.n_buffers < 0 || s.u.generic.n_buffers > 16)
-            return sanic_fail(ctx, SANIC_ERR_INVALID, "program: a generic stage needs a compiled kernel, its buffers and an output");
+            return fail(SANIC_ERR_INVALID, "program: unknown stage kind");
+        if (!s.u.generic.kernel || (pointers && !s.u.generic.out) || s.u.generic.n_buffers < 0 || s.u.generic.n_buffers > 16)
+            return fail(SANIC_ERR_INVALID, "program: a generic stage needs a compiled kernel, its buffers and an output");
         return SANIC_OK;
     }
     if (s.stage_kind == SANIC_STAGE_FUSED) {
         int32_t family = 0;
         int32_t rc = sanic_emit_select(&s.carrier, &family);
-        if (rc != SANIC_OK) return sanic_fail(ctx, rc, "program: no kernel for this carrier structure");
+        if (rc != SANIC_OK) return fail(rc, "program: no kernel for this carrier structure");
         bool ok = (s.op == SANIC_OP_GEMV && (family == SANIC_KERNEL_PLAIN_CONTRACTION ||
                                             family == SANIC_KERNEL_GROUPED_I4_CONTRACTION)) ||
                   (s.op == SANIC_OP_DECODE_ATTN && family == SANIC_KERNEL_ONLINE_SOFTMAX_FOLD) ||
-                  (s.op == SANIC_OP_ARGMAX && family == SANIC_KERNEL_EXTREMUM_INDEX);
-        if (!ok) return sanic_fail(ctx, SANIC_ERR_UNSUPPORTED, "program: stage op does not match its carrier");
+                  (s.op == SANIC_OP_ARGMAX && family == SANIC_KERNEL_EXTREMUM_INDEX) ||
+                  (s.op == SANIC_OP_ATTN_FWD && family == SANIC_KERNEL_ONLINE_SOFTMAX_FOLD) ||
+                  (s.op == SANIC_OP_GEMM_RMSNORM && family == SANIC_KERNEL_DEFERRED_NORM_CONTRACTION);
+        if (!ok) return fail(SANIC_ERR_UNSUPPORTED, "program: stage op does not match its carrier");
         if (s.op == SANIC_OP_GEMV) {
             bool i4 = s.u.gemv.weight_dtype == SANIC_I4;
             if (i4 != (family == SANIC_KERNEL_GROUPED_I4_CONTRACTION))
-                return sanic_fail(ctx, SANIC_ERR_DTYPE, "program: leaf storage does not match the weight buffer");
+                return fail(SANIC_ERR_DTYPE, "program: leaf storage does not match the weight buffer");
         }
     } else if (s.stage_kind == SANIC_STAGE_ELEMENTWISE) {
-        if (!(s.op == SANIC_OP_RMSNORM || s.op == SANIC_OP_ROPE_CACHE || s.op == SANIC_OP_ADVANCE))
-            return sanic_fail(ctx, SANIC_ERR_UNSUPPORTED, "program: not an elementwise stage");
+        if (!(s.op == SANIC_OP_RMSNORM || s.op == SANIC_OP_ROPE_CACHE || s.op == SANIC_OP_ADVANCE || s.op == SANIC_OP_ROPE))
+            return fail(SANIC_ERR_UNSUPPORTED, "program: not an elementwise stage");
     } else if (s.stage_kind == SANIC_STAGE_GATHER) {
-        if (s.op != SANIC_OP_EMBED) return sanic_fail(ctx, SANIC_ERR_UNSUPPORTED, "program: not a gather stage");
+        if (s.op != SANIC_OP_EMBED) return fail(SANIC_ERR_UNSUPPORTED, "program: not a gather stage");
     } else {
-        return sanic_fail(ctx, SANIC_ERR_INVALID, "program: unknown stage kind");
+        return fail(SANIC_ERR_INVALID, "program: unknown stage kind");
     }
     return SANIC_OK;
+}
+}  // namespace sanic
+
+namespace {
+int32_t check_stage(sanic_ctx* ctx, const sanic_stage_desc& s) {
+    std::string why;
+    const int32_t rc = sanic::stage_check(s, &why, true);
+    return rc == SANIC_OK ? rc : sanic_fail(ctx, rc, why);
 }
 int kernels_of(const sanic_stage_desc& s) { return s.op == SANIC_OP_ARGMAX ? 2 : 1; }
 
@@ -77,6 +91,14 @@ int32_t run_stage(sanic_ctx* ctx, const sanic_stage_desc& s, void* stream) {
                                       s.u.embed.vocab, s.u.embed.out, stream);
         case SANIC_OP_ROPE_CACHE: return sanic_rope_cache_write(ctx, &s.u.rope_cache, stream);
         case SANIC_OP_ADVANCE: return sanic_advance_position(ctx, s.u.advance.position, stream);
+        case SANIC_OP_ATTN_FWD:
+            if (s.u.attn.storage == SANIC_BF16) return sanic_attn_fwd_bf16(ctx, &s.u.attn.p, stream);
+            if (s.u.attn.storage == SANIC_F32) return sanic_attn_fwd_f32(ctx, &s.u.attn.p, stream);
+            return sanic_fail(ctx, SANIC_ERR_DTYPE, "program: attention operands are stored as f32 or bf16");
+        case SANIC_OP_GEMM_RMSNORM: return sanic_gemm_rmsnorm(ctx, &s.u.gemm, stream);
+        case SANIC_OP_ROPE:
+            return sanic_rope_bf16(ctx, s.u.rope.x, s.u.rope.out, s.u.rope.rows, s.u.rope.seq, s.u.rope.head_dim, s.u.rope.table,
+                                   s.u.rope.pos0, stream);
         case SANIC_OP_GENERIC:
             return sanic_generic_launch(ctx, s.u.generic.kernel, s.u.generic.buffers, s.u.generic.n_buffers, s.u.generic.out, stream);
         default: return sanic_fail(ctx, SANIC_ERR_INVALID, "program: unknown op");

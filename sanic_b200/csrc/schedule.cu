@@ -158,7 +158,9 @@ const char* op_name(int op) {
     switch (op) {
         case SANIC_OP_GEMV: return "contraction"; case SANIC_OP_DECODE_ATTN: return "online-softmax fold"; case SANIC_OP_ARGMAX: return "extremum index";
         case SANIC_OP_RMSNORM: return "rmsnorm"; case SANIC_OP_EMBED: return "gather"; case SANIC_OP_ROPE_CACHE: return "rope + cache write";
-        case SANIC_OP_ADVANCE: return "advance"; case SANIC_OP_GENERIC: return "generated"; default: return "?";
+        case SANIC_OP_ADVANCE: return "advance"; case SANIC_OP_GENERIC: return "generated";
+        case SANIC_OP_ATTN_FWD: return "online-softmax fold (forward)"; case SANIC_OP_GEMM_RMSNORM: return "deferred-norm contraction";
+        case SANIC_OP_ROPE: return "rope"; default: return "?";
     }
 }
 int32_t nan_scan(sanic_schedule* s, const std::vector<void*>& base, void* stream) {
@@ -185,6 +187,7 @@ void free_replay(sanic_replay* r) {
     delete r;
 }
 
+thread_local std::string g_compile_error;     // why this thread's last sanic_schedule_compile failed (it returns no handle)
 }  // namespace
 
 extern "C" {
@@ -196,7 +199,7 @@ int32_t sanic_schedule_compile(sanic_ctx* ctx, const sanic_schedule_desc* d, san
     sanic_schedule* s = new (std::nothrow) sanic_schedule();
     if (!s) return SANIC_ERR_NOMEM;
     s->ctx = ctx;
-    auto bad = [&](int32_t code, const std::string& msg) { if (ctx) ctx->err = msg; delete s; return code; };
+    auto bad = [&](int32_t code, const std::string& msg) { if (ctx) ctx->err = msg; g_compile_error = msg; delete s; return code; };
     if (!d->stages || d->n_stages <= 0) return bad(SANIC_ERR_INVALID, "schedule: cannot compile an empty stage list");      // CompileError::EmptyOutputs' sibling
     if (!d->outputs || d->n_outputs <= 0) return bad(SANIC_ERR_INVALID, "schedule: no output roots");                         // CompileError::EmptyOutputs
     if (!d->buffers || d->n_buffers <= 0) return bad(SANIC_ERR_INVALID, "schedule: empty buffer table");
@@ -218,6 +221,11 @@ int32_t sanic_schedule_compile(sanic_ctx* ctx, const sanic_schedule_desc* d, san
         s->bufs.push_back(x);
     }
     s->stages.assign(d->stages, d->stages + d->n_stages);
+    for (int i = 0; i < d->n_stages; ++i) {
+        std::string why;
+        const int32_t rc = sanic::stage_check(d->stages[i], &why, false);
+        if (rc != SANIC_OK) return bad(rc, "schedule: stage " + std::to_string(i) + ": " + why);
+    }
     for (int i = 0; i < d->n_relocs; ++i) {
         const sanic_reloc& r = d->relocs[i];
         if (r.stage < 0 || r.stage >= d->n_stages || r.buffer < 0 || r.buffer >= d->n_buffers || r.byte_offset < 0 ||
@@ -255,7 +263,7 @@ int32_t sanic_schedule_destroy(sanic_schedule* s) {
     return SANIC_OK;
 }
 
-const char* sanic_schedule_last_error(sanic_schedule* s) { return s ? s->err.c_str() : "null schedule"; }
+const char* sanic_schedule_last_error(sanic_schedule* s) { return s ? s->err.c_str() : g_compile_error.c_str(); }
 
 int32_t sanic_schedule_input_count(sanic_schedule* s) {
     if (!s) return -1;

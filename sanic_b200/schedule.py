@@ -123,6 +123,7 @@ class Program:
         self.dev = dev
         self.lib = dev.lib if dev is not None else abi.load()
         self._keep = []
+        self.n_stages = len(b.stages)
         n_b = len(b.buffers)
         decls = (abi.BufferDecl * max(1, n_b))()
         for i, (name, kind, dtype, shape) in enumerate(b.buffers):
@@ -150,7 +151,7 @@ class Program:
         h = C.c_void_p()
         rc = self.lib.sanic_schedule_compile(dev.h if dev is not None else None, C.byref(d), C.byref(h))
         if rc != abi.OK:
-            msg = self.lib.sanic_last_error(dev.h).decode() if dev is not None else f"status {rc}"
+            msg = self.lib.sanic_schedule_last_error(None).decode()
             raise CompileError(f"schedule_compile: {msg}")
         self.h = h
         self.n_outputs = len(b.outputs)

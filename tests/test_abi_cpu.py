@@ -76,6 +76,8 @@ int main(void) {
   printf("%zu %zu %zu %zu %zu %zu %zu %zu %zu %zu ", sizeof(sanic_buffer_decl), sizeof(sanic_reloc), sizeof(sanic_schedule_desc),
          sizeof(sanic_binding), sizeof(sanic_buffer_view), sizeof(sanic_state_decl), offsetof(sanic_stage_desc, u.embed.scales),
          offsetof(sanic_decode_params, kv_cap), offsetof(sanic_attn_params, accum_dtype), offsetof(sanic_peer_exchange, spin_limit));
+  printf("%zu %zu %zu %zu ", offsetof(sanic_stage_desc, u.attn.storage), offsetof(sanic_stage_desc, u.attn.p.mask),
+         offsetof(sanic_stage_desc, u.gemm.y), offsetof(sanic_stage_desc, u.rope.table));
   printf("%zu %zu %zu %zu %zu %zu %zu %zu %zu %zu %zu %zu %zu %zu %zu %zu %zu\n", sizeof(sanic_device_specs), sizeof(sanic_carrier_desc),
          sizeof(sanic_attn_params), sizeof(sanic_decode_params), sizeof(sanic_gemm_rmsnorm_params),
          sizeof(sanic_gemv_params), sizeof(sanic_rope_cache_params), sizeof(sanic_stage_desc),
@@ -94,6 +96,10 @@ int main(void) {
             C.sizeof(abi.BufferDecl), C.sizeof(abi.Reloc), C.sizeof(abi.ScheduleDesc), C.sizeof(abi.Binding), C.sizeof(abi.BufferView),
             C.sizeof(abi.StateDecl), abi.StageDesc.u.offset + abi._StageUnion.embed.offset + abi._EmbedStage.scales.offset,
             abi.DecodeParams.kv_cap.offset, abi.AttnParams.accum_dtype.offset, abi.PeerExchange.spin_limit.offset,
+            abi.StageDesc.u.offset + abi._StageUnion.attn.offset + abi._AttnStage.storage.offset,
+            abi.StageDesc.u.offset + abi._StageUnion.attn.offset + abi.AttnParams.mask.offset,
+            abi.StageDesc.u.offset + abi._StageUnion.gemm.offset + abi.GemmRmsnormParams.y.offset,
+            abi.StageDesc.u.offset + abi._StageUnion.rope.offset + abi._RopeStage.table.offset,
             C.sizeof(abi.DeviceSpecs), C.sizeof(abi.CarrierDesc), C.sizeof(abi.AttnParams), C.sizeof(abi.DecodeParams),
             C.sizeof(abi.GemmRmsnormParams), C.sizeof(abi.GemvParams), C.sizeof(abi.RopeCacheParams),
             C.sizeof(abi.StageDesc), abi.StageDesc.u.offset, C.sizeof(abi.PeerExchange), abi.PeerExchange.epoch.offset,

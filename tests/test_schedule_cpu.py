@@ -152,3 +152,37 @@ def test_schedule_compile_refusals():
         build(lambda b: b.in_place.append((0, b.index["x"])))                  # a root cannot overwrite an input of another shape
     with pytest.raises(CompileError):
         step_schedule().input("w", abi.BF16, (1,))                             # the builder refuses a duplicate name itself
+
+
+def test_one_shot_schedules_of_the_configurations_check_their_bindings():
+    """Attention, the RMSNorm-fused GEMM and split-KV decode as schedules: one fused stage each (plus the RoPE cut in
+    front of a fold over rotated operands), inputs bound by name with the reference's refusals."""
+    from sanic_b200 import schedules
+    assert _field_offset("attn.p.v") == abi.StageDesc.u.offset + abi.AttnParams.v.offset
+    assert _field_offset("gemm.w") == abi.StageDesc.u.offset + abi.GemmRmsnormParams.w.offset
+    assert _field_offset("rope.table") == abi.StageDesc.u.offset + abi._RopeStage.table.offset
+
+    c1 = schedules.attention(1, 1, 1, 256, 1024, 64, storage=abi.F32).compile()
+    assert c1.input_names() == ["q", "k", "v"] and c1.n_stages == 1
+    good = {"q": (P, abi.F32, (1, 1, 256, 64)), "k": (P, abi.F32, (1, 1, 1024, 64)), "v": (P, abi.F32, (1, 1, 1024, 64))}
+    c1.check_bindings(good)
+    assert kind_of(lambda: c1.check_bindings(dict(good, q=(P, abi.BF16, (1, 1, 256, 64))))) == "Dtype"
+    assert kind_of(lambda: c1.check_bindings(dict(good, k=(P, abi.F32, (1, 1, 1000, 64))))) == "Shape"
+    assert kind_of(lambda: c1.check_bindings({k: v for k, v in good.items() if k != "v"})) == "MissingInput"
+
+    c3 = schedules.attention(8, 32, 8, 4096, 4096, 64, storage=abi.BF16, causal=True, window=1024, rope=True).compile()
+    assert c3.input_names() == ["q", "k", "v", "rope_table"] and c3.n_stages == 3      # rotate q, rotate k, fold
+    c2 = schedules.rmsnorm_gemm(4096, 2048, 8192, w_is_nk=False).compile()
+    assert c2.input_names() == ["x", "gamma", "w"] and c2.n_stages == 1
+    assert kind_of(lambda: c2.check_bindings({"x": (P, abi.BF16, (4096, 2048)), "gamma": (P, abi.BF16, (2048,)),
+                                              "w": (P, abi.BF16, (8192, 2048))})) == "Shape"       # [K, N] was declared
+    c5 = schedules.splitkv_decode(4, 32, 8, 1 << 20, 128, n_splits=74).compile()
+    assert c5.input_names() == ["q", "k", "v"] and c5.n_stages == 1
+
+    # a stage whose op does not match its carrier is refused when the schedule is compiled
+    b = schedules.rmsnorm_gemm(128, 256, 256)
+    b.stages[0].carrier = carrier_contraction(abi.BF16)
+    with pytest.raises(CompileError, match="does not match its carrier"):
+        b.compile()
+    with pytest.raises(ValueError):
+        schedules.attention(1, 1, 1, 8, 8, 64, storage=abi.F32, rope=True)
