@@ -93,3 +93,38 @@ def test_generate_matches_manual_stepping(dev):
     assert got.tolist() == np.array(want).T.tolist()
     with pytest.raises(llama.RunError):
         m.generate(prompts, 100)
+
+
+def test_text_in_text_out(dev):
+    """The loop of the reference's example around the machine (examples/llama3_2.rs:454-470, 577-681): the prompt is
+    tokenized with its begin-of-text token, consumed through the decode step, and each generated id is decoded back to
+    text. Random weights give no language, so what is checked is the plumbing: the oracle stepping over the same ids
+    agrees with the generated ones (up to counted near-ties), both machine forms agree, and the text round-trips."""
+    from sanic_b200 import llama
+    from sanic_b200.tokenizer import Tokenizer
+    from llama_util import make_oracle
+    from test_tokenizer import SAMPLE, learn, spec
+    tok = Tokenizer(spec(learn(SAMPLE, 120)))
+    size = len(tok.vocab) + len(tok.added)
+    cfg = dict(SMALL, vocab=-(-size // 16) * 16)
+    prompt = "the cache grows by one row per step"
+    ids = tok.encode(prompt, add_special_tokens=True)
+    assert ids[0] == tok.added["<|begin_of_text|>"] and tok.decode(ids) == prompt
+    new = 12
+    w = llama.random_weights(cfg, 11, dev.torch_device)
+    outs = []
+    for persistent in (False, True):
+        m = llama.LlamaMachine(dev, cfg, w, ctx=64, batch=1, persistent=persistent)
+        outs.append(m.generate([ids], new)[0])
+    assert np.array_equal(outs[0], outs[1])
+    o = make_oracle(cfg, w, 64, 1, False)
+    cur, differ = None, 0
+    for pos, t in enumerate(ids):
+        cur = o.step(np.array([t], dtype=np.int32), pos)
+    for i in range(new):
+        differ += int(cur[0] != outs[0][i])
+        cur = o.step(np.array([outs[0][i]], dtype=np.int32), len(ids) + i)      # follow the device's ids
+    assert differ <= 1
+    known = [int(t) for t in outs[0] if int(t) in tok.id_to_token]
+    text = tok.decode(known)
+    assert isinstance(text, str) and tok.decode(tok.encode(text, False)) == text
