@@ -303,7 +303,8 @@ int32_t sanic_w4_unpack(sanic_ctx* ctx, const uint8_t* packed, size_t n_elems, f
 #define SANIC_MAX_SLOTS 8
 enum { SANIC_X_CONST = 1,   /* value */
        SANIC_X_LOAD = 2,    /* arg = operand index: a typed, strided read at the current point */
-       SANIC_X_COORD = 3,   /* arg = grid axis, n_axes for the streamed coordinate, n_axes + 1 for the inner coordinate of a
+       SANIC_X_COORD = 3,   /* arg = grid axis, n_axes for the streamed coordinate, n_axes + 2 + j for window coordinate j of a
+                               streamed window of several axes, n_axes + 1 for the inner coordinate of a
                                contracted leaf; as a float (Iota / Coordinate) */
        SANIC_X_ITEM = 4,    /* arg = leaf index (into, and project for stream-invariant leaves is not needed: use LOAD) */
        SANIC_X_A = 5, SANIC_X_B = 6,   /* arg = slot of the left / right accumulator (combine) */
@@ -328,6 +329,8 @@ typedef struct {
     int64_t inner_stride;               /* elements per step of a contracted leaf's inner axis */
     int64_t gather_stride;              /* elements per step of the gathered index (SANIC_X_GATHER only) */
     int64_t gather_extent;              /* valid indices are 0 .. gather_extent-1 */
+    int64_t stream_sub_stride[3];       /* with stream_dims > 1: elements per step of each axis of the streamed window (then
+                                           stream_stride is not read) */
 } sanic_operand;
 typedef struct {
     int32_t n_axes;                     /* output grid, row-major, last axis fastest */
@@ -360,6 +363,13 @@ typedef struct {
                                                              the in-place form of where(c, x, s) writing s's own buffer, which
                                                              never loads s (src/emit_metal.rs:1118-1178) */
     int32_t out_dtype;                                    /* SANIC_F32 / SANIC_BF16 (RNE) / SANIC_U32 (saturating) */
+    int32_t stream_dims;                                  /* 0 or 1: the streamed axis is one axis. 2 or 3: it is the row-major
+                                                             flattening of a window of that many axes (a reduce over several
+                                                             axes at once: the taps and input channels of a convolution, the
+                                                             window of a pooling), extents in stream_extent, product = stream;
+                                                             operands step by stream_sub_stride and COORD n_axes + 2 + j reads
+                                                             the j-th window coordinate */
+    int64_t stream_extent[3];
 } sanic_generic_desc;
 typedef struct sanic_generic_kernel sanic_generic_kernel;
 /* The generated CUDA C text (MetalKernel::msl). ctx may be NULL. *needed receives the size including the terminator. */

@@ -127,7 +127,7 @@ class Expr(C.Structure):
 
 class Operand(C.Structure):
     _fields_ = [("dtype", i32), ("buffer", i32), ("offset", i64), ("stride", i64 * MAX_AXES), ("stream_stride", i64),
-                ("inner_stride", i64), ("gather_stride", i64), ("gather_extent", i64)]
+                ("inner_stride", i64), ("gather_stride", i64), ("gather_extent", i64), ("stream_sub_stride", i64 * 3)]
 
 
 class GenericDesc(C.Structure):
@@ -135,7 +135,7 @@ class GenericDesc(C.Structure):
                 ("n_operands", i32), ("operands", C.POINTER(Operand)), ("n_ops", i32), ("ops", C.POINTER(ExprOp)),
                 ("n_leaves", i32), ("leaves", C.POINTER(Expr)), ("leaf_inner", C.POINTER(i64)), ("n_slots", i32), ("identity", C.POINTER(C.c_double)),
                 ("into", C.POINTER(Expr)), ("combine", C.POINTER(Expr)), ("project", Expr), ("epilogue", Expr),
-                ("store_if", Expr), ("out_dtype", i32)]
+                ("store_if", Expr), ("out_dtype", i32), ("stream_dims", i32), ("stream_extent", i64 * 3)]
 
 
 class BufferDecl(C.Structure):

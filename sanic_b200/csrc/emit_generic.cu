@@ -123,6 +123,18 @@ struct Gen {
         return buf;
     }
 
+    // window coordinate j of the flattened stream position `s` (row-major over stream_extent; extents are literals, so the
+    // divisions are by constants)
+    std::string window_coord(const std::string& s, int j) const {
+        long long below = 1;
+        for (int i = j + 1; i < d->stream_dims; ++i) below *= d->stream_extent[i];
+        std::ostringstream a;
+        a << "((" << s << " / " << below << "LL)";
+        if (j > 0) a << " % " << (long long)d->stream_extent[j] << "LL";
+        a << ")";
+        return a.str();
+    }
+
     // element index of operand k at the current point; `s` is the name of the stream variable ("" outside the loop)
     std::string address(int k, const std::string& s) {
         const sanic_operand& o = d->operands[k];
@@ -130,7 +142,10 @@ struct Gen {
         a << "(" << (long long)o.offset << "LL";
         for (int ax = 0; ax < d->n_axes; ++ax)
             if (o.stride[ax] != 0) a << " + c" << ax << " * " << (long long)o.stride[ax] << "LL";
-        if (!s.empty() && o.stream_stride != 0) a << " + " << s << " * " << (long long)o.stream_stride << "LL";
+        if (!s.empty() && d->stream_dims > 1) {
+            for (int j = 0; j < d->stream_dims; ++j)
+                if (o.stream_sub_stride[j] != 0) a << " + " << window_coord(s, j) << " * " << (long long)o.stream_sub_stride[j] << "LL";
+        } else if (!s.empty() && o.stream_stride != 0) a << " + " << s << " * " << (long long)o.stream_stride << "LL";
         if (!inner.empty() && o.inner_stride != 0) a << " + " << inner << " * " << (long long)o.inner_stride << "LL";
         a << ")";
         return a.str();
@@ -203,6 +218,9 @@ struct Gen {
                     } else if (op.arg == d->n_axes + 1) {
                         if (inner.empty()) { err = "generic emitter: inner coordinate read outside a contracted leaf"; st.push_back("0.0f"); }
                         else st.push_back("(float)" + inner);
+                    } else if (op.arg >= d->n_axes + 2 && op.arg < d->n_axes + 2 + d->stream_dims && d->stream_dims > 1) {
+                        if (s.empty()) { err = "generic emitter: window coordinate read outside the fold body"; st.push_back("0.0f"); }
+                        else st.push_back("(float)" + window_coord(s, op.arg - d->n_axes - 2));
                     } else if (op.arg >= 0 && op.arg < d->n_axes) st.push_back("(float)c" + std::to_string(op.arg));
                     else { err = "generic emitter: coordinate axis out of range"; st.push_back("0.0f"); }
                     break;
@@ -280,6 +298,15 @@ int32_t validate(sanic_ctx* ctx, const sanic_generic_desc* d) {
     SANIC_REQUIRE(ctx, d->n_ops >= 0 && (d->n_ops == 0 || d->ops), "generic emitter: bad op array");
     SANIC_REQUIRE(ctx, d->out_dtype == SANIC_F32 || d->out_dtype == SANIC_BF16 || d->out_dtype == SANIC_U32, "generic emitter: bad output dtype");
     SANIC_REQUIRE(ctx, d->stream >= 0, "generic emitter: negative stream extent");
+    SANIC_REQUIRE(ctx, d->stream_dims >= 0 && d->stream_dims <= 3, "generic emitter: a streamed window has at most 3 axes");
+    if (d->stream_dims > 1) {
+        long long prod = 1;
+        for (int j = 0; j < d->stream_dims; ++j) {
+            SANIC_REQUIRE(ctx, d->stream_extent[j] > 0, "generic emitter: window extents must be positive");
+            prod *= d->stream_extent[j];
+        }
+        SANIC_REQUIRE(ctx, prod == d->stream, "generic emitter: the window's extents must multiply to the streamed extent");
+    }
     if (d->stream > 0) {
         SANIC_REQUIRE(ctx, d->n_slots >= 1 && d->n_slots <= SANIC_MAX_SLOTS && d->identity && d->into && d->combine, "generic emitter: 1..8 slots with identity, into and combine");
         SANIC_REQUIRE(ctx, d->n_leaves >= 0 && d->n_leaves <= 16 && (d->n_leaves == 0 || d->leaves), "generic emitter: 0..16 leaves");

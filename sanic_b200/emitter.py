@@ -82,6 +82,7 @@ class Operand:
     inner_stride: int = 0      # for a contracted leaf: elements per step of its inner axis
     gather_stride: int = 0     # for `gather`: elements per step of the gathered index, and the number of valid indices
     gather_extent: int = 0
+    stream_strides: Sequence[int] = ()   # with a streamed window of several axes: elements per step of each window axis
 
 
 @dataclass
@@ -158,6 +159,37 @@ def attention(batch, q_heads, kv_heads, q_len, kv_len, head_dim, v_dim, scale, d
     return (batch, kv_heads, rep, L, Ev), S, [q, k, v], car
 
 
+def conv2d(batch, channels, height, width, out_channels, kh, kw, stride=1, dilation=1, dtype=abi.F32):
+    """y[n, co, oy, ox] = sum over (ci, ky, kx) of x[n, ci, oy*stride + ky*dilation, ox*stride + kx*dilation] * w[co, ci, ky, kx]:
+    the convolution as the reference states it, a window view of x times a broadcast view of w reduced over three axes at once
+    (no patch matrix is materialised: an implicit GEMM whose K axis is the window). No padding: a padded convolution pads its
+    input first. Returns (grid, window, operands, carrier); buffers are x [N,C,H,W] and w [CO,C,KH,KW]."""
+    oh = (height - dilation * (kh - 1) - 1) // stride + 1
+    ow = (width - dilation * (kw - 1) - 1) // stride + 1
+    if oh <= 0 or ow <= 0:
+        raise ValueError("the window does not fit the input")
+    x = Operand(0, dtype, [channels * height * width, 0, stride * width, stride],
+                stream_strides=[height * width, dilation * width, dilation])
+    w = Operand(1, dtype, [0, channels * kh * kw, 0, 0], stream_strides=[kh * kw, kw, 1])
+    return (batch, out_channels, oh, ow), (channels, kh, kw), [x, w], carrier_sum(load(0) * load(1))
+
+
+def pool2d(batch, channels, height, width, kh, kw, stride=None, kind="max", dtype=abi.F32):
+    """Max or mean over (kh, kw) windows stepping by `stride` (default: the window): a reduce over two window axes."""
+    sh, sw = (kh, kw) if stride is None else (stride, stride)
+    oh, ow = (height - kh) // sh + 1, (width - kw) // sw + 1
+    if oh <= 0 or ow <= 0:
+        raise ValueError("the window does not fit the input")
+    x = Operand(0, dtype, [channels * height * width, height * width, sh * width, sw], stream_strides=[width, 1])
+    if kind == "max":
+        car = carrier_max(load(0))
+    elif kind == "mean":
+        car = Carrier([load(0)], [item(0)], [A(0) + B(0)], [0.0], F(0) * (1.0 / (kh * kw)))
+    else:
+        raise ValueError("kind is 'max' or 'mean'")
+    return (batch, channels, oh, ow), (kh, kw), [x], car
+
+
 class Description:
     """A packed sanic_generic_desc with the ctypes arrays it points into kept alive."""
 
@@ -168,6 +200,14 @@ class Description:
             raise ValueError(f"at most {abi.MAX_AXES} grid axes")
         if (carrier is None) == (value is None):
             raise ValueError("give a carrier (a fold) or a value (a pointwise kernel), not both")
+        window = ()
+        if carrier is not None and not isinstance(stream, int):      # a window of several axes, reduced at once
+            window = tuple(int(e) for e in stream)
+            if not 2 <= len(window) <= 3:
+                raise ValueError("a streamed window has 2 or 3 axes (one axis: give its extent)")
+            stream = 1
+            for e in window:
+                stream *= e
         if carrier is not None and stream <= 0:
             raise ValueError("a fold needs a positive streamed extent")
         ops: list = []
@@ -182,6 +222,9 @@ class Description:
         for i, g in enumerate(grid):
             d.extent[i] = int(g)
         d.stream = int(stream) if carrier is not None else 0
+        d.stream_dims = len(window)
+        for j, e in enumerate(window):
+            d.stream_extent[j] = e
         d.lanes, d.warps, d.interleave = int(lanes), int(warps), int(bool(interleave))
         d.lane_axis = int(bool(lane_axis))
         self._operands = (abi.Operand * max(1, len(operands)))()
@@ -192,6 +235,11 @@ class Description:
             self._operands[i].offset, self._operands[i].stream_stride = int(o.offset), int(o.stream_stride)
             self._operands[i].gather_stride, self._operands[i].gather_extent = int(o.gather_stride), int(o.gather_extent)
             self._operands[i].inner_stride = int(o.inner_stride)
+            if window:
+                if len(o.stream_strides) != len(window):
+                    raise ValueError("with a streamed window an operand needs one stream stride per window axis")
+                for j, st in enumerate(o.stream_strides):
+                    self._operands[i].stream_sub_stride[j] = int(st)
             for a, s in enumerate(o.strides):
                 self._operands[i].stride[a] = int(s)
         d.n_operands, d.operands = len(operands), self._operands

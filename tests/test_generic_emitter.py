@@ -180,6 +180,10 @@ def all_descriptions():
     ops = [em.Operand(0, abi.F32, [0, 1]), em.Operand(1, abi.F32, [0, 0])]
     hit = (em.coord(0) < em.load(1) + 1.0) * (em.load(1) < em.coord(0) + 1.0)
     out["in-place row write"] = em.Description((16, 8), ops, value=em.load(0), store_if=hit, out_dtype=abi.BF16)
+    g, win, ops, car = em.conv2d(2, 3, 9, 8, 4, 3, 3, dtype=abi.BF16)
+    out["convolution over a three-axis window"] = em.Description(g, ops, carrier=car, stream=win, lanes=32)
+    g, win, ops, car = em.pool2d(2, 3, 8, 8, 2, 2)
+    out["pooling over a two-axis window"] = em.Description(g, ops, carrier=car, stream=win)
     return out
 
 
@@ -227,6 +231,15 @@ def test_malformed_programs_are_refused():
     d = em.Description((4,), ops, carrier=em.carrier_sum(em.load(0)), stream=8, lanes=7)
     with pytest.raises(ValueError):
         em.source(d)
+    # a streamed window: one stride per window axis on every operand, 2 or 3 axes, and a coordinate that exists
+    with pytest.raises(ValueError):
+        em.Description((4,), ops, carrier=em.carrier_sum(em.load(0)), stream=(2, 4))
+    with pytest.raises(ValueError):
+        em.Description((4,), [em.Operand(0, abi.F32, [1], stream_strides=[4, 1])], carrier=em.carrier_sum(em.load(0)), stream=(2, 2, 2, 2))
+    wops = [em.Operand(0, abi.F32, [8], stream_strides=[4, 1])]
+    assert "% 4LL" in em.source(em.Description((4,), wops, carrier=em.carrier_sum(em.load(0) * em.coord(3)), stream=(2, 4)))
+    with pytest.raises(ValueError):
+        em.source(em.Description((4,), wops, carrier=em.carrier_sum(em.load(0) * em.coord(5)), stream=(2, 4)))
 
 
 # ───────────────────────── GPU parity ─────────────────────────
@@ -626,3 +639,79 @@ def test_hand_written_merge_equals_the_carriers_own_combine(dev):
     assert nerr(gen, hand) <= 2e-6
     assert nerr(hand, orc.carrier_merge_mlo(parts)) <= F32_TOL
     kern.close()
+
+
+# ───────────── reduces over several axes at once, scans and top-k (the reference's tests/movement.rs compositions) ─────────────
+def _windows(x, kh, kw, stride, dilation=1):
+    """All (kh, kw) windows of the last two axes: [..., OH, OW, kh, kw], dense reference evaluation."""
+    span_h, span_w = dilation * (kh - 1) + 1, dilation * (kw - 1) + 1
+    v = np.lib.stride_tricks.sliding_window_view(x, (span_h, span_w), axis=(-2, -1))
+    return v[..., ::stride, ::stride, ::dilation, ::dilation]
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype,lanes,stride,dilation", [(abi.F32, 1, 1, 1), (abi.BF16, 32, 1, 1), (abi.F32, 32, 2, 1), (abi.BF16, 1, 1, 2)])
+def test_generic_convolution_is_an_implicit_gemm_over_a_window(dev, dtype, lanes, stride, dilation):
+    N, C, H, W, CO, KH, KW = 2, 5, 11, 9, 6, 3, 2
+    g = orc.Xorshift(0xC0471)
+    rd = (lambda a: orc.round_to(orc.DT_BF16, a)) if dtype == abi.BF16 else (lambda a: orc.round_to(orc.DT_F32, a))
+    x, w = rd(g.normal(N, C, H, W)), rd(0.2 * g.normal(CO, C, KH, KW))
+    grid, win, ops, car = em.conv2d(N, C, H, W, CO, KH, KW, stride=stride, dilation=dilation, dtype=dtype)
+    want = np.einsum("nchwyx,ocyx->nohw", _windows(x, KH, KW, stride, dilation), w)
+    assert want.shape == grid
+    got = run_kernel(dev, em.Description(grid, ops, carrier=car, stream=win, lanes=lanes),
+                     [on_device(dev, x, dtype), on_device(dev, w, dtype)], grid)
+    assert nerr(got, want) <= F32_TOL
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("kind,k,stride", [("max", 2, None), ("mean", 3, 2), ("max", 3, 1)])
+def test_generic_pooling(dev, kind, k, stride):
+    N, C, H, W = 2, 3, 10, 12
+    x = orc.round_to(orc.DT_F32, orc.Xorshift(0x9001).normal(N, C, H, W))
+    grid, win, ops, car = em.pool2d(N, C, H, W, k, k, stride=stride, kind=kind)
+    v = _windows(x, k, k, stride if stride else k)
+    want = v.max(axis=(-2, -1)) if kind == "max" else v.mean(axis=(-2, -1))
+    got = run_kernel(dev, em.Description(grid, ops, carrier=car, stream=win), [on_device(dev, x, abi.F32)], grid)
+    assert nerr(got, want) <= (0.0 if kind == "max" else F32_TOL)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("lanes", [1, 32])
+def test_generic_inclusive_scan_as_a_masked_fold(dev, lanes):
+    """cumsum[i] = sum over j of where(j <= i, x[j], 0): the scan the reference writes as a triangular mask under a reduce."""
+    rows, n = 4, 70
+    x = orc.round_to(orc.DT_F32, orc.Xorshift(0x5CA4).normal(rows, n))
+    ops = [em.Operand(0, abi.F32, [n, 0], 1)]
+    car = em.carrier_sum(em.where(em.coord(2) < em.coord(1) + 1.0, em.load(0), 0.0))
+    got = run_kernel(dev, em.Description((rows, n), ops, carrier=car, stream=n, lanes=lanes), [on_device(dev, x, abi.F32)], (rows, n))
+    assert nerr(got, np.cumsum(x, axis=1)) <= F32_TOL
+
+
+@pytest.mark.gpu
+def test_generic_top_k_as_repeated_first_argmax(dev):
+    """top-k as the composition it is in the reference: k rounds of the first-argmax fold, each masking the indices already
+    taken. Bit-exact indices, ties to the lowest index."""
+    import torch
+    rows, n, k = 5, 97, 4
+    x = orc.round_to(orc.DT_F32, orc.Xorshift(0x70B4).normal(rows, n))
+    x[1, 10] = x[1, 60] = x[1].max() + 1.0                      # a tie for the maximum: the lower index goes first
+    xd = on_device(dev, x, abi.F32)
+    taken = []
+    for r in range(k):
+        ops = [em.Operand(0, abi.F32, [n], 1)] + [em.Operand(1 + i, abi.U32, [1], 0) for i in range(r)]
+        same = 0.0
+        for i in range(r):
+            same = same + (em.coord(1) < em.load(1 + i) + 1.0) * (em.load(1 + i) < em.coord(1) + 1.0)
+        leaf = em.where(same, float("-inf"), em.load(0)) if r else em.load(0)
+        d = em.Description((rows,), ops, carrier=em.carrier_first_argmax(leaf, em.coord(1)), stream=n, lanes=32, out_dtype=abi.U32)
+        out = torch.empty(rows, dtype=torch.int32, device=dev.torch_device)
+        kern = em.GenericKernel(dev, d)
+        kern([xd] + taken, out)
+        dev.sync()
+        kern.close()
+        taken.append(out)
+    got = np.stack([t.cpu().numpy() for t in taken], axis=1)
+    want = np.argsort(-x, axis=1, kind="stable")[:, :k]
+    assert np.array_equal(got, want)
+    assert got[1, 0] == 10 and got[1, 1] == 60
