@@ -311,7 +311,11 @@ def suite(dev, torch, hbm_peak, tf_peak, quick, only=None, c2_shape=(4096, 2048,
         w = llama.random_weights(cfg, 11, td, w4=w4)
         # the step as one cooperative kernel wins at small batch, the captured launch list at batch 16 (measured)
         persistent = fused and (form == "persistent" or (form == "auto" and batch <= 4))
-        m = llama.LlamaMachine(dev, cfg, w, ctx=1088, batch=batch, w4=w4, fused=fused, persistent=persistent)
+        # SANIC_LLAMA_DEFERRED_NORM=0/1 forces the deferred normaliser off / on (A/B timing); default: the machine's choice
+        force = os.environ.get("SANIC_LLAMA_DEFERRED_NORM")
+        m = llama.LlamaMachine(dev, cfg, w, ctx=1088, batch=batch, w4=w4, fused=fused, persistent=persistent,
+                               deferred_norm=None if force is None else force != "0")
+        deferred = m.deferred_norm
         rng = np.random.default_rng(3)
         # prefill 1024 positions from random token ids by decoding on the device
         for p in range(1024 if not quick else 64):
@@ -334,7 +338,7 @@ def suite(dev, torch, hbm_peak, tf_peak, quick, only=None, c2_shape=(4096, 2048,
             out[f"c4_phase_profile_{name}"] = [[round(t * 1e6, 2) for t in ph] for ph in prof]
         out[f"c4_llama_decode_{name}"] = {
             "tok_per_s": batch / sec, "ms_per_step": sec * 1e3, "launches_per_step": m.kernel_count,
-            "form": "one cooperative kernel" if persistent else "captured launch list",
+            "form": "one cooperative kernel" if persistent else "captured launch list", "deferred_norm": bool(deferred),
             "algorithmic_bytes": wb + kv_bytes, "achieved_gbs": (wb + kv_bytes) / sec / 1e9,
             "frac_of_hbm_peak": (wb + kv_bytes) / sec / 1e9 / hbm_peak}
         del m, w

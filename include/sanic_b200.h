@@ -239,6 +239,14 @@ typedef struct {
      * *rope_position of the V cache [B,Hkv,D,ctx] (src/nn.rs:176-212); out[] is ignored. */
     const float* rope_table; const int32_t* rope_position; void* rope_q_out; void* rope_k_cache; void* rope_v_cache;
     int32_t rope_q_heads, rope_kv_heads, rope_head_dim, rope_ctx;
+    /* Deferred normaliser across two contractions (the defer-div carrier, tests/laws.rs:620-646, with its two sums produced
+     * where they are cheapest). Producer, RESIDUAL_ADD epilogue with f32 output only: besides y = residual + W x the epilogue
+     * writes nx_out[b, row] = bf16(y * nx_gamma[row]) (the next contraction's activations, stored(bf16) on x*g) and, per
+     * 16-row tile t, nx_partial[b, t] = sum of y^2 over the tile's rows ([batch, rows_0 / 16] f32). Consumer, any epilogue,
+     * no inlined norm: every output is multiplied by 1 / sqrt(sum_t ds_partial[b, t] / K + ds_eps) before the epilogue acts on
+     * it (ds_tiles = K / 16; the sum runs in a fixed order). All NULL / 0: off. */
+    void* nx_out; const void* nx_gamma; float* nx_partial;
+    const float* ds_partial; int32_t ds_tiles; float ds_eps;
 } sanic_gemv_params;
 int32_t sanic_gemv(sanic_ctx* ctx, const sanic_gemv_params* p, void* stream);
 

@@ -315,6 +315,8 @@ class Llama:
     (uint16 bf16 bits [out, in], or uint8 packed int4 when w4) and 'sq' ... 'sdown' (bf16 bits scales).
     cfg['w4_head'] = 1: 'embed' is packed int4 [vocab, hidden/2] with 'sembed' [vocab, hidden/group] scales.
     cfg['norm_store'] = 1: stored(bf16) sits on x*g and the RMSNorm division is deferred past each contraction.
+    cfg['norm_store'] = 2: the same at every norm a residual-add feeds; layer 0's attention norm (fed by the gather) keeps
+    stored(rms_norm(x)).
     """
 
     def __init__(self, cfg: dict, weights: dict):

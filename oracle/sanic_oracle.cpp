@@ -684,7 +684,9 @@ struct OrcLlamaCfg {
     int32_t norm_store;  // where stored(bf16) sits on a normed projection input (round_acts = 1):
                          //   0: on rms_norm(x) itself, bf16((x*g)/sqrt(mean(x^2)+eps));
                          //   1: on x*g, with the division deferred past the contraction (the defer-div carrier of
-                         //      tests/laws.rs:620-646: slots sum x^2 and sum bf16(x*g)*W, project = dot / sqrt(ss/n + eps))
+                         //      tests/laws.rs:620-646: slots sum x^2 and sum bf16(x*g)*W, project = dot / sqrt(ss/n + eps));
+                         //   2: as 1 at every norm whose input a residual-add produces, as 0 at the one norm whose input
+                         //      is the gathered embedding (layer 0's attention norm)
     double eps, theta;
 };
 struct OrcLlamaWeights {  // per layer arrays of pointers
@@ -724,10 +726,10 @@ static void maybe_round(const OrcLlama* m, std::vector<double>& v) {
 // norm_store 0: xn = stored(rms_norm(x, g)), den = 1. norm_store 1: xn = stored(x * g), den[b] = sqrt(mean(x^2) + eps):
 // the contraction runs on x*g and each output row is divided once afterwards (defer-div).
 static void normed_input(const OrcLlama* m, const std::vector<double>& x, const std::vector<double>& gamma, size_t B, size_t Hd,
-                         std::vector<double>& xn, std::vector<double>& den) {
+                         std::vector<double>& xn, std::vector<double>& den, bool after_gather = false) {
     xn.resize(B * Hd);
     den.assign(B, 1.0);
-    if (m->cfg.norm_store == 0) {
+    if (m->cfg.norm_store == 0 || (m->cfg.norm_store == 2 && after_gather)) {
         orc_rms_norm(x.data(), gamma.data(), B, Hd, m->cfg.eps, xn.data());
     } else {
         for (size_t b = 0; b < B; ++b) {
@@ -783,7 +785,7 @@ int orc_llama_step(OrcLlama* m, const int32_t* tokens_in, int64_t position, int3
     std::vector<double> pos(1, (double)position);
     for (size_t l = 0; l < c.layers; ++l) {
         orc_from_bf16_bits(m->w.attn_norm[l], gamma.data(), Hd);
-        normed_input(m, x, gamma, B, Hd, xn, den);
+        normed_input(m, x, gamma, B, Hd, xn, den, l == 0);
         project(m, m->w.wq[l], c.w4 ? m->w.sq[l] : nullptr, xn, B, Hq * D, Hd, q);
         project(m, m->w.wk[l], c.w4 ? m->w.sk[l] : nullptr, xn, B, Hk * D, Hd, k);
         project(m, m->w.wv[l], c.w4 ? m->w.sv[l] : nullptr, xn, B, Hk * D, Hd, v);

@@ -70,7 +70,8 @@ class GemvParams(C.Structure):
                 ("w", vp * 3), ("scales", vp * 3), ("rows", i32 * 3), ("out", vp * 3), ("out_dtype", i32),
                 ("epilogue", i32), ("residual", vp), ("norm_x", vp), ("norm_gamma", vp), ("norm_eps", f32),
                 ("rope_table", vp), ("rope_position", vp), ("rope_q_out", vp), ("rope_k_cache", vp), ("rope_v_cache", vp),
-                ("rope_q_heads", i32), ("rope_kv_heads", i32), ("rope_head_dim", i32), ("rope_ctx", i32)]
+                ("rope_q_heads", i32), ("rope_kv_heads", i32), ("rope_head_dim", i32), ("rope_ctx", i32),
+                ("nx_out", vp), ("nx_gamma", vp), ("nx_partial", vp), ("ds_partial", vp), ("ds_tiles", i32), ("ds_eps", f32)]
 
 
 class RopeCacheParams(C.Structure):

@@ -259,6 +259,7 @@ __device__ __forceinline__ bool consume_gemv(const Phase& P, const Ring& ring, u
             *(uint4*)(xs + (size_t)n * xpitch + c * 16) = v;
         }
     };
+    if (!NORM && P.fz.ds_partial) defer_scales<true>(P.fz, P.batch, scratch);     // once per phase
     if (DIRECT) {
         // nothing to stage
     } else if (NT == 1 && NORM && P.K == CONSUMERS * 8 && P.batch <= 2) {

@@ -19,6 +19,10 @@ struct Fused {
     const float* norm_x; const uint16_t* norm_gamma; float norm_eps;
     const float* rope_table; const int32_t* rope_position; uint16_t* rope_q_out; uint16_t* rope_k_cache; uint16_t* rope_v_cache;
     int q_heads, kv_heads, head_dim, ctx;
+    // deferred normaliser: what a residual-add epilogue also writes for the next contraction, and what a contraction's
+    // outputs are scaled by (see sanic_gemv_params)
+    uint16_t* nx_out; const uint16_t* nx_gamma; float* nx_partial;
+    const float* ds_partial; int ds_tiles; float ds_eps;
 };
 
 __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
@@ -91,6 +95,26 @@ __device__ __forceinline__ void row_norms(const Fused& fz, int batch, int K, flo
     block_sync<L2READ>();
 }
 
+// 1 / sqrt(mean(x^2) + eps) of every activation row from the per-tile sums a residual-add epilogue left
+// (Fused::ds_partial), into scratch[0..batch): the 16 threads of a row add tiles r, r+16, ... and meet in a fixed
+// xor tree. All GW*32 threads of the block call this.
+template <bool L2READ>
+__device__ __forceinline__ void defer_scales(const Fused& fz, int batch, float* scratch) {
+    const int tid = threadIdx.x, n = tid >> 4, r = tid & 15;
+    float v = 0.0f;
+    if (n < batch)
+        for (int t = r; t < fz.ds_tiles; t += 16) {
+            const float* p = fz.ds_partial + (size_t)n * fz.ds_tiles + t;
+            v += L2READ ? __ldcg(p) : __ldg(p);
+        }
+    v += __shfl_xor_sync(0xffffffffu, v, 8);
+    v += __shfl_xor_sync(0xffffffffu, v, 4);
+    v += __shfl_xor_sync(0xffffffffu, v, 2);
+    v += __shfl_xor_sync(0xffffffffu, v, 1);
+    if (n < batch && r == 0) scratch[n] = 1.0f / sqrtf(v * (1.0f / (float)(fz.ds_tiles * 16)) + fz.ds_eps);
+    block_sync<L2READ>();
+}
+
 // Shared scratch one tile needs, in floats: row norms [16], their per-warp parts [16][GW], the per-warp
 // accumulators [GW][NM][16][8*NT+1] and the block sum [NM][16][8*NT+1].
 template <int NT, bool DUAL>
@@ -109,6 +133,7 @@ __device__ __forceinline__ void tile_finish(float (&acc)[DUAL ? 2 : 1][NT][4], i
     float (*red)[NM][16][RW] = reinterpret_cast<float (*)[NM][16][RW]>(scratch + 16 + 16 * GW);            // [GW][NM][16][RW]
     float (*csum)[16][RW] = reinterpret_cast<float (*)[16][RW]>(scratch + 16 + 16 * GW + GW * NM * 16 * RW);  // [NM][16][RW]
     const bool rope = (epilogue == SANIC_EPI_ROPE_CACHE);
+    const bool scaled = fz.ds_partial != nullptr;      // scratch[n] holds the row's deferred 1/sqrt(.)
     // deterministic cross-warp sum: red[warp][matrix][row 0..15][col 0..8*NT)
 #pragma unroll
     for (int mI = 0; mI < NM; ++mI)
@@ -160,7 +185,8 @@ __device__ __forceinline__ void tile_finish(float (&acc)[DUAL ? 2 : 1][NT][4], i
         const int pos = *fz.rope_position;
         for (int idx = tid; idx < 8 * batch; idx += GW * 32) {
             const int n = idx / 8, r = idx % 8;
-            const float a = fin[0][r][n], b = fin[0][r + 8][n];
+            const float sc = scaled ? scratch[n] : 1.0f;
+            const float a = fin[0][r][n] * sc, b = fin[0][r + 8][n] * sc;
             const int d0 = 8 * sub + r;
             if (pos < 0 || pos >= fz.ctx) continue;
             if (seg < 2) {
@@ -183,9 +209,10 @@ __device__ __forceinline__ void tile_finish(float (&acc)[DUAL ? 2 : 1][NT][4], i
     void* outp = seg == 0 ? segs.out[0] : (seg == 1 ? segs.out[1] : segs.out[2]);
     for (int idx = tid; idx < 16 * batch; idx += GW * 32) {
         int n = idx / 16, r = idx % 16;  // consecutive threads -> consecutive rows (contiguous in out[n][row])
-        float y = fin[0][r][n];
+        const float sc = scaled ? scratch[n] : 1.0f;
+        float y = fin[0][r][n] * sc;
         if (DUAL) {  // silu(a) * b = (a * 1/(1+exp(-a))) * b  (reference src/ir.rs:1500-1509)
-            const float ga = y, up = fin[NM - 1][r][n];
+            const float ga = y, up = fin[NM - 1][r][n] * sc;
             float sig = 1.0f / (1.0f + expf(-ga));
             y = (ga * sig) * up;
         }
@@ -194,6 +221,19 @@ __device__ __forceinline__ void tile_finish(float (&acc)[DUAL ? 2 : 1][NT][4], i
         if (epilogue == SANIC_EPI_RESIDUAL_ADD) y = ((have_res && idx == tid) ? res_pre : (PERSIST ? __ldcg(residual + oi) : residual[oi])) + y;
         if (out_dtype == SANIC_BF16) ((uint16_t*)outp)[oi] = f32_to_bf16_bits(y);
         else ((float*)outp)[oi] = y;
+        if (epilogue == SANIC_EPI_RESIDUAL_ADD && fz.nx_out) {
+            // the next contraction's activations and this tile's share of sum y^2: the 16 threads of a batch row are 16
+            // neighbouring lanes (16 * batch is a multiple of 16, so the active lanes are whole groups)
+            fz.nx_out[oi] = f32_to_bf16_bits(y * bf16_to_f32(fz.nx_gamma[row0 + r]));
+            // lanes of this warp inside the loop: all 32, or the lower 16 when 16 * batch ends in the middle of the warp
+            const unsigned live = (16 * batch - (int)(threadIdx.x & ~31u) >= 32) ? 0xffffffffu : 0x0000ffffu;
+            float sq = y * y;
+            sq += __shfl_xor_sync(live, sq, 8);
+            sq += __shfl_xor_sync(live, sq, 4);
+            sq += __shfl_xor_sync(live, sq, 2);
+            sq += __shfl_xor_sync(live, sq, 1);
+            if (r == 0) fz.nx_partial[(size_t)n * (rows / 16) + tile] = sq;
+        }
     }
 }
 
@@ -254,6 +294,7 @@ __device__ __forceinline__ void gemv_tile(const uint16_t* __restrict__ x, int ba
     if (pdl) { griddep_launch(); griddep_wait(); }
 
     if (NORM && !PERSIST) row_norms<false>(fz, batch, K, scratch);
+    if (!NORM && !PERSIST && fz.ds_partial) defer_scales<false>(fz, batch, scratch);
 
     float acc[NM][NT][4];
 #pragma unroll
@@ -447,7 +488,13 @@ inline int32_t host_prepare(sanic_ctx* ctx, const sanic_gemv_params* p, SegTable
     for (int i = p->n_segments; i < 4; ++i) segs.tile_begin[i] = tiles;
     fz = Fused{p->norm_x, (const uint16_t*)p->norm_gamma, p->norm_eps, p->rope_table, p->rope_position,
                (uint16_t*)p->rope_q_out, (uint16_t*)p->rope_k_cache, (uint16_t*)p->rope_v_cache,
-               p->rope_q_heads, p->rope_kv_heads, p->rope_head_dim, p->rope_ctx};
+               p->rope_q_heads, p->rope_kv_heads, p->rope_head_dim, p->rope_ctx,
+               (uint16_t*)p->nx_out, (const uint16_t*)p->nx_gamma, p->nx_partial, p->ds_partial, p->ds_tiles, p->ds_eps};
+    const bool nx = p->nx_out || p->nx_gamma || p->nx_partial;
+    SANIC_REQUIRE(ctx, !nx || (p->nx_out && p->nx_gamma && p->nx_partial && p->epilogue == SANIC_EPI_RESIDUAL_ADD && p->out_dtype == SANIC_F32),
+                  "gemv: the deferred-norm outputs need all three buffers, the residual-add epilogue and an f32 output");
+    SANIC_REQUIRE(ctx, !p->ds_partial || (!p->norm_x && p->ds_tiles * 16 == p->K && p->ds_eps >= 0.0f),
+                  "gemv: a deferred scale needs ds_tiles = K / 16 and no inlined norm");
     return SANIC_OK;
 }
 

@@ -109,8 +109,18 @@ class LlamaMachine:
     """The decode step as a machine: owns the state buffers, replays one captured step per call."""
 
     def __init__(self, dev: CudaDevice, cfg: dict, weights: dict, ctx: int, batch: int, w4: bool = False,
-                 capture: bool = True, fused: bool = True, persistent: bool = False):
+                 capture: bool = True, fused: bool = True, persistent: bool = False, deferred_norm: bool | None = None):
         self.dev, self.cfg, self.ctx, self.batch, self.w4, self.fused = dev, dict(cfg), ctx, batch, w4, fused
+        # deferred normaliser (fused stage lists only): every RMSNorm whose input a residual-add produces is split into
+        # what that epilogue can do (multiply by gamma, per-tile sums of squares) and one multiply in the next contraction's
+        # epilogue; stored(bf16) then sits on x * gamma (the defer-div carrier of the reference's laws) instead of on the
+        # normalised value. Layer 0's attention norm, fed by the gather, is unchanged. Default: on where the norm would
+        # otherwise be a launch of its own (the launch list at batch > 4: 86 launches per step instead of 118, 1.10 against
+        # 1.23 ms at batch 16); the single-kernel step keeps the norm inlined into its staging pass, which measured faster
+        # there (0.875 against 0.935 ms: the scale's loads would sit in front of the staging loads).
+        if deferred_norm is None:
+            deferred_norm = fused and not persistent and batch > 4
+        self.deferred_norm = bool(deferred_norm and fused)
         H, Hq, Hkv, D = cfg["hidden"], cfg["q_heads"], cfg["kv_heads"], cfg["head_dim"]
         if H != Hq * D or Hq % Hkv or D not in (64, 128):
             raise CompileError("invalid graph: hidden must equal q_heads*head_dim and head_dim must be 64 or 128")
@@ -139,8 +149,11 @@ class LlamaMachine:
         return name
 
     def _gemv(self, b, x, keys, layer, outs, K, rows, epilogue=abi.EPI_STORE, residual=None, out_dtype=abi.F32, norm=None,
-              rope_layer=None):
-        """One contraction stage: activations `x` against the weight matrices `keys` of `layer` (None: the tied table)."""
+              rope_layer=None, next_norm=None, scaled=False):
+        """One contraction stage: activations `x` against the weight matrices `keys` of `layer` (None: the tied table).
+        `next_norm` (a residual-add stage): also write bf16(y * gamma) and the per-tile sums of y^2 for the next normed
+        contraction; `scaled`: this stage's activations are such a bf16(y * gamma) and its outputs take the deferred
+        1/sqrt(mean + eps)."""
         names = [self._names(layer, k) for k in keys]
         quant = self.w[keys[0]][layer].dtype == torch.uint8 if layer is not None else self.w["embed"].dtype == torch.uint8
         s = abi.StageDesc()
@@ -164,6 +177,11 @@ class LlamaMachine:
             g.norm_eps = float(self.cfg.get("eps", 1e-5))
         else:
             refs["gemv.x"] = x
+        if next_norm is not None:
+            refs["gemv.nx_out"], refs["gemv.nx_gamma"], refs["gemv.nx_partial"] = "xn", next_norm, "xn.partial"
+        if scaled:
+            refs["gemv.ds_partial"] = "xn.partial"
+            g.ds_tiles, g.ds_eps = K // 16, float(self.cfg.get("eps", 1e-5))
         if rope_layer is not None:
             cfg = self.cfg
             refs["gemv.rope_table"], refs["gemv.rope_position"], refs["gemv.rope_q_out"] = "rope_table", "position", "q_rope"
@@ -212,6 +230,7 @@ class LlamaMachine:
         # intermediates
         b.scratch("x", abi.F32, (B, H))
         b.scratch("xn", abi.BF16, (B, H))
+        b.scratch("xn.partial", abi.F32, (B, H // 16))
         if not fused:
             b.scratch("q", abi.F32, (B, Hq * D)); b.scratch("k", abi.F32, (B, Hkv * D)); b.scratch("v", abi.F32, (B, Hkv * D))
         b.scratch("q_rope", abi.BF16, (B, Hq, D))
@@ -233,7 +252,10 @@ class LlamaMachine:
         qkv_rows = [Hq * D, Hkv * D, Hkv * D]
         for l in range(L):
             attn_norm, mlp_norm = self._names(l, "attn_norm"), self._names(l, "mlp_norm")
-            if fused:
+            defer = self.deferred_norm
+            if fused and defer and l > 0:
+                self._gemv(b, "xn", ["wq", "wk", "wv"], l, [], H, qkv_rows, abi.EPI_ROPE_CACHE, rope_layer=l, scaled=True)
+            elif fused:
                 if not inline_norm:
                     self._rmsnorm(b, attn_norm)
                 self._gemv(b, "xn", ["wq", "wk", "wv"], l, [], H, qkv_rows, abi.EPI_ROPE_CACHE,
@@ -259,6 +281,12 @@ class LlamaMachine:
             p.out_dtype, p.kv_cap = abi.BF16, ctx
             b.stage(s, {"decode.q": "q_rope", "decode.k": f"cache.{l}.key.next", "decode.v": f"cache.{l}.value.next",
                         "decode.kv_len_dev": "position", "decode.partials": "attn.partials", "decode.out": "attended"})
+            if defer:
+                after = self._names(l + 1, "attn_norm") if l + 1 < L else "model.norm.weight"
+                self._gemv(b, "attended", ["wo"], l, ["x"], Hq * D, [H], abi.EPI_RESIDUAL_ADD, "x", next_norm=mlp_norm)
+                self._gemv(b, "xn", ["wgate", "wup"], l, ["h"], H, [F, F], abi.EPI_SILU_MUL, None, abi.BF16, scaled=True)
+                self._gemv(b, "h", ["wdown"], l, ["x"], F, [H], abi.EPI_RESIDUAL_ADD, "x", next_norm=after)
+                continue
             self._gemv(b, "attended", ["wo"], l, ["x"], Hq * D, [H], abi.EPI_RESIDUAL_ADD, "x")
             if inline_norm:
                 self._gemv(b, "xn", ["wgate", "wup"], l, ["h"], H, [F, F], abi.EPI_SILU_MUL, None, abi.BF16, norm=mlp_norm)
@@ -266,7 +294,9 @@ class LlamaMachine:
                 self._rmsnorm(b, mlp_norm)
                 self._gemv(b, "xn", ["wgate", "wup"], l, ["h"], H, [F, F], abi.EPI_SILU_MUL, None, abi.BF16)
             self._gemv(b, "h", ["wdown"], l, ["x"], F, [H], abi.EPI_RESIDUAL_ADD, "x")
-        if inline_norm:
+        if self.deferred_norm:
+            self._gemv(b, "xn", ["embed"], None, ["logits"], H, [V], scaled=True)
+        elif inline_norm:
             self._gemv(b, "xn", ["embed"], None, ["logits"], H, [V], norm="model.norm.weight")
         else:
             self._rmsnorm(b, "model.norm.weight")

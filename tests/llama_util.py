@@ -98,11 +98,12 @@ def lockstep(machines, o, cfg, prefill, steps, rng, label=""):
     return stats
 
 
-def run_pair(dev, cfg, ctx, batch, w4, steps, prefill, seed=5, fused=True, persistent=False):
+def run_pair(dev, cfg, ctx, batch, w4, steps, prefill, seed=5, fused=True, persistent=False, deferred_norm=None):
     from sanic_b200 import llama
     w = llama.random_weights(cfg, seed, dev.torch_device, w4=w4)
-    m = llama.LlamaMachine(dev, cfg, w, ctx=ctx, batch=batch, w4=w4, fused=fused, persistent=persistent)
-    o = make_oracle(cfg, w, ctx, batch, w4)
+    m = llama.LlamaMachine(dev, cfg, w, ctx=ctx, batch=batch, w4=w4, fused=fused, persistent=persistent, deferred_norm=deferred_norm)
+    # the oracle rounds where the machine does: stored(bf16) on x * gamma at the deferred norms
+    o = make_oracle(cfg, w, ctx, batch, w4, norm_store=2 if m.deferred_norm else 0)
     rng = np.random.default_rng(seed)
     prefill_on_device([m], o, cfg, prefill, rng)
     st = lockstep([m], o, cfg, prefill, steps, rng)[0]

@@ -329,6 +329,37 @@ def test_gemv_segments_and_epilogues(dev):
     assert nerr(res.cpu().numpy(), exp) <= 1e-4
 
 
+@pytest.mark.parametrize("batch", [9, 12, 16])
+def test_gemv_wide_batches_ring_fed_and_register_staged(dev, batch):
+    """Batches 9-16 run the contraction fed by bulk copies through a shared-memory ring when the shape has a ring geometry
+    (a stage of at least 256 inputs that divides K), else the register-staged kernel: both against the oracle, over one to
+    four ring stages per tile, more tiles than SMs, three row segments, the silu-mul pair and the residual epilogue."""
+    import ctypes as C
+    from sanic_b200 import abi
+    for K, rows in ((256, 48), (1024, 4752), (4096, 64), (1536, 32), (128, 16)):       # the last two have no ring geometry
+        x, xv = bf16t(normal(121, batch, K), dev)
+        w, wv = bf16t(normal(122, rows, K) * 0.02, dev)
+        assert nerr(dev.gemv(x, [w]).cpu().numpy(), orc.gemv_bf16w(orc.to_bf16_bits(wv), xv)) <= 1e-4, (K, rows)
+    for K, rows in ((4096, 48), (8192, 32), (512, 64)):
+        q, packed, pt, st, sv = _w4(rows, K, 131 + batch, dev)
+        x, xv = bf16t(normal(132, batch, K), dev)
+        assert nerr(dev.gemv(x, [pt], scales=[st]).cpu().numpy(), orc.w4_gemv(packed, sv, xv, rows, group=64)) <= 2e-4, (K, rows)
+    K = 2048
+    x, xv = bf16t(normal(141, batch, K), dev)
+    ws = [bf16t(normal(142 + i, r, K) * 0.05, dev) for i, r in enumerate((128, 32, 32))]
+    for (w, wv), o in zip(ws, dev.gemv(x, [w for w, _ in ws])):
+        assert nerr(o.cpu().numpy(), orc.gemv_bf16w(orc.to_bf16_bits(wv), xv)) <= 1e-4
+    a = orc.gemv_bf16w(orc.to_bf16_bits(ws[1][1]), xv)
+    b = orc.gemv_bf16w(orc.to_bf16_bits(ws[2][1]), xv)
+    got = dev.gemv(x, [ws[1][0], ws[2][0]], epilogue=abi.EPI_SILU_MUL)
+    assert nerr(got.cpu().numpy(), (a * (1.0 / (1.0 + np.exp(-a)))) * b) <= 1e-4
+    res = f32t(normal(149, batch, 128), dev)
+    exp = res.cpu().numpy().astype(np.float64) + orc.gemv_bf16w(orc.to_bf16_bits(ws[0][1]), xv)
+    p = dev.gemv_params(x, [ws[0][0]], [res], None, abi.EPI_RESIDUAL_ADD, res, abi.F32)
+    dev._check(dev.lib.sanic_gemv(dev.h, C.byref(p), dev.stream()), "gemv")
+    assert nerr(res.cpu().numpy(), exp) <= 1e-4
+
+
 @pytest.mark.parametrize("batch,w4", [(1, False), (16, False), (3, True)])
 def test_gemv_with_inlined_rmsnorm(dev, batch, w4):
     K, rows = 2048, 128

@@ -61,7 +61,10 @@ def test_batch16_and_replay_equals_eager(dev):
     assert np.array_equal(a.read_tokens(), b.read_tokens())
     assert int(a.position.item()) == 12
     assert a.kernel_count == a.n_stages + 1
-    assert a.n_stages == 1 + 7 * SMALL["layers"] + 4      # batch 16: norms stay separate stages, RoPE rides the projection
+    # batch 16: only layer 0's attention norm stays a stage of its own (the others are deferred across the contractions)
+    assert a.deferred_norm and a.n_stages == 1 + 1 + 5 * SMALL["layers"] + 3
+    c = llama.LlamaMachine(dev, SMALL, w, ctx=64, batch=16, deferred_norm=False)
+    assert c.n_stages == 1 + 7 * SMALL["layers"] + 4      # without it: both norms of every layer are stages
 
 
 def test_machine_refuses_bad_state(dev):
@@ -128,3 +131,15 @@ def test_text_in_text_out(dev):
     known = [int(t) for t in outs[0] if int(t) in tok.id_to_token]
     text = tok.decode(known)
     assert isinstance(text, str) and tok.decode(tok.encode(text, False)) == text
+
+
+@pytest.mark.parametrize("batch,w4,persistent", [(1, False, False), (3, True, False), (16, False, False), (16, True, False),
+                                                 (1, False, True), (2, True, True), (16, False, True)])
+def test_deferred_normaliser(dev, batch, w4, persistent):
+    """RMSNorm split across two contractions: the residual-add epilogue writes bf16(x * gamma) and per-tile sums of x^2,
+    the next contraction multiplies its outputs by 1/sqrt(mean + eps). The oracle moves its stored(bf16) point with it
+    (norm_store = 2) and the tokens must agree step for step, in the launch list and in the single-kernel form."""
+    m = run_pair(dev, SMALL, ctx=128, batch=batch, w4=w4, steps=32, prefill=40, persistent=persistent, deferred_norm=True)
+    L = SMALL["layers"]
+    first_norm = 0 if (batch <= 4 or persistent) else 1          # layer 0's attention norm: inlined, or a stage of its own
+    assert m.n_stages == 1 + first_norm + 5 * L + 3
