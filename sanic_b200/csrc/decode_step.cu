@@ -41,6 +41,7 @@ enum { PH_GEMV = 1, PH_DECODE, PH_EMBED, PH_RMSNORM, PH_ARGMAX_PART, PH_ARGMAX_F
 constexpr int CONSUMERS = 256;              // warps 0-7: the phase bodies
 constexpr int PRODUCERS = 4;                // warps 8..: the weight producers, ring stages dealt round-robin
 constexpr int THREADS = CONSUMERS + 32 * PRODUCERS;
+constexpr int RING_THREADS = CONSUMERS + 32;   // the stand-alone ring-fed contraction: one producer warp
 constexpr int AMAX_CHUNKS = 128;
 constexpr unsigned SPIN_LIMIT = 1u << 22;
 constexpr int SLOTS = 4;                    // weight ring
@@ -222,7 +223,7 @@ __device__ __noinline__ void stage_normed_rows(const Phase& P, float* scratch, u
 // DIRECT: the activations are not staged in shared memory; every use reads them from global memory through L1 (the
 // stand-alone ring-fed contraction: a kernel of its own starts with a clean L1, and its activations were written by an
 // earlier kernel, so the non-coherent path is safe there and 64 KB of them stay resident).
-template <bool W4, int NT, bool DUAL, bool NORM, bool DIRECT = false>
+template <bool W4, int NT, bool DUAL, bool NORM, bool DIRECT = false, int NSLOTS = SLOTS, int SLOTB = SLOT_BYTES>
 __device__ __forceinline__ bool consume_gemv(const Phase& P, const Ring& ring, uint32_t& drained, float* scratch, unsigned* gbar, int* err,
                                              unsigned long long* prof) {
     using namespace gemv;
@@ -299,12 +300,12 @@ __device__ __forceinline__ bool consume_gemv(const Phase& P, const Ring& ring, u
             }
         }
         for (int s = 0; s < G.n_stages; ++s, ++drained) {
-            const int slot = drained % SLOTS;
-            const uint32_t parity = (drained / SLOTS) & 1;
+            const int slot = drained % NSLOTS;
+            const uint32_t parity = (drained / NSLOTS) & 1;
             const int kbase = s * G.stage_k;
             ok = mbar_wait(&ring.full[slot], parity, gbar, err, 32);
             if (!ok) break;
-            const unsigned char* sb = ring.ptr + (size_t)slot * SLOT_BYTES;
+            const unsigned char* sb = ring.ptr + (size_t)slot * SLOTB;
             for (int sp = 0; sp < spans_per_stage; ++sp) {
             const int xbase = whole ? 0 : kbase + sp * xspan;
             if (!whole) { consumer_sync(); stage_x(xbase); consumer_sync(); }
@@ -406,6 +407,7 @@ __device__ __forceinline__ void amax_merge(float& v, int& i, float v2, int i2) {
 
 // The producers' half of one contraction phase: this block's tiles, stage by stage, into the ring. `fill` counts the ring
 // stages issued so far by all producer warps together; warp `pw` issues the stages with fill % PRODUCERS == pw.
+template <int NSLOTS = SLOTS, int NPROD = PRODUCERS, int SLOTB = SLOT_BYTES>
 __device__ __forceinline__ bool produce_phase(const Phase& P, const Ring& ring, uint64_t* s_full, uint64_t* s_empty, unsigned& fill, int lane,
                                               int pw, unsigned* bar, int* err) {
     bool ok = true;
@@ -435,17 +437,17 @@ __device__ __forceinline__ bool produce_phase(const Phase& P, const Ring& ring, 
                 }
             }
             for (int s = 0; s < G.n_stages && ok; ++s, ++fill) {
-                if ((int)(fill % PRODUCERS) != pw) continue;
-                const int slot = fill % SLOTS;
+                if ((int)(fill % NPROD) != pw) continue;
+                const int slot = fill % NSLOTS;
                 if (lane == 0) {
-                    ok = mbar_wait(&s_empty[slot], ((fill / SLOTS) & 1) ^ 1, bar, err, 33);
+                    ok = mbar_wait(&s_empty[slot], ((fill / NSLOTS) & 1) ^ 1, bar, err, 33);
                     if (ok) mbar_expect_tx(&s_full[slot], (uint32_t)(G.rows * (G.row_bytes + G.scale_row_bytes)));
                 }
                 ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
                 if (ok && lane < G.rows) {
-                    bulk_load(ring.base + slot * SLOT_BYTES + lane * G.pitch, src_row + (size_t)s * G.row_bytes, (uint32_t)G.row_bytes, &s_full[slot]);
+                    bulk_load(ring.base + slot * SLOTB + lane * G.pitch, src_row + (size_t)s * G.row_bytes, (uint32_t)G.row_bytes, &s_full[slot]);
                     if (G.scale_row_bytes)
-                        bulk_load(ring.base + slot * SLOT_BYTES + G.scale_off + lane * G.scale_row_bytes,
+                        bulk_load(ring.base + slot * SLOTB + G.scale_off + lane * G.scale_row_bytes,
                                   src_scale + (size_t)s * G.scale_row_bytes, (uint32_t)G.scale_row_bytes, &s_full[slot]);
                 }
             }
@@ -652,39 +654,43 @@ decode_step_kernel(const Phase* __restrict__ phases, int n_phases, unsigned* bar
 // the shared-memory ring with bulk copies, consumer warps take their activations from global memory through L1. Used by
 // the launch-list form at batch > 8, where the register-staged loads of gemv_mma_kernel (two 64-blocks per warp: what 128
 // registers hold beside two accumulator tiles) keep about 10 MB in flight and 19 MB saturate HBM; the ring holds
-// 4 x 32 KB per SM in flight whatever the consumers' registers do. The weights do not depend on the stream predecessor,
+// 64 KB per block in flight whatever the consumers' registers do. bf16: two slots and two blocks per SM (90 KB of shared
+// memory and at most 112 registers each), so that the blocks of the NEXT kernel of a launch list become resident while
+// this one drains and their producers stream weights through the kernel boundary; int4 needs more registers than two
+// blocks per SM leave and runs four slots, one block per SM. The weights do not depend on the stream predecessor,
 // so the producers start before the programmatic-launch wait; the consumers wait before they touch activations.
-template <bool W4, bool DUAL>
-__global__ void __launch_bounds__(THREADS, 1) gemv_ring_kernel(const __grid_constant__ Phase P, int* err) {
+template <bool W4, bool DUAL, int NSLOTS, int SLOTB, int PER_SM>
+__global__ void __launch_bounds__(RING_THREADS, PER_SM) gemv_ring_kernel(const __grid_constant__ Phase P, int* err) {
     extern __shared__ __align__(128) unsigned char dyn[];       // [weight ring][contraction scratch]
-    __shared__ __align__(8) uint64_t s_full[SLOTS], s_empty[SLOTS];
+    __shared__ __align__(8) uint64_t s_full[NSLOTS], s_empty[NSLOTS];
     __shared__ unsigned s_produced;
     const int tid = threadIdx.x;
     Ring ring{s_full, s_empty, smem_u32(dyn), dyn};
     if (tid == 0) {
-        for (int i = 0; i < SLOTS; ++i) { mbar_init(&s_full[i], 1); mbar_init(&s_empty[i], gemv::GW); }
+        for (int i = 0; i < NSLOTS; ++i) { mbar_init(&s_full[i], 1); mbar_init(&s_empty[i], gemv::GW); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         s_produced = 0;
     }
     __syncthreads();
     if (tid >= CONSUMERS) {
-        const int lane = tid & 31, pw = (tid - CONSUMERS) >> 5;
+        // one producer warp: a stage is 16 or 32 row copies issued by as many lanes
+        const int lane = tid & 31;
         unsigned fill = 0;
-        produce_phase(P, ring, s_full, s_empty, fill, lane, pw, nullptr, err);
-        if (lane == 0 && pw == 0) s_produced = fill;
+        produce_phase<NSLOTS, 1, SLOTB>(P, ring, s_full, s_empty, fill, lane, 0, nullptr, err);
+        if (lane == 0) s_produced = fill;
     } else {
         griddep_launch();
         griddep_wait();
         uint32_t drained = 0;
-        consume_gemv<W4, 2, DUAL, false, true>(P, ring, drained, (float*)(dyn + RING_BYTES), nullptr, err, nullptr);
+        consume_gemv<W4, 2, DUAL, false, true, NSLOTS, SLOTB>(P, ring, drained, (float*)(dyn + NSLOTS * SLOTB), nullptr, err, nullptr);
     }
     __syncthreads();
     if (tid == 0) {      // no copy into this CTA's shared memory may still be in flight when it exits
         const unsigned produced = s_produced;
-        const unsigned first = produced > SLOTS ? produced - SLOTS : 0;
+        const unsigned first = produced > (unsigned)NSLOTS ? produced - NSLOTS : 0;
         for (unsigned f = first; f < produced; ++f) {
             bool done = false;
-            for (unsigned it = 0; it < SPIN_LIMIT && !done; ++it) done = mbar_test(&s_full[f % SLOTS], (f / SLOTS) & 1);
+            for (unsigned it = 0; it < SPIN_LIMIT && !done; ++it) done = mbar_test(&s_full[f % NSLOTS], (f / NSLOTS) & 1);
         }
     }
     __syncthreads();
@@ -729,16 +735,26 @@ int32_t gemv_ring(sanic_ctx* ctx, const sanic_gemv_params* g, cudaStream_t strea
     P.variant = (w4 ? 1 : 0) | 2 | (dual ? 4 : 0);
     P.x = (const uint16_t*)g->x; P.batch = g->batch; P.K = g->K; P.n_segments = g->n_segments;
     P.out_dtype = g->out_dtype; P.epilogue = g->epilogue; P.residual = g->residual;
-    const size_t smem = RING_BYTES + SCRATCH_BYTES;
     sanic_set_device(ctx);
-    auto go = [&](auto kern) -> int32_t {
+    auto go = [&](auto kern, int slots, int slot_bytes, int scratch_bytes, int per_sm) -> int32_t {
+        const size_t smem = (size_t)slots * slot_bytes + scratch_bytes;
         SANIC_CUDA_CHECK(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        cudaError_t e = launch_pdl(kern, dim3(std::min(tiles, ctx->sm_count)), dim3(THREADS), smem, stream, P, ctx->status_dev);
+        // every block must be resident at once: the programmatic launch of the next kernel may only follow blocks that
+        // have started, and blocks of that kernel then hold SM slots until this one has finished
+        cudaError_t e = launch_pdl(kern, dim3(std::min(tiles, per_sm * ctx->sm_count)), dim3(RING_THREADS), smem, stream, P, ctx->status_dev);
         if (e != cudaSuccess) return sanic_fail(ctx, SANIC_ERR_CUDA, std::string("gemv (ring): ") + cudaGetErrorString(e));
         return SANIC_OK;
     };
-    if (w4) return dual ? go(gemv_ring_kernel<true, true>) : go(gemv_ring_kernel<true, false>);
-    return dual ? go(gemv_ring_kernel<false, true>) : go(gemv_ring_kernel<false, false>);
+    if (w4) return dual ? go(gemv_ring_kernel<true, true, 4, SLOT_BYTES, 1>, 4, SLOT_BYTES, SCRATCH_BYTES, 1)
+                        : go(gemv_ring_kernel<true, false, 4, SLOT_BYTES, 1>, 4, SLOT_BYTES, SCRATCH_BYTES, 1);
+    // bf16. More tiles than SMs: two slots, two blocks per SM (90 KB each). At most one tile per SM: three slots keep the bytes
+    // in flight up, and their 125 KB still leave room for a two-slot block of the next kernel beside them. (Three slots of
+    // exactly a stage's size, two blocks per SM, measured slower: 1.06 against 1.03 ms per step at batch 16.)
+    if (tiles <= ctx->sm_count)
+        return dual ? go(gemv_ring_kernel<false, true, 3, SLOT_BYTES, 2>, 3, SLOT_BYTES, SCRATCH_BYTES, 1)
+                    : go(gemv_ring_kernel<false, false, 3, SLOT_BYTES, 2>, 3, SLOT_BYTES, SCRATCH_BYTES, 1);
+    return dual ? go(gemv_ring_kernel<false, true, 2, SLOT_BYTES, 2>, 2, SLOT_BYTES, SCRATCH_BYTES, 2)
+                : go(gemv_ring_kernel<false, false, 2, SLOT_BYTES, 2>, 2, SLOT_BYTES, SCRATCH_BYTES, 2);
 }
 
 int32_t build(sanic_ctx* ctx, const std::vector<sanic_stage_desc>& stages, Plan** out) {
