@@ -390,6 +390,12 @@ int32_t sanic_generic_compile(sanic_ctx* ctx, const sanic_generic_desc* d, sanic
 int32_t sanic_generic_launch(sanic_ctx* ctx, sanic_generic_kernel* k, const void* const* buffers, int32_t n_buffers, void* out,
                              void* stream);
 int32_t sanic_generic_destroy(sanic_generic_kernel* k);
+/* A descriptive name of the kernel (kind, grid, streamed extent, schedule, output width): kernel_name of the reference's
+ * emitter (src/emit_metal.rs:1340-1370); a debug stage listing prints it. */
+const char* sanic_generic_kernel_name(sanic_generic_kernel* k);
+/* Kernel dedup across isomorphic stages (src/emit_metal.rs:1281-1330): stages that differ only in their buffers render the
+ * same text and are compiled once per process. Counts of texts compiled and of compilations answered from the cache. */
+int32_t sanic_generic_cache_stats(int64_t* compiled, int64_t* reused);
 
 /* ── stateful stepping: Graph::compile_for / StepProgram::instantiate / Machine::step
  *    (src/graph.rs:231-356) with capture/replay (src/compile.rs:820-1035, src/metal.rs:634-705) ── */

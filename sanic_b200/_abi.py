@@ -231,6 +231,8 @@ PROTOTYPES = {
     "sanic_generic_compile": (i32, [vp, C.POINTER(GenericDesc), C.POINTER(vp)]),
     "sanic_generic_launch": (i32, [vp, vp, C.POINTER(vp), i32, vp, vp]),
     "sanic_generic_destroy": (i32, [vp]),
+    "sanic_generic_kernel_name": (C.c_char_p, [vp]),
+    "sanic_generic_cache_stats": (i32, [C.POINTER(i64), C.POINTER(i64)]),
     "sanic_program_create": (i32, [vp, C.POINTER(StageDesc), i32, C.POINTER(vp)]),
     "sanic_program_destroy": (i32, [vp]),
     "sanic_program_kernel_count": (i32, [vp]),

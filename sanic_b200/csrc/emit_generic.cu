@@ -35,6 +35,8 @@
 #include <cmath>
 #include <cstdio>
 #include <cstring>
+#include <map>
+#include <mutex>
 #include <sstream>
 #include <vector>
 
@@ -565,7 +567,24 @@ int32_t render(sanic_ctx* ctx, const sanic_generic_desc* d, std::string* text) {
     return SANIC_OK;
 }
 
+// Kernel dedup across isomorphic stages (src/emit_metal.rs:1281-1330 canonicalises each kernel's source and keeps one entry
+// point per body): here buffers bind positionally at launch and every extent and dtype is baked into the text, so two
+// stages that differ only in their buffers render the SAME text, and the text is the key. One compilation per text per
+// process; every kernel object still loads its own module (a module belongs to a context).
+struct CubinCache {
+    std::mutex mu;
+    std::map<std::string, std::vector<char>> by_text;
+    long long compiled = 0, reused = 0;
+};
+CubinCache& cubin_cache() { static CubinCache c; return c; }
+
 int32_t compile_cubin(sanic_ctx* ctx, const std::string& text, std::vector<char>* cubin) {
+    {
+        CubinCache& c = cubin_cache();
+        std::lock_guard<std::mutex> lock(c.mu);
+        auto it = c.by_text.find(text);
+        if (it != c.by_text.end()) { *cubin = it->second; ++c.reused; return SANIC_OK; }
+    }
     Nvrtc& n = nvrtc();
     if (!n.ok) return sanic_fail(ctx, SANIC_ERR_UNSUPPORTED, "generic emitter: the NVRTC library could not be loaded");
     nvrtcProgram prog;
@@ -587,12 +606,36 @@ int32_t compile_cubin(sanic_ctx* ctx, const std::string& text, std::vector<char>
     if (sz) n.cubin(prog, cubin->data());
     n.destroy(&prog);
     if (!sz) return sanic_fail(ctx, SANIC_ERR_CUDA, "generated kernel: empty cubin");
+    CubinCache& c = cubin_cache();
+    std::lock_guard<std::mutex> lock(c.mu);
+    ++c.compiled;
+    if (c.by_text.size() < 4096) c.by_text.emplace(text, *cubin);
     return SANIC_OK;
+}
+
+// A descriptive name (kind, grid, streamed extent, schedule), as the reference composes one per kernel
+// (kernel_name, src/emit_metal.rs:1340-1370): what a stage listing or a profile shows instead of one entry-point name.
+std::string describe(const sanic_generic_desc* d) {
+    std::ostringstream o;
+    if (d->stream > 0) o << "fold" << d->n_slots; else o << "map";
+    o << "_g";
+    for (int a = 0; a < d->n_axes; ++a) o << (a ? "x" : "") << (long long)d->extent[a];
+    if (d->n_axes == 0) o << "1";
+    if (d->stream > 0) {
+        o << "_s";
+        if (d->stream_dims > 1) for (int j = 0; j < d->stream_dims; ++j) o << (j ? "x" : "") << (long long)d->stream_extent[j];
+        else o << (long long)d->stream;
+        if (d->lanes == 32) o << (d->lane_axis ? "_laneaxis" : (d->interleave ? "_lanes_interleaved" : "_lanes")) << (d->warps > 1 ? "_w" + std::to_string(d->warps) : "");
+        else o << "_thread";
+    }
+    o << (d->out_dtype == SANIC_BF16 ? "_bf16" : (d->out_dtype == SANIC_U32 ? "_u32" : "_f32"));
+    return o.str();
 }
 
 }  // namespace
 
 struct sanic_generic_kernel {
+    std::string name;
     CUmodule module = nullptr;
     CUfunction fn = nullptr;
     int64_t points = 0;     // launch units
@@ -645,6 +688,7 @@ int32_t sanic_generic_compile(sanic_ctx* ctx, const sanic_generic_desc* d, sanic
     if (cr != CUDA_SUCCESS) { delete k; return sanic_fail(ctx, SANIC_ERR_CUDA, "cuModuleLoadData failed with code " + std::to_string((int)cr)); }
     cr = dr.get_function(&k->fn, k->module, "sanic_generic");
     if (cr != CUDA_SUCCESS) { dr.module_unload(k->module); delete k; return sanic_fail(ctx, SANIC_ERR_CUDA, "cuModuleGetFunction failed with code " + std::to_string((int)cr)); }
+    k->name = describe(d);
     k->points = grid_points(d);
     if (d->stream > 0 && d->lanes == 32 && d->lane_axis) {      // a unit = 32 points of the last axis
         const int64_t ext = d->extent[d->n_axes - 1];
@@ -675,6 +719,16 @@ int32_t sanic_generic_launch(sanic_ctx* ctx, sanic_generic_kernel* k, const void
     sanic_set_device(ctx);
     CUresult cr = driver().launch(k->fn, (unsigned)blocks, 1, 1, (unsigned)k->block, 1, 1, 0, (CUstream)stream, args, nullptr);
     if (cr != CUDA_SUCCESS) return sanic_fail(ctx, SANIC_ERR_CUDA, "cuLaunchKernel failed with code " + std::to_string((int)cr));
+    return SANIC_OK;
+}
+
+const char* sanic_generic_kernel_name(sanic_generic_kernel* k) { return k ? k->name.c_str() : ""; }
+
+int32_t sanic_generic_cache_stats(int64_t* compiled, int64_t* reused) {
+    CubinCache& c = cubin_cache();
+    std::lock_guard<std::mutex> lock(c.mu);
+    if (compiled) *compiled = c.compiled;
+    if (reused) *reused = c.reused;
     return SANIC_OK;
 }
 

@@ -399,7 +399,9 @@ int32_t sanic_schedule_capture(sanic_schedule* s, const sanic_binding* b, int32_
                 s->bufs.size(), parities, sanic_program_kernel_count(r->parity[0]), persistent ? " (one cooperative kernel)" : "");
     if (debug_level() >= 3)
         for (size_t i = 0; i < s->stages.size(); ++i)
-            fprintf(stderr, "sanic:   stage %3zu  %-20s kind %d\n", i, op_name(s->stages[i].op), s->stages[i].stage_kind);
+            fprintf(stderr, "sanic:   stage %3zu  %-20s kind %d%s%s\n", i, op_name(s->stages[i].op), s->stages[i].stage_kind,
+                    s->stages[i].op == SANIC_OP_GENERIC ? "  " : "",
+                    s->stages[i].op == SANIC_OP_GENERIC ? sanic_generic_kernel_name(s->stages[i].u.generic.kernel) : "");
     *out = r;
     return SANIC_OK;
 }

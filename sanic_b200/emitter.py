@@ -295,6 +295,14 @@ def compiles(desc: Description) -> int:
     return n.value
 
 
+def cache_stats(lib=None):
+    """(texts compiled, compilations answered from the cache) of this process: isomorphic stages compile once."""
+    lib = lib or abi.load()
+    a, b = abi.i64(0), abi.i64(0)
+    lib.sanic_generic_cache_stats(C.byref(a), C.byref(b))
+    return a.value, b.value
+
+
 class GenericKernel:
     """A compiled and loaded generic kernel on one device (the Executable of one stage)."""
 
@@ -303,6 +311,11 @@ class GenericKernel:
         h = C.c_void_p()
         device._check(device.lib.sanic_generic_compile(device.h, C.byref(desc.desc), C.byref(h)), "generic_compile")
         self.h = h
+
+    @property
+    def name(self) -> str:
+        """Kind, grid, streamed extent, schedule and output width, e.g. 'fold1_g8x4_s16_lanes_f32'."""
+        return self.device.lib.sanic_generic_kernel_name(self.h).decode()
 
     def __call__(self, buffers, out):
         """buffers: torch tensors on the device, in buffer-index order; out: a tensor of grid size at the output dtype."""

@@ -715,3 +715,33 @@ def test_generic_top_k_as_repeated_first_argmax(dev):
     want = np.argsort(-x, axis=1, kind="stable")[:, :k]
     assert np.array_equal(got, want)
     assert got[1, 0] == 10 and got[1, 1] == 60
+
+
+def test_isomorphic_stages_compile_once_and_kernels_carry_descriptive_names():
+    """Two stages that differ only in the buffers they bind render the same text: one compilation (the reference dedups
+    per canonical body, src/emit_metal.rs:1281-1330). Needs NVRTC, not a device."""
+    grid, k, ops, car = matmul_case(8, 16, 4, abi.BF16)
+    d1 = em.Description(grid, ops, carrier=car, stream=k, lanes=32)
+    # the same stage over other buffers of the same layout
+    ops2 = [em.Operand(3, abi.BF16, [k, 0], 1), em.Operand(7, abi.BF16, [0, 1], 4)]
+    d2 = em.Description(grid, ops2, carrier=car, stream=k, lanes=32)
+    assert em.source(d1) != em.source(d2)          # buffer slots are part of the text: positional binding is per kernel
+    c0, r0 = em.cache_stats()
+    assert em.compiles(d1) > 0
+    c1, r1 = em.cache_stats()
+    assert em.compiles(d1) > 0 and em.compiles(em.Description(grid, ops, carrier=car, stream=k, lanes=32)) > 0
+    c2, r2 = em.cache_stats()
+    assert c2 == c1 and r2 == r1 + 2 and c1 - c0 <= 1
+
+
+@pytest.mark.gpu
+def test_generated_kernel_names(dev):
+    grid, k, ops, car = matmul_case(8, 16, 4, abi.BF16)
+    a = em.GenericKernel(dev, em.Description(grid, ops, carrier=car, stream=k, lanes=32))
+    b = em.GenericKernel(dev, em.Description(grid, ops, carrier=car, stream=k, out_dtype=abi.BF16))
+    g, win, cops, ccar = em.conv2d(2, 3, 9, 8, 4, 3, 3)
+    c = em.GenericKernel(dev, em.Description(g, cops, carrier=ccar, stream=win, lanes=32, warps=4))
+    assert a.name == "fold1_g8x4_s16_lanes_f32" and b.name == "fold1_g8x4_s16_thread_bf16"
+    assert c.name == "fold1_g2x4x7x6_s3x3x3_lanes_w4_f32"
+    for kk in (a, b, c):
+        kk.close()
