@@ -276,6 +276,10 @@ __device__ __forceinline__ bool consume_gemv(const Phase& P, const Ring& ring, u
     const unsigned char* xs1 = DIRECT ? (const unsigned char*)(P.x + (size_t)(xok1 ? g + 8 : 0) * P.K) : xs + (size_t)(xok1 ? g + 8 : 0) * xpitch;
     auto ldx = [](const unsigned char* p) { return DIRECT ? __ldg((const uint4*)p) : *(const uint4*)p; };
     bool ok = true;
+    // two sets of per-warp partial sums, used alternately, when the scratch holds them: a tile's epilogue then needs no barrier
+    // against the next tile's contraction (the one barrier inside every tile's finish orders the reuse two tiles later)
+    constexpr bool PINGPONG = (16 + 16 * GW + 2 * red_floats<NT, DUAL>()) * 4 <= SCRATCH_BYTES;
+    int parity = 0;
     for (int gt = blockIdx.x; gt < P.n_blocks && ok; gt += gridDim.x) {
         int seg, tile;
         seg_of_tile(P.segs, P.n_segments, DUAL, gt, seg, tile);
@@ -385,8 +389,9 @@ __device__ __forceinline__ bool consume_gemv(const Phase& P, const Ring& ring, u
         }
         if (!ok) break;
         stamp(prof, 1);      // the last tile's contraction is done (overwritten per tile)
-        tile_finish<NT, DUAL, true>(acc, P.batch, P.segs, P.out_dtype, P.epilogue, P.residual, P.fz, 1, 0, seg, tile, scratch, have_res, res_pre);
-        consumer_sync();   // the scratch is reused by the next tile
+        tile_finish<NT, DUAL, true>(acc, P.batch, P.segs, P.out_dtype, P.epilogue, P.residual, P.fz, 1, 0, seg, tile, scratch, have_res, res_pre, parity);
+        if (PINGPONG) parity ^= 1;
+        else consumer_sync();   // the scratch is reused by the next tile
     }
     stamp(prof, 2);          // sums and epilogue done: the block is ready for the grid barrier
     return ok;

@@ -122,16 +122,22 @@ __host__ __device__ constexpr int scratch_floats() {
     return 16 + 16 * GW + (GW + 1) * (DUAL ? 2 : 1) * 16 * (8 * NT + 1);
 }
 
-// Second half of a tile: the GW warps' partial sums are added in a fixed order, then the epilogue runs.
+// Floats of one set of per-warp partial sums; a caller that runs several tiles through one block may alternate between two
+// sets (`parity`) so that a tile's epilogue and the next tile's contraction need no barrier between them.
+template <int NT, bool DUAL>
+__host__ __device__ constexpr int red_floats() { return GW * (DUAL ? 2 : 1) * 16 * (8 * NT + 1); }
+
+// Second half of a tile: the GW warps' partial sums are added in a fixed order, then the epilogue runs. Without a K split
+// across a cluster the threads that run the epilogue add the eight partials themselves: one block barrier per tile.
 template <int NT, bool DUAL, bool PERSIST>
 __device__ __forceinline__ void tile_finish(float (&acc)[DUAL ? 2 : 1][NT][4], int batch, const SegTable& segs, int out_dtype,
                                             int epilogue, const float* residual, const Fused& fz, int KS, int krank, int seg,
-                                            int tile, float* scratch, bool have_res = false, float res_pre = 0.0f) {
+                                            int tile, float* scratch, bool have_res = false, float res_pre = 0.0f, int parity = 0) {
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, t = lane & 3;
     constexpr int NM = DUAL ? 2 : 1, RW = 8 * NT + 1;
-    float (*red)[NM][16][RW] = reinterpret_cast<float (*)[NM][16][RW]>(scratch + 16 + 16 * GW);            // [GW][NM][16][RW]
-    float (*csum)[16][RW] = reinterpret_cast<float (*)[16][RW]>(scratch + 16 + 16 * GW + GW * NM * 16 * RW);  // [NM][16][RW]
+    float (*red)[NM][16][RW] = reinterpret_cast<float (*)[NM][16][RW]>(scratch + 16 + 16 * GW + parity * red_floats<NT, DUAL>());   // [GW][NM][16][RW]
+    float (*csum)[16][RW] = reinterpret_cast<float (*)[16][RW]>(scratch + 16 + 16 * GW + GW * NM * 16 * RW);  // [NM][16][RW], K split only
     const bool rope = (epilogue == SANIC_EPI_ROPE_CACHE);
     const bool scaled = fz.ds_partial != nullptr;      // scratch[n] holds the row's deferred 1/sqrt(.)
     // deterministic cross-warp sum: red[warp][matrix][row 0..15][col 0..8*NT)
@@ -145,17 +151,17 @@ __device__ __forceinline__ void tile_finish(float (&acc)[DUAL ? 2 : 1][NT][4], i
             red[warp][mI][g + 8][8 * j + 2 * t + 1] = acc[mI][j][3];
         }
     block_sync<PERSIST>();
-    // CTA sum in a fixed warp order, then (KS > 1) the cluster's CTAs are summed in rank order by
-    // rank 0 through distributed shared memory: deterministic, no global scratch.
-    for (int idx = tid; idx < NM * 16 * 8 * NT; idx += GW * 32) {
-        const int n = idx % (8 * NT), r = (idx / (8 * NT)) % 16, mI = idx / (8 * NT * 16);
-        float sv = 0.0f;
-#pragma unroll
-        for (int w = 0; w < GW; ++w) sv += red[w][mI][r][n];
-        csum[mI][r][n] = sv;
-    }
-    block_sync<PERSIST>();
     if (KS > 1) {
+        // CTA sum in a fixed warp order, then the cluster's CTAs are summed in rank order by rank 0 through distributed
+        // shared memory: deterministic, no global scratch.
+        for (int idx = tid; idx < NM * 16 * 8 * NT; idx += GW * 32) {
+            const int n = idx % (8 * NT), r = (idx / (8 * NT)) % 16, mI = idx / (8 * NT * 16);
+            float sv = 0.0f;
+#pragma unroll
+            for (int w = 0; w < GW; ++w) sv += red[w][mI][r][n];
+            csum[mI][r][n] = sv;
+        }
+        block_sync<PERSIST>();
         asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
         if (krank == 0) {
             for (int idx = tid; idx < NM * 16 * 8 * NT; idx += GW * 32) {
@@ -176,8 +182,14 @@ __device__ __forceinline__ void tile_finish(float (&acc)[DUAL ? 2 : 1][NT][4], i
         if (krank != 0) return;
         block_sync<PERSIST>();
     }
-    // the epilogue reads the cluster total rank 0 published, or, without a K split, the block sum where it lies
-    const float (*fin)[16][RW] = (KS > 1) ? red[0] : csum;
+    // the epilogue reads the cluster total rank 0 published, or, without a K split, adds the warps' partials in warp order
+    auto total = [&](int mI, int r, int n) -> float {
+        if (KS > 1) return red[0][mI][r][n];
+        float sv = 0.0f;
+#pragma unroll
+        for (int w = 0; w < GW; ++w) sv += red[w][mI][r][n];
+        return sv;
+    };
     if (rope) {
         // thread (r < 8, n): partners a = row r (d0 = 8*sub + r) and b = row r + 8 (d0 + D/2)
         const int D = fz.head_dim, F = D / 2, tph = D / 16;
@@ -186,7 +198,7 @@ __device__ __forceinline__ void tile_finish(float (&acc)[DUAL ? 2 : 1][NT][4], i
         for (int idx = tid; idx < 8 * batch; idx += GW * 32) {
             const int n = idx / 8, r = idx % 8;
             const float sc = scaled ? scratch[n] : 1.0f;
-            const float a = fin[0][r][n] * sc, b = fin[0][r + 8][n] * sc;
+            const float a = total(0, r, n) * sc, b = total(0, r + 8, n) * sc;
             const int d0 = 8 * sub + r;
             if (pos < 0 || pos >= fz.ctx) continue;
             if (seg < 2) {
@@ -210,9 +222,9 @@ __device__ __forceinline__ void tile_finish(float (&acc)[DUAL ? 2 : 1][NT][4], i
     for (int idx = tid; idx < 16 * batch; idx += GW * 32) {
         int n = idx / 16, r = idx % 16;  // consecutive threads -> consecutive rows (contiguous in out[n][row])
         const float sc = scaled ? scratch[n] : 1.0f;
-        float y = fin[0][r][n] * sc;
+        float y = total(0, r, n) * sc;
         if (DUAL) {  // silu(a) * b = (a * 1/(1+exp(-a))) * b  (reference src/ir.rs:1500-1509)
-            const float ga = y, up = fin[NM - 1][r][n] * sc;
+            const float ga = y, up = total(NM - 1, r, n) * sc;
             float sig = 1.0f / (1.0f + expf(-ga));
             y = (ga * sig) * up;
         }
