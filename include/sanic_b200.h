@@ -321,6 +321,8 @@ enum { SANIC_X_CONST = 1,   /* value */
        SANIC_X_GATHER = 9,  /* arg = operand index; pops the index value: reads the operand at round(index) along its gather
                                axis (Gather: round, then a bounds check, src/interp.rs:378-379). An index out of range reads 0
                                and the next sanic_sync fails with SANIC_ERR_INVALID */
+       SANIC_X_GATHER_PAD = 10, /* the same read where an index out of range is padding: it reads 0 and is no error (a padded
+                               Reindex reads 0.0, src/interp.rs:270-430: padded windows of convolutions and sliding windows) */
        SANIC_X_ADD = 16, SANIC_X_SUB, SANIC_X_MUL, SANIC_X_DIV, SANIC_X_MAX, SANIC_X_MIN,
        SANIC_X_LT,          /* a < b as 1.0 / 0.0 */
        SANIC_X_NEG, SANIC_X_RECIP, SANIC_X_EXP, SANIC_X_LOG, SANIC_X_SQRT, SANIC_X_TANH, SANIC_X_SIN, SANIC_X_COS,

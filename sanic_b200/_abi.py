@@ -23,7 +23,7 @@ STAGE_FUSED, STAGE_ELEMENTWISE, STAGE_GATHER = 1, 2, 3
 OP_GEMV, OP_DECODE_ATTN, OP_ARGMAX, OP_RMSNORM, OP_EMBED, OP_ROPE_CACHE, OP_ADVANCE, OP_GENERIC = 1, 2, 3, 4, 5, 6, 7, 8
 OP_ATTN_FWD, OP_GEMM_RMSNORM, OP_ROPE = 9, 10, 11
 MAX_AXES, MAX_SLOTS = 6, 8
-X_CONST, X_LOAD, X_COORD, X_ITEM, X_A, X_B, X_F, X_RESULT, X_GATHER = 1, 2, 3, 4, 5, 6, 7, 8, 9
+X_CONST, X_LOAD, X_COORD, X_ITEM, X_A, X_B, X_F, X_RESULT, X_GATHER, X_GATHER_PAD = 1, 2, 3, 4, 5, 6, 7, 8, 9, 10
 (X_ADD, X_SUB, X_MUL, X_DIV, X_MAX, X_MIN, X_LT, X_NEG, X_RECIP, X_EXP, X_LOG, X_SQRT, X_TANH, X_SIN, X_COS, X_WHERE,
  X_ROUND) = range(16, 33)
 

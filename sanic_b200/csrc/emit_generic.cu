@@ -192,7 +192,8 @@ struct Gen {
                     if (op.arg < 0 || op.arg >= d->n_operands) { err = "generic emitter: operand index out of range"; st.push_back("0.0f"); }
                     else st.push_back(load(op.arg, s, indent));
                     break;
-                case SANIC_X_GATHER: {
+                case SANIC_X_GATHER:
+                case SANIC_X_GATHER_PAD: {
                     // index = round(value), half away from zero, then a bounds check (src/interp.rs:378-379); an index out
                     // of range reads 0 and leaves code 51 in the status word
                     if (op.arg < 0 || op.arg >= d->n_operands) { err = "generic emitter: operand index out of range"; st.push_back("0.0f"); break; }
@@ -209,7 +210,8 @@ struct Gen {
                     else if (o.dtype == SANIC_BF16) out << "widen_bf16(((const unsigned short*)" << base << ")" << at << ")";
                     else if (o.dtype == SANIC_U32) out << "(float)((const unsigned*)" << base << ")" << at;
                     else err = "generic emitter: operand dtype not supported";
-                    out << "; else atomicCAS(status, 0, 51);\n";
+                    if (op.op == SANIC_X_GATHER) out << "; else atomicCAS(status, 0, 51);\n";
+                    else out << ";\n";
                     st.push_back(t);
                     break;
                 }
@@ -326,7 +328,7 @@ bool reads_axis(const sanic_generic_desc* d, const sanic_expr& e, int axis) {
     for (int i = e.first; i < e.first + e.count && i < d->n_ops; ++i) {
         const sanic_expr_op& op = d->ops[i];
         if (op.op == SANIC_X_COORD && op.arg == axis) return true;
-        if ((op.op == SANIC_X_LOAD || op.op == SANIC_X_GATHER) && op.arg >= 0 && op.arg < d->n_operands &&
+        if ((op.op == SANIC_X_LOAD || op.op == SANIC_X_GATHER || op.op == SANIC_X_GATHER_PAD) && op.arg >= 0 && op.arg < d->n_operands &&
             d->operands[op.arg].stride[axis] != 0) return true;
     }
     return false;

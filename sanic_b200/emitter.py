@@ -53,6 +53,7 @@ def const(v) -> E: return E(abi.X_CONST, value=v)
 def load(operand: int) -> E: return E(abi.X_LOAD, arg=operand)
 def coord(axis: int) -> E: return E(abi.X_COORD, arg=axis)
 def gather(operand: int, index) -> E: return E(abi.X_GATHER, arg=operand, kids=(E.of(index),))
+def gather_pad(operand: int, index) -> E: return E(abi.X_GATHER_PAD, arg=operand, kids=(E.of(index),))   # out of range reads 0
 def item(i: int) -> E: return E(abi.X_ITEM, arg=i)
 def A(i: int) -> E: return E(abi.X_A, arg=i)
 def B(i: int) -> E: return E(abi.X_B, arg=i)
@@ -159,19 +160,30 @@ def attention(batch, q_heads, kv_heads, q_len, kv_len, head_dim, v_dim, scale, d
     return (batch, kv_heads, rep, L, Ev), S, [q, k, v], car
 
 
-def conv2d(batch, channels, height, width, out_channels, kh, kw, stride=1, dilation=1, dtype=abi.F32):
-    """y[n, co, oy, ox] = sum over (ci, ky, kx) of x[n, ci, oy*stride + ky*dilation, ox*stride + kx*dilation] * w[co, ci, ky, kx]:
-    the convolution as the reference states it, a window view of x times a broadcast view of w reduced over three axes at once
-    (no patch matrix is materialised: an implicit GEMM whose K axis is the window). No padding: a padded convolution pads its
-    input first. Returns (grid, window, operands, carrier); buffers are x [N,C,H,W] and w [CO,C,KH,KW]."""
-    oh = (height - dilation * (kh - 1) - 1) // stride + 1
-    ow = (width - dilation * (kw - 1) - 1) // stride + 1
+def conv2d(batch, channels, height, width, out_channels, kh, kw, stride=1, dilation=1, padding=0, dtype=abi.F32):
+    """y[n, co, oy, ox] = sum over (ci, ky, kx) of x[n, ci, oy*stride + ky*dilation - padding, ox*stride + kx*dilation - padding]
+    * w[co, ci, ky, kx], taps outside the input reading 0: the convolution as the reference states it, a (padded) window view of
+    x times a broadcast view of w reduced over three axes at once (no patch matrix is materialised: an implicit GEMM whose K axis
+    is the window). Returns (grid, window, operands, carrier); buffers are x [N,C,H,W] and w [CO,C,KH,KW]."""
+    oh = (height + 2 * padding - dilation * (kh - 1) - 1) // stride + 1
+    ow = (width + 2 * padding - dilation * (kw - 1) - 1) // stride + 1
     if oh <= 0 or ow <= 0:
         raise ValueError("the window does not fit the input")
-    x = Operand(0, dtype, [channels * height * width, 0, stride * width, stride],
-                stream_strides=[height * width, dilation * width, dilation])
     w = Operand(1, dtype, [0, channels * kh * kw, 0, 0], stream_strides=[kh * kw, kw, 1])
-    return (batch, out_channels, oh, ow), (channels, kh, kw), [x, w], carrier_sum(load(0) * load(1))
+    grid, window = (batch, out_channels, oh, ow), (channels, kh, kw)
+    if padding == 0:
+        x = Operand(0, dtype, [channels * height * width, 0, stride * width, stride],
+                    stream_strides=[height * width, dilation * width, dilation])
+        return grid, window, [x, w], carrier_sum(load(0) * load(1))
+    # padded: the tap's position inside the image plane is computed from the output and window coordinates and read through
+    # a padded gather; a tap whose row or column falls outside reads 0 whatever element its flat index happens to name
+    x = Operand(0, dtype, [channels * height * width, 0, 0, 0], stream_strides=[height * width, 0, 0],
+                gather_stride=1, gather_extent=height * width)
+    iy = coord(2) * float(stride) + coord(len(grid) + 3) * float(dilation) - float(padding)
+    ix = coord(3) * float(stride) + coord(len(grid) + 4) * float(dilation) - float(padding)
+    inside = (const(-1.0) < iy) * (iy < float(height)) * (const(-1.0) < ix) * (ix < float(width))
+    tap = where(inside, gather_pad(0, iy * float(width) + ix), 0.0)
+    return grid, window, [x, w], carrier_sum(tap * load(1))
 
 
 def pool2d(batch, channels, height, width, kh, kw, stride=None, kind="max", dtype=abi.F32):

@@ -25,7 +25,7 @@ _NAMES = {abi.X_CONST: "const", abi.X_LOAD: "load", abi.X_COORD: "coord", abi.X_
           abi.X_F: "f", abi.X_RESULT: "result", abi.X_ADD: "add", abi.X_SUB: "sub", abi.X_MUL: "mul", abi.X_DIV: "div",
           abi.X_MAX: "max", abi.X_MIN: "min", abi.X_LT: "lt", abi.X_NEG: "neg", abi.X_RECIP: "recip", abi.X_EXP: "exp",
           abi.X_LOG: "log", abi.X_SQRT: "sqrt", abi.X_TANH: "tanh", abi.X_SIN: "sin", abi.X_COS: "cos", abi.X_WHERE: "where",
-          abi.X_GATHER: "gather"}
+          abi.X_GATHER: "gather", abi.X_GATHER_PAD: "gather_pad"}
 
 
 def prog(e):
@@ -184,6 +184,8 @@ def all_descriptions():
     out["convolution over a three-axis window"] = em.Description(g, ops, carrier=car, stream=win, lanes=32)
     g, win, ops, car = em.pool2d(2, 3, 8, 8, 2, 2)
     out["pooling over a two-axis window"] = em.Description(g, ops, carrier=car, stream=win)
+    g, win, ops, car = em.conv2d(1, 2, 6, 6, 3, 3, 3, padding=1)
+    out["padded convolution"] = em.Description(g, ops, carrier=car, stream=win, lanes=32)
     return out
 
 
@@ -661,6 +663,24 @@ def test_generic_convolution_is_an_implicit_gemm_over_a_window(dev, dtype, lanes
     assert want.shape == grid
     got = run_kernel(dev, em.Description(grid, ops, carrier=car, stream=win, lanes=lanes),
                      [on_device(dev, x, dtype), on_device(dev, w, dtype)], grid)
+    assert nerr(got, want) <= F32_TOL
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("lanes,stride,padding", [(32, 1, 1), (1, 2, 2)])
+def test_generic_padded_convolution(dev, lanes, stride, padding):
+    """Taps outside the input read 0 through the padded gather (a padded Reindex reads 0.0 in the reference's interpreter),
+    and raise no status: the run must leave the context clean."""
+    N, C, H, W, CO, KH, KW = 2, 3, 7, 6, 4, 3, 3
+    g = orc.Xorshift(0x9AD)
+    x, w = orc.round_to(orc.DT_F32, g.normal(N, C, H, W)), orc.round_to(orc.DT_F32, 0.3 * g.normal(CO, C, KH, KW))
+    grid, win, ops, car = em.conv2d(N, C, H, W, CO, KH, KW, stride=stride, padding=padding)
+    xp = np.pad(x, ((0, 0), (0, 0), (padding, padding), (padding, padding)))
+    want = np.einsum("nchwyx,ocyx->nohw", _windows(xp, KH, KW, stride), w)
+    assert want.shape == grid
+    d = em.Description(grid, ops, carrier=car, stream=win, lanes=lanes)
+    assert "atomicCAS(status, 0, 51)" not in em.source(d)
+    got = run_kernel(dev, d, [on_device(dev, x, abi.F32), on_device(dev, w, abi.F32)], grid)      # run_kernel syncs: no status raised
     assert nerr(got, want) <= F32_TOL
 
 
