@@ -25,6 +25,11 @@
 // acquire-poll. Every spin (grid barrier, ring mbarriers) is bounded: a block that gives up raises the abort
 // word, records a code in the context's status word and leaves; the others see the abort word or run out of
 // spins themselves, and no block exits while a bulk copy into its shared memory is still in flight.
+//
+// The same producer and consumer halves also run as a kernel of their own, one contraction per launch
+// (gemv_ring_kernel, used by launch lists at batch 9-16): one producer warp, activations read through L1 instead of
+// staged, and for bf16 blocks small enough that two share an SM, so that the next kernel's producers stream weights
+// while this kernel drains.
 #include "decode_step.cuh"
 
 #include <algorithm>
