@@ -259,6 +259,16 @@ def suite(dev, torch, hbm_peak, tf_peak, quick, only=None, c2_shape=(4096, 2048,
             del ws
         del w
     del x
+    if only is not None and want("c2_profile"):
+        # clock counters of the pair tile with A through registers (one launch, SM pair 0): what its roles wait for
+        M, K, N = c2_shape
+        x = torch.randn(M, K, generator=g, device=td).to(torch.bfloat16)
+        gam = (1.0 + 0.1 * torch.randn(K, generator=g, device=td)).to(torch.bfloat16)
+        w = (0.02 * torch.randn(N, K, generator=g, device=td)).to(torch.bfloat16)
+        for _ in range(3):
+            prof, _y = dev.gemm_rmsnorm_pair_profile(x, gam, w, w_is_nk=True)
+        out["c2_pair_registers_profile"] = {k: ({a: round(b, 1) for a, b in v.items()} if isinstance(v, dict) else round(v, 1)) for k, v in prof.items()}
+        del x, w
     # config 3: causal flash attention with RoPE, B8 Hq32 Hkv8 D64 S4096 bf16 (+ 1024-token window)
     Bq, Hq3, Hk3, S3 = c3_shape[0], 32, 8, c3_shape[1]
     c3_scale = (Bq * S3 * S3) / (8.0 * 4096 * 4096)

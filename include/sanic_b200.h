@@ -208,6 +208,13 @@ int32_t sanic_gemm_rmsnorm(sanic_ctx* ctx, const sanic_gemm_rmsnorm_params* p, v
  * rewrite sum (x*g)*W = sum x*(g*W). sanic_gemm_rmsnorm with gamma == NULL then takes w_out as W: the activations go
  * to the tensor core as loaded and only sum x^2 is taken from them, which removes the per-stage transform from the
  * pipeline's latency. One factor is rounded to bf16 either way (x*g there, g*W here). */
+/* One launch of the 256 x 256 pair tile with A brought in through registers, with clock counters on in the roles of SM pair 0
+ * (a finer view than the per-kernel times of the reference's SANIC_DEBUG=4, src/compile.rs:1147-1346): out[0] k-blocks the
+ * MMA thread issued, [1] its clocks over its loop, [2] of those, clocks reading the progress counters, [3] counter reads,
+ * [4] clocks waiting for a free accumulator; [5] the B producer's clocks waiting for a free slot; transform warp 0 of the
+ * leader [6..11] and of the peer [12..17]: its k-blocks, then clocks in arithmetic (including the wait for its loads),
+ * waiting for the slot, storing, in the proxy fence, in the arrival. y is written as by sanic_gemm_rmsnorm. Synchronises. */
+int32_t sanic_gemm_rmsnorm_pair_profile(sanic_ctx* ctx, const sanic_gemm_rmsnorm_params* p, void* stream, uint64_t* out);
 int32_t sanic_gemm_prescale_weights(sanic_ctx* ctx, const void* gamma, const void* w, void* w_out, int32_t N, int32_t K,
                                     int32_t w_is_nk, void* stream);
 

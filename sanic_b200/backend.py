@@ -236,6 +236,27 @@ class CudaDevice:
         self._check(self.lib.sanic_gemm_rmsnorm(self.h, C.byref(p), self.stream()), "gemm_rmsnorm")
         return y
 
+    def gemm_rmsnorm_pair_profile(self, x, gamma, w, eps=1e-5, w_is_nk=True):
+        """One launch of the pair tile with A through registers with its clock counters on: a dict of clocks per k-block for
+        the MMA thread, the B producer and transform warp 0 of each CTA of SM pair 0 (see sanic_gemm_rmsnorm_pair_profile)."""
+        M, K = x.shape
+        N = w.shape[0] if w_is_nk else w.shape[1]
+        y = self.empty((M, N), torch.bfloat16)
+        p = abi.GemmRmsnormParams()
+        p.x, p.gamma, p.w, p.y = x.data_ptr(), (gamma.data_ptr() if gamma is not None else None), w.data_ptr(), y.data_ptr()
+        p.M, p.N, p.K, p.w_is_nk, p.eps, p.out_dtype = M, N, K, int(w_is_nk), float(eps), abi.BF16
+        out = (C.c_uint64 * 18)()
+        self._check(self.lib.sanic_gemm_rmsnorm_pair_profile(self.h, C.byref(p), self.stream(), out), "gemm_rmsnorm_pair_profile")
+        v = [int(t) for t in out]
+        n = max(v[0], 1)
+        res = {"k_blocks": v[0], "mma_thread_clocks_per_kb": v[1] / n, "of_which_reading_counters": v[2] / n,
+               "counter_reads_per_kb": v[3] / n, "waiting_for_accumulator_total": v[4], "b_producer_wait_per_kb": v[5] / n}
+        for name, o in (("leader", 6), ("peer", 12)):
+            m = max(v[o], 1)
+            res["transform_warp_" + name] = {"k_blocks": v[o], "arithmetic": v[o + 1] / m, "slot_wait": v[o + 2] / m,
+                                             "stores": v[o + 3] / m, "proxy_fence": v[o + 4] / m, "arrival": v[o + 5] / m}
+        return res, y
+
     # ── K2c: decode-batch contraction ──
     def gemv_params(self, x, weights, outs, scales=None, epilogue=abi.EPI_STORE, residual=None, out_dtype=abi.F32):
         batch, K = x.shape

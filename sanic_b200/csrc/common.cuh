@@ -26,6 +26,8 @@ struct sanic_ctx {
     // nonzero code here, the host reads it without a synchronising copy
     int* status_host = nullptr;
     int* status_dev = nullptr;
+    // device buffer of the GEMM's clock counters, non-null only inside sanic_gemm_rmsnorm_pair_profile
+    unsigned long long* gemm_prof = nullptr;
 };
 
 namespace sanic {

@@ -799,10 +799,17 @@ __device__ __forceinline__ void umma2_commit_both(uint64_t* bar) {
                  ::"r"(smem_u32(bar)), "h"(mask) : "memory");
 }
 
+// PROF: the roles of pair 0 count clocks in registers and write them to `prof` when they leave (what the profile entry
+// point reports): [0] k-blocks issued, [1] the MMA thread's clocks over its whole loop, [2] of those, clocks reading the
+// progress counters, [3] counter reads, [4] clocks waiting for a free accumulator; [5] the B producer's clocks waiting for a
+// free slot; for transform warp 0 of the leader [6..11] and of the peer [12..17]: its k-blocks, clocks in arithmetic (with
+// the wait for its loads), waiting for the slot, storing, in the proxy fence, in the arrival.
+template <bool PROF>
 __global__ void __launch_bounds__(P_NTHREADS, 1)
 gemm_rmsnorm_pair_reg_kernel(const __grid_constant__ CUtensorMap map_b, const __grid_constant__ CUtensorMap map_y,
                              const uint16_t* __restrict__ x, const uint16_t* __restrict__ gamma, void* __restrict__ y,
-                             int M, int N, int K, int w_is_nk, float eps, int out_dtype, int* err, int gamma_bytes, int bulk_store) {
+                             int M, int N, int K, int w_is_nk, float eps, int out_dtype, int* err, int gamma_bytes, int bulk_store,
+                             unsigned long long* prof) {
     extern __shared__ unsigned char smem_dyn[];
     const uint32_t raw = smem_u32(smem_dyn);
     const uint32_t base = (raw + 1023u) & ~1023u;
@@ -848,10 +855,13 @@ gemm_rmsnorm_pair_reg_kernel(const __grid_constant__ CUtensorMap map_b, const __
         if (lane == 0) {
             int stage = 0; uint32_t phase = 1;
             bool ok = true;
+            long long t_wait = 0;
             for (int t = pair; t < tiles && ok; t += n_pairs) {
                 const int n0 = (t / m_tiles) * BN + (int)rank * (BN / 2);
                 for (int kb = 0; kb < kblocks; ++kb) {
+                    const long long c0 = PROF ? clock64() : 0;
                     ok = mbar_wait_p2<false>(&sh->empty[stage], phase, sh, err, 21);
+                    if (PROF) t_wait += clock64() - c0;
                     if (!ok) break;
                     const uint32_t sb = b_ring + stage * PB_BYTES;
                     const uint32_t bar = map_to_rank(smem_u32(&sh->full_b[stage]), 0);
@@ -866,6 +876,7 @@ gemm_rmsnorm_pair_reg_kernel(const __grid_constant__ CUtensorMap map_b, const __
                     if (++stage == PB_SLOTS) { stage = 0; phase ^= 1; }
                 }
             }
+            if (PROF && blockIdx.x == 0) prof[5] = (unsigned long long)t_wait;
         }
     } else if (warp == 1) {
         // ── MMA issuer: the leader CTA only ──
@@ -876,9 +887,13 @@ gemm_rmsnorm_pair_reg_kernel(const __grid_constant__ CUtensorMap map_b, const __
             int use = 0;
             bool ok = true;
             uint32_t q = 0, avail = 0;
+            long long t_read = 0, n_read = 0, t_acc = 0;
+            const long long t_begin = PROF ? clock64() : 0;
             for (int t = pair; t < tiles && ok; t += n_pairs, ++use) {
                 const int ab = use & 1;
+                const long long c9 = PROF ? clock64() : 0;
                 ok = mbar_wait_p2<true>(&sh->tmem_empty[ab], ((use >> 1) & 1) ^ 1, sh, err, 22);
+                if (PROF) t_acc += clock64() - c9;
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t acc = tmem + (uint32_t)ab * BN;
@@ -888,6 +903,7 @@ gemm_rmsnorm_pair_reg_kernel(const __grid_constant__ CUtensorMap map_b, const __
                         // this thread about 210 clocks, a shared-memory load 55): the watcher threads below turn barrier
                         // completions into counters, and one read often covers several k-blocks
                         uint32_t it = 0;
+                        const long long c0 = PROF ? clock64() : 0;
                         for (;;) {
                             uint32_t pa, pp, pb;
                             asm volatile("ld.acquire.cta.shared.u32 %0, [%1];" : "=r"(pa) : "r"(smem_u32(&sh->seen_a)) : "memory");
@@ -899,6 +915,7 @@ gemm_rmsnorm_pair_reg_kernel(const __grid_constant__ CUtensorMap map_b, const __
                             if (++it > P_SPIN_LIMIT || ((it & 1023u) == 0 && sh->abort_flag)) { if (it > P_SPIN_LIMIT) { sh->abort_flag = 1; atomicCAS(err, 0, 23); } ok = false; break; }
                         }
                         if (!ok) break;
+                        if (PROF) { t_read += clock64() - c0; ++n_read; }
                     }
                     const uint32_t sb = b_ring + stage * PB_BYTES;
                     const uint64_t adesc = make_desc(base + stage * A_BYTES, 16, 1024);
@@ -913,6 +930,10 @@ gemm_rmsnorm_pair_reg_kernel(const __grid_constant__ CUtensorMap map_b, const __
                     if (++stage == PB_SLOTS) { stage = 0; phase ^= 1; }
                 }
                 if (ok) umma2_commit_both(&sh->tmem_full[ab]);
+            }
+            if (PROF && blockIdx.x == 0) {
+                prof[0] = q; prof[1] = (unsigned long long)(clock64() - t_begin); prof[2] = (unsigned long long)t_read;
+                prof[3] = (unsigned long long)n_read; prof[4] = (unsigned long long)t_acc;
             }
         }
     } else if (warp == 2 || warp == 3) {
@@ -988,10 +1009,12 @@ gemm_rmsnorm_pair_reg_kernel(const __grid_constant__ CUtensorMap map_b, const __
             return true;
         };
         int flushed = 0;
+        long long t_math = 0, t_slot = 0, t_store = 0, t_fence = 0, t_arrive = 0, n_own = 0;
         fetch();
         while (s_use < my_tiles && ok) {
             while (flushed < s_use && ok) { ok = flush(flushed); ++flushed; }
             if (!ok) break;
+            const long long c0 = PROF ? clock64() : 0;
             // multiply and square while the slot may still be busy: only the stores wait for it
             uint4 gv = make_uint4(0, 0, 0, 0);
             if (scaled) gv = *(const uint4*)(gsm + s_kb * BK + c * 8);
@@ -1008,16 +1031,24 @@ gemm_rmsnorm_pair_reg_kernel(const __grid_constant__ CUtensorMap map_b, const __
                 }
                 buf[j] = make_uint4(xs[0], xs[1], xs[2], xs[3]);
             }
+            const long long c1 = PROF ? clock64() : 0;
             ok = warp_wait_p2<false>(&sh->empty[stage], phase, sh, err, 24, lane);      // the pair's MMAs on this slot retired
             if (!ok) break;
+            const long long c2 = PROF ? clock64() : 0;
             const uint32_t slot = base + stage * A_BYTES + (uint32_t)r0 * 128u + swz;
 #pragma unroll
             for (int j = 0; j < RPT; ++j)
                 asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(slot + (uint32_t)(4 * WPG * j) * 128u),
                              "r"(buf[j].x), "r"(buf[j].y), "r"(buf[j].z), "r"(buf[j].w) : "memory");
+            const long long c3 = PROF ? clock64() : 0;
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // generic writes -> visible to the tensor core's reads
+            const long long c4 = PROF ? clock64() : 0;
             __syncwarp();
             if (lane == 0) mbar_arrive(&sh->ready[stage]);       // this CTA's barrier; its watcher tells the leader
+            if (PROF) {
+                const long long c5 = clock64();
+                t_math += c1 - c0; t_slot += c2 - c1; t_store += c3 - c2; t_fence += c4 - c3; t_arrive += c5 - c4; ++n_own;
+            }
             fetch();                                   // the next of this group's k-blocks, in flight until its slot frees
             s_kb += P2_GROUPS;
             while (s_kb >= kblocks) { s_kb -= kblocks; ++s_use; }
@@ -1025,6 +1056,11 @@ gemm_rmsnorm_pair_reg_kernel(const __grid_constant__ CUtensorMap map_b, const __
             if (stage >= PA_SLOTS) { stage -= PA_SLOTS; phase ^= 1; }
         }
         while (ok && flushed < my_tiles) { ok = flush(flushed); ++flushed; }
+        if (PROF && blockIdx.x < 2 && warp == 4 && lane == 0) {
+            unsigned long long* o = prof + 6 + 6 * blockIdx.x;
+            o[0] = (unsigned long long)n_own; o[1] = (unsigned long long)t_math; o[2] = (unsigned long long)t_slot;
+            o[3] = (unsigned long long)t_store; o[4] = (unsigned long long)t_fence; o[5] = (unsigned long long)t_arrive;
+        }
     } else if (warp >= 20) {
         // ── epilogue (both CTAs): this CTA's 128 rows of the 256 x 256 tile; two warps per lane quarter, 128 columns each ──
         const int q = warp & 3;
@@ -1213,7 +1249,7 @@ extern "C" int32_t sanic_gemm_rmsnorm(sanic_ctx* ctx, const sanic_gemm_rmsnorm_p
     const char* force = getenv("SANIC_GEMM_PAIR");
     // gamma == NULL: the weights were pre-scaled with sanic_gemm_prescale_weights (only the pair kernel has that form)
     const bool prescaled = (p->gamma == nullptr);
-    const bool use_pair = prescaled || (force ? (force[0] == '1' || force[0] == '2') : (p->M >= 4 * BM && pair_tiles >= ctx->sm_count / 2));
+    const bool use_pair = prescaled || ctx->gemm_prof || (force ? (force[0] == '1' || force[0] == '2') : (p->M >= 4 * BM && pair_tiles >= ctx->sm_count / 2));
     if (use_pair) {
         // the 256 x 256 tile on a pair of SMs: B's map has a 128-row box (this CTA's half)
         if (p->w_is_nk) {
@@ -1231,9 +1267,10 @@ extern "C" int32_t sanic_gemm_rmsnorm(sanic_ctx* ctx, const sanic_gemm_rmsnorm_p
             rc = encode_2d(ctx, &map_y, p->y, (uint64_t)p->N, (uint64_t)p->M, 32, 32, CU_TENSOR_MAP_SWIZZLE_64B);
             if (rc != SANIC_OK) return rc;
         }
-        const bool reg_path = force && force[0] == '2';
+        const bool reg_path = ctx->gemm_prof || (force && force[0] == '2');
         if (reg_path) {
-            SANIC_CUDA_CHECK(ctx, cudaFuncSetAttribute(gemm_rmsnorm_pair_reg_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, psmem));
+            SANIC_CUDA_CHECK(ctx, cudaFuncSetAttribute(gemm_rmsnorm_pair_reg_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, psmem));
+            SANIC_CUDA_CHECK(ctx, cudaFuncSetAttribute(gemm_rmsnorm_pair_reg_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, psmem));
         }
         SANIC_CUDA_CHECK(ctx, cudaFuncSetAttribute(gemm_rmsnorm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, psmem));
         const int ptiles = ((p->M + 2 * BM - 1) / (2 * BM)) * ((p->N + BN - 1) / BN);
@@ -1250,9 +1287,14 @@ extern "C" int32_t sanic_gemm_rmsnorm(sanic_ctx* ctx, const sanic_gemm_rmsnorm_p
         if (pairs > ctx->sm_count / 2) pairs = ctx->sm_count / 2;
         cfg.gridDim = dim3(2 * pairs);
         if (reg_path) {
-            cudaError_t le = cudaLaunchKernelEx(&cfg, gemm_rmsnorm_pair_reg_kernel, map_b, map_y, (const uint16_t*)p->x, (const uint16_t*)p->gamma, p->y,
-                                                (int)p->M, (int)p->N, (int)p->K, (int)p->w_is_nk, p->eps, (int)p->out_dtype, ctx->status_dev,
-                                                gamma_bytes, bulk_store);
+            unsigned long long* prof = ctx->gemm_prof;      // set only by sanic_gemm_rmsnorm_pair_profile, for the one launch it makes
+            cudaError_t le = prof
+                ? cudaLaunchKernelEx(&cfg, gemm_rmsnorm_pair_reg_kernel<true>, map_b, map_y, (const uint16_t*)p->x, (const uint16_t*)p->gamma, p->y,
+                                     (int)p->M, (int)p->N, (int)p->K, (int)p->w_is_nk, p->eps, (int)p->out_dtype, ctx->status_dev,
+                                     gamma_bytes, bulk_store, prof)
+                : cudaLaunchKernelEx(&cfg, gemm_rmsnorm_pair_reg_kernel<false>, map_b, map_y, (const uint16_t*)p->x, (const uint16_t*)p->gamma, p->y,
+                                     (int)p->M, (int)p->N, (int)p->K, (int)p->w_is_nk, p->eps, (int)p->out_dtype, ctx->status_dev,
+                                     gamma_bytes, bulk_store, prof);
             if (le != cudaSuccess) return sanic_fail(ctx, SANIC_ERR_CUDA, std::string("gemm_rmsnorm (pair, registers): ") + cudaGetErrorString(le));
             return SANIC_OK;
         }
@@ -1275,3 +1317,21 @@ extern "C" int32_t sanic_gemm_rmsnorm(sanic_ctx* ctx, const sanic_gemm_rmsnorm_p
 
 
 
+
+// One launch of the pair tile with A through registers with its clock counters on (see the kernel): `out` receives 18
+// numbers. The launch is a real one (y is written); it synchronises the stream.
+extern "C" int32_t sanic_gemm_rmsnorm_pair_profile(sanic_ctx* ctx, const sanic_gemm_rmsnorm_params* p, void* stream, uint64_t* out) {
+    if (!ctx || !p || !out) return SANIC_ERR_INVALID;
+    sanic_set_device(ctx);
+    unsigned long long* dev = nullptr;
+    SANIC_CUDA_CHECK(ctx, cudaMalloc(&dev, 18 * sizeof(unsigned long long)));
+    cudaMemsetAsync(dev, 0, 18 * sizeof(unsigned long long), (cudaStream_t)stream);
+    ctx->gemm_prof = dev;
+    int32_t rc = sanic_gemm_rmsnorm(ctx, p, stream);
+    ctx->gemm_prof = nullptr;
+    if (rc == SANIC_OK) rc = sanic_sync(ctx, stream);
+    if (rc == SANIC_OK && cudaMemcpy(out, dev, 18 * sizeof(unsigned long long), cudaMemcpyDeviceToHost) != cudaSuccess)
+        rc = sanic_fail(ctx, SANIC_ERR_CUDA, "gemm profile: copy failed");
+    cudaFree(dev);
+    return rc;
+}

@@ -524,6 +524,23 @@ def test_gemm_rmsnorm_both_tile_forms(dev, form, monkeypatch):
     _gemm_case(dev, 512, 8192, 256, True)                                   # the longest K: staging does not fit, direct stores
 
 
+def test_gemm_rmsnorm_pair_profile_counts_clocks_and_computes(dev):
+    """The profile entry point runs the pair tile with A through registers with its clock counters on: the result is the
+    contraction's, and the counters are those of a run (every k-block issued, clocks in every role)."""
+    M, K, N = 512, 512, 512
+    x, xv = bf16t(normal(201, M, K), dev)
+    g, gv = bf16t(1.0 + 0.1 * normal(202, K), dev)
+    w, wv = bf16t(0.02 * normal(203, N, K), dev)
+    prof, y = dev.gemm_rmsnorm_pair_profile(x, g, w, w_is_nk=True)
+    assert nerr(y.float().cpu().numpy(), orc.rmsnorm_gemm(xv, gv, wv, eps=1e-5, w_is_nk=True)) <= BF16_TOL
+    kb = K // 64
+    assert prof["k_blocks"] == kb * 1                              # pair 0 owns one of the four 256 x 256 tiles
+    assert prof["mma_thread_clocks_per_kb"] > 100 and prof["b_producer_wait_per_kb"] >= 0
+    for side in ("leader", "peer"):
+        t = prof["transform_warp_" + side]
+        assert t["k_blocks"] == kb // 4 and t["arithmetic"] > 0 and t["stores"] > 0
+
+
 @pytest.mark.parametrize("w_is_nk", [True, False])
 def test_gemm_rmsnorm_with_prescaled_weights(dev, w_is_nk):
     # weights bound once: W' = bf16(W * g) along K, then the contraction with gamma = None; the rewrite
