@@ -278,6 +278,12 @@ def suite(dev, torch, hbm_peak, tf_peak, quick, only=None, c2_shape=(4096, 2048,
     table = dev.rope_table([math.exp(i * (-math.log(500000.0) / 32)) for i in range(32)], S3)
     qr, kr = torch.empty_like(q3), torch.empty_like(k3)
     med_r, _ = time_events(lambda: (dev.rope_bf16(q3, table, out=qr), dev.rope_bf16(k3, table, out=kr)), 10, 3, torch)
+    if only is not None and "c3_profile" in only:
+        # clock counters of the flash forward's softmax warps and MMA thread (one launch, CTA 0)
+        for _ in range(3):
+            prof, _o = dev.attn_fwd_bf16_profile(qr, kr, v3, causal=True)
+        out["c3_flash_profile"] = {k: {a: ({x: round(y, 1) for x, y in b.items()} if isinstance(b, dict) else b) for a, b in v.items()}
+                                   for k, v in prof.items()}
     for name, win, fl in (("causal", 0, 5.498e11 * c3_scale), ("causal_window1024", 1024, 2.405e11 * c3_scale)):
         if not want("c3"):
             continue
@@ -297,7 +303,9 @@ def suite(dev, torch, hbm_peak, tf_peak, quick, only=None, c2_shape=(4096, 2048,
         import ctypes as C
         pr = {}
         for warps in (4, 8):       # 16 warps of this probe (128 live values per lane) do not fit one SM's register file
-            for mode, label in enumerate(("ex2", "ex2+fma", "ex2+fma+sum", "ex2+fma+sum+pack", "quarter_on_fma_pipe", "half_on_fma_pipe")):
+            for mode, label in enumerate(("ex2", "ex2+fma", "ex2+fma+sum", "ex2+fma+sum+pack", "quarter_on_fma_pipe", "half_on_fma_pipe",
+                                          "f16x2_ex2+fma", "f16x2_ex2+fma+sum+bf16_pack", "f16x2_ex2+fma+sum",
+                                          "ex2+fma+sum+pack+max3", "ex2+fma+sum+pack+two_max")):
                 rate, clk = C.c_double(0.0), C.c_double(0.0)
                 dev._check(dev.lib.sanic_probe_sfu(dev.h, warps, mode, 200, dev.stream(), C.byref(rate), C.byref(clk)), "probe_sfu")
                 pr[f"warps{warps}_{label}"] = {"exp_per_clk_per_sm": round(rate.value, 2), "clk_per_128_per_lane": clk.value}

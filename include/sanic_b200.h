@@ -70,7 +70,10 @@ int32_t sanic_specs(sanic_ctx* ctx, sanic_device_specs* out);
  * reference's in-context timing measures (src/compile.rs:1348-1630). Both probes are tiny, bounded kernels.
  * sanic_probe_sfu: `ex2.approx` per clock per SM with `warps_per_sm` resident warps (one CTA per SM); mode 0 = the
  * exponentials alone, 1 = + the scale-and-shift FMA per element, 2 = + the row-sum add, 3 = + the bf16x2 pack: the inner
- * loop of the online-softmax warps; 4 / 5 = mode 3 with every fourth / second pair of exponentials on the FMA pipe (cubic). *clk_per_128_per_warp (optional) is the raw figure: clocks per 128 elements per lane.
+ * loop of the online-softmax warps; 4 / 5 = mode 3 with every fourth / second pair of exponentials on the FMA pipe (cubic);
+ * 6-8 = a pair's exponentials as one packed f16x2 instruction (6: with the scale FMA and the conversion only, 7: + unpack,
+ * row sum and bf16x2 pack, 8: + unpack and row sum, result kept as f16); 9 / 10 = mode 3 with the row maximum in the same loop
+ * (one three-input max per pair / two two-input ones). *clk_per_128_per_warp (optional) is the raw figure: clocks per 128 elements per lane.
  * sanic_probe_stream: GB/s of a read-only sweep of `buffer` (best of `repeats`), the rate an HBM-bound fold is held to. */
 int32_t sanic_probe_sfu(sanic_ctx* ctx, int32_t warps_per_sm, int32_t mode, int32_t iters, void* stream, double* exp_per_clk_per_sm,
                         double* clk_per_128_per_warp);
@@ -129,6 +132,16 @@ int32_t sanic_attn_fwd_f32(sanic_ctx* ctx, const sanic_attn_params* p, void* str
 /* bf16 storage, tcgen05 contractions with accumulators in tensor memory, f32 carrier in registers. E = Ev = 64 (the
  * head size of the prefill configuration); any other head size is refused with SANIC_ERR_UNSUPPORTED. */
 int32_t sanic_attn_fwd_bf16(sanic_ctx* ctx, const sanic_attn_params* p, void* stream);
+/* One launch of the same kernel with clock counters on in CTA 0 (a finer view than the per-kernel times of the reference's
+ * SANIC_DEBUG=4, src/compile.rs:1147-1346). For query tile t (0, 1) of the CTA's work items, from the softmax warp of the
+ * tile's rows 0-31, out[10t + i] = clocks spent, summed over its key tiles: [0] waiting for the scores, [1] loading them
+ * and taking the row maximum, [2] the first 64 exponentials, [3] waiting for the previous PV product, [4] rescaling O,
+ * [5] storing P and the second 64 exponentials, [6] the store wait and the arrival, [7] epilogues and item switches;
+ * [8] key tiles folded, [9] clocks over all. For the tile's MMA thread, m = 20 + 8t: out[m] its polls, [m+1] of those
+ * without anything to issue, [m+2] its clocks, [m+3] score tiles issued, and its clocks in [m+4] barrier tests and idle
+ * sleeps, [m+5] issuing the score products (four MMAs and a commit each), [m+6] the value products (eight MMAs and two
+ * commits), [m+7] item switches. out (36 words, host memory) is written; the attention output too. Synchronises. */
+int32_t sanic_attn_fwd_bf16_profile(sanic_ctx* ctx, const sanic_attn_params* p, void* stream, uint64_t* out);
 
 /* Split-KV decode (one query token per sequence). Stage 1 folds contiguous chunks of
  * the key axis into raw (m, l, o) accumulators exactly as run_carrier_split chunks it

@@ -214,6 +214,7 @@ PROTOTYPES = {
     "sanic_attn_decode_suggest_splits": (i32, [vp, i32, i32, i32, i64]),
     "sanic_carrier_merge": (i32, [vp, vp, i32, i32, i32, vp, vp, i32, vp]),
     "sanic_gemm_rmsnorm": (i32, [vp, C.POINTER(GemmRmsnormParams), vp]),
+    "sanic_attn_fwd_bf16_profile": (i32, [vp, C.POINTER(AttnParams), vp, C.POINTER(C.c_uint64)]),
     "sanic_gemm_rmsnorm_pair_profile": (i32, [vp, C.POINTER(GemmRmsnormParams), vp, C.POINTER(C.c_uint64)]),
     "sanic_gemm_prescale_weights": (i32, [vp, vp, vp, vp, i32, i32, i32, vp]),
     "sanic_gemv": (i32, [vp, C.POINTER(GemvParams), vp]),

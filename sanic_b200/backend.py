@@ -137,6 +137,31 @@ class CudaDevice:
         self._check(self.lib.sanic_attn_fwd_bf16(self.h, C.byref(p), self.stream()), "attn_fwd_bf16")
         return out
 
+    def attn_fwd_bf16_profile(self, q, k, v, causal=False, window=0, scale=None):
+        """One launch of the flash forward with its clock counters on (CTA 0): returns (counters, out). Per query tile
+        the clocks its first softmax warp spent in each part of its loop, and its MMA thread's polls and clocks
+        (see sanic_attn_fwd_bf16_profile)."""
+        for n, t in (("q", q), ("k", k), ("v", v)):
+            self._on_device(n, t, torch.bfloat16)
+        out = self.empty((q.shape[0], q.shape[1], q.shape[2], v.shape[-1]), torch.bfloat16)
+        p = self._attn_params(q, k, v, out, causal, window, scale, None, abi.BF16)
+        raw = (C.c_uint64 * 40)()
+        self._check(self.lib.sanic_attn_fwd_bf16_profile(self.h, C.byref(p), self.stream(), raw), "attn_fwd_bf16_profile")
+        names = ("wait_scores", "load_scores", "row_max", "first_half_exponentials", "wait_previous_pv", "rescale",
+                 "stores_and_second_half", "store_wait_and_arrive", "epilogue_and_item_switch", "fence_after_scores_wait")
+        prof = {}
+        for t in range(2):
+            tiles = max(1, raw[t * 12 + 10])
+            prof[f"tile{t}"] = dict(key_tiles=int(raw[t * 12 + 10]), clocks=int(raw[t * 12 + 11]),
+                                    clocks_per_key_tile={nm: raw[t * 12 + i] / tiles for i, nm in enumerate(names)})
+        for t in range(2):
+            m = raw[24 + 8 * t:32 + 8 * t]
+            per = max(1, m[3])
+            prof[f"mma_thread{t}"] = dict(polls=int(m[0]), idle_polls=int(m[1]), clocks=int(m[2]), qk_issued=int(m[3]),
+                                          clocks_per_key_tile=dict(barrier_tests_and_sleep=m[4] / per, score_products=m[5] / per,
+                                                                   value_products=m[6] / per, item_switch=m[7] / per))
+        return prof, out
+
     def decode_scratch(self, batch, q_heads, head_dim, n_splits):
         nbytes = self.lib.sanic_attn_decode_scratch_bytes(batch, q_heads, head_dim, n_splits)
         key = ("decode", batch, q_heads, head_dim, n_splits)

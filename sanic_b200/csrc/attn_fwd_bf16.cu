@@ -6,7 +6,8 @@
 // One CTA folds 256 query rows of one (batch, query head) as two 128-row tiles that ping-pong on
 // the tensor core: while one tile's softmax warpgroup turns S into P, the other tile's MMAs run.
 //   warp 0       TMA producer: Q once, then K_j / V_j tiles of 128 keys through a 5-stage ring
-//   warp 1       MMA issuer: per key tile  PV(0,j) QK(0,j+1) PV(1,j) QK(1,j+1)
+//   warps 1, 3   MMA issuers, one warp per query tile (an elected lane issues): QK(t,j+1) when S(t,j) is in registers,
+//                PV(t,j) when P(t,j) is stored
 //   warp 2       TMEM allocator (S0 S1 | P0 P1 | O0 O1 = 2x128 + 2x64 + 2x64 columns, all 512)
 //   warps 4-7    softmax + correction + epilogue of tile 0
 //   warps 8-11   the same for tile 1
@@ -15,7 +16,9 @@
 // Masks: causal (key > row), sliding window (key < row - window + 1) and the ragged key tail are
 // applied only in tiles that straddle an edge; tiles wholly outside the visible range are never
 // loaded (a prefix-masked fold may stop at the mask edge: it contributes exact zeros).
-// The rescale of O by exp(m_old - m_new) is skipped when no row of the warp moved its max.
+// The rescale of O by exp(m_old - m_new) is skipped when no row of the warp moved its max, and after an item's first
+// key tile the row maximum is taken inside the first half of the exponentials (redone if a reference did move).
+// The first warpgroup hands registers to the softmax warpgroups (setmaxnreg: 56 / 224 per thread).
 // Every mbarrier wait is bounded and reports through the context's status word.
 //
 // Roofline: tensor-bound, 4*B*Hq*S^2*D/2 FLOP for causal; the exponentials (one per score) run on
@@ -109,9 +112,23 @@ __device__ __forceinline__ Item make_item(const FParams& p, int k, int nkv) {
     return it;
 }
 
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(pred));
+    return pred != 0;
+}
+__device__ __forceinline__ uint32_t clock32() {
+    uint32_t c;
+    asm volatile("mov.u32 %0, %%clock;" : "=r"(c)::"memory");
+    return c;
+}
+
+// PROF: the softmax warp of rows 0-31 of each tile, and the MMA thread, of CTA 0 count clocks per part of their loops
+// (prof[0..11] tile 0, [12..23] tile 1, [24..31] and [32..39] the MMA threads); the results are computed and stored all the same.
+template <bool PROF>
 __global__ void __launch_bounds__(NTHREADS, 1)
 attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-                   const __grid_constant__ CUtensorMap map_v, FParams p, int* err) {
+                   const __grid_constant__ CUtensorMap map_v, FParams p, int* err, unsigned long long* prof) {
     extern __shared__ unsigned char smem_dyn[];
     const uint32_t raw = smem_u32(smem_dyn);
     const uint32_t base = (raw + 1023u) & ~1023u;
@@ -123,8 +140,8 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     const int nkv = (p.kv_len + BN - 1) / BN;
 
     if (threadIdx.x == 0) {
-        for (int i = 0; i < 2; ++i) { mbar_init(&sh->q_full[i], 1); mbar_init(&sh->q_empty[i], 1); }
-        for (int s = 0; s < KV_STAGES; ++s) { mbar_init(&sh->k_full[s], 1); mbar_init(&sh->v_full[s], 1); mbar_init(&sh->kv_empty[s], 1); }
+        for (int i = 0; i < 2; ++i) { mbar_init(&sh->q_full[i], 1); mbar_init(&sh->q_empty[i], 2); }
+        for (int s = 0; s < KV_STAGES; ++s) { mbar_init(&sh->k_full[s], 1); mbar_init(&sh->v_full[s], 1); mbar_init(&sh->kv_empty[s], 2); }
         for (int t = 0; t < 2; ++t) {
             mbar_init(&sh->s_full[t], 1); mbar_init(&sh->s_free[t], 4); mbar_init(&sh->p_full[t], 4);
             mbar_init(&sh->pv_done[t], 1); mbar_init(&sh->o_free[t], 4);
@@ -138,9 +155,12 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     fence_after();
     const uint32_t tmem = sh->tmem_base;
     volatile int* abortp = &sh->abort_flag;
+    // The softmax threads hold a whole 128-score row each: the first warpgroup (producer, MMA issuers, allocator) gives
+    // registers up and the two softmax warpgroups take them (128 x 56 + 256 x 224 = the 64,512 the launch was given).
 
     // Every role walks the same item sequence: its own sub-list; all barrier
     // parities come from running counts, so nothing is re-initialised between items.
+    if (warp < 4) asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
     if (warp == 0) {
         if (lane == 0) {
             int stage = 0; uint32_t phase = 1;
@@ -168,89 +188,118 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                 }
             }
         }
-    } else if (warp == 1) {
-        if (lane == 0) {
+    } else if (warp == 1 || warp == 3) {
+        {
+            // The whole warp walks the role with warp-uniform control flow (barrier answers are made uniform by a vote) and
+            // one elected lane issues: the descriptors can then live in uniform registers (an MMA took 90 clocks to issue
+            // from a single diverged thread, 40 this way).
+            const bool leader = elect_one();
+            // One MMA-issuing warp per query tile (warp 1: tile 0, warp 3: tile 1), each serving its tile's two events
+            // (S free -> next QK, P full -> PV) in arrival order: a single thread serving both tiles spent its whole time
+            // in barrier tests and MMA issue (1950 clocks per key tile of each query tile). QK(t, j+1) is issued as soon as tile
+            // t's softmax warps have pulled S(t, j) into registers, so the next scores are ready before the exponentials
+            // of the current ones finish; PV(t, j) follows when P(t, j) is written. A ring slot and the query tiles go back
+            // to the producer when both threads have handed them back (barrier counts of 2).
+            const int t = __shfl_sync(0xffffffffu, warp == 3 ? 1 : 0, 0);
             constexpr uint32_t idesc_qk = make_idesc(BM, BN, false);
             constexpr uint32_t idesc_pv = make_idesc(BM, D, true);
-            // The two tiles advance independently. QK(t, j+1) is issued as soon as tile t's softmax
-            // warps have pulled S(t, j) into registers, so the next scores are ready before the
-            // exponentials of the current ones finish; PV(t, j) follows when P(t, j) is written.
-            // This thread serves the four events (S free / P full, per tile) in arrival order.
             bool ok = true;
             int n = 0;
             uint32_t u_base = 0;                 // key tiles of all earlier items: position in the K/V ring
-            uint32_t n_qk[2] = {0, 0}, n_pv[2] = {0, 0};   // QK / PV issues so far per tile, over all items
-            uint32_t n_act[2] = {0, 0};          // earlier items in which the tile had work (its O was read back)
+            uint32_t n_qk = 0, n_pv = 0;         // QK / PV issues so far, over all items
+            uint32_t n_act = 0;                  // earlier items in which the tile had work (its O was read back)
+            uint32_t polls = 0, idle_polls = 0, mc[4] = {0, 0, 0, 0};
+            const uint32_t mma_t0 = PROF ? clock32() : 0u;
+            uint32_t m_mark = mma_t0;
+#define SANIC_MTICK(i) do { if (PROF) { const uint32_t now_ = clock32(); mc[i] += now_ - m_mark; m_mark = now_; } } while (0)
             for (int k = item_of_round(0); k < p.n_items && ok; k = item_of_round(++n)) {
                 const Item w = make_item(p, k, nkv);
                 const int qb = n & 1;
-                ok = mbar_wait(&sh->q_full[qb], (n >> 1) & 1, abortp, err, 12);
+                ok = __all_sync(0xffffffffu, mbar_wait(&sh->q_full[qb], (n >> 1) & 1, abortp, err, 12));
                 if (!ok) break;
                 fence_after();
-                int jq[2] = {w.jb[0], w.jb[1]};      // next key tile whose QK is to be issued
-                int jp[2] = {w.jb[0], w.jb[1]};      // next key tile whose PV is to be issued
-                int jr = w.j_begin;                  // next ring slot to hand back to the producer
-                bool q_released = false;
+                const bool active = w.je[t] > w.jb[t];
+                const int lo = active ? max(w.jb[t], w.j_begin) : w.j_begin;
+                const int hi = active ? min(w.je[t], w.j_end) : w.j_begin;
+                // A key tile of the item that this query tile does not see goes back untouched. The arrival may only count
+                // for the slot's current use: its previous use must have been handed back by both threads first.
+                auto hand_back_unused = [&](int j) -> bool {
+                    const uint32_t u = u_base + (uint32_t)(j - w.j_begin);
+                    const int stage = u % KV_STAGES;
+                    if (u >= (uint32_t)KV_STAGES && !__all_sync(0xffffffffu, mbar_wait(&sh->kv_empty[stage], ((u / KV_STAGES) - 1) & 1, abortp, err, 14))) return false;
+                    if (leader) mbar_arrive(&sh->kv_empty[stage]);
+                    return true;
+                };
+                for (int j = w.j_begin; j < lo && ok; ++j) ok = hand_back_unused(j);
+                if (!active && ok && leader) mbar_arrive(&sh->q_empty[qb]);      // no rows of this tile in the item
+                int jq = lo;      // next key tile whose QK is to be issued
+                int jp = lo;      // next key tile whose PV is to be issued
                 uint32_t idle = 0;
-                while (ok && (jp[0] < w.je[0] || jp[1] < w.je[1])) {
+                SANIC_MTICK(3);
+                while (ok && jp < hi) {
                     bool progressed = false;
+                    if (jq < hi) {
+                        const uint32_t u = u_base + (uint32_t)(jq - w.j_begin);
+                        const int stage = u % KV_STAGES;
+                        if (__all_sync(0xffffffffu, (n_qk == 0 || mbar_test(&sh->s_free[t], (n_qk - 1) & 1)) && mbar_test(&sh->k_full[stage], (u / KV_STAGES) & 1))) {
+                            fence_after();
+                            SANIC_MTICK(0);
+                            const uint64_t ad = make_desc(q_addr + (qb * 2 + t) * Q_BYTES, 16, 1024);
+                            const uint64_t bd = make_desc(kv_addr + stage * 2 * KV_BYTES, 16, 1024);
 #pragma unroll
-                    for (int t = 0; t < 2; ++t) {
-                        if (jq[t] < w.je[t]) {
-                            const uint32_t u = u_base + (uint32_t)(jq[t] - w.j_begin);
-                            const int stage = u % KV_STAGES;
-                            if ((n_qk[t] == 0 || mbar_test(&sh->s_free[t], (n_qk[t] - 1) & 1)) &&
-                                mbar_test(&sh->k_full[stage], (u / KV_STAGES) & 1)) {
-                                fence_after();
-                                const uint64_t ad = make_desc(q_addr + (qb * 2 + t) * Q_BYTES, 16, 1024);
-                                const uint64_t bd = make_desc(kv_addr + stage * 2 * KV_BYTES, 16, 1024);
-#pragma unroll
-                                for (int kk = 0; kk < D / 16; ++kk) umma_f16(tmem + TM_S + t * BN, ad + 2 * kk, bd + 2 * kk, idesc_qk, kk > 0 ? 1u : 0u);
-                                umma_commit(&sh->s_full[t]);
-                                jq[t]++; n_qk[t]++; progressed = true;
-                            }
-                        }
-                        if (jp[t] < jq[t]) {
-                            const uint32_t u = u_base + (uint32_t)(jp[t] - w.j_begin);
-                            const int stage = u % KV_STAGES;
-                            const bool first = (jp[t] == w.jb[t]);
-                            // the first PV of an item overwrites O_t: the epilogue of the tile's previous item must have read it
-                            if (mbar_test(&sh->p_full[t], n_pv[t] & 1) && mbar_test(&sh->v_full[stage], (u / KV_STAGES) & 1) &&
-                                (!first || n_act[t] == 0 || mbar_test(&sh->o_free[t], (n_act[t] - 1) & 1))) {
-                                fence_after();
-                                const uint64_t vd = make_desc(kv_addr + stage * 2 * KV_BYTES + KV_BYTES, 1024, 1024);
-#pragma unroll
-                                for (int kk = 0; kk < BN / 16; ++kk)      // A = P_t from tensor memory: 16 keys = 8 columns per step
-                                    umma_f16_ts(tmem + TM_O + t * D, tmem + TM_P + t * (BN / 2) + 8 * kk, vd + 128 * kk, idesc_pv,
-                                                (!first || kk > 0) ? 1u : 0u);
-                                umma_commit(&sh->pv_done[t]);
-                                jp[t]++; n_pv[t]++; progressed = true;
-                            }
+                            for (int kk = 0; kk < D / 16; ++kk) if (leader) umma_f16(tmem + TM_S + t * BN, ad + 2 * kk, bd + 2 * kk, idesc_qk, kk > 0 ? 1u : 0u);
+                            if (leader) umma_commit(&sh->s_full[t]);
+                            jq++; n_qk++; progressed = true;
+                            if (jq == hi && leader) umma_commit(&sh->q_empty[qb]);     // every QK of the item is issued: the query tile goes back
+                            SANIC_MTICK(1);
                         }
                     }
-                    // the query tiles go back once every QK of the item is issued
-                    if (!q_released && jq[0] >= w.je[0] && jq[1] >= w.je[1]) { umma_commit(&sh->q_empty[qb]); q_released = true; }
-                    // a ring slot goes back once neither tile still has a QK or PV to issue on it
-                    while (jr < w.j_end && !(jp[0] < w.je[0] && jp[0] <= jr) && !(jp[1] < w.je[1] && jp[1] <= jr)) {
-                        umma_commit(&sh->kv_empty[(u_base + (uint32_t)(jr - w.j_begin)) % KV_STAGES]);
-                        ++jr;
+                    if (jp < jq) {
+                        const uint32_t u = u_base + (uint32_t)(jp - w.j_begin);
+                        const int stage = u % KV_STAGES;
+                        const bool first = (jp == lo);
+                        // the first PV of an item overwrites O_t: the epilogue of the tile's previous item must have read it
+                        if (__all_sync(0xffffffffu, mbar_test(&sh->p_full[t], n_pv & 1) && mbar_test(&sh->v_full[stage], (u / KV_STAGES) & 1) &&
+                                                     (!first || n_act == 0 || mbar_test(&sh->o_free[t], (n_act - 1) & 1)))) {
+                            fence_after();
+                            SANIC_MTICK(0);
+                            const uint64_t vd = make_desc(kv_addr + stage * 2 * KV_BYTES + KV_BYTES, 1024, 1024);
+#pragma unroll
+                            for (int kk = 0; kk < BN / 16; ++kk)      // A = P_t from tensor memory: 16 keys = 8 columns per step
+                                if (leader) umma_f16_ts(tmem + TM_O + t * D, tmem + TM_P + t * (BN / 2) + 8 * kk, vd + 128 * kk, idesc_pv,
+                                            (!first || kk > 0) ? 1u : 0u);
+                            if (leader) umma_commit(&sh->pv_done[t]);
+                            if (leader) umma_commit(&sh->kv_empty[stage]);      // this tile's QK and PV on the slot are issued
+                            jp++; n_pv++; progressed = true;
+                            SANIC_MTICK(2);
+                        }
                     }
+                    SANIC_MTICK(0);
+                    if (PROF) { ++polls; if (!progressed) ++idle_polls; }
                     if (progressed) idle = 0;
                     else {
                         __nanosleep(32);
-                        if (++idle > (SPIN_LIMIT >> 4) || ((idle & 1023u) == 0 && *abortp)) {
-                            if (idle > (SPIN_LIMIT >> 4)) { *abortp = 1; atomicCAS(err, 0, 13); }
+                        if (++idle > (SPIN_LIMIT >> 4) || ((idle & 1023u) == 0 && __any_sync(0xffffffffu, *abortp != 0))) {
+                            if (idle > (SPIN_LIMIT >> 4) && leader) { *abortp = 1; atomicCAS(err, 0, 13); }
                             ok = false;
                         }
                     }
                 }
-                if (ok && !q_released) umma_commit(&sh->q_empty[qb]);    // an item without key tiles
+                for (int j = hi; j < w.j_end && ok; ++j) ok = hand_back_unused(j);
+                SANIC_MTICK(3);
                 u_base += (uint32_t)(w.j_end - w.j_begin);
-                for (int t = 0; t < 2; ++t) if (w.je[t] > w.jb[t]) n_act[t]++;
+                if (active) n_act++;
             }
+            if (PROF && blockIdx.x == 0 && leader) {
+                unsigned long long* o = prof + 24 + 8 * t;
+                o[0] = polls; o[1] = idle_polls; o[2] = clock32() - mma_t0; o[3] = n_qk;
+                for (int i = 0; i < 4; ++i) o[4 + i] = mc[i];
+            }
+#undef SANIC_MTICK
         }
     } else if (warp >= 4) {
         // ── softmax, correction and epilogue for tile t; this thread owns one query row of the tile ──
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
         const int t = (warp - 4) >> 2;
         const int q4 = warp & 3;
         const int row = q4 * 32 + lane;
@@ -262,6 +311,12 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         uint32_t n_it = 0;           // key tiles folded so far by this tile, over all items
         bool ok = true;
         int n = 0;
+        // Each of the loop's two waits is asked ahead of time, with exponentials between the question and the use of its
+        // answer; the bounded wait (a loop with its abort checks) runs only when the early answer was no.
+        bool scores_ready = false;
+        uint32_t pc[10] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0}, t_mark = PROF ? clock32() : 0u;
+        const uint32_t t_start = t_mark;
+#define SANIC_TICK(i) do { if (PROF) { const uint32_t now_ = clock32(); pc[i] += now_ - t_mark; t_mark = now_; } } while (0)
         for (int k = item_of_round(0); k < p.n_items && ok; k = item_of_round(++n)) {
             const Item w = make_item(p, k, nkv);
             const int r0 = w.m0 + t * BM;
@@ -269,9 +324,14 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             float m = -INFINITY, l = 0.0f;
             for (int j = w.jb[t]; j < w.je[t] && ok; ++j, ++n_it) {
                 const bool first = (j == w.jb[t]);
-                ok = mbar_wait_spin(&sh->s_full[t], n_it & 1, abortp, err, 21);
-                if (!ok) break;
+                SANIC_TICK(8);
+                if (!scores_ready) {
+                    ok = mbar_wait_spin(&sh->s_full[t], n_it & 1, abortp, err, 21);
+                    if (!ok) break;
+                }
+                SANIC_TICK(0);
                 fence_after();
+                SANIC_TICK(9);
                 const int k0 = j * BN;
                 // does this tile straddle a mask edge for any of the 128 rows?
                 bool edge = (k0 + BN > p.kv_len);
@@ -280,79 +340,125 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                 int klo = 0, khi = p.kv_len;              // visible keys of this row: [klo, khi)
                 if (p.causal || p.window > 0) khi = min(khi, grow + 1);
                 if (p.window > 0) klo = max(0, grow - p.window + 1);
-                // The whole score row of this tile goes to registers in four 32-column loads; the row max of
-                // one chunk is taken while the next chunk is in flight.
+                // The whole score row of this tile goes to registers: four 32-column loads in flight together, one wait.
                 uint32_t r[BN];
-                float mxs[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-                tmem_ld32_nowait(s_tmem, *reinterpret_cast<uint32_t(*)[32]>(&r[0]));
 #pragma unroll
-                for (int c = 0; c < BN / 32; ++c) {
-                    tmem_ld_wait();
-                    if (c + 1 < BN / 32) tmem_ld32_nowait(s_tmem + (c + 1) * 32, *reinterpret_cast<uint32_t(*)[32]>(&r[(c + 1) * 32]));
-                    else {
-                        fence_before();
-                        __syncwarp();
-                        if (lane == 0) mbar_arrive(&sh->s_free[t]);   // S_t is in registers: the next QK of this tile may overwrite it
-                    }
-                    if (edge) {
+                for (int c = 0; c < BN / 32; ++c) tmem_ld32_nowait(s_tmem + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&r[c * 32]));
+                tmem_ld_wait();
+                fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&sh->s_free[t]);   // S_t is in registers: the next QK of this tile may overwrite it
+                SANIC_TICK(1);
+                if (edge) {
 #pragma unroll
-                        for (int i = c * 32; i < c * 32 + 32; ++i) { int kk = k0 + i; if (!(kk >= klo && kk < khi)) r[i] = 0xFF800000u; }  // -inf
-                    }
-#pragma unroll
-                    for (int i = 0; i < 32; i += 8) {      // four independent chains of three-input max
-                        mxs[0] = max3(mxs[0], __uint_as_float(r[c * 32 + i]), __uint_as_float(r[c * 32 + i + 1]));
-                        mxs[1] = max3(mxs[1], __uint_as_float(r[c * 32 + i + 2]), __uint_as_float(r[c * 32 + i + 3]));
-                        mxs[2] = max3(mxs[2], __uint_as_float(r[c * 32 + i + 4]), __uint_as_float(r[c * 32 + i + 5]));
-                        mxs[3] = max3(mxs[3], __uint_as_float(r[c * 32 + i + 6]), __uint_as_float(r[c * 32 + i + 7]));
-                    }
+                    for (int i = 0; i < BN; ++i) { int kk = k0 + i; if (!(kk >= klo && kk < khi)) r[i] = 0xFF800000u; }  // -inf
                 }
-                const float mx = fmaxf(fmaxf(mxs[0], mxs[1]), fmaxf(mxs[2], mxs[3]));
-                // Lazy rescale: keep the reference max until the running max has moved by more than
-                // 2^8; exp2(s - m_ref) then stays below 256, well inside bf16/f32 range, and o / l is
-                // unchanged because both carry the same reference.
-                const float m_cand = fmaxf(m, mx * sl2);
-                const bool need = (m_cand - m > 8.0f) || (!(m > -INFINITY) && m_cand > -INFINITY);
+                // Lazy rescale: the reference max is kept until the running max has moved by more than 2^8; exp2(s - m_ref)
+                // then stays below 256, well inside bf16/f32 range, and o / l is unchanged because both carry the same
+                // reference. So after an item's first key tile the reference almost never moves, and the row maximum (64
+                // three-input max instructions, about 500 clocks on their own) is taken inside the first half of the
+                // exponentials, where the SFU sets the pace: that half runs against the old reference, and is redone (its
+                // scores stay in registers: the half's bf16 pairs go to registers of their own) in the rare case that some
+                // row's reference did move.
+                // The first key tile has no reference yet: its maximum comes first. Under a sliding window so does the second's:
+                // the rows whose window opens after the first key tile still have none.
+                const bool spec = !first && !(p.window > 0 && j == w.jb[t] + 1);
+                float mxs[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
                 float alpha = 1.0f;
-                if (need) { alpha = (m > -INFINITY) ? ex2(m - m_cand) : 0.0f; m = m_cand; }
-                const float msub = (m > -INFINITY) ? m : 0.0f;
+                bool need = false;
+                auto new_reference = [&]() {
+                    const float mx = fmaxf(fmaxf(mxs[0], mxs[1]), fmaxf(mxs[2], mxs[3]));
+                    const float m_cand = fmaxf(m, mx * sl2);
+                    need = (m_cand - m > 8.0f) || (!(m > -INFINITY) && m_cand > -INFINITY);
+                    if (need) { alpha = (m > -INFINITY) ? ex2(m - m_cand) : 0.0f; m = m_cand; }
+                };
+                if (!spec) {
+#pragma unroll
+                    for (int i = 0; i < BN; i += 8) {      // four independent chains of three-input max
+                        mxs[0] = max3(mxs[0], __uint_as_float(r[i]), __uint_as_float(r[i + 1]));
+                        mxs[1] = max3(mxs[1], __uint_as_float(r[i + 2]), __uint_as_float(r[i + 3]));
+                        mxs[2] = max3(mxs[2], __uint_as_float(r[i + 4]), __uint_as_float(r[i + 5]));
+                        mxs[3] = max3(mxs[3], __uint_as_float(r[i + 6]), __uint_as_float(r[i + 7]));
+                    }
+                    new_reference();
+                }
+                SANIC_TICK(2);
+                float msub = (m > -INFINITY) ? m : 0.0f;
+                const bool pv_ready = n_it > 0 && mbar_test(&sh->pv_done[t], (n_it - 1) & 1);
                 // P = exp2(S*sl2 - m_ref) as bf16 pairs, packed in place over the score registers, and the row
                 // sum. The first half is stored while the second half is still in the SFU; only at that store
                 // is the previous PV of this tile needed (it has read P_t and finished O_t).
                 float sums[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+                uint32_t pk[32];        // the first half's pairs
 #pragma unroll
-                for (int hb = 0; hb < 2; ++hb) {
-#pragma unroll
-                    for (int i = hb * 32; i < hb * 32 + 32; ++i) {
-                        float x0, x1;
-                        ffma2(x0, x1, __uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]), sl2, -msub);
-                        const float p0 = ex2(x0), p1 = ex2(x1);
-                        fadd2(sums[(2 * i) & 7], sums[(2 * i + 1) & 7], p0, p1);
-                        r[i] = pack_bf16x2(p0, p1);
+                for (int i = 0; i < 32; ++i) {
+                    if (spec) {     // the row maximum of all 128 scores, four per step
+                        mxs[0] = max3(mxs[0], __uint_as_float(r[4 * i]), __uint_as_float(r[4 * i + 1]));
+                        mxs[1] = max3(mxs[1], __uint_as_float(r[4 * i + 2]), __uint_as_float(r[4 * i + 3]));
                     }
-                    if (hb == 0 && n_it > 0) {
-                        ok = mbar_wait_spin(&sh->pv_done[t], (n_it - 1) & 1, abortp, err, 22);
-                        if (!ok) break;
-                        fence_after();
-                        if (!first && __any_sync(0xffffffffu, need)) {
-#pragma unroll 1
-                            for (int c = 0; c < D / 32; ++c) {
-                                uint32_t o[32];
-                                tmem_ld32(o_tmem + c * 32, o);
+                    float x0, x1;
+                    ffma2(x0, x1, __uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]), sl2, -msub);
+                    const float p0 = ex2(x0), p1 = ex2(x1);
+                    fadd2(sums[(2 * i) & 7], sums[(2 * i + 1) & 7], p0, p1);
+                    pk[i] = pack_bf16x2(p0, p1);
+                }
+                if (spec) {
+                    new_reference();
+                    if (__any_sync(0xffffffffu, need)) {
+                        // some row's reference moved: the half is taken again against the new one
+                        msub = (m > -INFINITY) ? m : 0.0f;
 #pragma unroll
-                                for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-                                tmem_st32(o_tmem + c * 32, o);
-                            }
+                        for (int i = 0; i < 8; ++i) sums[i] = 0.0f;
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) {
+                            float x0, x1;
+                            ffma2(x0, x1, __uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]), sl2, -msub);
+                            const float p0 = ex2(x0), p1 = ex2(x1);
+                            fadd2(sums[(2 * i) & 7], sums[(2 * i + 1) & 7], p0, p1);
+                            pk[i] = pack_bf16x2(p0, p1);
                         }
                     }
-                    tmem_st32(p_tmem + hb * 32, *reinterpret_cast<uint32_t(*)[32]>(&r[hb * 32]));
                 }
+                if (n_it > 0) {
+                    SANIC_TICK(3);
+                    if (!pv_ready) {
+                        ok = mbar_wait_spin(&sh->pv_done[t], (n_it - 1) & 1, abortp, err, 22);
+                        if (!ok) break;
+                    }
+                    fence_after();
+                    SANIC_TICK(4);
+                    if (!first && __any_sync(0xffffffffu, need)) {
+#pragma unroll 1
+                        for (int c = 0; c < D / 32; ++c) {
+                            uint32_t o[32];
+                            tmem_ld32(o_tmem + c * 32, o);
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                            tmem_st32(o_tmem + c * 32, o);
+                        }
+                    }
+                    SANIC_TICK(5);
+                }
+                tmem_st32(p_tmem, pk);
+                scores_ready = (j + 1 < w.je[t]) && mbar_test(&sh->s_full[t], (n_it + 1) & 1);     // the next key tile's scores
+#pragma unroll
+                for (int i = 32; i < 64; ++i) {
+                    float x0, x1;
+                    ffma2(x0, x1, __uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]), sl2, -msub);
+                    const float p0 = ex2(x0), p1 = ex2(x1);
+                    fadd2(sums[(2 * i) & 7], sums[(2 * i + 1) & 7], p0, p1);
+                    r[i] = pack_bf16x2(p0, p1);
+                }
+                tmem_st32(p_tmem + 32, *reinterpret_cast<uint32_t(*)[32]>(&r[32]));
                 if (!ok) break;
                 const float sum = ((sums[0] + sums[1]) + (sums[2] + sums[3])) + ((sums[4] + sums[5]) + (sums[6] + sums[7]));
                 l = l * alpha + sum;
+                SANIC_TICK(6);
                 tmem_st_wait();
                 fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&sh->p_full[t]);
+                SANIC_TICK(7);
             }
             // epilogue: read O_t back, release it for the next item, project o / l and store bf16 rows
             if (ok && w.je[t] > w.jb[t]) {
@@ -393,6 +499,13 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                 }
             }
         }
+        if (PROF && blockIdx.x == 0 && q4 == 0 && lane == 0) {
+            SANIC_TICK(8);
+            for (int i = 0; i < 10; ++i) prof[t * 12 + i] = pc[i];
+            prof[t * 12 + 10] = n_it;
+            prof[t * 12 + 11] = t_mark - t_start;
+        }
+#undef SANIC_TICK
     }
     fence_before();
     __syncthreads();
@@ -400,7 +513,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
 }
 }  // namespace
 
-extern "C" int32_t sanic_attn_fwd_bf16(sanic_ctx* ctx, const sanic_attn_params* p, void* stream) {
+static int32_t attn_fwd_launch(sanic_ctx* ctx, const sanic_attn_params* p, void* stream, unsigned long long* prof) {
     if (!ctx || !p) return SANIC_ERR_INVALID;
     SANIC_REQUIRE(ctx, p->q && p->k && p->v && p->out, "attn_fwd_bf16: null tensor");
     SANIC_REQUIRE(ctx, p->batch > 0 && p->q_heads > 0 && p->kv_heads > 0 && p->q_heads % p->kv_heads == 0,
@@ -427,9 +540,34 @@ extern "C" int32_t sanic_attn_fwd_bf16(sanic_ctx* ctx, const sanic_attn_params* 
     SANIC_REQUIRE(ctx, items < (1ll << 30), "attn_fwd_bf16: too many query blocks");
     FParams fp{p->out, p->batch, p->q_heads, p->kv_heads, p->q_len, p->kv_len, p->causal, p->window, p->scale, n_mb, (int)items};
     const int smem = 4 * Q_BYTES + KV_STAGES * 2 * KV_BYTES + (int)sizeof(FShared) + 1024;
-    SANIC_CUDA_CHECK(ctx, cudaFuncSetAttribute(attn_fwd_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     dim3 grid((unsigned)std::min<long long>(items, ctx->sm_count));   // persistent: one CTA per SM walks the item list
-    attn_fwd_tc_kernel<<<grid, NTHREADS, smem, (cudaStream_t)stream>>>(mq, mk, mv, fp, ctx->status_dev);
+    if (prof) {
+        SANIC_CUDA_CHECK(ctx, cudaFuncSetAttribute(attn_fwd_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        attn_fwd_tc_kernel<true><<<grid, NTHREADS, smem, (cudaStream_t)stream>>>(mq, mk, mv, fp, ctx->status_dev, prof);
+    } else {
+        SANIC_CUDA_CHECK(ctx, cudaFuncSetAttribute(attn_fwd_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        attn_fwd_tc_kernel<false><<<grid, NTHREADS, smem, (cudaStream_t)stream>>>(mq, mk, mv, fp, ctx->status_dev, nullptr);
+    }
     SANIC_LAUNCH_CHECK(ctx, "attn_fwd_bf16");
     return SANIC_OK;
+}
+
+extern "C" int32_t sanic_attn_fwd_bf16(sanic_ctx* ctx, const sanic_attn_params* p, void* stream) {
+    return attn_fwd_launch(ctx, p, stream, nullptr);
+}
+
+extern "C" int32_t sanic_attn_fwd_bf16_profile(sanic_ctx* ctx, const sanic_attn_params* p, void* stream, uint64_t* out) {
+    if (!ctx || !p || !out) return SANIC_ERR_INVALID;
+    sanic_set_device(ctx);
+    unsigned long long* d = nullptr;
+    SANIC_CUDA_CHECK(ctx, cudaMalloc(&d, 40 * sizeof(unsigned long long)));
+    cudaError_t e = cudaMemsetAsync(d, 0, 40 * sizeof(unsigned long long), (cudaStream_t)stream);
+    int32_t rc = e == cudaSuccess ? attn_fwd_launch(ctx, p, stream, d) : SANIC_ERR_CUDA;
+    if (rc == SANIC_OK) {
+        e = cudaMemcpyAsync(out, d, 40 * sizeof(unsigned long long), cudaMemcpyDeviceToHost, (cudaStream_t)stream);
+        if (e == cudaSuccess) e = cudaStreamSynchronize((cudaStream_t)stream);
+        if (e != cudaSuccess) rc = sanic_fail(ctx, SANIC_ERR_CUDA, cudaGetErrorString(e));
+    }
+    cudaFree(d);
+    return rc;
 }

@@ -619,6 +619,26 @@ def test_flash_fwd_many_items_equals_single_round_calls(dev, mode):
             assert torch.equal(small[0], big[b, hk * grp:(hk + 1) * grp]), (b, hk)
 
 
+def test_flash_fwd_profile_counts_clocks_and_computes(dev):
+    """The profile entry point runs the same fold with clock counters on in CTA 0: the output is bit for bit the plain
+    call's, and the counters are those of a run (CTA 0's item is the last query block: 5 and 6 key tiles)."""
+    B, Hq, Hkv, L = 1, 4, 2, 700
+    q, _ = bf16t(normal(301, B, Hq, L, 64), dev)
+    k, _ = bf16t(normal(302, B, Hkv, L, 64), dev)
+    v, _ = bf16t(normal(303, B, Hkv, L, 64), dev)
+    plain = dev.attn_fwd_bf16(q, k, v, causal=True)
+    prof, out = dev.attn_fwd_bf16_profile(q, k, v, causal=True)
+    dev.sync()
+    assert torch.equal(plain, out)
+    assert prof["tile0"]["key_tiles"] == 5 and prof["tile1"]["key_tiles"] == 6
+    for t in ("tile0", "tile1"):
+        per = prof[t]["clocks_per_key_tile"]
+        assert per["first_half_exponentials"] > 0 and per["load_scores"] > 0 and per["row_max"] > 0
+        assert abs(sum(per.values()) * prof[t]["key_tiles"] - prof[t]["clocks"]) <= 10 * prof[t]["key_tiles"] + 10
+    for t, tiles in ((0, 5), (1, 6)):
+        assert prof[f"mma_thread{t}"]["qk_issued"] == tiles and prof[f"mma_thread{t}"]["polls"] >= tiles
+
+
 def test_flash_fwd_rope_pipeline_long(dev):
     # size-independent checks at a longer sequence: causal row 0 equals V row 0, and the output is
     # unchanged when keys beyond the causal edge are replaced (they must never be read into a result)
