@@ -88,29 +88,49 @@ __global__ void rope_table_kernel(const double* inv_freq, int n_freq, int n_pos,
 }
 
 // out[p=0,f] = x0*cos - x1*sin ; out[p=1,f] = x1*cos + x0*sin  (pair-major split of head_dim).
-// One thread rotates 8 consecutive frequencies: two 16-byte loads, two 16-byte stores.
-__global__ void rope_bf16_kernel(const uint16_t* x, uint16_t* out, long long rows, int seq, int D, const float* table,
-                                 int pos0) {
+// One thread rotates 8 consecutive frequencies of one position for ROPE_ROWS rows (batch x head) in turn: the 64 bytes of
+// (cos, sin) it needs are read once and kept in registers, where a thread per row read them again for every row (twice the
+// bytes of the data itself, all from L2); per row two 16-byte loads and two 16-byte stores, all rows' loads issued first.
+constexpr int ROPE_ROWS = 8;
+__global__ void rope_bf16_kernel(const uint16_t* x, uint16_t* out, long long rows, int seq, int D,
+                                 const float* __restrict__ table, int pos0) {
     const int F = D / 2, FV = F / 8;
+    const long long per_row = (long long)seq * FV;
     long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    long long total = rows * seq * FV;
-    if (idx >= total) return;
-    int f = (int)(idx % FV) * 8;
-    long long rs = idx / FV;
-    int s = (int)(rs % seq);
+    const long long groups = (rows + ROPE_ROWS - 1) / ROPE_ROWS;
+    if (idx >= groups * per_row) return;
+    const long long g = idx / per_row, sf = idx % per_row;
+    const int f = (int)(sf % FV) * 8, s = (int)(sf / FV);
     const float4* cs = (const float4*)(table + 2 * ((size_t)(pos0 + s) * F + f));
-    size_t base = (size_t)rs * D;
-    uint4 a = *(const uint4*)(x + base + f), b = *(const uint4*)(x + base + F + f);
-    uint32_t av[4] = {a.x, a.y, a.z, a.w}, bv[4] = {b.x, b.y, b.z, b.w}, oa[4], ob[4];
+    float4 t[4];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        float4 t = cs[i];   // (cos, sin) of frequencies f+2i and f+2i+1
-        float x0 = bf16lo(av[i]), x1 = bf16lo(bv[i]), y0 = bf16hi(av[i]), y1 = bf16hi(bv[i]);
-        oa[i] = pack_bf16x2(x0 * t.x + (-x1) * t.y, y0 * t.z + (-y1) * t.w);
-        ob[i] = pack_bf16x2(x1 * t.x + x0 * t.y, y1 * t.z + y0 * t.w);
+    for (int i = 0; i < 4; ++i) t[i] = __ldg(cs + i);   // (cos, sin) of frequencies f+2i and f+2i+1
+    const long long r0 = g * ROPE_ROWS;
+    uint4 a[ROPE_ROWS], b[ROPE_ROWS];
+#pragma unroll
+    for (int r = 0; r < ROPE_ROWS; ++r) {
+        if (r0 + r < rows) {
+            const size_t base = ((size_t)(r0 + r) * seq + s) * D;
+            a[r] = ldg_stream16((const uint4*)(x + base + f));
+            b[r] = ldg_stream16((const uint4*)(x + base + F + f));
+        }
     }
-    *(uint4*)(out + base + f) = make_uint4(oa[0], oa[1], oa[2], oa[3]);
-    *(uint4*)(out + base + F + f) = make_uint4(ob[0], ob[1], ob[2], ob[3]);
+#pragma unroll
+    for (int r = 0; r < ROPE_ROWS; ++r) {
+        if (r0 + r < rows) {
+            const size_t base = ((size_t)(r0 + r) * seq + s) * D;
+            const uint32_t av[4] = {a[r].x, a[r].y, a[r].z, a[r].w}, bv[4] = {b[r].x, b[r].y, b[r].z, b[r].w};
+            uint32_t oa[4], ob[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                float x0 = bf16lo(av[i]), x1 = bf16lo(bv[i]), y0 = bf16hi(av[i]), y1 = bf16hi(bv[i]);
+                oa[i] = pack_bf16x2(x0 * t[i].x + (-x1) * t[i].y, y0 * t[i].z + (-y1) * t[i].w);
+                ob[i] = pack_bf16x2(x1 * t[i].x + x0 * t[i].y, y1 * t[i].z + y0 * t[i].w);
+            }
+            *(uint4*)(out + base + f) = make_uint4(oa[0], oa[1], oa[2], oa[3]);
+            *(uint4*)(out + base + F + f) = make_uint4(ob[0], ob[1], ob[2], ob[3]);
+        }
+    }
 }
 __global__ void rope_bf16_scalar_kernel(const uint16_t* x, uint16_t* out, long long rows, int seq, int D,
                                         const float* table, int pos0) {
@@ -310,7 +330,7 @@ int32_t sanic_rope_bf16(sanic_ctx* ctx, const void* x, void* out, int64_t rows, 
                   "rope_bf16: bad arguments");
     sanic_set_device(ctx);
     if (head_dim % 16 == 0 && ((uintptr_t)x % 16) == 0 && ((uintptr_t)out % 16) == 0) {
-        long long total = (long long)rows * seq * (head_dim / 16);
+        long long total = ((long long)rows + ROPE_ROWS - 1) / ROPE_ROWS * seq * (head_dim / 16);
         rope_bf16_kernel<<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
             (const uint16_t*)x, (uint16_t*)out, rows, seq, head_dim, table, pos0);
     } else {
