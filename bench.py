@@ -319,40 +319,57 @@ def suite(dev, torch, hbm_peak, tf_peak, quick, only=None, c2_shape=(4096, 2048,
         out["probe"] = pr
       except Exception as e:      # a probe must not take the rest of the suite with it
         out["probe"] = {"error": repr(e)}
-    # the decode step's contractions one by one at batch 16: back to back in a CUDA graph, weight sets in rotation (more
-    # than L2 holds), so each figure is a kernel's own streaming rate without the step's launch-to-launch gaps.
-    # Not part of the default suite (name it with --only c4_contractions); SANIC_GEMV_RING=0 times the register-staged kernel.
-    if only is not None and want("c4_contractions"):
+    # the decode step's contractions one by one, bf16 and int4-g64 weights at batch 1 and 16: back to back in a CUDA graph,
+    # weight sets in rotation (more than L2 holds), so each figure is the stand-alone kernel's own streaming rate without the
+    # step's launch-to-launch gaps. Not part of the default suite: name it with --only c4_contractions, or one case of it as
+    # --only c4_contractions_int4_g64_b1_lm_head (weights, batch, contraction). SANIC_GEMV_RING=0 times the register-staged
+    # kernel at batch 16.
+    pick = [o for o in (only or []) if o.startswith("c4_contractions")]
+    if pick:
         from sanic_b200 import abi
-        B = 16
         res = {}
-        for name, rows, K, dual, nset in (("qkv_3072x2048", 3072, 2048, False, 16), ("o_2048x2048", 2048, 2048, False, 16),
-                                          ("gate_up_2x8192x2048", 8192, 2048, True, 8), ("down_2048x8192", 2048, 8192, False, 8),
-                                          ("lm_head_128256x2048", 128256, 2048, False, 2)):
-            sets = [[(0.02 * torch.randn(rows, K, device=td, generator=g)).to(torch.bfloat16) for _ in range(2 if dual else 1)]
-                    for _ in range(nset)]
-            xb = torch.randn(B, K, device=td, generator=g).to(torch.bfloat16)
-            kw = dict(epilogue=abi.EPI_SILU_MUL) if dual else {}
-            for ws in sets:
-                dev.gemv(xb, ws, **kw)
-            torch.cuda.synchronize()
-            graph, st = torch.cuda.CUDAGraph(), torch.cuda.Stream(device=td)
-            with torch.cuda.stream(st):
-                with torch.cuda.graph(graph, stream=st):
-                    for _ in range(4):
-                        for ws in sets:
-                            dev.gemv(xb, ws, **kw)
-                graph.replay()
-                torch.cuda.synchronize()
-                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                a.record(st); graph.replay(); b.record(st)
-                torch.cuda.synchronize()
-            us = a.elapsed_time(b) / (4 * nset) * 1e3
-            nbytes = rows * K * 2 * (2 if dual else 1)
-            res[name] = {"us": round(us, 2), "gbs": round(nbytes / us / 1e3, 1)}
-            del sets
-            torch.cuda.empty_cache()
-        out["c4_contractions_b16"] = res
+        for w4 in (False, True):
+            for B in (1, 16):
+                sub = {}
+                for name, rows, K, dual, mb in (("qkv_3072x2048", 3072, 2048, False, 12.6), ("o_2048x2048", 2048, 2048, False, 8.4),
+                                                ("gate_up_2x8192x2048", 8192, 2048, True, 67.1), ("down_2048x8192", 2048, 8192, False, 33.6),
+                                                ("lm_head_128256x2048", 128256, 2048, False, 525.3)):
+                    if not any(o in "c4_contractions_" + ("int4_g64" if w4 else "bf16") + f"_b{B}_" + name for o in pick):
+                        continue
+                    per_set = mb * (0.28125 if w4 else 1.0)                  # int4 g64: 0.5 + 2/64 bytes per weight against 2
+                    nset = max(2, min(16, int(300.0 / per_set) + 1))         # at least 300 MB in rotation
+                    n_mat = 2 if dual else 1
+                    if w4:
+                        sets = [([torch.randint(0, 256, (rows, K // 2), device=td, generator=g, dtype=torch.uint8) for _ in range(n_mat)],
+                                 [(0.002 + 0.001 * torch.rand(rows, K // 64, device=td, generator=g)).to(torch.bfloat16) for _ in range(n_mat)])
+                                for _ in range(nset)]
+                    else:
+                        sets = [([(0.02 * torch.randn(rows, K, device=td, generator=g)).to(torch.bfloat16) for _ in range(n_mat)], None)
+                                for _ in range(nset)]
+                    xb = torch.randn(B, K, device=td, generator=g).to(torch.bfloat16)
+                    kw = dict(epilogue=abi.EPI_SILU_MUL) if dual else {}
+                    for ws, sc in sets:
+                        dev.gemv(xb, ws, scales=sc, **kw)
+                    torch.cuda.synchronize()
+                    graph, st = torch.cuda.CUDAGraph(), torch.cuda.Stream(device=td)
+                    with torch.cuda.stream(st):
+                        with torch.cuda.graph(graph, stream=st):
+                            for _ in range(4):
+                                for ws, sc in sets:
+                                    dev.gemv(xb, ws, scales=sc, **kw)
+                        graph.replay()
+                        torch.cuda.synchronize()
+                        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                        a.record(st); graph.replay(); b.record(st)
+                        torch.cuda.synchronize()
+                    us = a.elapsed_time(b) / (4 * nset) * 1e3
+                    nbytes = n_mat * rows * (K // 2 + K // 64 * 2 if w4 else K * 2)
+                    sub[name] = {"us": round(us, 2), "gbs": round(nbytes / us / 1e3, 1), "frac_of_hbm_peak": round(nbytes / us / 1e3 / hbm_peak, 3)}
+                    del sets, graph
+                    torch.cuda.empty_cache()
+                if sub:
+                    res[("int4_g64" if w4 else "bf16") + f"_b{B}"] = sub
+        out["c4_contractions"] = res
     # config 4: Llama-3.2-1B-architecture decode step, ctx 1024 (+32 steps), CUDA-graph replays
     cfg = dict(llama.LLAMA_3_2_1B)
     if c4_layers:       # a shallower stack of the same layers (small cases for profiling)

@@ -79,7 +79,10 @@ __host__ __device__ inline Geom geom_of(bool w4, bool dual, int K) {
     g.n_stages = K / g.stage_k;
     g.rows = dual ? 32 : 16;
     g.row_bytes = w4 ? g.stage_k / 2 : g.stage_k * 2;
-    g.pitch = g.row_bytes + (w4 ? 32 : 64);      // rows land 4 bank groups apart: conflict-free fragment reads
+    // rows land 4 bank groups apart: conflict-free fragment reads. An int4 stage that holds whole rows is dense instead: the 16
+    // rows of a tile are then one contiguous piece of the matrix and arrive as ONE bulk copy (a 1 KB copy per row and a
+    // 64-byte one per scale row kept the copy engine, not HBM, busy); the fragment reads pay bank conflicts for it.
+    g.pitch = g.row_bytes + (w4 ? (g.n_stages == 1 ? 0 : 32) : 64);
     g.scale_off = g.rows * g.pitch;
     g.scale_row_bytes = (w4 && g.stage_k >= 512) ? g.stage_k / 64 * 2 : 0;   // 0: too short for a bulk copy, read from global
     return g;
@@ -425,6 +428,7 @@ __device__ __forceinline__ bool produce_phase(const Phase& P, const Ring& ring, 
         const bool w4 = P.variant & 1, dual = (P.variant & 4) != 0;
         const Geom G = geom_of(w4, dual, P.K);
         const size_t full_row = w4 ? (size_t)P.K / 2 : (size_t)P.K * 2;
+        const bool contiguous = w4 && G.n_stages == 1 && P.epilogue != SANIC_EPI_ROPE_CACHE;
         // The norm weight of an inlined RMSNorm is read once per step: cold in L2 by the time its phase starts
         // (gigabytes have streamed through since) and on the consumers' critical path. The producers reach the phase
         // a ring's depth early: ask L2 for it now.
@@ -454,7 +458,15 @@ __device__ __forceinline__ bool produce_phase(const Phase& P, const Ring& ring, 
                     if (ok) mbar_expect_tx(&s_full[slot], (uint32_t)(G.rows * (G.row_bytes + G.scale_row_bytes)));
                 }
                 ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-                if (ok && lane < G.rows) {
+                if (contiguous) {
+                    // whole rows, 16 consecutive ones per matrix: one copy of the weights and one of the scales per matrix
+                    if (ok && lane < G.rows && (lane & 15) == 0) {
+                        bulk_load(ring.base + slot * SLOTB + lane * G.pitch, src_row, (uint32_t)(16 * G.row_bytes), &s_full[slot]);
+                        if (G.scale_row_bytes)
+                            bulk_load(ring.base + slot * SLOTB + G.scale_off + lane * G.scale_row_bytes, src_scale,
+                                      (uint32_t)(16 * G.scale_row_bytes), &s_full[slot]);
+                    }
+                } else if (ok && lane < G.rows) {
                     bulk_load(ring.base + slot * SLOTB + lane * G.pitch, src_row + (size_t)s * G.row_bytes, (uint32_t)G.row_bytes, &s_full[slot]);
                     if (G.scale_row_bytes)
                         bulk_load(ring.base + slot * SLOTB + G.scale_off + lane * G.scale_row_bytes,

@@ -36,8 +36,11 @@ namespace {
 using namespace sanic;
 using namespace sanic::gemv;
 
-template <bool W4, int NT, bool DUAL, bool NORM>
-__global__ void __launch_bounds__(GW * 32, 2) gemv_mma_kernel(const uint16_t* __restrict__ x, int batch, int K,
+// MINB: resident blocks per SM the register allocation is held to. A block is one 16-row tile, every warp's part of it a
+// single batch of loads, so what hides the loads' latency is the number of resident blocks: three (80 registers) take the
+// int4 lm_head from 81 to 68 us at batch 1; the short contractions lose with fewer registers (3.5 -> 4.2 us) and keep two.
+template <bool W4, int NT, bool DUAL, bool NORM, int MINB = 2>
+__global__ void __launch_bounds__(GW * 32, MINB) gemv_mma_kernel(const uint16_t* __restrict__ x, int batch, int K,
                                                            SegTable segs, int n_segments, int out_dtype, int epilogue,
                                                            const float* residual, Fused fz, int KS) {
     __shared__ float scratch[scratch_floats<NT, DUAL>()];
@@ -60,8 +63,13 @@ int32_t launch(sanic_ctx* ctx, const sanic_gemv_params& p, const SegTable& segs,
     if (pdl) { attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization; attr[na].val.programmaticStreamSerializationAllowed = 1; ++na; }
     if (KS > 1) { attr[na].id = cudaLaunchAttributeClusterDimension; attr[na].val.clusterDim.x = KS; attr[na].val.clusterDim.y = 1; attr[na].val.clusterDim.z = 1; ++na; }
     cfg.attrs = attr; cfg.numAttrs = na;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, gemv_mma_kernel<W4, NT, DUAL, NORM>, (const uint16_t*)p.x, p.batch, p.K, segs,
-                                       p.n_segments, p.out_dtype, p.epilogue, p.residual, fz, KS);
+    cudaError_t e;
+    if (W4 && NT == 1 && !DUAL && !NORM && KS == 1 && p.K <= 2048 && tiles >= 8 * ctx->sm_count)
+        e = cudaLaunchKernelEx(&cfg, gemv_mma_kernel<W4, NT, DUAL, NORM, (W4 && NT == 1 && !DUAL && !NORM) ? 3 : 2>, (const uint16_t*)p.x, p.batch,
+                               p.K, segs, p.n_segments, p.out_dtype, p.epilogue, p.residual, fz, KS);
+    else
+        e = cudaLaunchKernelEx(&cfg, gemv_mma_kernel<W4, NT, DUAL, NORM>, (const uint16_t*)p.x, p.batch, p.K, segs,
+                               p.n_segments, p.out_dtype, p.epilogue, p.residual, fz, KS);
     if (e != cudaSuccess) return sanic_fail(ctx, SANIC_ERR_CUDA, std::string("gemv: ") + cudaGetErrorString(e));
     return SANIC_OK;
 }
