@@ -619,6 +619,26 @@ def test_flash_fwd_many_items_equals_single_round_calls(dev, mode):
             assert torch.equal(small[0], big[b, hk * grp:(hk + 1) * grp]), (b, hk)
 
 
+@pytest.mark.parametrize("mode", ["plain", "causal", "window"])
+def test_flash_fwd_running_maximum_rises_across_key_tiles(dev, mode):
+    # Keys grow with their position, so a row's maximum rises by more than 2^8 from one key tile to the next: every later
+    # tile moves the row's reference, which is the case in which the half of the exponentials taken against the old
+    # reference is redone and O and l are rescaled (with i.i.d. scores only an item's first key tile sets a reference).
+    B, Hq, Hkv, L = 1, 4, 2, 640
+    q, qv = bf16t(normal(311, B, Hq, L, 64), dev)
+    ramp = (1.0 + np.arange(L) / 32.0)[None, None, :, None]
+    k, kv = bf16t(normal(312, B, Hkv, L, 64) * ramp, dev)
+    v, vv = bf16t(normal(313, B, Hkv, L, 64), dev)
+    if mode == "plain":
+        exp, got = orc.sdpa(qv, kv, vv, enable_gqa=True), dev.attn_fwd_bf16(q, k, v)
+    elif mode == "causal":
+        exp, got = orc.sdpa(qv, kv, vv, is_causal=True, enable_gqa=True), dev.attn_fwd_bf16(q, k, v, causal=True)
+    else:
+        exp, got = orc.sdpa_window(qv, kv, vv, 300), dev.attn_fwd_bf16(q, k, v, causal=True, window=300)
+    dev.sync()
+    assert nerr(got.float().cpu().numpy(), exp) <= BF16_TOL
+
+
 def test_flash_fwd_profile_counts_clocks_and_computes(dev):
     """The profile entry point runs the same fold with clock counters on in CTA 0: the output is bit for bit the plain
     call's, and the counters are those of a run (CTA 0's item is the last query block: 5 and 6 key tiles)."""
