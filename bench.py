@@ -628,7 +628,8 @@ def main():
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-suite", action="store_true")
     ap.add_argument("--quick", action="store_true", help="shorter prefill in the suite")
-    ap.add_argument("--only", default="", help="comma-separated substrings of suite entries to run (c1,c2,c3,c4_bf16_b1,...)")
+    ap.add_argument("--only", default="", help="comma-separated substrings of suite entries to run (c1,c2,c3,c4_bf16_b1,...); entries outside the default suite "
+                         "run only when named: c2_profile, c3_profile, c4_contractions[_<weights>_b<batch>[_<name>]]")
     ap.add_argument("--c2-shape", default="4096,2048,8192", help="M,K,N of the suite's GEMM (small cases for profiling)")
     ap.add_argument("--llama-unfused", action="store_true", help="one stage per graph cone in the decode step")
     ap.add_argument("--exchange", default="auto", choices=["auto", "nccl", "peer", "fused"], help="how N > 1 ranks exchange their accumulators")
