@@ -407,7 +407,8 @@ def suite(dev, torch, hbm_peak, tf_peak, quick, only=None, c2_shape=(4096, 2048,
             out[f"c4_phase_profile_{name}"] = [[round(t * 1e6, 2) for t in ph] for ph in prof]
         out[f"c4_llama_decode_{name}"] = {
             "tok_per_s": batch / sec, "ms_per_step": sec * 1e3, "launches_per_step": m.kernel_count,
-            "form": "one cooperative kernel" if persistent else "captured launch list", "deferred_norm": bool(deferred),
+            "form": ("one cooperative kernel" if m.kernel_count == 1 else "one cooperative kernel, then the vocabulary contraction and the token choice as launches")
+                    if persistent else "captured launch list", "deferred_norm": bool(deferred),
             "algorithmic_bytes": wb + kv_bytes, "achieved_gbs": (wb + kv_bytes) / sec / 1e9,
             "frac_of_hbm_peak": (wb + kv_bytes) / sec / 1e9 / hbm_peak}
         del m, w

@@ -25,4 +25,12 @@ void destroy(Plan* plan);
 int32_t gemv_ring(sanic_ctx* ctx, const sanic_gemv_params* p, cudaStream_t stream);
 
 }  // namespace step
+
+namespace gemv {
+// Whether sanic_gemv serves this contraction with the warp-per-tile int4 kernel (gemv.cu: int4-g64 weights, batch <= 8, one
+// matrix of many row tiles, plain store): a program captured in its single-kernel form leaves such a stage, and what
+// follows it, to the launch list, because that kernel streams a vocabulary-sized matrix more than twice as fast as the
+// step kernel's eight consumer warps do.
+bool rows_form_applies(const sanic_ctx* ctx, const sanic_gemv_params& p);
+}  // namespace gemv
 }  // namespace sanic

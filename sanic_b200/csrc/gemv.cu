@@ -47,10 +47,158 @@ __global__ void __launch_bounds__(GW * 32, MINB) gemv_mma_kernel(const uint16_t*
     gemv_tile<W4, NT, DUAL, NORM>(x, batch, K, segs, n_segments, out_dtype, epilogue, residual, fz, KS, (int)blockIdx.x, true, scratch);
 }
 
+// int4-g64 weights, batch <= 8, one matrix with many row tiles and a plain store (the lm_head): a WARP owns whole 16-row
+// tiles. With a block per tile and the K axis split over its warps, a warp's share of a tile is one batch of loads and
+// every tile pays a block barrier and a cross-warp sum; here a warp walks the K axis of its tile four groups at a time with
+// the next four groups' loads (a 8-byte weight load per row and group: the four lanes of a row read one 32-byte sector; one
+// 8-byte load of four scales per row) in flight under the arithmetic, accumulates alone and stores its 16 rows itself.
+// What depends on the activations only is taken once per block: they are staged in shared memory as bf16 (norm applied),
+// already in the order of the MMA's B fragments (the byte permutes that pair activations like the nibbles are paired), and
+// the zero point's term, 136 x the sum of a group's activations, is kept per group (the four MMAs against ones that the
+// tile-per-block form issues for every tile and group).
+constexpr int WR_U = 4;
+template <bool NORM, int NT>
+__global__ void __launch_bounds__(GW * 32, 2) gemv_w4_rows_kernel(const uint16_t* __restrict__ x, int batch, int K, SegTable segs, int out_dtype,
+                                                                 Fused fz, int tiles) {
+    extern __shared__ __align__(16) unsigned char wr_smem[];
+    float* scratch = (float*)wr_smem;                                 // row norms or deferred scales: 16 + 16 * GW floats
+    const int G = K / 64, xpitch = K * 2 + 16;                        // rows 4 banks apart: conflict-free 16-byte reads by a quarter warp
+    float2* gsum = (float2*)(wr_smem + 1024);                         // [K / 64][NT][4]: sums of columns 2t, 2t+1 (+ 8 per half) per group
+    unsigned char* xs = wr_smem + 1024 + G * NT * 32;                 // [8 * NT][xpitch]: per group and lane quarter t, the 8 B-fragment registers
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+    griddep_launch();
+    griddep_wait();
+    if (NORM) row_norms<false>(fz, batch, K, scratch);
+    else if (fz.ds_partial) defer_scales<false>(fz, batch, scratch);        // the outputs' scale per batch row (deferred normaliser)
+    for (int i = tid; i < batch * (K / 16); i += GW * 32) {
+        const int n = i / (K / 16), c = i % (K / 16);     // c = 4 * group + t: 16 activations
+        const uint16_t* xr = NORM ? nullptr : x + (size_t)n * K;
+        const float* xf = NORM ? fz.norm_x + (size_t)n * K : nullptr;
+        const uint4 xa = load_x8<NORM, false>(xr, xf, fz.norm_gamma, NORM ? scratch[n] : 1.0f, c * 16, true);
+        const uint4 xc = load_x8<NORM, false>(xr, xf, fz.norm_gamma, NORM ? scratch[n] : 1.0f, c * 16 + 8, true);
+        // activation pairs matching the nibble pairing (n_i, n_{i+4})
+        uint4* dst = (uint4*)(xs + (size_t)n * xpitch + c * 32);
+        dst[0] = make_uint4(prmt(xa.x, xa.z, 0x5410), prmt(xa.x, xa.z, 0x7632), prmt(xa.y, xa.w, 0x5410), prmt(xa.y, xa.w, 0x7632));
+        dst[1] = make_uint4(prmt(xc.x, xc.z, 0x5410), prmt(xc.x, xc.z, 0x7632), prmt(xc.y, xc.w, 0x5410), prmt(xc.y, xc.w, 0x7632));
+    }
+    __syncthreads();
+    bool xok[NT];
+    const unsigned char* xrow[NT];
+#pragma unroll
+    for (int j = 0; j < NT; ++j) {
+        xok[j] = 8 * j + g < batch;
+        xrow[j] = xs + (size_t)(xok[j] ? 8 * j + g : 0) * xpitch + t * 32;
+    }
+    // the B fragments of group u for batch columns 8j .. 8j+7
+    auto x_frags = [&](int u, int j, uint32_t (&b)[8]) {
+        const uint4 lo = xok[j] ? *(const uint4*)(xrow[j] + (size_t)u * 128) : make_uint4(0, 0, 0, 0);
+        const uint4 hi = xok[j] ? *(const uint4*)(xrow[j] + (size_t)u * 128 + 16) : make_uint4(0, 0, 0, 0);
+        b[0] = lo.x; b[1] = lo.y; b[2] = lo.z; b[3] = lo.w; b[4] = hi.x; b[5] = hi.y; b[6] = hi.z; b[7] = hi.w;
+    };
+    {
+        const uint32_t ONES = 0x3F803F80u;
+        for (int u = warp; u < G; u += GW) {
+#pragma unroll
+            for (int j = 0; j < NT; ++j) {
+                uint32_t b[8];
+                x_frags(u, j, b);
+                float c1[4] = {0, 0, 0, 0};
+                mma_bf16_16816(c1, ONES, ONES, ONES, ONES, b[0], b[1]);
+                mma_bf16_16816(c1, ONES, ONES, ONES, ONES, b[2], b[3]);
+                mma_bf16_16816(c1, ONES, ONES, ONES, ONES, b[4], b[5]);
+                mma_bf16_16816(c1, ONES, ONES, ONES, ONES, b[6], b[7]);
+                if (g == 0) gsum[(u * NT + j) * 4 + t] = make_float2(c1[0], c1[1]);       // every row of c1 is the same
+            }
+        }
+    }
+    __syncthreads();
+    const uint8_t* W = (const uint8_t*)segs.w[0];
+    const uint16_t* S = segs.scales[0];
+    const int rows = segs.rows[0];
+    const bool scaled = !NORM && fz.ds_partial != nullptr;
+    for (int tile = blockIdx.x * GW + warp; tile < tiles; tile += gridDim.x * GW) {
+        const uint8_t* w0 = W + (size_t)(tile * 16 + g) * (K / 2) + t * 8;
+        const uint8_t* w1 = w0 + (size_t)8 * (K / 2);
+        const uint16_t* s0 = S + (size_t)(tile * 16 + g) * G;
+        const uint16_t* s1 = s0 + (size_t)8 * G;
+        float acc[NT][4];
+#pragma unroll
+        for (int j = 0; j < NT; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.0f;
+        uint2 wa[WR_U][2], sa[2];
+#pragma unroll
+        for (int u = 0; u < WR_U; ++u) { wa[u][0] = ldg_stream8(w0 + u * 32); wa[u][1] = ldg_stream8(w1 + u * 32); }
+        sa[0] = ldg_stream8(s0); sa[1] = ldg_stream8(s1);
+        for (int blk = 0; blk < G; blk += WR_U) {
+            uint2 wn[WR_U][2], sn[2];
+            const bool more = blk + WR_U < G;
+            if (more) {
+#pragma unroll
+                for (int u = 0; u < WR_U; ++u) {
+                    wn[u][0] = ldg_stream8(w0 + (size_t)(blk + WR_U + u) * 32);
+                    wn[u][1] = ldg_stream8(w1 + (size_t)(blk + WR_U + u) * 32);
+                }
+                sn[0] = ldg_stream8(s0 + blk + WR_U); sn[1] = ldg_stream8(s1 + blk + WR_U);
+            }
+#pragma unroll
+            for (int u = 0; u < WR_U; ++u) {
+                const uint32_t sw0 = (u < 2) ? sa[0].x : sa[0].y, sw1 = (u < 2) ? sa[1].x : sa[1].y;
+                const float sc0 = (u & 1) ? bf16hi(sw0) : bf16lo(sw0), sc1 = (u & 1) ? bf16hi(sw1) : bf16lo(sw1);
+                const uint32_t a0 = wa[u][0].x, a1 = wa[u][0].y, c0 = wa[u][1].x, c1w = wa[u][1].y;
+                const uint32_t f0 = nib_pair(a0), f1 = nib_pair(c0), f2 = nib_pair(a0 >> 4), f3 = nib_pair(c0 >> 4);
+                const uint32_t f4 = nib_pair(a0 >> 8), f5 = nib_pair(c0 >> 8), f6 = nib_pair(a0 >> 12), f7 = nib_pair(c0 >> 12);
+                const uint32_t h0 = nib_pair(a1), h1 = nib_pair(c1w), h2 = nib_pair(a1 >> 4), h3 = nib_pair(c1w >> 4);
+                const uint32_t h4 = nib_pair(a1 >> 8), h5 = nib_pair(c1w >> 8), h6 = nib_pair(a1 >> 12), h7 = nib_pair(c1w >> 12);
+#pragma unroll
+                for (int j = 0; j < NT; ++j) {
+                    uint32_t b[8];
+                    x_frags(blk + u, j, b);
+                    const float2 cs = gsum[((blk + u) * NT + j) * 4 + t];
+                    float c[4] = {0, 0, 0, 0};
+                    mma_bf16_16816(c, f0, f1, f2, f3, b[0], b[1]);
+                    mma_bf16_16816(c, f4, f5, f6, f7, b[2], b[3]);
+                    mma_bf16_16816(c, h0, h1, h2, h3, b[4], b[5]);
+                    mma_bf16_16816(c, h4, h5, h6, h7, b[6], b[7]);
+                    acc[j][0] = fmaf(sc0, fmaf(-136.0f, cs.x, c[0]), acc[j][0]);
+                    acc[j][1] = fmaf(sc0, fmaf(-136.0f, cs.y, c[1]), acc[j][1]);
+                    acc[j][2] = fmaf(sc1, fmaf(-136.0f, cs.x, c[2]), acc[j][2]);
+                    acc[j][3] = fmaf(sc1, fmaf(-136.0f, cs.y, c[3]), acc[j][3]);
+                }
+            }
+            if (more) {
+#pragma unroll
+                for (int u = 0; u < WR_U; ++u) { wa[u][0] = wn[u][0]; wa[u][1] = wn[u][1]; }
+                sa[0] = sn[0]; sa[1] = sn[1];
+            }
+        }
+        // C fragment: rows g and g+8 of the tile, batch columns 8j + 2t and 8j + 2t + 1
+#pragma unroll
+        for (int j = 0; j < NT; ++j)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int n = 8 * j + 2 * t + (i & 1), row = tile * 16 + g + (i >> 1) * 8;
+                if (n < batch) {
+                    const size_t oi = (size_t)n * rows + row;
+                    const float y = scaled ? acc[j][i] * scratch[n] : acc[j][i];
+                    if (out_dtype == SANIC_BF16) ((uint16_t*)segs.out[0])[oi] = f32_to_bf16_bits(y);
+                    else ((float*)segs.out[0])[oi] = y;
+                }
+            }
+    }
+}
+
 template <bool W4, int NT, bool DUAL, bool NORM>
 int32_t launch(sanic_ctx* ctx, const sanic_gemv_params& p, const SegTable& segs, const Fused& fz, int tiles, cudaStream_t st) {
     // Few row tiles cannot fill 148 SMs: split K over a cluster of KS CTAs per tile (each warp keeps
     // at least one 64-block of K).
+    if (W4 && !DUAL && rows_form_applies(ctx, p)) {
+        const size_t smem = 1024 + (size_t)(p.K / 64) * NT * 32 + (size_t)8 * NT * (p.K * 2 + 16);
+        auto kern = gemv_w4_rows_kernel<NORM, NT>;
+        SANIC_CUDA_CHECK(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        const int blocks = std::min((tiles + GW - 1) / GW, 2 * ctx->sm_count);
+        cudaError_t e = launch_pdl(kern, dim3(blocks), dim3(GW * 32), smem, st, (const uint16_t*)p.x, p.batch, p.K, segs, p.out_dtype, fz, tiles);
+        if (e != cudaSuccess) return sanic_fail(ctx, SANIC_ERR_CUDA, std::string("gemv (int4 rows): ") + cudaGetErrorString(e));
+        return SANIC_OK;
+    }
     int KS = 1;
     const int nblk = p.K / 64;
     static const int ks_cap = getenv("SANIC_GEMV_KS") ? atoi(getenv("SANIC_GEMV_KS")) : 1;   // tuning knob: measured no gain on B200 at decode shapes, so off by default
@@ -79,6 +227,12 @@ int32_t launch_n(sanic_ctx* ctx, const sanic_gemv_params& p, const SegTable& seg
 }
 }  // namespace
 
+bool sanic::gemv::rows_form_applies(const sanic_ctx* ctx, const sanic_gemv_params& p) {
+    return p.weight_dtype == SANIC_I4 && p.n_segments == 1 && p.epilogue == SANIC_EPI_STORE && !(p.ds_partial && p.norm_x) &&
+           p.K % 256 == 0 && p.K <= (p.batch > 8 ? 2048 : 4096) && p.rows[0] % 16 == 0 && p.rows[0] / 16 >= 16 * ctx->sm_count &&
+           !(getenv("SANIC_GEMV_W4_ROWS") && getenv("SANIC_GEMV_W4_ROWS")[0] == '0');
+}
+
 extern "C" int32_t sanic_gemv(sanic_ctx* ctx, const sanic_gemv_params* p, void* stream) {
     if (!ctx || !p) return SANIC_ERR_INVALID;
     SegTable segs;
@@ -94,7 +248,7 @@ extern "C" int32_t sanic_gemv(sanic_ctx* ctx, const sanic_gemv_params* p, void* 
     // batch > 8: the contraction fed through a shared-memory ring by bulk copies keeps twice the bytes in flight
     // (SANIC_GEMV_RING=0 keeps the register-staged kernel, for A/B timing)
     static const bool ring = !(getenv("SANIC_GEMV_RING") && getenv("SANIC_GEMV_RING")[0] == '0');
-    if (wide && ring && !p->norm_x) {
+    if (wide && ring && !p->norm_x && !rows_form_applies(ctx, *p)) {
         rc = sanic::step::gemv_ring(ctx, p, st);
         if (rc != SANIC_ERR_UNSUPPORTED) return rc;
     }

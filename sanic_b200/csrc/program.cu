@@ -156,8 +156,18 @@ static int32_t capture_impl(sanic_program* p, void* stream, bool want_persistent
     if (p->exec) { cudaGraphExecDestroy(p->exec); p->exec = nullptr; }
     if (p->graph) { cudaGraphDestroy(p->graph); p->graph = nullptr; }
     if (p->plan) { sanic::step::destroy(p->plan); p->plan = nullptr; }
+    // The tail of a decode step is a contraction over the whole vocabulary and the token choice. Where sanic_gemv has a faster
+    // stand-alone kernel for that contraction than the step kernel's phase (int4 weights at small batch), the cooperative
+    // kernel ends in front of it and the tail stays a launch list behind it.
+    size_t split = p->stages.size();
     if (want_persistent) {
-        int32_t brc = sanic::step::build(ctx, p->stages, &p->plan);
+        for (size_t i = p->stages.size(); i-- > 1;) {
+            if (p->stages[i].op != SANIC_OP_GEMV) continue;
+            if (sanic::gemv::rows_form_applies(ctx, p->stages[i].u.gemv)) split = i;
+            break;
+        }
+        const std::vector<sanic_stage_desc> head(p->stages.begin(), p->stages.begin() + split);
+        int32_t brc = sanic::step::build(ctx, head, &p->plan);
         if (brc != SANIC_OK) return brc == SANIC_ERR_UNSUPPORTED
                                         ? sanic_fail(ctx, brc, "program_capture_persistent: a stage of this list has no phase in the persistent kernel")
                                         : brc;
@@ -165,6 +175,10 @@ static int32_t capture_impl(sanic_program* p, void* stream, bool want_persistent
     SANIC_CUDA_CHECK(ctx, cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal));
     int32_t rc = p->plan ? sanic::step::launch(ctx, p->plan, st) : sanic_program_run(p, stream);
     p->step_kernels = p->plan ? 1 : p->kernels;
+    for (size_t i = split; p->plan && rc == SANIC_OK && i < p->stages.size(); ++i) {
+        rc = run_stage(ctx, p->stages[i], stream);
+        p->step_kernels += kernels_of(p->stages[i]);
+    }
     cudaGraph_t g = nullptr;
     cudaError_t e = cudaStreamEndCapture(st, &g);
     if (rc != SANIC_OK) { if (g) cudaGraphDestroy(g); return rc; }

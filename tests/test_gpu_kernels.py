@@ -296,6 +296,42 @@ def test_gemv_w4(dev, batch, K, rows):
     assert nerr(got, exp) <= 2e-4
 
 
+@pytest.mark.parametrize("batch,K,norm", [(1, 2048, False), (5, 2048, False), (8, 512, False), (3, 2048, True), (12, 2048, False),
+                                          (16, 1024, False)])
+def test_gemv_w4_many_row_tiles_warp_per_tile(dev, batch, K, norm):
+    # An int4 matrix with at least 16 row tiles per SM takes the warp-per-tile kernel (8 or 16 batch columns). Sampled rows (first and
+    # last tiles among them) against the oracle; the whole output against the tile-per-block kernel, which sums the same
+    # products in another order; bf16 output is the f32 one rounded.
+    import os
+    rows = 16 * 2400
+    gen = torch.Generator(device=dev.torch_device); gen.manual_seed(400 + batch)
+    pt = torch.randint(0, 256, (rows, K // 2), device=dev.torch_device, generator=gen, dtype=torch.uint8)
+    st = (0.004 * (1.0 + 0.25 * torch.rand(rows, K // 64, device=dev.torch_device, generator=gen))).to(torch.bfloat16)
+    if norm:
+        x = orc.round_to(orc.DT_F32, normal(401, batch, K) * 3.0)
+        g, gv = bf16t(1.0 + 0.1 * normal(402, K), dev)
+        xin, kw = f32t(x, dev), dict(norm_gamma=g)
+        xv = orc.round_to(orc.DT_BF16, orc.rms_norm(x, gv))
+    else:
+        xin, xv = bf16t(normal(401, batch, K), dev)
+        kw = {}
+    got = dev.gemv(xin, [pt], scales=[st], **kw)
+    got16 = dev.gemv(xin, [pt], scales=[st], out_dtype=torch.bfloat16, **kw)
+    os.environ["SANIC_GEMV_W4_ROWS"] = "0"
+    try:
+        old = dev.gemv(xin, [pt], scales=[st], **kw)
+    finally:
+        del os.environ["SANIC_GEMV_W4_ROWS"]
+    dev.sync()
+    assert nerr(got.cpu().numpy(), old.cpu().numpy()) <= 1e-5
+    assert torch.equal(got16, got.to(torch.bfloat16))
+    pick = np.concatenate([np.arange(0, 32), np.arange(rows // 2 - 8, rows // 2 + 24), np.arange(rows - 32, rows)])
+    packed = pt[torch.tensor(pick, device=dev.torch_device)].cpu().numpy().reshape(-1)
+    sv = st[torch.tensor(pick, device=dev.torch_device)].float().cpu().numpy().astype(np.float64)
+    exp = orc.w4_gemv(packed, sv, xv, len(pick), group=64)
+    assert nerr(got.cpu().numpy()[:, pick], exp) <= (5e-4 if norm else 2e-4)
+
+
 def test_w4_unpack_is_bit_exact(dev):
     q, packed, pt, _, _ = _w4(64, 512, 77, dev)
     got = dev.w4_unpack(pt.reshape(-1), q.size).cpu().numpy()
