@@ -378,8 +378,9 @@ def suite(dev, torch, hbm_peak, tf_peak, quick, only=None, c2_shape=(4096, 2048,
         if not want("c4_" + name):
             continue
         w = llama.random_weights(cfg, 11, td, w4=w4)
-        # the step as one cooperative kernel wins at small batch, the captured launch list at batch 16 (measured)
-        persistent = fused and (form == "persistent" or (form == "auto" and batch <= 4))
+        # the step as one cooperative kernel wins at small batch with bf16 weights (0.858 against 0.872 ms at batch 1), the
+        # captured launch list at batch 16 and with int4 weights (batch 1: 0.710 against 0.776 ms) (measured)
+        persistent = fused and (form == "persistent" or (form == "auto" and batch <= 4 and not w4))
         # SANIC_LLAMA_DEFERRED_NORM=0/1 forces the deferred normaliser off / on (A/B timing); default: the machine's choice
         force = os.environ.get("SANIC_LLAMA_DEFERRED_NORM")
         m = llama.LlamaMachine(dev, cfg, w, ctx=1088, batch=batch, w4=w4, fused=fused, persistent=persistent,

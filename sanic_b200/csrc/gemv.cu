@@ -186,6 +186,164 @@ __global__ void __launch_bounds__(GW * 32, 2) gemv_w4_rows_kernel(const uint16_t
     }
 }
 
+// int4-g64 silu(gate) * up at K <= 2048: a TEAM of four warps per dual tile (16 rows of each matrix), a quarter of the K axis
+// each. The layers' matrices have too few tiles for a warp per tile (512 dual tiles for 8192 rows) and too little work per tile
+// for a block per tile; with four warps per tile every resident warp has one tile's quarter, all of its loads in flight at
+// once (GPW groups x 2 matrices x 2 rows of 8 bytes). The three other warps hand their sums to the first through shared
+// memory at a barrier of the four; it adds them in a fixed order, scales, applies silu * up and stores.
+__device__ __forceinline__ void team_sync(int team) {      // the four warps of a team; a barrier of its own per team
+    if (team == 0) asm volatile("bar.sync 1, 128;" ::: "memory");
+    else asm volatile("bar.sync 2, 128;" ::: "memory");
+}
+template <bool NORM, int NT, int GPW>
+__global__ void __launch_bounds__(GW * 32, 2) gemv_w4_dual_team_kernel(const uint16_t* __restrict__ x, int batch, int K, SegTable segs, int out_dtype,
+                                                                      Fused fz, int tiles) {
+    extern __shared__ __align__(16) unsigned char wr_smem[];
+    float* scratch = (float*)wr_smem;
+    const int G = K / 64, xpitch = K * 2 + 16;
+    float2* gsum = (float2*)(wr_smem + 1024);
+    unsigned char* xs = wr_smem + 1024 + G * NT * 32;
+    float4* comb = (float4*)(xs + 8 * NT * xpitch);       // [2 teams][3 warps][32 lanes][2 * NT]
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+    griddep_launch();
+    griddep_wait();
+    if (NORM) row_norms<false>(fz, batch, K, scratch);
+    else if (fz.ds_partial) defer_scales<false>(fz, batch, scratch);
+    for (int i = tid; i < batch * (K / 16); i += GW * 32) {
+        const int n = i / (K / 16), c = i % (K / 16);
+        const uint16_t* xr = NORM ? nullptr : x + (size_t)n * K;
+        const float* xf = NORM ? fz.norm_x + (size_t)n * K : nullptr;
+        const uint4 xa = load_x8<NORM, false>(xr, xf, fz.norm_gamma, NORM ? scratch[n] : 1.0f, c * 16, true);
+        const uint4 xc = load_x8<NORM, false>(xr, xf, fz.norm_gamma, NORM ? scratch[n] : 1.0f, c * 16 + 8, true);
+        uint4* dst = (uint4*)(xs + (size_t)n * xpitch + c * 32);
+        dst[0] = make_uint4(prmt(xa.x, xa.z, 0x5410), prmt(xa.x, xa.z, 0x7632), prmt(xa.y, xa.w, 0x5410), prmt(xa.y, xa.w, 0x7632));
+        dst[1] = make_uint4(prmt(xc.x, xc.z, 0x5410), prmt(xc.x, xc.z, 0x7632), prmt(xc.y, xc.w, 0x5410), prmt(xc.y, xc.w, 0x7632));
+    }
+    __syncthreads();
+    bool xok[NT];
+    const unsigned char* xrow[NT];
+#pragma unroll
+    for (int j = 0; j < NT; ++j) {
+        xok[j] = 8 * j + g < batch;
+        xrow[j] = xs + (size_t)(xok[j] ? 8 * j + g : 0) * xpitch + t * 32;
+    }
+    auto x_frags = [&](int u, int j, uint32_t (&b)[8]) {
+        const uint4 lo = xok[j] ? *(const uint4*)(xrow[j] + (size_t)u * 128) : make_uint4(0, 0, 0, 0);
+        const uint4 hi = xok[j] ? *(const uint4*)(xrow[j] + (size_t)u * 128 + 16) : make_uint4(0, 0, 0, 0);
+        b[0] = lo.x; b[1] = lo.y; b[2] = lo.z; b[3] = lo.w; b[4] = hi.x; b[5] = hi.y; b[6] = hi.z; b[7] = hi.w;
+    };
+    {
+        const uint32_t ONES = 0x3F803F80u;
+        for (int u = warp; u < G; u += GW) {
+#pragma unroll
+            for (int j = 0; j < NT; ++j) {
+                uint32_t b[8];
+                x_frags(u, j, b);
+                float c1[4] = {0, 0, 0, 0};
+                mma_bf16_16816(c1, ONES, ONES, ONES, ONES, b[0], b[1]);
+                mma_bf16_16816(c1, ONES, ONES, ONES, ONES, b[2], b[3]);
+                mma_bf16_16816(c1, ONES, ONES, ONES, ONES, b[4], b[5]);
+                mma_bf16_16816(c1, ONES, ONES, ONES, ONES, b[6], b[7]);
+                if (g == 0) gsum[(u * NT + j) * 4 + t] = make_float2(c1[0], c1[1]);
+            }
+        }
+    }
+    __syncthreads();
+    const int rows = segs.rows[0];
+    const bool scaled = !NORM && fz.ds_partial != nullptr;
+    const int team = warp >> 2, sub = warp & 3, g0 = sub * GPW;
+    for (int tile = blockIdx.x * 2 + team; tile < tiles; tile += gridDim.x * 2) {
+        // every load of this warp's quarter of the tile: GPW groups of rows g and g+8 of both matrices, and their scales
+        uint2 wv[2][2][GPW];
+        uint32_t sv[2][2][GPW / 2];
+#pragma unroll
+        for (int mI = 0; mI < 2; ++mI) {
+            const uint8_t* Wm = (const uint8_t*)segs.w[mI];
+            const uint16_t* Sm = segs.scales[mI];
+#pragma unroll
+            for (int r = 0; r < 2; ++r) {
+                const size_t wrow = (size_t)(tile * 16 + g + 8 * r);
+#pragma unroll
+                for (int u = 0; u < GPW; ++u) wv[mI][r][u] = ldg_stream8(Wm + wrow * (K / 2) + (size_t)(g0 + u) * 32 + t * 8);
+#pragma unroll
+                for (int u = 0; u < GPW / 2; ++u) sv[mI][r][u] = __ldg((const uint32_t*)(Sm + wrow * G + g0) + u);
+            }
+        }
+        float acc[2][NT][4];
+#pragma unroll
+        for (int mI = 0; mI < 2; ++mI)
+#pragma unroll
+            for (int j = 0; j < NT; ++j) acc[mI][j][0] = acc[mI][j][1] = acc[mI][j][2] = acc[mI][j][3] = 0.0f;
+#pragma unroll
+        for (int u = 0; u < GPW; ++u) {
+            uint32_t b[NT][8];
+            float2 cs[NT];
+#pragma unroll
+            for (int j = 0; j < NT; ++j) { x_frags(g0 + u, j, b[j]); cs[j] = gsum[((g0 + u) * NT + j) * 4 + t]; }
+#pragma unroll
+            for (int mI = 0; mI < 2; ++mI) {
+                const uint32_t a0 = wv[mI][0][u].x, a1 = wv[mI][0][u].y, c0 = wv[mI][1][u].x, c1w = wv[mI][1][u].y;
+                const uint32_t s0w = sv[mI][0][u >> 1], s1w = sv[mI][1][u >> 1];
+                const float sc0 = (u & 1) ? bf16hi(s0w) : bf16lo(s0w), sc1 = (u & 1) ? bf16hi(s1w) : bf16lo(s1w);
+                const uint32_t f0 = nib_pair(a0), f1 = nib_pair(c0), f2 = nib_pair(a0 >> 4), f3 = nib_pair(c0 >> 4);
+                const uint32_t f4 = nib_pair(a0 >> 8), f5 = nib_pair(c0 >> 8), f6 = nib_pair(a0 >> 12), f7 = nib_pair(c0 >> 12);
+                const uint32_t h0 = nib_pair(a1), h1 = nib_pair(c1w), h2 = nib_pair(a1 >> 4), h3 = nib_pair(c1w >> 4);
+                const uint32_t h4 = nib_pair(a1 >> 8), h5 = nib_pair(c1w >> 8), h6 = nib_pair(a1 >> 12), h7 = nib_pair(c1w >> 12);
+#pragma unroll
+                for (int j = 0; j < NT; ++j) {
+                    float c[4] = {0, 0, 0, 0};
+                    mma_bf16_16816(c, f0, f1, f2, f3, b[j][0], b[j][1]);
+                    mma_bf16_16816(c, f4, f5, f6, f7, b[j][2], b[j][3]);
+                    mma_bf16_16816(c, h0, h1, h2, h3, b[j][4], b[j][5]);
+                    mma_bf16_16816(c, h4, h5, h6, h7, b[j][6], b[j][7]);
+                    acc[mI][j][0] = fmaf(sc0, fmaf(-136.0f, cs[j].x, c[0]), acc[mI][j][0]);
+                    acc[mI][j][1] = fmaf(sc0, fmaf(-136.0f, cs[j].y, c[1]), acc[mI][j][1]);
+                    acc[mI][j][2] = fmaf(sc1, fmaf(-136.0f, cs[j].x, c[2]), acc[mI][j][2]);
+                    acc[mI][j][3] = fmaf(sc1, fmaf(-136.0f, cs[j].y, c[3]), acc[mI][j][3]);
+                }
+            }
+        }
+        // the other three warps' sums to the first, in the order of their K quarters
+        float4* mine = comb + ((size_t)(team * 3 + (sub - 1)) * 32 + lane) * (2 * NT);
+        if (sub != 0) {
+#pragma unroll
+            for (int mI = 0; mI < 2; ++mI)
+#pragma unroll
+                for (int j = 0; j < NT; ++j) mine[mI * NT + j] = make_float4(acc[mI][j][0], acc[mI][j][1], acc[mI][j][2], acc[mI][j][3]);
+        }
+        team_sync(team);
+        if (sub == 0) {
+#pragma unroll
+            for (int w = 0; w < 3; ++w) {
+                const float4* theirs = comb + ((size_t)(team * 3 + w) * 32 + lane) * (2 * NT);
+#pragma unroll
+                for (int mI = 0; mI < 2; ++mI)
+#pragma unroll
+                    for (int j = 0; j < NT; ++j) {
+                        const float4 o = theirs[mI * NT + j];
+                        acc[mI][j][0] += o.x; acc[mI][j][1] += o.y; acc[mI][j][2] += o.z; acc[mI][j][3] += o.w;
+                    }
+            }
+#pragma unroll
+            for (int j = 0; j < NT; ++j)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int n = 8 * j + 2 * t + (i & 1), row = tile * 16 + g + (i >> 1) * 8;
+                    if (n < batch) {
+                        const float sc = scaled ? scratch[n] : 1.0f;
+                        const float ga = acc[0][j][i] * sc, up = acc[1][j][i] * sc;
+                        const float sig = 1.0f / (1.0f + expf(-ga));       // silu(a) * b = (a * 1/(1+exp(-a))) * b  (reference src/ir.rs:1500-1509)
+                        const float y = (ga * sig) * up;
+                        const size_t oi = (size_t)n * rows + row;
+                        if (out_dtype == SANIC_BF16) ((uint16_t*)segs.out[0])[oi] = f32_to_bf16_bits(y);
+                        else ((float*)segs.out[0])[oi] = y;
+                    }
+                }
+        }
+        team_sync(team);      // the hand-over places are free again
+    }
+}
+
 template <bool W4, int NT, bool DUAL, bool NORM>
 int32_t launch(sanic_ctx* ctx, const sanic_gemv_params& p, const SegTable& segs, const Fused& fz, int tiles, cudaStream_t st) {
     // Few row tiles cannot fill 148 SMs: split K over a cluster of KS CTAs per tile (each warp keeps
@@ -197,6 +355,25 @@ int32_t launch(sanic_ctx* ctx, const sanic_gemv_params& p, const SegTable& segs,
         const int blocks = std::min((tiles + GW - 1) / GW, 2 * ctx->sm_count);
         cudaError_t e = launch_pdl(kern, dim3(blocks), dim3(GW * 32), smem, st, (const uint16_t*)p.x, p.batch, p.K, segs, p.out_dtype, fz, tiles);
         if (e != cudaSuccess) return sanic_fail(ctx, SANIC_ERR_CUDA, std::string("gemv (int4 rows): ") + cudaGetErrorString(e));
+        return SANIC_OK;
+    }
+    // (at batch > 8 the contraction is bound by instruction issue in either form: 13.5 us against the ring-fed kernel's 14.2 stand-alone,
+    // and slower inside a step, where the ring-fed kernel's start overlaps its predecessor's end; so only up to batch 8)
+    if (W4 && DUAL && NT == 1 && (p.K == 2048 || p.K == 1024) && p.rows[0] % 16 == 0 && tiles >= ctx->sm_count &&
+        !(getenv("SANIC_GEMV_W4_ROWS") && getenv("SANIC_GEMV_W4_ROWS")[0] == '0')) {
+        const size_t smem = 1024 + (size_t)(p.K / 64) * NT * 32 + (size_t)8 * NT * (p.K * 2 + 16) + (size_t)2 * 3 * 32 * 2 * NT * sizeof(float4);
+        const int blocks = std::min((tiles + 1) / 2, 2 * ctx->sm_count);
+        cudaError_t e;
+        if (p.K == 2048) {
+            auto kern = gemv_w4_dual_team_kernel<NORM, NT, 8>;
+            SANIC_CUDA_CHECK(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            e = launch_pdl(kern, dim3(blocks), dim3(GW * 32), smem, st, (const uint16_t*)p.x, p.batch, p.K, segs, p.out_dtype, fz, tiles);
+        } else {
+            auto kern = gemv_w4_dual_team_kernel<NORM, NT, 4>;
+            SANIC_CUDA_CHECK(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            e = launch_pdl(kern, dim3(blocks), dim3(GW * 32), smem, st, (const uint16_t*)p.x, p.batch, p.K, segs, p.out_dtype, fz, tiles);
+        }
+        if (e != cudaSuccess) return sanic_fail(ctx, SANIC_ERR_CUDA, std::string("gemv (int4 silu-mul teams): ") + cudaGetErrorString(e));
         return SANIC_OK;
     }
     int KS = 1;

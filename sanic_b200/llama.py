@@ -114,12 +114,14 @@ class LlamaMachine:
         # deferred normaliser (fused stage lists only): every RMSNorm whose input a residual-add produces is split into
         # what that epilogue can do (multiply by gamma, per-tile sums of squares) and one multiply in the next contraction's
         # epilogue; stored(bf16) then sits on x * gamma (the defer-div carrier of the reference's laws) instead of on the
-        # normalised value. Layer 0's attention norm, fed by the gather, is unchanged. Default: on where the norm would
-        # otherwise be a launch of its own (the launch list at batch > 4: 86 launches per step instead of 118, 1.10 against
-        # 1.23 ms at batch 16); the single-kernel step keeps the norm inlined into its staging pass, which measured faster
-        # there (0.875 against 0.935 ms: the scale's loads would sit in front of the staging loads).
+        # normalised value. Layer 0's attention norm, fed by the gather, is unchanged. Default: on for the launch list (at
+        # batch > 4 the norm would otherwise be a launch of its own: 86 launches per step instead of 118, 1.10 against 1.23 ms
+        # at batch 16; at batch 1, where it would be inlined into the contractions' activation loads, 0.872 against 0.945 ms
+        # with bf16 weights and 0.710 against 0.738 with int4); the single-kernel step keeps the norm inlined into its
+        # staging pass, which measured faster there (0.875 against 0.935 ms: the scale's loads would sit in front of the
+        # staging loads).
         if deferred_norm is None:
-            deferred_norm = fused and not persistent and batch > 4
+            deferred_norm = fused and not persistent
         self.deferred_norm = bool(deferred_norm and fused)
         H, Hq, Hkv, D = cfg["hidden"], cfg["q_heads"], cfg["kv_heads"], cfg["head_dim"]
         if H != Hq * D or Hq % Hkv or D not in (64, 128):

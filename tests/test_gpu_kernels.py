@@ -332,6 +332,41 @@ def test_gemv_w4_many_row_tiles_warp_per_tile(dev, batch, K, norm):
     assert nerr(got.cpu().numpy()[:, pick], exp) <= (5e-4 if norm else 2e-4)
 
 
+@pytest.mark.parametrize("batch,K,norm", [(1, 2048, False), (5, 1024, False), (8, 2048, False), (2, 2048, True)])
+def test_gemv_w4_silu_mul_team_per_tile(dev, batch, K, norm):
+    # silu(gate x) * (up x) with int4 matrices of at least one dual tile per SM takes, up to batch 8, the kernel with a team of
+    # four warps per tile. The whole output against the tile-per-block (or ring-fed) form; sampled rows against the oracle.
+    import os
+    from sanic_b200 import abi
+    rows = 16 * 256
+    gen = torch.Generator(device=dev.torch_device); gen.manual_seed(500 + batch)
+    pts = [torch.randint(0, 256, (rows, K // 2), device=dev.torch_device, generator=gen, dtype=torch.uint8) for _ in range(2)]
+    sts = [(0.004 * (1.0 + 0.25 * torch.rand(rows, K // 64, device=dev.torch_device, generator=gen))).to(torch.bfloat16) for _ in range(2)]
+    if norm:
+        x = orc.round_to(orc.DT_F32, normal(501, batch, K) * 3.0)
+        g, gv = bf16t(1.0 + 0.1 * normal(502, K), dev)
+        xin, kw = f32t(x, dev), dict(norm_gamma=g)
+        xv = orc.round_to(orc.DT_BF16, orc.rms_norm(x, gv))
+    else:
+        xin, xv = bf16t(normal(501, batch, K), dev)
+        kw = {}
+    got = dev.gemv(xin, pts, scales=sts, epilogue=abi.EPI_SILU_MUL, **kw)
+    os.environ["SANIC_GEMV_W4_ROWS"] = "0"
+    try:
+        old = dev.gemv(xin, pts, scales=sts, epilogue=abi.EPI_SILU_MUL, **kw)
+    finally:
+        del os.environ["SANIC_GEMV_W4_ROWS"]
+    dev.sync()
+    assert got.shape == (batch, rows)
+    assert nerr(got.cpu().numpy(), old.cpu().numpy()) <= 2e-5
+    pick = np.concatenate([np.arange(0, 32), np.arange(rows // 2 - 8, rows // 2 + 24), np.arange(rows - 32, rows)])
+    idx = torch.tensor(pick, device=dev.torch_device)
+    ab = [orc.w4_gemv(pt[idx].cpu().numpy().reshape(-1), st[idx].float().cpu().numpy().astype(np.float64), xv, len(pick), group=64)
+          for pt, st in zip(pts, sts)]
+    exp = ab[0] / (1.0 + np.exp(-ab[0])) * ab[1]
+    assert nerr(got.cpu().numpy()[:, pick], exp) <= (1e-3 if norm else 4e-4)
+
+
 def test_w4_unpack_is_bit_exact(dev):
     q, packed, pt, _, _ = _w4(64, 512, 77, dev)
     got = dev.w4_unpack(pt.reshape(-1), q.size).cpu().numpy()
