@@ -378,9 +378,9 @@ def suite(dev, torch, hbm_peak, tf_peak, quick, only=None, c2_shape=(4096, 2048,
         if not want("c4_" + name):
             continue
         w = llama.random_weights(cfg, 11, td, w4=w4)
-        # the step as one cooperative kernel wins at small batch with bf16 weights (0.858 against 0.872 ms at batch 1), the
-        # captured launch list at batch 16 and with int4 weights (batch 1: 0.710 against 0.776 ms) (measured)
-        persistent = fused and (form == "persistent" or (form == "auto" and batch <= 4 and not w4))
+        # the captured launch list measures faster than the step as one cooperative kernel in all four cases (batch 1: 0.810
+        # against 0.858 ms with bf16 weights, 0.657 against 0.776 with int4; batch 16: 1.02 against 1.91 ms)
+        persistent = fused and form == "persistent"
         # SANIC_LLAMA_DEFERRED_NORM=0/1 forces the deferred normaliser off / on (A/B timing); default: the machine's choice
         force = os.environ.get("SANIC_LLAMA_DEFERRED_NORM")
         m = llama.LlamaMachine(dev, cfg, w, ctx=1088, batch=batch, w4=w4, fused=fused, persistent=persistent,

@@ -378,7 +378,11 @@ int32_t launch(sanic_ctx* ctx, const sanic_gemv_params& p, const SegTable& segs,
     }
     int KS = 1;
     const int nblk = p.K / 64;
-    static const int ks_cap = getenv("SANIC_GEMV_KS") ? atoi(getenv("SANIC_GEMV_KS")) : 1;   // tuning knob: measured no gain on B200 at decode shapes, so off by default
+    // SANIC_GEMV_KS caps the split (tuning knob). Default: two CTAs per tile for a long K axis with at most one tile per SM
+    // (the down projection: 2048 x 8192, four passes of loads per warp; int4 at batch 1 9.8 -> 7.1 us). The short-K
+    // contractions lose with it (q/k/v with the RoPE epilogue 3.6 -> 6.9 us), and four CTAs per tile lose everywhere.
+    static const int ks_env = getenv("SANIC_GEMV_KS") ? atoi(getenv("SANIC_GEMV_KS")) : 0;
+    const int ks_cap = ks_env > 0 ? ks_env : ((p.K >= 4096 && tiles <= ctx->sm_count && (p.epilogue == SANIC_EPI_STORE || p.epilogue == SANIC_EPI_RESIDUAL_ADD)) ? 2 : 1);
     while (KS < ks_cap && tiles * KS < 2 * ctx->sm_count && nblk / (KS * 2) >= GW) KS *= 2;
     static const bool pdl = (getenv("SANIC_NO_PDL") == nullptr);
     cudaLaunchConfig_t cfg = {};
