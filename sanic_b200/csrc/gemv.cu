@@ -17,9 +17,15 @@
 //
 // Work split: one CTA = 16 output rows (x 2 matrices for the silu(a)*b pair), its 8
 // warps take contiguous K ranges and are summed in a fixed order through shared memory.
-// When there are too few row tiles to fill the SMs, a thread-block cluster of 2-8 CTAs
-// shares a tile, splits K, and rank 0 adds the peers' sums in rank order through
-// distributed shared memory. Results are deterministic.
+// A thread-block cluster of 2-8 CTAs can share a tile, split K, and have rank 0 add the
+// peers' sums in rank order through distributed shared memory; two CTAs per tile are the
+// default for a K axis of 4096 or more with at most one tile per SM (the down projection).
+// Results are deterministic. Three other forms take the shapes this split serves badly:
+//   * batch 9-16: gemv_ring_kernel (decode_step.cu), weights through a shared-memory ring;
+//   * one int4 matrix of at least 16 row tiles per SM with a plain store (the lm_head):
+//     gemv_w4_rows_kernel below, a warp per 16-row tile;
+//   * int4 silu(a)*b at K <= 2048 up to batch 8: gemv_w4_dual_team_kernel below, four warps
+//     per dual tile.
 //
 // Fusions that remove launches from a decode step:
 //   * NORM: the producer cone of the activations (RMSNorm of the f32 residual stream) is
